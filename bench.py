@@ -1,0 +1,322 @@
+#!/usr/bin/env python
+"""MoE-layer throughput benchmark.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--tokens T] [--impl reference]
+
+One "step" is one pass of the whole MoE block (router -> routed NVFP4 experts -> shared expert ->
+combine) over one batch of synthetic tokens.  At N = 1 the workload is the decode configuration
+(T = 64 tokens, hidden 2048, 256 resident NVFP4 experts, top-8, one bf16 shared expert).  The step
+cycles through several independently seeded layers and batches so that successive steps touch
+different expert bytes (a layer's banks are 455 MB, larger than the 126 MB L2).
+
+Rank 0 prints ONE JSON line.  `value` is tokens/s with inputs resident in HBM, timed with CUDA
+events; `e2e` is the same metric through the public call with HOST buffers (pinned host x copied in,
+the block run, the result copied out, every step, inside the timed region); `roofline` is the
+dominant kernel's algorithmic bytes over its own CUDA-event time (per-kernel profile pass);
+`cpu_baseline` is the CPU restatement of the reference's host path timed on this box's cores.
+
+--impl reference times the reference's CPU algorithm (the C restatement under oracle/: the Rust
+reference cannot be compiled in this image) on the same workload, bounded to a sample per step.
+"""
+from __future__ import annotations
+
+import argparse
+import importlib
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+HIDDEN, INTER, EXPERTS, TOP_K, SHARED = 2048, 512, 256, 8, 512
+EXPERT_BYTES = 1775616                      # six bank rows of one expert
+GATE_UP_BYTES = 1048576 + 131072 + 2048     # packed + scales + globals of gate_up
+DOWN_BYTES = 524288 + 65536 + 4096
+METRIC = "moe_layer_tokens_per_s"
+UNIT = "tokens/s"
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=40)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--tokens", type=int, default=0, help="tokens per step (default: 64 at N=1)")
+    ap.add_argument("--layers", type=int, default=4, help="independent layers cycled through")
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--sweep", action="store_true", help="also report T = 1, 8, 512, 2048")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "which": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "which": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except Exception:
+                continue
+            for name, col in (("hw_slowdown", 5), ("hw_thermal_slowdown", 6), ("sw_thermal_slowdown", 7),
+                              ("sw_power_cap", 8)):
+                if len(r) > col and r[col].lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------ CPU reference arm / baseline
+
+def host_layer_for_cpu(seed: int):
+    pkg = importlib.import_module("ferrum-torrens_b200")
+    from oracle import oracle as o
+    lay = pkg.synth.make_layer(seed)
+    banks = o.HostBanks(*lay.banks, slots=EXPERTS, gu_rows=2 * INTER, gu_cols=HIDDEN, dn_rows=HIDDEN, dn_cols=INTER)
+    ol = o.Layer(HIDDEN, INTER, EXPERTS, TOP_K, SHARED, lay.gate_w, lay.sh_gate_up, lay.sh_down, lay.sh_gate, banks)
+    return pkg, o, lay, ol
+
+
+def time_cpu(tokens_sample: int, steps: int, warmup: int, seed: int = 2024):
+    """tokens/s of the CPU restatement of the reference's host path, all host threads."""
+    pkg, o, lay, ol = host_layer_for_cpu(seed)
+    threads = o.max_threads()
+    times = []
+    for i in range(warmup + steps):
+        x = pkg.synth.bf16_bits_to_f32(pkg.synth.make_x(seed + i, tokens_sample, HIDDEN))
+        t0 = time.perf_counter()
+        o.moe_block(ol, x, threads=threads)
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    return tokens_sample * len(times) / sum(times), threads, sum(times) / len(times)
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    tokens = args.tokens or 64
+    sample = min(tokens, 16)
+    steps, warmup = max(1, min(args.steps, 8)), max(1, min(args.warmup, 2))
+    tps, threads, sec = time_cpu(sample, steps, warmup)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"decode T={tokens}, hidden {HIDDEN}, {EXPERTS} NVFP4 experts top-{TOP_K}, shared {SHARED}",
+                   "sample": f"{sample} tokens per step"},
+        "cpu_baseline": {"value": tps, "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": f"{sample} tokens of the T={tokens} batch per step, whole block, "
+                                   f"{steps} steps; C restatement of the reference's host path (the Rust "
+                                   f"reference cannot be compiled in this image)"},
+        "e2e": {"value": tps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------ B200 arm
+
+def run_b200(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device(f"cuda:{local}")
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    import __graft_entry__ as ge
+    if rank == 0:
+        ge.build()
+    if world > 1:
+        dist.barrier()
+    pkg = importlib.import_module("ferrum-torrens_b200")
+
+    T = args.tokens or 64
+    nlayers = max(1, args.layers)
+    moe = pkg.B200MoE(local, pkg.ExpertShapes(HIDDEN, INTER), EXPERTS * nlayers, experts=EXPERTS, layers=nlayers,
+                      top_k=TOP_K, shared_inter=SHARED, max_tokens=max(T, 64))
+    dense, xs = [], []
+    for l in range(nlayers):
+        pkg.synth.fill_banks_on_device(moe, l, seed=1000 + 17 * rank + l, slot0=l * EXPERTS)
+        dense.append(pkg.synth.device_dense_weights(2000 + 17 * rank + l, dev))
+        xs.append(pkg.synth.device_x(3000 + 17 * rank + l, T, HIDDEN, dev))
+    out = torch.empty((T, HIDDEN), dtype=torch.bfloat16, device=dev)
+    ids = torch.empty((T, TOP_K), dtype=torch.int32, device=dev)
+    wts = torch.empty((T, TOP_K), dtype=torch.float32, device=dev)
+
+    def step(i, x=None):
+        l = i % nlayers
+        g, su, sd, sg = dense[l]
+        moe.moe_block(l, xs[l] if x is None else x, g, su, sd, sg, out, ids_out=ids, weights_out=wts)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, warmup):
+        for i in range(warmup):
+            fn(i)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            fn(warmup + i)
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    W, K = max(3, args.warmup), max(1, args.steps)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    l0 = moe.kernel_launches()
+    total_ms = timed(step, K, W)
+    launches = (moe.kernel_launches() - l0) * K // (K + W)
+    clocks = sampler.stop() if rank == 0 else None
+    value = world * T * K / (total_ms * 1e-3)
+
+    # end to end: pinned host x in, block, result out, every step
+    x_host = [x.cpu().pin_memory() for x in xs]
+    x_stage = torch.empty_like(xs[0])
+    out_host = torch.empty((T, HIDDEN), dtype=torch.bfloat16).pin_memory()
+
+    def step_e2e(i):
+        x_stage.copy_(x_host[i % nlayers], non_blocking=True)
+        step(i, x_stage)
+        out_host.copy_(out, non_blocking=True)
+
+    e2e_ms = timed(step_e2e, K, W)
+    e2e = {"value": world * T * K / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": T * HIDDEN * 2,
+           "d2h_bytes_per_step": T * HIDDEN * 2}
+
+    # per-kernel profile pass (CUDA events around every launch) for the roofline of the dominant kernel
+    moe.profile(True)
+    uniq = []
+    for i in range(K):
+        step(W + i)
+        if i < nlayers:
+            torch.cuda.synchronize()
+            uniq.append(int(torch.unique(ids).numel()))
+    prof = moe.profile_read()
+    moe.profile(False)
+    U = sum(uniq) / len(uniq)
+    pk = peaks()
+    gate_kind = "expert_gate_up" if "expert_gate_up" in prof else "grouped_gate_up"
+    g_ms, g_n = prof[gate_kind]
+    gu_bytes = U * GATE_UP_BYTES + T * HIDDEN * 2
+    achieved = gu_bytes / (g_ms / g_n * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "kernel": gate_kind, "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                "frac": achieved / pk["hbm_gbs"], "peak_source": pk["which"], "frac_of_nominal_8000": achieved / 8000.0,
+                "traffic": None, "distinct_experts": U, "bytes_per_launch": gu_bytes,
+                "us_per_launch": g_ms / g_n * 1e3,
+                "kernels": {k: {"us_per_launch": ms / n * 1e3, "launches": n} for k, (ms, n) in prof.items()}}
+    if "expert_down" in prof:
+        d_ms, d_n = prof["expert_down"]
+        dn = (U * DOWN_BYTES) / (d_ms / d_n * 1e-3) / 1e9
+        roofline["down"] = {"achieved": dn, "frac": dn / pk["hbm_gbs"]}
+        both = (U * EXPERT_BYTES) / ((g_ms / g_n + d_ms / d_n) * 1e-3) / 1e9
+        roofline["expert_weights_gbs"] = both
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": total_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16 activations x NVFP4 (e2m1 + e4m3 block scales) weights, f32 accumulate", "data": "synthetic",
+        "config": {"workload": f"decode T={T} tokens/step, hidden {HIDDEN}, {EXPERTS} resident NVFP4 experts top-{TOP_K}, "
+                               f"bf16 shared expert {SHARED}",
+                   "l2": f"inputs larger than L2: {nlayers} independently seeded layers "
+                         f"({nlayers * EXPERTS * EXPERT_BYTES / 1e6:.0f} MB of banks) cycled step by step",
+                   "timed_region": "whole block (router, routed experts, shared expert, combine), CUDA events"},
+        "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline, "clocks": clocks,
+    }
+
+    if args.sweep and world == 1:
+        sweep = {}
+        for t in (1, 8, 512, 2048):
+            if t > moe.max_tokens:
+                continue
+            xt = [pkg.synth.device_x(4000 + l, t, HIDDEN, dev) for l in range(nlayers)]
+            o2 = torch.empty((t, HIDDEN), dtype=torch.bfloat16, device=dev)
+
+            def st(i, t=t, xt=xt, o2=o2):
+                l = i % nlayers
+                g, su, sd, sg = dense[l]
+                moe.moe_block(l, xt[l], g, su, sd, sg, o2)
+            ms = timed(st, K, W)
+            sweep[f"T={t}"] = {"tokens_per_s": t * K / (ms * 1e-3), "us_per_step": ms / K * 1e3}
+        line["sweep"] = sweep
+
+    if rank == 0 and not args.no_cpu_baseline:
+        sample = min(T, 16)
+        tps, threads, sec = time_cpu(sample, 3, 1)
+        line["cpu_baseline"] = {"value": tps, "unit": UNIT, "cores": threads, "kind": "port",
+                                "sample": f"{sample} tokens of the same block per step, 3 steps, all host threads; "
+                                          f"C restatement of the reference's host path"}
+    if rank == 0:
+        print(json.dumps(line))
+    moe.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

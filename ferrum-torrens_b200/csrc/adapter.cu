@@ -1,0 +1,750 @@
+// The device MoE adapter behind the C ABI of include/ftmoe.h.
+//
+// It plays the role of the reference's `CudaMoE` (src/infrastructure/cuda_moe.rs:145-195): it owns
+// the six expert banks (slot-major, stable addresses for the adapter's life), the residency table,
+// the per-step scratch, and it launches the kernels.  With every expert resident in HBM the
+// reference's host-offload slot cache collapses to an identity indirection, which is kept: routes
+// name slots, a slot of -1 contributes nothing, and the dense expert ids of the serving call are
+// mapped to slots on the device.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/ftmoe.h"
+#include "expert_cache.hpp"
+#include "kernels.cuh"
+
+using namespace ftm;
+
+namespace {
+
+thread_local std::string g_create_error;
+
+const char* const kKindNames[K_NUM_KINDS] = {
+    "router_logits", "router_topk", "slot_rewrite", "csr_build", "expert_gate_up", "expert_down", "sum_routes",
+    "shared_phase1", "shared_phase2", "cast_bf16",   "combine",  "grouped_gate_up", "grouped_down"};
+
+}  // namespace
+
+// CUDA-event timing of every kernel launch while enabled (the counterpart of the reference's
+// FT_PROFILE stage timer, src/infrastructure/profile.rs:1-14).  Off by default: no events.
+struct ftm::Profiler {
+    struct Rec {
+        int kind;
+        cudaEvent_t a, b;
+    };
+    bool on = false;
+    std::vector<Rec> recs;
+    std::vector<cudaEvent_t> pool;
+    double total_ms[K_NUM_KINDS] = {};
+    uint64_t count[K_NUM_KINDS] = {};
+    cudaEvent_t get() {
+        if (!pool.empty()) {
+            cudaEvent_t e = pool.back();
+            pool.pop_back();
+            return e;
+        }
+        cudaEvent_t e = nullptr;
+        cudaEventCreate(&e);
+        return e;
+    }
+    void drain() {  // caller has synchronised the streams
+        for (auto& r : recs) {
+            float ms = 0.f;
+            if (cudaEventElapsedTime(&ms, r.a, r.b) == cudaSuccess) {
+                total_ms[r.kind] += ms;
+                count[r.kind]++;
+            }
+            pool.push_back(r.a);
+            pool.push_back(r.b);
+        }
+        recs.clear();
+    }
+    ~Profiler() {
+        for (auto& r : recs) {
+            cudaEventDestroy(r.a);
+            cudaEventDestroy(r.b);
+        }
+        for (auto e : pool) cudaEventDestroy(e);
+    }
+};
+
+void ftm::Ctx::begin(int kind) const {
+    if (!prof || !prof->on) return;
+    Profiler::Rec r{kind, prof->get(), prof->get()};
+    cudaEventRecord(r.a, s);
+    prof->recs.push_back(r);
+}
+
+void ftm::Ctx::end() const {
+    if (!prof || !prof->on || prof->recs.empty()) return;
+    cudaEventRecord(prof->recs.back().b, s);
+}
+
+struct ftm_handle {
+    ftm_config cfg{};
+    cudaStream_t stream = nullptr;
+    cudaStream_t aux = nullptr;  // shared expert runs here, ordered by events
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    mutable std::mutex mu;
+    mutable std::string err;
+
+    size_t row_bytes[FTM_NUM_BANKS]{};
+    void* banks[FTM_NUM_BANKS]{};
+    bool resident = false;
+
+    std::vector<int32_t> slot_for_id;  // host mirror, [layers * experts]
+    std::vector<int32_t> id_of_slot;   // [slots]
+    int32_t* d_slot_for_id = nullptr;
+    std::unique_ptr<ExpertCache> cache;
+
+    // scratch, sized for cfg.max_tokens at creation (the serving call never allocates)
+    __nv_bfloat16* x_bf16 = nullptr;
+    int32_t *route_slot = nullptr, *route_expert = nullptr, *seg = nullptr, *route_idx = nullptr;
+    int32_t *csr_scratch = nullptr, *flags = nullptr, *ids = nullptr;
+    float *ic2 = nullptr, *yroute = nullptr, *logits = nullptr, *rweights = nullptr;
+    float *ic2s = nullptr, *shared_out = nullptr, *se_gate = nullptr, *routed_f32 = nullptr;
+    std::vector<void*> allocs;
+
+    uint64_t steps = 0;
+    uint64_t launches = 0;
+    Profiler prof;
+    Ctx ctx(cudaStream_t s) { return Ctx{s, &prof}; }
+};
+
+namespace {
+
+int fail(const ftm_handle* h, int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    if (h)
+        h->err = buf;
+    else
+        g_create_error = buf;
+    return code;
+}
+
+int cuda_fail(const ftm_handle* h, cudaError_t e, const char* what) {
+    if (e == cudaErrorMemoryAllocation)
+        return fail(h, FTM_ERR_OUT_OF_MEMORY, "moe: out of device memory: %s: out of memory", what);
+    return fail(h, FTM_ERR_CUDA, "moe: driver: %s: %s", what, cudaGetErrorString(e));
+}
+
+#define CU(h, call)                                       \
+    do {                                                  \
+        cudaError_t e__ = (call);                         \
+        if (e__ != cudaSuccess) return cuda_fail(h, e__, #call); \
+    } while (0)
+
+template <typename T>
+int dev_alloc(ftm_handle* h, T** out, size_t count) {
+    void* p = nullptr;
+    size_t bytes = (count ? count : 1) * sizeof(T);
+    cudaError_t e = cudaMalloc(&p, bytes);
+    if (e != cudaSuccess) return cuda_fail(h, e, "cudaMalloc(scratch)");
+    h->allocs.push_back(p);
+    *out = reinterpret_cast<T*>(p);
+    return FTM_OK;
+}
+
+int alloc_banks(ftm_handle* h) {
+    for (int b = 0; b < FTM_NUM_BANKS; b++) {
+        size_t bytes = h->row_bytes[b] * (size_t)h->cfg.slots;
+        cudaError_t e = cudaMalloc(&h->banks[b], bytes);
+        if (e != cudaSuccess) {
+            for (int q = 0; q < b; q++) {
+                cudaFree(h->banks[q]);
+                h->banks[q] = nullptr;
+            }
+            h->banks[b] = nullptr;
+            return cuda_fail(h, e, "cudaMalloc(expert bank)");
+        }
+    }
+    h->resident = true;
+    return FTM_OK;
+}
+
+BankView bank_view(const ftm_handle* h) {
+    BankView v;
+    v.gu_packed = (const uint8_t*)h->banks[0];
+    v.gu_scale = (const uint8_t*)h->banks[1];
+    v.gu_global = (const uint16_t*)h->banks[2];
+    v.dn_packed = (const uint8_t*)h->banks[3];
+    v.dn_scale = (const uint8_t*)h->banks[4];
+    v.dn_global = (const uint16_t*)h->banks[5];
+    v.hidden = h->cfg.hidden;
+    v.inter = h->cfg.inter;
+    v.slots = h->cfg.slots;
+    return v;
+}
+
+void clear_residency(ftm_handle* h) {
+    std::fill(h->slot_for_id.begin(), h->slot_for_id.end(), -1);
+    std::fill(h->id_of_slot.begin(), h->id_of_slot.end(), -1);
+    if (h->cache) h->cache->reset();
+}
+
+cudaStream_t pick(const ftm_handle* h, void* s) { return s ? (cudaStream_t)s : h->stream; }
+
+// the checks of check_batch (src/infrastructure/cuda_moe.rs:959-1003)
+int check_tokens(const ftm_handle* h, int64_t tokens, int top_k) {
+    if (top_k != h->cfg.top_k)
+        return fail(h, FTM_ERR_BAD, "moe: the adapter was built for top_k %d, got %d", h->cfg.top_k, top_k);
+    if (tokens <= 0) return fail(h, FTM_ERR_BAD, "moe: grouped_moe: %lld tokens", (long long)tokens);
+    if (tokens > h->cfg.max_tokens)
+        return fail(h, FTM_ERR_BAD, "moe: %lld tokens exceed the adapter's max_tokens %d", (long long)tokens,
+                    h->cfg.max_tokens);
+    if (!h->resident) return fail(h, FTM_ERR_BAD, "moe: grouped_moe while the expert banks are released");
+    return FTM_OK;
+}
+
+// routed experts over route_slot / weights -> out (routed sum only when shared == nullptr)
+// `join`, when set, is waited on just before the pass that reads `shared`.
+int run_routed(ftm_handle* h, const __nv_bfloat16* x, const int32_t* route_slot, const float* weights, int tokens,
+               const float* shared, const float* se_gate, cudaEvent_t join, void* out, int out_dtype, int path,
+               cudaStream_t s) {
+    (void)path;
+    BankView b = bank_view(h);
+    h->launches += launch_decode_routes(b, x, route_slot, weights, tokens, h->cfg.top_k, h->ic2, h->yroute, h->ctx(s));
+    if (join) CU(h, cudaStreamWaitEvent(s, join, 0));
+    h->launches += launch_sum_routes(h->yroute, tokens, h->cfg.top_k, h->cfg.hidden, shared, se_gate, out, out_dtype, h->ctx(s));
+    return FTM_OK;
+}
+
+// activations as bf16: the caller's buffer when it already is, else a cast into scratch
+int stage_x(ftm_handle* h, const void* x, int x_dtype, int tokens, const __nv_bfloat16** out, cudaStream_t s) {
+    if (x_dtype == FTM_BF16) {
+        *out = (const __nv_bfloat16*)x;
+        return FTM_OK;
+    }
+    if (x_dtype != FTM_F32) return fail(h, FTM_ERR_BAD, "moe: activations cannot be dtype %d", x_dtype);
+    h->launches += launch_cast_to_bf16(x, x_dtype, (size_t)tokens * h->cfg.hidden, h->x_bf16, h->ctx(s));
+    *out = h->x_bf16;
+    return FTM_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+FTM_API int ftm_abi_version(void) { return FTM_ABI_VERSION; }
+
+FTM_API const char* ftm_last_error(const ftm_handle* h) { return h ? h->err.c_str() : g_create_error.c_str(); }
+
+FTM_API int ftm_create(const ftm_config* c, void* stream, ftm_handle** out) {
+    if (!c || !out) return fail(nullptr, FTM_ERR_BAD, "moe: null config or output");
+    *out = nullptr;
+    if (c->hidden <= 0 || c->inter <= 0 || c->hidden % 16 || c->inter % 16)
+        return fail(nullptr, FTM_ERR_BAD, "moe: expert shapes hidden %d inter %d must be nonzero multiples of 16",
+                    c->hidden, c->inter);
+    if (c->slots < 1) return fail(nullptr, FTM_ERR_BAD, "moe: the slot cache needs at least one slot");
+    if (c->experts < 1 || c->experts > 512 || c->layers < 1)
+        return fail(nullptr, FTM_ERR_BAD, "moe: experts %d (1..512) layers %d", c->experts, c->layers);
+    if (c->top_k < 1 || c->top_k > 32 || c->top_k > c->experts)
+        return fail(nullptr, FTM_ERR_BAD, "moe: top_k %d for %d experts", c->top_k, c->experts);
+    if (c->max_tokens < 1) return fail(nullptr, FTM_ERR_BAD, "moe: max_tokens %d", c->max_tokens);
+    if (c->shared_inter < 0 || c->shared_inter % 16)
+        return fail(nullptr, FTM_ERR_BAD, "moe: shared_inter %d must be a multiple of 16", c->shared_inter);
+    if (c->ep_size < 1 || c->ep_rank < 0 || c->ep_rank >= c->ep_size)
+        return fail(nullptr, FTM_ERR_BAD, "moe: expert-parallel rank %d of %d", c->ep_rank, c->ep_size);
+    int ndev = 0;
+    cudaError_t e = cudaGetDeviceCount(&ndev);
+    if (e != cudaSuccess || ndev == 0)
+        return fail(nullptr, FTM_ERR_CUDA, "moe: driver: no CUDA device (%s); this library has no CPU path",
+                    cudaGetErrorString(e));
+    if (c->ordinal < 0 || c->ordinal >= ndev)
+        return fail(nullptr, FTM_ERR_BAD, "moe: device ordinal %d of %d", c->ordinal, ndev);
+    e = cudaSetDevice(c->ordinal);
+    if (e != cudaSuccess) return cuda_fail(nullptr, e, "cudaSetDevice");
+
+    std::unique_ptr<ftm_handle> h(new ftm_handle);
+    h->cfg = *c;
+    h->stream = (cudaStream_t)stream;
+    const size_t H = c->hidden, I = c->inter;
+    h->row_bytes[0] = 2 * I * H / 2;
+    h->row_bytes[1] = 2 * I * H / 16;
+    h->row_bytes[2] = 2 * I * 2;
+    h->row_bytes[3] = H * I / 2;
+    h->row_bytes[4] = H * I / 16;
+    h->row_bytes[5] = H * 2;
+    int rc = alloc_banks(h.get());
+    if (rc != FTM_OK) {
+        g_create_error = h->err;
+        return rc;
+    }
+    const size_t n_ids = (size_t)c->layers * c->experts;
+    h->slot_for_id.assign(n_ids, -1);
+    h->id_of_slot.assign(c->slots, -1);
+    h->cache.reset(new ExpertCache(c->layers, c->experts, c->slots));
+
+    const size_t T = c->max_tokens, R = T * c->top_k, SI = c->shared_inter;
+    const int bins = c->experts > c->slots ? c->experts : (c->slots < 1024 ? c->slots : c->experts);
+    ftm_handle* hp = h.get();
+    auto A = [&](int r) {
+        if (r != FTM_OK && rc == FTM_OK) rc = r;
+    };
+    A(dev_alloc(hp, &h->d_slot_for_id, n_ids));
+    A(dev_alloc(hp, &h->x_bf16, T * H));
+    A(dev_alloc(hp, &h->route_slot, R));
+    A(dev_alloc(hp, &h->route_expert, R));
+    A(dev_alloc(hp, &h->seg, (size_t)1024 + 1));
+    A(dev_alloc(hp, &h->route_idx, R));
+    A(dev_alloc(hp, &h->csr_scratch, csr_scratch_ints((int)R, 1024)));
+    A(dev_alloc(hp, &h->flags, 8));
+    A(dev_alloc(hp, &h->ids, R));
+    A(dev_alloc(hp, &h->rweights, R));
+    A(dev_alloc(hp, &h->ic2, R * I));
+    A(dev_alloc(hp, &h->yroute, R * H));
+    A(dev_alloc(hp, &h->logits, T * c->experts));
+    A(dev_alloc(hp, &h->ic2s, T * (SI ? SI : 1)));
+    A(dev_alloc(hp, &h->shared_out, T * H));
+    A(dev_alloc(hp, &h->se_gate, T));
+    A(dev_alloc(hp, &h->routed_f32, T * H));
+    (void)bins;
+    if (rc == FTM_OK) {
+        e = cudaMemset(h->d_slot_for_id, 0xff, n_ids * sizeof(int32_t));
+        if (e == cudaSuccess) e = cudaMemset(h->flags, 0, 8 * sizeof(int32_t));
+        if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&h->aux, cudaStreamNonBlocking);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->ev_fork, cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->ev_join, cudaEventDisableTiming);
+        if (e != cudaSuccess) rc = cuda_fail(hp, e, "adapter setup");
+    }
+    if (rc != FTM_OK) {
+        g_create_error = h->err;
+        ftm_destroy(h.release());
+        return rc;
+    }
+    *out = h.release();
+    return FTM_OK;
+}
+
+FTM_API void ftm_destroy(ftm_handle* h) {
+    if (!h) return;
+    cudaSetDevice(h->cfg.ordinal);
+    cudaDeviceSynchronize();
+    for (void* p : h->allocs) cudaFree(p);
+    for (int b = 0; b < FTM_NUM_BANKS; b++)
+        if (h->banks[b]) cudaFree(h->banks[b]);
+    if (h->aux) cudaStreamDestroy(h->aux);
+    if (h->ev_fork) cudaEventDestroy(h->ev_fork);
+    if (h->ev_join) cudaEventDestroy(h->ev_join);
+    delete h;
+}
+
+// ---- ExpertSlotStore ------------------------------------------------------------------------
+
+static int load_common(ftm_handle* h, int32_t layer, int32_t expert, int32_t slot, const void* const fields[],
+                       const size_t lens[], cudaMemcpyKind kind) {
+    if (!h) return FTM_ERR_BAD;
+    std::lock_guard<std::mutex> lk(h->mu);
+    if (!h->resident) return fail(h, FTM_ERR_BAD, "moe: load while the expert banks are released");
+    if (layer < 0 || layer >= h->cfg.layers || expert < 0 || expert >= h->cfg.experts)
+        return fail(h, FTM_ERR_MISSING, "moe: no expert bank entry L%05d expert %d", layer, expert);
+    if (slot < 0 || slot >= h->cfg.slots)
+        return fail(h, FTM_ERR_SLOT_OUT_OF_RANGE, "moe: slot %d out of range (capacity %d)", slot, h->cfg.slots);
+    if (!fields || !lens) return fail(h, FTM_ERR_BAD, "moe: null expert fields");
+    for (int b = 0; b < FTM_NUM_BANKS; b++) {
+        if (!fields[b]) return fail(h, FTM_ERR_BAD, "moe: expert field %d is null", b);
+        if (lens[b] != h->row_bytes[b])
+            return fail(h, FTM_ERR_BAD, "moe: expert field %d has %zu bytes, the bank row is %zu", b, lens[b],
+                        h->row_bytes[b]);
+    }
+    CU(h, cudaSetDevice(h->cfg.ordinal));
+    for (int b = 0; b < FTM_NUM_BANKS; b++) {
+        uint8_t* dst = (uint8_t*)h->banks[b] + (size_t)slot * h->row_bytes[b];
+        if (fields[b] == dst) continue;  // the bytes were written in place through ftm_bank_ptrs
+        CU(h, cudaMemcpyAsync(dst, fields[b], lens[b], kind, h->stream));
+    }
+    // residency: the slot's previous occupant leaves, the expert's previous slot empties
+    const int32_t id = layer * h->cfg.experts + expert;
+    int32_t old_id = h->id_of_slot[slot];
+    if (old_id >= 0 && old_id != id) {
+        h->slot_for_id[old_id] = -1;
+        CU(h, cudaMemcpyAsync(h->d_slot_for_id + old_id, &h->slot_for_id[old_id], sizeof(int32_t),
+                              cudaMemcpyHostToDevice, h->stream));
+    }
+    int32_t old_slot = h->slot_for_id[id];
+    if (old_slot >= 0 && old_slot != slot) h->id_of_slot[old_slot] = -1;
+    h->id_of_slot[slot] = id;
+    h->slot_for_id[id] = slot;
+    CU(h, cudaMemcpyAsync(h->d_slot_for_id + id, &h->slot_for_id[id], sizeof(int32_t), cudaMemcpyHostToDevice,
+                          h->stream));
+    if (kind == cudaMemcpyHostToDevice) CU(h, cudaStreamSynchronize(h->stream));
+    return FTM_OK;
+}
+
+FTM_API int ftm_load_expert(ftm_handle* h, int32_t layer, int32_t expert, int32_t slot,
+                    const uint8_t* const host_fields[FTM_NUM_BANKS], const size_t lens[FTM_NUM_BANKS]) {
+    return load_common(h, layer, expert, slot, (const void* const*)host_fields, lens, cudaMemcpyHostToDevice);
+}
+
+FTM_API int ftm_load_expert_dev(ftm_handle* h, int32_t layer, int32_t expert, int32_t slot,
+                        const void* const dev_fields[FTM_NUM_BANKS], const size_t lens[FTM_NUM_BANKS]) {
+    int rc = load_common(h, layer, expert, slot, dev_fields, lens, cudaMemcpyDeviceToDevice);
+    // the table entry was copied from host memory that may change: make it land before returning
+    if (rc == FTM_OK) cudaStreamSynchronize(h->stream);
+    return rc;
+}
+
+FTM_API int ftm_slots(const ftm_handle* h) { return h ? h->cfg.slots : 0; }
+
+FTM_API int ftm_release_banks(ftm_handle* h) {
+    if (!h) return FTM_ERR_BAD;
+    std::lock_guard<std::mutex> lk(h->mu);
+    if (!h->resident) return FTM_OK;
+    CU(h, cudaSetDevice(h->cfg.ordinal));
+    CU(h, cudaDeviceSynchronize());
+    for (int b = 0; b < FTM_NUM_BANKS; b++) {
+        CU(h, cudaFree(h->banks[b]));
+        h->banks[b] = nullptr;
+    }
+    h->resident = false;
+    clear_residency(h);
+    CU(h, cudaMemset(h->d_slot_for_id, 0xff, h->slot_for_id.size() * sizeof(int32_t)));
+    return FTM_OK;
+}
+
+FTM_API int ftm_rehydrate_banks(ftm_handle* h) {
+    if (!h) return FTM_ERR_BAD;
+    std::lock_guard<std::mutex> lk(h->mu);
+    if (h->resident) return FTM_OK;
+    CU(h, cudaSetDevice(h->cfg.ordinal));
+    return alloc_banks(h);
+}
+
+FTM_API int ftm_banks_resident(const ftm_handle* h) { return h && h->resident ? 1 : 0; }
+
+FTM_API int ftm_bank_ptrs(const ftm_handle* h, uint64_t out[FTM_NUM_BANKS]) {
+    if (!h || !out) return FTM_ERR_BAD;
+    if (!h->resident) return fail(h, FTM_ERR_BAD, "moe: the expert banks are released");
+    for (int b = 0; b < FTM_NUM_BANKS; b++) out[b] = (uint64_t)(uintptr_t)h->banks[b];
+    return FTM_OK;
+}
+
+FTM_API size_t ftm_bank_row_bytes(const ftm_handle* h, int bank) {
+    return (h && bank >= 0 && bank < FTM_NUM_BANKS) ? h->row_bytes[bank] : 0;
+}
+
+FTM_API int32_t ftm_slot_of(const ftm_handle* h, int32_t layer, int32_t expert) {
+    if (!h || layer < 0 || layer >= h->cfg.layers || expert < 0 || expert >= h->cfg.experts) return -1;
+    std::lock_guard<std::mutex> lk(h->mu);
+    return h->slot_for_id[(size_t)layer * h->cfg.experts + expert];
+}
+
+FTM_API int ftm_ensure_experts(ftm_handle* h, int32_t layer, const uint32_t* routed, size_t n, uint32_t* misses,
+                       uint32_t* write_slots, int32_t* rewrites, size_t* n_miss) {
+    if (!h) return FTM_ERR_BAD;
+    std::lock_guard<std::mutex> lk(h->mu);
+    if (layer < 0 || layer >= h->cfg.layers) return fail(h, FTM_ERR_BAD, "moe: layer %d of %d", layer, h->cfg.layers);
+    if ((n && !routed) || !n_miss) return fail(h, FTM_ERR_BAD, "moe: null routed ids");
+    for (size_t i = 0; i < n; i++)
+        if (routed[i] >= (uint32_t)h->cfg.experts)
+            return fail(h, FTM_ERR_BAD, "moe: routed expert %u of %d", routed[i], h->cfg.experts);
+    ExpertPlan p = h->cache->ensure_experts((size_t)layer, routed, n);
+    *n_miss = p.misses.size();
+    for (size_t i = 0; i < p.misses.size(); i++) {
+        if (misses) misses[i] = p.misses[i];
+        if (write_slots) write_slots[i] = p.write_slots[i];
+    }
+    if (rewrites)
+        for (size_t i = 0; i < n; i++) rewrites[i] = p.rewrites[i];
+    return FTM_OK;
+}
+
+// ---- router ---------------------------------------------------------------------------------
+
+FTM_API int ftm_router_from_logits(ftm_handle* h, const float* logits, int32_t tokens, int32_t* ids_out,
+                           float* weights_out, void* stream) {
+    if (!h) return FTM_ERR_BAD;
+    std::lock_guard<std::mutex> lk(h->mu);
+    if (!logits || !ids_out || !weights_out) return fail(h, FTM_ERR_BAD, "moe: router: null buffer");
+    if (tokens <= 0) return fail(h, FTM_ERR_BAD, "moe: router: %d tokens", tokens);
+    h->launches += launch_router_topk(logits, tokens, h->cfg.experts, h->cfg.top_k, ids_out, weights_out, h->ctx(pick(h, stream)));
+    CU(h, cudaGetLastError());
+    return FTM_OK;
+}
+
+static int router_locked(ftm_handle* h, const void* x, const void* gate_w, int32_t tokens, int32_t* ids_out,
+                         float* weights_out, cudaStream_t s) {
+    if (!x || !gate_w || !ids_out || !weights_out) return fail(h, FTM_ERR_BAD, "moe: router: null buffer");
+    if (tokens <= 0 || tokens > h->cfg.max_tokens)
+        return fail(h, FTM_ERR_BAD, "moe: router: %d tokens (max_tokens %d)", tokens, h->cfg.max_tokens);
+    h->launches += launch_router_logits((const __nv_bfloat16*)x, (const __nv_bfloat16*)gate_w, tokens, h->cfg.experts,
+                                        h->cfg.hidden, h->logits, h->ctx(s));
+    h->launches += launch_router_topk(h->logits, tokens, h->cfg.experts, h->cfg.top_k, ids_out, weights_out, h->ctx(s));
+    CU(h, cudaGetLastError());
+    return FTM_OK;
+}
+
+FTM_API int ftm_router(ftm_handle* h, const void* x_bf16, const void* gate_w_bf16, int32_t tokens, int32_t* ids_out,
+               float* weights_out, void* stream) {
+    if (!h) return FTM_ERR_BAD;
+    std::lock_guard<std::mutex> lk(h->mu);
+    return router_locked(h, x_bf16, gate_w_bf16, tokens, ids_out, weights_out, pick(h, stream));
+}
+
+// ---- permutation ----------------------------------------------------------------------------
+
+FTM_API int ftm_csr_build(ftm_handle* h, const int32_t* route_slot, int32_t routes, int32_t bins, int32_t* seg_out,
+                  int32_t* route_idx_out, void* stream) {
+    if (!h) return FTM_ERR_BAD;
+    std::lock_guard<std::mutex> lk(h->mu);
+    if (!route_slot || !seg_out || !route_idx_out) return fail(h, FTM_ERR_BAD, "moe: csr: null buffer");
+    if (routes <= 0 || (int64_t)routes > (int64_t)h->cfg.max_tokens * h->cfg.top_k)
+        return fail(h, FTM_ERR_BAD, "moe: csr: %d routes (cap %lld)", routes,
+                    (long long)h->cfg.max_tokens * h->cfg.top_k);
+    if (bins < 1 || bins > 1024) return fail(h, FTM_ERR_BAD, "moe: csr: %d bins (1..1024)", bins);
+    cudaStream_t s = pick(h, stream);
+    CU(h, cudaMemsetAsync(h->flags, 0, sizeof(int32_t), s));
+    h->launches += launch_csr_build(route_slot, routes, bins, seg_out, route_idx_out, h->csr_scratch, h->flags, h->ctx(s));
+    CU(h, cudaGetLastError());
+    return FTM_OK;
+}
+
+FTM_API int ftm_csr_bad(ftm_handle* h, void* stream, int32_t* bad_out) {
+    if (!h || !bad_out) return FTM_ERR_BAD;
+    std::lock_guard<std::mutex> lk(h->mu);
+    cudaStream_t s = pick(h, stream);
+    CU(h, cudaMemcpyAsync(bad_out, h->flags, sizeof(int32_t), cudaMemcpyDeviceToHost, s));
+    CU(h, cudaStreamSynchronize(s));
+    return FTM_OK;
+}
+
+// ---- ExpertGemm -----------------------------------------------------------------------------
+
+static int check_host_routes(const ftm_handle* h, const int32_t* routes, size_t n) {
+    for (size_t i = 0; i < n; i++)
+        if (routes[i] >= h->cfg.slots)
+            return fail(h, FTM_ERR_SLOT_OUT_OF_RANGE, "moe: slot %d out of range (capacity %d)", routes[i],
+                        h->cfg.slots);
+    return FTM_OK;
+}
+
+FTM_API int ftm_grouped_moe_host(ftm_handle* h, const float* x, size_t x_len, int32_t top_k, const int32_t* routes,
+                         size_t routes_len, const float* weights, size_t weights_len, float* out, size_t out_len) {
+    if (!h) return FTM_ERR_BAD;
+    std::lock_guard<std::mutex> lk(h->mu);
+    if (!x || !routes || !weights || !out) return fail(h, FTM_ERR_BAD, "moe: grouped_moe: null buffer");
+    const size_t H = h->cfg.hidden;
+    if (x_len == 0 || x_len % H) return fail(h, FTM_ERR_BAD, "moe: grouped_moe: %zu activations for hidden %zu", x_len, H);
+    const size_t tokens = x_len / H;
+    int rc = check_tokens(h, (int64_t)tokens, top_k);
+    if (rc != FTM_OK) return rc;
+    const size_t R = tokens * top_k;
+    if (routes_len != R || weights_len < R)
+        return fail(h, FTM_ERR_BAD, "moe: grouped_moe: %zu routes and %zu weights for %zu tokens x top_k %d",
+                    routes_len, weights_len, tokens, top_k);
+    if (out_len < tokens * H) return fail(h, FTM_ERR_BAD, "moe: grouped_moe: out holds %zu, needs %zu", out_len, tokens * H);
+    if ((rc = check_host_routes(h, routes, R)) != FTM_OK) return rc;
+    CU(h, cudaSetDevice(h->cfg.ordinal));
+    cudaStream_t s = h->stream;
+    // narrow to bf16 on the host, as the reference adapter does before its upload
+    std::vector<uint16_t> xb(x_len);
+    for (size_t i = 0; i < x_len; i++) xb[i] = ftm_f32_to_bf16_bits(x[i]);
+    CU(h, cudaMemcpyAsync(h->x_bf16, xb.data(), x_len * 2, cudaMemcpyHostToDevice, s));
+    CU(h, cudaMemcpyAsync(h->route_slot, routes, R * sizeof(int32_t), cudaMemcpyHostToDevice, s));
+    CU(h, cudaMemcpyAsync(h->rweights, weights, R * sizeof(float), cudaMemcpyHostToDevice, s));
+    rc = run_routed(h, h->x_bf16, h->route_slot, h->rweights, (int)tokens, nullptr, nullptr, nullptr, h->routed_f32,
+                    FTM_F32, FTM_PATH_AUTO, s);
+    if (rc != FTM_OK) return rc;
+    CU(h, cudaGetLastError());
+    CU(h, cudaMemcpyAsync(out, h->routed_f32, tokens * H * sizeof(float), cudaMemcpyDeviceToHost, s));
+    CU(h, cudaStreamSynchronize(s));
+    h->steps++;
+    return FTM_OK;
+}
+
+FTM_API int ftm_grouped_moe_dev(ftm_handle* h, const void* x, int x_dtype, int32_t tokens, int32_t top_k,
+                        const int32_t* routes_host, size_t routes_len, const float* weights_dev, void* out,
+                        int out_dtype, void* stream) {
+    if (!h) return FTM_ERR_BAD;
+    std::lock_guard<std::mutex> lk(h->mu);
+    if (!x || !routes_host || !weights_dev || !out) return fail(h, FTM_ERR_BAD, "moe: grouped_moe_dev: null buffer");
+    int rc = check_tokens(h, tokens, top_k);
+    if (rc != FTM_OK) return rc;
+    const size_t R = (size_t)tokens * top_k;
+    if (routes_len != R)
+        return fail(h, FTM_ERR_BAD, "moe: grouped_moe: %zu routes for %d tokens x top_k %d", routes_len, tokens, top_k);
+    if (out_dtype != FTM_BF16 && out_dtype != FTM_F32) return fail(h, FTM_ERR_BAD, "moe: out cannot be dtype %d", out_dtype);
+    if ((rc = check_host_routes(h, routes_host, R)) != FTM_OK) return rc;
+    cudaStream_t s = pick(h, stream);
+    const __nv_bfloat16* xb = nullptr;
+    if ((rc = stage_x(h, x, x_dtype, tokens, &xb, s)) != FTM_OK) return rc;
+    CU(h, cudaMemcpyAsync(h->route_slot, routes_host, R * sizeof(int32_t), cudaMemcpyHostToDevice, s));
+    rc = run_routed(h, xb, h->route_slot, weights_dev, tokens, nullptr, nullptr, nullptr, out, out_dtype,
+                    FTM_PATH_AUTO, s);
+    if (rc != FTM_OK) return rc;
+    CU(h, cudaGetLastError());
+    h->steps++;
+    return FTM_OK;
+}
+
+static int staged_locked(ftm_handle* h, int32_t layer, const void* x, int x_dtype, const void* expert_ids,
+                         int ids_dtype, const float* weights, int32_t tokens, const float* shared,
+                         const float* se_gate, cudaEvent_t join, void* out, int out_dtype, int path,
+                         cudaStream_t s) {
+    if (!x || !expert_ids || !weights || !out) return fail(h, FTM_ERR_BAD, "moe: grouped_moe_staged: null buffer");
+    if (layer < 0 || layer >= h->cfg.layers) return fail(h, FTM_ERR_BAD, "moe: layer %d of %d", layer, h->cfg.layers);
+    int rc = check_tokens(h, tokens, h->cfg.top_k);
+    if (rc != FTM_OK) return rc;
+    if (ids_dtype != FTM_I32 && ids_dtype != FTM_I64 && ids_dtype != FTM_F32)
+        return fail(h, FTM_ERR_BAD, "moe: expert ids cannot be dtype %d", ids_dtype);
+    if (out_dtype != FTM_BF16 && out_dtype != FTM_F32) return fail(h, FTM_ERR_BAD, "moe: out cannot be dtype %d", out_dtype);
+    if (path < FTM_PATH_AUTO || path > FTM_PATH_GROUPED) return fail(h, FTM_ERR_BAD, "moe: unknown path %d", path);
+    const __nv_bfloat16* xb = nullptr;
+    if ((rc = stage_x(h, x, x_dtype, tokens, &xb, s)) != FTM_OK) return rc;
+    const int R = tokens * h->cfg.top_k;
+    // the adapter's own copy of the ids, rewritten to slots through the residency table
+    h->launches += launch_slot_rewrite(expert_ids, ids_dtype, R, layer, h->cfg.experts, h->d_slot_for_id,
+                                       (int)h->slot_for_id.size(), h->route_slot, h->route_expert, h->flags + 1, h->ctx(s));
+    rc = run_routed(h, xb, h->route_slot, weights, tokens, shared, se_gate, join, out, out_dtype, path, s);
+    if (rc != FTM_OK) return rc;
+    CU(h, cudaGetLastError());
+    h->steps++;
+    return FTM_OK;
+}
+
+FTM_API int ftm_moe_layer_staged(ftm_handle* h, int32_t layer, const void* x, int x_dtype, const void* expert_ids,
+                         int ids_dtype, const float* weights, int32_t tokens, void* out, int out_dtype, int path,
+                         void* stream) {
+    if (!h) return FTM_ERR_BAD;
+    std::lock_guard<std::mutex> lk(h->mu);
+    return staged_locked(h, layer, x, x_dtype, expert_ids, ids_dtype, weights, tokens, nullptr, nullptr, nullptr,
+                         out, out_dtype, path, pick(h, stream));
+}
+
+FTM_API int ftm_moe_begin(ftm_handle* h, int32_t, const void*, int, const void*, int, const float*, int32_t, void*) {
+    if (!h) return FTM_ERR_BAD;
+    std::lock_guard<std::mutex> lk(h->mu);
+    return fail(h, FTM_ERR_NOT_SUPPORTED,
+                "moe: no overlapped path: every expert is resident, call ftm_moe_layer_staged");
+}
+
+FTM_API int ftm_moe_finish(ftm_handle* h, void*, int, void*) {
+    if (!h) return FTM_ERR_BAD;
+    std::lock_guard<std::mutex> lk(h->mu);
+    return fail(h, FTM_ERR_NOT_SUPPORTED, "moe: no pending step");
+}
+
+FTM_API size_t ftm_route_cap(const ftm_handle* h) { return h ? (size_t)h->cfg.max_tokens * h->cfg.top_k : 0; }
+
+FTM_API int ftm_reset_staging(ftm_handle* h) {
+    if (!h) return FTM_ERR_BAD;
+    std::lock_guard<std::mutex> lk(h->mu);
+    clear_residency(h);
+    CU(h, cudaSetDevice(h->cfg.ordinal));
+    CU(h, cudaMemsetAsync(h->d_slot_for_id, 0xff, h->slot_for_id.size() * sizeof(int32_t), h->stream));
+    CU(h, cudaStreamSynchronize(h->stream));
+    return FTM_OK;
+}
+
+FTM_API uint64_t ftm_steps(const ftm_handle* h) { return h ? h->steps : 0; }
+
+FTM_API int ftm_profile_enable(ftm_handle* h, int on) {
+    if (!h) return FTM_ERR_BAD;
+    std::lock_guard<std::mutex> lk(h->mu);
+    CU(h, cudaSetDevice(h->cfg.ordinal));
+    CU(h, cudaDeviceSynchronize());
+    h->prof.drain();
+    if (on) {
+        for (int k = 0; k < K_NUM_KINDS; k++) {
+            h->prof.total_ms[k] = 0;
+            h->prof.count[k] = 0;
+        }
+    }
+    h->prof.on = on != 0;
+    return FTM_OK;
+}
+
+FTM_API int ftm_profile_read(ftm_handle* h, int kind, double* total_ms, uint64_t* launches) {
+    if (!h) return FTM_ERR_BAD;
+    std::lock_guard<std::mutex> lk(h->mu);
+    if (kind < 0 || kind >= K_NUM_KINDS) return fail(h, FTM_ERR_BAD, "moe: profile kind %d", kind);
+    CU(h, cudaSetDevice(h->cfg.ordinal));
+    CU(h, cudaDeviceSynchronize());
+    h->prof.drain();
+    if (total_ms) *total_ms = h->prof.total_ms[kind];
+    if (launches) *launches = h->prof.count[kind];
+    return FTM_OK;
+}
+
+FTM_API const char* ftm_profile_kind_name(int kind) {
+    return (kind >= 0 && kind < K_NUM_KINDS) ? kKindNames[kind] : nullptr;
+}
+FTM_API uint64_t ftm_kernel_launches(const ftm_handle* h) { return h ? h->launches : 0; }
+
+// ---- shared expert, combine, whole block ----------------------------------------------------
+
+static int shared_locked(ftm_handle* h, const void* x, int32_t tokens, const void* gate_up, const void* down,
+                         const void* shared_gate, float* shared_out, float* se_gate_out, cudaStream_t s) {
+    if (!x || !gate_up || !down || !shared_gate || !shared_out || !se_gate_out)
+        return fail(h, FTM_ERR_BAD, "moe: shared expert: null buffer");
+    if (h->cfg.shared_inter <= 0) return fail(h, FTM_ERR_BAD, "moe: the adapter was built without a shared expert");
+    if (tokens <= 0 || tokens > h->cfg.max_tokens)
+        return fail(h, FTM_ERR_BAD, "moe: shared expert: %d tokens (max_tokens %d)", tokens, h->cfg.max_tokens);
+    h->launches += launch_shared_expert((const __nv_bfloat16*)x, tokens, h->cfg.hidden, h->cfg.shared_inter,
+                                        (const __nv_bfloat16*)gate_up, (const __nv_bfloat16*)down,
+                                        (const __nv_bfloat16*)shared_gate, h->ic2s, shared_out, se_gate_out, h->ctx(s));
+    CU(h, cudaGetLastError());
+    return FTM_OK;
+}
+
+FTM_API int ftm_shared_expert(ftm_handle* h, const void* x_bf16, int32_t tokens, const void* gate_up_bf16,
+                      const void* down_bf16, const void* shared_gate_bf16, float* shared_out, float* se_gate_out,
+                      void* stream) {
+    if (!h) return FTM_ERR_BAD;
+    std::lock_guard<std::mutex> lk(h->mu);
+    return shared_locked(h, x_bf16, tokens, gate_up_bf16, down_bf16, shared_gate_bf16, shared_out, se_gate_out,
+                         pick(h, stream));
+}
+
+FTM_API int ftm_combine(ftm_handle* h, const void* routed, int routed_dtype, const float* shared, const float* se_gate,
+                int32_t tokens, void* out, int out_dtype, void* stream) {
+    if (!h) return FTM_ERR_BAD;
+    std::lock_guard<std::mutex> lk(h->mu);
+    if (!routed || !shared || !se_gate || !out) return fail(h, FTM_ERR_BAD, "moe: combine: null buffer");
+    if (tokens <= 0) return fail(h, FTM_ERR_BAD, "moe: combine: %d tokens", tokens);
+    if ((routed_dtype != FTM_BF16 && routed_dtype != FTM_F32) || (out_dtype != FTM_BF16 && out_dtype != FTM_F32))
+        return fail(h, FTM_ERR_BAD, "moe: combine: dtypes %d -> %d", routed_dtype, out_dtype);
+    h->launches += launch_combine(routed, routed_dtype, shared, se_gate, tokens, h->cfg.hidden, out, out_dtype, h->ctx(pick(h, stream)));
+    CU(h, cudaGetLastError());
+    return FTM_OK;
+}
+
+FTM_API int ftm_moe_block(ftm_handle* h, int32_t layer, const void* x_bf16, int32_t tokens, const void* gate_w_bf16,
+                  const void* sh_gate_up_bf16, const void* sh_down_bf16, const void* sh_gate_bf16, void* out,
+                  int out_dtype, int32_t* ids_out, float* weights_out, int path, void* stream) {
+    if (!h) return FTM_ERR_BAD;
+    std::lock_guard<std::mutex> lk(h->mu);
+    cudaStream_t s = pick(h, stream);
+    if (!x_bf16 || !out) return fail(h, FTM_ERR_BAD, "moe: moe_block: null buffer");
+    int rc = check_tokens(h, tokens, h->cfg.top_k);
+    if (rc != FTM_OK) return rc;
+    // shared expert on the second stream, forked from and joined back into s
+    CU(h, cudaEventRecord(h->ev_fork, s));
+    CU(h, cudaStreamWaitEvent(h->aux, h->ev_fork, 0));
+    rc = shared_locked(h, x_bf16, tokens, sh_gate_up_bf16, sh_down_bf16, sh_gate_bf16, h->shared_out, h->se_gate,
+                       h->aux);
+    CU(h, cudaEventRecord(h->ev_join, h->aux));
+    if (rc != FTM_OK) {
+        cudaStreamWaitEvent(s, h->ev_join, 0);
+        return rc;
+    }
+    int32_t* ids = ids_out ? ids_out : h->ids;
+    float* w = weights_out ? weights_out : h->rweights;
+    rc = router_locked(h, x_bf16, gate_w_bf16, tokens, ids, w, s);
+    if (rc == FTM_OK)
+        rc = staged_locked(h, layer, x_bf16, FTM_BF16, ids, FTM_I32, w, tokens, h->shared_out, h->se_gate,
+                           h->ev_join, out, out_dtype, path, s);
+    if (rc != FTM_OK) cudaStreamWaitEvent(s, h->ev_join, 0);  // never leave the fork unjoined
+    return rc;
+}
+
+}  // extern "C"

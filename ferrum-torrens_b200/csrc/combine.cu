@@ -1,0 +1,87 @@
+// Weighted un-permute / combine and the gated shared-expert add.
+//
+// Reference behaviour (src/models/qwen3_6/forward.rs:737-742, :785-787; device form
+// python/ferrum_kernel/nvfp4_moe.py:423-445 `_sum_reduce_kernel` followed by `se.add(&routed)`,
+// src/models/qwen3_6/forward_cudarc.rs:1590):
+//   out[t] = se_gate[t] * shared[t] + sum_{j < top_k} w[t,j] * ic3[t,j]
+// with the routes added in j order.  The route weights were applied by the down projection, so
+// this pass reads each per-route row once and writes the token row once.
+#include "kernels.cuh"
+
+namespace ftm {
+
+namespace {
+
+// yroute [T*top_k, H] f32 (already weighted); shared / se_gate may be null (routed sum only)
+__global__ void sum_routes_kernel(const float* __restrict__ yroute, int tokens, int top_k, int H,
+                                  const float* __restrict__ shared, const float* __restrict__ se_gate,
+                                  void* __restrict__ out, int out_dtype) {
+    const int t = blockIdx.y;
+    const int d = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (d >= H) return;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (shared) {
+        const float g = se_gate[t];
+        const float4 sv = *reinterpret_cast<const float4*>(shared + (size_t)t * H + d);
+        acc = make_float4(sv.x * g, sv.y * g, sv.z * g, sv.w * g);
+    }
+    for (int j = 0; j < top_k; j++) {
+        const float4 y = *reinterpret_cast<const float4*>(yroute + ((size_t)t * top_k + j) * H + d);
+        acc.x += y.x; acc.y += y.y; acc.z += y.z; acc.w += y.w;
+    }
+    const size_t o = (size_t)t * H + d;
+    if (out_dtype == 0) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+        uint2 pk = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+        *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(out) + o) = pk;
+    } else {
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + o) = acc;
+    }
+}
+
+__global__ void combine_kernel(const void* __restrict__ routed, int routed_dtype, const float* __restrict__ shared,
+                               const float* __restrict__ se_gate, int tokens, int H, void* __restrict__ out,
+                               int out_dtype) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)tokens * H) return;
+    int t = (int)(i / H);
+    float v = shared[i] * se_gate[t] + load_act(routed, routed_dtype, i);
+    store_act(out, out_dtype, i, v);
+}
+
+__global__ void cast_to_bf16_kernel(const void* __restrict__ src, int src_dtype, size_t n,
+                                    __nv_bfloat16* __restrict__ dst) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) dst[i] = __float2bfloat16_rn(load_act(src, src_dtype, i));
+}
+
+}  // namespace
+
+int launch_sum_routes(const float* yroute, int tokens, int top_k, int hidden, const float* shared,
+                      const float* se_gate, void* out, int out_dtype, const Ctx& c) {
+    int threads = 128;
+    dim3 grid((hidden / 4 + threads - 1) / threads, tokens);
+    c.begin(K_SUM_ROUTES);
+    sum_routes_kernel<<<grid, threads, 0, c.s>>>(yroute, tokens, top_k, hidden, shared, se_gate, out, out_dtype);
+    c.end();
+    return 1;
+}
+
+int launch_combine(const void* routed, int routed_dtype, const float* shared, const float* se_gate, int tokens,
+                   int hidden, void* out, int out_dtype, const Ctx& c) {
+    size_t n = (size_t)tokens * hidden;
+    c.begin(K_COMBINE);
+    combine_kernel<<<(unsigned)((n + 255) / 256), 256, 0, c.s>>>(routed, routed_dtype, shared, se_gate, tokens, hidden,
+                                                               out, out_dtype);
+    c.end();
+    return 1;
+}
+
+int launch_cast_to_bf16(const void* src, int src_dtype, size_t n, __nv_bfloat16* dst, const Ctx& c) {
+    c.begin(K_CAST);
+    cast_to_bf16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, c.s>>>(src, src_dtype, n, dst);
+    c.end();
+    return 1;
+}
+
+}  // namespace ftm

@@ -1,0 +1,69 @@
+// Launchers of the MoE kernels; each returns the number of kernel launches it enqueued.
+#pragma once
+
+#include "common.cuh"
+
+namespace ftm {
+
+// kinds of kernels, for the per-kernel CUDA-event profile (ftm_profile_*)
+enum Kind {
+    K_ROUTER_LOGITS = 0,
+    K_ROUTER_TOPK,
+    K_SLOT_REWRITE,
+    K_CSR,
+    K_EXPERT_GATE_UP,
+    K_EXPERT_DOWN,
+    K_SUM_ROUTES,
+    K_SHARED_PHASE1,
+    K_SHARED_PHASE2,
+    K_CAST,
+    K_COMBINE,
+    K_GROUPED_GATE_UP,
+    K_GROUPED_DOWN,
+    K_NUM_KINDS
+};
+
+struct Profiler;
+
+// what every launcher gets: the stream, and the profiler when one is recording
+struct Ctx {
+    cudaStream_t s;
+    Profiler* prof;
+    void begin(int kind) const;  // records an event before a launch when profiling
+    void end() const;            // and one after it
+};
+
+// router.cu
+int launch_router_logits(const __nv_bfloat16* x, const __nv_bfloat16* gate_w, int tokens, int experts,
+                         int hidden, float* logits, const Ctx& c);
+int launch_router_topk(const float* logits, int tokens, int experts, int top_k, int32_t* ids,
+                       float* weights, const Ctx& c);
+
+// permute.cu
+// scratch: cta_hist needs csr_scratch_ints(routes, bins) int32 entries
+size_t csr_scratch_ints(int routes, int bins);
+int launch_csr_build(const int32_t* route_bin, int routes, int bins, int32_t* seg, int32_t* route_idx,
+                     int32_t* scratch, int32_t* bad_flag, const Ctx& c);
+int launch_slot_rewrite(const void* expert_ids, int ids_dtype, int routes, int layer, int experts,
+                        const int32_t* slot_for_id, int n_ids, int32_t* route_slot, int32_t* route_expert,
+                        int32_t* bad_flag, const Ctx& c);
+
+// decode_gemv.cu
+int launch_decode_routes(const BankView& b, const __nv_bfloat16* x, const int32_t* route_slot,
+                         const float* route_weight, int tokens, int top_k, float* ic2, float* yroute,
+                         const Ctx& c);
+
+// shared_expert.cu
+int launch_shared_expert(const __nv_bfloat16* x, int tokens, int hidden, int shared_inter,
+                         const __nv_bfloat16* gate_up, const __nv_bfloat16* down,
+                         const __nv_bfloat16* shared_gate, float* ic2s, float* shared_out,
+                         float* se_gate, const Ctx& c);
+
+// combine.cu
+int launch_sum_routes(const float* yroute, int tokens, int top_k, int hidden, const float* shared,
+                      const float* se_gate, void* out, int out_dtype, const Ctx& c);
+int launch_combine(const void* routed, int routed_dtype, const float* shared, const float* se_gate,
+                   int tokens, int hidden, void* out, int out_dtype, const Ctx& c);
+int launch_cast_to_bf16(const void* src, int src_dtype, size_t n, __nv_bfloat16* dst, const Ctx& c);
+
+}  // namespace ftm

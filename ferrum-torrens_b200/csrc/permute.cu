@@ -1,0 +1,253 @@
+// Token permutation for the routed experts: per-bin histogram, prefix scan, stable scatter.
+//
+// Reference behaviour (src/infrastructure/cuda_moe.rs:2328-2362 `build_grouped_csr_host`,
+// python/ferrum_kernel/moe_prefill.py:30-89): seg[b] .. seg[b+1] indexes route_idx, which holds the
+// original route ids of bin b in ascending order; a route whose bin is outside [0, bins) raises a
+// device flag.  The reference scans all R routes once per bin (O(bins * R)); here every route is
+// read twice in total.
+//
+// Layout of the work: the routes are cut into chunks of kChunkRoutes, one CTA per chunk, and each
+// warp of a CTA owns a contiguous sub-range, so "ascending route id" is "CTA order, then warp
+// order, then lane order".  Pass 1 counts per (CTA, bin); pass 2 (one CTA) turns the counts into
+// per-(CTA, bin) start offsets; pass 3 recounts per warp and scatters with a warp-level rank.
+// When everything fits one CTA the three passes run inside a single launch.
+#include "kernels.cuh"
+
+namespace ftm {
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+constexpr int kChunkRoutes = 2048;                    // routes per CTA
+constexpr int kWarpRoutes = kChunkRoutes / kWarps;    // contiguous routes per warp
+constexpr int kMaxBins = 1024;
+
+__device__ __forceinline__ void count_chunk(const int32_t* __restrict__ route_bin, int routes, int bins,
+                                            int chunk_begin, int* whist /* [kWarps][bins] smem */,
+                                            int32_t* bad_flag) {
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    for (int i = threadIdx.x; i < kWarps * bins; i += kThreads) whist[i] = 0;
+    __syncthreads();
+    const int begin = chunk_begin + warp * kWarpRoutes;
+    const int end = min(begin + kWarpRoutes, routes);
+    for (int r = begin + lane; r < end; r += 32) {
+        int b = route_bin[r];
+        if (b < 0 || b >= bins) {
+            atomicExch(bad_flag, 1);
+            continue;
+        }
+        atomicAdd(&whist[warp * bins + b], 1);
+    }
+    __syncthreads();
+}
+
+// stable scatter of this CTA's chunk; wbase[w][b] = first output position of warp w's routes of bin b
+__device__ __forceinline__ void scatter_chunk(const int32_t* __restrict__ route_bin, int routes, int bins,
+                                              int chunk_begin, int* wbase, int32_t* __restrict__ route_idx) {
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int begin = chunk_begin + warp * kWarpRoutes;
+    const int end = min(begin + kWarpRoutes, routes);
+    int* mine = wbase + warp * bins;
+    for (int r0 = begin; r0 < end; r0 += 32) {
+        int r = r0 + lane;
+        int b = (r < end) ? route_bin[r] : -1;
+        bool ok = b >= 0 && b < bins;
+        unsigned peers = __match_any_sync(0xffffffffu, ok ? b : -1 - lane);
+        if (ok) {
+            int rank = __popc(peers & ((1u << lane) - 1u));
+            int pos = mine[b] + rank;
+            route_idx[pos] = r;
+        }
+        __syncwarp();
+        if (ok && lane == 31 - __clz(peers)) mine[b] += __popc(peers);
+        __syncwarp();
+    }
+}
+
+// single-CTA build: routes <= kChunkRoutes
+__global__ void __launch_bounds__(kThreads)
+csr_small_kernel(const int32_t* __restrict__ route_bin, int routes, int bins, int32_t* __restrict__ seg,
+                 int32_t* __restrict__ route_idx, int32_t* bad_flag) {
+    extern __shared__ int sm[];
+    int* whist = sm;                   // [kWarps][bins]
+    int* binbase = sm + kWarps * bins; // [bins + 1]
+    count_chunk(route_bin, routes, bins, 0, whist, bad_flag);
+    // per-bin totals, then an exclusive scan over bins by warp 0
+    for (int b = threadIdx.x; b < bins; b += kThreads) {
+        int tot = 0;
+        for (int w = 0; w < kWarps; w++) tot += whist[w * bins + b];
+        binbase[b] = tot;
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        int lane = threadIdx.x, carry = 0;
+        for (int b0 = 0; b0 < bins; b0 += 32) {
+            int b = b0 + lane;
+            int c = (b < bins) ? binbase[b] : 0;
+            int incl = c;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                int n = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += n;
+            }
+            if (b < bins) {
+                binbase[b] = carry + incl - c;
+                seg[b] = carry + incl - c;
+            }
+            carry += __shfl_sync(0xffffffffu, incl, 31);
+        }
+        if (lane == 0) seg[bins] = carry;
+    }
+    __syncthreads();
+    // warp bases: bin start + counts of earlier warps
+    for (int b = threadIdx.x; b < bins; b += kThreads) {
+        int run = binbase[b];
+        for (int w = 0; w < kWarps; w++) {
+            int c = whist[w * bins + b];
+            whist[w * bins + b] = run;
+            run += c;
+        }
+    }
+    __syncthreads();
+    scatter_chunk(route_bin, routes, bins, 0, whist, route_idx);
+}
+
+// pass 1: per-(CTA, bin) counts -> cta_hist[cta][bin]
+__global__ void __launch_bounds__(kThreads)
+csr_count_kernel(const int32_t* __restrict__ route_bin, int routes, int bins, int32_t* __restrict__ cta_hist,
+                 int32_t* bad_flag) {
+    extern __shared__ int sm[];
+    count_chunk(route_bin, routes, bins, blockIdx.x * kChunkRoutes, sm, bad_flag);
+    for (int b = threadIdx.x; b < bins; b += kThreads) {
+        int tot = 0;
+        for (int w = 0; w < kWarps; w++) tot += sm[w * bins + b];
+        cta_hist[(size_t)blockIdx.x * bins + b] = tot;
+    }
+}
+
+// pass 2 (one CTA): cta_hist[c][b] <- seg[b] + sum of counts of CTAs before c; writes seg
+__global__ void __launch_bounds__(kMaxBins)
+csr_scan_kernel(int32_t* __restrict__ cta_hist, int nctas, int bins, int32_t* __restrict__ seg) {
+    __shared__ int wsum[32];
+    const int b = threadIdx.x;
+    int total = 0;
+    if (b < bins)
+        for (int c = 0; c < nctas; c++) total += cta_hist[(size_t)c * bins + b];
+    // exclusive scan over bins (block-wide: warp scan + scan of warp totals)
+    const int lane = b % 32, warp = b / 32;
+    int incl = (b < bins) ? total : 0;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        int n = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += n;
+    }
+    if (lane == 31) wsum[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        int v = (lane < (int)(blockDim.x / 32)) ? wsum[lane] : 0;
+        int inc2 = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            int n = __shfl_up_sync(0xffffffffu, inc2, o);
+            if (lane >= o) inc2 += n;
+        }
+        wsum[lane] = inc2 - v;
+    }
+    __syncthreads();
+    int excl = wsum[warp] + incl - ((b < bins) ? total : 0);
+    if (b < bins) {
+        seg[b] = excl;
+        if (b == bins - 1) seg[bins] = excl + total;
+        int run = excl;
+        for (int c = 0; c < nctas; c++) {
+            int v = cta_hist[(size_t)c * bins + b];
+            cta_hist[(size_t)c * bins + b] = run;
+            run += v;
+        }
+    }
+}
+
+// pass 3: recount per warp, then ranked scatter from the CTA's bases
+__global__ void __launch_bounds__(kThreads)
+csr_scatter_kernel(const int32_t* __restrict__ route_bin, int routes, int bins,
+                   const int32_t* __restrict__ cta_base, int32_t* __restrict__ route_idx, int32_t* scratch_flag) {
+    extern __shared__ int sm[];
+    count_chunk(route_bin, routes, bins, blockIdx.x * kChunkRoutes, sm, scratch_flag);
+    for (int b = threadIdx.x; b < bins; b += kThreads) {
+        int run = cta_base[(size_t)blockIdx.x * bins + b];
+        for (int w = 0; w < kWarps; w++) {
+            int c = sm[w * bins + b];
+            sm[w * bins + b] = run;
+            run += c;
+        }
+    }
+    __syncthreads();
+    scatter_chunk(route_bin, routes, bins, blockIdx.x * kChunkRoutes, sm, route_idx);
+}
+
+// dense expert ids of one layer -> slot ids through the residency table
+__global__ void slot_rewrite_kernel(const void* __restrict__ expert_ids, int ids_dtype, int routes, int layer,
+                                    int experts, const int32_t* __restrict__ slot_for_id, int n_ids,
+                                    int32_t* __restrict__ route_slot, int32_t* __restrict__ route_expert,
+                                    int32_t* bad_flag) {
+    int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= routes) return;
+    // ids arrive as i32, i64 or f32 (src/infrastructure/cuda_moe.rs:67-86 accepts all three)
+    long long e;
+    if (ids_dtype == 3)
+        e = reinterpret_cast<const long long*>(expert_ids)[r];
+    else if (ids_dtype == 1)
+        e = (long long)reinterpret_cast<const float*>(expert_ids)[r];
+    else
+        e = (long long)reinterpret_cast<const int32_t*>(expert_ids)[r];
+    int slot = -1;
+    if (e >= 0 && e < experts) {
+        long long id = (long long)layer * experts + e;
+        if (id < n_ids) slot = slot_for_id[id];
+    } else {
+        atomicExch(bad_flag, 1);
+    }
+    route_slot[r] = slot;
+    if (route_expert) route_expert[r] = (slot >= 0) ? (int32_t)e : -1;
+}
+
+}  // namespace
+
+size_t csr_scratch_ints(int routes, int bins) {
+    size_t nctas = ((size_t)routes + kChunkRoutes - 1) / kChunkRoutes;
+    return (nctas ? nctas : 1) * (size_t)bins;
+}
+
+int launch_csr_build(const int32_t* route_bin, int routes, int bins, int32_t* seg, int32_t* route_idx,
+                     int32_t* scratch, int32_t* bad_flag, const Ctx& c) {
+    if (routes <= kChunkRoutes) {
+        size_t smem = ((size_t)kWarps * bins + bins + 1) * sizeof(int);
+        c.begin(K_CSR);
+        csr_small_kernel<<<1, kThreads, smem, c.s>>>(route_bin, routes, bins, seg, route_idx, bad_flag);
+        c.end();
+        return 1;
+    }
+    int nctas = (routes + kChunkRoutes - 1) / kChunkRoutes;
+    size_t smem = (size_t)kWarps * bins * sizeof(int);
+    c.begin(K_CSR);
+    csr_count_kernel<<<nctas, kThreads, smem, c.s>>>(route_bin, routes, bins, scratch, bad_flag);
+    int scan_threads = ((bins + 31) / 32) * 32;
+    csr_scan_kernel<<<1, scan_threads, 0, c.s>>>(scratch, nctas, bins, seg);
+    csr_scatter_kernel<<<nctas, kThreads, smem, c.s>>>(route_bin, routes, bins, scratch, route_idx, bad_flag);
+    c.end();
+    return 3;
+}
+
+int launch_slot_rewrite(const void* expert_ids, int ids_dtype, int routes, int layer, int experts,
+                        const int32_t* slot_for_id, int n_ids, int32_t* route_slot, int32_t* route_expert,
+                        int32_t* bad_flag, const Ctx& c) {
+    int threads = 256;
+    c.begin(K_SLOT_REWRITE);
+    slot_rewrite_kernel<<<(routes + threads - 1) / threads, threads, 0, c.s>>>(
+        expert_ids, ids_dtype, routes, layer, experts, slot_for_id, n_ids, route_slot, route_expert, bad_flag);
+    c.end();
+    return 1;
+}
+
+}  // namespace ftm

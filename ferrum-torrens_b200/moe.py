@@ -1,0 +1,524 @@
+"""Host-side mirror of the reference's MoE ports over the C ABI of libftmoe.so.
+
+The names, argument meanings and error behaviour follow the reference's traits so that code
+written against them reads the same:
+
+* `ExpertSlotStore` + `ExpertGemm`  -> `B200MoE`     (src/domain/expert_kernel.rs:140-161, :246-294;
+                                                      adapter src/infrastructure/cuda_moe.rs:145-195)
+* `MoEExecutor`                     -> `CachedExperts` (src/domain/expert_kernel.rs:372-424;
+                                                      src/application/run_experts.rs:103-189)
+* `ExpertCache`, `route_lists`, `run_experts`, `MoEGroup`, `MoEDeviceRequest`, `MoEError`
+
+Device buffers are torch CUDA tensors (torch is only the allocator and stream provider); every
+computation goes through the library, which has no CPU path.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+import numpy as np
+
+from . import _lib as L
+
+# bank order: gate_up then down, packed / scale / global within each (expert_kernel.rs:62-80)
+BANKS = ("GateUpPacked", "GateUpScale", "GateUpGlobal", "DownPacked", "DownScale", "DownGlobal")
+
+
+class MoEError(Exception):
+    """MoEError (src/domain/expert_kernel.rs:21-39).  `kind` is the variant name."""
+
+    KINDS = {L.ERR_BAD: "Bad", L.ERR_SLOT_OUT_OF_RANGE: "SlotOutOfRange", L.ERR_MISSING: "Missing",
+             L.ERR_OUT_OF_MEMORY: "OutOfMemory", L.ERR_READ: "Read", L.ERR_NOT_SUPPORTED: "NotSupported",
+             L.ERR_CUDA: "Bad"}
+
+    def __init__(self, code: int, msg: str):
+        super().__init__(msg)
+        self.code = code
+        self.kind = self.KINDS.get(code, "Bad")
+
+    @property
+    def retryable(self) -> bool:
+        """Out of device memory is answered with a retryable 503 (expert_kernel.rs:17-19, :30-34)."""
+        return self.kind == "OutOfMemory"
+
+
+def bad(msg: str) -> MoEError:
+    return MoEError(L.ERR_BAD, "moe: " + msg)
+
+
+@dataclass(frozen=True)
+class ExpertShapes:
+    """ExpertShapes (expert_kernel.rs:179-219): gate_up [2*inter, hidden], down [hidden, inter]."""
+    hidden: int
+    inter: int
+
+    def __post_init__(self):
+        if self.hidden <= 0 or self.inter <= 0 or self.hidden % 16 or self.inter % 16:
+            raise bad(f"expert shapes hidden {self.hidden} inter {self.inter} must be nonzero multiples of 16")
+
+    def gate_up_rows(self) -> int:
+        return 2 * self.inter
+
+    def slab_shape(self, part: str):
+        return (2 * self.inter, self.hidden) if part == "GateUp" else (self.hidden, self.inter)
+
+    def bank_row_bytes(self, bank: str) -> int:
+        rows, cols = self.slab_shape("GateUp" if bank.startswith("GateUp") else "Down")
+        if bank.endswith("Packed"):
+            return rows * cols // 2
+        if bank.endswith("Scale"):
+            return rows * cols // 16
+        return rows * 2
+
+
+def route_lists(routes: Sequence[int], tokens: int, top_k: int):
+    """route_lists (expert_kernel.rs:223-243): flatten dense [tokens, top_k] slot ids."""
+    routes = np.asarray(routes, np.int32).reshape(-1)
+    if tokens == 0 or top_k == 0 or routes.size != tokens * top_k:
+        raise bad(f"routes {routes.size} for {tokens} tokens x top_k {top_k}")
+    return np.repeat(np.arange(tokens, dtype=np.int32), top_k), routes.copy()
+
+
+@dataclass
+class MoEGroup:
+    """MoEGroup (expert_kernel.rs:167-174): host hand-off, routes are slot ids (-1 = skip)."""
+    hidden: int
+    inter: int
+    x: np.ndarray
+    top_k: int
+    routes: np.ndarray
+    weights: np.ndarray
+
+
+@dataclass
+class MoEDeviceRequest:
+    """MoEDeviceRequest (expert_kernel.rs:332-340): everything on the device; `experts` are the
+    router's dense ids [tokens, top_k]."""
+    layer: int
+    hidden: int
+    inter: int
+    top_k: int
+    x: "torch.Tensor"
+    experts: "torch.Tensor"
+    weights: "torch.Tensor"
+
+
+def _torch():
+    import torch
+    return torch
+
+
+def _dtype_code(t) -> int:
+    torch = _torch()
+    table = {torch.bfloat16: L.BF16, torch.float32: L.F32, torch.int32: L.I32, torch.int64: L.I64}
+    if t.dtype not in table:
+        raise bad(f"tensor cannot be {t.dtype}")
+    return table[t.dtype]
+
+
+def _dev(t, what: str):
+    if not t.is_cuda:
+        raise bad(f"{what} must be a device tensor")
+    if not t.is_contiguous():
+        raise bad(f"{what} must be contiguous")
+    return C.c_void_p(t.data_ptr())
+
+
+def _stream_ptr(stream) -> C.c_void_p:
+    if stream is None:
+        return C.c_void_p(_torch().cuda.current_stream().cuda_stream)
+    if isinstance(stream, int):
+        return C.c_void_p(stream)
+    return C.c_void_p(stream.cuda_stream)
+
+
+class _RawDeviceArray:
+    """A borrowed device range exposed through __cuda_array_interface__ (no ownership)."""
+
+    def __init__(self, ptr: int, nbytes: int, owner):
+        self._owner = owner
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3,
+                                         "strides": None}
+
+
+class B200MoE:
+    """The device adapter: `ExpertSlotStore` + `ExpertGemm` over the C ABI (CudaMoE).
+
+    `source`, when given, is an ExpertSlabSource: an object with `slab(layer, expert, part)`
+    returning `(packed, scale, global)` uint8 arrays (expert_kernel.rs:121-131); `load` reads
+    through it like the reference adapter does (cuda_moe.rs:552-576).
+    """
+
+    def __init__(self, device: int, shapes: ExpertShapes, slots: int, *, source=None, experts: int = 256,
+                 layers: int = 1, top_k: int = 8, shared_inter: int = 512, max_tokens: int = 2048, ep_rank: int = 0,
+                 ep_size: int = 1, stream=None):
+        self._h = C.c_void_p()
+        self._lib = L.lib()
+        self.shapes, self.source = shapes, source
+        self.experts, self.layers, self.top_k = experts, layers, top_k
+        self.shared_inter, self.max_tokens = shared_inter, max_tokens
+        self.device = device
+        cfg = L.Config(device, shapes.hidden, shapes.inter, top_k, experts, layers, slots, shared_inter, max_tokens,
+                       ep_rank, ep_size)
+        sp = _stream_ptr(stream) if stream is not None else C.c_void_p(0)
+        h = C.c_void_p()
+        rc = self._lib.ftm_create(C.byref(cfg), sp, C.byref(h))
+        if rc != L.OK:
+            raise MoEError(rc, (self._lib.ftm_last_error(None) or b"").decode())
+        self._h = h
+
+    # -- plumbing ---------------------------------------------------------------------------
+    def close(self):
+        if getattr(self, "_h", None):
+            self._lib.ftm_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, rc: int):
+        if rc != L.OK:
+            raise MoEError(rc, (self._lib.ftm_last_error(self._h) or b"").decode())
+
+    # -- ExpertSlotStore --------------------------------------------------------------------
+    def load(self, layer: int, expert: int, slot: int, fields=None):
+        """load(layer, expert, slot): stage one expert's six byte fields into `slot`.
+
+        `fields` (six uint8 arrays in bank order, numpy or CUDA tensors) overrides the source."""
+        if fields is None:
+            if self.source is None:
+                raise MoEError(L.ERR_MISSING, f"moe: no expert bank entry L{layer:05d}")
+            gu = self.source.slab(layer, expert, "GateUp")
+            dn = self.source.slab(layer, expert, "Down")
+            fields = [*gu, *dn]
+        if len(fields) != L.NUM_BANKS:
+            raise bad(f"{len(fields)} expert fields, expected {L.NUM_BANKS}")
+        ptrs = (C.c_void_p * L.NUM_BANKS)()
+        lens = (C.c_size_t * L.NUM_BANKS)()
+        on_device = hasattr(fields[0], "is_cuda") and fields[0].is_cuda
+        keep = []
+        for b, f in enumerate(fields):
+            if on_device:
+                keep.append(f)
+                ptrs[b], lens[b] = f.data_ptr(), f.numel() * f.element_size()
+            else:
+                a = np.ascontiguousarray(f).view(np.uint8).reshape(-1)
+                keep.append(a)
+                ptrs[b], lens[b] = a.ctypes.data, a.size
+        fn = self._lib.ftm_load_expert_dev if on_device else self._lib.ftm_load_expert
+        self._check(fn(self._h, layer, expert, slot, ptrs, lens))
+
+    def slots(self) -> int:
+        return int(self._lib.ftm_slots(self._h))
+
+    def release_banks(self):
+        self._check(self._lib.ftm_release_banks(self._h))
+
+    def rehydrate_banks(self):
+        self._check(self._lib.ftm_rehydrate_banks(self._h))
+
+    def banks_resident(self) -> bool:
+        return bool(self._lib.ftm_banks_resident(self._h))
+
+    def bank_ptrs(self) -> list[int]:
+        out = (C.c_uint64 * L.NUM_BANKS)()
+        self._check(self._lib.ftm_bank_ptrs(self._h, out))
+        return [int(v) for v in out]
+
+    def bank_row_bytes(self, bank: int) -> int:
+        return int(self._lib.ftm_bank_row_bytes(self._h, bank))
+
+    def bank_tensors(self):
+        """The six banks as uint8 CUDA tensors [slots, row_bytes] aliasing the adapter's memory."""
+        torch = _torch()
+        out = []
+        for b, ptr in enumerate(self.bank_ptrs()):
+            rb = self.bank_row_bytes(b)
+            raw = _RawDeviceArray(ptr, rb * self.slots(), self)
+            out.append(torch.as_tensor(raw, device=f"cuda:{self.device}").view(self.slots(), rb))
+        return out
+
+    def adopt(self, layer: int, expert: int, slot: int):
+        """Marks (layer, expert) resident in `slot` whose bytes were written through bank_tensors()."""
+        ptrs = (C.c_void_p * L.NUM_BANKS)()
+        lens = (C.c_size_t * L.NUM_BANKS)()
+        for b, base in enumerate(self.bank_ptrs()):
+            rb = self.bank_row_bytes(b)
+            ptrs[b], lens[b] = base + slot * rb, rb
+        self._check(self._lib.ftm_load_expert_dev(self._h, layer, expert, slot, ptrs, lens))
+
+    def slot_of(self, layer: int, expert: int) -> int:
+        return int(self._lib.ftm_slot_of(self._h, layer, expert))
+
+    # -- ExpertGemm -------------------------------------------------------------------------
+    def grouped_moe(self, req: MoEGroup, out: np.ndarray):
+        """grouped_moe(&MoEGroup, &mut [f32]): host hand-off, synchronous."""
+        if req.hidden != self.shapes.hidden or req.inter != self.shapes.inter:
+            raise bad(f"the adapter is built for hidden {self.shapes.hidden} inter {self.shapes.inter}, "
+                      f"not {req.hidden}x{req.inter}")
+        x = np.ascontiguousarray(req.x, np.float32).reshape(-1)
+        routes = np.ascontiguousarray(req.routes, np.int32).reshape(-1)
+        weights = np.ascontiguousarray(req.weights, np.float32).reshape(-1)
+        if out.dtype != np.float32 or not out.flags.c_contiguous:
+            raise bad("out must be contiguous f32")
+        p = lambda a: C.c_void_p(a.ctypes.data)
+        self._check(self._lib.ftm_grouped_moe_host(self._h, p(x), x.size, req.top_k, p(routes), routes.size,
+                                                   p(weights), weights.size, p(out), out.size))
+
+    def grouped_moe_dev(self, hidden: int, inter: int, top_k: int, x, routes, weights, out, stream=None):
+        """grouped_moe_dev(&MoEDeviceGroup, out): x / weights / out on the device, routes on the host."""
+        if hidden != self.shapes.hidden or inter != self.shapes.inter:
+            raise bad(f"the adapter is built for hidden {self.shapes.hidden} inter {self.shapes.inter}")
+        if x.numel() == 0 or x.numel() % hidden:
+            raise bad(f"grouped_moe: {x.numel()} activations for hidden {hidden}")
+        tokens = x.numel() // hidden
+        routes = np.ascontiguousarray(routes, np.int32).reshape(-1)
+        if weights.numel() < tokens * top_k:
+            raise bad(f"grouped_moe: {routes.size} routes and {weights.numel()} weights for {tokens} tokens x top_k {top_k}")
+        if out.numel() != tokens * hidden:
+            raise bad(f"out holds {out.numel()}, the step produces {tokens * hidden}")
+        if weights.dtype != _torch().float32:
+            raise bad("route weights must be f32")
+        self._check(self._lib.ftm_grouped_moe_dev(self._h, _dev(x, "the activations"), _dtype_code(x), tokens, top_k,
+                                                  C.c_void_p(routes.ctypes.data), routes.size,
+                                                  _dev(weights, "the weights"), _dev(out, "the output"),
+                                                  _dtype_code(out), _stream_ptr(stream)))
+
+    def grouped_moe_staged(self, req: MoEDeviceRequest, out, *, path: int = L.PATH_AUTO, stream=None):
+        """grouped_moe_staged(&MoEDeviceRequest, out): the serving call, asynchronous."""
+        tokens = _check_device_step(req)
+        if req.hidden != self.shapes.hidden or req.inter != self.shapes.inter:
+            raise bad(f"the adapter is built for hidden {self.shapes.hidden} inter {self.shapes.inter}")
+        if out.numel() != tokens * req.hidden:
+            raise bad(f"out holds {out.numel()}, the step produces {tokens * req.hidden}")
+        if req.weights.dtype != _torch().float32:
+            raise bad("route weights must be f32")
+        if req.top_k != self.top_k:
+            raise bad(f"the adapter was built for top_k {self.top_k}, got {req.top_k}")
+        self._check(self._lib.ftm_moe_layer_staged(
+            self._h, req.layer, _dev(req.x, "the activations"), _dtype_code(req.x), _dev(req.experts, "the expert ids"),
+            _dtype_code(req.experts), _dev(req.weights, "the weights"), tokens, _dev(out, "the output"),
+            _dtype_code(out), path, _stream_ptr(stream)))
+
+    def begin_staged(self, req: MoEDeviceRequest, stream=None):
+        """begin_staged: `None` means "no overlapped path, call grouped_moe_staged" (expert_kernel.rs:275-281)."""
+        tokens = _check_device_step(req)
+        rc = self._lib.ftm_moe_begin(self._h, req.layer, _dev(req.x, "x"), _dtype_code(req.x), _dev(req.experts, "ids"),
+                                     _dtype_code(req.experts), _dev(req.weights, "w"), tokens, _stream_ptr(stream))
+        if rc == L.ERR_NOT_SUPPORTED:
+            return None
+        self._check(rc)
+        return None
+
+    def staged_route_cap(self) -> int:
+        return int(self._lib.ftm_route_cap(self._h))
+
+    def reset_staging(self):
+        self._check(self._lib.ftm_reset_staging(self._h))
+
+    def steps(self) -> int:
+        return int(self._lib.ftm_steps(self._h))
+
+    def kernel_launches(self) -> int:
+        return int(self._lib.ftm_kernel_launches(self._h))
+
+    def profile(self, on: bool):
+        """Per-kernel CUDA-event timing (FT_PROFILE, src/infrastructure/profile.rs:1-14)."""
+        self._check(self._lib.ftm_profile_enable(self._h, 1 if on else 0))
+
+    def profile_read(self) -> dict:
+        """{kernel kind: (total_ms, launches)} since profiling was enabled."""
+        out, k = {}, 0
+        while True:
+            name = self._lib.ftm_profile_kind_name(k)
+            if not name:
+                return out
+            ms, n = C.c_double(0), C.c_uint64(0)
+            self._check(self._lib.ftm_profile_read(self._h, k, C.byref(ms), C.byref(n)))
+            if n.value:
+                out[name.decode()] = (ms.value, int(n.value))
+            k += 1
+
+    # -- router, permutation, shared expert, combine, whole block ----------------------------
+    def router(self, x, gate_w, stream=None):
+        """Gate projection + fused_topk_softmax: returns (ids [T,k] i32, weights [T,k] f32)."""
+        torch = _torch()
+        tokens = x.numel() // self.shapes.hidden
+        ids = torch.empty((tokens, self.top_k), dtype=torch.int32, device=x.device)
+        w = torch.empty((tokens, self.top_k), dtype=torch.float32, device=x.device)
+        if x.dtype != torch.bfloat16 or gate_w.dtype != torch.bfloat16:
+            raise bad("router activations and gate weight must be bf16")
+        if gate_w.numel() != self.experts * self.shapes.hidden:
+            raise bad(f"gate weight holds {gate_w.numel()}, expected {self.experts}x{self.shapes.hidden}")
+        self._check(self._lib.ftm_router(self._h, _dev(x, "x"), _dev(gate_w, "gate"), tokens, _dev(ids, "ids"),
+                                         _dev(w, "w"), _stream_ptr(stream)))
+        return ids, w
+
+    def fused_topk_softmax(self, logits, stream=None):
+        """Tensor::fused_topk_softmax(k) on f32 logits [T, experts] (cudarc.rs:1147-1171)."""
+        torch = _torch()
+        if logits.dtype != torch.float32 or logits.shape[-1] != self.experts:
+            raise bad(f"logits must be f32 [T, {self.experts}]")
+        tokens = logits.numel() // self.experts
+        ids = torch.empty((tokens, self.top_k), dtype=torch.int32, device=logits.device)
+        w = torch.empty((tokens, self.top_k), dtype=torch.float32, device=logits.device)
+        self._check(self._lib.ftm_router_from_logits(self._h, _dev(logits, "logits"), tokens, _dev(ids, "ids"),
+                                                     _dev(w, "w"), _stream_ptr(stream)))
+        return ids, w
+
+    def csr_build(self, route_slot, bins: int, stream=None):
+        """csr_build: (seg [bins+1], route_idx [R], bad flag) (cuda_moe.rs:1198-1253)."""
+        torch = _torch()
+        if route_slot.dtype != torch.int32:
+            raise bad("route slots must be i32")
+        r = route_slot.numel()
+        seg = torch.zeros(bins + 1, dtype=torch.int32, device=route_slot.device)
+        idx = torch.full((r,), -1, dtype=torch.int32, device=route_slot.device)
+        self._check(self._lib.ftm_csr_build(self._h, _dev(route_slot, "route_slot"), r, bins, _dev(seg, "seg"),
+                                            _dev(idx, "idx"), _stream_ptr(stream)))
+        flag = C.c_int32(0)
+        self._check(self._lib.ftm_csr_bad(self._h, _stream_ptr(stream), C.byref(flag)))
+        return seg, idx, int(flag.value)
+
+    def shared_expert(self, x, gate_up, down, shared_gate, stream=None):
+        """Returns (shared [T,H] f32 ungated, se_gate [T] f32)."""
+        torch = _torch()
+        tokens = x.numel() // self.shapes.hidden
+        shared = torch.empty((tokens, self.shapes.hidden), dtype=torch.float32, device=x.device)
+        gate = torch.empty((tokens,), dtype=torch.float32, device=x.device)
+        for t, n in ((x, "x"), (gate_up, "gate_up"), (down, "down"), (shared_gate, "shared_gate")):
+            if t.dtype != torch.bfloat16:
+                raise bad(f"shared expert {n} must be bf16")
+        self._check(self._lib.ftm_shared_expert(self._h, _dev(x, "x"), tokens, _dev(gate_up, "gate_up"),
+                                                _dev(down, "down"), _dev(shared_gate, "shared_gate"),
+                                                _dev(shared, "shared"), _dev(gate, "gate"), _stream_ptr(stream)))
+        return shared, gate
+
+    def combine(self, routed, shared, se_gate, out, stream=None):
+        tokens = routed.numel() // self.shapes.hidden
+        self._check(self._lib.ftm_combine(self._h, _dev(routed, "routed"), _dtype_code(routed), _dev(shared, "shared"),
+                                          _dev(se_gate, "se_gate"), tokens, _dev(out, "out"), _dtype_code(out),
+                                          _stream_ptr(stream)))
+
+    def moe_block(self, layer: int, x, gate_w, sh_gate_up, sh_down, sh_gate, out, *, ids_out=None, weights_out=None,
+                  path: int = L.PATH_AUTO, stream=None):
+        """The whole block: router, routed experts, shared expert, combine (moe_parts)."""
+        tokens = x.numel() // self.shapes.hidden
+        if out.numel() != tokens * self.shapes.hidden:
+            raise bad(f"out holds {out.numel()}, the block produces {tokens * self.shapes.hidden}")
+        null = C.c_void_p(0)
+        self._check(self._lib.ftm_moe_block(
+            self._h, layer, _dev(x, "x"), tokens, _dev(gate_w, "gate"), _dev(sh_gate_up, "sh_gate_up"),
+            _dev(sh_down, "sh_down"), _dev(sh_gate, "sh_gate"), _dev(out, "out"), _dtype_code(out),
+            _dev(ids_out, "ids") if ids_out is not None else null,
+            _dev(weights_out, "weights") if weights_out is not None else null, path, _stream_ptr(stream)))
+
+
+def _check_device_step(step: MoEDeviceRequest) -> int:
+    """check_device_step (src/application/run_experts.rs:251-268): element counts only."""
+    hidden, top_k = step.hidden, step.top_k
+    x_len, ne, nw = step.x.numel(), step.experts.numel(), step.weights.numel()
+    if hidden == 0 or top_k == 0 or x_len == 0 or x_len % hidden:
+        raise bad(f"device expert step: hidden {hidden} top_k {top_k} x {x_len}")
+    tokens = x_len // hidden
+    if ne != tokens * top_k or nw != tokens * top_k:
+        raise bad(f"device expert step: {ne} experts and {nw} weights for {tokens} tokens x top_k {top_k}")
+    return tokens
+
+
+class ExpertCache:
+    """ExpertCache (src/domain/expert_cache.rs:8-134) kept inside the adapter."""
+
+    def __init__(self, moe: B200MoE):
+        self._moe = moe
+        self.num_layers, self.num_experts = moe.layers, moe.experts
+
+    def cache_size(self) -> int:
+        return self._moe.slots()
+
+    def ensure_experts(self, layer: int, routed):
+        """Returns (misses, write_slots, rewrites)."""
+        routed = np.ascontiguousarray(routed, np.uint32).reshape(-1)
+        n = routed.size
+        misses = np.zeros(max(n, 1), np.uint32)
+        slots = np.zeros(max(n, 1), np.uint32)
+        rewrites = np.zeros(max(n, 1), np.int32)
+        nm = C.c_size_t(0)
+        p = lambda a: C.c_void_p(a.ctypes.data)
+        m = self._moe
+        m._check(m._lib.ftm_ensure_experts(m._h, layer, p(routed), n, p(misses), p(slots), p(rewrites), C.byref(nm)))
+        return misses[:nm.value].tolist(), slots[:nm.value].tolist(), rewrites[:n].tolist()
+
+
+def _stage_and_route(cache: ExpertCache, store: B200MoE, layer: int, experts) -> np.ndarray:
+    """stage_and_route (run_experts.rs:318-338): plan, load the misses, hand back slot routes."""
+    if cache.cache_size() < store.slots():
+        raise bad(f"slot cache holds {cache.cache_size()} slots but the adapter stages {store.slots()}")
+    misses, write_slots, rewrites = cache.ensure_experts(layer, experts)
+    for e, s in zip(misses, write_slots):
+        store.load(layer, e, s)
+    return np.asarray(rewrites, np.int32)
+
+
+def run_experts(cache: ExpertCache, store: B200MoE, gemm: B200MoE, layer: int, hidden: int, inter: int, top_k: int, x,
+                experts, weights, out: np.ndarray):
+    """run_experts (run_experts.rs:209-246): the host-plan step; `out` receives tokens*hidden f32."""
+    x = np.ascontiguousarray(x, np.float32).reshape(-1)
+    experts = np.ascontiguousarray(experts, np.uint32).reshape(-1)
+    weights = np.ascontiguousarray(weights, np.float32).reshape(-1)
+    if hidden == 0 or top_k == 0 or x.size % hidden:
+        raise bad(f"expert step: hidden {hidden} top_k {top_k} x {x.size}")
+    tokens = x.size // hidden
+    if experts.size != tokens * top_k or weights.size != tokens * top_k:
+        raise bad(f"expert step: {experts.size} experts and {weights.size} weights for {tokens} tokens x top_k {top_k}")
+    routes = _stage_and_route(cache, store, layer, experts)
+    gemm.grouped_moe(MoEGroup(hidden, inter, x, top_k, routes, weights), out)
+
+
+class CachedExperts:
+    """MoEExecutor over a B200MoE (src/application/run_experts.rs:103-189).
+
+    staged=True hands the router's ids to the device path; staged=False runs the host plan."""
+
+    def __init__(self, moe: B200MoE, staged: bool = True):
+        self.moe, self.staged = moe, staged
+        self.cache = ExpertCache(moe)
+        self._steps = 0
+
+    def steps(self) -> int:
+        return self._steps
+
+    def release_cache(self):
+        self.moe.release_banks()
+
+    def rehydrate_cache(self):
+        self.moe.rehydrate_banks()
+
+    def cache_resident(self) -> bool:
+        return self.moe.banks_resident()
+
+    def reset_staging(self):
+        self.moe.reset_staging()
+
+    def begin_device(self, req: MoEDeviceRequest):
+        if not self.staged:
+            return None
+        return self.moe.begin_staged(req)
+
+    def execute_device(self, req: MoEDeviceRequest, out, stream=None):
+        # counted before the work, so a refused step still shows the port was reached
+        self._steps += 1
+        tokens = _check_device_step(req)
+        if out.numel() < tokens * req.hidden:
+            raise bad(f"device expert step: {out.numel()} outputs for {tokens} tokens x hidden {req.hidden}")
+        if self.staged:
+            return self.moe.grouped_moe_staged(req, out, stream=stream)
+        experts = req.experts.to("cpu").reshape(-1).numpy().astype(np.uint32)
+        routes = _stage_and_route(self.cache, self.moe, req.layer, experts)
+        return self.moe.grouped_moe_dev(req.hidden, req.inter, req.top_k, req.x, routes, req.weights, out,
+                                        stream=stream)

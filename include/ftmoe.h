@@ -1,0 +1,230 @@
+/*
+ * libftmoe -- C ABI of the B200 (sm_100a) NVFP4 mixture-of-experts layer.
+ *
+ * This is the seam a host engine binds through FFI.  Every entry point takes
+ * plain pointers, sizes and integer codes; no C++ or framework types cross it.
+ * Each declaration names the interface of the reference engine it stands in
+ * for (path:line inside the reference project, butzist/ferrum-torrens).
+ *
+ * Conventions
+ *  - "dev" pointers are device addresses valid in the PRIMARY context of the
+ *    ordinal given at creation (the context the engine's tensor runtime uses,
+ *    src/infrastructure/cuda_driver.rs:389-399).  "host" pointers are ordinary
+ *    host memory.
+ *  - `stream` is a CUstream / cudaStream_t passed as void*.  NULL selects the
+ *    stream given to ftm_create.  Calls documented as asynchronous only enqueue
+ *    work: no allocation, no host read-back, no synchronisation
+ *    (src/infrastructure/cuda_moe.rs:1283-1286).
+ *  - Every shape, dtype and length is validated before anything is launched
+ *    (src/infrastructure/cuda_moe.rs:959-1003); a rejected call has no effect.
+ *  - Return value: FTM_OK or one of the codes below, which map one to one onto
+ *    the reference's MoEError variants (src/domain/expert_kernel.rs:21-39).
+ *    ftm_last_error(h) returns the message of the last failed call on h.
+ *    Nothing aborts or throws across this boundary.
+ *  - One handle serialises its calls internally (the reference wraps its
+ *    adapter in one Mutex, src/infrastructure/cuda_moe.rs:197-203).
+ */
+#ifndef FTMOE_H
+#define FTMOE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FTM_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define FTM_API __attribute__((visibility("default")))
+#else
+#define FTM_API
+#endif
+
+typedef struct ftm_handle ftm_handle;
+
+/* MoEError (src/domain/expert_kernel.rs:21-39) */
+enum {
+    FTM_OK = 0,
+    FTM_ERR_BAD = 1,               /* MoEError::Bad */
+    FTM_ERR_SLOT_OUT_OF_RANGE = 2, /* MoEError::SlotOutOfRange */
+    FTM_ERR_MISSING = 3,           /* MoEError::Missing */
+    FTM_ERR_OUT_OF_MEMORY = 4,     /* MoEError::OutOfMemory (retryable) */
+    FTM_ERR_READ = 5,              /* MoEError::Read */
+    FTM_ERR_NOT_SUPPORTED = 6,     /* the `Ok(None)` answers of begin_staged */
+    FTM_ERR_CUDA = 7               /* a CUDA runtime error; reported as MoEError::Bad("driver: ..") */
+};
+
+/* element types accepted at the boundary (src/infrastructure/cuda_moe.rs:67-86, :1101-1107) */
+enum { FTM_BF16 = 0, FTM_F32 = 1, FTM_I32 = 2, FTM_I64 = 3 };
+
+/* bank order, a cross-adapter contract (src/domain/expert_kernel.rs:62-80) */
+enum {
+    FTM_BANK_GATE_UP_PACKED = 0,
+    FTM_BANK_GATE_UP_SCALE = 1,
+    FTM_BANK_GATE_UP_GLOBAL = 2,
+    FTM_BANK_DOWN_PACKED = 3,
+    FTM_BANK_DOWN_SCALE = 4,
+    FTM_BANK_DOWN_GLOBAL = 5,
+    FTM_NUM_BANKS = 6
+};
+
+/* which routed-expert kernels a call may use */
+enum {
+    FTM_PATH_AUTO = 0,   /* decode GEMV for small batches, grouped GEMM for large */
+    FTM_PATH_GEMV = 1,   /* bandwidth-bound decode path */
+    FTM_PATH_GROUPED = 2 /* tcgen05 grouped GEMM (prefill) */
+};
+
+/* CudaMoE::new_with_stream(device, source, shapes, slots, stream)
+ * (src/infrastructure/cuda_moe.rs:406-480) */
+typedef struct ftm_config {
+    int32_t ordinal;      /* CUDA device ordinal; its primary context is used */
+    int32_t hidden;       /* 2048; nonzero multiple of 16 (ExpertShapes::new, expert_kernel.rs:186-193) */
+    int32_t inter;        /* 512;  nonzero multiple of 16 */
+    int32_t top_k;        /* 8 */
+    int32_t experts;      /* experts per layer (256) */
+    int32_t layers;       /* layers sharing the banks (flat id = layer * experts + expert) */
+    int32_t slots;        /* expert slots in the device banks, >= 1.  layers * experts keeps
+                             every expert resident, which is the B200 configuration. */
+    int32_t shared_inter; /* shared-expert intermediate size (512); 0 = no shared expert calls */
+    int32_t max_tokens;   /* largest token count of one call; scratch is allocated for it here */
+    int32_t ep_rank;      /* expert-parallel rank and size; 0 / 1 on one GPU */
+    int32_t ep_size;
+} ftm_config;
+
+FTM_API int ftm_abi_version(void);
+
+/* Creates the adapter, allocates banks and scratch.  `stream` is the engine's
+ * stream; all work is ordered on it unless a call passes another one. */
+FTM_API int ftm_create(const ftm_config* cfg, void* stream, ftm_handle** out);
+FTM_API void ftm_destroy(ftm_handle* h);
+/* Message of the last failed call; valid until the next call on h.  ftm_last_error(NULL)
+ * returns the message of the last failed ftm_create on this thread. */
+FTM_API const char* ftm_last_error(const ftm_handle* h);
+
+/* ---- ExpertSlotStore (src/domain/expert_kernel.rs:140-161) ------------------------------ */
+
+/* `load(layer, expert, slot)`: copies one expert's six byte fields (bank order) from host
+ * memory into row `slot` of each bank and records the expert as resident in that slot,
+ * displacing the slot's previous occupant (src/infrastructure/cuda_moe.rs:552-576).
+ * lens[b] must equal bank_row_bytes(b) (expert_kernel.rs:211-218).  Synchronous. */
+FTM_API int ftm_load_expert(ftm_handle* h, int32_t layer, int32_t expert, int32_t slot,
+                    const uint8_t* const host_fields[FTM_NUM_BANKS], const size_t lens[FTM_NUM_BANKS]);
+/* same, the six fields already in device memory (asynchronous on the handle's stream) */
+FTM_API int ftm_load_expert_dev(ftm_handle* h, int32_t layer, int32_t expert, int32_t slot,
+                        const void* const dev_fields[FTM_NUM_BANKS], const size_t lens[FTM_NUM_BANKS]);
+FTM_API int ftm_slots(const ftm_handle* h);
+FTM_API int ftm_release_banks(ftm_handle* h);   /* :596-611 frees the banks, keeps the slot count */
+FTM_API int ftm_rehydrate_banks(ftm_handle* h); /* :613-625 reallocates them, every slot empty */
+FTM_API int ftm_banks_resident(const ftm_handle* h);
+/* device base address of each bank, bank order (src/infrastructure/cuda_moe.rs:531-549) */
+FTM_API int ftm_bank_ptrs(const ftm_handle* h, uint64_t out[FTM_NUM_BANKS]);
+/* bytes of one expert's row in bank b (ExpertShapes::bank_row_bytes) */
+FTM_API size_t ftm_bank_row_bytes(const ftm_handle* h, int bank);
+/* slot holding (layer, expert), or -1 */
+FTM_API int32_t ftm_slot_of(const ftm_handle* h, int32_t layer, int32_t expert);
+
+/* ---- ExpertCache, the host slot machine (src/domain/expert_cache.rs:8-134) -------------- */
+/* ensure_experts(layer, routed): marks hits used, assigns LRU victims to the misses
+ * (ascending expert id) and rewrites every routed id to its slot.  Returns FTM_OK and
+ * *n_miss; misses / write_slots need room for n entries.  Purely a plan: the caller
+ * performs the loads (run_experts, src/application/run_experts.rs:209-246). */
+FTM_API int ftm_ensure_experts(ftm_handle* h, int32_t layer, const uint32_t* routed, size_t n,
+                       uint32_t* misses, uint32_t* write_slots, int32_t* rewrites, size_t* n_miss);
+
+/* ---- router (src/models/qwen3_6/forward_cudarc.rs:1403-1435) ---------------------------- */
+/* Fused gate projection + softmax + top-k + renormalise.  x [T, hidden] bf16 dev,
+ * gate_w [experts, hidden] bf16 dev -> ids [T, top_k] i32 dev, weights [T, top_k] f32 dev.
+ * Logits are f32 sums taken over k in ascending order, so the selected ids equal the host
+ * path's (forward.rs:162-179, :793-830); equal probabilities go to the lowest expert index.
+ * Asynchronous. */
+FTM_API int ftm_router(ftm_handle* h, const void* x_bf16, const void* gate_w_bf16, int32_t tokens,
+               int32_t* ids_out, float* weights_out, void* stream);
+/* Tensor::fused_topk_softmax(k) (src/infrastructure/cudarc.rs:1147-1171;
+ * python/ferrum_kernel/elementwise.py:350-382): logits [T, experts] f32 dev. */
+FTM_API int ftm_router_from_logits(ftm_handle* h, const float* logits, int32_t tokens, int32_t* ids_out,
+                           float* weights_out, void* stream);
+
+/* ---- permutation (src/infrastructure/cuda_moe.rs:1198-1253, :2328-2362) ----------------- */
+/* csr_build: route_slot [R] i32 dev -> seg [bins+1] i32 dev (exclusive prefix of per-bin
+ * counts) and route_idx [R] i32 dev (route ids sorted by bin, ascending route id inside a
+ * bin).  A slot outside [0, bins) raises the device flag read by ftm_csr_bad.  Asynchronous. */
+FTM_API int ftm_csr_build(ftm_handle* h, const int32_t* route_slot, int32_t routes, int32_t bins,
+                  int32_t* seg_out, int32_t* route_idx_out, void* stream);
+/* synchronises the stream and returns the flag (0 = all routes were in range) */
+FTM_API int ftm_csr_bad(ftm_handle* h, void* stream, int32_t* bad_out);
+
+/* ---- ExpertGemm (src/domain/expert_kernel.rs:246-294) ----------------------------------- */
+/* grouped_moe(&MoEGroup, &mut [f32]): host hand-off.  x [T, hidden] f32 host (narrowed to bf16
+ * like the reference adapter, cuda_moe.rs:1022-1045), routes [T*top_k] i32 slot ids (-1 = not
+ * resident, contributes nothing), weights [T*top_k] f32, out [T, hidden] f32 host.  Synchronous. */
+FTM_API int ftm_grouped_moe_host(ftm_handle* h, const float* x, size_t x_len, int32_t top_k,
+                         const int32_t* routes, size_t routes_len, const float* weights,
+                         size_t weights_len, float* out, size_t out_len);
+/* grouped_moe_dev: x / weights / out on the device, routes (slot ids) on the host
+ * (expert_kernel.rs:345-352, cuda_moe.rs:1531-1539).  Asynchronous after the routes upload. */
+FTM_API int ftm_grouped_moe_dev(ftm_handle* h, const void* x, int x_dtype, int32_t tokens, int32_t top_k,
+                        const int32_t* routes_host, size_t routes_len, const float* weights_dev,
+                        void* out, int out_dtype, void* stream);
+/* grouped_moe_staged(&MoEDeviceRequest, out): THE SERVING CALL (expert_kernel.rs:261-273,
+ * :332-340; cuda_moe.rs:1545-1622).  experts [T, top_k] are the router's dense expert ids of
+ * `layer` (i32 or i64 dev); the adapter maps them to slots on the device through its residency
+ * table and works on its own copy.  x bf16 or f32, weights f32, out bf16 or f32, exact shape
+ * [T, hidden].  out receives the routed sum only.  Asynchronous, capturable. */
+FTM_API int ftm_moe_layer_staged(ftm_handle* h, int32_t layer, const void* x, int x_dtype,
+                         const void* expert_ids, int ids_dtype, const float* weights,
+                         int32_t tokens, void* out, int out_dtype, int path, void* stream);
+/* begin_staged / PendingMoE::finish (expert_kernel.rs:275-281, :359-361).  With every expert
+ * resident there is no miss copy to overlap, so begin answers FTM_ERR_NOT_SUPPORTED, the
+ * reference's `Ok(None)`: call ftm_moe_layer_staged. */
+FTM_API int ftm_moe_begin(ftm_handle* h, int32_t layer, const void* x, int x_dtype, const void* expert_ids,
+                  int ids_dtype, const float* weights, int32_t tokens, void* stream);
+FTM_API int ftm_moe_finish(ftm_handle* h, void* out, int out_dtype, void* stream);
+/* staged_route_cap (expert_kernel.rs:283-287): largest tokens * top_k of one staged call */
+FTM_API size_t ftm_route_cap(const ftm_handle* h);
+/* reset_staging (expert_kernel.rs:289-293): forgets residency; the banks keep their bytes */
+FTM_API int ftm_reset_staging(ftm_handle* h);
+/* MoEExecutor::steps (expert_kernel.rs:390-395): routed steps run since creation */
+FTM_API uint64_t ftm_steps(const ftm_handle* h);
+
+/* ---- shared expert and combine (forward_cudarc.rs:1455-1562, :1590) --------------------- */
+/* SharedExpertFused::{phase1, phase2} (src/infrastructure/cuda_linear.rs:391-450) and the
+ * T > 1 path (forward_cudarc.rs:1541-1561): shared[t] = down_s(silu(gate_s x) * up_s x),
+ * se_gate[t] = sigmoid(x . shared_gate).  gate_up [2*shared_inter, hidden], down [hidden,
+ * shared_inter], shared_gate [hidden], all bf16 dev.  shared_out [T, hidden] f32 dev receives the
+ * UNGATED shared-expert output, se_gate_out [T] f32 dev the gate.  Asynchronous. */
+FTM_API int ftm_shared_expert(ftm_handle* h, const void* x_bf16, int32_t tokens, const void* gate_up_bf16,
+                      const void* down_bf16, const void* shared_gate_bf16, float* shared_out,
+                      float* se_gate_out, void* stream);
+/* out[t] = se_gate[t] * shared[t] + routed[t]  (forward.rs:737-742, :785-787; `se.add(&routed)`).
+ * routed is [T, hidden] bf16 or f32.  Asynchronous. */
+FTM_API int ftm_combine(ftm_handle* h, const void* routed, int routed_dtype, const float* shared,
+                const float* se_gate, int32_t tokens, void* out, int out_dtype, void* stream);
+
+/* ---- the whole block (moe_parts, forward_cudarc.rs:1388-1591; moe_block, forward.rs:716-791) */
+/* router -> residency rewrite -> routed experts -> fused weighted combine + gated shared
+ * expert, with the shared expert overlapped on a second stream.  ids_out / weights_out may
+ * be NULL.  out [T, hidden] bf16 or f32 dev.  Asynchronous. */
+FTM_API int ftm_moe_block(ftm_handle* h, int32_t layer, const void* x_bf16, int32_t tokens,
+                  const void* gate_w_bf16, const void* sh_gate_up_bf16, const void* sh_down_bf16,
+                  const void* sh_gate_bf16, void* out, int out_dtype, int32_t* ids_out,
+                  float* weights_out, int path, void* stream);
+
+/* ---- per-kernel timing (the reference's FT_PROFILE stage timer, src/infrastructure/profile.rs:1-14) */
+/* While enabled, every kernel launch of h is bracketed by CUDA events on its stream.  Enabling
+ * resets the accumulators; both calls synchronise the device.  Not for use under stream capture. */
+FTM_API int ftm_profile_enable(ftm_handle* h, int on);
+/* accumulated device time and launch count of one kernel kind since profiling was enabled */
+FTM_API int ftm_profile_read(ftm_handle* h, int kind, double* total_ms, uint64_t* launches);
+/* name of kernel kind 0, 1, ..; NULL past the last kind */
+FTM_API const char* ftm_profile_kind_name(int kind);
+
+/* number of this library's kernels launched on h since creation (a diagnostics counter) */
+FTM_API uint64_t ftm_kernel_launches(const ftm_handle* h);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FTMOE_H */

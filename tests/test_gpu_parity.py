@@ -1,0 +1,508 @@
+"""GPU parity: the CUDA path, called through the C ABI, against the CPU checker.
+
+Bars (from the build's target):
+* routed expert ids and the permutation: bit-exact (ties to the lowest expert index);
+* router weights: within 1e-6 of the CPU path (tests/cudarc_forward.rs:253-254 of the reference);
+* layer outputs: relative L2 <= 1e-2, and max |diff| <= 2e-2 of the largest reference magnitude.
+  The synthetic experts (unit globals, block scales up to 1) produce outputs of magnitude ~1e4,
+  where a bf16 ulp alone is 64, so the max-abs bound is taken relative to max |reference| -- the
+  same normalisation the reference's kernel gate uses (python/ferrum_kernel/selftest.py:936).
+"""
+import importlib
+import os
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+pkg = importlib.import_module("ferrum-torrens_b200")
+from oracle import oracle as o  # noqa: E402
+
+REL_L2 = 1e-2
+MAX_ABS_REL = 2e-2
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def dev():
+    return torch.device("cuda:0")
+
+
+def bf16_dev(bits: np.ndarray):
+    return torch.from_numpy(np.ascontiguousarray(bits).view(np.int16)).to(dev()).view(torch.bfloat16)
+
+
+def check_close(got: np.ndarray, want: np.ndarray, rel_l2=REL_L2, max_abs_rel=MAX_ABS_REL):
+    denom = np.linalg.norm(want)
+    rel = np.linalg.norm(got - want) / max(denom, 1e-30)
+    mx = np.abs(got - want).max() / max(np.abs(want).max(), 1e-30)
+    assert rel <= rel_l2, f"relative L2 {rel:.3e}"
+    assert mx <= max_abs_rel, f"max abs (relative to max |ref|) {mx:.3e}"
+    return rel, mx
+
+
+def oracle_layer(lay):
+    banks = o.HostBanks(*lay.banks, slots=lay.experts, gu_rows=2 * lay.inter, gu_cols=lay.hidden,
+                        dn_rows=lay.hidden, dn_cols=lay.inter)
+    return o.Layer(lay.hidden, lay.inter, lay.experts, lay.top_k, lay.shared_inter, lay.gate_w, lay.sh_gate_up,
+                   lay.sh_down, lay.sh_gate, banks)
+
+
+def make_moe(lay, max_tokens=256, layers=1, slots=None):
+    moe = pkg.B200MoE(0, pkg.ExpertShapes(lay.hidden, lay.inter), slots or lay.experts * layers, experts=lay.experts,
+                      layers=layers, top_k=lay.top_k, shared_inter=lay.shared_inter, max_tokens=max_tokens)
+    return moe
+
+
+def load_all(moe, lay, layer=0, slot0=0):
+    for e in range(lay.experts):
+        moe.load(layer, e, slot0 + e, lay.fields(e))
+
+
+# ------------------------------------------------------------------ small layer shared by many tests
+@pytest.fixture(scope="module")
+def small():
+    lay = pkg.synth.make_layer(11, hidden=256, inter=128, experts=32, top_k=4, shared_inter=64)
+    moe = make_moe(lay, max_tokens=4096)
+    load_all(moe, lay)
+    yield lay, moe, oracle_layer(lay)
+    moe.close()
+
+
+@pytest.fixture(scope="module")
+def full():
+    """The benchmark layer: hidden 2048, inter 512, 256 experts, top-8, shared 512."""
+    lay = pkg.synth.make_layer(2024)
+    moe = make_moe(lay, max_tokens=2048)
+    load_all(moe, lay)
+    yield lay, moe, oracle_layer(lay)
+    moe.close()
+
+
+# ------------------------------------------------------------------ router
+@pytest.mark.parametrize("tokens", [1, 3, 8, 33, 300])
+def test_router_ids_bit_exact_small(small, tokens):
+    lay, moe, ol = small
+    xb = pkg.synth.make_x(tokens, tokens, lay.hidden)
+    ids, w = moe.router(bf16_dev(xb), bf16_dev(lay.gate_w))
+    want_ids, want_w = o.router(ol, pkg.synth.bf16_bits_to_f32(xb))
+    assert np.array_equal(ids.cpu().numpy(), want_ids)
+    assert np.abs(w.cpu().numpy() - want_w).max() <= 1e-6
+    assert np.array_equal(w.cpu().numpy(), want_w), "same operations in the same order: weights are bit-equal too"
+
+
+@pytest.mark.parametrize("tokens", [1, 16, 64, 512])
+def test_router_ids_bit_exact_full(full, tokens):
+    lay, moe, ol = full
+    xb = pkg.synth.make_x(100 + tokens, tokens, lay.hidden)
+    ids, w = moe.router(bf16_dev(xb), bf16_dev(lay.gate_w))
+    want_ids, want_w = o.router(ol, pkg.synth.bf16_bits_to_f32(xb))
+    assert np.array_equal(ids.cpu().numpy(), want_ids)
+    assert np.abs(w.cpu().numpy() - want_w).max() <= 1e-6
+
+
+def test_router_ties_take_the_lowest_index(small):
+    lay, moe, _ = small
+    e = lay.experts
+    logits = np.zeros((3, e), np.float32)
+    logits[1, [5, 9, 20]] = 2.0          # three-way tie on top, the rest tie at zero
+    logits[2] = np.linspace(1, 0, e)     # strictly descending: ids 0..k-1
+    ids, w = moe.fused_topk_softmax(torch.from_numpy(logits).to(dev()))
+    ids = ids.cpu().numpy()
+    assert ids[0].tolist() == [0, 1, 2, 3]
+    assert ids[1].tolist() == [5, 9, 20, 0]
+    assert ids[2].tolist() == [0, 1, 2, 3]
+    want_ids, want_w = o.topk_renorm(o.softmax_rows(logits), lay.top_k)
+    assert np.array_equal(ids, want_ids)
+    assert np.array_equal(w.cpu().numpy(), want_w)
+    assert np.allclose(w.cpu().numpy().sum(1), 1.0, atol=1e-6)
+
+
+def test_router_from_logits_matches_reference_topk_case(small):
+    """forward.rs:1229-1236 in probability form: p = [.5, .2, .3] -> ids [0, 2]."""
+    lay, moe, _ = small
+    logits = np.full((1, lay.experts), -30.0, np.float32)
+    logits[0, :3] = np.log(np.array([0.5, 0.2, 0.3], np.float32))
+    ids, w = moe.fused_topk_softmax(torch.from_numpy(logits).to(dev()))
+    assert ids.cpu().numpy()[0, :2].tolist() == [0, 2]
+
+
+# ------------------------------------------------------------------ permutation
+CSR_CASES = [([2, 0, 2, 0, 0, 1], 3), ([0] * 37, 8), ([7], 8), ([3, 3, 3, 1, 1, 2, 2, 2, 2], 8), ([5, 5, 5, 5], 8)]
+
+
+@pytest.mark.parametrize("routes,bins", CSR_CASES)
+def test_csr_reference_cases(small, routes, bins):
+    """cuda_moe.rs:2718-2720 and the fixed cases of :2764-2769."""
+    _, moe, _ = small
+    seg, idx, badf = moe.csr_build(torch.tensor(routes, dtype=torch.int32, device=dev()), bins)
+    want_seg, want_idx = o.build_grouped_csr(routes, bins)
+    assert seg.cpu().numpy().tolist() == want_seg.tolist()
+    assert idx.cpu().numpy().tolist() == want_idx.tolist()
+    assert badf == 0
+    if routes == [2, 0, 2, 0, 0, 1]:
+        assert want_seg.tolist() == [0, 3, 4, 6] and want_idx.tolist() == [1, 3, 4, 5, 0, 2]
+
+
+@pytest.mark.parametrize("n,bins", [(1, 8), (2, 8), (7, 8), (33, 8), (128, 8), (1025, 8), (2048, 256), (2049, 256),
+                                    (16384, 256), (13001, 32)])
+def test_csr_random_matches_host(small, n, bins):
+    """xorshift-seeded cases as in cuda_moe.rs:2752-2772, plus multi-CTA sizes."""
+    _, moe, _ = small
+    seed = 0x2545F4914F6CDD1D
+    vals = []
+    for _ in range(n):
+        seed ^= (seed << 13) & 0xFFFFFFFFFFFFFFFF
+        seed ^= seed >> 7
+        seed ^= (seed << 17) & 0xFFFFFFFFFFFFFFFF
+        vals.append(seed % bins)
+    seg, idx, badf = moe.csr_build(torch.tensor(vals, dtype=torch.int32, device=dev()), bins)
+    want_seg, want_idx = o.build_grouped_csr(vals, bins)
+    assert np.array_equal(seg.cpu().numpy(), want_seg)
+    assert np.array_equal(idx.cpu().numpy(), want_idx)
+    assert badf == 0
+    # size-independent properties: a complete permutation, sorted by bin, ascending inside a bin
+    got = idx.cpu().numpy()
+    assert np.array_equal(np.sort(got), np.arange(n))
+    b = np.asarray(vals)[got]
+    assert (np.diff(b) >= 0).all()
+    assert all((np.diff(got[seg_a:seg_b]) > 0).all() for seg_a, seg_b in zip(want_seg[:-1], want_seg[1:]))
+
+
+def test_csr_flags_slots_outside_the_bank(small):
+    _, moe, _ = small
+    for routes in ([-1, 0], [3]):
+        _, _, badf = moe.csr_build(torch.tensor(routes, dtype=torch.int32, device=dev()), 3)
+        assert badf == 1
+
+
+# ------------------------------------------------------------------ routed half, known answers
+H16 = 16
+F16 = {0.5: 0x3800, 1.0: 0x3C00, -1.0: 0xBC00, 4.0: 0x4400}
+
+
+def slab(rows, cols, packed, scale, glob):
+    g = np.tile(np.array([F16[glob] & 0xFF, F16[glob] >> 8], np.uint8), rows)
+    return [np.full(rows * cols // 2, packed, np.uint8), np.full(rows * cols // 16, scale, np.uint8), g]
+
+
+def tiny_moe(gus, dns, h=H16, i=H16, top_k=1):
+    moe = pkg.B200MoE(0, pkg.ExpertShapes(h, i), len(gus), experts=len(gus), layers=1, top_k=top_k, shared_inter=16,
+                      max_tokens=8)
+    for s, (g, d) in enumerate(zip(gus, dns)):
+        moe.load(0, s, s, [*g, *d])
+    return moe
+
+
+def silu(v):
+    v = np.float32(v)
+    return float(v / (np.float32(1.0) + np.exp(-v, dtype=np.float32)))
+
+
+def run_host(moe, h, i, x, top_k, routes, weights):
+    out = np.full(len(x) // h * h, 7.0, np.float32)
+    moe.grouped_moe(pkg.MoEGroup(h, i, np.asarray(x, np.float32), top_k, np.asarray(routes, np.int32),
+                                 np.asarray(weights, np.float32)), out)
+    return out
+
+
+def test_hand_computed_case_matches():
+    """expert_kernel.rs:744-790"""
+    moe = tiny_moe([slab(32, 16, 0x10, 0x38, 1.0)], [slab(16, 16, 0x10, 0x38, 1.0)])
+    out = run_host(moe, 16, 16, np.ones(16), 1, [0], [0.5])
+    want = 0.5 * (8.0 * 0.5 * silu(4.0) * 4.0)
+    assert np.allclose(out, want, rtol=1e-4)
+    moe.close()
+
+
+def test_non_resident_route_contributes_nothing():
+    """expert_kernel.rs:851-888"""
+    moe = tiny_moe([slab(32, 16, 0x10, 0x38, 1.0)], [slab(16, 16, 0x10, 0x38, 1.0)])
+    out = run_host(moe, 16, 16, np.ones(16), 1, [-1], [1.0])
+    assert np.array_equal(out, np.zeros(16, np.float32))
+    moe.close()
+
+
+def test_slot_selects_its_own_expert_and_cancelling_routes():
+    """expert_kernel.rs:890-979 and :792-849"""
+    moe = tiny_moe([slab(32, 16, 0x01, 0x38, 1.0), slab(32, 16, 0x10, 0x38, 1.0)],
+                   [slab(16, 16, 0x01, 0x38, 1.0), slab(16, 16, 0x10, 0x38, 1.0)])
+    x = np.array([1.0 if k % 2 == 0 else 2.0 for k in range(16)], np.float32)
+    assert np.allclose(run_host(moe, 16, 16, x, 1, [0], [1.0]), 8.0 * 0.5 * silu(4.0) * 4.0, rtol=1e-4)
+    assert np.allclose(run_host(moe, 16, 16, x, 1, [1], [1.0]), 8.0 * 0.5 * silu(8.0) * 8.0, rtol=1e-4)
+    moe.close()
+    moe = tiny_moe([slab(32, 16, 0x10, 0x38, 1.0)] * 2, [slab(16, 16, 0x10, 0x38, 1.0), slab(16, 16, 0x10, 0x38, -1.0)],
+                   top_k=2)
+    out = run_host(moe, 16, 16, np.ones(16), 2, [0, 1], [1.0, 1.0])
+    assert np.abs(out).max() <= 1e-4 * 2 * 4.0 * silu(4.0) * 4.0
+    moe.close()
+
+
+def test_global_and_block_scales():
+    """expert_kernel.rs:981-1023 and :1025-1075"""
+    moe = tiny_moe([slab(32, 16, 0x10, 0x38, 4.0)], [slab(16, 16, 0x10, 0x38, 0.5)])
+    out = run_host(moe, 16, 16, np.ones(16), 1, [0], [1.0])
+    ic2 = silu(16.0) * 16.0
+    assert np.allclose(out, 8.0 * 0.5 * ic2 * 0.5, rtol=1e-4)
+    moe.close()
+    s1 = slab(32, 32, 0x10, 0x40, 1.0)
+    s1[1] = np.array([0x40 if b % 2 == 1 else 0x38 for b in range(32 * 32 // 16)], np.uint8)
+    moe = tiny_moe([slab(32, 32, 0x10, 0x38, 1.0), s1], [slab(32, 16, 0x10, 0x38, 1.0)] * 2, h=32, i=16)
+    out = run_host(moe, 32, 16, np.ones(32), 1, [1], [1.0])
+    ic2 = silu(12.0) * 12.0
+    assert np.allclose(out, 8.0 * 0.5 * ic2, rtol=1e-4)
+    moe.close()
+
+
+def test_shape_and_slot_mismatches_are_errors():
+    """expert_kernel.rs:1141-1181; the adapter validates before any launch (cuda_moe.rs:959-1003)."""
+    moe = tiny_moe([slab(32, 16, 0x10, 0x38, 1.0)], [slab(16, 16, 0x10, 0x38, 1.0)])
+    with pytest.raises(pkg.MoEError) as e:
+        run_host(moe, 32, 16, np.ones(16), 1, [0], [1.0])
+    assert e.value.kind == "Bad"
+    with pytest.raises(pkg.MoEError) as e:
+        run_host(moe, 16, 16, np.ones(16), 1, [5], [1.0])
+    assert e.value.kind == "SlotOutOfRange" and "slot 5 out of range (capacity 1)" in str(e.value)
+    with pytest.raises(pkg.MoEError) as e:
+        run_host(moe, 16, 16, np.ones(16), 1, [0, 0], [1.0, 1.0])
+    assert e.value.kind == "Bad"
+    with pytest.raises(pkg.MoEError) as e:
+        moe.load(0, 0, 3, [*slab(32, 16, 0, 0, 1.0), *slab(16, 16, 0, 0, 1.0)])
+    assert e.value.kind == "SlotOutOfRange"
+    with pytest.raises(pkg.MoEError) as e:
+        moe.load(0, 0, 0, [*slab(32, 16, 0, 0, 1.0), *slab(16, 32, 0, 0, 1.0)])
+    assert e.value.kind == "Bad"
+    moe.close()
+
+
+# ------------------------------------------------------------------ routed half vs the reference's torch oracle
+def _golden():
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("make_golden", os.path.join(HERE, "golden", "make_golden.py"))
+    mg = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mg)
+    return mg, np.load(os.path.join(HERE, "golden", "ref_torch_oracle.npz"))
+
+
+@pytest.mark.parametrize("case", [0, 1, 2])
+def test_routed_half_matches_reference_fixtures(case):
+    mg, G = _golden()
+    label, tokens, hidden, inter, slots, top_k, seed = mg.LARGE_CASES[case]
+    x, gu, dn, slot, weight = mg.golden_inputs(tokens, hidden, inter, slots, top_k, seed)
+    moe = pkg.B200MoE(0, pkg.ExpertShapes(hidden, inter), slots, experts=slots, layers=1, top_k=top_k,
+                      shared_inter=16, max_tokens=16)
+    for s in range(slots):
+        moe.load(0, s, s, [gu[0][s], gu[1][s], gu[2][s].view(np.uint8), dn[0][s], dn[1][s], dn[2][s].view(np.uint8)])
+    out = run_host(moe, hidden, inter, x.reshape(-1), top_k, slot, weight).reshape(tokens, hidden)
+    want = G[f"{label}/want"]
+    banks = o.HostBanks(gu[0], gu[1], gu[2].view(np.uint8), dn[0], dn[1], dn[2].view(np.uint8), slots, 2 * inter,
+                        hidden, hidden, inter)
+    mine, abs_sum = o.grouped_moe_reference(banks, hidden, inter, x, top_k, slot, weight, want_abs_sum=True)
+    # the reference's own yardstick: error against the size of the summed terms (f32 path: 1e-5)
+    assert np.abs(out - want).max() <= 2e-5 * abs_sum.max()
+    assert np.abs(out - mine).max() <= 2e-5 * abs_sum.max()
+    moe.close()
+
+
+# ------------------------------------------------------------------ device hand-offs on a small layer
+@pytest.mark.parametrize("tokens", [1, 5, 64, 257])
+@pytest.mark.parametrize("xdt,odt", [("bf16", "bf16"), ("f32", "f32")])
+def test_staged_call_matches_cpu_path(small, tokens, xdt, odt):
+    lay, moe, ol = small
+    rng = np.random.default_rng(tokens)
+    xb = pkg.synth.make_x(tokens + 7, tokens, lay.hidden)
+    xf = pkg.synth.bf16_bits_to_f32(xb)
+    ids = np.stack([rng.permutation(lay.experts)[:lay.top_k] for _ in range(tokens)]).astype(np.int32)
+    w = rng.uniform(0.05, 0.5, (tokens, lay.top_k)).astype(np.float32)
+    x_d = bf16_dev(xb) if xdt == "bf16" else torch.from_numpy(xf).to(dev())
+    out = torch.empty((tokens, lay.hidden), dtype=torch.bfloat16 if odt == "bf16" else torch.float32, device=dev())
+    before = moe.steps()
+    req = pkg.MoEDeviceRequest(0, lay.hidden, lay.inter, lay.top_k, x_d, torch.from_numpy(ids).to(dev()),
+                               torch.from_numpy(w).to(dev()))
+    moe.grouped_moe_staged(req, out)
+    torch.cuda.synchronize()
+    assert moe.steps() == before + 1
+    want = o.grouped_moe_reference_mt(ol.banks, lay.hidden, lay.inter, xf, lay.top_k, ids.reshape(-1), w.reshape(-1))
+    check_close(out.float().cpu().numpy(), want)
+    # i64 ids are accepted too (cuda_moe.rs:67-86)
+    req64 = pkg.MoEDeviceRequest(0, lay.hidden, lay.inter, lay.top_k, x_d, torch.from_numpy(ids.astype(np.int64)).to(dev()),
+                                 torch.from_numpy(w).to(dev()))
+    out2 = torch.empty_like(out)
+    moe.grouped_moe_staged(req64, out2)
+    torch.cuda.synchronize()
+    assert torch.equal(out, out2)
+
+
+def test_device_group_with_host_routes_and_missing_slots(small):
+    lay, moe, ol = small
+    tokens = 6
+    rng = np.random.default_rng(5)
+    xb = pkg.synth.make_x(55, tokens, lay.hidden)
+    xf = pkg.synth.bf16_bits_to_f32(xb)
+    routes = rng.integers(-1, lay.experts, tokens * lay.top_k).astype(np.int32)
+    routes[:3] = -1
+    w = rng.uniform(0.05, 0.5, tokens * lay.top_k).astype(np.float32)
+    out = torch.empty((tokens, lay.hidden), dtype=torch.float32, device=dev())
+    moe.grouped_moe_dev(lay.hidden, lay.inter, lay.top_k, bf16_dev(xb), routes, torch.from_numpy(w).to(dev()), out)
+    torch.cuda.synchronize()
+    want = o.grouped_moe_reference(ol.banks, lay.hidden, lay.inter, xf, lay.top_k, routes, w)
+    check_close(out.cpu().numpy(), want)
+    with pytest.raises(pkg.MoEError) as e:
+        bad_routes = routes.copy()
+        bad_routes[0] = lay.experts + 3
+        moe.grouped_moe_dev(lay.hidden, lay.inter, lay.top_k, bf16_dev(xb), bad_routes, torch.from_numpy(w).to(dev()), out)
+    assert e.value.kind == "SlotOutOfRange"
+
+
+def test_shared_expert_and_combine(small):
+    lay, moe, ol = small
+    tokens = 19
+    xb = pkg.synth.make_x(9, tokens, lay.hidden)
+    xf = pkg.synth.bf16_bits_to_f32(xb)
+    shared, gate = moe.shared_expert(bf16_dev(xb), bf16_dev(lay.sh_gate_up), bf16_dev(lay.sh_down), bf16_dev(lay.sh_gate))
+    torch.cuda.synchronize()
+    want = o.shared_expert(ol, xf)
+    check_close(shared.cpu().numpy(), want, rel_l2=1e-4, max_abs_rel=1e-4)
+    g = o.bf16_gemm(xf, lay.sh_gate, tokens, 1, lay.hidden).reshape(-1)
+    want_gate = np.array([o.sigmoid(float(v)) for v in g], np.float32)
+    assert np.abs(gate.cpu().numpy() - want_gate).max() <= 1e-5
+    routed = torch.randn((tokens, lay.hidden), device=dev())
+    out = torch.empty((tokens, lay.hidden), dtype=torch.float32, device=dev())
+    moe.combine(routed, shared, gate, out)
+    torch.cuda.synchronize()
+    assert torch.allclose(out, shared * gate[:, None] + routed, rtol=1e-6, atol=1e-6)
+
+
+@pytest.mark.parametrize("tokens", [1, 7, 64, 300])
+def test_whole_block_small(small, tokens):
+    lay, moe, ol = small
+    xb = pkg.synth.make_x(1000 + tokens, tokens, lay.hidden)
+    out = torch.empty((tokens, lay.hidden), dtype=torch.bfloat16, device=dev())
+    ids = torch.empty((tokens, lay.top_k), dtype=torch.int32, device=dev())
+    w = torch.empty((tokens, lay.top_k), dtype=torch.float32, device=dev())
+    moe.moe_block(0, bf16_dev(xb), bf16_dev(lay.gate_w), bf16_dev(lay.sh_gate_up), bf16_dev(lay.sh_down),
+                  bf16_dev(lay.sh_gate), out, ids_out=ids, weights_out=w)
+    torch.cuda.synchronize()
+    want, want_ids, want_w = o.moe_block(ol, pkg.synth.bf16_bits_to_f32(xb), threads=o.max_threads())
+    assert np.array_equal(ids.cpu().numpy(), want_ids)
+    assert np.abs(w.cpu().numpy() - want_w).max() <= 1e-6
+    check_close(out.float().cpu().numpy(), want)
+
+
+# ------------------------------------------------------------------ the benchmark layer (configs 1 and 2)
+@pytest.mark.parametrize("tokens", [16, 1, 8, 64])
+def test_whole_block_full_size(full, tokens):
+    """Config 1 (T=16) and the decode sizes of config 2 at hidden 2048 / 256 experts / top-8."""
+    lay, moe, ol = full
+    xb = pkg.synth.make_x(4242 + tokens, tokens, lay.hidden)
+    out = torch.empty((tokens, lay.hidden), dtype=torch.bfloat16, device=dev())
+    ids = torch.empty((tokens, lay.top_k), dtype=torch.int32, device=dev())
+    w = torch.empty((tokens, lay.top_k), dtype=torch.float32, device=dev())
+    moe.moe_block(0, bf16_dev(xb), bf16_dev(lay.gate_w), bf16_dev(lay.sh_gate_up), bf16_dev(lay.sh_down),
+                  bf16_dev(lay.sh_gate), out, ids_out=ids, weights_out=w)
+    torch.cuda.synchronize()
+    want, want_ids, want_w = o.moe_block(ol, pkg.synth.bf16_bits_to_f32(xb), threads=o.max_threads())
+    assert np.array_equal(ids.cpu().numpy(), want_ids), "routed expert ids must be bit-exact"
+    assert np.abs(w.cpu().numpy() - want_w).max() <= 1e-6
+    check_close(out.float().cpu().numpy(), want)
+    # permutation of these routes: bit-exact against the host CSR
+    seg, idx, badf = moe.csr_build(ids.reshape(-1), lay.experts)
+    want_seg, want_idx = o.build_grouped_csr(want_ids.reshape(-1), lay.experts)
+    assert np.array_equal(seg.cpu().numpy(), want_seg) and np.array_equal(idx.cpu().numpy(), want_idx) and badf == 0
+
+
+def test_linearity_in_route_weights_full_size(full):
+    """A size-independent property of the routed half: doubling the route weights doubles the sum."""
+    lay, moe, _ = full
+    tokens = 32
+    xb = pkg.synth.make_x(77, tokens, lay.hidden)
+    rng = np.random.default_rng(3)
+    ids = np.stack([rng.permutation(lay.experts)[:lay.top_k] for _ in range(tokens)]).astype(np.int32)
+    w = rng.uniform(0.05, 0.5, (tokens, lay.top_k)).astype(np.float32)
+    outs = []
+    for scale in (1.0, 2.0):
+        out = torch.empty((tokens, lay.hidden), dtype=torch.float32, device=dev())
+        req = pkg.MoEDeviceRequest(0, lay.hidden, lay.inter, lay.top_k, bf16_dev(xb), torch.from_numpy(ids).to(dev()),
+                                   torch.from_numpy(w * np.float32(scale)).to(dev()))
+        moe.grouped_moe_staged(req, out)
+        torch.cuda.synchronize()
+        outs.append(out.cpu().numpy())
+    assert np.array_equal(outs[1], 2.0 * outs[0])
+
+
+# ------------------------------------------------------------------ slot store behaviour
+def test_slot_store_release_rehydrate_and_residency():
+    lay = pkg.synth.make_layer(5, hidden=64, inter=32, experts=4, top_k=2, shared_inter=16)
+    moe = make_moe(lay, max_tokens=8, layers=2, slots=8)
+    assert moe.slots() == 8 and moe.banks_resident()
+    ptrs = moe.bank_ptrs()
+    assert len(ptrs) == 6 and all(p % 256 == 0 for p in ptrs)
+    load_all(moe, lay, layer=1, slot0=4)
+    assert moe.bank_ptrs() == ptrs, "bank addresses are stable for the adapter's life"
+    assert moe.slot_of(1, 2) == 6 and moe.slot_of(0, 2) == -1
+    # a layer whose experts are not resident contributes nothing (slot -1)
+    xb = pkg.synth.make_x(1, 3, 64)
+    ids = torch.tensor([[0, 1], [2, 3], [1, 2]], dtype=torch.int32, device=dev())
+    w = torch.full((3, 2), 0.5, device=dev())
+    out = torch.empty((3, 64), dtype=torch.float32, device=dev())
+    moe.grouped_moe_staged(pkg.MoEDeviceRequest(0, 64, 32, 2, bf16_dev(xb), ids, w), out)
+    torch.cuda.synchronize()
+    assert float(out.abs().max()) == 0.0
+    moe.grouped_moe_staged(pkg.MoEDeviceRequest(1, 64, 32, 2, bf16_dev(xb), ids, w), out)
+    torch.cuda.synchronize()
+    assert float(out.abs().max()) > 0.0
+    # loading another expert into an occupied slot displaces the occupant
+    moe.load(0, 0, 4, lay.fields(0))
+    assert moe.slot_of(0, 0) == 4 and moe.slot_of(1, 0) == -1
+    moe.reset_staging()
+    assert moe.slot_of(0, 0) == -1
+    moe.release_banks()
+    assert not moe.banks_resident()
+    with pytest.raises(pkg.MoEError):
+        moe.grouped_moe_staged(pkg.MoEDeviceRequest(1, 64, 32, 2, bf16_dev(xb), ids, w), out)
+    moe.rehydrate_banks()
+    assert moe.banks_resident() and moe.slot_of(1, 2) == -1
+    assert moe.begin_staged(pkg.MoEDeviceRequest(1, 64, 32, 2, bf16_dev(xb), ids, w)) is None
+    assert moe.staged_route_cap() == 8 * 2
+    moe.close()
+
+
+def test_host_plan_executor_matches_staged_executor():
+    """run_experts / CachedExperts (src/application/run_experts.rs): host plan with a slot cache that
+    holds every expert gives the same sum as the device-staged path."""
+    lay = pkg.synth.make_layer(6, hidden=64, inter=32, experts=8, top_k=2, shared_inter=16)
+
+    class Source:
+        def slab(self, layer, expert, part):
+            f = lay.fields(expert)
+            return f[:3] if part == "GateUp" else f[3:]
+
+    moe = pkg.B200MoE(0, pkg.ExpertShapes(64, 32), 8, source=Source(), experts=8, layers=1, top_k=2, shared_inter=16,
+                      max_tokens=8)
+    tokens = 5
+    xb = pkg.synth.make_x(2, tokens, 64)
+    xf = pkg.synth.bf16_bits_to_f32(xb)
+    rng = np.random.default_rng(1)
+    experts = np.stack([rng.permutation(8)[:2] for _ in range(tokens)]).astype(np.uint32)
+    w = rng.uniform(0.1, 0.6, (tokens, 2)).astype(np.float32)
+    out = np.zeros(tokens * 64, np.float32)
+    cache = pkg.ExpertCache(moe)
+    pkg.run_experts(cache, moe, moe, 0, 64, 32, 2, xf, experts, w, out)
+    ol = oracle_layer(lay)
+    want = o.grouped_moe_reference(ol.banks, 64, 32, xf, 2, experts.astype(np.int32).reshape(-1), w.reshape(-1))
+    check_close(out.reshape(tokens, 64), want)
+    ex = pkg.CachedExperts(moe, staged=True)
+    out_d = torch.empty((tokens, 64), dtype=torch.float32, device=dev())
+    req = pkg.MoEDeviceRequest(0, 64, 32, 2, bf16_dev(xb), torch.from_numpy(experts.astype(np.int32)).to(dev()),
+                               torch.from_numpy(w).to(dev()))
+    ex.execute_device(req, out_d)
+    torch.cuda.synchronize()
+    assert ex.steps() == 1
+    assert np.array_equal(out_d.cpu().numpy().reshape(-1), out)
+    ex2 = pkg.CachedExperts(moe, staged=False)
+    out_h = torch.empty((tokens, 64), dtype=torch.float32, device=dev())
+    ex2.execute_device(req, out_h)
+    torch.cuda.synchronize()
+    assert np.array_equal(out_h.cpu().numpy().reshape(-1), out)
+    moe.close()
