@@ -13,7 +13,7 @@ LIB_PATH = os.path.join(HERE, "libftmoe.so")
 
 OK, ERR_BAD, ERR_SLOT_OUT_OF_RANGE, ERR_MISSING, ERR_OUT_OF_MEMORY, ERR_READ, ERR_NOT_SUPPORTED, ERR_CUDA = range(8)
 BF16, F32, I32, I64 = range(4)
-PATH_AUTO, PATH_GEMV, PATH_GROUPED = range(3)
+PATH_AUTO, PATH_GEMV, PATH_GROUPED, PATH_SCALAR = range(4)
 NUM_BANKS = 6
 
 
@@ -50,6 +50,7 @@ _PROTOS = {
     "ftm_route_cap": (_sz, [_vp]),
     "ftm_reset_staging": (_int, [_vp]),
     "ftm_steps": (C.c_uint64, [_vp]),
+    "ftm_sync_status": (_int, [_vp, _vp]),
     "ftm_shared_expert": (_int, [_vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp]),
     "ftm_combine": (_int, [_vp, _vp, _int, _vp, _vp, _i32, _vp, _int, _vp]),
     "ftm_moe_block": (_int, [_vp, _i32, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _int, _vp, _vp, _int, _vp]),

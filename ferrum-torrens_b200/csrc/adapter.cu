@@ -26,7 +26,8 @@ thread_local std::string g_create_error;
 
 const char* const kKindNames[K_NUM_KINDS] = {
     "router_logits", "router_topk", "slot_rewrite", "csr_build", "expert_gate_up", "expert_down", "sum_routes",
-    "shared_phase1", "shared_phase2", "cast_bf16",   "combine",  "grouped_gate_up", "grouped_down"};
+    "shared_phase1", "shared_phase2", "cast_bf16",   "combine",  "grouped_gate_up", "grouped_down",
+    "permute_act",   "decode_plan"};
 
 }  // namespace
 
@@ -108,6 +109,10 @@ struct ftm_handle {
     int32_t *csr_scratch = nullptr, *flags = nullptr, *ids = nullptr;
     float *ic2 = nullptr, *yroute = nullptr, *logits = nullptr, *rweights = nullptr;
     float *ic2s = nullptr, *shared_out = nullptr, *se_gate = nullptr, *routed_f32 = nullptr;
+    __nv_bfloat16 *xperm = nullptr, *ic2p = nullptr;
+    int4* groups = nullptr;
+    int32_t *sorted_route = nullptr, *n_groups = nullptr;
+    int sm_count = 148;
     std::vector<void*> allocs;
 
     uint64_t steps = 0;
@@ -210,9 +215,16 @@ int check_tokens(const ftm_handle* h, int64_t tokens, int top_k) {
 int run_routed(ftm_handle* h, const __nv_bfloat16* x, const int32_t* route_slot, const float* weights, int tokens,
                const float* shared, const float* se_gate, cudaEvent_t join, void* out, int out_dtype, int path,
                cudaStream_t s) {
-    (void)path;
     BankView b = bank_view(h);
-    h->launches += launch_decode_routes(b, x, route_slot, weights, tokens, h->cfg.top_k, h->ic2, h->yroute, h->ctx(s));
+    const int routes = tokens * h->cfg.top_k;
+    if (path != FTM_PATH_SCALAR && decode_mma_supported(h->cfg.hidden, h->cfg.inter, routes)) {
+        DecodeScratch sc{h->xperm, h->ic2p, h->groups, h->sorted_route, h->n_groups, h->yroute, h->flags + 2};
+        h->launches += launch_decode_mma(b, x, FTM_BF16, route_slot, weights, tokens, h->cfg.top_k, sc, h->sm_count,
+                                         h->ctx(s));
+    } else {
+        h->launches += launch_decode_routes(b, x, route_slot, weights, tokens, h->cfg.top_k, h->ic2, h->yroute,
+                                            h->ctx(s));
+    }
     if (join) CU(h, cudaStreamWaitEvent(s, join, 0));
     h->launches += launch_sum_routes(h->yroute, tokens, h->cfg.top_k, h->cfg.hidden, shared, se_gate, out, out_dtype, h->ctx(s));
     return FTM_OK;
@@ -307,6 +319,12 @@ FTM_API int ftm_create(const ftm_config* c, void* stream, ftm_handle** out) {
     A(dev_alloc(hp, &h->shared_out, T * H));
     A(dev_alloc(hp, &h->se_gate, T));
     A(dev_alloc(hp, &h->routed_f32, T * H));
+    A(dev_alloc(hp, &h->xperm, T * H));
+    A(dev_alloc(hp, &h->ic2p, R * I));
+    A(dev_alloc(hp, &h->groups, R));
+    A(dev_alloc(hp, &h->sorted_route, R));
+    A(dev_alloc(hp, &h->n_groups, 1));
+    cudaDeviceGetAttribute(&h->sm_count, cudaDevAttrMultiProcessorCount, c->ordinal);
     (void)bins;
     if (rc == FTM_OK) {
         e = cudaMemset(h->d_slot_for_id, 0xff, n_ids * sizeof(int32_t));
@@ -597,7 +615,7 @@ static int staged_locked(ftm_handle* h, int32_t layer, const void* x, int x_dtyp
     if (ids_dtype != FTM_I32 && ids_dtype != FTM_I64 && ids_dtype != FTM_F32)
         return fail(h, FTM_ERR_BAD, "moe: expert ids cannot be dtype %d", ids_dtype);
     if (out_dtype != FTM_BF16 && out_dtype != FTM_F32) return fail(h, FTM_ERR_BAD, "moe: out cannot be dtype %d", out_dtype);
-    if (path < FTM_PATH_AUTO || path > FTM_PATH_GROUPED) return fail(h, FTM_ERR_BAD, "moe: unknown path %d", path);
+    if (path < FTM_PATH_AUTO || path > FTM_PATH_SCALAR) return fail(h, FTM_ERR_BAD, "moe: unknown path %d", path);
     const __nv_bfloat16* xb = nullptr;
     if ((rc = stage_x(h, x, x_dtype, tokens, &xb, s)) != FTM_OK) return rc;
     const int R = tokens * h->cfg.top_k;
@@ -646,6 +664,25 @@ FTM_API int ftm_reset_staging(ftm_handle* h) {
 }
 
 FTM_API uint64_t ftm_steps(const ftm_handle* h) { return h ? h->steps : 0; }
+
+FTM_API int ftm_sync_status(ftm_handle* h, void* stream) {
+    if (!h) return FTM_ERR_BAD;
+    std::lock_guard<std::mutex> lk(h->mu);
+    cudaStream_t s = pick(h, stream);
+    int32_t f[8] = {};
+    CU(h, cudaMemcpyAsync(f, h->flags, sizeof f, cudaMemcpyDeviceToHost, s));
+    CU(h, cudaStreamSynchronize(s));
+    if (f[2]) {
+        cudaMemsetAsync(h->flags + 2, 0, sizeof(int32_t), s);
+        return fail(h, FTM_ERR_CUDA, "moe: driver: a kernel gave up a bounded wait (code %d); the step's output is invalid",
+                    f[2]);
+    }
+    if (f[1]) {
+        cudaMemsetAsync(h->flags + 1, 0, sizeof(int32_t), s);
+        return fail(h, FTM_ERR_BAD, "moe: an expert id was outside [0, %d)", h->cfg.experts);
+    }
+    return FTM_OK;
+}
 
 FTM_API int ftm_profile_enable(ftm_handle* h, int on) {
     if (!h) return FTM_ERR_BAD;

@@ -1,0 +1,584 @@
+// Routed experts for small batches (decode): a bandwidth-bound grouped GEMV.
+//
+// Same arithmetic as the per-route kernels in decode_gemv.cu (reference:
+// src/domain/expert_kernel.rs:547-618, python/ferrum_kernel/nvfp4_moe.py:186-294), organised so
+// that every expert byte is read from HBM once per step however many tokens route to it:
+//
+//   plan      one CTA sorts the routes by slot (stable), cuts every slot's run into groups of at
+//             most 8 routes and writes the group list.  No host round trip: the expert kernels
+//             read the group count from device memory.
+//   permute   activations are copied once into a k-permuted bf16 matrix whose rows can be fetched
+//             with one bulk copy and read as tensor-core B fragments without bank conflicts.
+//   experts   persistent CTAs, one per SM, each owning a contiguous range of (group, row-block)
+//             items.  A producer warp streams the packed E2M1 rows and E4M3 scales of an item into
+//             a ring of shared-memory stages with bulk async copies (TMA engine, mbarrier
+//             completion); eight consumer warps read 128-bit fragments, dequantise in registers
+//             (bit-placement E2M1 -> bf16, times the block scale, exact) and feed
+//             mma.sync.m16n8k16 with the group's (<= 8) tokens as the N dimension, f32 accumulate.
+//             K is split across the warps of a row tile and reduced through shared memory.
+//             gate_up fuses global scale + silu(gate) * up and writes ic2 (bf16, k-permuted for the
+//             down pass); down fuses global scale and route weight and writes one f32 row per route.
+//
+// The weights stay in the reference's bank layout (row-major packed nibbles, low nibble = even k).
+#include "kernels.cuh"
+
+namespace ftm {
+
+namespace {
+
+// ------------------------------------------------------------------------------------------
+// k-permutation shared by the activation matrix and the kernels.
+//
+// Inside every window of 128 k, logical k = 32*t + 8*j + n (t, j in 0..3, n in 0..7) is stored at
+// position 8*(4*j + t) + pos8(n), pos8 = [0,2,4,6,1,3,5,7][n].  Lane t of a fragment group then
+// finds, for step j, its eight k as one 16-byte chunk, the four lanes' chunks are contiguous
+// (conflict-free 128-bit shared loads), and inside the chunk the pairs (n, n+4) are adjacent 32-bit
+// words, which is the pairing the nibble extraction below produces.
+// ------------------------------------------------------------------------------------------
+__host__ __device__ __forceinline__ int perm_k(int k) {
+    const int w = k & ~127, r = k & 127;
+    const int t = r >> 5, j = (r >> 3) & 3, n = r & 7;
+    const int pos8 = (n < 4) ? 2 * n : 2 * (n - 4) + 1;
+    return w + 8 * (4 * j + t) + pos8;
+}
+
+__global__ void permute_act_kernel(const void* __restrict__ x, int dtype, int rows, int K,
+                                   __nv_bfloat16* __restrict__ xp) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)rows * K) return;
+    const int k = (int)(i % K);
+    const size_t row = i / K;
+    xp[row * K + perm_k(k)] = __float2bfloat16_rn(load_act(x, dtype, i));
+}
+
+// ------------------------------------------------------------------------------------------
+// plan: stable sort of the routes by slot, groups of <= 8 routes of one slot
+// ------------------------------------------------------------------------------------------
+constexpr int kPlanThreads = 1024;
+constexpr int kPlanMaxRoutes = 2048;
+
+__global__ void __launch_bounds__(kPlanThreads)
+decode_plan_kernel(const int32_t* __restrict__ route_slot, int routes, int4* __restrict__ groups,
+                   int32_t* __restrict__ sorted_route, int32_t* __restrict__ n_groups) {
+    __shared__ uint32_t keys[kPlanMaxRoutes];
+    __shared__ int scan[kPlanMaxRoutes];
+    __shared__ int wsum[32];
+    const int tid = threadIdx.x;
+    int n = 1;
+    while (n < routes) n <<= 1;
+    if (n < 2) n = 2;
+    // key = (slot + 1, route): non-resident routes (slot -1) sort first, padding sorts last
+    for (int i = tid; i < n; i += kPlanThreads) {
+        uint32_t k = 0xffffffffu;
+        if (i < routes) {
+            int s = route_slot[i];
+            k = ((uint32_t)(s < 0 ? 0 : s + 1) << 11) | (uint32_t)i;
+        }
+        keys[i] = k;
+    }
+    __syncthreads();
+    for (int size = 2; size <= n; size <<= 1) {
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            for (int i = tid; i < n / 2; i += kPlanThreads) {
+                int lo = 2 * i - (i & (stride - 1));
+                int hi = lo + stride;
+                bool up = ((lo & size) == 0);
+                uint32_t a = keys[lo], b = keys[hi];
+                if ((a > b) == up) {
+                    keys[lo] = b;
+                    keys[hi] = a;
+                }
+            }
+            __syncthreads();
+        }
+    }
+    // group starts: a resident route whose position inside its slot's run is a multiple of 8.
+    // Position inside the run = i - start(i); start(i) by a running maximum over run starts.
+    for (int i = tid; i < n; i += kPlanThreads) {
+        int v = 0;
+        if (i < routes) {
+            uint32_t s = keys[i] >> 11;
+            bool start = (i == 0) || ((keys[i - 1] >> 11) != s);
+            v = start ? i : 0;
+        }
+        scan[i] = v;
+    }
+    __syncthreads();
+    // inclusive max-scan (Hillis-Steele over shared memory; n <= 2048)
+    for (int off = 1; off < n; off <<= 1) {
+        int v0 = 0, v1 = 0;
+        int i0 = tid, i1 = tid + kPlanThreads;
+        if (i0 < n) v0 = (i0 >= off) ? max(scan[i0], scan[i0 - off]) : scan[i0];
+        if (i1 < n) v1 = (i1 >= off) ? max(scan[i1], scan[i1 - off]) : scan[i1];
+        __syncthreads();
+        if (i0 < n) scan[i0] = v0;
+        if (i1 < n) scan[i1] = v1;
+        __syncthreads();
+    }
+    // flags -> exclusive sum scan (two elements per thread, warp scan + block scan)
+    int f[2], idx[2];
+#pragma unroll
+    for (int q = 0; q < 2; q++) {
+        int i = 2 * tid + q;
+        idx[q] = i;
+        f[q] = 0;
+        if (i < routes) {
+            uint32_t s = keys[i] >> 11;
+            if (s != 0 && ((i - scan[i]) & 7) == 0) f[q] = 1;
+        }
+    }
+    int local = f[0] + f[1];
+    int incl = local;
+    const int lane = tid & 31, warp = tid >> 5;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+    }
+    if (lane == 31) wsum[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        int v = wsum[lane], inc2 = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            int u = __shfl_up_sync(0xffffffffu, inc2, o);
+            if (lane >= o) inc2 += u;
+        }
+        wsum[lane] = inc2 - v;
+        if (lane == 31) *n_groups = inc2;
+    }
+    __syncthreads();
+    int base = wsum[warp] + incl - local;
+#pragma unroll
+    for (int q = 0; q < 2; q++) {
+        int i = idx[q];
+        if (i < routes) sorted_route[i] = (int32_t)(keys[i] & 2047u);
+        if (f[q]) {
+            uint32_t s = keys[i] >> 11;
+            int cnt = 1;
+            while (cnt < 8 && i + cnt < routes && (keys[i + cnt] >> 11) == s) cnt++;
+            groups[base] = make_int4((int)s - 1, i, cnt, 0);
+            base++;
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// PTX helpers: mbarrier, bulk async copy, mma
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after kSpinLimit polls, raises the error flag and reports failure, so a
+// lost completion can never hang the GPU.
+constexpr uint32_t kSpinLimit = 1u << 22;
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int32_t* err) {
+    for (uint32_t i = 0; i < kSpinLimit; i++)
+        if (mbar_try_wait(bar, parity)) return true;
+    atomicExch(err, 2);
+    return false;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t hmul2_bf16(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds16(uint32_t addr) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return v;
+}
+
+// Eight E2M1 codes of one word -> four bf16x2, value = e2m1 * 2^-126 (the code's s|ee|m bits are
+// placed at bf16 bit 15 and bits 8:6; ee = 0 lands on bf16 subnormals, which keeps 0 and 0.5 exact).
+// Output pair i holds nibbles (i, i + 4) in its (low, high) halves.
+__device__ __forceinline__ void e2m1x8_to_bf16x2(uint32_t w, uint32_t (&q)[4]) {
+    q[0] = ((w << 12) & 0x80008000u) | ((w << 6) & 0x01c001c0u);
+    q[1] = ((w << 8) & 0x80008000u) | ((w << 2) & 0x01c001c0u);
+    q[2] = ((w << 4) & 0x80008000u) | ((w >> 2) & 0x01c001c0u);
+    q[3] = (w & 0x80008000u) | ((w >> 6) & 0x01c001c0u);
+}
+
+// Two E4M3 block scales (low byte = first block) -> two bf16x2 with the scale in both halves,
+// times 2^110, so that (e2m1 * 2^-126) * (scale * 2^110) = weight * 2^-16 is a normal bf16 and exact.
+// Route: hardware e4m3x2 -> f16x2 (exact, subnormals included), then rebias the f16 bit pattern.
+__device__ __forceinline__ void e4m3x2_to_bf16_scales(uint32_t two, uint32_t& s0, uint32_t& s1) {
+    uint32_t h2;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"((uint16_t)two));
+    // f16 (1,5,10) -> bf16 (1,8,7) of value * 2^110: exponent + (127 - 15 + 110) = + 222
+    uint32_t b2 = (((h2 >> 3) & 0x0fff0fffu) + 0x6f006f00u) | (h2 & 0x80008000u);
+    // an f16 zero (scale code 0) must stay zero
+    if ((h2 & 0x00007fffu) == 0) b2 &= 0xffff0000u;
+    if ((h2 & 0x7fff0000u) == 0) b2 &= 0x0000ffffu;
+    s0 = __byte_perm(b2, b2, 0x1010);
+    s1 = __byte_perm(b2, b2, 0x3232);
+}
+
+// ------------------------------------------------------------------------------------------
+// the expert kernel
+// ------------------------------------------------------------------------------------------
+constexpr int kConsumerWarps = 8;
+constexpr int kThreads = (kConsumerWarps + 1) * 32;
+constexpr int kGroupTokens = 8;
+
+template <bool GATE_UP, int KS>
+struct Cfg {
+    // GATE_UP: K = hidden, item = ROWS/2 gate rows + ROWS/2 up rows; else K = inter, item = ROWS rows
+    static constexpr int kRowTiles = kConsumerWarps / KS;  // 16-row MMA tiles per item
+    static constexpr int kRows = 16 * kRowTiles;
+};
+
+struct ExpertArgs {
+    const uint8_t* packed;    // bank base [slots, N, K/2]
+    const uint8_t* scale;     // [slots, N, K/16]
+    const uint16_t* global;   // [slots, N]
+    const __nv_bfloat16* act; // k-permuted activations: gate_up [tokens, K], down [routes, K]
+    const int4* groups;
+    const int32_t* sorted_route;
+    const int32_t* n_groups;
+    const float* route_weight;  // down only
+    __nv_bfloat16* ic2;         // gate_up out: [routes, inter] bf16, k-permuted
+    float* yroute;              // down out: [routes, hidden] f32, weighted
+    int32_t* err;
+    int K, N, top_k, stages;
+};
+
+template <bool GATE_UP, int KS>
+__global__ void __launch_bounds__(kThreads, 1) expert_mma_kernel(ExpertArgs a) {
+    using C = Cfg<GATE_UP, KS>;
+    constexpr int ROWS = C::kRows;
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int K = a.K;
+    const int rsa = K / 2 + 64;                 // packed row stride: +64 B keeps 128-bit loads conflict-free
+    const int rss = K / 16 + 16;                // scale row stride
+    const int rsx = K * 2 + 64;                 // activation row stride
+    const int stage_bytes = ROWS * (rsa + rss);
+    const int x_bytes = kGroupTokens * rsx;
+    // layout: [stages][packed rows | scale rows] | x[2] | reduce[2][warps][32 lanes][4 f32] | barriers
+    uint8_t* const stage0 = smem;
+    uint8_t* const xbuf0 = stage0 + (size_t)a.stages * stage_bytes;
+    float* const red = reinterpret_cast<float*>(xbuf0 + 2 * (size_t)x_bytes);
+    uint64_t* const bars = reinterpret_cast<uint64_t*>(red + 2 * kConsumerWarps * 128);
+    // bars: full[stages], empty[stages], xfull[2], xempty[2], redfull[2], redempty[2]
+    const uint32_t bar0 = smem_u32(bars);
+    auto FULL = [&](int s) { return bar0 + 8u * s; };
+    auto EMPTY = [&](int s) { return bar0 + 8u * (a.stages + s); };
+    auto XFULL = [&](int s) { return bar0 + 8u * (2 * a.stages + s); };
+    auto XEMPTY = [&](int s) { return bar0 + 8u * (2 * a.stages + 2 + s); };
+    auto RFULL = [&](int s) { return bar0 + 8u * (2 * a.stages + 4 + s); };
+    auto REMPTY = [&](int s) { return bar0 + 8u * (2 * a.stages + 6 + s); };
+
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < a.stages; s++) {
+            mbar_init(FULL(s), 1);
+            mbar_init(EMPTY(s), kConsumerWarps);
+        }
+        for (int s = 0; s < 2; s++) {
+            mbar_init(XFULL(s), 1);
+            mbar_init(XEMPTY(s), kConsumerWarps);
+            mbar_init(RFULL(s), KS - 1 > 0 ? (KS - 1) * C::kRowTiles : 1);
+            mbar_init(REMPTY(s), C::kRowTiles);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    // contiguous item range of this CTA: item = group * blocks + block
+    const int n_groups = *a.n_groups;
+    const int rows_per_item_out = GATE_UP ? ROWS / 2 : ROWS;       // output rows (pairs for gate_up)
+    const int blocks = (GATE_UP ? a.N / 2 : a.N) / rows_per_item_out;
+    const long long total = (long long)n_groups * blocks;
+    const int item_begin = (int)(total * blockIdx.x / gridDim.x);
+    const int item_end = (int)(total * (blockIdx.x + 1) / gridDim.x);
+    if (item_begin >= item_end) return;
+
+    if (warp == kConsumerWarps) {
+        // ===================== producer: bulk copies of weights, scales and activations ==========
+        int xs = 0, xphase = 0, cur_group = -1;
+        int st = 0, phase = 0;
+        for (int item = item_begin; item < item_end; item++) {
+            const int g = item / blocks, blk = item % blocks;
+            const int4 grp = a.groups[g];
+            if (g != cur_group) {
+                // this group's token rows into the next activation buffer
+                if (!mbar_wait(XEMPTY(xs), xphase ^ 1, a.err)) return;
+                if (lane == 0) mbar_expect_tx(XFULL(xs), (uint32_t)(grp.z * K * 2));
+                __syncwarp();
+                if (lane < grp.z) {
+                    const int route = a.sorted_route[grp.y + lane];
+                    const int row = GATE_UP ? route / a.top_k : route;
+                    bulk_g2s(smem_u32(xbuf0 + (size_t)xs * x_bytes + (size_t)lane * rsx), a.act + (size_t)row * K,
+                             (uint32_t)(K * 2), XFULL(xs));
+                }
+                cur_group = g;
+                xs ^= 1;
+                if (xs == 0) xphase ^= 1;
+            }
+            if (!mbar_wait(EMPTY(st), phase ^ 1, a.err)) return;
+            if (lane == 0) mbar_expect_tx(FULL(st), (uint32_t)(ROWS * (K / 2 + K / 16)));
+            __syncwarp();
+            uint8_t* const sp = stage0 + (size_t)st * stage_bytes;
+            const size_t slot_rows = (size_t)grp.x * a.N;
+            for (int r = lane; r < ROWS; r += 32) {
+                int n;
+                if (GATE_UP) {
+                    const int tile = r / 16, m = r % 16;
+                    const int pair = blk * (ROWS / 2) + tile * 8 + (m & 7);
+                    n = (m < 8) ? pair : a.N / 2 + pair;
+                } else {
+                    n = blk * ROWS + r;
+                }
+                bulk_g2s(smem_u32(sp + (size_t)r * rsa), a.packed + (slot_rows + n) * (size_t)(K / 2), (uint32_t)(K / 2),
+                         FULL(st));
+                bulk_g2s(smem_u32(sp + (size_t)ROWS * rsa + (size_t)r * rss), a.scale + (slot_rows + n) * (size_t)(K / 16),
+                         (uint32_t)(K / 16), FULL(st));
+            }
+            if (++st == a.stages) {
+                st = 0;
+                phase ^= 1;
+            }
+        }
+        return;
+    }
+
+    // ===================== consumers ==========================================================
+    const int tile = warp / KS, ks = warp % KS;     // row tile of the item, K split index
+    const int g8 = lane >> 2, t4 = lane & 3;        // fragment row group and k lane
+    const int windows = K / 128 / KS;               // 128-k windows per warp
+    int xs = -1, xphase = 0, cur_group = -1;
+    int st = 0, phase = 0;
+    int rs = 0, rphase = 0;
+    for (int item = item_begin; item < item_end; item++) {
+        const int g = item / blocks, blk = item % blocks;
+        const int4 grp = a.groups[g];
+        if (g != cur_group) {
+            if (cur_group >= 0) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(XEMPTY(xs));
+            }
+            xs = (xs < 0) ? 0 : (xs ^ 1);
+            if (cur_group >= 0 && xs == 0) xphase ^= 1;
+            if (!mbar_wait(XFULL(xs), xphase, a.err)) return;
+            cur_group = g;
+        }
+        if (!mbar_wait(FULL(st), phase, a.err)) return;
+        const uint32_t sp = smem_u32(stage0 + (size_t)st * stage_bytes);
+        const uint32_t xa = smem_u32(xbuf0 + (size_t)xs * x_bytes) + g8 * rsx + t4 * 16;
+        const uint32_t row_lo = sp + (tile * 16 + g8) * rsa + t4 * 16;
+        const uint32_t row_hi = row_lo + 8 * rsa;
+        const uint32_t sc_lo = sp + ROWS * rsa + (tile * 16 + g8) * rss + t4 * 2;
+        const uint32_t sc_hi = sc_lo + 8 * rss;
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int wi = 0; wi < windows; wi++) {
+            const int win = ks * windows + wi;
+            const uint4 plo = lds128(row_lo + win * 64);
+            const uint4 phi = lds128(row_hi + win * 64);
+            uint32_t slo0, slo1, shi0, shi1;
+            e4m3x2_to_bf16_scales(lds16(sc_lo + win * 8), slo0, slo1);
+            e4m3x2_to_bf16_scales(lds16(sc_hi + win * 8), shi0, shi1);
+            const uint32_t wl[4] = {plo.x, plo.y, plo.z, plo.w};
+            const uint32_t wh[4] = {phi.x, phi.y, phi.z, phi.w};
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const uint4 xb = lds128(xa + win * 256 + j * 64);
+                uint32_t ql[4], qh[4];
+                e2m1x8_to_bf16x2(wl[j], ql);
+                e2m1x8_to_bf16x2(wh[j], qh);
+                const uint32_t sl = (j < 2) ? slo0 : slo1, sh = (j < 2) ? shi0 : shi1;
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    ql[q] = hmul2_bf16(ql[q], sl);
+                    qh[q] = hmul2_bf16(qh[q], sh);
+                }
+                mma_bf16(acc, ql[0], qh[0], ql[1], qh[1], xb.x, xb.y);
+                mma_bf16(acc, ql[2], qh[2], ql[3], qh[3], xb.z, xb.w);
+            }
+        }
+        // the stage is consumed once every warp has read its fragments
+        __syncwarp();
+        if (lane == 0) mbar_arrive(EMPTY(st));
+        if (++st == a.stages) {
+            st = 0;
+            phase ^= 1;
+        }
+
+        // ---- K reduction across the warps of this row tile: warp ks == 0 gathers ----
+        if (KS > 1) {
+            float* const buf = red + (size_t)rs * kConsumerWarps * 128;
+            if (ks != 0) {
+                if (!mbar_wait(REMPTY(rs), rphase ^ 1, a.err)) return;
+                *reinterpret_cast<float4*>(buf + warp * 128 + lane * 4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(RFULL(rs));
+            } else {
+                if (!mbar_wait(RFULL(rs), rphase, a.err)) return;
+#pragma unroll
+                for (int o = 1; o < KS; o++) {
+                    const float4 v = *reinterpret_cast<const float4*>(buf + (warp + o) * 128 + lane * 4);
+                    acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(REMPTY(rs));
+            }
+            rs ^= 1;
+            if (rs == 0) rphase ^= 1;
+        }
+        if (ks != 0) continue;
+
+        // ---- epilogue (warp ks == 0 of each row tile) ----
+        // acc[0], acc[1]: fragment row g8, tokens 2*t4, 2*t4+1;  acc[2], acc[3]: row g8 + 8
+        const float unscale = 65536.0f;  // the weights carried 2^-16
+        const size_t slot_rows = (size_t)grp.x * a.N;
+        if (GATE_UP) {
+            const int pair = blk * (ROWS / 2) + tile * 8 + g8;
+            const float gg = f16_global_to_f32(a.global[slot_rows + pair]) * unscale;
+            const float gu = f16_global_to_f32(a.global[slot_rows + a.N / 2 + pair]) * unscale;
+            const int pk = perm_k(pair);
+#pragma unroll
+            for (int c = 0; c < 2; c++) {
+                const int tok = 2 * t4 + c;
+                if (tok < grp.z) {
+                    const float gate = acc[c] * gg, up = acc[2 + c] * gu;
+                    const float v = (gate / (1.0f + __expf(-gate))) * up;
+                    const int route = a.sorted_route[grp.y + tok];
+                    a.ic2[(size_t)route * (a.N / 2) + pk] = __float2bfloat16_rn(v);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const int d = blk * ROWS + tile * 16 + g8 + 8 * h;
+                const float gd = f16_global_to_f32(a.global[slot_rows + d]) * unscale;
+#pragma unroll
+                for (int c = 0; c < 2; c++) {
+                    const int tok = 2 * t4 + c;
+                    if (tok < grp.z) {
+                        const int route = a.sorted_route[grp.y + tok];
+                        a.yroute[(size_t)route * a.N + d] = a.route_weight[route] * (acc[2 * h + c] * gd);
+                    }
+                }
+            }
+        }
+    }
+    // release the last activation buffer (keeps the producer's bookkeeping symmetric)
+    __syncwarp();
+    if (lane == 0 && cur_group >= 0) mbar_arrive(XEMPTY(xs));
+}
+
+// rows whose slot is -1 contribute zeros: clear the per-route outputs that no group will write
+__global__ void zero_missing_routes_kernel(const int32_t* __restrict__ route_slot, int routes, int H,
+                                           float* __restrict__ yroute) {
+    const int r = blockIdx.x;
+    if (route_slot[r] >= 0) return;
+    for (int d = threadIdx.x; d < H; d += blockDim.x) yroute[(size_t)r * H + d] = 0.f;
+}
+
+template <bool GATE_UP, int KS>
+size_t expert_smem_bytes(int K, int stages) {
+    const int rows = Cfg<GATE_UP, KS>::kRows;
+    size_t stage = (size_t)rows * (K / 2 + 64 + K / 16 + 16);
+    size_t x = (size_t)kGroupTokens * (K * 2 + 64);
+    return stages * stage + 2 * x + 2 * kConsumerWarps * 128 * sizeof(float) + (2 * stages + 8) * sizeof(uint64_t) + 128;
+}
+
+template <bool GATE_UP, int KS>
+void launch_expert(ExpertArgs a, int grid, cudaStream_t s) {
+    // as many stages as fit in 200 KB, at most 8
+    int stages = 8;
+    while (stages > 2 && expert_smem_bytes<GATE_UP, KS>(a.K, stages) > 200 * 1024) stages--;
+    a.stages = stages;
+    const size_t smem = expert_smem_bytes<GATE_UP, KS>(a.K, stages);
+    static bool attr = false;
+    if (!attr) {
+        cudaFuncSetAttribute(expert_mma_kernel<GATE_UP, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        attr = true;
+    }
+    expert_mma_kernel<GATE_UP, KS><<<grid, kThreads, smem, s>>>(a);
+}
+
+}  // namespace
+
+bool decode_mma_supported(int hidden, int inter, int routes) {
+    // gate_up splits K = hidden over 8 warps in 128-k windows; down splits K = inter over 1 or 2
+    return hidden % 1024 == 0 && inter % 256 == 0 && routes <= kPlanMaxRoutes && hidden <= 4096 && inter <= 4096;
+}
+
+int launch_decode_mma(const BankView& b, const void* x, int x_dtype, const int32_t* route_slot,
+                      const float* route_weight, int tokens, int top_k, DecodeScratch sc, int sm_count,
+                      const Ctx& c) {
+    const int routes = tokens * top_k;
+    int launches = 0;
+    c.begin(K_PERMUTE_ACT);
+    {
+        size_t n = (size_t)tokens * b.hidden;
+        permute_act_kernel<<<(unsigned)((n + 255) / 256), 256, 0, c.s>>>(x, x_dtype, tokens, b.hidden, sc.xperm);
+    }
+    c.end();
+    c.begin(K_DECODE_PLAN);
+    decode_plan_kernel<<<1, kPlanThreads, 0, c.s>>>(route_slot, routes, sc.groups, sc.sorted_route, sc.n_groups);
+    zero_missing_routes_kernel<<<routes, 256, 0, c.s>>>(route_slot, routes, b.hidden, sc.yroute);
+    c.end();
+    launches += 3;
+
+    ExpertArgs a{};
+    a.groups = sc.groups;
+    a.sorted_route = sc.sorted_route;
+    a.n_groups = sc.n_groups;
+    a.err = sc.err;
+    a.top_k = top_k;
+    // gate_up: K = hidden, N = 2 * inter rows
+    a.packed = b.gu_packed; a.scale = b.gu_scale; a.global = b.gu_global;
+    a.act = sc.xperm; a.ic2 = sc.ic2p; a.K = b.hidden; a.N = 2 * b.inter;
+    c.begin(K_EXPERT_GATE_UP);
+    launch_expert<true, 8>(a, sm_count, c.s);
+    c.end();
+    // down: K = inter, N = hidden rows
+    a.packed = b.dn_packed; a.scale = b.dn_scale; a.global = b.dn_global;
+    a.act = sc.ic2p; a.yroute = sc.yroute; a.route_weight = route_weight; a.K = b.inter; a.N = b.hidden;
+    c.begin(K_EXPERT_DOWN);
+    if (routes <= 128)
+        launch_expert<false, 2>(a, sm_count, c.s);
+    else
+        launch_expert<false, 1>(a, sm_count, c.s);
+    c.end();
+    return launches + 2;
+}
+
+}  // namespace ftm

@@ -20,6 +20,8 @@ enum Kind {
     K_COMBINE,
     K_GROUPED_GATE_UP,
     K_GROUPED_DOWN,
+    K_PERMUTE_ACT,
+    K_DECODE_PLAN,
     K_NUM_KINDS
 };
 
@@ -52,6 +54,21 @@ int launch_slot_rewrite(const void* expert_ids, int ids_dtype, int routes, int l
 int launch_decode_routes(const BankView& b, const __nv_bfloat16* x, const int32_t* route_slot,
                          const float* route_weight, int tokens, int top_k, float* ic2, float* yroute,
                          const Ctx& c);
+
+// decode_mma.cu: grouped decode path (plan + k-permuted activations + TMA/mma.sync expert kernels)
+struct DecodeScratch {
+    __nv_bfloat16* xperm;   // [tokens, hidden] bf16, k-permuted
+    __nv_bfloat16* ic2p;    // [routes, inter] bf16, k-permuted
+    int4* groups;           // [routes] (slot, first sorted position, count <= 8, 0)
+    int32_t* sorted_route;  // [routes]
+    int32_t* n_groups;      // [1]
+    float* yroute;          // [routes, hidden] f32
+    int32_t* err;           // raised when a bounded wait gives up
+};
+bool decode_mma_supported(int hidden, int inter, int routes);
+int launch_decode_mma(const BankView& b, const void* x, int x_dtype, const int32_t* route_slot,
+                      const float* route_weight, int tokens, int top_k, DecodeScratch sc, int sm_count,
+                      const Ctx& c);
 
 // shared_expert.cu
 int launch_shared_expert(const __nv_bfloat16* x, int tokens, int hidden, int shared_inter,

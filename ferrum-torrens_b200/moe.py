@@ -324,6 +324,10 @@ class B200MoE:
     def steps(self) -> int:
         return int(self._lib.ftm_steps(self._h))
 
+    def sync_status(self, stream=None):
+        """Waits for the stream; raises if an asynchronous step saw a bad expert id or gave up a wait."""
+        self._check(self._lib.ftm_sync_status(self._h, _stream_ptr(stream)))
+
     def kernel_launches(self) -> int:
         return int(self._lib.ftm_kernel_launches(self._h))
 

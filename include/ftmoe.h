@@ -74,7 +74,8 @@ enum {
 enum {
     FTM_PATH_AUTO = 0,   /* decode GEMV for small batches, grouped GEMM for large */
     FTM_PATH_GEMV = 1,   /* bandwidth-bound decode path */
-    FTM_PATH_GROUPED = 2 /* tcgen05 grouped GEMM (prefill) */
+    FTM_PATH_GROUPED = 2, /* tcgen05 grouped GEMM (prefill) */
+    FTM_PATH_SCALAR = 3   /* one CTA column per route, CUDA-core dot products; any multiple-of-16 shape */
 };
 
 /* CudaMoE::new_with_stream(device, source, shapes, slots, stream)
@@ -186,6 +187,10 @@ FTM_API int ftm_moe_finish(ftm_handle* h, void* out, int out_dtype, void* stream
 FTM_API size_t ftm_route_cap(const ftm_handle* h);
 /* reset_staging (expert_kernel.rs:289-293): forgets residency; the banks keep their bytes */
 FTM_API int ftm_reset_staging(ftm_handle* h);
+/* Waits for `stream` and reports what the asynchronous calls could not: an expert id outside the
+ * layer (the reference's device `bad` flag, python/ferrum_kernel/moe_prefill.py:49-56) or a kernel
+ * that gave up a bounded wait.  FTM_OK when the steps since the last call were clean. */
+FTM_API int ftm_sync_status(ftm_handle* h, void* stream);
 /* MoEExecutor::steps (expert_kernel.rs:390-395): routed steps run since creation */
 FTM_API uint64_t ftm_steps(const ftm_handle* h);
 
