@@ -257,13 +257,6 @@ constexpr int kConsumerWarps = 8;
 constexpr int kThreads = (kConsumerWarps + 1) * 32;
 constexpr int kGroupTokens = 8;
 
-template <bool GATE_UP, int KS>
-struct Cfg {
-    // GATE_UP: K = hidden, item = ROWS/2 gate rows + ROWS/2 up rows; else K = inter, item = ROWS rows
-    static constexpr int kRowTiles = kConsumerWarps / KS;  // 16-row MMA tiles per item
-    static constexpr int kRows = 16 * kRowTiles;
-};
-
 struct ExpertArgs {
     const uint8_t* packed;    // bank base [slots, N, K/2]
     const uint8_t* scale;     // [slots, N, K/16]
@@ -276,33 +269,43 @@ struct ExpertArgs {
     __nv_bfloat16* ic2;         // gate_up out: [routes, inter] bf16, k-permuted
     float* yroute;              // down out: [routes, hidden] f32, weighted
     int32_t* err;
-    int K, N, top_k, stages;
+    int N, top_k, stages;
 };
 
-template <bool GATE_UP, int KS>
+// GATE_UP: K = hidden, an item is ROWS/2 gate rows and the matching ROWS/2 up rows, so that the
+// silu(gate) * up epilogue stays inside one thread.  Otherwise K = inter and an item is ROWS rows.
+// KS warps split K for one 16-row tile; WIN = K / 128 / KS windows of 128 k per warp.
+template <bool GATE_UP, int KS, int WIN>
+struct Cfg {
+    static constexpr int K = 128 * KS * WIN;
+    static constexpr int kRowTiles = kConsumerWarps / KS;
+    static constexpr int ROWS = 16 * kRowTiles;
+    // gate_up rows are copied one by one with 64 B of padding (conflict-free 128-bit reads); down
+    // rows are contiguous in the bank and arrive with one copy (two-way conflicts on the reads)
+    static constexpr int RSA = GATE_UP ? K / 2 + 64 : K / 2;
+    static constexpr int RSS = K / 16;
+    static constexpr int RSX = K * 2 + 64;
+    static constexpr int kStageBytes = ROWS * (RSA + RSS);
+    static constexpr int kXBytes = kGroupTokens * RSX;
+};
+
+template <bool GATE_UP, int KS, int WIN>
 __global__ void __launch_bounds__(kThreads, 1) expert_mma_kernel(ExpertArgs a) {
-    using C = Cfg<GATE_UP, KS>;
-    constexpr int ROWS = C::kRows;
+    using C = Cfg<GATE_UP, KS, WIN>;
+    constexpr int K = C::K, ROWS = C::ROWS, RSA = C::RSA, RSS = C::RSS, RSX = C::RSX;
     extern __shared__ __align__(128) uint8_t smem[];
-    const int K = a.K;
-    const int rsa = K / 2 + 64;                 // packed row stride: +64 B keeps 128-bit loads conflict-free
-    const int rss = K / 16 + 16;                // scale row stride
-    const int rsx = K * 2 + 64;                 // activation row stride
-    const int stage_bytes = ROWS * (rsa + rss);
-    const int x_bytes = kGroupTokens * rsx;
-    // layout: [stages][packed rows | scale rows] | x[2] | reduce[2][warps][32 lanes][4 f32] | barriers
+    // layout: [stages][packed rows | scale rows] | x | reduce[2][warps][32 lanes][4 f32] | barriers
     uint8_t* const stage0 = smem;
-    uint8_t* const xbuf0 = stage0 + (size_t)a.stages * stage_bytes;
-    float* const red = reinterpret_cast<float*>(xbuf0 + 2 * (size_t)x_bytes);
+    uint8_t* const xbuf = stage0 + (size_t)a.stages * C::kStageBytes;
+    float* const red = reinterpret_cast<float*>(xbuf + C::kXBytes);
     uint64_t* const bars = reinterpret_cast<uint64_t*>(red + 2 * kConsumerWarps * 128);
-    // bars: full[stages], empty[stages], xfull[2], xempty[2], redfull[2], redempty[2]
+    // bars: full[stages], empty[stages], xfull, xempty, redfull[2], redempty[2]
     const uint32_t bar0 = smem_u32(bars);
     auto FULL = [&](int s) { return bar0 + 8u * s; };
     auto EMPTY = [&](int s) { return bar0 + 8u * (a.stages + s); };
-    auto XFULL = [&](int s) { return bar0 + 8u * (2 * a.stages + s); };
-    auto XEMPTY = [&](int s) { return bar0 + 8u * (2 * a.stages + 2 + s); };
-    auto RFULL = [&](int s) { return bar0 + 8u * (2 * a.stages + 4 + s); };
-    auto REMPTY = [&](int s) { return bar0 + 8u * (2 * a.stages + 6 + s); };
+    const uint32_t XFULL = bar0 + 8u * (2 * a.stages), XEMPTY = XFULL + 8u;
+    auto RFULL = [&](int s) { return bar0 + 8u * (2 * a.stages + 2 + s); };
+    auto REMPTY = [&](int s) { return bar0 + 8u * (2 * a.stages + 4 + s); };
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     if (threadIdx.x == 0) {
@@ -310,10 +313,10 @@ __global__ void __launch_bounds__(kThreads, 1) expert_mma_kernel(ExpertArgs a) {
             mbar_init(FULL(s), 1);
             mbar_init(EMPTY(s), kConsumerWarps);
         }
+        mbar_init(XFULL, 1);
+        mbar_init(XEMPTY, kConsumerWarps);
         for (int s = 0; s < 2; s++) {
-            mbar_init(XFULL(s), 1);
-            mbar_init(XEMPTY(s), kConsumerWarps);
-            mbar_init(RFULL(s), KS - 1 > 0 ? (KS - 1) * C::kRowTiles : 1);
+            mbar_init(RFULL(s), KS > 1 ? (KS - 1) * C::kRowTiles : 1);
             mbar_init(REMPTY(s), C::kRowTiles);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -322,8 +325,8 @@ __global__ void __launch_bounds__(kThreads, 1) expert_mma_kernel(ExpertArgs a) {
 
     // contiguous item range of this CTA: item = group * blocks + block
     const int n_groups = *a.n_groups;
-    const int rows_per_item_out = GATE_UP ? ROWS / 2 : ROWS;       // output rows (pairs for gate_up)
-    const int blocks = (GATE_UP ? a.N / 2 : a.N) / rows_per_item_out;
+    constexpr int kOutRows = GATE_UP ? ROWS / 2 : ROWS;  // output rows per item (pairs for gate_up)
+    const int blocks = (GATE_UP ? a.N / 2 : a.N) / kOutRows;
     const long long total = (long long)n_groups * blocks;
     const int item_begin = (int)(total * blockIdx.x / gridDim.x);
     const int item_end = (int)(total * (blockIdx.x + 1) / gridDim.x);
@@ -331,44 +334,50 @@ __global__ void __launch_bounds__(kThreads, 1) expert_mma_kernel(ExpertArgs a) {
 
     if (warp == kConsumerWarps) {
         // ===================== producer: bulk copies of weights, scales and activations ==========
-        int xs = 0, xphase = 0, cur_group = -1;
+        int xphase = 0, cur_group = -1;
         int st = 0, phase = 0;
         for (int item = item_begin; item < item_end; item++) {
             const int g = item / blocks, blk = item % blocks;
             const int4 grp = a.groups[g];
             if (g != cur_group) {
-                // this group's token rows into the next activation buffer
-                if (!mbar_wait(XEMPTY(xs), xphase ^ 1, a.err)) return;
-                if (lane == 0) mbar_expect_tx(XFULL(xs), (uint32_t)(grp.z * K * 2));
+                // the group's token rows; the buffer is free once every warp holds its fragments
+                if (!mbar_wait(XEMPTY, xphase ^ 1, a.err)) return;
+                if (lane == 0) mbar_expect_tx(XFULL, (uint32_t)(grp.z * K * 2));
                 __syncwarp();
                 if (lane < grp.z) {
                     const int route = a.sorted_route[grp.y + lane];
                     const int row = GATE_UP ? route / a.top_k : route;
-                    bulk_g2s(smem_u32(xbuf0 + (size_t)xs * x_bytes + (size_t)lane * rsx), a.act + (size_t)row * K,
-                             (uint32_t)(K * 2), XFULL(xs));
+                    bulk_g2s(smem_u32(xbuf + (size_t)lane * RSX), a.act + (size_t)row * K, (uint32_t)(K * 2), XFULL);
                 }
                 cur_group = g;
-                xs ^= 1;
-                if (xs == 0) xphase ^= 1;
+                xphase ^= 1;
             }
             if (!mbar_wait(EMPTY(st), phase ^ 1, a.err)) return;
             if (lane == 0) mbar_expect_tx(FULL(st), (uint32_t)(ROWS * (K / 2 + K / 16)));
             __syncwarp();
-            uint8_t* const sp = stage0 + (size_t)st * stage_bytes;
+            uint8_t* const sp = stage0 + (size_t)st * C::kStageBytes;
             const size_t slot_rows = (size_t)grp.x * a.N;
-            for (int r = lane; r < ROWS; r += 32) {
-                int n;
-                if (GATE_UP) {
+            if (GATE_UP) {
+                // stage row r = tile * 16 + m: m < 8 gate row, m >= 8 the matching up row
+                for (int r = lane; r < ROWS; r += 32) {
                     const int tile = r / 16, m = r % 16;
                     const int pair = blk * (ROWS / 2) + tile * 8 + (m & 7);
-                    n = (m < 8) ? pair : a.N / 2 + pair;
-                } else {
-                    n = blk * ROWS + r;
+                    const int n = (m < 8) ? pair : a.N / 2 + pair;
+                    bulk_g2s(smem_u32(sp + (size_t)r * RSA), a.packed + (slot_rows + n) * (size_t)(K / 2),
+                             (uint32_t)(K / 2), FULL(st));
                 }
-                bulk_g2s(smem_u32(sp + (size_t)r * rsa), a.packed + (slot_rows + n) * (size_t)(K / 2), (uint32_t)(K / 2),
+                // scales: eight consecutive rows per copy
+                for (int c8 = lane; c8 < ROWS / 8; c8 += 32) {
+                    const int tile = c8 / 2, up = c8 & 1;
+                    const int n = (up ? a.N / 2 : 0) + blk * (ROWS / 2) + tile * 8;
+                    bulk_g2s(smem_u32(sp + (size_t)ROWS * RSA + (size_t)c8 * 8 * RSS),
+                             a.scale + (slot_rows + n) * (size_t)(K / 16), (uint32_t)(8 * K / 16), FULL(st));
+                }
+            } else if (lane == 0) {
+                const size_t n = slot_rows + (size_t)blk * ROWS;
+                bulk_g2s(smem_u32(sp), a.packed + n * (size_t)(K / 2), (uint32_t)(ROWS * (K / 2)), FULL(st));
+                bulk_g2s(smem_u32(sp + (size_t)ROWS * RSA), a.scale + n * (size_t)(K / 16), (uint32_t)(ROWS * (K / 16)),
                          FULL(st));
-                bulk_g2s(smem_u32(sp + (size_t)ROWS * rsa + (size_t)r * rss), a.scale + (slot_rows + n) * (size_t)(K / 16),
-                         (uint32_t)(K / 16), FULL(st));
             }
             if (++st == a.stages) {
                 st = 0;
@@ -381,43 +390,77 @@ __global__ void __launch_bounds__(kThreads, 1) expert_mma_kernel(ExpertArgs a) {
     // ===================== consumers ==========================================================
     const int tile = warp / KS, ks = warp % KS;     // row tile of the item, K split index
     const int g8 = lane >> 2, t4 = lane & 3;        // fragment row group and k lane
-    const int windows = K / 128 / KS;               // 128-k windows per warp
-    int xs = -1, xphase = 0, cur_group = -1;
+    uint4 xf[WIN * 4];                              // this warp's B fragments of the current group
+    int xphase = 0, cur_group = -1;
     int st = 0, phase = 0;
     int rs = 0, rphase = 0;
     for (int item = item_begin; item < item_end; item++) {
         const int g = item / blocks, blk = item % blocks;
         const int4 grp = a.groups[g];
         if (g != cur_group) {
-            if (cur_group >= 0) {
-                __syncwarp();
-                if (lane == 0) mbar_arrive(XEMPTY(xs));
-            }
-            xs = (xs < 0) ? 0 : (xs ^ 1);
-            if (cur_group >= 0 && xs == 0) xphase ^= 1;
-            if (!mbar_wait(XFULL(xs), xphase, a.err)) return;
+            if (!mbar_wait(XFULL, xphase, a.err)) return;
+            const uint32_t xa = smem_u32(xbuf) + g8 * RSX + t4 * 16 + ks * WIN * 256;
+#pragma unroll
+            for (int wi = 0; wi < WIN; wi++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) xf[wi * 4 + j] = lds128(xa + wi * 256 + j * 64);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(XEMPTY);
+            xphase ^= 1;
             cur_group = g;
         }
+        // operands of the epilogue, requested now so that their latency hides behind the MMAs
+        const size_t slot_rows = (size_t)grp.x * a.N;
+        float ga = 0.f, gb = 0.f, rw0 = 0.f, rw1 = 0.f;
+        int route0 = 0, route1 = 0;
+        if (ks == 0) {
+            if (2 * t4 < grp.z) route0 = a.sorted_route[grp.y + 2 * t4];
+            if (2 * t4 + 1 < grp.z) route1 = a.sorted_route[grp.y + 2 * t4 + 1];
+            if (GATE_UP) {
+                const int pair = blk * (ROWS / 2) + tile * 8 + g8;
+                ga = f16_global_to_f32(a.global[slot_rows + pair]);
+                gb = f16_global_to_f32(a.global[slot_rows + a.N / 2 + pair]);
+            } else {
+                const int d = blk * ROWS + tile * 16 + g8;
+                ga = f16_global_to_f32(a.global[slot_rows + d]);
+                gb = f16_global_to_f32(a.global[slot_rows + d + 8]);
+                if (2 * t4 < grp.z) rw0 = a.route_weight[route0];
+                if (2 * t4 + 1 < grp.z) rw1 = a.route_weight[route1];
+            }
+        }
+
         if (!mbar_wait(FULL(st), phase, a.err)) return;
-        const uint32_t sp = smem_u32(stage0 + (size_t)st * stage_bytes);
-        const uint32_t xa = smem_u32(xbuf0 + (size_t)xs * x_bytes) + g8 * rsx + t4 * 16;
-        const uint32_t row_lo = sp + (tile * 16 + g8) * rsa + t4 * 16;
-        const uint32_t row_hi = row_lo + 8 * rsa;
-        const uint32_t sc_lo = sp + ROWS * rsa + (tile * 16 + g8) * rss + t4 * 2;
-        const uint32_t sc_hi = sc_lo + 8 * rss;
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int wi = 0; wi < windows; wi++) {
-            const int win = ks * windows + wi;
-            const uint4 plo = lds128(row_lo + win * 64);
-            const uint4 phi = lds128(row_hi + win * 64);
+        const uint32_t sp = smem_u32(stage0 + (size_t)st * C::kStageBytes);
+        const uint32_t row_lo = sp + (tile * 16 + g8) * RSA + t4 * 16 + ks * WIN * 64;
+        const uint32_t row_hi = row_lo + 8 * RSA;
+        // this warp's scale bytes of the two rows: WIN * 8 consecutive bytes each
+        const uint32_t sc_lo = sp + ROWS * RSA + (tile * 16 + g8) * RSS + ks * WIN * 8;
+        const uint32_t sc_hi = sc_lo + 8 * RSS;
+        uint32_t scl[WIN * 2], sch[WIN * 2];
+        if (WIN * 8 >= 16) {
+#pragma unroll
+            for (int q = 0; q < WIN / 2; q++) {
+                const uint4 v = lds128(sc_lo + q * 16), u = lds128(sc_hi + q * 16);
+                scl[q * 4 + 0] = v.x; scl[q * 4 + 1] = v.y; scl[q * 4 + 2] = v.z; scl[q * 4 + 3] = v.w;
+                sch[q * 4 + 0] = u.x; sch[q * 4 + 1] = u.y; sch[q * 4 + 2] = u.z; sch[q * 4 + 3] = u.w;
+            }
+        }
+        float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+        for (int wi = 0; wi < WIN; wi++) {
+            const uint4 plo = lds128(row_lo + wi * 64);
+            const uint4 phi = lds128(row_hi + wi * 64);
+            // the lane's two scale bytes of this window: bytes 2*t4, 2*t4+1 of the window's eight
+            const uint32_t wl2 = (t4 & 2) ? scl[wi * 2 + 1] : scl[wi * 2];
+            const uint32_t wh2 = (t4 & 2) ? sch[wi * 2 + 1] : sch[wi * 2];
             uint32_t slo0, slo1, shi0, shi1;
-            e4m3x2_to_bf16_scales(lds16(sc_lo + win * 8), slo0, slo1);
-            e4m3x2_to_bf16_scales(lds16(sc_hi + win * 8), shi0, shi1);
+            e4m3x2_to_bf16_scales((t4 & 1) ? (wl2 >> 16) : (wl2 & 0xffffu), slo0, slo1);
+            e4m3x2_to_bf16_scales((t4 & 1) ? (wh2 >> 16) : (wh2 & 0xffffu), shi0, shi1);
             const uint32_t wl[4] = {plo.x, plo.y, plo.z, plo.w};
             const uint32_t wh[4] = {phi.x, phi.y, phi.z, phi.w};
 #pragma unroll
             for (int j = 0; j < 4; j++) {
-                const uint4 xb = lds128(xa + win * 256 + j * 64);
+                const uint4 xb = xf[wi * 4 + j];
                 uint32_t ql[4], qh[4];
                 e2m1x8_to_bf16x2(wl[j], ql);
                 e2m1x8_to_bf16x2(wh[j], qh);
@@ -427,8 +470,8 @@ __global__ void __launch_bounds__(kThreads, 1) expert_mma_kernel(ExpertArgs a) {
                     ql[q] = hmul2_bf16(ql[q], sl);
                     qh[q] = hmul2_bf16(qh[q], sh);
                 }
-                mma_bf16(acc, ql[0], qh[0], ql[1], qh[1], xb.x, xb.y);
-                mma_bf16(acc, ql[2], qh[2], ql[3], qh[3], xb.z, xb.w);
+                mma_bf16(acc[0], ql[0], qh[0], ql[1], qh[1], xb.x, xb.y);
+                mma_bf16(acc[1], ql[2], qh[2], ql[3], qh[3], xb.z, xb.w);
             }
         }
         // the stage is consumed once every warp has read its fragments
@@ -438,13 +481,16 @@ __global__ void __launch_bounds__(kThreads, 1) expert_mma_kernel(ExpertArgs a) {
             st = 0;
             phase ^= 1;
         }
+        float c4[4];
+#pragma unroll
+        for (int q = 0; q < 4; q++) c4[q] = acc[0][q] + acc[1][q];
 
         // ---- K reduction across the warps of this row tile: warp ks == 0 gathers ----
         if (KS > 1) {
             float* const buf = red + (size_t)rs * kConsumerWarps * 128;
             if (ks != 0) {
                 if (!mbar_wait(REMPTY(rs), rphase ^ 1, a.err)) return;
-                *reinterpret_cast<float4*>(buf + warp * 128 + lane * 4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+                *reinterpret_cast<float4*>(buf + warp * 128 + lane * 4) = make_float4(c4[0], c4[1], c4[2], c4[3]);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(RFULL(rs));
             } else {
@@ -452,7 +498,7 @@ __global__ void __launch_bounds__(kThreads, 1) expert_mma_kernel(ExpertArgs a) {
 #pragma unroll
                 for (int o = 1; o < KS; o++) {
                     const float4 v = *reinterpret_cast<const float4*>(buf + (warp + o) * 128 + lane * 4);
-                    acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
+                    c4[0] += v.x; c4[1] += v.y; c4[2] += v.z; c4[3] += v.w;
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(REMPTY(rs));
@@ -463,43 +509,31 @@ __global__ void __launch_bounds__(kThreads, 1) expert_mma_kernel(ExpertArgs a) {
         if (ks != 0) continue;
 
         // ---- epilogue (warp ks == 0 of each row tile) ----
-        // acc[0], acc[1]: fragment row g8, tokens 2*t4, 2*t4+1;  acc[2], acc[3]: row g8 + 8
+        // c4[0], c4[1]: fragment row g8, tokens 2*t4, 2*t4+1;  c4[2], c4[3]: row g8 + 8
         const float unscale = 65536.0f;  // the weights carried 2^-16
-        const size_t slot_rows = (size_t)grp.x * a.N;
         if (GATE_UP) {
-            const int pair = blk * (ROWS / 2) + tile * 8 + g8;
-            const float gg = f16_global_to_f32(a.global[slot_rows + pair]) * unscale;
-            const float gu = f16_global_to_f32(a.global[slot_rows + a.N / 2 + pair]) * unscale;
-            const int pk = perm_k(pair);
+            const int pk = perm_k(blk * (ROWS / 2) + tile * 8 + g8);
+            const float gg = ga * unscale, gu = gb * unscale;
 #pragma unroll
             for (int c = 0; c < 2; c++) {
-                const int tok = 2 * t4 + c;
-                if (tok < grp.z) {
-                    const float gate = acc[c] * gg, up = acc[2 + c] * gu;
+                if (2 * t4 + c < grp.z) {
+                    const float gate = c4[c] * gg, up = c4[2 + c] * gu;
                     const float v = (gate / (1.0f + __expf(-gate))) * up;
-                    const int route = a.sorted_route[grp.y + tok];
-                    a.ic2[(size_t)route * (a.N / 2) + pk] = __float2bfloat16_rn(v);
+                    a.ic2[(size_t)(c ? route1 : route0) * (a.N / 2) + pk] = __float2bfloat16_rn(v);
                 }
             }
         } else {
+            const int d = blk * ROWS + tile * 16 + g8;
 #pragma unroll
             for (int h = 0; h < 2; h++) {
-                const int d = blk * ROWS + tile * 16 + g8 + 8 * h;
-                const float gd = f16_global_to_f32(a.global[slot_rows + d]) * unscale;
+                const float gd = (h ? gb : ga) * unscale;
 #pragma unroll
-                for (int c = 0; c < 2; c++) {
-                    const int tok = 2 * t4 + c;
-                    if (tok < grp.z) {
-                        const int route = a.sorted_route[grp.y + tok];
-                        a.yroute[(size_t)route * a.N + d] = a.route_weight[route] * (acc[2 * h + c] * gd);
-                    }
-                }
+                for (int c = 0; c < 2; c++)
+                    if (2 * t4 + c < grp.z)
+                        a.yroute[(size_t)(c ? route1 : route0) * a.N + d + 8 * h] = (c ? rw1 : rw0) * (c4[2 * h + c] * gd);
             }
         }
     }
-    // release the last activation buffer (keeps the producer's bookkeeping symmetric)
-    __syncwarp();
-    if (lane == 0 && cur_group >= 0) mbar_arrive(XEMPTY(xs));
 }
 
 // rows whose slot is -1 contribute zeros: clear the per-route outputs that no group will write
@@ -510,34 +544,35 @@ __global__ void zero_missing_routes_kernel(const int32_t* __restrict__ route_slo
     for (int d = threadIdx.x; d < H; d += blockDim.x) yroute[(size_t)r * H + d] = 0.f;
 }
 
-template <bool GATE_UP, int KS>
-size_t expert_smem_bytes(int K, int stages) {
-    const int rows = Cfg<GATE_UP, KS>::kRows;
-    size_t stage = (size_t)rows * (K / 2 + 64 + K / 16 + 16);
-    size_t x = (size_t)kGroupTokens * (K * 2 + 64);
-    return stages * stage + 2 * x + 2 * kConsumerWarps * 128 * sizeof(float) + (2 * stages + 8) * sizeof(uint64_t) + 128;
+template <bool GATE_UP, int KS, int WIN>
+size_t expert_smem_bytes(int stages) {
+    using C = Cfg<GATE_UP, KS, WIN>;
+    return (size_t)stages * C::kStageBytes + C::kXBytes + 2 * kConsumerWarps * 128 * sizeof(float) +
+           (2 * stages + 6) * sizeof(uint64_t) + 128;
 }
 
-template <bool GATE_UP, int KS>
+template <bool GATE_UP, int KS, int WIN>
 void launch_expert(ExpertArgs a, int grid, cudaStream_t s) {
     // as many stages as fit in 200 KB, at most 8
     int stages = 8;
-    while (stages > 2 && expert_smem_bytes<GATE_UP, KS>(a.K, stages) > 200 * 1024) stages--;
+    while (stages > 2 && expert_smem_bytes<GATE_UP, KS, WIN>(stages) > 200 * 1024) stages--;
     a.stages = stages;
-    const size_t smem = expert_smem_bytes<GATE_UP, KS>(a.K, stages);
+    const size_t smem = expert_smem_bytes<GATE_UP, KS, WIN>(stages);
     static bool attr = false;
     if (!attr) {
-        cudaFuncSetAttribute(expert_mma_kernel<GATE_UP, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        cudaFuncSetAttribute(expert_mma_kernel<GATE_UP, KS, WIN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             220 * 1024);
         attr = true;
     }
-    expert_mma_kernel<GATE_UP, KS><<<grid, kThreads, smem, s>>>(a);
+    expert_mma_kernel<GATE_UP, KS, WIN><<<grid, kThreads, smem, s>>>(a);
 }
 
 }  // namespace
 
 bool decode_mma_supported(int hidden, int inter, int routes) {
-    // gate_up splits K = hidden over 8 warps in 128-k windows; down splits K = inter over 1 or 2
-    return hidden % 1024 == 0 && inter % 256 == 0 && routes <= kPlanMaxRoutes && hidden <= 4096 && inter <= 4096;
+    // the tensor-core decode kernels are instantiated for the production expert shape; every other
+    // multiple-of-16 shape takes the per-route kernels
+    return hidden == 2048 && inter == 512 && routes <= kPlanMaxRoutes;
 }
 
 int launch_decode_mma(const BankView& b, const void* x, int x_dtype, const int32_t* route_slot,
@@ -565,18 +600,18 @@ int launch_decode_mma(const BankView& b, const void* x, int x_dtype, const int32
     a.top_k = top_k;
     // gate_up: K = hidden, N = 2 * inter rows
     a.packed = b.gu_packed; a.scale = b.gu_scale; a.global = b.gu_global;
-    a.act = sc.xperm; a.ic2 = sc.ic2p; a.K = b.hidden; a.N = 2 * b.inter;
+    a.act = sc.xperm; a.ic2 = sc.ic2p; a.N = 2 * b.inter;
     c.begin(K_EXPERT_GATE_UP);
-    launch_expert<true, 8>(a, sm_count, c.s);
+    launch_expert<true, 4, 4>(a, sm_count, c.s);   // K = 2048: 4 warps x 4 windows, 32 rows per item
     c.end();
     // down: K = inter, N = hidden rows
     a.packed = b.dn_packed; a.scale = b.dn_scale; a.global = b.dn_global;
-    a.act = sc.ic2p; a.yroute = sc.yroute; a.route_weight = route_weight; a.K = b.inter; a.N = b.hidden;
+    a.act = sc.ic2p; a.yroute = sc.yroute; a.route_weight = route_weight; a.N = b.hidden;
     c.begin(K_EXPERT_DOWN);
     if (routes <= 128)
-        launch_expert<false, 2>(a, sm_count, c.s);
+        launch_expert<false, 2, 2>(a, sm_count, c.s);  // K = 512: 2 warps x 2 windows, 64 rows per item
     else
-        launch_expert<false, 1>(a, sm_count, c.s);
+        launch_expert<false, 1, 4>(a, sm_count, c.s);  // 4 windows per warp, 128 rows per item
     c.end();
     return launches + 2;
 }

@@ -299,9 +299,13 @@ def test_routed_half_matches_reference_fixtures(case):
     banks = o.HostBanks(gu[0], gu[1], gu[2].view(np.uint8), dn[0], dn[1], dn[2].view(np.uint8), slots, 2 * inter,
                         hidden, hidden, inter)
     mine, abs_sum = o.grouped_moe_reference(banks, hidden, inter, x, top_k, slot, weight, want_abs_sum=True)
-    # the reference's own yardstick: error against the size of the summed terms (f32 path: 1e-5)
-    assert np.abs(out - want).max() <= 2e-5 * abs_sum.max()
-    assert np.abs(out - mine).max() <= 2e-5 * abs_sum.max()
+    # the reference's own yardstick: error against the size of the summed terms.  The per-route f32
+    # kernels differ from the host sums only by association (2e-5); the tensor-core decode kernels round
+    # ic2 to bf16 like the reference's device path, whose gate is 4 * 2^-9 of the term magnitude
+    # (tests/cuda_moe_matches_reference.rs:43-53)
+    tol = 4.0 / 512.0 if (hidden, inter) == (2048, 512) else 2e-5
+    assert np.abs(out - want).max() <= tol * abs_sum.max()
+    assert np.abs(out - mine).max() <= tol * abs_sum.max()
     moe.close()
 
 
