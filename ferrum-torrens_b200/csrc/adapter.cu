@@ -109,7 +109,8 @@ struct ftm_handle {
     int32_t *csr_scratch = nullptr, *flags = nullptr, *ids = nullptr;
     float *ic2 = nullptr, *yroute = nullptr, *logits = nullptr, *rweights = nullptr;
     float *ic2s = nullptr, *shared_out = nullptr, *se_gate = nullptr, *routed_f32 = nullptr;
-    __nv_bfloat16 *xperm = nullptr, *ic2p = nullptr;
+    __half* xh = nullptr;
+    float *tok_scale = nullptr, *ic2p = nullptr;
     int4* groups = nullptr;
     int32_t *sorted_route = nullptr, *n_groups = nullptr;
     int sm_count = 148;
@@ -218,7 +219,7 @@ int run_routed(ftm_handle* h, const __nv_bfloat16* x, const int32_t* route_slot,
     BankView b = bank_view(h);
     const int routes = tokens * h->cfg.top_k;
     if (path != FTM_PATH_SCALAR && decode_mma_supported(h->cfg.hidden, h->cfg.inter, routes)) {
-        DecodeScratch sc{h->xperm, h->ic2p, h->groups, h->sorted_route, h->n_groups, h->yroute, h->flags + 2};
+        DecodeScratch sc{h->xh, h->tok_scale, h->ic2p, h->groups, h->sorted_route, h->n_groups, h->yroute, h->flags + 2};
         h->launches += launch_decode_mma(b, x, FTM_BF16, route_slot, weights, tokens, h->cfg.top_k, sc, h->sm_count,
                                          h->ctx(s));
     } else {
@@ -319,7 +320,8 @@ FTM_API int ftm_create(const ftm_config* c, void* stream, ftm_handle** out) {
     A(dev_alloc(hp, &h->shared_out, T * H));
     A(dev_alloc(hp, &h->se_gate, T));
     A(dev_alloc(hp, &h->routed_f32, T * H));
-    A(dev_alloc(hp, &h->xperm, T * H));
+    A(dev_alloc(hp, &h->xh, T * H));
+    A(dev_alloc(hp, &h->tok_scale, T));
     A(dev_alloc(hp, &h->ic2p, R * I));
     A(dev_alloc(hp, &h->groups, R));
     A(dev_alloc(hp, &h->sorted_route, R));

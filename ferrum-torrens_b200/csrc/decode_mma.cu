@@ -27,28 +27,52 @@ namespace ftm {
 namespace {
 
 // ------------------------------------------------------------------------------------------
-// k-permutation shared by the activation matrix and the kernels.
+// k-permutation shared by the activation matrices and the kernels.
 //
 // Inside every window of 128 k, logical k = 32*t + 8*j + n (t, j in 0..3, n in 0..7) is stored at
-// position 8*(4*j + t) + pos8(n), pos8 = [0,2,4,6,1,3,5,7][n].  Lane t of a fragment group then
-// finds, for step j, its eight k as one 16-byte chunk, the four lanes' chunks are contiguous
-// (conflict-free 128-bit shared loads), and inside the chunk the pairs (n, n+4) are adjacent 32-bit
-// words, which is the pairing the nibble extraction below produces.
+// position 8*(4*j + t) + n.  Lane t of a fragment group then finds, for step j, its eight k as one
+// contiguous chunk, and the four lanes' chunks are contiguous too (conflict-free 128-bit shared
+// loads).  A lane's eight k are the eight nibbles of one packed weight word.
 // ------------------------------------------------------------------------------------------
 __host__ __device__ __forceinline__ int perm_k(int k) {
     const int w = k & ~127, r = k & 127;
     const int t = r >> 5, j = (r >> 3) & 3, n = r & 7;
-    const int pos8 = (n < 4) ? 2 * n : 2 * (n - 4) + 1;
-    return w + 8 * (4 * j + t) + pos8;
+    return w + 8 * (4 * j + t) + n;
 }
 
-__global__ void permute_act_kernel(const void* __restrict__ x, int dtype, int rows, int K,
-                                   __nv_bfloat16* __restrict__ xp) {
-    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= (size_t)rows * K) return;
-    const int k = (int)(i % K);
-    const size_t row = i / K;
-    xp[row * K + perm_k(k)] = __float2bfloat16_rn(load_act(x, dtype, i));
+// Activations -> f16, k-permuted, each token scaled by a power of two so that its largest
+// magnitude lands in [2^14, 2^15): the tensor-core operands are f16 (the E2M1 -> f16 conversion is a
+// hardware instruction), and the per-token scale keeps any bf16/f32 input inside the f16 range
+// without losing bits (bf16 carries 8 significant bits, f16 11).  tok_scale[t] undoes it.
+__global__ void __launch_bounds__(256)
+prep_act_kernel(const void* __restrict__ x, int dtype, int K, __half* __restrict__ xh, float* __restrict__ tok_scale) {
+    __shared__ float wmax[8];
+    __shared__ float s_inv;
+    const int t = blockIdx.x;
+    const size_t base = (size_t)t * K;
+    float m = 0.f;
+    for (int k = threadIdx.x; k < K; k += 256) m = fmaxf(m, fabsf(load_act(x, dtype, base + k)));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if ((threadIdx.x & 31) == 0) wmax[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float mm = 0.f;
+        for (int w = 0; w < 8; w++) mm = fmaxf(mm, wmax[w]);
+        // 2^(14 - floor(log2 mm)) by exponent arithmetic; zero, subnormal or non-finite rows keep scale 1
+        const int e = (int)((__float_as_uint(mm) >> 23) & 0xff);
+        float inv = 1.0f, sc = 1.0f;
+        if (e > 0 && e < 255) {
+            inv = __uint_as_float((uint32_t)(127 + 14 - (e - 127)) << 23);
+            sc = __uint_as_float((uint32_t)(127 - 14 + (e - 127)) << 23);
+        }
+        s_inv = inv;
+        tok_scale[t] = sc;
+    }
+    __syncthreads();
+    const float inv = s_inv;
+    for (int k = threadIdx.x; k < K; k += 256)
+        xh[base + perm_k(k)] = __float2half_rn(load_act(x, dtype, base + k) * inv);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -202,16 +226,16 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
                  "l"(src), "r"(bytes), "r"(bar)
                  : "memory");
 }
-__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                         uint32_t b0, uint32_t b1) {
+__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                        uint32_t b1) {
     asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ uint32_t hmul2_bf16(uint32_t a, uint32_t b) {
+__device__ __forceinline__ uint32_t hmul2_f16(uint32_t a, uint32_t b) {
     uint32_t d;
-    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
     return d;
 }
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
@@ -219,35 +243,27 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
     return v;
 }
-__device__ __forceinline__ uint32_t lds16(uint32_t addr) {
-    uint16_t v;
-    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
-    return v;
+
+// Eight E2M1 codes of one packed word -> four f16x2, one hardware conversion per byte.  Byte b holds
+// k = 2b (low nibble, low half of the result) and k = 2b + 1.  The values 0, 0.5 .. 6 are exact.
+__device__ __forceinline__ void e2m1x8_to_f16x2(uint32_t w, uint32_t (&q)[4]) {
+    asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+        "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %2, b2;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %3, b3;\n\t}"
+        : "=r"(q[0]), "=r"(q[1]), "=r"(q[2]), "=r"(q[3])
+        : "r"(w));
 }
 
-// Eight E2M1 codes of one word -> four bf16x2, value = e2m1 * 2^-126 (the code's s|ee|m bits are
-// placed at bf16 bit 15 and bits 8:6; ee = 0 lands on bf16 subnormals, which keeps 0 and 0.5 exact).
-// Output pair i holds nibbles (i, i + 4) in its (low, high) halves.
-__device__ __forceinline__ void e2m1x8_to_bf16x2(uint32_t w, uint32_t (&q)[4]) {
-    q[0] = ((w << 12) & 0x80008000u) | ((w << 6) & 0x01c001c0u);
-    q[1] = ((w << 8) & 0x80008000u) | ((w << 2) & 0x01c001c0u);
-    q[2] = ((w << 4) & 0x80008000u) | ((w >> 2) & 0x01c001c0u);
-    q[3] = (w & 0x80008000u) | ((w >> 6) & 0x01c001c0u);
-}
-
-// Two E4M3 block scales (low byte = first block) -> two bf16x2 with the scale in both halves,
-// times 2^110, so that (e2m1 * 2^-126) * (scale * 2^110) = weight * 2^-16 is a normal bf16 and exact.
-// Route: hardware e4m3x2 -> f16x2 (exact, subnormals included), then rebias the f16 bit pattern.
-__device__ __forceinline__ void e4m3x2_to_bf16_scales(uint32_t two, uint32_t& s0, uint32_t& s1) {
+// Two E4M3 block scales (low byte = first block) -> two f16x2 with the scale in both halves.
+// e2m1 * e4m3 needs at most 6 significant bits and stays inside [2^-10, 2688]: exact in f16.
+__device__ __forceinline__ void e4m3x2_to_f16_scales(uint32_t two, uint32_t& s0, uint32_t& s1) {
     uint32_t h2;
     asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"((uint16_t)two));
-    // f16 (1,5,10) -> bf16 (1,8,7) of value * 2^110: exponent + (127 - 15 + 110) = + 222
-    uint32_t b2 = (((h2 >> 3) & 0x0fff0fffu) + 0x6f006f00u) | (h2 & 0x80008000u);
-    // an f16 zero (scale code 0) must stay zero
-    if ((h2 & 0x00007fffu) == 0) b2 &= 0xffff0000u;
-    if ((h2 & 0x7fff0000u) == 0) b2 &= 0x0000ffffu;
-    s0 = __byte_perm(b2, b2, 0x1010);
-    s1 = __byte_perm(b2, b2, 0x3232);
+    s0 = __byte_perm(h2, h2, 0x1010);
+    s1 = __byte_perm(h2, h2, 0x3232);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -261,12 +277,13 @@ struct ExpertArgs {
     const uint8_t* packed;    // bank base [slots, N, K/2]
     const uint8_t* scale;     // [slots, N, K/16]
     const uint16_t* global;   // [slots, N]
-    const __nv_bfloat16* act; // k-permuted activations: gate_up [tokens, K], down [routes, K]
+    const void* act;          // k-permuted activations: gate_up f16 [tokens, K], down f32 [routes, K]
+    const float* tok_scale;   // gate_up: per-token power-of-two scale of act
     const int4* groups;
     const int32_t* sorted_route;
     const int32_t* n_groups;
     const float* route_weight;  // down only
-    __nv_bfloat16* ic2;         // gate_up out: [routes, inter] bf16, k-permuted
+    float* ic2;                 // gate_up out: [routes, inter] f32, k-permuted
     float* yroute;              // down out: [routes, hidden] f32, weighted
     int32_t* err;
     int N, top_k, stages;
@@ -284,7 +301,9 @@ struct Cfg {
     // rows are contiguous in the bank and arrive with one copy (two-way conflicts on the reads)
     static constexpr int RSA = GATE_UP ? K / 2 + 64 : K / 2;
     static constexpr int RSS = K / 16;
-    static constexpr int RSX = K * 2 + 64;
+    // activation tile rows: f16 for gate_up, f32 for down; the padding keeps the reads conflict-free
+    static constexpr int kActBytes = GATE_UP ? 2 : 4;
+    static constexpr int RSX = K * kActBytes + (GATE_UP ? 64 : 16);
     static constexpr int kStageBytes = ROWS * (RSA + RSS);
     static constexpr int kXBytes = kGroupTokens * RSX;
 };
@@ -331,26 +350,29 @@ __global__ void __launch_bounds__(kThreads, 1) expert_mma_kernel(ExpertArgs a) {
     const int item_begin = (int)(total * blockIdx.x / gridDim.x);
     const int item_end = (int)(total * (blockIdx.x + 1) / gridDim.x);
     if (item_begin >= item_end) return;
+    int g = item_begin / blocks, blk = item_begin % blocks;
+    int4 grp = a.groups[g];
 
     if (warp == kConsumerWarps) {
         // ===================== producer: bulk copies of weights, scales and activations ==========
-        int xphase = 0, cur_group = -1;
+        int xphase = 0;
         int st = 0, phase = 0;
+        bool new_group = true;
         for (int item = item_begin; item < item_end; item++) {
-            const int g = item / blocks, blk = item % blocks;
-            const int4 grp = a.groups[g];
-            if (g != cur_group) {
+            if (new_group) {
                 // the group's token rows; the buffer is free once every warp holds its fragments
                 if (!mbar_wait(XEMPTY, xphase ^ 1, a.err)) return;
-                if (lane == 0) mbar_expect_tx(XFULL, (uint32_t)(grp.z * K * 2));
+                if (lane == 0) mbar_expect_tx(XFULL, (uint32_t)(grp.z * K * C::kActBytes));
                 __syncwarp();
                 if (lane < grp.z) {
                     const int route = a.sorted_route[grp.y + lane];
                     const int row = GATE_UP ? route / a.top_k : route;
-                    bulk_g2s(smem_u32(xbuf + (size_t)lane * RSX), a.act + (size_t)row * K, (uint32_t)(K * 2), XFULL);
+                    bulk_g2s(smem_u32(xbuf + (size_t)lane * RSX),
+                             reinterpret_cast<const uint8_t*>(a.act) + (size_t)row * K * C::kActBytes,
+                             (uint32_t)(K * C::kActBytes), XFULL);
                 }
-                cur_group = g;
                 xphase ^= 1;
+                new_group = false;
             }
             if (!mbar_wait(EMPTY(st), phase ^ 1, a.err)) return;
             if (lane == 0) mbar_expect_tx(FULL(st), (uint32_t)(ROWS * (K / 2 + K / 16)));
@@ -383,6 +405,12 @@ __global__ void __launch_bounds__(kThreads, 1) expert_mma_kernel(ExpertArgs a) {
                 st = 0;
                 phase ^= 1;
             }
+            if (++blk == blocks) {
+                blk = 0;
+                g++;
+                if (item + 1 < item_end) grp = a.groups[g];
+                new_group = true;
+            }
         }
         return;
     }
@@ -391,23 +419,62 @@ __global__ void __launch_bounds__(kThreads, 1) expert_mma_kernel(ExpertArgs a) {
     const int tile = warp / KS, ks = warp % KS;     // row tile of the item, K split index
     const int g8 = lane >> 2, t4 = lane & 3;        // fragment row group and k lane
     uint4 xf[WIN * 4];                              // this warp's B fragments of the current group
-    int xphase = 0, cur_group = -1;
+    float xscale = 1.0f;                            // down: this lane's token (g8) scale
+    int xphase = 0;
     int st = 0, phase = 0;
     int rs = 0, rphase = 0;
+    bool new_group = true;
     for (int item = item_begin; item < item_end; item++) {
-        const int g = item / blocks, blk = item % blocks;
-        const int4 grp = a.groups[g];
-        if (g != cur_group) {
+        if (new_group) {
             if (!mbar_wait(XFULL, xphase, a.err)) return;
-            const uint32_t xa = smem_u32(xbuf) + g8 * RSX + t4 * 16 + ks * WIN * 256;
+            if (GATE_UP) {
+                const uint32_t xa = smem_u32(xbuf) + g8 * RSX + t4 * 16 + ks * WIN * 256;
 #pragma unroll
-            for (int wi = 0; wi < WIN; wi++)
+                for (int wi = 0; wi < WIN; wi++)
 #pragma unroll
-                for (int j = 0; j < 4; j++) xf[wi * 4 + j] = lds128(xa + wi * 256 + j * 64);
+                    for (int j = 0; j < 4; j++) xf[wi * 4 + j] = lds128(xa + wi * 256 + j * 64);
+            } else {
+                // ic2 arrives as f32: scale token g8 by a power of two into the f16 range and pack.
+                // The scale is taken over this warp's own k slice, the partial sums are rescaled
+                // before they leave the warp.
+                const uint32_t xa = smem_u32(xbuf) + g8 * RSX + t4 * 32 + ks * WIN * 512;
+                float m = 0.f;
+#pragma unroll
+                for (int wi = 0; wi < WIN; wi++)
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const uint4 u = lds128(xa + wi * 512 + j * 128), v = lds128(xa + wi * 512 + j * 128 + 16);
+                        m = fmaxf(m, fmaxf(fmaxf(fabsf(__uint_as_float(u.x)), fabsf(__uint_as_float(u.y))),
+                                           fmaxf(fabsf(__uint_as_float(u.z)), fabsf(__uint_as_float(u.w)))));
+                        m = fmaxf(m, fmaxf(fmaxf(fabsf(__uint_as_float(v.x)), fabsf(__uint_as_float(v.y))),
+                                           fmaxf(fabsf(__uint_as_float(v.z)), fabsf(__uint_as_float(v.w)))));
+                    }
+                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+                const int e = (int)((__float_as_uint(m) >> 23) & 0xff);
+                float inv = 1.0f;
+                xscale = 1.0f;
+                if (e > 0 && e < 255) {
+                    inv = __uint_as_float((uint32_t)(127 + 14 - (e - 127)) << 23);
+                    xscale = __uint_as_float((uint32_t)(127 - 14 + (e - 127)) << 23);
+                }
+#pragma unroll
+                for (int wi = 0; wi < WIN; wi++)
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const uint4 u = lds128(xa + wi * 512 + j * 128), v = lds128(xa + wi * 512 + j * 128 + 16);
+                        __half2 h0 = __floats2half2_rn(__uint_as_float(u.x) * inv, __uint_as_float(u.y) * inv);
+                        __half2 h1 = __floats2half2_rn(__uint_as_float(u.z) * inv, __uint_as_float(u.w) * inv);
+                        __half2 h2 = __floats2half2_rn(__uint_as_float(v.x) * inv, __uint_as_float(v.y) * inv);
+                        __half2 h3 = __floats2half2_rn(__uint_as_float(v.z) * inv, __uint_as_float(v.w) * inv);
+                        xf[wi * 4 + j] = make_uint4(*reinterpret_cast<uint32_t*>(&h0), *reinterpret_cast<uint32_t*>(&h1),
+                                                    *reinterpret_cast<uint32_t*>(&h2), *reinterpret_cast<uint32_t*>(&h3));
+                    }
+            }
             __syncwarp();
             if (lane == 0) mbar_arrive(XEMPTY);
             xphase ^= 1;
-            cur_group = g;
+            new_group = false;
         }
         // operands of the epilogue, requested now so that their latency hides behind the MMAs
         const size_t slot_rows = (size_t)grp.x * a.N;
@@ -420,6 +487,9 @@ __global__ void __launch_bounds__(kThreads, 1) expert_mma_kernel(ExpertArgs a) {
                 const int pair = blk * (ROWS / 2) + tile * 8 + g8;
                 ga = f16_global_to_f32(a.global[slot_rows + pair]);
                 gb = f16_global_to_f32(a.global[slot_rows + a.N / 2 + pair]);
+                // per-token power-of-two scale of the f16 activations
+                if (2 * t4 < grp.z) rw0 = a.tok_scale[route0 / a.top_k];
+                if (2 * t4 + 1 < grp.z) rw1 = a.tok_scale[route1 / a.top_k];
             } else {
                 const int d = blk * ROWS + tile * 16 + g8;
                 ga = f16_global_to_f32(a.global[slot_rows + d]);
@@ -437,13 +507,11 @@ __global__ void __launch_bounds__(kThreads, 1) expert_mma_kernel(ExpertArgs a) {
         const uint32_t sc_lo = sp + ROWS * RSA + (tile * 16 + g8) * RSS + ks * WIN * 8;
         const uint32_t sc_hi = sc_lo + 8 * RSS;
         uint32_t scl[WIN * 2], sch[WIN * 2];
-        if (WIN * 8 >= 16) {
 #pragma unroll
-            for (int q = 0; q < WIN / 2; q++) {
-                const uint4 v = lds128(sc_lo + q * 16), u = lds128(sc_hi + q * 16);
-                scl[q * 4 + 0] = v.x; scl[q * 4 + 1] = v.y; scl[q * 4 + 2] = v.z; scl[q * 4 + 3] = v.w;
-                sch[q * 4 + 0] = u.x; sch[q * 4 + 1] = u.y; sch[q * 4 + 2] = u.z; sch[q * 4 + 3] = u.w;
-            }
+        for (int q = 0; q < WIN / 2; q++) {
+            const uint4 v = lds128(sc_lo + q * 16), u = lds128(sc_hi + q * 16);
+            scl[q * 4 + 0] = v.x; scl[q * 4 + 1] = v.y; scl[q * 4 + 2] = v.z; scl[q * 4 + 3] = v.w;
+            sch[q * 4 + 0] = u.x; sch[q * 4 + 1] = u.y; sch[q * 4 + 2] = u.z; sch[q * 4 + 3] = u.w;
         }
         float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
@@ -454,24 +522,25 @@ __global__ void __launch_bounds__(kThreads, 1) expert_mma_kernel(ExpertArgs a) {
             const uint32_t wl2 = (t4 & 2) ? scl[wi * 2 + 1] : scl[wi * 2];
             const uint32_t wh2 = (t4 & 2) ? sch[wi * 2 + 1] : sch[wi * 2];
             uint32_t slo0, slo1, shi0, shi1;
-            e4m3x2_to_bf16_scales((t4 & 1) ? (wl2 >> 16) : (wl2 & 0xffffu), slo0, slo1);
-            e4m3x2_to_bf16_scales((t4 & 1) ? (wh2 >> 16) : (wh2 & 0xffffu), shi0, shi1);
+            e4m3x2_to_f16_scales((t4 & 1) ? (wl2 >> 16) : (wl2 & 0xffffu), slo0, slo1);
+            e4m3x2_to_f16_scales((t4 & 1) ? (wh2 >> 16) : (wh2 & 0xffffu), shi0, shi1);
             const uint32_t wl[4] = {plo.x, plo.y, plo.z, plo.w};
             const uint32_t wh[4] = {phi.x, phi.y, phi.z, phi.w};
 #pragma unroll
             for (int j = 0; j < 4; j++) {
                 const uint4 xb = xf[wi * 4 + j];
                 uint32_t ql[4], qh[4];
-                e2m1x8_to_bf16x2(wl[j], ql);
-                e2m1x8_to_bf16x2(wh[j], qh);
+                e2m1x8_to_f16x2(wl[j], ql);
+                e2m1x8_to_f16x2(wh[j], qh);
                 const uint32_t sl = (j < 2) ? slo0 : slo1, sh = (j < 2) ? shi0 : shi1;
 #pragma unroll
                 for (int q = 0; q < 4; q++) {
-                    ql[q] = hmul2_bf16(ql[q], sl);
-                    qh[q] = hmul2_bf16(qh[q], sh);
+                    ql[q] = hmul2_f16(ql[q], sl);
+                    qh[q] = hmul2_f16(qh[q], sh);
                 }
-                mma_bf16(acc[0], ql[0], qh[0], ql[1], qh[1], xb.x, xb.y);
-                mma_bf16(acc[1], ql[2], qh[2], ql[3], qh[3], xb.z, xb.w);
+                // k slots (2t, 2t+1 | 2t+8, 2t+9) of the two MMAs <- the word's k (0,1 | 2,3) and (4,5 | 6,7)
+                mma_f16(acc[0], ql[0], qh[0], ql[1], qh[1], xb.x, xb.y);
+                mma_f16(acc[1], ql[2], qh[2], ql[3], qh[3], xb.z, xb.w);
             }
         }
         // the stage is consumed once every warp has read its fragments
@@ -484,6 +553,12 @@ __global__ void __launch_bounds__(kThreads, 1) expert_mma_kernel(ExpertArgs a) {
         float c4[4];
 #pragma unroll
         for (int q = 0; q < 4; q++) c4[q] = acc[0][q] + acc[1][q];
+        if (!GATE_UP) {
+            // undo this warp's token scales: columns 2*t4, 2*t4+1 belong to the lanes with g8 == column
+            const float s0 = __shfl_sync(0xffffffffu, xscale, (2 * t4) * 4);
+            const float s1 = __shfl_sync(0xffffffffu, xscale, (2 * t4 + 1) * 4);
+            c4[0] *= s0; c4[1] *= s1; c4[2] *= s0; c4[3] *= s1;
+        }
 
         // ---- K reduction across the warps of this row tile: warp ks == 0 gathers ----
         if (KS > 1) {
@@ -506,32 +581,38 @@ __global__ void __launch_bounds__(kThreads, 1) expert_mma_kernel(ExpertArgs a) {
             rs ^= 1;
             if (rs == 0) rphase ^= 1;
         }
-        if (ks != 0) continue;
 
         // ---- epilogue (warp ks == 0 of each row tile) ----
         // c4[0], c4[1]: fragment row g8, tokens 2*t4, 2*t4+1;  c4[2], c4[3]: row g8 + 8
-        const float unscale = 65536.0f;  // the weights carried 2^-16
-        if (GATE_UP) {
-            const int pk = perm_k(blk * (ROWS / 2) + tile * 8 + g8);
-            const float gg = ga * unscale, gu = gb * unscale;
+        if (ks == 0) {
+            if (GATE_UP) {
+                const int pk = perm_k(blk * (ROWS / 2) + tile * 8 + g8);
 #pragma unroll
-            for (int c = 0; c < 2; c++) {
-                if (2 * t4 + c < grp.z) {
-                    const float gate = c4[c] * gg, up = c4[2 + c] * gu;
-                    const float v = (gate / (1.0f + __expf(-gate))) * up;
-                    a.ic2[(size_t)(c ? route1 : route0) * (a.N / 2) + pk] = __float2bfloat16_rn(v);
+                for (int c = 0; c < 2; c++) {
+                    if (2 * t4 + c < grp.z) {
+                        const float ts = c ? rw1 : rw0;
+                        const float gate = c4[c] * ga * ts, up = c4[2 + c] * gb * ts;
+                        a.ic2[(size_t)(c ? route1 : route0) * (a.N / 2) + pk] = (gate / (1.0f + __expf(-gate))) * up;
+                    }
+                }
+            } else {
+                const int d = blk * ROWS + tile * 16 + g8;
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    const float gd = h ? gb : ga;
+#pragma unroll
+                    for (int c = 0; c < 2; c++)
+                        if (2 * t4 + c < grp.z)
+                            a.yroute[(size_t)(c ? route1 : route0) * a.N + d + 8 * h] =
+                                (c ? rw1 : rw0) * (c4[2 * h + c] * gd);
                 }
             }
-        } else {
-            const int d = blk * ROWS + tile * 16 + g8;
-#pragma unroll
-            for (int h = 0; h < 2; h++) {
-                const float gd = (h ? gb : ga) * unscale;
-#pragma unroll
-                for (int c = 0; c < 2; c++)
-                    if (2 * t4 + c < grp.z)
-                        a.yroute[(size_t)(c ? route1 : route0) * a.N + d + 8 * h] = (c ? rw1 : rw0) * (c4[2 * h + c] * gd);
-            }
+        }
+        if (++blk == blocks) {
+            blk = 0;
+            g++;
+            if (item + 1 < item_end) grp = a.groups[g];
+            new_group = true;
         }
     }
 }
@@ -581,10 +662,7 @@ int launch_decode_mma(const BankView& b, const void* x, int x_dtype, const int32
     const int routes = tokens * top_k;
     int launches = 0;
     c.begin(K_PERMUTE_ACT);
-    {
-        size_t n = (size_t)tokens * b.hidden;
-        permute_act_kernel<<<(unsigned)((n + 255) / 256), 256, 0, c.s>>>(x, x_dtype, tokens, b.hidden, sc.xperm);
-    }
+    prep_act_kernel<<<tokens, 256, 0, c.s>>>(x, x_dtype, b.hidden, sc.xh, sc.tok_scale);
     c.end();
     c.begin(K_DECODE_PLAN);
     decode_plan_kernel<<<1, kPlanThreads, 0, c.s>>>(route_slot, routes, sc.groups, sc.sorted_route, sc.n_groups);
@@ -600,7 +678,7 @@ int launch_decode_mma(const BankView& b, const void* x, int x_dtype, const int32
     a.top_k = top_k;
     // gate_up: K = hidden, N = 2 * inter rows
     a.packed = b.gu_packed; a.scale = b.gu_scale; a.global = b.gu_global;
-    a.act = sc.xperm; a.ic2 = sc.ic2p; a.N = 2 * b.inter;
+    a.act = sc.xh; a.tok_scale = sc.tok_scale; a.ic2 = sc.ic2p; a.N = 2 * b.inter;
     c.begin(K_EXPERT_GATE_UP);
     launch_expert<true, 4, 4>(a, sm_count, c.s);   // K = 2048: 4 warps x 4 windows, 32 rows per item
     c.end();

@@ -57,8 +57,9 @@ int launch_decode_routes(const BankView& b, const __nv_bfloat16* x, const int32_
 
 // decode_mma.cu: grouped decode path (plan + k-permuted activations + TMA/mma.sync expert kernels)
 struct DecodeScratch {
-    __nv_bfloat16* xperm;   // [tokens, hidden] bf16, k-permuted
-    __nv_bfloat16* ic2p;    // [routes, inter] bf16, k-permuted
+    __half* xh;             // [tokens, hidden] f16, k-permuted, scaled per token
+    float* tok_scale;       // [tokens] power-of-two scale that undoes it
+    float* ic2p;            // [routes, inter] f32, k-permuted
     int4* groups;           // [routes] (slot, first sorted position, count <= 8, 0)
     int32_t* sorted_route;  // [routes]
     int32_t* n_groups;      // [1]

@@ -85,6 +85,116 @@ router_logits_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
     }
 }
 
+// ---- tiled variant for hidden % 256 == 0 -----------------------------------------------------
+// CTA = 4 warps, tile = 32 experts x 16 tokens; lane = expert, each warp owns 4 tokens, so a thread
+// walks 4 independent chains (enough to cover the FMA latency).  The gate rows stream through a
+// double-buffered shared tile filled with 16-byte cp.async; the activations are widened to f32
+// and stored k-major so that one broadcast 128-bit load feeds the warp's 4 tokens.
+constexpr int kTileE = 32, kTileT = 16, kKC = 256;
+constexpr int kWStride = kKC * 2 + 16;  // bytes per expert row in shared memory (conflict-free 128-bit reads)
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+
+__global__ void __launch_bounds__(128)
+router_logits_tiled_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gate_w,
+                           int tokens, int experts, int hidden, float* __restrict__ logits) {
+    extern __shared__ __align__(16) uint8_t rsm[];
+    uint8_t* const wbuf = rsm;                                                  // [2][32][kWStride]
+    float* const xbuf = reinterpret_cast<float*>(rsm + 2 * kTileE * kWStride);  // [2][kKC][16]
+    const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+    const int e0 = blockIdx.x * kTileE, t0 = blockIdx.y * kTileT;
+    const int nchunks = hidden / kKC;
+    const uint32_t wbase = (uint32_t)__cvta_generic_to_shared(wbuf);
+
+    auto issue_w = [&](int c, int b) {
+        for (int i = tid; i < kTileE * (kKC / 8); i += 128) {
+            const int row = i / (kKC / 8), piece = i % (kKC / 8);
+            const int e = min(e0 + row, experts - 1);
+            cp_async16(wbase + b * kTileE * kWStride + row * kWStride + piece * 16,
+                       gate_w + (size_t)e * hidden + c * kKC + piece * 8);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    // activations: thread -> token tid % 16, 16-byte pieces tid / 16 + 8 * i
+    const int xtl = tid % 16, xpc = tid / 16;
+    uint4 xr[4];
+    auto load_x = [&](int c) {
+        const int t = t0 + xtl;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            xr[i] = make_uint4(0, 0, 0, 0);
+            if (t < tokens)
+                xr[i] = *reinterpret_cast<const uint4*>(x + (size_t)t * hidden + c * kKC + (xpc + 8 * i) * 8);
+        }
+    };
+    auto store_x = [&](int b) {
+        float* xs = xbuf + b * kKC * kTileT;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int k = (xpc + 8 * i) * 8;
+            const uint32_t w[4] = {xr[i].x, xr[i].y, xr[i].z, xr[i].w};
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const float2 v = bf16x2_to_f32(w[q]);
+                xs[(k + 2 * q) * kTileT + xtl] = v.x;
+                xs[(k + 2 * q + 1) * kTileT + xtl] = v.y;
+            }
+        }
+    };
+
+    issue_w(0, 0);
+    load_x(0);
+    store_x(0);
+    const bool active = t0 + warp * 4 < tokens;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int c = 0; c < nchunks; c++) {
+        const int b = c & 1;
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        if (c + 1 < nchunks) {
+            issue_w(c + 1, b ^ 1);
+            load_x(c + 1);
+        }
+        if (active) {
+            const uint32_t wrow = wbase + b * kTileE * kWStride + lane * kWStride;
+            const float* xs = xbuf + b * kKC * kTileT + warp * 4;
+#pragma unroll 4
+            for (int kk = 0; kk < kKC; kk += 8) {
+                uint4 wv;
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(wv.x), "=r"(wv.y), "=r"(wv.z), "=r"(wv.w)
+                             : "r"(wrow + kk * 2));
+                const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    const float2 w2 = bf16x2_to_f32(ww[q]);
+                    const float4 xa = *reinterpret_cast<const float4*>(xs + (kk + 2 * q) * kTileT);
+                    const float4 xb = *reinterpret_cast<const float4*>(xs + (kk + 2 * q + 1) * kTileT);
+                    acc[0] = __fmaf_rn(xa.x, w2.x, acc[0]);
+                    acc[1] = __fmaf_rn(xa.y, w2.x, acc[1]);
+                    acc[2] = __fmaf_rn(xa.z, w2.x, acc[2]);
+                    acc[3] = __fmaf_rn(xa.w, w2.x, acc[3]);
+                    acc[0] = __fmaf_rn(xb.x, w2.y, acc[0]);
+                    acc[1] = __fmaf_rn(xb.y, w2.y, acc[1]);
+                    acc[2] = __fmaf_rn(xb.z, w2.y, acc[2]);
+                    acc[3] = __fmaf_rn(xb.w, w2.y, acc[3]);
+                }
+            }
+        }
+        if (c + 1 < nchunks) store_x(b ^ 1);
+    }
+    const int e = e0 + lane;
+    if (active && e < experts) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int t = t0 + warp * 4 + i;
+            if (t < tokens) logits[(size_t)t * experts + e] = acc[i];
+        }
+    }
+}
+
 // One warp per token.  experts <= 32 * kMaxPerLane.
 constexpr int kMaxPerLane = 16;
 constexpr int kTopkWarps = 4;
@@ -92,11 +202,9 @@ constexpr int kTopkWarps = 4;
 __global__ void __launch_bounds__(kTopkWarps * 32)
 router_topk_kernel(const float* __restrict__ logits, int tokens, int experts, int top_k,
                    int32_t* __restrict__ ids, float* __restrict__ weights) {
-    extern __shared__ float es[];  // [kTopkWarps][experts]
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int t = blockIdx.x * kTopkWarps + warp;
     if (t >= tokens) return;
-    float* e_row = es + warp * experts;
     const float* row = logits + (size_t)t * experts;
     const int per = (experts + 31) / 32;
 
@@ -117,15 +225,18 @@ router_topk_kernel(const float* __restrict__ logits, int tokens, int experts, in
         int e = lane * per + i;
         if (i < per && e < experts) {
             v[i] = ftm_expf(__fadd_rn(v[i], -mx));
-            e_row[e] = v[i];
         }
     }
-    __syncwarp();
-    // the host sums the exponentials over e ascending; one lane repeats that order
+    // the host sums the exponentials over e ascending: the running sum is handed from lane to lane,
+    // each adding its own (contiguous) experts in order
     float sum = 0.0f;
-    if (lane == 0)
-        for (int e = 0; e < experts; e++) sum = __fadd_rn(sum, e_row[e]);
-    sum = __shfl_sync(0xffffffffu, sum, 0);
+    for (int l = 0; l < 32; l++) {
+        float s2 = sum;
+#pragma unroll
+        for (int i = 0; i < kMaxPerLane; i++)
+            if (i < per && lane * per + i < experts) s2 = __fadd_rn(s2, v[i]);
+        sum = __shfl_sync(0xffffffffu, s2, l);
+    }
     const float inv = __fdiv_rn(1.0f, sum);
 #pragma unroll
     for (int i = 0; i < kMaxPerLane; i++) {
@@ -177,6 +288,19 @@ router_topk_kernel(const float* __restrict__ logits, int tokens, int experts, in
 
 int launch_router_logits(const __nv_bfloat16* x, const __nv_bfloat16* gate_w, int tokens, int experts,
                          int hidden, float* logits, const Ctx& c) {
+    if (hidden % kKC == 0) {
+        dim3 grid((experts + kTileE - 1) / kTileE, (tokens + kTileT - 1) / kTileT);
+        const size_t smem = 2 * kTileE * kWStride + 2 * kKC * kTileT * sizeof(float);
+        static bool attr2 = false;
+        if (!attr2) {
+            cudaFuncSetAttribute(router_logits_tiled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            attr2 = true;
+        }
+        c.begin(K_ROUTER_LOGITS);
+        router_logits_tiled_kernel<<<grid, 128, smem, c.s>>>(x, gate_w, tokens, experts, hidden, logits);
+        c.end();
+        return 1;
+    }
     dim3 block(kExpertsPerCta, kTokGroups);
     int etiles = (experts + kExpertsPerCta - 1) / kExpertsPerCta;
     if (tokens <= kTokGroups) {
@@ -205,9 +329,8 @@ int launch_router_logits(const __nv_bfloat16* x, const __nv_bfloat16* gate_w, in
 int launch_router_topk(const float* logits, int tokens, int experts, int top_k, int32_t* ids,
                        float* weights, const Ctx& c) {
     int grid = (tokens + kTopkWarps - 1) / kTopkWarps;
-    size_t smem = (size_t)kTopkWarps * experts * sizeof(float);
     c.begin(K_ROUTER_TOPK);
-    router_topk_kernel<<<grid, kTopkWarps * 32, smem, c.s>>>(logits, tokens, experts, top_k, ids, weights);
+    router_topk_kernel<<<grid, kTopkWarps * 32, 0, c.s>>>(logits, tokens, experts, top_k, ids, weights);
     c.end();
     return 1;
 }
