@@ -241,15 +241,30 @@ def run_b200(args):
     e2e = {"value": world * T * K / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": T * HIDDEN * 2,
            "d2h_bytes_per_step": T * HIDDEN * 2}
 
-    # per-kernel profile pass (CUDA events around every launch) for the roofline of the dominant kernel
+    # per-kernel profile pass (CUDA events around every launch) for the roofline of the dominant kernel.
+    # The routed half runs alone here (serving call with the router's ids), so that the shared expert,
+    # which the whole block overlaps on a second stream, does not share the SMs with the timed kernels.
+    routed = []
+    for l in range(nlayers):
+        step(l)
+        torch.cuda.synchronize()
+        routed.append((ids.clone(), wts.clone()))
+    uniq = [int(torch.unique(i).numel()) for i, _ in routed]
+    reqs = [pkg.MoEDeviceRequest(l, HIDDEN, INTER, TOP_K, xs[l], routed[l][0], routed[l][1]) for l in range(nlayers)]
+    for i in range(W):
+        moe.grouped_moe_staged(reqs[i % nlayers], out)
     moe.profile(True)
-    uniq = []
     for i in range(K):
-        step(W + i)
-        if i < nlayers:
-            torch.cuda.synchronize()
-            uniq.append(int(torch.unique(ids).numel()))
+        moe.grouped_moe_staged(reqs[i % nlayers], out)
     prof = moe.profile_read()
+    moe.profile(False)
+    # the router and shared-expert kernels, each alone on the stream
+    moe.profile(True)
+    for i in range(K):
+        g, su, sd, sg = dense[i % nlayers]
+        moe.router(xs[i % nlayers], g)
+        moe.shared_expert(xs[i % nlayers], su, sd, sg)
+    prof.update(moe.profile_read())
     moe.profile(False)
     U = sum(uniq) / len(uniq)
     pk = peaks()

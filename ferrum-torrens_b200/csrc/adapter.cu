@@ -211,19 +211,30 @@ int check_tokens(const ftm_handle* h, int64_t tokens, int top_k) {
     return FTM_OK;
 }
 
-// routed experts over route_slot / weights -> out (routed sum only when shared == nullptr)
+int stage_x(ftm_handle* h, const void* x, int x_dtype, int tokens, const __nv_bfloat16** out, cudaStream_t s);
+
+// routed experts -> out (routed sum only when shared == nullptr).  The routes are slot ids in
+// h->route_slot, or, when `expert_ids` is set, dense expert ids of `layer` still to be mapped.
 // `join`, when set, is waited on just before the pass that reads `shared`.
-int run_routed(ftm_handle* h, const __nv_bfloat16* x, const int32_t* route_slot, const float* weights, int tokens,
-               const float* shared, const float* se_gate, cudaEvent_t join, void* out, int out_dtype, int path,
-               cudaStream_t s) {
+int run_routed(ftm_handle* h, const void* x, int x_dtype, const void* expert_ids, int ids_dtype, int layer,
+               const float* weights, int tokens, const float* shared, const float* se_gate, cudaEvent_t join,
+               void* out, int out_dtype, int path, cudaStream_t s) {
     BankView b = bank_view(h);
     const int routes = tokens * h->cfg.top_k;
-    if (path != FTM_PATH_SCALAR && decode_mma_supported(h->cfg.hidden, h->cfg.inter, routes)) {
+    if (path != FTM_PATH_SCALAR && decode_mma_supported(h->cfg.hidden, h->cfg.inter, routes, h->cfg.slots)) {
         DecodeScratch sc{h->xh, h->tok_scale, h->ic2p, h->groups, h->sorted_route, h->n_groups, h->yroute, h->flags + 2};
-        h->launches += launch_decode_mma(b, x, FTM_BF16, route_slot, weights, tokens, h->cfg.top_k, sc, h->sm_count,
-                                         h->ctx(s));
+        DecodeRoutes rt{expert_ids ? nullptr : h->route_slot, expert_ids, ids_dtype, layer, h->cfg.experts,
+                        (int)h->slot_for_id.size(), h->d_slot_for_id, h->route_slot, h->flags + 1};
+        h->launches += launch_decode_mma(b, x, x_dtype, rt, weights, tokens, h->cfg.top_k, sc, h->sm_count, h->ctx(s));
     } else {
-        h->launches += launch_decode_routes(b, x, route_slot, weights, tokens, h->cfg.top_k, h->ic2, h->yroute,
+        const __nv_bfloat16* xb = nullptr;
+        int rc = stage_x(h, x, x_dtype, tokens, &xb, s);
+        if (rc != FTM_OK) return rc;
+        if (expert_ids)
+            h->launches += launch_slot_rewrite(expert_ids, ids_dtype, routes, layer, h->cfg.experts, h->d_slot_for_id,
+                                               (int)h->slot_for_id.size(), h->route_slot, h->route_expert,
+                                               h->flags + 1, h->ctx(s));
+        h->launches += launch_decode_routes(b, xb, h->route_slot, weights, tokens, h->cfg.top_k, h->ic2, h->yroute,
                                             h->ctx(s));
     }
     if (join) CU(h, cudaStreamWaitEvent(s, join, 0));
@@ -571,8 +582,8 @@ FTM_API int ftm_grouped_moe_host(ftm_handle* h, const float* x, size_t x_len, in
     CU(h, cudaMemcpyAsync(h->x_bf16, xb.data(), x_len * 2, cudaMemcpyHostToDevice, s));
     CU(h, cudaMemcpyAsync(h->route_slot, routes, R * sizeof(int32_t), cudaMemcpyHostToDevice, s));
     CU(h, cudaMemcpyAsync(h->rweights, weights, R * sizeof(float), cudaMemcpyHostToDevice, s));
-    rc = run_routed(h, h->x_bf16, h->route_slot, h->rweights, (int)tokens, nullptr, nullptr, nullptr, h->routed_f32,
-                    FTM_F32, FTM_PATH_AUTO, s);
+    rc = run_routed(h, h->x_bf16, FTM_BF16, nullptr, 0, 0, h->rweights, (int)tokens, nullptr, nullptr, nullptr,
+                    h->routed_f32, FTM_F32, FTM_PATH_AUTO, s);
     if (rc != FTM_OK) return rc;
     CU(h, cudaGetLastError());
     CU(h, cudaMemcpyAsync(out, h->routed_f32, tokens * H * sizeof(float), cudaMemcpyDeviceToHost, s));
@@ -595,10 +606,9 @@ FTM_API int ftm_grouped_moe_dev(ftm_handle* h, const void* x, int x_dtype, int32
     if (out_dtype != FTM_BF16 && out_dtype != FTM_F32) return fail(h, FTM_ERR_BAD, "moe: out cannot be dtype %d", out_dtype);
     if ((rc = check_host_routes(h, routes_host, R)) != FTM_OK) return rc;
     cudaStream_t s = pick(h, stream);
-    const __nv_bfloat16* xb = nullptr;
-    if ((rc = stage_x(h, x, x_dtype, tokens, &xb, s)) != FTM_OK) return rc;
+    if (x_dtype != FTM_BF16 && x_dtype != FTM_F32) return fail(h, FTM_ERR_BAD, "moe: activations cannot be dtype %d", x_dtype);
     CU(h, cudaMemcpyAsync(h->route_slot, routes_host, R * sizeof(int32_t), cudaMemcpyHostToDevice, s));
-    rc = run_routed(h, xb, h->route_slot, weights_dev, tokens, nullptr, nullptr, nullptr, out, out_dtype,
+    rc = run_routed(h, x, x_dtype, nullptr, 0, 0, weights_dev, tokens, nullptr, nullptr, nullptr, out, out_dtype,
                     FTM_PATH_AUTO, s);
     if (rc != FTM_OK) return rc;
     CU(h, cudaGetLastError());
@@ -618,13 +628,10 @@ static int staged_locked(ftm_handle* h, int32_t layer, const void* x, int x_dtyp
         return fail(h, FTM_ERR_BAD, "moe: expert ids cannot be dtype %d", ids_dtype);
     if (out_dtype != FTM_BF16 && out_dtype != FTM_F32) return fail(h, FTM_ERR_BAD, "moe: out cannot be dtype %d", out_dtype);
     if (path < FTM_PATH_AUTO || path > FTM_PATH_SCALAR) return fail(h, FTM_ERR_BAD, "moe: unknown path %d", path);
-    const __nv_bfloat16* xb = nullptr;
-    if ((rc = stage_x(h, x, x_dtype, tokens, &xb, s)) != FTM_OK) return rc;
-    const int R = tokens * h->cfg.top_k;
-    // the adapter's own copy of the ids, rewritten to slots through the residency table
-    h->launches += launch_slot_rewrite(expert_ids, ids_dtype, R, layer, h->cfg.experts, h->d_slot_for_id,
-                                       (int)h->slot_for_id.size(), h->route_slot, h->route_expert, h->flags + 1, h->ctx(s));
-    rc = run_routed(h, xb, h->route_slot, weights, tokens, shared, se_gate, join, out, out_dtype, path, s);
+    if (x_dtype != FTM_BF16 && x_dtype != FTM_F32) return fail(h, FTM_ERR_BAD, "moe: activations cannot be dtype %d", x_dtype);
+    // the adapter keeps its own copy of the ids, rewritten to slots through the residency table
+    rc = run_routed(h, x, x_dtype, expert_ids, ids_dtype, layer, weights, tokens, shared, se_gate, join, out,
+                    out_dtype, path, s);
     if (rc != FTM_OK) return rc;
     CU(h, cudaGetLastError());
     h->steps++;

@@ -76,114 +76,141 @@ prep_act_kernel(const void* __restrict__ x, int dtype, int K, __half* __restrict
 }
 
 // ------------------------------------------------------------------------------------------
-// plan: stable sort of the routes by slot, groups of <= 8 routes of one slot
+// plan: bucket the routes by slot, cut every slot's bucket into groups of <= 8 routes
+//
+// One CTA.  A counting sort over the slot range (histogram in shared memory, prefix sums of the
+// counts and of the group counts, scatter through the claimed positions).  Which routes of a slot
+// share a group depends on the order the atomics land in, which does not matter: every route's
+// result is computed from its own activations only.  The same pass maps dense expert ids to slots
+// through the residency table (the serving call) and clears the output rows of routes whose expert
+// is not resident.
 // ------------------------------------------------------------------------------------------
 constexpr int kPlanThreads = 1024;
 constexpr int kPlanMaxRoutes = 2048;
 
-__global__ void __launch_bounds__(kPlanThreads)
-decode_plan_kernel(const int32_t* __restrict__ route_slot, int routes, int4* __restrict__ groups,
-                   int32_t* __restrict__ sorted_route, int32_t* __restrict__ n_groups) {
-    __shared__ uint32_t keys[kPlanMaxRoutes];
-    __shared__ int scan[kPlanMaxRoutes];
-    __shared__ int wsum[32];
-    const int tid = threadIdx.x;
-    int n = 1;
-    while (n < routes) n <<= 1;
-    if (n < 2) n = 2;
-    // key = (slot + 1, route): non-resident routes (slot -1) sort first, padding sorts last
-    for (int i = tid; i < n; i += kPlanThreads) {
-        uint32_t k = 0xffffffffu;
-        if (i < routes) {
-            int s = route_slot[i];
-            k = ((uint32_t)(s < 0 ? 0 : s + 1) << 11) | (uint32_t)i;
-        }
-        keys[i] = k;
-    }
+struct PlanArgs {
+    const int32_t* route_slot_in;  // slot ids, or null when expert ids are given
+    const void* expert_ids;        // dense expert ids of `layer` (i32 / i64 / f32)
+    int ids_dtype, layer, experts, n_ids;
+    const int32_t* slot_for_id;
+    int32_t* route_slot_out;       // slot per route (-1 = not resident); may alias route_slot_in
+    int routes, slots, hidden;
+    int4* groups;
+    int32_t* sorted_route;
+    int32_t* n_groups;
+    float* yroute;
+    int32_t* bad_flag;
+};
+
+__global__ void __launch_bounds__(kPlanThreads) decode_plan_kernel(PlanArgs a) {
+    extern __shared__ int psm[];
+    int* const cnt = psm;                 // [slots]
+    int* const pos_base = cnt + a.slots;  // [slots]
+    int* const grp_base = pos_base + a.slots;
+    __shared__ int wsum_pos[32], wsum_grp[32];
+    __shared__ int s_missing[kPlanMaxRoutes];
+    __shared__ int s_nmissing;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int i = tid; i < a.slots; i += kPlanThreads) cnt[i] = 0;
+    if (tid == 0) s_nmissing = 0;
     __syncthreads();
-    for (int size = 2; size <= n; size <<= 1) {
-        for (int stride = size >> 1; stride > 0; stride >>= 1) {
-            for (int i = tid; i < n / 2; i += kPlanThreads) {
-                int lo = 2 * i - (i & (stride - 1));
-                int hi = lo + stride;
-                bool up = ((lo & size) == 0);
-                uint32_t a = keys[lo], b = keys[hi];
-                if ((a > b) == up) {
-                    keys[lo] = b;
-                    keys[hi] = a;
+    // each thread owns up to two routes
+    int slot[2], claim[2];
+#pragma unroll
+    for (int q = 0; q < 2; q++) {
+        const int r = tid + q * kPlanThreads;
+        slot[q] = -2;
+        claim[q] = 0;
+        if (r < a.routes) {
+            int sl;
+            if (a.route_slot_in) {
+                sl = a.route_slot_in[r];
+            } else {
+                long long e;
+                if (a.ids_dtype == 3)
+                    e = reinterpret_cast<const long long*>(a.expert_ids)[r];
+                else if (a.ids_dtype == 1)
+                    e = (long long)reinterpret_cast<const float*>(a.expert_ids)[r];
+                else
+                    e = (long long)reinterpret_cast<const int32_t*>(a.expert_ids)[r];
+                sl = -1;
+                if (e >= 0 && e < a.experts) {
+                    const long long id = (long long)a.layer * a.experts + e;
+                    if (id < a.n_ids) sl = a.slot_for_id[id];
+                } else {
+                    atomicExch(a.bad_flag, 1);
                 }
             }
-            __syncthreads();
+            if (sl >= a.slots) sl = -1;
+            if (a.route_slot_out) a.route_slot_out[r] = sl;
+            slot[q] = sl;
+            if (sl >= 0)
+                claim[q] = atomicAdd(&cnt[sl], 1);
+            else
+                s_missing[atomicAdd(&s_nmissing, 1)] = r;
         }
-    }
-    // group starts: a resident route whose position inside its slot's run is a multiple of 8.
-    // Position inside the run = i - start(i); start(i) by a running maximum over run starts.
-    for (int i = tid; i < n; i += kPlanThreads) {
-        int v = 0;
-        if (i < routes) {
-            uint32_t s = keys[i] >> 11;
-            bool start = (i == 0) || ((keys[i - 1] >> 11) != s);
-            v = start ? i : 0;
-        }
-        scan[i] = v;
     }
     __syncthreads();
-    // inclusive max-scan (Hillis-Steele over shared memory; n <= 2048)
-    for (int off = 1; off < n; off <<= 1) {
-        int v0 = 0, v1 = 0;
-        int i0 = tid, i1 = tid + kPlanThreads;
-        if (i0 < n) v0 = (i0 >= off) ? max(scan[i0], scan[i0 - off]) : scan[i0];
-        if (i1 < n) v1 = (i1 >= off) ? max(scan[i1], scan[i1 - off]) : scan[i1];
-        __syncthreads();
-        if (i0 < n) scan[i0] = v0;
-        if (i1 < n) scan[i1] = v1;
-        __syncthreads();
+    // prefix sums over the slots: thread t scans slots [t*per, (t+1)*per)
+    const int per = (a.slots + kPlanThreads - 1) / kPlanThreads;
+    const int s0 = tid * per, s1 = min(s0 + per, a.slots);
+    int lp = 0, lg = 0;
+    for (int i = s0; i < s1; i++) {
+        lp += cnt[i];
+        lg += (cnt[i] + 7) >> 3;
     }
-    // flags -> exclusive sum scan (two elements per thread, warp scan + block scan)
-    int f[2], idx[2];
-#pragma unroll
-    for (int q = 0; q < 2; q++) {
-        int i = 2 * tid + q;
-        idx[q] = i;
-        f[q] = 0;
-        if (i < routes) {
-            uint32_t s = keys[i] >> 11;
-            if (s != 0 && ((i - scan[i]) & 7) == 0) f[q] = 1;
-        }
-    }
-    int local = f[0] + f[1];
-    int incl = local;
-    const int lane = tid & 31, warp = tid >> 5;
+    int ip = lp, ig = lg;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
-        int v = __shfl_up_sync(0xffffffffu, incl, o);
-        if (lane >= o) incl += v;
+        const int vp = __shfl_up_sync(0xffffffffu, ip, o), vg = __shfl_up_sync(0xffffffffu, ig, o);
+        if (lane >= o) {
+            ip += vp;
+            ig += vg;
+        }
     }
-    if (lane == 31) wsum[warp] = incl;
+    if (lane == 31) {
+        wsum_pos[warp] = ip;
+        wsum_grp[warp] = ig;
+    }
     __syncthreads();
     if (warp == 0) {
-        int v = wsum[lane], inc2 = v;
+        const int vp = wsum_pos[lane], vg = wsum_grp[lane];
+        int jp = vp, jg = vg;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
-            int u = __shfl_up_sync(0xffffffffu, inc2, o);
-            if (lane >= o) inc2 += u;
+            const int up = __shfl_up_sync(0xffffffffu, jp, o), ug = __shfl_up_sync(0xffffffffu, jg, o);
+            if (lane >= o) {
+                jp += up;
+                jg += ug;
+            }
         }
-        wsum[lane] = inc2 - v;
-        if (lane == 31) *n_groups = inc2;
+        wsum_pos[lane] = jp - vp;
+        wsum_grp[lane] = jg - vg;
+        if (lane == 31) *a.n_groups = jg;
     }
     __syncthreads();
-    int base = wsum[warp] + incl - local;
+    int bp = wsum_pos[warp] + ip - lp, bg = wsum_grp[warp] + ig - lg;
+    for (int i = s0; i < s1; i++) {
+        pos_base[i] = bp;
+        grp_base[i] = bg;
+        bp += cnt[i];
+        bg += (cnt[i] + 7) >> 3;
+    }
+    __syncthreads();
 #pragma unroll
     for (int q = 0; q < 2; q++) {
-        int i = idx[q];
-        if (i < routes) sorted_route[i] = (int32_t)(keys[i] & 2047u);
-        if (f[q]) {
-            uint32_t s = keys[i] >> 11;
-            int cnt = 1;
-            while (cnt < 8 && i + cnt < routes && (keys[i + cnt] >> 11) == s) cnt++;
-            groups[base] = make_int4((int)s - 1, i, cnt, 0);
-            base++;
+        const int r = tid + q * kPlanThreads;
+        if (slot[q] >= 0) {
+            const int sl = slot[q], c = claim[q];
+            a.sorted_route[pos_base[sl] + c] = r;
+            if ((c & 7) == 0) a.groups[grp_base[sl] + (c >> 3)] = make_int4(sl, pos_base[sl] + c, min(8, cnt[sl] - c), 0);
         }
+    }
+    // routes without a resident expert contribute zeros
+    const int nm = s_nmissing;
+    for (int m = 0; m < nm; m++) {
+        float* row = a.yroute + (size_t)s_missing[m] * a.hidden;
+        for (int d = tid; d < a.hidden; d += kPlanThreads) row[d] = 0.f;
     }
 }
 
@@ -308,8 +335,8 @@ struct Cfg {
     static constexpr int kXBytes = kGroupTokens * RSX;
 };
 
-template <bool GATE_UP, int KS, int WIN>
-__global__ void __launch_bounds__(kThreads, 1) expert_mma_kernel(ExpertArgs a) {
+template <bool GATE_UP, int KS, int WIN, int OCC>
+__global__ void __launch_bounds__(kThreads, OCC) expert_mma_kernel(ExpertArgs a) {
     using C = Cfg<GATE_UP, KS, WIN>;
     constexpr int K = C::K, ROWS = C::ROWS, RSA = C::RSA, RSS = C::RSS, RSX = C::RSX;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -420,12 +447,22 @@ __global__ void __launch_bounds__(kThreads, 1) expert_mma_kernel(ExpertArgs a) {
     const int g8 = lane >> 2, t4 = lane & 3;        // fragment row group and k lane
     uint4 xf[WIN * 4];                              // this warp's B fragments of the current group
     float xscale = 1.0f;                            // down: this lane's token (g8) scale
+    // per group, for the two token columns (2*t4, 2*t4+1) this lane's accumulators hold: the route
+    // and its factor (gate_up: the token's activation scale; down: the route weight)
+    int route0 = 0, route1 = 0;
+    float rw0 = 0.f, rw1 = 0.f;
     int xphase = 0;
     int st = 0, phase = 0;
     int rs = 0, rphase = 0;
     bool new_group = true;
     for (int item = item_begin; item < item_end; item++) {
         if (new_group) {
+            if (ks == 0) {
+                route0 = (2 * t4 < grp.z) ? a.sorted_route[grp.y + 2 * t4] : 0;
+                route1 = (2 * t4 + 1 < grp.z) ? a.sorted_route[grp.y + 2 * t4 + 1] : 0;
+                rw0 = GATE_UP ? a.tok_scale[route0 / a.top_k] : a.route_weight[route0];
+                rw1 = GATE_UP ? a.tok_scale[route1 / a.top_k] : a.route_weight[route1];
+            }
             if (!mbar_wait(XFULL, xphase, a.err)) return;
             if (GATE_UP) {
                 const uint32_t xa = smem_u32(xbuf) + g8 * RSX + t4 * 16 + ks * WIN * 256;
@@ -476,26 +513,18 @@ __global__ void __launch_bounds__(kThreads, 1) expert_mma_kernel(ExpertArgs a) {
             xphase ^= 1;
             new_group = false;
         }
-        // operands of the epilogue, requested now so that their latency hides behind the MMAs
-        const size_t slot_rows = (size_t)grp.x * a.N;
-        float ga = 0.f, gb = 0.f, rw0 = 0.f, rw1 = 0.f;
-        int route0 = 0, route1 = 0;
+        // the two rows' f16 globals: requested now (raw), converted after the MMAs
+        uint16_t graw_a = 0, graw_b = 0;
         if (ks == 0) {
-            if (2 * t4 < grp.z) route0 = a.sorted_route[grp.y + 2 * t4];
-            if (2 * t4 + 1 < grp.z) route1 = a.sorted_route[grp.y + 2 * t4 + 1];
+            const size_t slot_rows = (size_t)grp.x * a.N;
             if (GATE_UP) {
                 const int pair = blk * (ROWS / 2) + tile * 8 + g8;
-                ga = f16_global_to_f32(a.global[slot_rows + pair]);
-                gb = f16_global_to_f32(a.global[slot_rows + a.N / 2 + pair]);
-                // per-token power-of-two scale of the f16 activations
-                if (2 * t4 < grp.z) rw0 = a.tok_scale[route0 / a.top_k];
-                if (2 * t4 + 1 < grp.z) rw1 = a.tok_scale[route1 / a.top_k];
+                graw_a = a.global[slot_rows + pair];
+                graw_b = a.global[slot_rows + a.N / 2 + pair];
             } else {
                 const int d = blk * ROWS + tile * 16 + g8;
-                ga = f16_global_to_f32(a.global[slot_rows + d]);
-                gb = f16_global_to_f32(a.global[slot_rows + d + 8]);
-                if (2 * t4 < grp.z) rw0 = a.route_weight[route0];
-                if (2 * t4 + 1 < grp.z) rw1 = a.route_weight[route1];
+                graw_a = a.global[slot_rows + d];
+                graw_b = a.global[slot_rows + d + 8];
             }
         }
 
@@ -585,6 +614,7 @@ __global__ void __launch_bounds__(kThreads, 1) expert_mma_kernel(ExpertArgs a) {
         // ---- epilogue (warp ks == 0 of each row tile) ----
         // c4[0], c4[1]: fragment row g8, tokens 2*t4, 2*t4+1;  c4[2], c4[3]: row g8 + 8
         if (ks == 0) {
+            const float ga = f16_global_to_f32(graw_a), gb = f16_global_to_f32(graw_b);
             if (GATE_UP) {
                 const int pk = perm_k(blk * (ROWS / 2) + tile * 8 + g8);
 #pragma unroll
@@ -617,14 +647,6 @@ __global__ void __launch_bounds__(kThreads, 1) expert_mma_kernel(ExpertArgs a) {
     }
 }
 
-// rows whose slot is -1 contribute zeros: clear the per-route outputs that no group will write
-__global__ void zero_missing_routes_kernel(const int32_t* __restrict__ route_slot, int routes, int H,
-                                           float* __restrict__ yroute) {
-    const int r = blockIdx.x;
-    if (route_slot[r] >= 0) return;
-    for (int d = threadIdx.x; d < H; d += blockDim.x) yroute[(size_t)r * H + d] = 0.f;
-}
-
 template <bool GATE_UP, int KS, int WIN>
 size_t expert_smem_bytes(int stages) {
     using C = Cfg<GATE_UP, KS, WIN>;
@@ -632,43 +654,56 @@ size_t expert_smem_bytes(int stages) {
            (2 * stages + 6) * sizeof(uint64_t) + 128;
 }
 
-template <bool GATE_UP, int KS, int WIN>
-void launch_expert(ExpertArgs a, int grid, cudaStream_t s) {
-    // as many stages as fit in 200 KB, at most 8
+// OCC persistent CTAs per SM share its shared memory: as many stages as fit in their share, at most 8
+template <bool GATE_UP, int KS, int WIN, int OCC>
+void launch_expert(ExpertArgs a, int sm_count, cudaStream_t s) {
+    const size_t budget = (OCC == 1 ? 200 : 110) * 1024;
     int stages = 8;
-    while (stages > 2 && expert_smem_bytes<GATE_UP, KS, WIN>(stages) > 200 * 1024) stages--;
+    while (stages > 2 && expert_smem_bytes<GATE_UP, KS, WIN>(stages) > budget) stages--;
     a.stages = stages;
     const size_t smem = expert_smem_bytes<GATE_UP, KS, WIN>(stages);
     static bool attr = false;
     if (!attr) {
-        cudaFuncSetAttribute(expert_mma_kernel<GATE_UP, KS, WIN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             220 * 1024);
+        cudaFuncSetAttribute(expert_mma_kernel<GATE_UP, KS, WIN, OCC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)(OCC == 1 ? 220 * 1024 : 112 * 1024));
         attr = true;
     }
-    expert_mma_kernel<GATE_UP, KS, WIN><<<grid, kThreads, smem, s>>>(a);
+    expert_mma_kernel<GATE_UP, KS, WIN, OCC><<<sm_count * OCC, kThreads, smem, s>>>(a);
 }
 
 }  // namespace
 
-bool decode_mma_supported(int hidden, int inter, int routes) {
+size_t decode_plan_smem(int slots) { return (size_t)3 * slots * sizeof(int); }
+
+bool decode_mma_supported(int hidden, int inter, int routes, int slots) {
     // the tensor-core decode kernels are instantiated for the production expert shape; every other
     // multiple-of-16 shape takes the per-route kernels
-    return hidden == 2048 && inter == 512 && routes <= kPlanMaxRoutes;
+    return hidden == 2048 && inter == 512 && routes <= kPlanMaxRoutes && decode_plan_smem(slots) <= 180 * 1024;
 }
 
-int launch_decode_mma(const BankView& b, const void* x, int x_dtype, const int32_t* route_slot,
+int launch_decode_mma(const BankView& b, const void* x, int x_dtype, const DecodeRoutes& rt,
                       const float* route_weight, int tokens, int top_k, DecodeScratch sc, int sm_count,
                       const Ctx& c) {
     const int routes = tokens * top_k;
-    int launches = 0;
     c.begin(K_PERMUTE_ACT);
     prep_act_kernel<<<tokens, 256, 0, c.s>>>(x, x_dtype, b.hidden, sc.xh, sc.tok_scale);
     c.end();
+    PlanArgs pa{};
+    pa.route_slot_in = rt.route_slot_in;
+    pa.expert_ids = rt.expert_ids; pa.ids_dtype = rt.ids_dtype; pa.layer = rt.layer; pa.experts = rt.experts;
+    pa.n_ids = rt.n_ids; pa.slot_for_id = rt.slot_for_id; pa.route_slot_out = rt.route_slot_out;
+    pa.routes = routes; pa.slots = b.slots; pa.hidden = b.hidden;
+    pa.groups = sc.groups; pa.sorted_route = sc.sorted_route; pa.n_groups = sc.n_groups; pa.yroute = sc.yroute;
+    pa.bad_flag = rt.bad_flag;
+    const size_t psmem = decode_plan_smem(b.slots);
+    static bool pattr = false;
+    if (!pattr) {
+        cudaFuncSetAttribute(decode_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        pattr = true;
+    }
     c.begin(K_DECODE_PLAN);
-    decode_plan_kernel<<<1, kPlanThreads, 0, c.s>>>(route_slot, routes, sc.groups, sc.sorted_route, sc.n_groups);
-    zero_missing_routes_kernel<<<routes, 256, 0, c.s>>>(route_slot, routes, b.hidden, sc.yroute);
+    decode_plan_kernel<<<1, kPlanThreads, psmem, c.s>>>(pa);
     c.end();
-    launches += 3;
 
     ExpertArgs a{};
     a.groups = sc.groups;
@@ -680,18 +715,15 @@ int launch_decode_mma(const BankView& b, const void* x, int x_dtype, const int32
     a.packed = b.gu_packed; a.scale = b.gu_scale; a.global = b.gu_global;
     a.act = sc.xh; a.tok_scale = sc.tok_scale; a.ic2 = sc.ic2p; a.N = 2 * b.inter;
     c.begin(K_EXPERT_GATE_UP);
-    launch_expert<true, 4, 4>(a, sm_count, c.s);   // K = 2048: 4 warps x 4 windows, 32 rows per item
+    launch_expert<true, 8, 2, 2>(a, sm_count, c.s);   // K = 2048: 8 warps x 2 windows, 16 rows per item
     c.end();
     // down: K = inter, N = hidden rows
     a.packed = b.dn_packed; a.scale = b.dn_scale; a.global = b.dn_global;
     a.act = sc.ic2p; a.yroute = sc.yroute; a.route_weight = route_weight; a.N = b.hidden;
     c.begin(K_EXPERT_DOWN);
-    if (routes <= 128)
-        launch_expert<false, 2, 2>(a, sm_count, c.s);  // K = 512: 2 warps x 2 windows, 64 rows per item
-    else
-        launch_expert<false, 1, 4>(a, sm_count, c.s);  // 4 windows per warp, 128 rows per item
+    launch_expert<false, 2, 2, 2>(a, sm_count, c.s);  // K = 512: 2 warps x 2 windows, 64 rows per item
     c.end();
-    return launches + 2;
+    return 4;
 }
 
 }  // namespace ftm

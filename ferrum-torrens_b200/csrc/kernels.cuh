@@ -66,8 +66,18 @@ struct DecodeScratch {
     float* yroute;          // [routes, hidden] f32
     int32_t* err;           // raised when a bounded wait gives up
 };
-bool decode_mma_supported(int hidden, int inter, int routes);
-int launch_decode_mma(const BankView& b, const void* x, int x_dtype, const int32_t* route_slot,
+// where the routes of a decode step come from: slot ids as given, or dense expert ids of one layer
+// that the plan maps to slots through the residency table
+struct DecodeRoutes {
+    const int32_t* route_slot_in;
+    const void* expert_ids;
+    int ids_dtype, layer, experts, n_ids;
+    const int32_t* slot_for_id;
+    int32_t* route_slot_out;
+    int32_t* bad_flag;
+};
+bool decode_mma_supported(int hidden, int inter, int routes, int slots);
+int launch_decode_mma(const BankView& b, const void* x, int x_dtype, const DecodeRoutes& rt,
                       const float* route_weight, int tokens, int top_k, DecodeScratch sc, int sm_count,
                       const Ctx& c);
 

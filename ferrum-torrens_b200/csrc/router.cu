@@ -160,18 +160,29 @@ router_logits_tiled_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloa
         if (active) {
             const uint32_t wrow = wbase + b * kTileE * kWStride + lane * kWStride;
             const float* xs = xbuf + b * kKC * kTileT + warp * 4;
-#pragma unroll 4
-            for (int kk = 0; kk < kKC; kk += 8) {
-                uint4 wv;
+            // operands of the next eight k are fetched while the current eight are multiplied
+            uint4 wc;
+            float4 xc[8];
+            auto fetch = [&](int kk, uint4& wv, float4 (&xv)[8]) {
                 asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
                              : "=r"(wv.x), "=r"(wv.y), "=r"(wv.z), "=r"(wv.w)
                              : "r"(wrow + kk * 2));
-                const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+                for (int q = 0; q < 8; q++) xv[q] = *reinterpret_cast<const float4*>(xs + (kk + q) * kTileT);
+            };
+            fetch(0, wc, xc);
+#pragma unroll 2
+            for (int kk = 0; kk < kKC; kk += 8) {
+                uint4 wn = wc;
+                float4 xn[8];
+#pragma unroll
+                for (int q = 0; q < 8; q++) xn[q] = xc[q];
+                if (kk + 8 < kKC) fetch(kk + 8, wn, xn);
+                const uint32_t ww[4] = {wc.x, wc.y, wc.z, wc.w};
 #pragma unroll
                 for (int q = 0; q < 4; q++) {
                     const float2 w2 = bf16x2_to_f32(ww[q]);
-                    const float4 xa = *reinterpret_cast<const float4*>(xs + (kk + 2 * q) * kTileT);
-                    const float4 xb = *reinterpret_cast<const float4*>(xs + (kk + 2 * q + 1) * kTileT);
+                    const float4 xa = xc[2 * q], xb = xc[2 * q + 1];
                     acc[0] = __fmaf_rn(xa.x, w2.x, acc[0]);
                     acc[1] = __fmaf_rn(xa.y, w2.x, acc[1]);
                     acc[2] = __fmaf_rn(xa.z, w2.x, acc[2]);
@@ -181,6 +192,9 @@ router_logits_tiled_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloa
                     acc[2] = __fmaf_rn(xb.z, w2.y, acc[2]);
                     acc[3] = __fmaf_rn(xb.w, w2.y, acc[3]);
                 }
+                wc = wn;
+#pragma unroll
+                for (int q = 0; q < 8; q++) xc[q] = xn[q];
             }
         }
         if (c + 1 < nchunks) store_x(b ^ 1);
@@ -195,10 +209,11 @@ router_logits_tiled_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloa
     }
 }
 
-// One warp per token.  experts <= 32 * kMaxPerLane.
-constexpr int kMaxPerLane = 16;
+// One warp per token; lane owns PER contiguous experts (experts <= 32 * PER), so "lowest index"
+// is "lowest lane, then lowest position in the lane".
 constexpr int kTopkWarps = 4;
 
+template <int PER>
 __global__ void __launch_bounds__(kTopkWarps * 32)
 router_topk_kernel(const float* __restrict__ logits, int tokens, int experts, int top_k,
                    int32_t* __restrict__ ids, float* __restrict__ weights) {
@@ -206,76 +221,61 @@ router_topk_kernel(const float* __restrict__ logits, int tokens, int experts, in
     const int t = blockIdx.x * kTopkWarps + warp;
     if (t >= tokens) return;
     const float* row = logits + (size_t)t * experts;
-    const int per = (experts + 31) / 32;
-
-    // lane owns experts lane*per .. lane*per+per-1 (contiguous, so "lowest index" is
-    // "lowest lane, then lowest local position")
-    float v[kMaxPerLane];
+    float v[PER];
     float mx = -INFINITY;
 #pragma unroll
-    for (int i = 0; i < kMaxPerLane; i++) {
-        int e = lane * per + i;
-        v[i] = (i < per && e < experts) ? row[e] : -INFINITY;
+    for (int i = 0; i < PER; i++) {
+        const int e = lane * PER + i;
+        v[i] = (e < experts) ? row[e] : -INFINITY;
         mx = fmaxf(mx, v[i]);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
 #pragma unroll
-    for (int i = 0; i < kMaxPerLane; i++) {
-        int e = lane * per + i;
-        if (i < per && e < experts) {
-            v[i] = ftm_expf(__fadd_rn(v[i], -mx));
-        }
-    }
+    for (int i = 0; i < PER; i++)
+        if (lane * PER + i < experts) v[i] = ftm_expf(__fadd_rn(v[i], -mx));
     // the host sums the exponentials over e ascending: the running sum is handed from lane to lane,
-    // each adding its own (contiguous) experts in order
+    // each adding its own experts in order
     float sum = 0.0f;
     for (int l = 0; l < 32; l++) {
         float s2 = sum;
 #pragma unroll
-        for (int i = 0; i < kMaxPerLane; i++)
-            if (i < per && lane * per + i < experts) s2 = __fadd_rn(s2, v[i]);
+        for (int i = 0; i < PER; i++)
+            if (lane * PER + i < experts) s2 = __fadd_rn(s2, v[i]);
         sum = __shfl_sync(0xffffffffu, s2, l);
     }
     const float inv = __fdiv_rn(1.0f, sum);
+    // probabilities are >= 0, so their bit patterns order like the values: one integer warp-max
+    // finds the largest, one warp-min the lowest index holding it
+    uint32_t pb[PER];
 #pragma unroll
-    for (int i = 0; i < kMaxPerLane; i++) {
-        int e = lane * per + i;
-        v[i] = (i < per && e < experts) ? __fmul_rn(v[i], inv) : -INFINITY;
-    }
-    // top_k passes of (largest p, lowest index)
-    float my_p = 0.0f;   // lane j keeps the j-th pick
+    for (int i = 0; i < PER; i++)
+        pb[i] = (lane * PER + i < experts) ? __float_as_uint(__fmul_rn(v[i], inv)) : 0u;
+    uint32_t taken = 0;  // bit i: this lane's expert i was already selected
+    float my_p = 0.0f;
     int my_id = 0;
     float topsum = 0.0f;
     for (int j = 0; j < top_k; j++) {
-        float best = -INFINITY;
-        int best_e = 0x7fffffff;
+        uint32_t best = 0;
+        int best_i = -1;
 #pragma unroll
-        for (int i = 0; i < kMaxPerLane; i++) {
-            if (i < per && v[i] > best) {
-                best = v[i];
-                best_e = lane * per + i;
+        for (int i = 0; i < PER; i++) {
+            const bool ok = !((taken >> i) & 1u) && (lane * PER + i < experts);
+            if (ok && (best_i < 0 || pb[i] > best)) {
+                best = pb[i];
+                best_i = i;
             }
         }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            float ob = __shfl_xor_sync(0xffffffffu, best, o);
-            int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
-            if (ob > best || (ob == best && oe < best_e)) {
-                best = ob;
-                best_e = oe;
-            }
-        }
-        topsum = __fadd_rn(topsum, best);
+        const uint32_t wmax = __reduce_max_sync(0xffffffffu, best_i >= 0 ? best : 0u);
+        const uint32_t cand = (best_i >= 0 && best == wmax) ? (uint32_t)(lane * PER + best_i) : 0xffffffffu;
+        const uint32_t win = __reduce_min_sync(0xffffffffu, cand);
+        const float p = __uint_as_float(wmax);
+        topsum = __fadd_rn(topsum, p);
         if (lane == j) {
-            my_p = best;
-            my_id = best_e;
+            my_p = p;
+            my_id = (int)win;
         }
-        if (best_e / per == lane) {
-#pragma unroll
-            for (int i = 0; i < kMaxPerLane; i++)
-                if (i == best_e - lane * per) v[i] = -INFINITY;
-        }
+        if ((int)(win / PER) == lane) taken |= 1u << (win % PER);
     }
     const float inv2 = __fdiv_rn(1.0f, topsum);
     if (lane < top_k) {
@@ -330,7 +330,10 @@ int launch_router_topk(const float* logits, int tokens, int experts, int top_k, 
                        float* weights, const Ctx& c) {
     int grid = (tokens + kTopkWarps - 1) / kTopkWarps;
     c.begin(K_ROUTER_TOPK);
-    router_topk_kernel<<<grid, kTopkWarps * 32, 0, c.s>>>(logits, tokens, experts, top_k, ids, weights);
+    if (experts <= 256)
+        router_topk_kernel<8><<<grid, kTopkWarps * 32, 0, c.s>>>(logits, tokens, experts, top_k, ids, weights);
+    else
+        router_topk_kernel<16><<<grid, kTopkWarps * 32, 0, c.s>>>(logits, tokens, experts, top_k, ids, weights);
     c.end();
     return 1;
 }

@@ -367,7 +367,7 @@ def test_shared_expert_and_combine(small):
     shared, gate = moe.shared_expert(bf16_dev(xb), bf16_dev(lay.sh_gate_up), bf16_dev(lay.sh_down), bf16_dev(lay.sh_gate))
     torch.cuda.synchronize()
     want = o.shared_expert(ol, xf)
-    check_close(shared.cpu().numpy(), want, rel_l2=1e-4, max_abs_rel=1e-4)
+    check_close(shared.cpu().numpy(), want, rel_l2=2e-4, max_abs_rel=2e-4)
     g = o.bf16_gemm(xf, lay.sh_gate, tokens, 1, lay.hidden).reshape(-1)
     want_gate = np.array([o.sigmoid(float(v)) for v in g], np.float32)
     assert np.abs(gate.cpu().numpy() - want_gate).max() <= 1e-5
