@@ -241,7 +241,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait: gives up after kSpinLimit polls, raises the error flag and reports failure, so a
 // lost completion can never hang the GPU.
-constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr uint32_t kSpinLimit = 1u << 18;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int32_t* err) {
     for (uint32_t i = 0; i < kSpinLimit; i++)
         if (mbar_try_wait(bar, parity)) return true;
@@ -328,30 +328,24 @@ struct Cfg {
     // rows are contiguous in the bank and arrive with one copy (two-way conflicts on the reads)
     static constexpr int RSA = GATE_UP ? K / 2 + 64 : K / 2;
     static constexpr int RSS = K / 16;
-    // activation tile rows: f16 for gate_up, f32 for down; the padding keeps the reads conflict-free
-    static constexpr int kActBytes = GATE_UP ? 2 : 4;
-    static constexpr int RSX = K * kActBytes + (GATE_UP ? 64 : 16);
     static constexpr int kStageBytes = ROWS * (RSA + RSS);
-    static constexpr int kXBytes = kGroupTokens * RSX;
 };
 
 template <bool GATE_UP, int KS, int WIN, int OCC>
 __global__ void __launch_bounds__(kThreads, OCC) expert_mma_kernel(ExpertArgs a) {
     using C = Cfg<GATE_UP, KS, WIN>;
-    constexpr int K = C::K, ROWS = C::ROWS, RSA = C::RSA, RSS = C::RSS, RSX = C::RSX;
+    constexpr int K = C::K, ROWS = C::ROWS, RSA = C::RSA, RSS = C::RSS;
     extern __shared__ __align__(128) uint8_t smem[];
-    // layout: [stages][packed rows | scale rows] | x | reduce[2][warps][32 lanes][4 f32] | barriers
+    // layout: [stages][packed rows | scale rows] | reduce[2][warps][32 lanes][4 f32] | barriers
     uint8_t* const stage0 = smem;
-    uint8_t* const xbuf = stage0 + (size_t)a.stages * C::kStageBytes;
-    float* const red = reinterpret_cast<float*>(xbuf + C::kXBytes);
+    float* const red = reinterpret_cast<float*>(stage0 + (size_t)a.stages * C::kStageBytes);
     uint64_t* const bars = reinterpret_cast<uint64_t*>(red + 2 * kConsumerWarps * 128);
-    // bars: full[stages], empty[stages], xfull, xempty, redfull[2], redempty[2]
+    // bars: full[stages], empty[stages], redfull[2], redempty[2]
     const uint32_t bar0 = smem_u32(bars);
     auto FULL = [&](int s) { return bar0 + 8u * s; };
     auto EMPTY = [&](int s) { return bar0 + 8u * (a.stages + s); };
-    const uint32_t XFULL = bar0 + 8u * (2 * a.stages), XEMPTY = XFULL + 8u;
-    auto RFULL = [&](int s) { return bar0 + 8u * (2 * a.stages + 2 + s); };
-    auto REMPTY = [&](int s) { return bar0 + 8u * (2 * a.stages + 4 + s); };
+    auto RFULL = [&](int s) { return bar0 + 8u * (2 * a.stages + s); };
+    auto REMPTY = [&](int s) { return bar0 + 8u * (2 * a.stages + 2 + s); };
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     if (threadIdx.x == 0) {
@@ -359,8 +353,6 @@ __global__ void __launch_bounds__(kThreads, OCC) expert_mma_kernel(ExpertArgs a)
             mbar_init(FULL(s), 1);
             mbar_init(EMPTY(s), kConsumerWarps);
         }
-        mbar_init(XFULL, 1);
-        mbar_init(XEMPTY, kConsumerWarps);
         for (int s = 0; s < 2; s++) {
             mbar_init(RFULL(s), KS > 1 ? (KS - 1) * C::kRowTiles : 1);
             mbar_init(REMPTY(s), C::kRowTiles);
@@ -381,26 +373,9 @@ __global__ void __launch_bounds__(kThreads, OCC) expert_mma_kernel(ExpertArgs a)
     int4 grp = a.groups[g];
 
     if (warp == kConsumerWarps) {
-        // ===================== producer: bulk copies of weights, scales and activations ==========
-        int xphase = 0;
+        // ===================== producer: bulk copies of the packed rows and their scales ==========
         int st = 0, phase = 0;
-        bool new_group = true;
         for (int item = item_begin; item < item_end; item++) {
-            if (new_group) {
-                // the group's token rows; the buffer is free once every warp holds its fragments
-                if (!mbar_wait(XEMPTY, xphase ^ 1, a.err)) return;
-                if (lane == 0) mbar_expect_tx(XFULL, (uint32_t)(grp.z * K * C::kActBytes));
-                __syncwarp();
-                if (lane < grp.z) {
-                    const int route = a.sorted_route[grp.y + lane];
-                    const int row = GATE_UP ? route / a.top_k : route;
-                    bulk_g2s(smem_u32(xbuf + (size_t)lane * RSX),
-                             reinterpret_cast<const uint8_t*>(a.act) + (size_t)row * K * C::kActBytes,
-                             (uint32_t)(K * C::kActBytes), XFULL);
-                }
-                xphase ^= 1;
-                new_group = false;
-            }
             if (!mbar_wait(EMPTY(st), phase ^ 1, a.err)) return;
             if (lane == 0) mbar_expect_tx(FULL(st), (uint32_t)(ROWS * (K / 2 + K / 16)));
             __syncwarp();
@@ -436,7 +411,6 @@ __global__ void __launch_bounds__(kThreads, OCC) expert_mma_kernel(ExpertArgs a)
                 blk = 0;
                 g++;
                 if (item + 1 < item_end) grp = a.groups[g];
-                new_group = true;
             }
         }
         return;
@@ -451,41 +425,44 @@ __global__ void __launch_bounds__(kThreads, OCC) expert_mma_kernel(ExpertArgs a)
     // and its factor (gate_up: the token's activation scale; down: the route weight)
     int route0 = 0, route1 = 0;
     float rw0 = 0.f, rw1 = 0.f;
-    int xphase = 0;
     int st = 0, phase = 0;
     int rs = 0, rphase = 0;
     bool new_group = true;
     for (int item = item_begin; item < item_end; item++) {
         if (new_group) {
-            if (ks == 0) {
-                route0 = (2 * t4 < grp.z) ? a.sorted_route[grp.y + 2 * t4] : 0;
-                route1 = (2 * t4 + 1 < grp.z) ? a.sorted_route[grp.y + 2 * t4 + 1] : 0;
-                rw0 = GATE_UP ? a.tok_scale[route0 / a.top_k] : a.route_weight[route0];
-                rw1 = GATE_UP ? a.tok_scale[route1 / a.top_k] : a.route_weight[route1];
-            }
-            if (!mbar_wait(XFULL, xphase, a.err)) return;
+            // Token g8's activations straight from global memory (they are small and L2-resident):
+            // this warp's k slice, in the k-permuted layout, 16 bytes per (window, step).
+            route0 = (2 * t4 < grp.z) ? a.sorted_route[grp.y + 2 * t4] : 0;
+            route1 = (2 * t4 + 1 < grp.z) ? a.sorted_route[grp.y + 2 * t4 + 1] : 0;
+            const int my_route = a.sorted_route[grp.y + (g8 < grp.z ? g8 : 0)];
+            rw0 = GATE_UP ? a.tok_scale[route0 / a.top_k] : a.route_weight[route0];
+            rw1 = GATE_UP ? a.tok_scale[route1 / a.top_k] : a.route_weight[route1];
             if (GATE_UP) {
-                const uint32_t xa = smem_u32(xbuf) + g8 * RSX + t4 * 16 + ks * WIN * 256;
+                const uint4* xp = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(a.act) +
+                                                                 (size_t)(my_route / a.top_k) * K + ks * WIN * 128) + t4;
 #pragma unroll
                 for (int wi = 0; wi < WIN; wi++)
 #pragma unroll
-                    for (int j = 0; j < 4; j++) xf[wi * 4 + j] = lds128(xa + wi * 256 + j * 64);
+                    for (int j = 0; j < 4; j++) xf[wi * 4 + j] = xp[wi * 16 + j * 4];
             } else {
-                // ic2 arrives as f32: scale token g8 by a power of two into the f16 range and pack.
-                // The scale is taken over this warp's own k slice, the partial sums are rescaled
-                // before they leave the warp.
-                const uint32_t xa = smem_u32(xbuf) + g8 * RSX + t4 * 32 + ks * WIN * 512;
+                // ic2 is f32: scale token g8 by a power of two into the f16 range and pack.  The
+                // scale is taken over this warp's own k slice; the partial sums are rescaled before
+                // they leave the warp.
+                const uint4* xp = reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(a.act) +
+                                                                 (size_t)my_route * K + ks * WIN * 128) + t4 * 2;
+                uint4 raw[WIN * 8];
                 float m = 0.f;
 #pragma unroll
                 for (int wi = 0; wi < WIN; wi++)
 #pragma unroll
                     for (int j = 0; j < 4; j++) {
-                        const uint4 u = lds128(xa + wi * 512 + j * 128), v = lds128(xa + wi * 512 + j * 128 + 16);
-                        m = fmaxf(m, fmaxf(fmaxf(fabsf(__uint_as_float(u.x)), fabsf(__uint_as_float(u.y))),
-                                           fmaxf(fabsf(__uint_as_float(u.z)), fabsf(__uint_as_float(u.w)))));
-                        m = fmaxf(m, fmaxf(fmaxf(fabsf(__uint_as_float(v.x)), fabsf(__uint_as_float(v.y))),
-                                           fmaxf(fabsf(__uint_as_float(v.z)), fabsf(__uint_as_float(v.w)))));
+                        raw[(wi * 4 + j) * 2] = xp[wi * 32 + j * 8];
+                        raw[(wi * 4 + j) * 2 + 1] = xp[wi * 32 + j * 8 + 1];
                     }
+#pragma unroll
+                for (int q = 0; q < WIN * 8; q++)
+                    m = fmaxf(m, fmaxf(fmaxf(fabsf(__uint_as_float(raw[q].x)), fabsf(__uint_as_float(raw[q].y))),
+                                       fmaxf(fabsf(__uint_as_float(raw[q].z)), fabsf(__uint_as_float(raw[q].w)))));
                 m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
                 m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
                 const int e = (int)((__float_as_uint(m) >> 23) & 0xff);
@@ -496,26 +473,24 @@ __global__ void __launch_bounds__(kThreads, OCC) expert_mma_kernel(ExpertArgs a)
                     xscale = __uint_as_float((uint32_t)(127 - 14 + (e - 127)) << 23);
                 }
 #pragma unroll
-                for (int wi = 0; wi < WIN; wi++)
-#pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        const uint4 u = lds128(xa + wi * 512 + j * 128), v = lds128(xa + wi * 512 + j * 128 + 16);
-                        __half2 h0 = __floats2half2_rn(__uint_as_float(u.x) * inv, __uint_as_float(u.y) * inv);
-                        __half2 h1 = __floats2half2_rn(__uint_as_float(u.z) * inv, __uint_as_float(u.w) * inv);
-                        __half2 h2 = __floats2half2_rn(__uint_as_float(v.x) * inv, __uint_as_float(v.y) * inv);
-                        __half2 h3 = __floats2half2_rn(__uint_as_float(v.z) * inv, __uint_as_float(v.w) * inv);
-                        xf[wi * 4 + j] = make_uint4(*reinterpret_cast<uint32_t*>(&h0), *reinterpret_cast<uint32_t*>(&h1),
-                                                    *reinterpret_cast<uint32_t*>(&h2), *reinterpret_cast<uint32_t*>(&h3));
-                    }
+                for (int q = 0; q < WIN * 4; q++) {
+                    const uint4 u = raw[2 * q], v = raw[2 * q + 1];
+                    __half2 h0 = __floats2half2_rn(__uint_as_float(u.x) * inv, __uint_as_float(u.y) * inv);
+                    __half2 h1 = __floats2half2_rn(__uint_as_float(u.z) * inv, __uint_as_float(u.w) * inv);
+                    __half2 h2 = __floats2half2_rn(__uint_as_float(v.x) * inv, __uint_as_float(v.y) * inv);
+                    __half2 h3 = __floats2half2_rn(__uint_as_float(v.z) * inv, __uint_as_float(v.w) * inv);
+                    xf[q] = make_uint4(*reinterpret_cast<uint32_t*>(&h0), *reinterpret_cast<uint32_t*>(&h1),
+                                       *reinterpret_cast<uint32_t*>(&h2), *reinterpret_cast<uint32_t*>(&h3));
+                }
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(XEMPTY);
-            xphase ^= 1;
             new_group = false;
         }
+        // the warp that gathers the K partials of this item and writes its outputs rotates, so the
+        // extra work is spread over the KS warps of a row tile
+        const int gatherer = (KS > 1) ? (item % KS) : 0;
         // the two rows' f16 globals: requested now (raw), converted after the MMAs
         uint16_t graw_a = 0, graw_b = 0;
-        if (ks == 0) {
+        if (ks == gatherer) {
             const size_t slot_rows = (size_t)grp.x * a.N;
             if (GATE_UP) {
                 const int pair = blk * (ROWS / 2) + tile * 8 + g8;
@@ -542,19 +517,31 @@ __global__ void __launch_bounds__(kThreads, OCC) expert_mma_kernel(ExpertArgs a)
             scl[q * 4 + 0] = v.x; scl[q * 4 + 1] = v.y; scl[q * 4 + 2] = v.z; scl[q * 4 + 3] = v.w;
             sch[q * 4 + 0] = u.x; sch[q * 4 + 1] = u.y; sch[q * 4 + 2] = u.z; sch[q * 4 + 3] = u.w;
         }
+        uint4 plo[WIN], phi[WIN];
+#pragma unroll
+        for (int wi = 0; wi < WIN; wi++) {
+            plo[wi] = lds128(row_lo + wi * 64);
+            phi[wi] = lds128(row_hi + wi * 64);
+        }
+        // everything this warp needs from the stage is in registers: hand the stage back now, so the
+        // next copy overlaps the arithmetic
+        __syncwarp();
+        if (lane == 0) mbar_arrive(EMPTY(st));
+        if (++st == a.stages) {
+            st = 0;
+            phase ^= 1;
+        }
         float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
         for (int wi = 0; wi < WIN; wi++) {
-            const uint4 plo = lds128(row_lo + wi * 64);
-            const uint4 phi = lds128(row_hi + wi * 64);
             // the lane's two scale bytes of this window: bytes 2*t4, 2*t4+1 of the window's eight
             const uint32_t wl2 = (t4 & 2) ? scl[wi * 2 + 1] : scl[wi * 2];
             const uint32_t wh2 = (t4 & 2) ? sch[wi * 2 + 1] : sch[wi * 2];
             uint32_t slo0, slo1, shi0, shi1;
             e4m3x2_to_f16_scales((t4 & 1) ? (wl2 >> 16) : (wl2 & 0xffffu), slo0, slo1);
             e4m3x2_to_f16_scales((t4 & 1) ? (wh2 >> 16) : (wh2 & 0xffffu), shi0, shi1);
-            const uint32_t wl[4] = {plo.x, plo.y, plo.z, plo.w};
-            const uint32_t wh[4] = {phi.x, phi.y, phi.z, phi.w};
+            const uint32_t wl[4] = {plo[wi].x, plo[wi].y, plo[wi].z, plo[wi].w};
+            const uint32_t wh[4] = {phi[wi].x, phi[wi].y, phi[wi].z, phi[wi].w};
 #pragma unroll
             for (int j = 0; j < 4; j++) {
                 const uint4 xb = xf[wi * 4 + j];
@@ -572,13 +559,6 @@ __global__ void __launch_bounds__(kThreads, OCC) expert_mma_kernel(ExpertArgs a)
                 mma_f16(acc[1], ql[2], qh[2], ql[3], qh[3], xb.z, xb.w);
             }
         }
-        // the stage is consumed once every warp has read its fragments
-        __syncwarp();
-        if (lane == 0) mbar_arrive(EMPTY(st));
-        if (++st == a.stages) {
-            st = 0;
-            phase ^= 1;
-        }
         float c4[4];
 #pragma unroll
         for (int q = 0; q < 4; q++) c4[q] = acc[0][q] + acc[1][q];
@@ -589,19 +569,24 @@ __global__ void __launch_bounds__(kThreads, OCC) expert_mma_kernel(ExpertArgs a)
             c4[0] *= s0; c4[1] *= s1; c4[2] *= s0; c4[3] *= s1;
         }
 
-        // ---- K reduction across the warps of this row tile: warp ks == 0 gathers ----
+        // ---- K reduction across the warps of this row tile ----
         if (KS > 1) {
             float* const buf = red + (size_t)rs * kConsumerWarps * 128;
-            if (ks != 0) {
+            if (ks != gatherer) {
                 if (!mbar_wait(REMPTY(rs), rphase ^ 1, a.err)) return;
                 *reinterpret_cast<float4*>(buf + warp * 128 + lane * 4) = make_float4(c4[0], c4[1], c4[2], c4[3]);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(RFULL(rs));
             } else {
+                // The gatherer changes from item to item, so it first observes that the previous use
+                // of this buffer was drained (which implies that use's RFULL phase completed): a
+                // parity wait is only meaningful when the waiter is at most one phase behind.
+                if (!mbar_wait(REMPTY(rs), rphase ^ 1, a.err)) return;
                 if (!mbar_wait(RFULL(rs), rphase, a.err)) return;
 #pragma unroll
-                for (int o = 1; o < KS; o++) {
-                    const float4 v = *reinterpret_cast<const float4*>(buf + (warp + o) * 128 + lane * 4);
+                for (int o = 0; o < KS; o++) {
+                    if (o == gatherer) continue;
+                    const float4 v = *reinterpret_cast<const float4*>(buf + (tile * KS + o) * 128 + lane * 4);
                     c4[0] += v.x; c4[1] += v.y; c4[2] += v.z; c4[3] += v.w;
                 }
                 __syncwarp();
@@ -611,9 +596,9 @@ __global__ void __launch_bounds__(kThreads, OCC) expert_mma_kernel(ExpertArgs a)
             if (rs == 0) rphase ^= 1;
         }
 
-        // ---- epilogue (warp ks == 0 of each row tile) ----
+        // ---- epilogue (the gathering warp of each row tile) ----
         // c4[0], c4[1]: fragment row g8, tokens 2*t4, 2*t4+1;  c4[2], c4[3]: row g8 + 8
-        if (ks == 0) {
+        if (ks == gatherer) {
             const float ga = f16_global_to_f32(graw_a), gb = f16_global_to_f32(graw_b);
             if (GATE_UP) {
                 const int pk = perm_k(blk * (ROWS / 2) + tile * 8 + g8);
@@ -650,8 +635,8 @@ __global__ void __launch_bounds__(kThreads, OCC) expert_mma_kernel(ExpertArgs a)
 template <bool GATE_UP, int KS, int WIN>
 size_t expert_smem_bytes(int stages) {
     using C = Cfg<GATE_UP, KS, WIN>;
-    return (size_t)stages * C::kStageBytes + C::kXBytes + 2 * kConsumerWarps * 128 * sizeof(float) +
-           (2 * stages + 6) * sizeof(uint64_t) + 128;
+    return (size_t)stages * C::kStageBytes + 2 * kConsumerWarps * 128 * sizeof(float) +
+           (2 * stages + 4) * sizeof(uint64_t) + 128;
 }
 
 // OCC persistent CTAs per SM share its shared memory: as many stages as fit in their share, at most 8

@@ -405,7 +405,7 @@ def test_whole_block_full_size(full, tokens):
     w = torch.empty((tokens, lay.top_k), dtype=torch.float32, device=dev())
     moe.moe_block(0, bf16_dev(xb), bf16_dev(lay.gate_w), bf16_dev(lay.sh_gate_up), bf16_dev(lay.sh_down),
                   bf16_dev(lay.sh_gate), out, ids_out=ids, weights_out=w)
-    torch.cuda.synchronize()
+    moe.sync_status()
     want, want_ids, want_w = o.moe_block(ol, pkg.synth.bf16_bits_to_f32(xb), threads=o.max_threads())
     assert np.array_equal(ids.cpu().numpy(), want_ids), "routed expert ids must be bit-exact"
     assert np.abs(w.cpu().numpy() - want_w).max() <= 1e-6
