@@ -221,8 +221,10 @@ int run_routed(ftm_handle* h, const void* x, int x_dtype, const void* expert_ids
                void* out, int out_dtype, int path, cudaStream_t s) {
     BankView b = bank_view(h);
     const int routes = tokens * h->cfg.top_k;
-    if (path != FTM_PATH_SCALAR && decode_mma_supported(h->cfg.hidden, h->cfg.inter, routes, h->cfg.slots)) {
-        DecodeScratch sc{h->xh, h->tok_scale, h->ic2p, h->groups, h->sorted_route, h->n_groups, h->yroute, h->flags + 2};
+    if (path != FTM_PATH_SCALAR &&
+        decode_mma_supported(h->cfg.hidden, h->cfg.inter, routes, h->cfg.slots, h->cfg.experts, expert_ids != nullptr)) {
+        DecodeScratch sc{h->ic2p, h->groups, h->sorted_route, h->n_groups, h->yroute, h->flags + 2,
+                         h->route_expert, h->seg, h->csr_scratch, h->flags + 3};
         DecodeRoutes rt{expert_ids ? nullptr : h->route_slot, expert_ids, ids_dtype, layer, h->cfg.experts,
                         (int)h->slot_for_id.size(), h->d_slot_for_id, h->route_slot, h->flags + 1};
         h->launches += launch_decode_mma(b, x, x_dtype, rt, weights, tokens, h->cfg.top_k, sc, h->sm_count, h->ctx(s));

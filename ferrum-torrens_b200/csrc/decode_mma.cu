@@ -20,6 +20,8 @@
 //             down pass); down fuses global scale and route weight and writes one f32 row per route.
 //
 // The weights stay in the reference's bank layout (row-major packed nibbles, low nibble = even k).
+#include <cstdlib>
+
 #include "kernels.cuh"
 
 namespace ftm {
@@ -38,41 +40,6 @@ __host__ __device__ __forceinline__ int perm_k(int k) {
     const int w = k & ~127, r = k & 127;
     const int t = r >> 5, j = (r >> 3) & 3, n = r & 7;
     return w + 8 * (4 * j + t) + n;
-}
-
-// Activations -> f16, k-permuted, each token scaled by a power of two so that its largest
-// magnitude lands in [2^14, 2^15): the tensor-core operands are f16 (the E2M1 -> f16 conversion is a
-// hardware instruction), and the per-token scale keeps any bf16/f32 input inside the f16 range
-// without losing bits (bf16 carries 8 significant bits, f16 11).  tok_scale[t] undoes it.
-__global__ void __launch_bounds__(256)
-prep_act_kernel(const void* __restrict__ x, int dtype, int K, __half* __restrict__ xh, float* __restrict__ tok_scale) {
-    __shared__ float wmax[8];
-    __shared__ float s_inv;
-    const int t = blockIdx.x;
-    const size_t base = (size_t)t * K;
-    float m = 0.f;
-    for (int k = threadIdx.x; k < K; k += 256) m = fmaxf(m, fabsf(load_act(x, dtype, base + k)));
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    if ((threadIdx.x & 31) == 0) wmax[threadIdx.x >> 5] = m;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        float mm = 0.f;
-        for (int w = 0; w < 8; w++) mm = fmaxf(mm, wmax[w]);
-        // 2^(14 - floor(log2 mm)) by exponent arithmetic; zero, subnormal or non-finite rows keep scale 1
-        const int e = (int)((__float_as_uint(mm) >> 23) & 0xff);
-        float inv = 1.0f, sc = 1.0f;
-        if (e > 0 && e < 255) {
-            inv = __uint_as_float((uint32_t)(127 + 14 - (e - 127)) << 23);
-            sc = __uint_as_float((uint32_t)(127 - 14 + (e - 127)) << 23);
-        }
-        s_inv = inv;
-        tok_scale[t] = sc;
-    }
-    __syncthreads();
-    const float inv = s_inv;
-    for (int k = threadIdx.x; k < K; k += 256)
-        xh[base + perm_k(k)] = __float2half_rn(load_act(x, dtype, base + k) * inv);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -225,9 +192,6 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
@@ -295,402 +259,470 @@ __device__ __forceinline__ void e4m3x2_to_f16_scales(uint32_t two, uint32_t& s0,
 
 // ------------------------------------------------------------------------------------------
 // the expert kernel
+//
+// Every warp is an independent worker: a warp item is one 16-row MMA tile over the full K, for one
+// group (<= 8 tokens).  The warp streams its own packed rows and scales through a private
+// double-buffered ring with bulk async copies that it issues itself (one mbarrier per buffer, the
+// TMA engine signals the bytes), so there is no producer warp, no cross-warp reduction and no
+// per-item handshake between warps.  The warps of a CTA share only the group's activation tile:
+// when the CTA's contiguous item range crosses into a new group, warp t converts token t's row
+// (power-of-two scale into the f16 range, k-permuted) into shared memory between two CTA barriers.
 // ------------------------------------------------------------------------------------------
-constexpr int kConsumerWarps = 8;
-constexpr int kThreads = (kConsumerWarps + 1) * 32;
 constexpr int kGroupTokens = 8;
 
 struct ExpertArgs {
-    const uint8_t* packed;    // bank base [slots, N, K/2]
-    const uint8_t* scale;     // [slots, N, K/16]
-    const uint16_t* global;   // [slots, N]
-    const void* act;          // k-permuted activations: gate_up f16 [tokens, K], down f32 [routes, K]
-    const float* tok_scale;   // gate_up: per-token power-of-two scale of act
+    const uint8_t* packed;      // bank base [slots, N, K/2]
+    const uint8_t* scale;       // [slots, N, K/16]
+    const uint16_t* global;     // [slots, N]
+    const void* act;            // gate_up: the layer input [tokens, K] (bf16 or f32); down: ic2 f32 [routes, K]
+    int act_dtype;
     const int4* groups;
     const int32_t* sorted_route;
     const int32_t* n_groups;
     const float* route_weight;  // down only
-    float* ic2;                 // gate_up out: [routes, inter] f32, k-permuted
+    float* ic2;                 // gate_up out: [routes, inter] f32
     float* yroute;              // down out: [routes, hidden] f32, weighted
     int32_t* err;
-    int N, top_k, stages;
+    int N, top_k;
+    int debug;  // diagnostics: 1 = skip the arithmetic (copy pipeline only), 2 = every group reads slot 0
 };
 
-// GATE_UP: K = hidden, an item is ROWS/2 gate rows and the matching ROWS/2 up rows, so that the
-// silu(gate) * up epilogue stays inside one thread.  Otherwise K = inter and an item is ROWS rows.
-// KS warps split K for one 16-row tile; WIN = K / 128 / KS windows of 128 k per warp.
-template <bool GATE_UP, int KS, int WIN>
+// GATE_UP: K = hidden, a warp item is 8 gate rows and the 8 matching up rows, so that the
+// silu(gate) * up epilogue stays inside one thread; K is streamed in SUB pieces.  Otherwise
+// K = inter and a warp item is 16 consecutive rows in one piece.
+template <bool GATE_UP, int K_, int NT_>
 struct Cfg {
-    static constexpr int K = 128 * KS * WIN;
-    static constexpr int kRowTiles = kConsumerWarps / KS;
-    static constexpr int ROWS = 16 * kRowTiles;
+    static constexpr int K = K_;
+    static constexpr int NT = NT_;                       // token tiles of 8 per group
+    static constexpr int kWarps = GATE_UP ? 8 : 16;      // independent workers per CTA
+    static constexpr int kThreads = kWarps * 32;
+    static constexpr int SUB = GATE_UP ? (NT == 1 ? 2 : 4) : 1;  // pieces of K per item
+    static constexpr int D = 2;            // ring depth: pieces in flight per warp
+    static constexpr int KSUB = K / SUB;
+    static constexpr int WIN = KSUB / 128;               // 128-k windows per piece
     // gate_up rows are copied one by one with 64 B of padding (conflict-free 128-bit reads); down
     // rows are contiguous in the bank and arrive with one copy (two-way conflicts on the reads)
-    static constexpr int RSA = GATE_UP ? K / 2 + 64 : K / 2;
-    static constexpr int RSS = K / 16;
-    static constexpr int kStageBytes = ROWS * (RSA + RSS);
+    static constexpr int RSA = GATE_UP ? KSUB / 2 + 64 : KSUB / 2;
+    static constexpr int RSS = K / 16;                   // scale row: the whole K
+    static constexpr int kStageBytes = 16 * RSA;
+    static constexpr int kScaleBytes = 16 * RSS;
+    // scales travel with an item's first piece; an item's scales must outlive all its pieces
+    static constexpr int NSB = (D + SUB - 2) / SUB + 1;
+    static constexpr int kWarpBytes = D * kStageBytes + NSB * kScaleBytes;
+    static constexpr int RSX = K * 2 + 64;               // f16 activation row, padded
+    static constexpr int kXBytes = kGroupTokens * NT * RSX;
+    static constexpr size_t kSmem = (size_t)kWarps * kWarpBytes + kXBytes + 96 * NT + 8 * kWarps * D + 32;
 };
 
-template <bool GATE_UP, int KS, int WIN, int OCC>
-__global__ void __launch_bounds__(kThreads, OCC) expert_mma_kernel(ExpertArgs a) {
-    using C = Cfg<GATE_UP, KS, WIN>;
-    constexpr int K = C::K, ROWS = C::ROWS, RSA = C::RSA, RSS = C::RSS;
-    extern __shared__ __align__(128) uint8_t smem[];
-    // layout: [stages][packed rows | scale rows] | reduce[2][warps][32 lanes][4 f32] | barriers
-    uint8_t* const stage0 = smem;
-    float* const red = reinterpret_cast<float*>(stage0 + (size_t)a.stages * C::kStageBytes);
-    uint64_t* const bars = reinterpret_cast<uint64_t*>(red + 2 * kConsumerWarps * 128);
-    // bars: full[stages], empty[stages], redfull[2], redempty[2]
-    const uint32_t bar0 = smem_u32(bars);
-    auto FULL = [&](int s) { return bar0 + 8u * s; };
-    auto EMPTY = [&](int s) { return bar0 + 8u * (a.stages + s); };
-    auto RFULL = [&](int s) { return bar0 + 8u * (2 * a.stages + s); };
-    auto REMPTY = [&](int s) { return bar0 + 8u * (2 * a.stages + 2 + s); };
+// the items of one warp inside its CTA's contiguous range [ib, ie): within every group segment the
+// warp takes items first + w, first + w + 8, ...
+struct ItemIter {
+    int g, it, ie, blocks, w, nw;
+    __device__ __forceinline__ void start(int ib, int ie_, int blocks_, int w_, int nw_) {
+        ie = ie_; blocks = blocks_; w = w_; nw = nw_;
+        g = ib / blocks;
+        it = ib + w;
+        settle(ib);
+    }
+    // moves to the next group segment until `it` lies inside [segment begin, segment end)
+    __device__ __forceinline__ void settle(int ib) {
+        while (g * blocks < ie && it >= min(ie, (g + 1) * blocks)) {
+            g++;
+            it = max(ib, g * blocks) + w;
+        }
+    }
+    __device__ __forceinline__ bool valid() const { return g * blocks < ie && it < ie; }
+    __device__ __forceinline__ void next(int ib) {
+        it += nw;
+        settle(ib);
+    }
+};
 
+template <bool GATE_UP, int K_, int NT, int OCC>
+__global__ void __launch_bounds__(Cfg<GATE_UP, K_, NT>::kThreads, OCC) expert_mma_kernel(ExpertArgs a) {
+    using C = Cfg<GATE_UP, K_, NT>;
+    constexpr int kWarps = C::kWarps;
+    constexpr int kTok = kGroupTokens * NT;  // tokens per group
+    constexpr int K = C::K, SUB = C::SUB, D = C::D, NSB = C::NSB, KSUB = C::KSUB, WIN = C::WIN, RSA = C::RSA, RSS = C::RSS,
+                  RSX = C::RSX;
+    extern __shared__ __align__(128) uint8_t smem[];
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < a.stages; s++) {
-            mbar_init(FULL(s), 1);
-            mbar_init(EMPTY(s), kConsumerWarps);
-        }
-        for (int s = 0; s < 2; s++) {
-            mbar_init(RFULL(s), KS > 1 ? (KS - 1) * C::kRowTiles : 1);
-            mbar_init(REMPTY(s), C::kRowTiles);
-        }
+    const int g8 = lane >> 2, t4 = lane & 3;
+    uint8_t* const wbase = smem + (size_t)warp * C::kWarpBytes;   // [2 stages | 2 scale buffers]
+    uint8_t* const xtile = smem + (size_t)kWarps * C::kWarpBytes;
+    float* const s_xscale = reinterpret_cast<float*>(xtile + C::kXBytes);  // [kTok] token scales
+    float* const s_factor = s_xscale + kTok;                               // [kTok] route weights (down)
+    int* const s_route = reinterpret_cast<int*>(s_factor + kTok);          // [kTok] routes of the group
+    uint64_t* const bars = reinterpret_cast<uint64_t*>(s_route + kTok);    // [kWarps][D]
+    const uint32_t full0 = smem_u32(bars) + 8u * D * warp;
+    if (lane == 0) {
+        for (int q = 0; q < D; q++) mbar_init(full0 + 8u * q, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
 
     // contiguous item range of this CTA: item = group * blocks + block
     const int n_groups = *a.n_groups;
-    constexpr int kOutRows = GATE_UP ? ROWS / 2 : ROWS;  // output rows per item (pairs for gate_up)
-    const int blocks = (GATE_UP ? a.N / 2 : a.N) / kOutRows;
+    const int blocks = (GATE_UP ? a.N / 2 : a.N) / (GATE_UP ? 8 : 16);
     const long long total = (long long)n_groups * blocks;
-    const int item_begin = (int)(total * blockIdx.x / gridDim.x);
-    const int item_end = (int)(total * (blockIdx.x + 1) / gridDim.x);
-    if (item_begin >= item_end) return;
-    int g = item_begin / blocks, blk = item_begin % blocks;
-    int4 grp = a.groups[g];
+    const int ib = (int)(total * blockIdx.x / gridDim.x);
+    const int ie = (int)(total * (blockIdx.x + 1) / gridDim.x);
+    if (ib >= ie) return;
 
-    if (warp == kConsumerWarps) {
-        // ===================== producer: bulk copies of the packed rows and their scales ==========
-        int st = 0, phase = 0;
-        for (int item = item_begin; item < item_end; item++) {
-            if (!mbar_wait(EMPTY(st), phase ^ 1, a.err)) return;
-            if (lane == 0) mbar_expect_tx(FULL(st), (uint32_t)(ROWS * (K / 2 + K / 16)));
-            __syncwarp();
-            uint8_t* const sp = stage0 + (size_t)st * C::kStageBytes;
-            const size_t slot_rows = (size_t)grp.x * a.N;
-            if (GATE_UP) {
-                // stage row r = tile * 16 + m: m < 8 gate row, m >= 8 the matching up row
-                for (int r = lane; r < ROWS; r += 32) {
-                    const int tile = r / 16, m = r % 16;
-                    const int pair = blk * (ROWS / 2) + tile * 8 + (m & 7);
-                    const int n = (m < 8) ? pair : a.N / 2 + pair;
-                    bulk_g2s(smem_u32(sp + (size_t)r * RSA), a.packed + (slot_rows + n) * (size_t)(K / 2),
-                             (uint32_t)(K / 2), FULL(st));
-                }
-                // scales: eight consecutive rows per copy
-                for (int c8 = lane; c8 < ROWS / 8; c8 += 32) {
-                    const int tile = c8 / 2, up = c8 & 1;
-                    const int n = (up ? a.N / 2 : 0) + blk * (ROWS / 2) + tile * 8;
-                    bulk_g2s(smem_u32(sp + (size_t)ROWS * RSA + (size_t)c8 * 8 * RSS),
-                             a.scale + (slot_rows + n) * (size_t)(K / 16), (uint32_t)(8 * K / 16), FULL(st));
-                }
-            } else if (lane == 0) {
-                const size_t n = slot_rows + (size_t)blk * ROWS;
-                bulk_g2s(smem_u32(sp), a.packed + n * (size_t)(K / 2), (uint32_t)(ROWS * (K / 2)), FULL(st));
-                bulk_g2s(smem_u32(sp + (size_t)ROWS * RSA), a.scale + n * (size_t)(K / 16), (uint32_t)(ROWS * (K / 16)),
-                         FULL(st));
-            }
-            if (++st == a.stages) {
-                st = 0;
-                phase ^= 1;
-            }
-            if (++blk == blocks) {
-                blk = 0;
-                g++;
-                if (item + 1 < item_end) grp = a.groups[g];
-            }
-        }
-        return;
-    }
-
-    // ===================== consumers ==========================================================
-    const int tile = warp / KS, ks = warp % KS;     // row tile of the item, K split index
-    const int g8 = lane >> 2, t4 = lane & 3;        // fragment row group and k lane
-    uint4 xf[WIN * 4];                              // this warp's B fragments of the current group
-    float xscale = 1.0f;                            // down: this lane's token (g8) scale
-    // per group, for the two token columns (2*t4, 2*t4+1) this lane's accumulators hold: the route
-    // and its factor (gate_up: the token's activation scale; down: the route weight)
-    int route0 = 0, route1 = 0;
-    float rw0 = 0.f, rw1 = 0.f;
-    int st = 0, phase = 0;
-    int rs = 0, rphase = 0;
-    bool new_group = true;
-    for (int item = item_begin; item < item_end; item++) {
-        if (new_group) {
-            // Token g8's activations straight from global memory (they are small and L2-resident):
-            // this warp's k slice, in the k-permuted layout, 16 bytes per (window, step).
-            route0 = (2 * t4 < grp.z) ? a.sorted_route[grp.y + 2 * t4] : 0;
-            route1 = (2 * t4 + 1 < grp.z) ? a.sorted_route[grp.y + 2 * t4 + 1] : 0;
-            const int my_route = a.sorted_route[grp.y + (g8 < grp.z ? g8 : 0)];
-            rw0 = GATE_UP ? a.tok_scale[route0 / a.top_k] : a.route_weight[route0];
-            rw1 = GATE_UP ? a.tok_scale[route1 / a.top_k] : a.route_weight[route1];
-            if (GATE_UP) {
-                const uint4* xp = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(a.act) +
-                                                                 (size_t)(my_route / a.top_k) * K + ks * WIN * 128) + t4;
-#pragma unroll
-                for (int wi = 0; wi < WIN; wi++)
-#pragma unroll
-                    for (int j = 0; j < 4; j++) xf[wi * 4 + j] = xp[wi * 16 + j * 4];
-            } else {
-                // ic2 is f32: scale token g8 by a power of two into the f16 range and pack.  The
-                // scale is taken over this warp's own k slice; the partial sums are rescaled before
-                // they leave the warp.
-                const uint4* xp = reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(a.act) +
-                                                                 (size_t)my_route * K + ks * WIN * 128) + t4 * 2;
-                uint4 raw[WIN * 8];
-                float m = 0.f;
-#pragma unroll
-                for (int wi = 0; wi < WIN; wi++)
-#pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        raw[(wi * 4 + j) * 2] = xp[wi * 32 + j * 8];
-                        raw[(wi * 4 + j) * 2 + 1] = xp[wi * 32 + j * 8 + 1];
-                    }
-#pragma unroll
-                for (int q = 0; q < WIN * 8; q++)
-                    m = fmaxf(m, fmaxf(fmaxf(fabsf(__uint_as_float(raw[q].x)), fabsf(__uint_as_float(raw[q].y))),
-                                       fmaxf(fabsf(__uint_as_float(raw[q].z)), fabsf(__uint_as_float(raw[q].w)))));
-                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
-                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
-                const int e = (int)((__float_as_uint(m) >> 23) & 0xff);
-                float inv = 1.0f;
-                xscale = 1.0f;
-                if (e > 0 && e < 255) {
-                    inv = __uint_as_float((uint32_t)(127 + 14 - (e - 127)) << 23);
-                    xscale = __uint_as_float((uint32_t)(127 - 14 + (e - 127)) << 23);
-                }
-#pragma unroll
-                for (int q = 0; q < WIN * 4; q++) {
-                    const uint4 u = raw[2 * q], v = raw[2 * q + 1];
-                    __half2 h0 = __floats2half2_rn(__uint_as_float(u.x) * inv, __uint_as_float(u.y) * inv);
-                    __half2 h1 = __floats2half2_rn(__uint_as_float(u.z) * inv, __uint_as_float(u.w) * inv);
-                    __half2 h2 = __floats2half2_rn(__uint_as_float(v.x) * inv, __uint_as_float(v.y) * inv);
-                    __half2 h3 = __floats2half2_rn(__uint_as_float(v.z) * inv, __uint_as_float(v.w) * inv);
-                    xf[q] = make_uint4(*reinterpret_cast<uint32_t*>(&h0), *reinterpret_cast<uint32_t*>(&h1),
-                                       *reinterpret_cast<uint32_t*>(&h2), *reinterpret_cast<uint32_t*>(&h3));
-                }
-            }
-            new_group = false;
-        }
-        // the warp that gathers the K partials of this item and writes its outputs rotates, so the
-        // extra work is spread over the KS warps of a row tile
-        const int gatherer = (KS > 1) ? (item % KS) : 0;
-        // the two rows' f16 globals: requested now (raw), converted after the MMAs
-        uint16_t graw_a = 0, graw_b = 0;
-        if (ks == gatherer) {
-            const size_t slot_rows = (size_t)grp.x * a.N;
-            if (GATE_UP) {
-                const int pair = blk * (ROWS / 2) + tile * 8 + g8;
-                graw_a = a.global[slot_rows + pair];
-                graw_b = a.global[slot_rows + a.N / 2 + pair];
-            } else {
-                const int d = blk * ROWS + tile * 16 + g8;
-                graw_a = a.global[slot_rows + d];
-                graw_b = a.global[slot_rows + d + 8];
-            }
-        }
-
-        if (!mbar_wait(FULL(st), phase, a.err)) return;
-        const uint32_t sp = smem_u32(stage0 + (size_t)st * C::kStageBytes);
-        const uint32_t row_lo = sp + (tile * 16 + g8) * RSA + t4 * 16 + ks * WIN * 64;
-        const uint32_t row_hi = row_lo + 8 * RSA;
-        // this warp's scale bytes of the two rows: WIN * 8 consecutive bytes each
-        const uint32_t sc_lo = sp + ROWS * RSA + (tile * 16 + g8) * RSS + ks * WIN * 8;
-        const uint32_t sc_hi = sc_lo + 8 * RSS;
-        uint32_t scl[WIN * 2], sch[WIN * 2];
-#pragma unroll
-        for (int q = 0; q < WIN / 2; q++) {
-            const uint4 v = lds128(sc_lo + q * 16), u = lds128(sc_hi + q * 16);
-            scl[q * 4 + 0] = v.x; scl[q * 4 + 1] = v.y; scl[q * 4 + 2] = v.z; scl[q * 4 + 3] = v.w;
-            sch[q * 4 + 0] = u.x; sch[q * 4 + 1] = u.y; sch[q * 4 + 2] = u.z; sch[q * 4 + 3] = u.w;
-        }
-        uint4 plo[WIN], phi[WIN];
-#pragma unroll
-        for (int wi = 0; wi < WIN; wi++) {
-            plo[wi] = lds128(row_lo + wi * 64);
-            phi[wi] = lds128(row_hi + wi * 64);
-        }
-        // everything this warp needs from the stage is in registers: hand the stage back now, so the
-        // next copy overlaps the arithmetic
+    // ---- copy issue: piece `half` of item `it` (group descriptor `grp`) into ring position n % D ----
+    auto issue = [&](const int4 grp, int it, int half, int n) {
+        const int blk = it % blocks;
+        const size_t slot_rows = (a.debug == 2) ? 0 : (size_t)grp.x * a.N;
+        const uint32_t bar = full0 + 8u * (n % D);
+        uint8_t* const sp = wbase + (size_t)(n % D) * C::kStageBytes;
+        uint8_t* const sc = wbase + D * C::kStageBytes + (size_t)((n / SUB) % NSB) * C::kScaleBytes;
+        const uint32_t bytes = 16 * (KSUB / 2) + (half == 0 ? 16 * RSS : 0);
+        if (lane == 0) mbar_expect_tx(bar, bytes);
         __syncwarp();
-        if (lane == 0) mbar_arrive(EMPTY(st));
-        if (++st == a.stages) {
-            st = 0;
-            phase ^= 1;
+        if (GATE_UP) {
+            // ring row m: m < 8 gate row, m >= 8 the matching up row
+            if (lane < 16) {
+                const int pair = blk * 8 + (lane & 7);
+                const int nrow = (lane < 8) ? pair : a.N / 2 + pair;
+                bulk_g2s(smem_u32(sp + (size_t)lane * RSA),
+                         a.packed + (slot_rows + nrow) * (size_t)(K / 2) + (size_t)half * (KSUB / 2), (uint32_t)(KSUB / 2), bar);
+            } else if (lane < 18 && half == 0) {
+                const int up = lane - 16;
+                const int nrow = (up ? a.N / 2 : 0) + blk * 8;
+                bulk_g2s(smem_u32(sc + (size_t)up * 8 * RSS), a.scale + (slot_rows + nrow) * (size_t)RSS, (uint32_t)(8 * RSS), bar);
+            }
+        } else {
+            const size_t nrow = slot_rows + (size_t)blk * 16;
+            if (lane == 0) bulk_g2s(smem_u32(sp), a.packed + nrow * (size_t)(K / 2), (uint32_t)(16 * (K / 2)), bar);
+            if (lane == 1) bulk_g2s(smem_u32(sc), a.scale + nrow * (size_t)RSS, (uint32_t)(16 * RSS), bar);
         }
-        float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    };
+
+    ItemIter cur, pre;   // the item being computed, and the one whose copies are issued next
+    cur.start(ib, ie, blocks, warp, kWarps);
+    pre = cur;
+    int pre_half = 0, n_issued = 0, n_done = 0;
+    int pre_g = -1;
+    int4 pre_grp = make_int4(0, 0, 0, 0);
+    auto issue_next = [&]() {
+        if (!pre.valid()) return;
+        if (pre.g != pre_g) {
+            pre_g = pre.g;
+            pre_grp = a.groups[pre_g];
+        }
+        issue(pre_grp, pre.it, pre_half, n_issued++);
+        if (++pre_half == SUB) {
+            pre_half = 0;
+            pre.next(ib);
+        }
+    };
+    // prologue: D pieces in flight
+    for (int q = 0; q < D; q++) issue_next();
+
+    // A warp whose bounded wait gave up stops working but keeps meeting the CTA barriers below.
+    bool dead = false;
+    const int g_first = ib / blocks, g_last = (ie - 1) / blocks;
+    for (int g = g_first; g <= g_last; g++) {
+        const int4 grp = a.groups[g];
+        // ---- the group's activation tile: warp t converts token t ----
+        __syncthreads();  // every warp is done with the previous group's tile
+        for (int tk = warp; tk < grp.z; tk += kWarps) {
+            const int route = a.sorted_route[grp.y + tk];
+            const size_t row = GATE_UP ? (size_t)(route / a.top_k) : (size_t)route;
+            const bool is_bf16 = GATE_UP && a.act_dtype == 0;
+            // the lane's K / 32 values, eight consecutive k at a time, kept in registers
+            float v[K / 256][8];
 #pragma unroll
-        for (int wi = 0; wi < WIN; wi++) {
-            // the lane's two scale bytes of this window: bytes 2*t4, 2*t4+1 of the window's eight
-            const uint32_t wl2 = (t4 & 2) ? scl[wi * 2 + 1] : scl[wi * 2];
-            const uint32_t wh2 = (t4 & 2) ? sch[wi * 2 + 1] : sch[wi * 2];
-            uint32_t slo0, slo1, shi0, shi1;
-            e4m3x2_to_f16_scales((t4 & 1) ? (wl2 >> 16) : (wl2 & 0xffffu), slo0, slo1);
-            e4m3x2_to_f16_scales((t4 & 1) ? (wh2 >> 16) : (wh2 & 0xffffu), shi0, shi1);
-            const uint32_t wl[4] = {plo[wi].x, plo[wi].y, plo[wi].z, plo[wi].w};
-            const uint32_t wh[4] = {phi[wi].x, phi[wi].y, phi[wi].z, phi[wi].w};
+            for (int c8 = 0; c8 < K / 256; c8++) {
+                const size_t k = row * K + c8 * 256 + lane * 8;
+                if (is_bf16) {
+                    const uint4 u = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.act) + k);
+                    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const uint4 xb = xf[wi * 4 + j];
-                uint32_t ql[4], qh[4];
-                e2m1x8_to_f16x2(wl[j], ql);
-                e2m1x8_to_f16x2(wh[j], qh);
-                const uint32_t sl = (j < 2) ? slo0 : slo1, sh = (j < 2) ? shi0 : shi1;
-#pragma unroll
-                for (int q = 0; q < 4; q++) {
-                    ql[q] = hmul2_f16(ql[q], sl);
-                    qh[q] = hmul2_f16(qh[q], sh);
+                    for (int q = 0; q < 4; q++) {
+                        const float2 f = bf16x2_to_f32(w[q]);
+                        v[c8][2 * q] = f.x;
+                        v[c8][2 * q + 1] = f.y;
+                    }
+                } else {
+                    const float4 f0 = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.act) + k);
+                    const float4 f1 = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.act) + k + 4);
+                    v[c8][0] = f0.x; v[c8][1] = f0.y; v[c8][2] = f0.z; v[c8][3] = f0.w;
+                    v[c8][4] = f1.x; v[c8][5] = f1.y; v[c8][6] = f1.z; v[c8][7] = f1.w;
                 }
-                // k slots (2t, 2t+1 | 2t+8, 2t+9) of the two MMAs <- the word's k (0,1 | 2,3) and (4,5 | 6,7)
-                mma_f16(acc[0], ql[0], qh[0], ql[1], qh[1], xb.x, xb.y);
-                mma_f16(acc[1], ql[2], qh[2], ql[3], qh[3], xb.z, xb.w);
+            }
+            float m = 0.f;
+#pragma unroll
+            for (int c8 = 0; c8 < K / 256; c8++)
+#pragma unroll
+                for (int q = 0; q < 8; q++) m = fmaxf(m, fabsf(v[c8][q]));
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+            // largest magnitude into [2^14, 2^15): exact power-of-two scaling, f16 keeps every bit of
+            // a bf16 input and 11 bits of an f32 one
+            const int e = (int)((__float_as_uint(m) >> 23) & 0xff);
+            float inv = 1.0f, sc = 1.0f;
+            if (e > 0 && e < 255) {
+                inv = __uint_as_float((uint32_t)(127 + 14 - (e - 127)) << 23);
+                sc = __uint_as_float((uint32_t)(127 - 14 + (e - 127)) << 23);
+            }
+            __half* xrow = reinterpret_cast<__half*>(xtile + (size_t)tk * RSX);
+#pragma unroll
+            for (int c8 = 0; c8 < K / 256; c8++) {
+                __half2 h[4];
+#pragma unroll
+                for (int q = 0; q < 4; q++) h[q] = __floats2half2_rn(v[c8][2 * q] * inv, v[c8][2 * q + 1] * inv);
+                // eight consecutive k are one 16-byte chunk of the k-permuted row
+                *reinterpret_cast<uint4*>(xrow + perm_k(c8 * 256 + lane * 8)) =
+                    make_uint4(*reinterpret_cast<uint32_t*>(&h[0]), *reinterpret_cast<uint32_t*>(&h[1]),
+                               *reinterpret_cast<uint32_t*>(&h[2]), *reinterpret_cast<uint32_t*>(&h[3]));
+            }
+            if (lane == 0) {
+                s_xscale[tk] = sc;
+                s_route[tk] = route;
+                s_factor[tk] = GATE_UP ? 1.0f : a.route_weight[route];
             }
         }
-        float c4[4];
-#pragma unroll
-        for (int q = 0; q < 4; q++) c4[q] = acc[0][q] + acc[1][q];
-        if (!GATE_UP) {
-            // undo this warp's token scales: columns 2*t4, 2*t4+1 belong to the lanes with g8 == column
-            const float s0 = __shfl_sync(0xffffffffu, xscale, (2 * t4) * 4);
-            const float s1 = __shfl_sync(0xffffffffu, xscale, (2 * t4 + 1) * 4);
-            c4[0] *= s0; c4[1] *= s1; c4[2] *= s0; c4[3] *= s1;
-        }
+        __syncthreads();
 
-        // ---- K reduction across the warps of this row tile ----
-        if (KS > 1) {
-            float* const buf = red + (size_t)rs * kConsumerWarps * 128;
-            if (ks != gatherer) {
-                if (!mbar_wait(REMPTY(rs), rphase ^ 1, a.err)) return;
-                *reinterpret_cast<float4*>(buf + warp * 128 + lane * 4) = make_float4(c4[0], c4[1], c4[2], c4[3]);
-                __syncwarp();
-                if (lane == 0) mbar_arrive(RFULL(rs));
-            } else {
-                // The gatherer changes from item to item, so it first observes that the previous use
-                // of this buffer was drained (which implies that use's RFULL phase completed): a
-                // parity wait is only meaningful when the waiter is at most one phase behind.
-                if (!mbar_wait(REMPTY(rs), rphase ^ 1, a.err)) return;
-                if (!mbar_wait(RFULL(rs), rphase, a.err)) return;
-#pragma unroll
-                for (int o = 0; o < KS; o++) {
-                    if (o == gatherer) continue;
-                    const float4 v = *reinterpret_cast<const float4*>(buf + (tile * KS + o) * 128 + lane * 4);
-                    c4[0] += v.x; c4[1] += v.y; c4[2] += v.z; c4[3] += v.w;
-                }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(REMPTY(rs));
-            }
-            rs ^= 1;
-            if (rs == 0) rphase ^= 1;
-        }
-
-        // ---- epilogue (the gathering warp of each row tile) ----
-        // c4[0], c4[1]: fragment row g8, tokens 2*t4, 2*t4+1;  c4[2], c4[3]: row g8 + 8
-        if (ks == gatherer) {
-            const float ga = f16_global_to_f32(graw_a), gb = f16_global_to_f32(graw_b);
+        // ---- this warp's items of the group ----
+        const int seg_end = min(ie, (g + 1) * blocks);
+        while (!dead && cur.valid() && cur.g == g && cur.it < seg_end) {
+            const int blk = cur.it % blocks;
+            const size_t slot_rows = (size_t)grp.x * a.N;
+            // the two rows' f16 globals: requested now (raw), converted after the MMAs
+            uint16_t graw_a, graw_b;
             if (GATE_UP) {
-                const int pk = perm_k(blk * (ROWS / 2) + tile * 8 + g8);
+                graw_a = a.global[slot_rows + blk * 8 + g8];
+                graw_b = a.global[slot_rows + a.N / 2 + blk * 8 + g8];
+            } else {
+                graw_a = a.global[slot_rows + blk * 16 + g8];
+                graw_b = a.global[slot_rows + blk * 16 + 8 + g8];
+            }
+            float acc[NT][4][4];
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+                for (int q = 0; q < 4; q++)
+#pragma unroll
+                    for (int r = 0; r < 4; r++) acc[nt][q][r] = 0.f;
+#pragma unroll
+            for (int half = 0; half < SUB; half++) {
+                const int n = n_done;
+                if (!mbar_wait(full0 + 8u * (n % D), (n / D) & 1, a.err)) {
+                    dead = true;
+                    break;
+                }
+                const uint32_t sp = smem_u32(wbase + (size_t)(n % D) * C::kStageBytes);
+                const uint32_t sc = smem_u32(wbase + D * C::kStageBytes + (size_t)((n / SUB) % NSB) * C::kScaleBytes);
+                const uint32_t row_lo = sp + g8 * RSA + t4 * 16, row_hi = row_lo + 8 * RSA;
+                const uint32_t sc_lo = sc + g8 * RSS + half * (KSUB / 16), sc_hi = sc_lo + 8 * RSS;
+                const uint32_t xa = smem_u32(xtile) + g8 * RSX + t4 * 16 + half * (KSUB * 2);
+                if (a.debug != 1) {
+#pragma unroll
+                    for (int w2 = 0; w2 < WIN / 2; w2++) {
+                        // scales of two windows: 16 bytes per row
+                        const uint4 sl4 = lds128(sc_lo + w2 * 16), sh4 = lds128(sc_hi + w2 * 16);
+                        const uint32_t slw[4] = {sl4.x, sl4.y, sl4.z, sl4.w}, shw[4] = {sh4.x, sh4.y, sh4.z, sh4.w};
+#pragma unroll
+                        for (int wq = 0; wq < 2; wq++) {
+                            const int wi = w2 * 2 + wq;
+                            const uint4 plo = lds128(row_lo + wi * 64), phi = lds128(row_hi + wi * 64);
+                            // the lane's two scale bytes of this window: bytes 2*t4, 2*t4+1 of the window's eight
+                            const uint32_t wl2 = (t4 & 2) ? slw[wq * 2 + 1] : slw[wq * 2];
+                            const uint32_t wh2 = (t4 & 2) ? shw[wq * 2 + 1] : shw[wq * 2];
+                            uint32_t slo0, slo1, shi0, shi1;
+                            e4m3x2_to_f16_scales((t4 & 1) ? (wl2 >> 16) : (wl2 & 0xffffu), slo0, slo1);
+                            e4m3x2_to_f16_scales((t4 & 1) ? (wh2 >> 16) : (wh2 & 0xffffu), shi0, shi1);
+                            const uint32_t wl[4] = {plo.x, plo.y, plo.z, plo.w};
+                            const uint32_t wh[4] = {phi.x, phi.y, phi.z, phi.w};
+#pragma unroll
+                            for (int j = 0; j < 4; j++) {
+                                uint32_t ql[4], qh[4];
+                                e2m1x8_to_f16x2(wl[j], ql);
+                                e2m1x8_to_f16x2(wh[j], qh);
+                                const uint32_t sl = (j < 2) ? slo0 : slo1, sh = (j < 2) ? shi0 : shi1;
+#pragma unroll
+                                for (int q = 0; q < 4; q++) {
+                                    ql[q] = hmul2_f16(ql[q], sl);
+                                    qh[q] = hmul2_f16(qh[q], sh);
+                                }
+                                // k slots (2t, 2t+1 | 2t+8, 2t+9) of the two MMAs <- the word's k (0,1 | 2,3), (4,5 | 6,7);
+                                // the dequantised fragments serve every token tile of the group
+#pragma unroll
+                                for (int nt = 0; nt < NT; nt++) {
+                                    const uint4 xb = lds128(xa + nt * 8 * RSX + wi * 256 + j * 64);
+                                    mma_f16(acc[nt][(j & 1) * 2], ql[0], qh[0], ql[1], qh[1], xb.x, xb.y);
+                                    mma_f16(acc[nt][(j & 1) * 2 + 1], ql[2], qh[2], ql[3], qh[3], xb.z, xb.w);
+                                }
+                            }
+                        }
+                    }
+                } else {
+                    const uint4 plo = lds128(row_lo), phi = lds128(row_hi + (WIN - 1) * 64);
+                    acc[0][0][0] = __uint_as_float(plo.x ^ phi.w);
+                }
+                n_done++;
+                // the buffer has been read: order those reads before the async writes that refill it
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                issue_next();
+            }
+            if (dead) break;
+            // ---- epilogue: rows g8 (acc[.][0..1]) and g8 + 8 (acc[.][2..3]), tokens 2*t4, 2*t4 + 1 ----
+            const float ga = f16_global_to_f32(graw_a), gb = f16_global_to_f32(graw_b);
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                float c4[4];
+#pragma unroll
+                for (int r = 0; r < 4; r++) c4[r] = (acc[nt][0][r] + acc[nt][1][r]) + (acc[nt][2][r] + acc[nt][3][r]);
 #pragma unroll
                 for (int c = 0; c < 2; c++) {
-                    if (2 * t4 + c < grp.z) {
-                        const float ts = c ? rw1 : rw0;
-                        const float gate = c4[c] * ga * ts, up = c4[2 + c] * gb * ts;
-                        a.ic2[(size_t)(c ? route1 : route0) * (a.N / 2) + pk] = (gate / (1.0f + __expf(-gate))) * up;
+                    const int tok = nt * 8 + 2 * t4 + c;
+                    if (tok < grp.z) {
+                        const float ts = s_xscale[tok];
+                        const int route = s_route[tok];
+                        if (GATE_UP) {
+                            const float gate = c4[c] * ga * ts, up = c4[2 + c] * gb * ts;
+                            a.ic2[(size_t)route * (a.N / 2) + blk * 8 + g8] = (gate / (1.0f + __expf(-gate))) * up;
+                        } else {
+                            const float wr = s_factor[tok];
+                            a.yroute[(size_t)route * a.N + blk * 16 + g8] = wr * ((c4[c] * ts) * ga);
+                            a.yroute[(size_t)route * a.N + blk * 16 + 8 + g8] = wr * ((c4[2 + c] * ts) * gb);
+                        }
                     }
                 }
-            } else {
-                const int d = blk * ROWS + tile * 16 + g8;
-#pragma unroll
-                for (int h = 0; h < 2; h++) {
-                    const float gd = h ? gb : ga;
-#pragma unroll
-                    for (int c = 0; c < 2; c++)
-                        if (2 * t4 + c < grp.z)
-                            a.yroute[(size_t)(c ? route1 : route0) * a.N + d + 8 * h] =
-                                (c ? rw1 : rw0) * (c4[2 * h + c] * gd);
-                }
             }
-        }
-        if (++blk == blocks) {
-            blk = 0;
-            g++;
-            if (item + 1 < item_end) grp = a.groups[g];
-            new_group = true;
+            cur.next(ib);
         }
     }
 }
 
-template <bool GATE_UP, int KS, int WIN>
-size_t expert_smem_bytes(int stages) {
-    using C = Cfg<GATE_UP, KS, WIN>;
-    return (size_t)stages * C::kStageBytes + 2 * kConsumerWarps * 128 * sizeof(float) +
-           (2 * stages + 4) * sizeof(uint64_t) + 128;
-}
-
-// OCC persistent CTAs per SM share its shared memory: as many stages as fit in their share, at most 8
-template <bool GATE_UP, int KS, int WIN, int OCC>
+template <bool GATE_UP, int K_, int NT, int OCC>
 void launch_expert(ExpertArgs a, int sm_count, cudaStream_t s) {
-    const size_t budget = (OCC == 1 ? 200 : 110) * 1024;
-    int stages = 8;
-    while (stages > 2 && expert_smem_bytes<GATE_UP, KS, WIN>(stages) > budget) stages--;
-    a.stages = stages;
-    const size_t smem = expert_smem_bytes<GATE_UP, KS, WIN>(stages);
+    using C = Cfg<GATE_UP, K_, NT>;
     static bool attr = false;
     if (!attr) {
-        cudaFuncSetAttribute(expert_mma_kernel<GATE_UP, KS, WIN, OCC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)(OCC == 1 ? 220 * 1024 : 112 * 1024));
+        cudaFuncSetAttribute(expert_mma_kernel<GATE_UP, K_, NT, OCC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)C::kSmem);
         attr = true;
     }
-    expert_mma_kernel<GATE_UP, KS, WIN, OCC><<<sm_count * OCC, kThreads, smem, s>>>(a);
+    expert_mma_kernel<GATE_UP, K_, NT, OCC><<<sm_count * OCC, C::kThreads, C::kSmem, s>>>(a);
+}
+
+// Large batches: the routes are bucketed by the multi-CTA CSR build (seg / route_idx); this turns every
+// bucket into groups of at most `group` routes.  One CTA; bins <= 1024.
+__global__ void __launch_bounds__(1024)
+groups_from_csr_kernel(const int32_t* __restrict__ seg, int bins, const int32_t* __restrict__ slot_of_bin, int slots,
+                       int group, int4* __restrict__ groups, int32_t* __restrict__ n_groups) {
+    __shared__ int wsum[32];
+    const int b = threadIdx.x, lane = b & 31, warp = b >> 5;
+    int cnt = 0, slot = -1;
+    if (b < bins) {
+        cnt = seg[b + 1] - seg[b];
+        slot = slot_of_bin ? slot_of_bin[b] : b;
+        if (slot < 0 || slot >= slots) cnt = 0;
+    }
+    const int ng = (cnt + group - 1) / group;
+    int incl = ng;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+    }
+    if (lane == 31) wsum[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        const int v = wsum[lane];
+        int j = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int u = __shfl_up_sync(0xffffffffu, j, o);
+            if (lane >= o) j += u;
+        }
+        wsum[lane] = j - v;
+        if (lane == 31) *n_groups = j;
+    }
+    __syncthreads();
+    int base = wsum[warp] + incl - ng;
+    if (b < bins) {
+        const int start = seg[b];
+        for (int q = 0; q < ng; q++) groups[base + q] = make_int4(slot, start + q * group, min(group, cnt - q * group), 0);
+    }
+}
+
+// rows whose slot is -1 contribute zeros: clear the per-route outputs that no group will write
+__global__ void zero_missing_routes_kernel(const int32_t* __restrict__ route_slot, int routes, int H,
+                                           float* __restrict__ yroute) {
+    const int r = blockIdx.x;
+    if (route_slot[r] >= 0) return;
+    for (int d = threadIdx.x; d < H; d += blockDim.x) yroute[(size_t)r * H + d] = 0.f;
 }
 
 }  // namespace
 
 size_t decode_plan_smem(int slots) { return (size_t)3 * slots * sizeof(int); }
 
-bool decode_mma_supported(int hidden, int inter, int routes, int slots) {
-    // the tensor-core decode kernels are instantiated for the production expert shape; every other
+bool decode_mma_supported(int hidden, int inter, int routes, int slots, int experts, bool have_expert_ids) {
+    // the tensor-core kernels are instantiated for the production expert shape; every other
     // multiple-of-16 shape takes the per-route kernels
-    return hidden == 2048 && inter == 512 && routes <= kPlanMaxRoutes && decode_plan_smem(slots) <= 180 * 1024;
+    if (hidden != 2048 || inter != 512) return false;
+    if (routes <= kPlanMaxRoutes) return decode_plan_smem(slots) <= 180 * 1024;
+    // larger batches bucket by expert id (or by slot when slot ids were given): at most 1024 bins
+    return have_expert_ids ? experts <= 1024 : slots <= 1024;
 }
 
 int launch_decode_mma(const BankView& b, const void* x, int x_dtype, const DecodeRoutes& rt,
                       const float* route_weight, int tokens, int top_k, DecodeScratch sc, int sm_count,
                       const Ctx& c) {
     const int routes = tokens * top_k;
-    c.begin(K_PERMUTE_ACT);
-    prep_act_kernel<<<tokens, 256, 0, c.s>>>(x, x_dtype, b.hidden, sc.xh, sc.tok_scale);
-    c.end();
-    PlanArgs pa{};
-    pa.route_slot_in = rt.route_slot_in;
-    pa.expert_ids = rt.expert_ids; pa.ids_dtype = rt.ids_dtype; pa.layer = rt.layer; pa.experts = rt.experts;
-    pa.n_ids = rt.n_ids; pa.slot_for_id = rt.slot_for_id; pa.route_slot_out = rt.route_slot_out;
-    pa.routes = routes; pa.slots = b.slots; pa.hidden = b.hidden;
-    pa.groups = sc.groups; pa.sorted_route = sc.sorted_route; pa.n_groups = sc.n_groups; pa.yroute = sc.yroute;
-    pa.bad_flag = rt.bad_flag;
-    const size_t psmem = decode_plan_smem(b.slots);
-    static bool pattr = false;
-    if (!pattr) {
-        cudaFuncSetAttribute(decode_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        pattr = true;
+    const bool small = routes <= kPlanMaxRoutes;
+    int launches = 0;
+    if (small) {
+        PlanArgs pa{};
+        pa.route_slot_in = rt.route_slot_in;
+        pa.expert_ids = rt.expert_ids; pa.ids_dtype = rt.ids_dtype; pa.layer = rt.layer; pa.experts = rt.experts;
+        pa.n_ids = rt.n_ids; pa.slot_for_id = rt.slot_for_id; pa.route_slot_out = rt.route_slot_out;
+        pa.routes = routes; pa.slots = b.slots; pa.hidden = b.hidden;
+        pa.groups = sc.groups; pa.sorted_route = sc.sorted_route; pa.n_groups = sc.n_groups; pa.yroute = sc.yroute;
+        pa.bad_flag = rt.bad_flag;
+        const size_t psmem = decode_plan_smem(b.slots);
+        static bool pattr = false;
+        if (!pattr) {
+            cudaFuncSetAttribute(decode_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            pattr = true;
+        }
+        c.begin(K_DECODE_PLAN);
+        decode_plan_kernel<<<1, kPlanThreads, psmem, c.s>>>(pa);
+        c.end();
+        launches += 1;
+    } else {
+        // bucket by expert id of the layer (serving call) or by slot id, then cut into groups of 16
+        const int32_t* bins_of_route;
+        const int32_t* slot_of_bin = nullptr;
+        int nbins;
+        if (rt.expert_ids) {
+            launches += launch_slot_rewrite(rt.expert_ids, rt.ids_dtype, routes, rt.layer, rt.experts, rt.slot_for_id,
+                                            rt.n_ids, rt.route_slot_out, sc.route_bin, rt.bad_flag, c);
+            bins_of_route = sc.route_bin;
+            slot_of_bin = rt.slot_for_id + (size_t)rt.layer * rt.experts;
+            nbins = rt.experts;
+        } else {
+            bins_of_route = rt.route_slot_in;
+            nbins = b.slots;
+        }
+        launches += launch_csr_build(bins_of_route, routes, nbins, sc.seg, sc.sorted_route, sc.csr_scratch, sc.csr_flag, c);
+        c.begin(K_DECODE_PLAN);
+        groups_from_csr_kernel<<<1, 1024, 0, c.s>>>(sc.seg, nbins, slot_of_bin, b.slots, 16, sc.groups, sc.n_groups);
+        zero_missing_routes_kernel<<<routes, 256, 0, c.s>>>(rt.expert_ids ? rt.route_slot_out : rt.route_slot_in, routes,
+                                                           b.hidden, sc.yroute);
+        c.end();
+        launches += 2;
     }
-    c.begin(K_DECODE_PLAN);
-    decode_plan_kernel<<<1, kPlanThreads, psmem, c.s>>>(pa);
-    c.end();
 
     ExpertArgs a{};
+    static const int debug_mode = [] { const char* e = getenv("FTM_DEBUG_EXPERT"); return e ? atoi(e) : 0; }();
+    a.debug = debug_mode;
     a.groups = sc.groups;
     a.sorted_route = sc.sorted_route;
     a.n_groups = sc.n_groups;
@@ -698,17 +730,23 @@ int launch_decode_mma(const BankView& b, const void* x, int x_dtype, const Decod
     a.top_k = top_k;
     // gate_up: K = hidden, N = 2 * inter rows
     a.packed = b.gu_packed; a.scale = b.gu_scale; a.global = b.gu_global;
-    a.act = sc.xh; a.tok_scale = sc.tok_scale; a.ic2 = sc.ic2p; a.N = 2 * b.inter;
+    a.act = x; a.act_dtype = x_dtype; a.ic2 = sc.ic2p; a.N = 2 * b.inter;
     c.begin(K_EXPERT_GATE_UP);
-    launch_expert<true, 8, 2, 2>(a, sm_count, c.s);   // K = 2048: 8 warps x 2 windows, 16 rows per item
+    if (small)
+        launch_expert<true, 2048, 1, 1>(a, sm_count, c.s);
+    else
+        launch_expert<true, 2048, 2, 1>(a, sm_count, c.s);
     c.end();
     // down: K = inter, N = hidden rows
     a.packed = b.dn_packed; a.scale = b.dn_scale; a.global = b.dn_global;
-    a.act = sc.ic2p; a.yroute = sc.yroute; a.route_weight = route_weight; a.N = b.hidden;
+    a.act = sc.ic2p; a.act_dtype = 1; a.yroute = sc.yroute; a.route_weight = route_weight; a.N = b.hidden;
     c.begin(K_EXPERT_DOWN);
-    launch_expert<false, 2, 2, 2>(a, sm_count, c.s);  // K = 512: 2 warps x 2 windows, 64 rows per item
+    if (small)
+        launch_expert<false, 512, 1, 1>(a, sm_count, c.s);
+    else
+        launch_expert<false, 512, 2, 1>(a, sm_count, c.s);
     c.end();
-    return 4;
+    return launches + 2;
 }
 
 }  // namespace ftm

@@ -57,14 +57,17 @@ int launch_decode_routes(const BankView& b, const __nv_bfloat16* x, const int32_
 
 // decode_mma.cu: grouped decode path (plan + k-permuted activations + TMA/mma.sync expert kernels)
 struct DecodeScratch {
-    __half* xh;             // [tokens, hidden] f16, k-permuted, scaled per token
-    float* tok_scale;       // [tokens] power-of-two scale that undoes it
-    float* ic2p;            // [routes, inter] f32, k-permuted
-    int4* groups;           // [routes] (slot, first sorted position, count <= 8, 0)
+    float* ic2p;            // [routes, inter] f32
+    int4* groups;           // [routes] (slot, first sorted position, count, 0)
     int32_t* sorted_route;  // [routes]
     int32_t* n_groups;      // [1]
     float* yroute;          // [routes, hidden] f32
     int32_t* err;           // raised when a bounded wait gives up
+    // large batches: buckets through the multi-CTA CSR build
+    int32_t* route_bin;     // [routes]
+    int32_t* seg;           // [bins + 1]
+    int32_t* csr_scratch;
+    int32_t* csr_flag;
 };
 // where the routes of a decode step come from: slot ids as given, or dense expert ids of one layer
 // that the plan maps to slots through the residency table
@@ -76,7 +79,7 @@ struct DecodeRoutes {
     int32_t* route_slot_out;
     int32_t* bad_flag;
 };
-bool decode_mma_supported(int hidden, int inter, int routes, int slots);
+bool decode_mma_supported(int hidden, int inter, int routes, int slots, int experts, bool have_expert_ids);
 int launch_decode_mma(const BankView& b, const void* x, int x_dtype, const DecodeRoutes& rt,
                       const float* route_weight, int tokens, int top_k, DecodeScratch sc, int sm_count,
                       const Ctx& c);

@@ -571,3 +571,66 @@ def test_decode_path_reports_no_async_errors(full):
     with pytest.raises(pkg.MoEError, match="expert id"):
         moe.sync_status()
     moe.sync_status()
+
+
+# ------------------------------------------------------------------ large batches (prefill sizes)
+def _zipf_ids(rng, tokens, experts, top_k, alpha):
+    """Skewed routing: expert popularity ~ rank^-alpha, top_k distinct experts per token."""
+    p = (np.arange(1, experts + 1) ** -alpha)
+    p /= p.sum()
+    p = p[rng.permutation(experts)]
+    return np.stack([rng.choice(experts, top_k, replace=False, p=p) for _ in range(tokens)]).astype(np.int32)
+
+
+@pytest.mark.parametrize("tokens", [300, 512])
+def test_large_batch_path_matches_cpu_path(full, tokens):
+    """More than 2048 routes: CSR buckets cut into groups of 16 tokens (Zipf 1.1 skew: some experts get
+    no token, hot ones many groups)."""
+    lay, moe, ol = full
+    rng = np.random.default_rng(tokens)
+    xb = pkg.synth.make_x(31 + tokens, tokens, lay.hidden)
+    xf = pkg.synth.bf16_bits_to_f32(xb)
+    ids = _zipf_ids(rng, tokens, lay.experts, lay.top_k, 1.1)
+    w = rng.uniform(0.05, 0.5, (tokens, lay.top_k)).astype(np.float32)
+    out = torch.empty((tokens, lay.hidden), dtype=torch.float32, device=dev())
+    req = pkg.MoEDeviceRequest(0, lay.hidden, lay.inter, lay.top_k, bf16_dev(xb), torch.from_numpy(ids).to(dev()),
+                               torch.from_numpy(w).to(dev()))
+    moe.grouped_moe_staged(req, out)
+    moe.sync_status()
+    want = o.grouped_moe_reference_mt(ol.banks, lay.hidden, lay.inter, xf, lay.top_k, ids.reshape(-1), w.reshape(-1))
+    rel, _ = check_close(out.cpu().numpy(), want)
+    assert rel < 1e-3
+    counts = np.bincount(ids.reshape(-1), minlength=lay.experts)
+    assert counts.max() > 16, "the case must cut at least one expert into several groups"
+
+
+def test_prefill_2048_tokens_paths_agree_and_block_properties(full):
+    """T = 2048 (config 3 size): the grouped tensor-core path against the per-route scalar path on the same
+    routes, and the whole block's routed ids against the CPU router."""
+    lay, moe, ol = full
+    tokens = 2048
+    rng = np.random.default_rng(7)
+    xb = pkg.synth.make_x(2048, tokens, lay.hidden)
+    ids = _zipf_ids(rng, tokens, lay.experts, lay.top_k, 1.1)
+    w = rng.uniform(0.05, 0.5, (tokens, lay.top_k)).astype(np.float32)
+    req = pkg.MoEDeviceRequest(0, lay.hidden, lay.inter, lay.top_k, bf16_dev(xb), torch.from_numpy(ids).to(dev()),
+                               torch.from_numpy(w).to(dev()))
+    outs = []
+    for path in (pkg._lib.PATH_AUTO, pkg._lib.PATH_SCALAR):
+        out = torch.empty((tokens, lay.hidden), dtype=torch.float32, device=dev())
+        moe.grouped_moe_staged(req, out, path=path)
+        moe.sync_status()
+        outs.append(out.cpu().numpy())
+    rel, _ = check_close(outs[0], outs[1])
+    assert rel < 1e-3
+    # whole block: ids bit-exact against the CPU router at the full size
+    out = torch.empty((tokens, lay.hidden), dtype=torch.bfloat16, device=dev())
+    got_ids = torch.empty((tokens, lay.top_k), dtype=torch.int32, device=dev())
+    got_w = torch.empty((tokens, lay.top_k), dtype=torch.float32, device=dev())
+    moe.moe_block(0, bf16_dev(xb), bf16_dev(lay.gate_w), bf16_dev(lay.sh_gate_up), bf16_dev(lay.sh_down),
+                  bf16_dev(lay.sh_gate), out, ids_out=got_ids, weights_out=got_w)
+    moe.sync_status()
+    want_ids, want_w = o.router(ol, pkg.synth.bf16_bits_to_f32(xb))
+    assert np.array_equal(got_ids.cpu().numpy(), want_ids)
+    assert np.abs(got_w.cpu().numpy() - want_w).max() <= 1e-6
+    assert torch.isfinite(out.float()).all()
