@@ -42,6 +42,7 @@ _PROTOS = {
     "ftm_router_from_logits": (_int, [_vp, _vp, _i32, _vp, _vp, _vp]),
     "ftm_csr_build": (_int, [_vp, _vp, _i32, _i32, _vp, _vp, _vp]),
     "ftm_csr_bad": (_int, [_vp, _vp, C.POINTER(_i32)]),
+    "ftm_csr_build_noalloc": (_int, [_vp, _i32, _i32, _vp, _vp, _vp, _vp]),
     "ftm_grouped_moe_host": (_int, [_vp, _vp, _sz, _i32, _vp, _sz, _vp, _sz, _vp, _sz]),
     "ftm_grouped_moe_dev": (_int, [_vp, _vp, _int, _i32, _i32, _vp, _sz, _vp, _vp, _int, _vp]),
     "ftm_moe_layer_staged": (_int, [_vp, _i32, _vp, _int, _vp, _int, _vp, _i32, _vp, _int, _int, _vp]),

@@ -11,6 +11,9 @@
 // order, then lane order".  Pass 1 counts per (CTA, bin); pass 2 (one CTA) turns the counts into
 // per-(CTA, bin) start offsets; pass 3 recounts per warp and scatters with a warp-level rank.
 // When everything fits one CTA the three passes run inside a single launch.
+#include <mutex>
+
+#include "../../include/ftmoe.h"
 #include "kernels.cuh"
 
 namespace ftm {
@@ -214,6 +217,24 @@ __global__ void slot_rewrite_kernel(const void* __restrict__ expert_ids, int ids
 
 }  // namespace
 
+// ---- permutation build without any allocation ------------------------------------------------
+// Scratch of the multi-CTA build (per-CTA histograms and the out-of-range flag) for callers that
+// must not allocate.  It lives in the library image: every GPU that loads the library carries these
+// bytes until the process exits.
+constexpr int kNoAllocMaxRoutes = 262144;                                // 128 chunks of 2048 routes
+constexpr int kNoAllocMaxBins = 1024;
+constexpr int kNoAllocScratchInts = (kNoAllocMaxRoutes / 2048) * kNoAllocMaxBins;  // 512 KiB
+static __device__ __align__(256) int32_t g_noalloc_scratch[kNoAllocScratchInts + 64];
+
+namespace {
+
+// device address of g_noalloc_scratch per device ordinal, looked up once with that device current
+constexpr int kMaxDevices = 64;
+int32_t* g_noalloc_ptr[kMaxDevices] = {};
+std::mutex g_noalloc_mu;
+
+}  // namespace
+
 size_t csr_scratch_ints(int routes, int bins) {
     size_t nctas = ((size_t)routes + kChunkRoutes - 1) / kChunkRoutes;
     return (nctas ? nctas : 1) * (size_t)bins;
@@ -251,3 +272,44 @@ int launch_slot_rewrite(const void* expert_ids, int ids_dtype, int routes, int l
 }
 
 }  // namespace ftm
+
+// The permutation build for callers that cannot allocate device memory: an engine that runs under
+// a fixed memory plan (every byte handed out at start-up, the allocator then locked), or a call site
+// inside a region where allocation is forbidden.  It needs no adapter handle: the per-CTA histograms
+// and the out-of-range flag live in g_noalloc_scratch above.
+//
+//  - Limits: routes <= 262144 and bins <= 1024 (the array's size); anything larger is refused.
+//  - The first call on a device looks the array's device address up (cudaGetSymbolAddress, with that
+//    device current) and keeps it; make that first call before any stream capture begins.
+//  - All calls on one device share the array.  The flag is cleared at the start of every call, the
+//    histograms are fully rewritten by the first pass; two calls that overlap on the GPU (different
+//    streams) race on it.
+//  - bad_out (device, may be NULL) receives 1 when a slot was outside [0, bins), else 0.
+extern "C" FTM_API int ftm_csr_build_noalloc(const int32_t* route_slot, int32_t routes, int32_t bins,
+                                             int32_t* seg_out, int32_t* route_idx_out, int32_t* bad_out,
+                                             void* stream) {
+    using namespace ftm;
+    if (!route_slot || !seg_out || !route_idx_out) return FTM_ERR_BAD;
+    if (routes <= 0 || routes > kNoAllocMaxRoutes || bins < 1 || bins > kNoAllocMaxBins) return FTM_ERR_BAD;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return FTM_ERR_CUDA;
+    int32_t* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(g_noalloc_mu);
+        if (!g_noalloc_ptr[dev]) {
+            void* p = nullptr;
+            if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || !p) return FTM_ERR_CUDA;
+            g_noalloc_ptr[dev] = reinterpret_cast<int32_t*>(p);
+        }
+        scratch = g_noalloc_ptr[dev];
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    int32_t* flag = scratch + kNoAllocScratchInts;  // the last 256 bytes of the array
+    if (cudaMemsetAsync(flag, 0, sizeof(int32_t), s) != cudaSuccess) return FTM_ERR_CUDA;
+    Ctx c{s, nullptr};
+    launch_csr_build(route_slot, routes, bins, seg_out, route_idx_out, scratch, flag, c);
+    if (bad_out && cudaMemcpyAsync(bad_out, flag, sizeof(int32_t), cudaMemcpyDeviceToDevice, s) != cudaSuccess)
+        return FTM_ERR_CUDA;
+    return cudaGetLastError() == cudaSuccess ? FTM_OK : FTM_ERR_CUDA;
+}
+

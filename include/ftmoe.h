@@ -156,6 +156,17 @@ FTM_API int ftm_csr_build(ftm_handle* h, const int32_t* route_slot, int32_t rout
                   int32_t* seg_out, int32_t* route_idx_out, void* stream);
 /* synchronises the stream and returns the flag (0 = all routes were in range) */
 FTM_API int ftm_csr_bad(ftm_handle* h, void* stream, int32_t* bad_out);
+/* No counterpart in the reference.  The same permutation build for callers that cannot allocate device
+ * memory (an engine running under a fixed memory plan whose allocator is locked after start-up, or
+ * a call site where allocation is forbidden): it takes no handle, and its scratch (per-CTA histograms
+ * and the out-of-range flag) is a fixed array inside the library image, held by every GPU that loads
+ * the library until the process exits.  Limits: routes <= 262144, bins <= 1024; larger sizes return
+ * FTM_ERR_BAD.  It calls no allocating routine.  The first call on a device looks up the array's
+ * device address (with that device current): make it before any stream capture.  Calls on one
+ * device share the array, so two calls that overlap on the GPU race.  bad_out (device pointer, may
+ * be NULL) receives 1 when a slot was outside [0, bins).  Asynchronous on `stream`. */
+FTM_API int ftm_csr_build_noalloc(const int32_t* route_slot, int32_t routes, int32_t bins, int32_t* seg_out,
+                                  int32_t* route_idx_out, int32_t* bad_out, void* stream);
 
 /* ---- ExpertGemm (src/domain/expert_kernel.rs:246-294) ----------------------------------- */
 /* grouped_moe(&MoEGroup, &mut [f32]): host hand-off.  x [T, hidden] f32 host (narrowed to bf16
