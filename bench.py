@@ -179,6 +179,9 @@ def run_b200(args):
         dist.barrier()
     pkg = importlib.import_module("ferrum-torrens_b200")
 
+    if world > 1:
+        return run_ep(args, pkg, dev, world, rank, local)
+
     T = args.tokens or 64
     nlayers = max(1, args.layers)
     moe = pkg.B200MoE(local, pkg.ExpertShapes(HIDDEN, INTER), EXPERTS * nlayers, experts=EXPERTS, layers=nlayers,
@@ -326,6 +329,105 @@ def run_b200(args):
     moe.close()
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_ep(args, pkg, dev, world, rank, local):
+    """N > 1: the expert-parallel layer (256 experts split over the ranks, T = 8192 tokens per GPU,
+    dispatch / combine by NCCL all-to-all).  Weak scaling: per-GPU tokens are fixed."""
+    import torch
+    import torch.distributed as dist
+    ep = importlib.import_module("ferrum-torrens_b200.ep")
+
+    T = args.tokens or 8192
+    nlayers = min(max(1, args.layers), 2)
+    per = EXPERTS // world
+    be = ep.LibBackend(local, rank, world, pkg.ExpertShapes(HIDDEN, INTER), experts=EXPERTS, layers=nlayers,
+                       top_k=TOP_K, shared_inter=SHARED, max_tokens=T)
+    dense, xs = [], []
+    for l in range(nlayers):
+        pkg.synth.fill_banks_on_device(be.owner, l, seed=1000 + 977 * rank + l, experts=per, slot0=l * per,
+                                       expert0=rank * per)
+        dense.append(pkg.synth.device_dense_weights(2000 + l, dev))          # replicated: same seed on every rank
+        xs.append(pkg.synth.device_x(3000 + 17 * rank + l, T, HIDDEN, dev))
+    out = torch.empty((T, HIDDEN), dtype=torch.bfloat16, device=dev)
+    layer = ep.ExpertParallelMoE(be, world)
+
+    def step(i, record=None):
+        l = i % nlayers
+        g, su, sd, sg = dense[l]
+        layer.forward(l, xs[l], g, su, sd, sg, out, record=record)
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    W, K = max(3, args.warmup), max(1, args.steps)
+    step(0)
+    be.front.sync_status()
+    be.owner.sync_status()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    for i in range(W):
+        step(i)
+    barrier()
+    l0 = be.front.kernel_launches() + be.owner.kernel_launches()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(K):
+        step(W + i)
+    e1.record()
+    barrier()
+    launches = be.front.kernel_launches() + be.owner.kernel_launches() - l0
+    ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    total_ms = float(ms.item())
+    clocks = sampler.stop() if rank == 0 else None
+
+    # phase breakdown of a few steps: time between the marks, max over ranks
+    names = ["packed", "dispatched", "computed", "returned", "combined"]
+    acc = torch.zeros(len(names), device=dev)
+    reps = min(K, 5)
+    for i in range(reps):
+        evs = {}
+        start = torch.cuda.Event(enable_timing=True)
+        start.record()
+
+        def rec(name):
+            evs[name] = torch.cuda.Event(enable_timing=True)
+            evs[name].record()
+        step(W + i, record=rec)
+        torch.cuda.synchronize()
+        prev = start
+        for j, n in enumerate(names):
+            acc[j] += prev.elapsed_time(evs[n])
+            prev = evs[n]
+    acc /= reps
+    dist.all_reduce(acc, op=dist.ReduceOp.MAX)
+    phases = {n: float(v) for n, v in zip(["router_shared_pack_ms", "dispatch_a2a_ms", "experts_ms", "return_a2a_ms",
+                                           "combine_ms"], acc.tolist())}
+    sent = torch.tensor([sum(layer.last_counts[0]) - layer.last_counts[0][rank]], device=dev, dtype=torch.float32)
+    dist.all_reduce(sent, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": world * T * K / (total_ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": K,
+            "warmup": W, "ms_per_step": total_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16 activations x NVFP4 (e2m1 + e4m3 block scales) weights, f32 accumulate",
+            "data": "synthetic",
+            "config": {"workload": f"expert-parallel layer, T={T} tokens per GPU, {EXPERTS} experts split {per} per GPU, "
+                                   f"top-{TOP_K}, uniform routing, NCCL all-to-all dispatch/combine",
+                       "l2": f"inputs larger than L2: {nlayers} layers cycled, {T * TOP_K} routes x 4 KB rows per step",
+                       "timed_region": "whole block incl. both all-to-alls, CUDA events, max over ranks"},
+            "gpu_launches": int(launches), "clocks": clocks,
+            "ep": {"phases_ms_max_over_ranks": phases,
+                   "exposed_comm_ms": phases["dispatch_a2a_ms"] + phases["return_a2a_ms"],
+                   "max_routes_sent_off_rank": float(sent.item()),
+                   "nvlink_bytes_each_way_per_gpu": float(sent.item()) * HIDDEN * 2},
+            "e2e": None, "roofline": None,
+        }
+        print(json.dumps(line))
+    be.close()
+    dist.destroy_process_group()
 
 
 def main():

@@ -56,6 +56,8 @@ _PROTOS = {
     "ftm_combine": (_int, [_vp, _vp, _int, _vp, _vp, _i32, _vp, _int, _vp]),
     "ftm_moe_block": (_int, [_vp, _i32, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _int, _vp, _vp, _int, _vp]),
     "ftm_kernel_launches": (C.c_uint64, [_vp]),
+    "ftm_ep_pack": (_int, [_vp, _vp, _vp, _vp, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "ftm_ep_combine": (_int, [_vp, _vp, _int, _vp, _vp, _vp, _i32, _vp, _int, _vp]),
     "ftm_profile_enable": (_int, [_vp, _int]),
     "ftm_profile_read": (_int, [_vp, _int, C.POINTER(C.c_double), C.POINTER(C.c_uint64)]),
     "ftm_profile_kind_name": (C.c_char_p, [_int]),

@@ -27,7 +27,7 @@ thread_local std::string g_create_error;
 const char* const kKindNames[K_NUM_KINDS] = {
     "router_logits", "router_topk", "slot_rewrite", "csr_build", "expert_gate_up", "expert_down", "sum_routes",
     "shared_phase1", "shared_phase2", "cast_bf16",   "combine",  "grouped_gate_up", "grouped_down",
-    "permute_act",   "decode_plan"};
+    "permute_act",   "decode_plan",   "ep_pack",         "ep_combine"};
 
 }  // namespace
 
@@ -727,6 +727,45 @@ FTM_API const char* ftm_profile_kind_name(int kind) {
     return (kind >= 0 && kind < K_NUM_KINDS) ? kKindNames[kind] : nullptr;
 }
 FTM_API uint64_t ftm_kernel_launches(const ftm_handle* h) { return h ? h->launches : 0; }
+
+// ---- expert-parallel dispatch / combine -------------------------------------------------------
+
+FTM_API int ftm_ep_pack(ftm_handle* h, const void* x_bf16, const int32_t* ids, const float* weights, int32_t tokens,
+                        int32_t ep_size, void* send_x, int32_t* send_expert, float* send_weight, int32_t* route_idx,
+                        int32_t* counts, void* stream) {
+    if (!h) return FTM_ERR_BAD;
+    std::lock_guard<std::mutex> lk(h->mu);
+    if (!x_bf16 || !ids || !weights || !send_x || !send_expert || !send_weight || !route_idx || !counts)
+        return fail(h, FTM_ERR_BAD, "moe: ep_pack: null buffer");
+    if (tokens <= 0 || tokens > h->cfg.max_tokens)
+        return fail(h, FTM_ERR_BAD, "moe: ep_pack: %d tokens (max_tokens %d)", tokens, h->cfg.max_tokens);
+    if (ep_size < 1 || ep_size > 32 || h->cfg.experts % ep_size)
+        return fail(h, FTM_ERR_BAD, "moe: ep_pack: %d experts do not split over %d ranks", h->cfg.experts, ep_size);
+    cudaStream_t s = pick(h, stream);
+    const int routes = tokens * h->cfg.top_k;
+    CU(h, cudaMemsetAsync(h->flags + 1, 0, sizeof(int32_t), s));
+    h->launches += launch_csr_build(ids, routes, h->cfg.experts, h->seg, route_idx, h->csr_scratch, h->flags + 1, h->ctx(s));
+    h->launches += launch_ep_pack((const __nv_bfloat16*)x_bf16, ids, weights, route_idx, h->seg, tokens, h->cfg.top_k,
+                                  h->cfg.hidden, h->cfg.experts, ep_size, (__nv_bfloat16*)send_x, send_expert,
+                                  send_weight, counts, h->ctx(s));
+    CU(h, cudaGetLastError());
+    return FTM_OK;
+}
+
+FTM_API int ftm_ep_combine(ftm_handle* h, const void* y, int y_dtype, const int32_t* route_idx, const float* shared,
+                           const float* se_gate, int32_t tokens, void* out, int out_dtype, void* stream) {
+    if (!h) return FTM_ERR_BAD;
+    std::lock_guard<std::mutex> lk(h->mu);
+    if (!y || !route_idx || !out || (shared && !se_gate)) return fail(h, FTM_ERR_BAD, "moe: ep_combine: null buffer");
+    if (tokens <= 0 || tokens > h->cfg.max_tokens)
+        return fail(h, FTM_ERR_BAD, "moe: ep_combine: %d tokens (max_tokens %d)", tokens, h->cfg.max_tokens);
+    if ((y_dtype != FTM_BF16 && y_dtype != FTM_F32) || (out_dtype != FTM_BF16 && out_dtype != FTM_F32))
+        return fail(h, FTM_ERR_BAD, "moe: ep_combine: dtypes %d -> %d", y_dtype, out_dtype);
+    h->launches += launch_ep_combine(y, y_dtype, route_idx, h->route_expert, tokens, h->cfg.top_k, h->cfg.hidden, shared,
+                                     se_gate, out, out_dtype, h->ctx(pick(h, stream)));
+    CU(h, cudaGetLastError());
+    return FTM_OK;
+}
 
 // ---- shared expert, combine, whole block ----------------------------------------------------
 

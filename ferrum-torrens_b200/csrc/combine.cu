@@ -55,6 +55,73 @@ __global__ void cast_to_bf16_kernel(const void* __restrict__ src, int src_dtype,
     if (i < n) dst[i] = __float2bfloat16_rn(load_act(src, src_dtype, i));
 }
 
+// ---- expert-parallel dispatch / combine ----------------------------------------------------
+// pack: position i of the send buffers takes route r = route_idx[i] (routes sorted by global expert
+// id, hence by owning rank): the token's activation row, the expert id and the route weight
+__global__ void ep_pack_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ ids,
+                               const float* __restrict__ weights, const int32_t* __restrict__ route_idx, int routes,
+                               int top_k, int H, __nv_bfloat16* __restrict__ send_x, int32_t* __restrict__ send_expert,
+                               float* __restrict__ send_weight) {
+    const int i = blockIdx.x;
+    const int r = route_idx[i];
+    const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)(r / top_k) * H);
+    uint4* dst = reinterpret_cast<uint4*>(send_x + (size_t)i * H);
+    for (int c = threadIdx.x; c < H / 8; c += blockDim.x) dst[c] = src[c];
+    if (threadIdx.x == 0) {
+        send_expert[i] = ids[r];
+        send_weight[i] = weights[r];
+    }
+}
+
+// routes per owning rank from the per-expert prefix: rank p owns experts [p*per, (p+1)*per)
+__global__ void ep_rank_counts_kernel(const int32_t* __restrict__ seg, int experts, int ranks,
+                                      int32_t* __restrict__ counts) {
+    const int p = threadIdx.x;
+    if (p < ranks) {
+        const int per = experts / ranks;
+        counts[p] = seg[(p + 1) * per] - seg[p * per];
+    }
+}
+
+__global__ void ep_invert_kernel(const int32_t* __restrict__ route_idx, int routes, int32_t* __restrict__ pos_of_route) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < routes) pos_of_route[route_idx[i]] = i;
+}
+
+// out[t] = se_gate[t] * shared[t] + sum_j y[pos_of_route[t*k + j]]   (weights were applied by the owner)
+__global__ void ep_combine_kernel(const void* __restrict__ y, int y_dtype, const int32_t* __restrict__ pos_of_route,
+                                  int top_k, int H, const float* __restrict__ shared, const float* __restrict__ se_gate,
+                                  void* __restrict__ out, int out_dtype) {
+    const int t = blockIdx.y;
+    const int d = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (d >= H) return;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (shared) {
+        const float g = se_gate[t];
+        const float4 sv = *reinterpret_cast<const float4*>(shared + (size_t)t * H + d);
+        acc = make_float4(sv.x * g, sv.y * g, sv.z * g, sv.w * g);
+    }
+    for (int j = 0; j < top_k; j++) {
+        const size_t row = (size_t)pos_of_route[t * top_k + j] * H + d;
+        if (y_dtype == 0) {
+            const uint2 pk = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(y) + row);
+            const float2 a = bf16x2_to_f32(pk.x), b = bf16x2_to_f32(pk.y);
+            acc.x += a.x; acc.y += a.y; acc.z += b.x; acc.w += b.y;
+        } else {
+            const float4 v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(y) + row);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+    }
+    const size_t o = (size_t)t * H + d;
+    if (out_dtype == 0) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+        *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(out) + o) =
+            make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+    } else {
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + o) = acc;
+    }
+}
+
 }  // namespace
 
 int launch_sum_routes(const float* yroute, int tokens, int top_k, int hidden, const float* shared,
@@ -82,6 +149,30 @@ int launch_cast_to_bf16(const void* src, int src_dtype, size_t n, __nv_bfloat16*
     cast_to_bf16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, c.s>>>(src, src_dtype, n, dst);
     c.end();
     return 1;
+}
+
+int launch_ep_pack(const __nv_bfloat16* x, const int32_t* ids, const float* weights, const int32_t* route_idx,
+                   const int32_t* seg, int tokens, int top_k, int hidden, int experts, int ranks,
+                   __nv_bfloat16* send_x, int32_t* send_expert, float* send_weight, int32_t* counts, const Ctx& c) {
+    const int routes = tokens * top_k;
+    c.begin(K_EP_PACK);
+    ep_pack_kernel<<<routes, 128, 0, c.s>>>(x, ids, weights, route_idx, routes, top_k, hidden, send_x, send_expert,
+                                           send_weight);
+    ep_rank_counts_kernel<<<1, 32, 0, c.s>>>(seg, experts, ranks, counts);
+    c.end();
+    return 2;
+}
+
+int launch_ep_combine(const void* y, int y_dtype, const int32_t* route_idx, int32_t* pos_scratch, int tokens,
+                      int top_k, int hidden, const float* shared, const float* se_gate, void* out, int out_dtype,
+                      const Ctx& c) {
+    const int routes = tokens * top_k;
+    c.begin(K_EP_COMBINE);
+    ep_invert_kernel<<<(routes + 255) / 256, 256, 0, c.s>>>(route_idx, routes, pos_scratch);
+    dim3 grid((hidden / 4 + 127) / 128, tokens);
+    ep_combine_kernel<<<grid, 128, 0, c.s>>>(y, y_dtype, pos_scratch, top_k, hidden, shared, se_gate, out, out_dtype);
+    c.end();
+    return 2;
 }
 
 }  // namespace ftm

@@ -22,6 +22,8 @@ enum Kind {
     K_GROUPED_DOWN,
     K_PERMUTE_ACT,
     K_DECODE_PLAN,
+    K_EP_PACK,
+    K_EP_COMBINE,
     K_NUM_KINDS
 };
 
@@ -95,6 +97,12 @@ int launch_sum_routes(const float* yroute, int tokens, int top_k, int hidden, co
                       const float* se_gate, void* out, int out_dtype, const Ctx& c);
 int launch_combine(const void* routed, int routed_dtype, const float* shared, const float* se_gate,
                    int tokens, int hidden, void* out, int out_dtype, const Ctx& c);
+int launch_ep_pack(const __nv_bfloat16* x, const int32_t* ids, const float* weights, const int32_t* route_idx,
+                   const int32_t* seg, int tokens, int top_k, int hidden, int experts, int ranks,
+                   __nv_bfloat16* send_x, int32_t* send_expert, float* send_weight, int32_t* counts, const Ctx& c);
+int launch_ep_combine(const void* y, int y_dtype, const int32_t* route_idx, int32_t* pos_scratch, int tokens,
+                      int top_k, int hidden, const float* shared, const float* se_gate, void* out, int out_dtype,
+                      const Ctx& c);
 int launch_cast_to_bf16(const void* src, int src_dtype, size_t n, __nv_bfloat16* dst, const Ctx& c);
 
 }  // namespace ftm

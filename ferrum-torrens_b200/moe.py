@@ -409,6 +409,34 @@ class B200MoE:
                                           _dev(se_gate, "se_gate"), tokens, _dev(out, "out"), _dtype_code(out),
                                           _stream_ptr(stream)))
 
+    def ep_pack(self, x, ids, weights, ep_size: int, stream=None):
+        """Sort this rank's routes by owning rank / expert and fill the all-to-all send buffers.
+        Returns (send_x [R,H] bf16, send_expert [R] i32, send_weight [R] f32, route_idx [R] i32, counts [n] i32)."""
+        torch = _torch()
+        tokens = x.numel() // self.shapes.hidden
+        r = tokens * self.top_k
+        dev = x.device
+        send_x = torch.empty((r, self.shapes.hidden), dtype=torch.bfloat16, device=dev)
+        send_e = torch.empty((r,), dtype=torch.int32, device=dev)
+        send_w = torch.empty((r,), dtype=torch.float32, device=dev)
+        route_idx = torch.empty((r,), dtype=torch.int32, device=dev)
+        counts = torch.empty((ep_size,), dtype=torch.int32, device=dev)
+        if x.dtype != torch.bfloat16 or ids.dtype != torch.int32 or weights.dtype != torch.float32:
+            raise bad("ep_pack takes bf16 activations, i32 ids and f32 weights")
+        self._check(self._lib.ftm_ep_pack(self._h, _dev(x, "x"), _dev(ids, "ids"), _dev(weights, "weights"), tokens,
+                                          ep_size, _dev(send_x, "send_x"), _dev(send_e, "send_e"), _dev(send_w, "send_w"),
+                                          _dev(route_idx, "route_idx"), _dev(counts, "counts"), _stream_ptr(stream)))
+        return send_x, send_e, send_w, route_idx, counts
+
+    def ep_combine(self, y, route_idx, shared, se_gate, out, stream=None):
+        """out[t] = se_gate[t] * shared[t] + sum_j y[position of route t*k + j] (weights applied by the owner)."""
+        tokens = out.numel() // self.shapes.hidden
+        null = C.c_void_p(0)
+        self._check(self._lib.ftm_ep_combine(self._h, _dev(y, "y"), _dtype_code(y), _dev(route_idx, "route_idx"),
+                                             _dev(shared, "shared") if shared is not None else null,
+                                             _dev(se_gate, "se_gate") if se_gate is not None else null, tokens,
+                                             _dev(out, "out"), _dtype_code(out), _stream_ptr(stream)))
+
     def moe_block(self, layer: int, x, gate_w, sh_gate_up, sh_down, sh_gate, out, *, ids_out=None, weights_out=None,
                   path: int = L.PATH_AUTO, stream=None):
         """The whole block: router, routed experts, shared expert, combine (moe_parts)."""

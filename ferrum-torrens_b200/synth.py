@@ -107,9 +107,10 @@ def make_x(seed: int, tokens: int, hidden: int, biased: bool = False) -> np.ndar
 
 # ---- device-side generation for the benchmark --------------------------------------------------
 
-def fill_banks_on_device(moe, layer: int, seed: int, experts: int | None = None, slot0: int = 0, chunk: int = 64):
-    """Draws every expert of `layer` straight into the adapter's banks (slot = slot0 + expert) and
-    marks them resident.  Same distributions as make_layer."""
+def fill_banks_on_device(moe, layer: int, seed: int, experts: int | None = None, slot0: int = 0, chunk: int = 64,
+                         expert0: int = 0):
+    """Draws `experts` experts of `layer` (ids expert0, expert0 + 1, ..) straight into the adapter's banks
+    (slot = slot0 + i) and marks them resident.  Same distributions as make_layer."""
     import torch
     experts = experts if experts is not None else moe.experts
     g = torch.Generator(device=f"cuda:{moe.device}").manual_seed(seed)
@@ -128,7 +129,7 @@ def fill_banks_on_device(moe, layer: int, seed: int, experts: int | None = None,
                 part.view(torch.int16).fill_(0x3C00)
     torch.cuda.synchronize()
     for e in range(experts):
-        moe.adopt(layer, e, slot0 + e)
+        moe.adopt(layer, expert0 + e, slot0 + e)
 
 
 def device_dense_weights(seed: int, device, hidden: int = 2048, experts: int = 256, shared_inter: int = 512,

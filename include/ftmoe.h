@@ -237,6 +237,23 @@ FTM_API int ftm_profile_read(ftm_handle* h, int kind, double* total_ms, uint64_t
 /* name of kernel kind 0, 1, ..; NULL past the last kind */
 FTM_API const char* ftm_profile_kind_name(int kind);
 
+/* ---- expert parallelism (no counterpart in the reference, which is single-GPU: README.md:132) ------
+ * The layer is split over ep_size GPUs, rank p owning experts [p*E/n, (p+1)*E/n) of every layer.
+ * ftm_ep_pack sorts this rank's T*top_k routes by global expert id (hence by owning rank, ascending
+ * route id inside an expert: the CSR order) and fills the send buffers: send_x [R, hidden] bf16 (the
+ * token's row), send_expert [R] (global expert id), send_weight [R], route_idx [R] (the route at each
+ * position) and counts [ep_size] (routes per owning rank), all device memory.  After the all-to-all
+ * the owner runs ftm_moe_layer_staged on a handle created with top_k = 1 (one received route = one
+ * token, ids = the received global expert ids, only its own experts resident) and sends the weighted
+ * rows back.  ftm_ep_combine is the fused weighted un-permute + gated shared-expert add:
+ * out[t] = se_gate[t] * shared[t] + sum_j y[position of route t*top_k + j]; y is [R, hidden] bf16 or
+ * f32 in send order; shared may be NULL.  Both asynchronous. */
+FTM_API int ftm_ep_pack(ftm_handle* h, const void* x_bf16, const int32_t* ids, const float* weights, int32_t tokens,
+                        int32_t ep_size, void* send_x, int32_t* send_expert, float* send_weight, int32_t* route_idx,
+                        int32_t* counts, void* stream);
+FTM_API int ftm_ep_combine(ftm_handle* h, const void* y, int y_dtype, const int32_t* route_idx, const float* shared,
+                           const float* se_gate, int32_t tokens, void* out, int out_dtype, void* stream);
+
 /* number of this library's kernels launched on h since creation (a diagnostics counter) */
 FTM_API uint64_t ftm_kernel_launches(const ftm_handle* h);
 

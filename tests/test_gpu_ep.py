@@ -1,0 +1,80 @@
+"""Expert parallelism on real GPUs (needs at least two): the n-rank result equals the single-GPU result
+on the same seeded inputs.  Run by hand with `gpurun --gpus 2`; skipped on a one-GPU box."""
+import importlib
+import os
+import socket
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+pkg = importlib.import_module("ferrum-torrens_b200")
+
+H, I, E, K, SI = 2048, 512, 32, 8, 512
+
+
+def _bf16(bits, dev):
+    return torch.from_numpy(np.ascontiguousarray(bits).view(np.int16)).to(dev).view(torch.bfloat16)
+
+
+def _worker(rank, world, port, tokens, q):
+    import torch.distributed as dist
+    ep = importlib.import_module("ferrum-torrens_b200.ep")
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device(f"cuda:{rank}")
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        lay = pkg.synth.make_layer(77, hidden=H, inter=I, experts=E, top_k=K, shared_inter=SI)
+        xb = pkg.synth.make_x(500 + rank, tokens, H)
+        be = ep.LibBackend(rank, rank, world, pkg.ExpertShapes(H, I), experts=E, layers=1, top_k=K, shared_inter=SI,
+                           max_tokens=tokens)
+        for e in range(E):
+            if be.owned(e):
+                be.load_expert(0, e, lay.fields(e))
+        layer = ep.ExpertParallelMoE(be, world)
+        out = torch.empty((tokens, H), dtype=torch.float32, device=dev)
+        w = [_bf16(a, dev) for a in (lay.gate_w, lay.sh_gate_up, lay.sh_down, lay.sh_gate)]
+        ids, wts = layer.forward(0, _bf16(xb, dev), *w, out)
+        be.front.sync_status()
+        be.owner.sync_status()
+        # the same tokens through one adapter that holds every expert
+        solo = pkg.B200MoE(rank, pkg.ExpertShapes(H, I), E, experts=E, layers=1, top_k=K, shared_inter=SI,
+                           max_tokens=tokens)
+        for e in range(E):
+            solo.load(0, e, e, lay.fields(e))
+        want = torch.empty((tokens, H), dtype=torch.float32, device=dev)
+        want_ids = torch.empty((tokens, K), dtype=torch.int32, device=dev)
+        solo.moe_block(0, _bf16(xb, dev), *w, want, ids_out=want_ids)
+        solo.sync_status()
+        same_ids = bool(torch.equal(ids, want_ids))
+        rel = float((out - want).norm() / want.norm())
+        q.put((rank, same_ids, rel))
+        solo.close()
+        be.close()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("tokens", [16, 700])
+def test_two_gpu_expert_parallel_matches_single_gpu(tokens):
+    import torch.multiprocessing as mp
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, tokens, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    for rank, same_ids, rel in res:
+        assert same_ids
+        # the owner returns bf16 rows (half the NVLink bytes); one rounding per route
+        assert rel < 5e-3, (rank, rel)
