@@ -384,10 +384,35 @@ def run_ep(args, pkg, dev, world, rank, local):
     total_ms = float(ms.item())
     clocks = sampler.stop() if rank == 0 else None
 
-    # phase breakdown of a few steps: time between the marks, max over ranks
+    # end to end: pinned host activations in, the result out, every step
+    x_host = [x.cpu().pin_memory() for x in xs]
+    x_stage = torch.empty_like(xs[0])
+    out_host = torch.empty((T, HIDDEN), dtype=torch.bfloat16).pin_memory()
+
+    def step_e2e(i):
+        l = i % nlayers
+        x_stage.copy_(x_host[l], non_blocking=True)
+        g, su, sd, sg = dense[l]
+        layer.forward(l, x_stage, g, su, sd, sg, out)
+        out_host.copy_(out, non_blocking=True)
+
+    for i in range(2):
+        step_e2e(i)
+    barrier()
+    e0.record()
+    for i in range(K):
+        step_e2e(W + i)
+    e1.record()
+    barrier()
+    ms2 = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    dist.all_reduce(ms2, op=dist.ReduceOp.MAX)
+    e2e = {"value": world * T * K / (float(ms2.item()) * 1e-3), "unit": UNIT, "h2d_bytes_per_step": T * HIDDEN * 2,
+           "d2h_bytes_per_step": T * HIDDEN * 2}
+
+    # phase breakdown of a few steps: time between the marks, median over steps, max over ranks
     names = ["packed", "dispatched", "computed", "returned", "combined"]
-    acc = torch.zeros(len(names), device=dev)
-    reps = min(K, 5)
+    reps = max(3, min(K, 7))
+    samples = torch.zeros((reps, len(names)), device=dev)
     for i in range(reps):
         evs = {}
         start = torch.cuda.Event(enable_timing=True)
@@ -400,9 +425,9 @@ def run_ep(args, pkg, dev, world, rank, local):
         torch.cuda.synchronize()
         prev = start
         for j, n in enumerate(names):
-            acc[j] += prev.elapsed_time(evs[n])
+            samples[i, j] = prev.elapsed_time(evs[n])
             prev = evs[n]
-    acc /= reps
+    acc = samples.median(dim=0).values
     dist.all_reduce(acc, op=dist.ReduceOp.MAX)
     phases = {n: float(v) for n, v in zip(["router_shared_pack_ms", "dispatch_a2a_ms", "experts_ms", "return_a2a_ms",
                                            "combine_ms"], acc.tolist())}
@@ -423,7 +448,7 @@ def run_ep(args, pkg, dev, world, rank, local):
                    "exposed_comm_ms": phases["dispatch_a2a_ms"] + phases["return_a2a_ms"],
                    "max_routes_sent_off_rank": float(sent.item()),
                    "nvlink_bytes_each_way_per_gpu": float(sent.item()) * HIDDEN * 2},
-            "e2e": None, "roofline": None,
+            "e2e": e2e, "roofline": None,
         }
         print(json.dumps(line))
     be.close()

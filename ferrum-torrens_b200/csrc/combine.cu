@@ -16,8 +16,8 @@ namespace {
 __global__ void sum_routes_kernel(const float* __restrict__ yroute, int tokens, int top_k, int H,
                                   const float* __restrict__ shared, const float* __restrict__ se_gate,
                                   void* __restrict__ out, int out_dtype) {
-    const int t = blockIdx.y;
-    const int d = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    const int t = blockIdx.x;  // tokens on x: the owner side of expert parallelism runs > 65535 rows
+    const int d = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
     if (d >= H) return;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     if (shared) {
@@ -92,8 +92,8 @@ __global__ void ep_invert_kernel(const int32_t* __restrict__ route_idx, int rout
 __global__ void ep_combine_kernel(const void* __restrict__ y, int y_dtype, const int32_t* __restrict__ pos_of_route,
                                   int top_k, int H, const float* __restrict__ shared, const float* __restrict__ se_gate,
                                   void* __restrict__ out, int out_dtype) {
-    const int t = blockIdx.y;
-    const int d = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    const int t = blockIdx.x;
+    const int d = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
     if (d >= H) return;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     if (shared) {
@@ -127,7 +127,7 @@ __global__ void ep_combine_kernel(const void* __restrict__ y, int y_dtype, const
 int launch_sum_routes(const float* yroute, int tokens, int top_k, int hidden, const float* shared,
                       const float* se_gate, void* out, int out_dtype, const Ctx& c) {
     int threads = 128;
-    dim3 grid((hidden / 4 + threads - 1) / threads, tokens);
+    dim3 grid(tokens, (hidden / 4 + threads - 1) / threads);
     c.begin(K_SUM_ROUTES);
     sum_routes_kernel<<<grid, threads, 0, c.s>>>(yroute, tokens, top_k, hidden, shared, se_gate, out, out_dtype);
     c.end();
@@ -169,7 +169,7 @@ int launch_ep_combine(const void* y, int y_dtype, const int32_t* route_idx, int3
     const int routes = tokens * top_k;
     c.begin(K_EP_COMBINE);
     ep_invert_kernel<<<(routes + 255) / 256, 256, 0, c.s>>>(route_idx, routes, pos_scratch);
-    dim3 grid((hidden / 4 + 127) / 128, tokens);
+    dim3 grid(tokens, (hidden / 4 + 127) / 128);
     ep_combine_kernel<<<grid, 128, 0, c.s>>>(y, y_dtype, pos_scratch, top_k, hidden, shared, se_gate, out, out_dtype);
     c.end();
     return 2;
