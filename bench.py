@@ -277,10 +277,13 @@ def run_b200(args):
     gate_kind = "expert_gate_up" if "expert_gate_up" in prof else "grouped_gate_up"
     g_ms, g_n = prof[gate_kind]
     gu_bytes = U * GATE_UP_BYTES + T * HIDDEN * 2
+    # DRAM traffic per algorithmic byte of this kernel from the ncu capture summarised in
+    # profiles/expert_mma_gate_up_T64.md (dram__bytes_read + dram__bytes_write over one launch)
+    NCU_TRAFFIC_RATIO = 1.042
     achieved = gu_bytes / (g_ms / g_n * 1e-3) / 1e9
     roofline = {"bound": "hbm", "kernel": gate_kind, "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                 "frac": achieved / pk["hbm_gbs"], "peak_source": pk["which"], "frac_of_nominal_8000": achieved / 8000.0,
-                "traffic": None, "distinct_experts": U, "bytes_per_launch": gu_bytes,
+                "traffic": NCU_TRAFFIC_RATIO * gu_bytes, "distinct_experts": U, "bytes_per_launch": gu_bytes,
                 "us_per_launch": g_ms / g_n * 1e3,
                 "kernels": {k: {"us_per_launch": ms / n * 1e3, "launches": n} for k, (ms, n) in prof.items()}}
     if "expert_down" in prof:

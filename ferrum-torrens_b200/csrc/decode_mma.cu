@@ -563,8 +563,8 @@ __global__ void __launch_bounds__(Cfg<GATE_UP, K_, NT>::kThreads, OCC) expert_mm
                     acc[0][0][0] = __uint_as_float(plo.x ^ phi.w);
                 }
                 n_done++;
-                // the buffer has been read: order those reads before the async writes that refill it
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                // every lane's reads of the buffer have returned (their values fed the MMAs above), so the
+                // refill may be issued: a write-after-read across the proxies needs no fence
                 __syncwarp();
                 issue_next();
             }
