@@ -27,7 +27,7 @@ thread_local std::string g_create_error;
 const char* const kKindNames[K_NUM_KINDS] = {
     "router_logits", "router_topk", "slot_rewrite", "csr_build", "expert_gate_up", "expert_down", "sum_routes",
     "shared_phase1", "shared_phase2", "cast_bf16",   "combine",  "grouped_gate_up", "grouped_down",
-    "permute_act",   "decode_plan",   "ep_pack",         "ep_combine"};
+    "permute_act",   "decode_plan",   "ep_pack",         "ep_combine", "prefill_rescale"};
 
 }  // namespace
 
@@ -111,6 +111,8 @@ struct ftm_handle {
     float *ic2s = nullptr, *shared_out = nullptr, *se_gate = nullptr, *routed_f32 = nullptr;
     __half* xh = nullptr;
     float *tok_scale = nullptr, *ic2p = nullptr;
+    __half* xg = nullptr;        // [R, H] sorted activations of the grouped GEMM
+    float *row_scale = nullptr, *row_scale2 = nullptr;
     int4* groups = nullptr;
     int32_t *sorted_route = nullptr, *n_groups = nullptr;
     int sm_count = 148;
@@ -213,6 +215,9 @@ int check_tokens(const ftm_handle* h, int64_t tokens, int top_k) {
 
 int stage_x(ftm_handle* h, const void* x, int x_dtype, int tokens, const __nv_bfloat16** out, cudaStream_t s);
 
+// above this many routes FTM_PATH_AUTO takes the tcgen05 grouped GEMM instead of the decode kernels
+constexpr int kGroupedMinRoutes = 2048;
+
 // routed experts -> out (routed sum only when shared == nullptr).  The routes are slot ids in
 // h->route_slot, or, when `expert_ids` is set, dense expert ids of `layer` still to be mapped.
 // `join`, when set, is waited on just before the pass that reads `shared`.
@@ -221,6 +226,22 @@ int run_routed(ftm_handle* h, const void* x, int x_dtype, const void* expert_ids
                void* out, int out_dtype, int path, cudaStream_t s) {
     BankView b = bank_view(h);
     const int routes = tokens * h->cfg.top_k;
+    // large batches (or FTM_PATH_GROUPED): the tcgen05 grouped GEMM, which also does the combine
+    if ((path == FTM_PATH_GROUPED || (path == FTM_PATH_AUTO && routes > kGroupedMinRoutes)) &&
+        prefill_umma_supported(h->cfg.hidden, h->cfg.inter, h->cfg.slots, h->cfg.experts, expert_ids != nullptr)) {
+        PrefillScratch sc{};
+        sc.route_bin = h->route_expert; sc.seg = h->seg; sc.route_idx = h->sorted_route; sc.pos_of_route = h->route_idx;
+        sc.csr_scratch = h->csr_scratch; sc.csr_flag = h->flags + 3; sc.groups = h->groups; sc.n_groups = h->n_groups;
+        sc.xg = h->xg; sc.row_scale = h->row_scale; sc.ic2 = h->ic2p; sc.ic2h = reinterpret_cast<__half*>(h->ic2);
+        sc.row_scale2 = h->row_scale2; sc.y = h->yroute; sc.err = h->flags + 2;
+        DecodeRoutes rt{expert_ids ? nullptr : h->route_slot, expert_ids, ids_dtype, layer, h->cfg.experts,
+                        (int)h->slot_for_id.size(), h->d_slot_for_id, h->route_slot, h->flags + 1};
+        int n = launch_prefill_umma(b, x, x_dtype, rt, weights, tokens, h->cfg.top_k, sc, h->sm_count, shared, se_gate, join,
+                                    out, out_dtype, h->ctx(s));
+        if (n < 0) return fail(h, FTM_ERR_CUDA, "moe: driver: cuTensorMapEncodeTiled failed");
+        h->launches += n;
+        return FTM_OK;
+    }
     if (path != FTM_PATH_SCALAR &&
         decode_mma_supported(h->cfg.hidden, h->cfg.inter, routes, h->cfg.slots, h->cfg.experts, expert_ids != nullptr)) {
         DecodeScratch sc{h->ic2p, h->groups, h->sorted_route, h->n_groups, h->yroute, h->flags + 2,
@@ -339,6 +360,9 @@ FTM_API int ftm_create(const ftm_config* c, void* stream, ftm_handle** out) {
     A(dev_alloc(hp, &h->groups, R));
     A(dev_alloc(hp, &h->sorted_route, R));
     A(dev_alloc(hp, &h->n_groups, 1));
+    A(dev_alloc(hp, &h->xg, R * H));
+    A(dev_alloc(hp, &h->row_scale, R));
+    A(dev_alloc(hp, &h->row_scale2, R));
     cudaDeviceGetAttribute(&h->sm_count, cudaDevAttrMultiProcessorCount, c->ordinal);
     (void)bins;
     if (rc == FTM_OK) {

@@ -661,6 +661,14 @@ __global__ void zero_missing_routes_kernel(const int32_t* __restrict__ route_slo
 
 }  // namespace
 
+int launch_groups_from_csr(const int32_t* seg, int bins, const int32_t* slot_of_bin, int slots, int group,
+                           int4* groups, int32_t* n_groups, const Ctx& c) {
+    c.begin(K_DECODE_PLAN);
+    groups_from_csr_kernel<<<1, 1024, 0, c.s>>>(seg, bins, slot_of_bin, slots, group, groups, n_groups);
+    c.end();
+    return 1;
+}
+
 size_t decode_plan_smem(int slots) { return (size_t)3 * slots * sizeof(int); }
 
 bool decode_mma_supported(int hidden, int inter, int routes, int slots, int experts, bool have_expert_ids) {

@@ -24,6 +24,7 @@ enum Kind {
     K_DECODE_PLAN,
     K_EP_PACK,
     K_EP_COMBINE,
+    K_PREFILL_RESCALE,
     K_NUM_KINDS
 };
 
@@ -85,6 +86,33 @@ bool decode_mma_supported(int hidden, int inter, int routes, int slots, int expe
 int launch_decode_mma(const BankView& b, const void* x, int x_dtype, const DecodeRoutes& rt,
                       const float* route_weight, int tokens, int top_k, DecodeScratch sc, int sm_count,
                       const Ctx& c);
+
+int launch_groups_from_csr(const int32_t* seg, int bins, const int32_t* slot_of_bin, int slots, int group,
+                           int4* groups, int32_t* n_groups, const Ctx& c);
+
+// prefill_umma.cu: grouped GEMM on tcgen05 tensor cores for large batches
+struct PrefillScratch {
+    int32_t* route_bin;      // [routes]
+    int32_t* seg;            // [bins + 1]
+    int32_t* route_idx;      // [routes] sorted position -> route
+    int32_t* pos_of_route;   // [routes]
+    int32_t* csr_scratch;
+    int32_t* csr_flag;
+    int4* groups;            // [routes / 1 ..] (slot, first sorted row, rows, 0)
+    int32_t* n_groups;
+    __half* xg;              // [routes, hidden] sorted activations, scaled f16
+    float* row_scale;        // [routes]
+    float* ic2;              // [routes, inter] f32
+    __half* ic2h;            // [routes, inter]
+    float* row_scale2;       // [routes]
+    void* y;                 // [routes, hidden] weighted expert outputs, sorted rows: bf16, or f32 for f32 outputs
+    int32_t* err;
+};
+bool prefill_umma_supported(int hidden, int inter, int slots, int experts, bool have_expert_ids);
+int launch_prefill_umma(const BankView& b, const void* x, int x_dtype, const DecodeRoutes& rt,
+                        const float* route_weight, int tokens, int top_k, PrefillScratch sc, int sm_count,
+                        const float* shared, const float* se_gate, cudaEvent_t join, void* out, int out_dtype,
+                        const Ctx& c);
 
 // shared_expert.cu
 int launch_shared_expert(const __nv_bfloat16* x, int tokens, int hidden, int shared_inter,
