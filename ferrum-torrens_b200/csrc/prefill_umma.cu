@@ -37,7 +37,7 @@ constexpr int kStepK = 64;    // k per pipeline step: one 128-byte swizzle atom 
 constexpr int kMaxTokTiles = 2;               // <= 256 tokens per pass
 constexpr int kAStages = 3;
 constexpr int kTileBytes = kTileM * kStepK * 2;  // 16 KiB, also the B tile
-constexpr int kThreads = 192;
+constexpr int kThreads = 512;
 constexpr uint32_t kSpin = 1u << 20;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -216,9 +216,7 @@ prefill_rescale_kernel(const float* __restrict__ ic2, const int32_t* __restrict_
 
 // ---- the grouped GEMM ------------------------------------------------------------------------
 struct UmmaArgs {
-    const uint8_t* packed;     // bank base [slots, N, K/2]
-    const uint8_t* scale;      // [slots, N, K/16]
-    const uint16_t* global;    // [slots, N]
+    const uint16_t* global;    // [slots, N] f16 row globals
     const int4* groups;        // (slot, first sorted row, rows <= 256, 0)
     const int32_t* n_groups;
     const int32_t* route_idx;  // sorted position -> route
@@ -231,24 +229,38 @@ struct UmmaArgs {
     int N;                     // rows of the weight matrix (2 * inter or hidden)
 };
 
+// warp roles of the GEMM CTA (16 warps)
+constexpr int kWarpActTma = 0, kWarpMma = 1, kWarpRawTma = 2, kWarpEpi0 = 4, kWarpDeq0 = 8;
+constexpr int kDeqThreads = 256;
+constexpr int kRawStages = 5;
+constexpr int kRawPackedBytes = kTileN * 64;   // one chunk of 128 k: 128 rows x 64 bytes
+constexpr int kRawScaleBytes = kTileN * 16;    // 128 rows x 16 scale bytes (256 k: the chunk's half is used)
+constexpr int kRawStageBytes = kRawPackedBytes + kRawScaleBytes;
+constexpr int kAccStages = 2;                  // accumulator sets in tensor memory (2 x 256 columns)
+
 template <bool GATE_UP, int K>
 __global__ void __launch_bounds__(kThreads, 1)
-umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, UmmaArgs a) {
+umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_packed,
+                         const __grid_constant__ CUtensorMap tmap_scale, UmmaArgs a) {
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment for the swizzled tiles
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* const a_tiles = smem;                                                  // [kAStages][kMaxTokTiles][16 KiB]
     uint8_t* const b_tiles = a_tiles + kAStages * kMaxTokTiles * kTileBytes;        // [2 buffers][2 k-steps][16 KiB]
-    float* const s_glob2 = reinterpret_cast<float*>(b_tiles + 4 * kTileBytes);       // [2][128] row globals, by unit parity
-    uint64_t* const bars = reinterpret_cast<uint64_t*>(s_glob2 + 2 * kTileN);
-    uint32_t* const s_tmem = reinterpret_cast<uint32_t*>(bars + 16);
+    uint8_t* const raw_ring = b_tiles + 4 * kTileBytes;                              // [kRawStages][packed | scales]
+    float* const s_glob = reinterpret_cast<float*>(raw_ring + kRawStages * kRawStageBytes);  // [4 epilogue warps][128]
+    uint64_t* const bars = reinterpret_cast<uint64_t*>(s_glob + 4 * kTileN);
+    uint32_t* const s_tmem = reinterpret_cast<uint32_t*>(bars + 32);
     volatile int* const s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
     const uint32_t bar0 = smem_u32(bars);
     auto A_FULL = [&](int s) { return bar0 + 8u * s; };
     auto A_EMPTY = [&](int s) { return bar0 + 8u * (3 + s); };
     auto B_READY = [&](int s) { return bar0 + 8u * (6 + s); };
     auto B_FREE = [&](int s) { return bar0 + 8u * (8 + s); };
-    const uint32_t TMEM_FULL = bar0 + 8u * 10, TMEM_EMPTY = bar0 + 8u * 11;
+    auto ACC_FULL = [&](int s) { return bar0 + 8u * (10 + s); };
+    auto ACC_EMPTY = [&](int s) { return bar0 + 8u * (12 + s); };
+    auto RAW_FULL = [&](int s) { return bar0 + 8u * (14 + s); };
+    auto RAW_EMPTY = [&](int s) { return bar0 + 8u * (19 + s); };
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     if (threadIdx.x == 0) {
@@ -257,17 +269,21 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, UmmaArgs a)
             mbar_init(A_EMPTY(s), 1);
         }
         for (int s = 0; s < 2; s++) {
-            mbar_init(B_READY(s), 128);
+            mbar_init(B_READY(s), kDeqThreads);
             mbar_init(B_FREE(s), 1);
+            mbar_init(ACC_FULL(s), 1);
+            mbar_init(ACC_EMPTY(s), 128);
         }
-        mbar_init(TMEM_FULL, 1);
-        mbar_init(TMEM_EMPTY, 128);
+        for (int s = 0; s < kRawStages; s++) {
+            mbar_init(RAW_FULL(s), 1);
+            mbar_init(RAW_EMPTY(s), kDeqThreads);
+        }
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {
-        // 256 columns of tensor memory: two accumulator tiles of 128 f32 columns
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 256;" ::"r"(smem_u32(s_tmem)) : "memory");
+    if (warp == kWarpMma) {
+        // all 512 columns of tensor memory: two accumulator sets of two 128-column f32 tiles
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(s_tmem)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -276,35 +292,75 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, UmmaArgs a)
     const uint32_t tmem_base = *s_tmem;
 
     constexpr int kSteps = K / kStepK;
+    constexpr int kChunks = K / 128;
     const int n_tiles = a.N / kTileN;
     const int n_units = *a.n_groups * n_tiles;
+    // tile row n of tile nt -> weight row: gate_up tiles are 64 gate rows followed by the 64 matching up rows
+    auto weight_row = [&](int nt, int n) -> int {
+        if (GATE_UP) return (n < 64) ? nt * 64 + n : a.N / 2 + nt * 64 + (n - 64);
+        return nt * kTileN + n;
+    };
 
-    if (warp == 0) {
-        // ===================== TMA producer ====================================================
+    if (warp == kWarpActTma) {
+        // ===================== activation tiles: TMA, 128-byte swizzle ============================
         if (lane == 0) {
             uint32_t it = 0;
             for (int u = blockIdx.x; u < n_units && !*s_abort; u += gridDim.x) {
                 const int4 grp = a.groups[u / n_tiles];
                 const int ntt = (grp.z + kTileM - 1) / kTileM;
-                for (int ks = 0; ks < kSteps; ks++, it++) {
+                bool ok = true;
+                for (int ks = 0; ks < kSteps && ok; ks++, it++) {
                     const int st = it % kAStages;
-                    if (!mbar_wait(A_EMPTY(st), ((it / kAStages) & 1) ^ 1, s_abort, a.err)) break;
+                    ok = mbar_wait(A_EMPTY(st), ((it / kAStages) & 1) ^ 1, s_abort, a.err);
+                    if (!ok) break;
                     mbar_expect_tx(A_FULL(st), (uint32_t)(ntt * kTileBytes));
                     for (int t = 0; t < ntt; t++)
                         tma_load_2d(smem_u32(a_tiles + (size_t)(st * kMaxTokTiles + t) * kTileBytes), &tmap_a, ks * kStepK,
                                     grp.y + t * kTileM, A_FULL(st));
                 }
+                if (!ok) break;
             }
         }
-    } else if (warp == 1) {
+    } else if (warp == kWarpRawTma) {
+        // ===================== packed weights and block scales: TMA into the raw ring ===============
+        if (lane == 0) {
+            uint32_t it = 0;
+            for (int u = blockIdx.x; u < n_units && !*s_abort; u += gridDim.x) {
+                const int4 grp = a.groups[u / n_tiles];
+                const int nt = u % n_tiles;
+                const int row0 = grp.x * a.N;
+                bool ok = true;
+                for (int c = 0; c < kChunks && ok; c++, it++) {
+                    const int st = it % kRawStages;
+                    ok = mbar_wait(RAW_EMPTY(st), ((it / kRawStages) & 1) ^ 1, s_abort, a.err);
+                    if (!ok) break;
+                    const uint32_t dst = smem_u32(raw_ring + (size_t)st * kRawStageBytes);
+                    mbar_expect_tx(RAW_FULL(st), kRawStageBytes);
+                    if (GATE_UP) {
+                        // boxes of 64 rows: the gate rows, then the matching up rows
+                        tma_load_2d(dst, &tmap_packed, c * 64, row0 + weight_row(nt, 0), RAW_FULL(st));
+                        tma_load_2d(dst + kRawPackedBytes / 2, &tmap_packed, c * 64, row0 + weight_row(nt, 64), RAW_FULL(st));
+                        tma_load_2d(dst + kRawPackedBytes, &tmap_scale, (c >> 1) * 16, row0 + weight_row(nt, 0), RAW_FULL(st));
+                        tma_load_2d(dst + kRawPackedBytes + kRawScaleBytes / 2, &tmap_scale, (c >> 1) * 16,
+                                    row0 + weight_row(nt, 64), RAW_FULL(st));
+                    } else {
+                        tma_load_2d(dst, &tmap_packed, c * 64, row0 + weight_row(nt, 0), RAW_FULL(st));
+                        tma_load_2d(dst + kRawPackedBytes, &tmap_scale, (c >> 1) * 16, row0 + weight_row(nt, 0), RAW_FULL(st));
+                    }
+                }
+                if (!ok) break;
+            }
+        }
+    } else if (warp == kWarpMma) {
         // ===================== MMA issuer ======================================================
         if (lane == 0) {
             uint32_t it = 0, chunk = 0, unit_i = 0;
             for (int u = blockIdx.x; u < n_units && !*s_abort; u += gridDim.x, unit_i++) {
                 const int4 grp = a.groups[u / n_tiles];
                 const int ntt = (grp.z + kTileM - 1) / kTileM;
-                // the previous unit's accumulators must have been read back
-                if (!mbar_wait(TMEM_EMPTY, (unit_i & 1) ^ 1, s_abort, a.err)) break;
+                const int acc = unit_i & 1;
+                // this accumulator set must have been read back (two units ago)
+                if (!mbar_wait(ACC_EMPTY(acc), ((unit_i >> 1) & 1) ^ 1, s_abort, a.err)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 bool ok = true;
                 for (int ks = 0; ks < kSteps && ok; ks++, it++) {
@@ -319,8 +375,8 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, UmmaArgs a)
                         const uint32_t a_addr = smem_u32(a_tiles + (size_t)(st * kMaxTokTiles + t) * kTileBytes);
 #pragma unroll
                         for (int kk = 0; kk < kStepK / 16; kk++)
-                            umma_f16(tmem_base + t * kTileN, umma_desc(a_addr + kk * 32), umma_desc(b_addr + kk * 32),
-                                     (ks > 0 || kk > 0) ? 1u : 0u);
+                            umma_f16(tmem_base + acc * (kMaxTokTiles * kTileN) + t * kTileN, umma_desc(a_addr + kk * 32),
+                                     umma_desc(b_addr + kk * 32), (ks > 0 || kk > 0) ? 1u : 0u);
                     }
                     umma_commit(A_EMPTY(st));            // the activation stage is free once these MMAs retire
                     if (ks & 1) {
@@ -329,40 +385,29 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, UmmaArgs a)
                     }
                 }
                 if (!ok) break;
-                umma_commit(TMEM_FULL);
+                umma_commit(ACC_FULL(acc));
             }
         }
-    } else {
-        // ===================== dequantisers / epilogue (warps 2..5, 128 threads) ==================
-        const int tid = threadIdx.x - 64;              // 0..127
-        const int quarter = warp & 3;                  // TMEM lane quarter this warp may read
-        uint32_t chunk = 0, unit_i = 0;
-        for (int u = blockIdx.x; u < n_units && !*s_abort; u += gridDim.x, unit_i++) {
-            const int4 grp = a.groups[u / n_tiles];
-            const int nt = u % n_tiles;
-            const int ntt = (grp.z + kTileM - 1) / kTileM;
-            const size_t slot_rows = (size_t)grp.x * a.N;
-            // tile row n -> weight row: gate_up tiles are 64 gate rows followed by the 64 matching up rows
-            auto weight_row = [&](int n) -> int {
-                if (GATE_UP) return (n < 64) ? nt * 64 + n : a.N / 2 + nt * 64 + (n - 64);
-                return nt * kTileN + n;
-            };
-            // two copies by unit parity: a warp may still read the previous unit's globals in its epilogue
-            float* const s_glob = s_glob2 + (unit_i & 1) * kTileN;
-            s_glob[tid] = f16_global_to_f32(a.global[slot_rows + weight_row(tid)]);
+    } else if (warp >= kWarpDeq0) {
+        // ===================== dequantisers (8 warps): raw ring -> swizzled f16 B tiles ==============
+        const int tid = threadIdx.x - kWarpDeq0 * 32;   // 0..255
+        uint32_t chunk = 0;
+        for (int u = blockIdx.x; u < n_units && !*s_abort; u += gridDim.x) {
             bool ok = true;
-            for (int c = 0; c < K / 128 && ok; c++, chunk++) {
-                const int buf = chunk & 1;
-                ok = mbar_wait(B_FREE(buf), ((chunk >> 1) & 1) ^ 1, s_abort, a.err);
+            for (int c = 0; c < kChunks && ok; c++, chunk++) {
+                const int buf = chunk & 1, st = chunk % kRawStages;
+                ok = mbar_wait(RAW_FULL(st), (chunk / kRawStages) & 1, s_abort, a.err);
+                if (ok) ok = mbar_wait(B_FREE(buf), ((chunk >> 1) & 1) ^ 1, s_abort, a.err);
                 if (!ok) break;
+                const uint8_t* const rp = raw_ring + (size_t)st * kRawStageBytes;
                 // 128 rows x 4 pieces of 16 bytes (32 k, two scale blocks); four lanes share a row
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const int unit = tid + 128 * i;
+                for (int i = 0; i < 2; i++) {
+                    const int unit = tid + kDeqThreads * i;
                     const int row = unit >> 2, piece = unit & 3;
-                    const size_t wrow = slot_rows + weight_row(row);
-                    const uint4 raw = *reinterpret_cast<const uint4*>(a.packed + wrow * (K / 2) + c * 64 + piece * 16);
-                    const uint16_t sc2 = *reinterpret_cast<const uint16_t*>(a.scale + wrow * (K / 16) + c * 8 + piece * 2);
+                    const uint4 raw = *reinterpret_cast<const uint4*>(rp + row * 64 + piece * 16);
+                    const uint16_t sc2 =
+                        *reinterpret_cast<const uint16_t*>(rp + kRawPackedBytes + row * 16 + (c & 1) * 8 + piece * 2);
                     uint32_t h2;
                     asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(sc2));
                     const uint32_t s0 = __byte_perm(h2, h2, 0x1010), s1 = __byte_perm(h2, h2, 0x3232);
@@ -380,21 +425,37 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, UmmaArgs a)
                         *reinterpret_cast<uint4*>(brow + ((c16 ^ (row & 7)) << 4)) = make_uint4(q[0], q[1], q[2], q[3]);
                     }
                 }
+                mbar_arrive(RAW_EMPTY(st));
                 // generic-proxy writes must be visible to the tensor core's async-proxy reads
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 mbar_arrive(B_READY(buf));
             }
             if (!ok) break;
-
-            // ---- epilogue ----
-            if (!mbar_wait(TMEM_FULL, unit_i & 1, s_abort, a.err)) break;
+        }
+    } else if (warp >= kWarpEpi0) {
+        // ===================== epilogue (warps 4..7: TMEM lane quarters 0..3) =======================
+        const int quarter = warp & 3;
+        float* const my_glob = s_glob + quarter * kTileN;   // private to this warp
+        uint32_t unit_i = 0;
+        for (int u = blockIdx.x; u < n_units && !*s_abort; u += gridDim.x, unit_i++) {
+            const int4 grp = a.groups[u / n_tiles];
+            const int nt = u % n_tiles;
+            const int ntt = (grp.z + kTileM - 1) / kTileM;
+            const int acc = unit_i & 1;
+            __syncwarp();
+#pragma unroll
+            for (int q = 0; q < 4; q++)
+                my_glob[lane + 32 * q] = f16_global_to_f32(a.global[(size_t)grp.x * a.N + weight_row(nt, lane + 32 * q)]);
+            __syncwarp();
+            if (!mbar_wait(ACC_FULL(acc), (unit_i >> 1) & 1, s_abort, a.err)) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             for (int t = 0; t < ntt; t++) {
                 const int row_in_pass = t * kTileM + quarter * 32 + lane;
                 const bool valid = row_in_pass < grp.z;
                 const int pos = grp.y + row_in_pass;
                 const float rs = valid ? a.row_scale[pos] : 0.f;
-                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + t * kTileN;
+                const uint32_t taddr =
+                    tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * (kMaxTokTiles * kTileN) + t * kTileN;
                 if (GATE_UP) {
 #pragma unroll 1
                     for (int c0 = 0; c0 < 64; c0 += 16) {
@@ -406,7 +467,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, UmmaArgs a)
                             float o[16];
 #pragma unroll
                             for (int j = 0; j < 16; j++) {
-                                const float gate = g[j] * s_glob[c0 + j] * rs, upv = up[j] * s_glob[64 + c0 + j] * rs;
+                                const float gate = g[j] * my_glob[c0 + j] * rs, upv = up[j] * my_glob[64 + c0 + j] * rs;
                                 o[j] = (gate / (1.0f + __expf(-gate))) * upv;
                             }
                             float4* dst = reinterpret_cast<float4*>(a.ic2 + (size_t)pos * (a.N / 2) + nt * 64 + c0);
@@ -423,7 +484,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, UmmaArgs a)
                         tmem_ld_wait();
                         if (valid) {
 #pragma unroll
-                            for (int j = 0; j < 16; j++) v[j] = wr * ((v[j] * rs) * s_glob[c0 + j]);
+                            for (int j = 0; j < 16; j++) v[j] = wr * ((v[j] * rs) * my_glob[c0 + j]);
                             const size_t o = (size_t)pos * a.N + nt * kTileN + c0;
                             if (a.y_f32) {
                                 float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(a.y) + o);
@@ -445,18 +506,20 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, UmmaArgs a)
                 }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(TMEM_EMPTY);
+            mbar_arrive(ACC_EMPTY(acc));
         }
     }
     // drain: nobody frees tensor memory while another role may still touch it
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;" ::"r"(tmem_base) : "memory");
+    if (warp == kWarpMma) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
     }
 }
 
-constexpr size_t kUmmaSmem = 1024 + (size_t)(kAStages * kMaxTokTiles + 4) * kTileBytes + 2 * kTileN * 4 + 16 * 8 + 64;
+constexpr size_t kUmmaSmem = 1024 + (size_t)(kAStages * kMaxTokTiles + 4) * kTileBytes + (size_t)kRawStages * kRawStageBytes +
+                             4 * kTileN * 4 + 32 * 8 + 64;
+static_assert(kUmmaSmem <= 227 * 1024, "shared memory of the grouped GEMM CTA");
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -528,6 +591,19 @@ __global__ void prefill_combine_kernel(const void* __restrict__ y, int y_f32, co
     }
 }
 
+// u8 matrix [rows, row_bytes] row-major (packed nibbles or block scales), box = box_bytes x box_rows, no swizzle
+bool make_raw_map(CUtensorMap* map, const void* base, size_t rows, int row_bytes, int box_bytes, int box_rows) {
+    EncodeTiledFn fn = encode_tiled();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
+    cuuint32_t box[2] = {(cuuint32_t)box_bytes, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 }  // namespace
 
 bool prefill_umma_supported(int hidden, int inter, int slots, int experts, bool have_expert_ids) {
@@ -569,8 +645,13 @@ int launch_prefill_umma(const BankView& b, const void* x, int x_dtype, const Dec
     c.end();
     launches++;
 
-    CUtensorMap map_x, map_h;
-    if (!make_act_map(&map_x, sc.xg, (size_t)routes, b.hidden) || !make_act_map(&map_h, sc.ic2h, (size_t)routes, b.inter))
+    CUtensorMap map_x, map_h, map_gp, map_gs, map_dp, map_ds;
+    const size_t gu_rows = (size_t)b.slots * 2 * b.inter, dn_rows = (size_t)b.slots * b.hidden;
+    if (!make_act_map(&map_x, sc.xg, (size_t)routes, b.hidden) || !make_act_map(&map_h, sc.ic2h, (size_t)routes, b.inter) ||
+        !make_raw_map(&map_gp, b.gu_packed, gu_rows, b.hidden / 2, 64, 64) ||
+        !make_raw_map(&map_gs, b.gu_scale, gu_rows, b.hidden / 16, 16, 64) ||
+        !make_raw_map(&map_dp, b.dn_packed, dn_rows, b.inter / 2, 64, 128) ||
+        !make_raw_map(&map_ds, b.dn_scale, dn_rows, b.inter / 16, 16, 128))
         return -1;
     static bool attr = false;
     if (!attr) {
@@ -580,18 +661,18 @@ int launch_prefill_umma(const BankView& b, const void* x, int x_dtype, const Dec
     }
     UmmaArgs a{};
     a.groups = sc.groups; a.n_groups = sc.n_groups; a.route_idx = sc.route_idx; a.err = sc.err;
-    a.packed = b.gu_packed; a.scale = b.gu_scale; a.global = b.gu_global; a.row_scale = sc.row_scale;
+    a.global = b.gu_global; a.row_scale = sc.row_scale;
     a.ic2 = sc.ic2; a.N = 2 * b.inter;
     c.begin(K_GROUPED_GATE_UP);
-    umma_grouped_gemm_kernel<true, 2048><<<sm_count, kThreads, kUmmaSmem, c.s>>>(map_x, a);
+    umma_grouped_gemm_kernel<true, 2048><<<sm_count, kThreads, kUmmaSmem, c.s>>>(map_x, map_gp, map_gs, a);
     c.end();
     c.begin(K_PREFILL_RESCALE);
     prefill_rescale_kernel<<<(routes + 7) / 8, 256, 0, c.s>>>(sc.ic2, sc.seg + nbins, b.inter, sc.ic2h, sc.row_scale2);
     c.end();
-    a.packed = b.dn_packed; a.scale = b.dn_scale; a.global = b.dn_global; a.row_scale = sc.row_scale2;
+    a.global = b.dn_global; a.row_scale = sc.row_scale2;
     a.route_weight = route_weight; a.y = sc.y; a.y_f32 = (out_dtype == 1); a.N = b.hidden;
     c.begin(K_GROUPED_DOWN);
-    umma_grouped_gemm_kernel<false, 512><<<sm_count, kThreads, kUmmaSmem, c.s>>>(map_h, a);
+    umma_grouped_gemm_kernel<false, 512><<<sm_count, kThreads, kUmmaSmem, c.s>>>(map_h, map_dp, map_ds, a);
     c.end();
     launches += 3;
     // 4. un-permute and sum in route order; routes of experts that are not resident are skipped
