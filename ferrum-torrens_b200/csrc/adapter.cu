@@ -232,7 +232,7 @@ int run_routed(ftm_handle* h, const void* x, int x_dtype, const void* expert_ids
         PrefillScratch sc{};
         sc.route_bin = h->route_expert; sc.seg = h->seg; sc.route_idx = h->sorted_route; sc.pos_of_route = h->route_idx;
         sc.csr_scratch = h->csr_scratch; sc.csr_flag = h->flags + 3; sc.groups = h->groups; sc.n_groups = h->n_groups;
-        sc.xg = h->xg; sc.row_scale = h->row_scale; sc.ic2 = h->ic2p; sc.ic2h = reinterpret_cast<__half*>(h->ic2);
+        sc.xg = h->xg; sc.row_scale = h->row_scale; sc.ic1 = h->ic2p; sc.ic2h = reinterpret_cast<__half*>(h->ic2);
         sc.row_scale2 = h->row_scale2; sc.y = h->yroute; sc.err = h->flags + 2;
         DecodeRoutes rt{expert_ids ? nullptr : h->route_slot, expert_ids, ids_dtype, layer, h->cfg.experts,
                         (int)h->slot_for_id.size(), h->d_slot_for_id, h->route_slot, h->flags + 1};
@@ -356,7 +356,7 @@ FTM_API int ftm_create(const ftm_config* c, void* stream, ftm_handle** out) {
     A(dev_alloc(hp, &h->routed_f32, T * H));
     A(dev_alloc(hp, &h->xh, T * H));
     A(dev_alloc(hp, &h->tok_scale, T));
-    A(dev_alloc(hp, &h->ic2p, R * I));
+    A(dev_alloc(hp, &h->ic2p, R * 2 * I));  // also gate | up of the grouped GEMM
     A(dev_alloc(hp, &h->groups, R));
     A(dev_alloc(hp, &h->sorted_route, R));
     A(dev_alloc(hp, &h->n_groups, 1));

@@ -102,7 +102,7 @@ struct PrefillScratch {
     int32_t* n_groups;
     __half* xg;              // [routes, hidden] sorted activations, scaled f16
     float* row_scale;        // [routes]
-    float* ic2;              // [routes, inter] f32
+    float* ic1;              // [routes, 2 * inter] f32: gate | up of every sorted row
     __half* ic2h;            // [routes, inter]
     float* row_scale2;       // [routes]
     void* y;                 // [routes, hidden] weighted expert outputs, sorted rows: bf16, or f32 for f32 outputs

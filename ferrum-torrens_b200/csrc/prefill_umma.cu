@@ -8,19 +8,22 @@
 //
 //   gather    the routes are sorted by expert (CSR); xg[i] = f16(x[token of route_idx[i]] * 2^-e) with a
 //             per-row power-of-two scale (exact, keeps any bf16 / f32 input inside the f16 range)
-//   gemm      persistent CTAs over (segment pass of <= 256 tokens, tile of 128 weight rows):
-//               warp 0      TMA producer: activation tiles [128 tokens x 64 k] f16, 128-byte swizzle
-//               warp 1      allocates tensor memory, issues tcgen05.mma (M = 128 tokens, N = 128 rows,
-//                           K = 16 per instruction, f16 x f16 -> f32), commits to mbarriers
-//               warps 2..5  dequantise the packed rows straight from global memory (hardware
-//                           e2m1x2 / e4m3x2 -> f16x2 conversions, exact product with the block scale)
-//                           into the K-major, 128-byte-swizzled B tile in shared memory; after the
-//                           mainloop they read the accumulators back (tcgen05.ld) and run the epilogue
-//             gate_up tiles hold 64 gate rows and the 64 matching up rows, so silu(gate) * up stays in
-//             one thread; the epilogue applies the globals and the row scale and writes ic2 (f32).
-//             down tiles apply global, row scale and route weight and write one bf16 row per route.
-//   rescale   ic2 (f32) -> f16 with a per-route power-of-two scale, between the two GEMMs
-//   combine   out[t] = se_gate[t] * shared[t] + sum_j y[position of route (t, j)]  (ep_combine_kernel)
+//   gemm      D[128 weight rows, n tokens] per unit = (pass of <= 128 sorted rows of one expert, tile of
+//             128 weight rows); persistent CTAs, 16 warps:
+//               warp 0      TMA: activation tiles [128 tokens x 64 k] f16, 128-byte swizzle (B operand)
+//               warp 2      TMA: packed weight rows (64-byte swizzle) and block scales into a raw ring
+//               warps 8..15 dequantise (hardware e2m1x2 / e4m3x2 -> f16x2, exact product with the block
+//                           scale) and store the f16 weights into tensor memory (tcgen05.st): they are the
+//                           A operand, one TMEM lane per weight row, so the dequantised weights never
+//                           cross shared memory
+//               warp 1      issues tcgen05.mma (M = 128, N = tokens rounded up to 16, K = 16 per
+//                           instruction, f16 x f16 -> f32 in TMEM), commits to mbarriers
+//               warps 4..7  epilogue: tcgen05.ld of one of two accumulator sets while the next unit's
+//                           mainloop runs; a thread owns a weight row, so stores are coalesced over rows
+//             gate_up writes gate and up (globals and row scale applied) as f32; down applies global,
+//             row scale and route weight and writes one row per route (bf16, or f32 for f32 outputs).
+//   rescale   silu(gate) * up -> f16 with a per-route power-of-two scale, between the two GEMMs
+//   combine   out[t] = se_gate[t] * shared[t] + sum_j y[position of route (t, j)], j ascending
 //
 // Every mbarrier wait is bounded; a wait that gives up raises the error flag and the CTA drains.
 #include <cuda.h>
@@ -31,13 +34,12 @@ namespace ftm {
 
 namespace {
 
-constexpr int kTileM = 128;   // tokens per accumulator tile (MMA M, one TMEM lane per token)
-constexpr int kTileN = 128;   // weight rows per tile (MMA N, one TMEM column per row)
+constexpr int kTileM = 128;   // weight rows per tile (MMA M, one TMEM lane per row)
+constexpr int kTileTok = 128; // most tokens per pass (MMA N <= 128, one TMEM column per token)
 constexpr int kStepK = 64;    // k per pipeline step: one 128-byte swizzle atom of f16
-constexpr int kMaxTokTiles = 2;               // <= 256 tokens per pass
-constexpr int kAStages = 3;
-constexpr int kTileBytes = kTileM * kStepK * 2;  // 16 KiB, also the B tile
-constexpr int kThreads = 512;
+constexpr int kXStages = 8;
+constexpr int kTileBytes = kTileTok * kStepK * 2;  // 16 KiB activation tile
+constexpr int kThreads = 768;
 constexpr uint32_t kSpin = 1u << 20;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -90,18 +92,9 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
     d |= (uint64_t)2 << 61;                      // 128-byte swizzle
     return d;
 }
-// instruction descriptor: f16 x f16 -> f32, both operands K-major, M = 128, N = 128
-constexpr uint32_t kIdesc = (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(kTileN >> 3) << 17) |
-                            ((uint32_t)(kTileM >> 4) << 24);
+// instruction descriptor: f16 x f16 -> f32, both operands K-major, M = 128; N (bits 17..22, N >> 3) per unit
+constexpr uint32_t kIdescBase = (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(kTileM >> 4) << 24);
 
-__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-        "l"(adesc), "l"(bdesc), "r"(kIdesc), "r"(accumulate)
-        : "memory");
-}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -182,9 +175,10 @@ prefill_gather_kernel(const void* __restrict__ x, int x_dtype, const int32_t* __
     }
 }
 
-// ic2 (f32, sorted rows) -> f16 with a per-row power-of-two scale.  One warp per row; K == 512.
+// ic1 (f32, sorted rows: gate | up) -> ic2 = silu(gate) * up as f16 with a per-row power-of-two scale.
+// One warp per row; K == 512.
 __global__ void __launch_bounds__(256)
-prefill_rescale_kernel(const float* __restrict__ ic2, const int32_t* __restrict__ n_sorted, int K,
+prefill_rescale_kernel(const float* __restrict__ ic1, const int32_t* __restrict__ n_sorted, int K,
                        __half* __restrict__ ic2h, float* __restrict__ row_scale) {
     const int row = blockIdx.x * 8 + threadIdx.x / 32, lane = threadIdx.x % 32;
     if (row >= *n_sorted) return;
@@ -192,9 +186,14 @@ prefill_rescale_kernel(const float* __restrict__ ic2, const int32_t* __restrict_
     float m = 0.f;
 #pragma unroll
     for (int c = 0; c < 4; c++) {
-        const float4 f = *reinterpret_cast<const float4*>(ic2 + (size_t)row * K + c * 128 + lane * 4);
-        v[4 * c] = f.x; v[4 * c + 1] = f.y; v[4 * c + 2] = f.z; v[4 * c + 3] = f.w;
-        m = fmaxf(m, fmaxf(fmaxf(fabsf(f.x), fabsf(f.y)), fmaxf(fabsf(f.z), fabsf(f.w))));
+        const float4 g = *reinterpret_cast<const float4*>(ic1 + (size_t)row * 2 * K + c * 128 + lane * 4);
+        const float4 u = *reinterpret_cast<const float4*>(ic1 + (size_t)row * 2 * K + K + c * 128 + lane * 4);
+        v[4 * c] = (g.x / (1.0f + __expf(-g.x))) * u.x;
+        v[4 * c + 1] = (g.y / (1.0f + __expf(-g.y))) * u.y;
+        v[4 * c + 2] = (g.z / (1.0f + __expf(-g.z))) * u.z;
+        v[4 * c + 3] = (g.w / (1.0f + __expf(-g.w))) * u.w;
+#pragma unroll
+        for (int q = 0; q < 4; q++) m = fmaxf(m, fabsf(v[4 * c + q]));
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
@@ -222,67 +221,90 @@ struct UmmaArgs {
     const int32_t* route_idx;  // sorted position -> route
     const float* row_scale;    // per sorted row: power-of-two scale of the activations
     const float* route_weight; // down only, indexed by route
-    float* ic2;                // gate_up out [rows, inter] f32 (sorted rows)
+    float* ic1;                // gate_up out [rows, 2 * inter] f32 (sorted rows): gate | up, before silu
     void* y;                   // down out [rows, hidden], bf16 or f32 (sorted rows)
     int y_f32;
     int32_t* err;
     int N;                     // rows of the weight matrix (2 * inter or hidden)
 };
 
-// warp roles of the GEMM CTA (16 warps)
+// warp roles of the GEMM CTA (24 warps)
 constexpr int kWarpActTma = 0, kWarpMma = 1, kWarpRawTma = 2, kWarpEpi0 = 4, kWarpDeq0 = 8;
-constexpr int kDeqThreads = 256;
-constexpr int kRawStages = 5;
-constexpr int kRawPackedBytes = kTileN * 64;   // one chunk of 128 k: 128 rows x 64 bytes
-constexpr int kRawScaleBytes = kTileN * 16;    // 128 rows x 16 scale bytes (256 k: the chunk's half is used)
+constexpr int kDeqSets = 4;                    // dequantiser sets of 4 warps (128 threads = 128 weight rows)
+constexpr int kRawStages = 6;
+constexpr int kRawPackedBytes = kTileM * 64;   // one chunk of 128 k: 128 weight rows x 64 bytes, 64-byte swizzle
+constexpr int kRawScaleBytes = kTileM * 16;    // 128 rows x 16 scale bytes (256 k: the chunk's half is used)
 constexpr int kRawStageBytes = kRawPackedBytes + kRawScaleBytes;
-constexpr int kAccStages = 2;                  // accumulator sets in tensor memory (2 x 256 columns)
+constexpr int kWBufs = kDeqSets;               // dequantised weight chunks in tensor memory, 64 columns each
+constexpr int kWCols = 64;
+constexpr int kAccCol0 = kWBufs * kWCols;      // accumulators: a ring of two tiles of 128 f32 columns behind them
 
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
+                                            uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+
+// D[128 weight rows, n tokens] += W[128, K] * X[n, K]^T.  The dequantised weights are the A operand in
+// tensor memory (one lane per weight row, two f16 per 32-bit column), the activation tiles are the B
+// operand in shared memory.  A unit covers up to two token tiles, so a weight chunk is dequantised once
+// for up to 256 tokens; n of the last tile is its row count rounded up to 16.
 template <bool GATE_UP, int K>
 __global__ void __launch_bounds__(kThreads, 1)
-umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_packed,
+umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_packed,
                          const __grid_constant__ CUtensorMap tmap_scale, UmmaArgs a) {
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment for the swizzled tiles
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint8_t* const a_tiles = smem;                                                  // [kAStages][kMaxTokTiles][16 KiB]
-    uint8_t* const b_tiles = a_tiles + kAStages * kMaxTokTiles * kTileBytes;        // [2 buffers][2 k-steps][16 KiB]
-    uint8_t* const raw_ring = b_tiles + 4 * kTileBytes;                              // [kRawStages][packed | scales]
-    float* const s_glob = reinterpret_cast<float*>(raw_ring + kRawStages * kRawStageBytes);  // [4 epilogue warps][128]
-    uint64_t* const bars = reinterpret_cast<uint64_t*>(s_glob + 4 * kTileN);
-    uint32_t* const s_tmem = reinterpret_cast<uint32_t*>(bars + 32);
+    uint8_t* const x_tiles = smem;                                         // [kXStages][16 KiB]: 128 tokens x 64 k
+    uint8_t* const raw_ring = x_tiles + kXStages * kTileBytes;             // [kRawStages][packed | scales]
+    uint64_t* const bars = reinterpret_cast<uint64_t*>(raw_ring + kRawStages * kRawStageBytes);
+    uint32_t* const s_tmem = reinterpret_cast<uint32_t*>(bars + 40);
     volatile int* const s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
     const uint32_t bar0 = smem_u32(bars);
-    auto A_FULL = [&](int s) { return bar0 + 8u * s; };
-    auto A_EMPTY = [&](int s) { return bar0 + 8u * (3 + s); };
-    auto B_READY = [&](int s) { return bar0 + 8u * (6 + s); };
-    auto B_FREE = [&](int s) { return bar0 + 8u * (8 + s); };
-    auto ACC_FULL = [&](int s) { return bar0 + 8u * (10 + s); };
-    auto ACC_EMPTY = [&](int s) { return bar0 + 8u * (12 + s); };
-    auto RAW_FULL = [&](int s) { return bar0 + 8u * (14 + s); };
-    auto RAW_EMPTY = [&](int s) { return bar0 + 8u * (19 + s); };
+    auto X_FULL = [&](int s) { return bar0 + 8u * s; };                 // kXStages <= 8
+    auto X_EMPTY = [&](int s) { return bar0 + 8u * (8 + s); };
+    auto RAW_FULL = [&](int s) { return bar0 + 8u * (16 + s); };         // kRawStages <= 6
+    auto RAW_EMPTY = [&](int s) { return bar0 + 8u * (22 + s); };
+    auto W_READY = [&](int s) { return bar0 + 8u * (28 + s); };          // kWBufs <= 4
+    auto W_FREE = [&](int s) { return bar0 + 8u * (32 + s); };
+    auto ACC_FULL = [&](int s) { return bar0 + 8u * (36 + s); };
+    auto ACC_EMPTY = [&](int s) { return bar0 + 8u * (38 + s); };
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kAStages; s++) {
-            mbar_init(A_FULL(s), 1);
-            mbar_init(A_EMPTY(s), 1);
-        }
-        for (int s = 0; s < 2; s++) {
-            mbar_init(B_READY(s), kDeqThreads);
-            mbar_init(B_FREE(s), 1);
-            mbar_init(ACC_FULL(s), 1);
-            mbar_init(ACC_EMPTY(s), 128);
+        for (int s = 0; s < kXStages; s++) {
+            mbar_init(X_FULL(s), 1);
+            mbar_init(X_EMPTY(s), 1);
         }
         for (int s = 0; s < kRawStages; s++) {
             mbar_init(RAW_FULL(s), 1);
-            mbar_init(RAW_EMPTY(s), kDeqThreads);
+            mbar_init(RAW_EMPTY(s), 128);
+        }
+        for (int s = 0; s < kWBufs; s++) {
+            mbar_init(W_READY(s), 128);
+            mbar_init(W_FREE(s), 1);
+        }
+        for (int s = 0; s < 2; s++) {
+            mbar_init(ACC_FULL(s), 1);
+            mbar_init(ACC_EMPTY(s), 128);
         }
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == kWarpMma) {
-        // all 512 columns of tensor memory: two accumulator sets of two 128-column f32 tiles
+        // all 512 columns of tensor memory: four weight chunks and two accumulator tiles
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(s_tmem)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -291,15 +313,10 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *s_tmem;
 
-    constexpr int kSteps = K / kStepK;
     constexpr int kChunks = K / 128;
-    const int n_tiles = a.N / kTileN;
+    static_assert(kChunks % kDeqSets == 0, "every dequantiser set sees the same chunks of every unit");
+    const int n_tiles = a.N / kTileM;
     const int n_units = *a.n_groups * n_tiles;
-    // tile row n of tile nt -> weight row: gate_up tiles are 64 gate rows followed by the 64 matching up rows
-    auto weight_row = [&](int nt, int n) -> int {
-        if (GATE_UP) return (n < 64) ? nt * 64 + n : a.N / 2 + nt * 64 + (n - 64);
-        return nt * kTileN + n;
-    };
 
     if (warp == kWarpActTma) {
         // ===================== activation tiles: TMA, 128-byte swizzle ============================
@@ -307,16 +324,17 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             uint32_t it = 0;
             for (int u = blockIdx.x; u < n_units && !*s_abort; u += gridDim.x) {
                 const int4 grp = a.groups[u / n_tiles];
-                const int ntt = (grp.z + kTileM - 1) / kTileM;
+                const int ntt = (grp.z + kTileTok - 1) / kTileTok;
                 bool ok = true;
-                for (int ks = 0; ks < kSteps && ok; ks++, it++) {
-                    const int st = it % kAStages;
-                    ok = mbar_wait(A_EMPTY(st), ((it / kAStages) & 1) ^ 1, s_abort, a.err);
-                    if (!ok) break;
-                    mbar_expect_tx(A_FULL(st), (uint32_t)(ntt * kTileBytes));
-                    for (int t = 0; t < ntt; t++)
-                        tma_load_2d(smem_u32(a_tiles + (size_t)(st * kMaxTokTiles + t) * kTileBytes), &tmap_a, ks * kStepK,
-                                    grp.y + t * kTileM, A_FULL(st));
+                for (int ks = 0; ks < K / kStepK && ok; ks++) {
+                    for (int t = 0; t < ntt && ok; t++, it++) {
+                        const int st = it % kXStages;
+                        ok = mbar_wait(X_EMPTY(st), ((it / kXStages) & 1) ^ 1, s_abort, a.err);
+                        if (!ok) break;
+                        mbar_expect_tx(X_FULL(st), kTileBytes);
+                        tma_load_2d(smem_u32(x_tiles + (size_t)st * kTileBytes), &tmap_x, ks * kStepK, grp.y + t * kTileTok,
+                                    X_FULL(st));
+                    }
                 }
                 if (!ok) break;
             }
@@ -327,8 +345,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             uint32_t it = 0;
             for (int u = blockIdx.x; u < n_units && !*s_abort; u += gridDim.x) {
                 const int4 grp = a.groups[u / n_tiles];
-                const int nt = u % n_tiles;
-                const int row0 = grp.x * a.N;
+                const int row0 = grp.x * a.N + (u % n_tiles) * kTileM;
                 bool ok = true;
                 for (int c = 0; c < kChunks && ok; c++, it++) {
                     const int st = it % kRawStages;
@@ -336,17 +353,8 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                     if (!ok) break;
                     const uint32_t dst = smem_u32(raw_ring + (size_t)st * kRawStageBytes);
                     mbar_expect_tx(RAW_FULL(st), kRawStageBytes);
-                    if (GATE_UP) {
-                        // boxes of 64 rows: the gate rows, then the matching up rows
-                        tma_load_2d(dst, &tmap_packed, c * 64, row0 + weight_row(nt, 0), RAW_FULL(st));
-                        tma_load_2d(dst + kRawPackedBytes / 2, &tmap_packed, c * 64, row0 + weight_row(nt, 64), RAW_FULL(st));
-                        tma_load_2d(dst + kRawPackedBytes, &tmap_scale, (c >> 1) * 16, row0 + weight_row(nt, 0), RAW_FULL(st));
-                        tma_load_2d(dst + kRawPackedBytes + kRawScaleBytes / 2, &tmap_scale, (c >> 1) * 16,
-                                    row0 + weight_row(nt, 64), RAW_FULL(st));
-                    } else {
-                        tma_load_2d(dst, &tmap_packed, c * 64, row0 + weight_row(nt, 0), RAW_FULL(st));
-                        tma_load_2d(dst + kRawPackedBytes, &tmap_scale, (c >> 1) * 16, row0 + weight_row(nt, 0), RAW_FULL(st));
-                    }
+                    tma_load_2d(dst, &tmap_packed, c * 64, row0, RAW_FULL(st));
+                    tma_load_2d(dst + kRawPackedBytes, &tmap_scale, (c >> 1) * 16, row0, RAW_FULL(st));
                 }
                 if (!ok) break;
             }
@@ -354,159 +362,158 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     } else if (warp == kWarpMma) {
         // ===================== MMA issuer ======================================================
         if (lane == 0) {
-            uint32_t it = 0, chunk = 0, unit_i = 0;
-            for (int u = blockIdx.x; u < n_units && !*s_abort; u += gridDim.x, unit_i++) {
+            uint32_t it = 0, chunk = 0, tile_seq = 0;
+            for (int u = blockIdx.x; u < n_units && !*s_abort; u += gridDim.x) {
                 const int4 grp = a.groups[u / n_tiles];
-                const int ntt = (grp.z + kTileM - 1) / kTileM;
-                const int acc = unit_i & 1;
-                // this accumulator set must have been read back (two units ago)
-                if (!mbar_wait(ACC_EMPTY(acc), ((unit_i >> 1) & 1) ^ 1, s_abort, a.err)) break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const int ntt = (grp.z + kTileTok - 1) / kTileTok;
                 bool ok = true;
-                for (int ks = 0; ks < kSteps && ok; ks++, it++) {
-                    const int st = it % kAStages;
-                    const int buf = chunk & 1;
-                    if ((ks & 1) == 0) ok = mbar_wait(B_READY(buf), (chunk >> 1) & 1, s_abort, a.err);
-                    if (ok) ok = mbar_wait(A_FULL(st), (it / kAStages) & 1, s_abort, a.err);
-                    if (!ok) break;
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t b_addr = smem_u32(b_tiles + (size_t)(buf * 2 + (ks & 1)) * kTileBytes);
-                    for (int t = 0; t < ntt; t++) {
-                        const uint32_t a_addr = smem_u32(a_tiles + (size_t)(st * kMaxTokTiles + t) * kTileBytes);
+                uint32_t idesc[2], d_tmem[2];
+                for (int t = 0; t < ntt && ok; t++) {
+                    const int n_pad = max(16, (min(grp.z - t * kTileTok, kTileTok) + 15) & ~15);
+                    idesc[t] = kIdescBase | ((uint32_t)(n_pad >> 3) << 17);
+                    const uint32_t ts = tile_seq + t;
+                    d_tmem[t] = tmem_base + kAccCol0 + (ts & 1) * kTileTok;
+                    // the accumulator tile must have been read back
+                    ok = mbar_wait(ACC_EMPTY(ts & 1), ((ts >> 1) & 1) ^ 1, s_abort, a.err);
+                }
+                for (int c = 0; c < kChunks && ok; c++, chunk++) {
+                    const int wb = chunk % kWBufs;
+                    ok = mbar_wait(W_READY(wb), (chunk / kWBufs) & 1, s_abort, a.err);
+                    for (int h = 0; h < 2 && ok; h++) {
+                        for (int t = 0; t < ntt && ok; t++, it++) {
+                            const int st = it % kXStages;
+                            ok = mbar_wait(X_FULL(st), (it / kXStages) & 1, s_abort, a.err);
+                            if (!ok) break;
+                            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                            const uint32_t x_addr = smem_u32(x_tiles + (size_t)st * kTileBytes);
 #pragma unroll
-                        for (int kk = 0; kk < kStepK / 16; kk++)
-                            umma_f16(tmem_base + acc * (kMaxTokTiles * kTileN) + t * kTileN, umma_desc(a_addr + kk * 32),
-                                     umma_desc(b_addr + kk * 32), (ks > 0 || kk > 0) ? 1u : 0u);
+                            for (int kk = 0; kk < 4; kk++)
+                                umma_f16_ts(d_tmem[t], tmem_base + wb * kWCols + (h * 4 + kk) * 8, umma_desc(x_addr + kk * 32),
+                                            idesc[t], (c > 0 || h > 0 || kk > 0) ? 1u : 0u);
+                            umma_commit(X_EMPTY(st));    // the activation stage is free once these MMAs retire
+                        }
                     }
-                    umma_commit(A_EMPTY(st));            // the activation stage is free once these MMAs retire
-                    if (ks & 1) {
-                        umma_commit(B_FREE(buf));        // and so is the dequantised buffer
-                        chunk++;
-                    }
+                    if (!ok) break;
+                    umma_commit(W_FREE(wb));             // and so is the weight chunk
                 }
                 if (!ok) break;
-                umma_commit(ACC_FULL(acc));
+                for (int t = 0; t < ntt; t++) umma_commit(ACC_FULL((tile_seq + t) & 1));
+                tile_seq += ntt;
             }
         }
     } else if (warp >= kWarpDeq0) {
-        // ===================== dequantisers (8 warps): raw ring -> swizzled f16 B tiles ==============
-        const int tid = threadIdx.x - kWarpDeq0 * 32;   // 0..255
-        uint32_t chunk = 0;
-        for (int u = blockIdx.x; u < n_units && !*s_abort; u += gridDim.x) {
+        // ===================== dequantisers: raw ring -> f16 weights in tensor memory ================
+        // Four sets of four warps; set s takes the chunks c = s (mod 4) of every unit and owns weight
+        // buffer s.  Warp quarter q may touch TMEM lanes 32q..32q+31; a thread owns one weight row of
+        // the chunk: 64 packed bytes, eight block scales, 64 columns.
+        const int quarter = warp & 3, set = (warp - kWarpDeq0) >> 2;
+        const int row = quarter * 32 + lane;
+        const int sw = (row >> 1) & 3;      // 64-byte swizzle of the TMA box: 16-byte chunk index ^ ((row >> 1) & 3)
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + set * kWCols;
+        uint32_t chunk0 = 0;                // chunks before this unit
+        for (int u = blockIdx.x; u < n_units && !*s_abort; u += gridDim.x, chunk0 += kChunks) {
             bool ok = true;
-            for (int c = 0; c < kChunks && ok; c++, chunk++) {
-                const int buf = chunk & 1, st = chunk % kRawStages;
+            for (int c = set; c < kChunks && ok; c += kDeqSets) {
+                const uint32_t chunk = chunk0 + c;
+                const int st = chunk % kRawStages;
                 ok = mbar_wait(RAW_FULL(st), (chunk / kRawStages) & 1, s_abort, a.err);
-                if (ok) ok = mbar_wait(B_FREE(buf), ((chunk >> 1) & 1) ^ 1, s_abort, a.err);
+                if (ok) ok = mbar_wait(W_FREE(set), ((chunk / kWBufs) & 1) ^ 1, s_abort, a.err);
                 if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint8_t* const rp = raw_ring + (size_t)st * kRawStageBytes;
-                // 128 rows x 4 pieces of 16 bytes (32 k, two scale blocks); four lanes share a row
+                const uint2 sc8 = *reinterpret_cast<const uint2*>(rp + kRawPackedBytes + row * 16 + (c & 1) * 8);
+                uint4 raw[4];
 #pragma unroll
-                for (int i = 0; i < 2; i++) {
-                    const int unit = tid + kDeqThreads * i;
-                    const int row = unit >> 2, piece = unit & 3;
-                    const uint4 raw = *reinterpret_cast<const uint4*>(rp + row * 64 + piece * 16);
-                    const uint16_t sc2 =
-                        *reinterpret_cast<const uint16_t*>(rp + kRawPackedBytes + row * 16 + (c & 1) * 8 + piece * 2);
+                for (int g = 0; g < 4; g++) raw[g] = *reinterpret_cast<const uint4*>(rp + row * 64 + ((g ^ sw) << 4));
+#pragma unroll
+                for (int g = 0; g < 4; g++) {
+                    // 32 k: two block scales
+                    const uint32_t two = ((g & 2) ? sc8.y : sc8.x) >> ((g & 1) * 16);
                     uint32_t h2;
-                    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(sc2));
+                    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"((uint16_t)(two & 0xffffu)));
                     const uint32_t s0 = __byte_perm(h2, h2, 0x1010), s1 = __byte_perm(h2, h2, 0x3232);
-                    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-                    // piece -> k-step (piece / 2) and 16-byte chunks (piece % 2) * 4 + j of the 128-byte row
-                    uint8_t* const brow = b_tiles + (size_t)(buf * 2 + (piece >> 1)) * kTileBytes + row * 128;
+                    const uint32_t w[4] = {raw[g].x, raw[g].y, raw[g].z, raw[g].w};
+                    uint32_t r[16];
 #pragma unroll
                     for (int j = 0; j < 4; j++) {
                         uint32_t q[4];
                         e2m1x8_to_f16x2(w[j], q);
-                        const uint32_t s = (j < 2) ? s0 : s1;
 #pragma unroll
-                        for (int r = 0; r < 4; r++) q[r] = hmul2_f16(q[r], s);
-                        const int c16 = (piece & 1) * 4 + j;
-                        *reinterpret_cast<uint4*>(brow + ((c16 ^ (row & 7)) << 4)) = make_uint4(q[0], q[1], q[2], q[3]);
+                        for (int e = 0; e < 4; e++) r[4 * j + e] = hmul2_f16(q[e], (j < 2) ? s0 : s1);
                     }
+                    tmem_st16(taddr + g * 16, r);
                 }
                 mbar_arrive(RAW_EMPTY(st));
-                // generic-proxy writes must be visible to the tensor core's async-proxy reads
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                mbar_arrive(B_READY(buf));
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                mbar_arrive(W_READY(set));
             }
             if (!ok) break;
         }
     } else if (warp >= kWarpEpi0) {
         // ===================== epilogue (warps 4..7: TMEM lane quarters 0..3) =======================
+        // one thread = one weight row; a column = one token of the tile.  Lane l keeps the per-token
+        // factors of tokens l, l + 32, l + 64, l + 96 and hands them out by shuffle.
         const int quarter = warp & 3;
-        float* const my_glob = s_glob + quarter * kTileN;   // private to this warp
-        uint32_t unit_i = 0;
-        for (int u = blockIdx.x; u < n_units && !*s_abort; u += gridDim.x, unit_i++) {
+        uint32_t tile_seq = 0;
+        for (int u = blockIdx.x; u < n_units && !*s_abort; u += gridDim.x) {
             const int4 grp = a.groups[u / n_tiles];
-            const int nt = u % n_tiles;
-            const int ntt = (grp.z + kTileM - 1) / kTileM;
-            const int acc = unit_i & 1;
-            __syncwarp();
+            const int ntt = (grp.z + kTileTok - 1) / kTileTok;
+            const int wrow = (u % n_tiles) * kTileM + quarter * 32 + lane;
+            const float glob = f16_global_to_f32(a.global[(size_t)grp.x * a.N + wrow]);
+            bool ok = true;
+            for (int t = 0; t < ntt && ok; t++, tile_seq++) {
+                const int cnt = min(grp.z - t * kTileTok, kTileTok);
+                const int pos0 = grp.y + t * kTileTok;
+                float fac[4];
 #pragma unroll
-            for (int q = 0; q < 4; q++)
-                my_glob[lane + 32 * q] = f16_global_to_f32(a.global[(size_t)grp.x * a.N + weight_row(nt, lane + 32 * q)]);
-            __syncwarp();
-            if (!mbar_wait(ACC_FULL(acc), (unit_i >> 1) & 1, s_abort, a.err)) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            for (int t = 0; t < ntt; t++) {
-                const int row_in_pass = t * kTileM + quarter * 32 + lane;
-                const bool valid = row_in_pass < grp.z;
-                const int pos = grp.y + row_in_pass;
-                const float rs = valid ? a.row_scale[pos] : 0.f;
-                const uint32_t taddr =
-                    tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * (kMaxTokTiles * kTileN) + t * kTileN;
-                if (GATE_UP) {
-#pragma unroll 1
-                    for (int c0 = 0; c0 < 64; c0 += 16) {
-                        float g[16], up[16];
-                        tmem_ld16(taddr + c0, g);
-                        tmem_ld16(taddr + 64 + c0, up);
-                        tmem_ld_wait();
-                        if (valid) {
-                            float o[16];
-#pragma unroll
-                            for (int j = 0; j < 16; j++) {
-                                const float gate = g[j] * my_glob[c0 + j] * rs, upv = up[j] * my_glob[64 + c0 + j] * rs;
-                                o[j] = (gate / (1.0f + __expf(-gate))) * upv;
-                            }
-                            float4* dst = reinterpret_cast<float4*>(a.ic2 + (size_t)pos * (a.N / 2) + nt * 64 + c0);
-#pragma unroll
-                            for (int j = 0; j < 4; j++) dst[j] = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
-                        }
+                for (int q = 0; q < 4; q++) {
+                    const int i = q * 32 + lane;
+                    float f = 0.f;
+                    if (i < cnt) {
+                        f = a.row_scale[pos0 + i];
+                        if (!GATE_UP) f *= a.route_weight[a.route_idx[pos0 + i]];
                     }
-                } else {
-                    const float wr = valid ? a.route_weight[a.route_idx[pos]] : 0.f;
-#pragma unroll 1
-                    for (int c0 = 0; c0 < kTileN; c0 += 16) {
+                    fac[q] = f;
+                }
+                ok = mbar_wait(ACC_FULL(tile_seq & 1), (tile_seq >> 1) & 1, s_abort, a.err);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + kAccCol0 + (tile_seq & 1) * kTileTok;
+#pragma unroll
+                for (int c0 = 0; c0 < kTileTok; c0 += 16) {
+                    if (c0 < cnt) {     // uniform over the warp
                         float v[16];
                         tmem_ld16(taddr + c0, v);
                         tmem_ld_wait();
-                        if (valid) {
 #pragma unroll
-                            for (int j = 0; j < 16; j++) v[j] = wr * ((v[j] * rs) * my_glob[c0 + j]);
-                            const size_t o = (size_t)pos * a.N + nt * kTileN + c0;
-                            if (a.y_f32) {
-                                float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(a.y) + o);
+                        for (int j = 0; j < 16; j++)
+                            v[j] = (v[j] * glob) * __shfl_sync(0xffffffffu, fac[c0 >> 5], (c0 & 31) + j);
+                        if (GATE_UP || a.y_f32) {
+                            float* const dst = GATE_UP ? a.ic1 : reinterpret_cast<float*>(a.y);
 #pragma unroll
-                                for (int j = 0; j < 4; j++) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                            } else {
-                                uint32_t pk[8];
+                            for (int j = 0; j < 16; j++)
+                                if (c0 + j < cnt) dst[(size_t)(pos0 + c0 + j) * a.N + wrow] = v[j];
+                        } else {
+                            // bf16 rows: neighbouring lanes swap so that every lane stores a pair of rows of one token
+                            __nv_bfloat16* const dst = reinterpret_cast<__nv_bfloat16*>(a.y);
 #pragma unroll
-                                for (int j = 0; j < 8; j++) {
-                                    __nv_bfloat162 b2 = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-                                    pk[j] = *reinterpret_cast<uint32_t*>(&b2);
-                                }
-                                uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.y) + o);
-                                dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-                                dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+                            for (int j = 0; j < 16; j += 2) {
+                                const float mine = (lane & 1) ? v[j + 1] : v[j];
+                                const float give = (lane & 1) ? v[j] : v[j + 1];
+                                const float got = __shfl_xor_sync(0xffffffffu, give, 1);
+                                const int tok = c0 + j + (lane & 1);
+                                const __nv_bfloat162 pr = (lane & 1) ? __floats2bfloat162_rn(got, mine) : __floats2bfloat162_rn(mine, got);
+                                if (tok < cnt)
+                                    *reinterpret_cast<__nv_bfloat162*>(dst + (size_t)(pos0 + tok) * a.N + (wrow & ~1)) = pr;
                             }
                         }
                     }
                 }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                mbar_arrive(ACC_EMPTY(tile_seq & 1));
             }
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(ACC_EMPTY(acc));
+            if (!ok) break;
         }
     }
     // drain: nobody frees tensor memory while another role may still touch it
@@ -517,8 +524,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     }
 }
 
-constexpr size_t kUmmaSmem = 1024 + (size_t)(kAStages * kMaxTokTiles + 4) * kTileBytes + (size_t)kRawStages * kRawStageBytes +
-                             4 * kTileN * 4 + 32 * 8 + 64;
+constexpr size_t kUmmaSmem = 1024 + (size_t)kXStages * kTileBytes + (size_t)kRawStages * kRawStageBytes + 40 * 8 + 64;
 static_assert(kUmmaSmem <= 227 * 1024, "shared memory of the grouped GEMM CTA");
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -541,7 +547,7 @@ bool make_act_map(CUtensorMap* map, const void* base, size_t rows, int K) {
     if (!fn) return false;
     cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-    cuuint32_t box[2] = {(cuuint32_t)kStepK, (cuuint32_t)kTileM};
+    cuuint32_t box[2] = {(cuuint32_t)kStepK, (cuuint32_t)kTileTok};
     cuuint32_t estr[2] = {1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -591,8 +597,9 @@ __global__ void prefill_combine_kernel(const void* __restrict__ y, int y_f32, co
     }
 }
 
-// u8 matrix [rows, row_bytes] row-major (packed nibbles or block scales), box = box_bytes x box_rows, no swizzle
-bool make_raw_map(CUtensorMap* map, const void* base, size_t rows, int row_bytes, int box_bytes, int box_rows) {
+// u8 matrix [rows, row_bytes] row-major (packed nibbles or block scales), box = box_bytes x box_rows
+bool make_raw_map(CUtensorMap* map, const void* base, size_t rows, int row_bytes, int box_bytes, int box_rows,
+                  CUtensorMapSwizzle swizzle) {
     EncodeTiledFn fn = encode_tiled();
     if (!fn) return false;
     cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)rows};
@@ -600,7 +607,7 @@ bool make_raw_map(CUtensorMap* map, const void* base, size_t rows, int row_bytes
     cuuint32_t box[2] = {(cuuint32_t)box_bytes, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -637,7 +644,7 @@ int launch_prefill_umma(const BankView& b, const void* x, int x_dtype, const Dec
     }
     launches += launch_csr_build(bins_of_route, routes, nbins, sc.seg, sc.route_idx, sc.csr_scratch, sc.csr_flag, c);
     // 2. passes of <= 256 sorted rows per expert
-    launches += launch_groups_from_csr(sc.seg, nbins, slot_of_bin, b.slots, kMaxTokTiles * kTileM, sc.groups, sc.n_groups, c);
+    launches += launch_groups_from_csr(sc.seg, nbins, slot_of_bin, b.slots, 2 * kTileTok, sc.groups, sc.n_groups, c);
     // 3. sorted, scaled f16 activations
     c.begin(K_PERMUTE_ACT);
     prefill_gather_kernel<<<routes, 256, 0, c.s>>>(x, x_dtype, sc.route_idx, sc.seg + nbins, top_k, b.hidden, sc.xg,
@@ -648,10 +655,10 @@ int launch_prefill_umma(const BankView& b, const void* x, int x_dtype, const Dec
     CUtensorMap map_x, map_h, map_gp, map_gs, map_dp, map_ds;
     const size_t gu_rows = (size_t)b.slots * 2 * b.inter, dn_rows = (size_t)b.slots * b.hidden;
     if (!make_act_map(&map_x, sc.xg, (size_t)routes, b.hidden) || !make_act_map(&map_h, sc.ic2h, (size_t)routes, b.inter) ||
-        !make_raw_map(&map_gp, b.gu_packed, gu_rows, b.hidden / 2, 64, 64) ||
-        !make_raw_map(&map_gs, b.gu_scale, gu_rows, b.hidden / 16, 16, 64) ||
-        !make_raw_map(&map_dp, b.dn_packed, dn_rows, b.inter / 2, 64, 128) ||
-        !make_raw_map(&map_ds, b.dn_scale, dn_rows, b.inter / 16, 16, 128))
+        !make_raw_map(&map_gp, b.gu_packed, gu_rows, b.hidden / 2, 64, kTileM, CU_TENSOR_MAP_SWIZZLE_64B) ||
+        !make_raw_map(&map_gs, b.gu_scale, gu_rows, b.hidden / 16, 16, kTileM, CU_TENSOR_MAP_SWIZZLE_NONE) ||
+        !make_raw_map(&map_dp, b.dn_packed, dn_rows, b.inter / 2, 64, kTileM, CU_TENSOR_MAP_SWIZZLE_64B) ||
+        !make_raw_map(&map_ds, b.dn_scale, dn_rows, b.inter / 16, 16, kTileM, CU_TENSOR_MAP_SWIZZLE_NONE))
         return -1;
     static bool attr = false;
     if (!attr) {
@@ -662,12 +669,12 @@ int launch_prefill_umma(const BankView& b, const void* x, int x_dtype, const Dec
     UmmaArgs a{};
     a.groups = sc.groups; a.n_groups = sc.n_groups; a.route_idx = sc.route_idx; a.err = sc.err;
     a.global = b.gu_global; a.row_scale = sc.row_scale;
-    a.ic2 = sc.ic2; a.N = 2 * b.inter;
+    a.ic1 = sc.ic1; a.N = 2 * b.inter;
     c.begin(K_GROUPED_GATE_UP);
     umma_grouped_gemm_kernel<true, 2048><<<sm_count, kThreads, kUmmaSmem, c.s>>>(map_x, map_gp, map_gs, a);
     c.end();
     c.begin(K_PREFILL_RESCALE);
-    prefill_rescale_kernel<<<(routes + 7) / 8, 256, 0, c.s>>>(sc.ic2, sc.seg + nbins, b.inter, sc.ic2h, sc.row_scale2);
+    prefill_rescale_kernel<<<(routes + 7) / 8, 256, 0, c.s>>>(sc.ic1, sc.seg + nbins, b.inter, sc.ic2h, sc.row_scale2);
     c.end();
     a.global = b.dn_global; a.row_scale = sc.row_scale2;
     a.route_weight = route_weight; a.y = sc.y; a.y_f32 = (out_dtype == 1); a.N = b.hidden;
