@@ -216,7 +216,7 @@ prefill_rescale_kernel(const float* __restrict__ ic1, const int32_t* __restrict_
 // ---- the grouped GEMM ------------------------------------------------------------------------
 struct UmmaArgs {
     const uint16_t* global;    // [slots, N] f16 row globals
-    const int4* groups;        // (slot, first sorted row, rows <= 256, 0)
+    const int4* groups;        // (slot, first sorted row, rows <= 128, 0)
     const int32_t* n_groups;
     const int32_t* route_idx;  // sorted position -> route
     const float* row_scale;    // per sorted row: power-of-two scale of the activations
@@ -230,6 +230,7 @@ struct UmmaArgs {
 
 // warp roles of the GEMM CTA (24 warps)
 constexpr int kWarpActTma = 0, kWarpMma = 1, kWarpRawTma = 2, kWarpEpi0 = 4, kWarpDeq0 = 8;
+constexpr int kEpiWarps = 4;
 constexpr int kDeqSets = 4;                    // dequantiser sets of 4 warps (128 threads = 128 weight rows)
 constexpr int kRawStages = 6;
 constexpr int kRawPackedBytes = kTileM * 64;   // one chunk of 128 k: 128 weight rows x 64 bytes, 64-byte swizzle
@@ -256,13 +257,19 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
         : "memory");
 }
 
-// D[128 weight rows, n tokens] += W[128, K] * X[n, K]^T.  The dequantised weights are the A operand in
-// tensor memory (one lane per weight row, two f16 per 32-bit column), the activation tiles are the B
-// operand in shared memory.  A unit covers up to two token tiles, so a weight chunk is dequantised once
-// for up to 256 tokens; n of the last tile is its row count rounded up to 16.
+// activation tile maps by box height: 32, 64, 96 or 128 token rows, so that a small group does not
+// pull 128 rows through L2
+struct XMaps {
+    CUtensorMap m[4];
+};
+
+// D[256 weight rows, n tokens] += W[256, K] * X[n, K]^T as two accumulator tiles of 128 rows.  The
+// dequantised weights are the A operand in tensor memory (one lane per weight row, two f16 per 32-bit
+// column), the activation tile is the B operand in shared memory and is read by both row tiles; n is
+// the group's row count rounded up to 16.
 template <bool GATE_UP, int K>
 __global__ void __launch_bounds__(kThreads, 1)
-umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_packed,
+umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_constant__ CUtensorMap tmap_packed,
                          const __grid_constant__ CUtensorMap tmap_scale, UmmaArgs a) {
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment for the swizzled tiles
@@ -279,8 +286,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
     auto RAW_EMPTY = [&](int s) { return bar0 + 8u * (22 + s); };
     auto W_READY = [&](int s) { return bar0 + 8u * (28 + s); };          // kWBufs <= 4
     auto W_FREE = [&](int s) { return bar0 + 8u * (32 + s); };
-    auto ACC_FULL = [&](int s) { return bar0 + 8u * (36 + s); };
-    auto ACC_EMPTY = [&](int s) { return bar0 + 8u * (38 + s); };
+    const uint32_t ACC_FULL = bar0 + 8u * 36, ACC_EMPTY = bar0 + 8u * 37;
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     if (threadIdx.x == 0) {
@@ -296,15 +302,13 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
             mbar_init(W_READY(s), 128);
             mbar_init(W_FREE(s), 1);
         }
-        for (int s = 0; s < 2; s++) {
-            mbar_init(ACC_FULL(s), 1);
-            mbar_init(ACC_EMPTY(s), 128);
-        }
+        mbar_init(ACC_FULL, 1);
+        mbar_init(ACC_EMPTY, kEpiWarps * 32);
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == kWarpMma) {
-        // all 512 columns of tensor memory: four weight chunks and two accumulator tiles
+        // all 512 columns of tensor memory: four weight buffers and two accumulator tiles
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(s_tmem)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -314,27 +318,26 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
     const uint32_t tmem_base = *s_tmem;
 
     constexpr int kChunks = K / 128;
-    static_assert(kChunks % kDeqSets == 0, "every dequantiser set sees the same chunks of every unit");
-    const int n_tiles = a.N / kTileM;
-    const int n_units = *a.n_groups * n_tiles;
+    constexpr int kItems = 2 * kChunks;   // (chunk, row tile) pieces of a unit, one weight buffer each
+    static_assert(kItems % kDeqSets == 0, "every dequantiser set sees the same pieces of every unit");
+    const int n_pairs = a.N / (2 * kTileM);
+    const int n_units = *a.n_groups * n_pairs;
 
     if (warp == kWarpActTma) {
         // ===================== activation tiles: TMA, 128-byte swizzle ============================
         if (lane == 0) {
             uint32_t it = 0;
             for (int u = blockIdx.x; u < n_units && !*s_abort; u += gridDim.x) {
-                const int4 grp = a.groups[u / n_tiles];
-                const int ntt = (grp.z + kTileTok - 1) / kTileTok;
+                const int4 grp = a.groups[u / n_pairs];
+                const int sel = (grp.z + 31) / 32 - 1;     // box of 32 * (sel + 1) rows
+                const uint32_t bytes = (uint32_t)(sel + 1) * 32 * 128;
                 bool ok = true;
-                for (int ks = 0; ks < K / kStepK && ok; ks++) {
-                    for (int t = 0; t < ntt && ok; t++, it++) {
-                        const int st = it % kXStages;
-                        ok = mbar_wait(X_EMPTY(st), ((it / kXStages) & 1) ^ 1, s_abort, a.err);
-                        if (!ok) break;
-                        mbar_expect_tx(X_FULL(st), kTileBytes);
-                        tma_load_2d(smem_u32(x_tiles + (size_t)st * kTileBytes), &tmap_x, ks * kStepK, grp.y + t * kTileTok,
-                                    X_FULL(st));
-                    }
+                for (int ks = 0; ks < K / kStepK && ok; ks++, it++) {
+                    const int st = it % kXStages;
+                    ok = mbar_wait(X_EMPTY(st), ((it / kXStages) & 1) ^ 1, s_abort, a.err);
+                    if (!ok) break;
+                    mbar_expect_tx(X_FULL(st), bytes);
+                    tma_load_2d(smem_u32(x_tiles + (size_t)st * kTileBytes), &xmaps.m[sel], ks * kStepK, grp.y, X_FULL(st));
                 }
                 if (!ok) break;
             }
@@ -344,17 +347,18 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
         if (lane == 0) {
             uint32_t it = 0;
             for (int u = blockIdx.x; u < n_units && !*s_abort; u += gridDim.x) {
-                const int4 grp = a.groups[u / n_tiles];
-                const int row0 = grp.x * a.N + (u % n_tiles) * kTileM;
+                const int4 grp = a.groups[u / n_pairs];
+                const int row0 = grp.x * a.N + (u % n_pairs) * 2 * kTileM;
                 bool ok = true;
-                for (int c = 0; c < kChunks && ok; c++, it++) {
+                for (int w = 0; w < kItems && ok; w++, it++) {
+                    const int c = w >> 1, r = w & 1;
                     const int st = it % kRawStages;
                     ok = mbar_wait(RAW_EMPTY(st), ((it / kRawStages) & 1) ^ 1, s_abort, a.err);
                     if (!ok) break;
                     const uint32_t dst = smem_u32(raw_ring + (size_t)st * kRawStageBytes);
                     mbar_expect_tx(RAW_FULL(st), kRawStageBytes);
-                    tma_load_2d(dst, &tmap_packed, c * 64, row0, RAW_FULL(st));
-                    tma_load_2d(dst + kRawPackedBytes, &tmap_scale, (c >> 1) * 16, row0, RAW_FULL(st));
+                    tma_load_2d(dst, &tmap_packed, c * 64, row0 + r * kTileM, RAW_FULL(st));
+                    tma_load_2d(dst + kRawPackedBytes, &tmap_scale, (c >> 1) * 16, row0 + r * kTileM, RAW_FULL(st));
                 }
                 if (!ok) break;
             }
@@ -362,62 +366,57 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
     } else if (warp == kWarpMma) {
         // ===================== MMA issuer ======================================================
         if (lane == 0) {
-            uint32_t it = 0, chunk = 0, tile_seq = 0;
-            for (int u = blockIdx.x; u < n_units && !*s_abort; u += gridDim.x) {
-                const int4 grp = a.groups[u / n_tiles];
-                const int ntt = (grp.z + kTileTok - 1) / kTileTok;
-                bool ok = true;
-                uint32_t idesc[2], d_tmem[2];
-                for (int t = 0; t < ntt && ok; t++) {
-                    const int n_pad = max(16, (min(grp.z - t * kTileTok, kTileTok) + 15) & ~15);
-                    idesc[t] = kIdescBase | ((uint32_t)(n_pad >> 3) << 17);
-                    const uint32_t ts = tile_seq + t;
-                    d_tmem[t] = tmem_base + kAccCol0 + (ts & 1) * kTileTok;
-                    // the accumulator tile must have been read back
-                    ok = mbar_wait(ACC_EMPTY(ts & 1), ((ts >> 1) & 1) ^ 1, s_abort, a.err);
-                }
-                for (int c = 0; c < kChunks && ok; c++, chunk++) {
-                    const int wb = chunk % kWBufs;
-                    ok = mbar_wait(W_READY(wb), (chunk / kWBufs) & 1, s_abort, a.err);
-                    for (int h = 0; h < 2 && ok; h++) {
-                        for (int t = 0; t < ntt && ok; t++, it++) {
-                            const int st = it % kXStages;
-                            ok = mbar_wait(X_FULL(st), (it / kXStages) & 1, s_abort, a.err);
-                            if (!ok) break;
-                            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                            const uint32_t x_addr = smem_u32(x_tiles + (size_t)st * kTileBytes);
+            uint32_t it = 0, item = 0, unit_i = 0;
+            for (int u = blockIdx.x; u < n_units && !*s_abort; u += gridDim.x, unit_i++) {
+                const int4 grp = a.groups[u / n_pairs];
+                const int n_pad = max(16, (grp.z + 15) & ~15);
+                const uint32_t idesc = kIdescBase | ((uint32_t)(n_pad >> 3) << 17);
+                // the accumulators must have been read back
+                bool ok = mbar_wait(ACC_EMPTY, (unit_i & 1) ^ 1, s_abort, a.err);
+                for (int c = 0; c < kChunks && ok; c++, item += 2) {
+                    const int wb0 = item % kWBufs;                 // row tile 0; row tile 1 is the next buffer
+                    ok = mbar_wait(W_READY(wb0), (item / kWBufs) & 1, s_abort, a.err);
+                    if (ok) ok = mbar_wait(W_READY(wb0 + 1), (item / kWBufs) & 1, s_abort, a.err);
+                    for (int h = 0; h < 2 && ok; h++, it++) {
+                        const int st = it % kXStages;
+                        ok = mbar_wait(X_FULL(st), (it / kXStages) & 1, s_abort, a.err);
+                        if (!ok) break;
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        const uint32_t x_addr = smem_u32(x_tiles + (size_t)st * kTileBytes);
+#pragma unroll
+                        for (int r = 0; r < 2; r++)
 #pragma unroll
                             for (int kk = 0; kk < 4; kk++)
-                                umma_f16_ts(d_tmem[t], tmem_base + wb * kWCols + (h * 4 + kk) * 8, umma_desc(x_addr + kk * 32),
-                                            idesc[t], (c > 0 || h > 0 || kk > 0) ? 1u : 0u);
-                            umma_commit(X_EMPTY(st));    // the activation stage is free once these MMAs retire
-                        }
+                                umma_f16_ts(tmem_base + kAccCol0 + r * kTileTok, tmem_base + (wb0 + r) * kWCols + (h * 4 + kk) * 8,
+                                            umma_desc(x_addr + kk * 32), idesc, (c > 0 || h > 0 || kk > 0) ? 1u : 0u);
+                        umma_commit(X_EMPTY(st));        // the activation stage is free once these MMAs retire
                     }
                     if (!ok) break;
-                    umma_commit(W_FREE(wb));             // and so is the weight chunk
+                    umma_commit(W_FREE(wb0));            // and so are the two weight buffers
+                    umma_commit(W_FREE(wb0 + 1));
                 }
                 if (!ok) break;
-                for (int t = 0; t < ntt; t++) umma_commit(ACC_FULL((tile_seq + t) & 1));
-                tile_seq += ntt;
+                umma_commit(ACC_FULL);
             }
         }
     } else if (warp >= kWarpDeq0) {
         // ===================== dequantisers: raw ring -> f16 weights in tensor memory ================
-        // Four sets of four warps; set s takes the chunks c = s (mod 4) of every unit and owns weight
-        // buffer s.  Warp quarter q may touch TMEM lanes 32q..32q+31; a thread owns one weight row of
-        // the chunk: 64 packed bytes, eight block scales, 64 columns.
+        // Four sets of four warps; set s takes the pieces w = s (mod 4) of every unit (w = 2 * chunk +
+        // row tile) and owns weight buffer s.  Warp quarter q may touch TMEM lanes 32q..32q+31; a thread
+        // owns one weight row of the piece: 64 packed bytes, eight block scales, 64 columns.
         const int quarter = warp & 3, set = (warp - kWarpDeq0) >> 2;
         const int row = quarter * 32 + lane;
         const int sw = (row >> 1) & 3;      // 64-byte swizzle of the TMA box: 16-byte chunk index ^ ((row >> 1) & 3)
         const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + set * kWCols;
-        uint32_t chunk0 = 0;                // chunks before this unit
-        for (int u = blockIdx.x; u < n_units && !*s_abort; u += gridDim.x, chunk0 += kChunks) {
+        uint32_t item0 = 0;                 // pieces before this unit
+        for (int u = blockIdx.x; u < n_units && !*s_abort; u += gridDim.x, item0 += kItems) {
             bool ok = true;
-            for (int c = set; c < kChunks && ok; c += kDeqSets) {
-                const uint32_t chunk = chunk0 + c;
-                const int st = chunk % kRawStages;
-                ok = mbar_wait(RAW_FULL(st), (chunk / kRawStages) & 1, s_abort, a.err);
-                if (ok) ok = mbar_wait(W_FREE(set), ((chunk / kWBufs) & 1) ^ 1, s_abort, a.err);
+            for (int w = set; w < kItems && ok; w += kDeqSets) {
+                const uint32_t item = item0 + w;
+                const int c = w >> 1;
+                const int st = item % kRawStages;
+                ok = mbar_wait(RAW_FULL(st), (item / kRawStages) & 1, s_abort, a.err);
+                if (ok) ok = mbar_wait(W_FREE(set), ((item / kWBufs) & 1) ^ 1, s_abort, a.err);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint8_t* const rp = raw_ring + (size_t)st * kRawStageBytes;
@@ -432,12 +431,12 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
                     uint32_t h2;
                     asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"((uint16_t)(two & 0xffffu)));
                     const uint32_t s0 = __byte_perm(h2, h2, 0x1010), s1 = __byte_perm(h2, h2, 0x3232);
-                    const uint32_t w[4] = {raw[g].x, raw[g].y, raw[g].z, raw[g].w};
+                    const uint32_t wd[4] = {raw[g].x, raw[g].y, raw[g].z, raw[g].w};
                     uint32_t r[16];
 #pragma unroll
                     for (int j = 0; j < 4; j++) {
                         uint32_t q[4];
-                        e2m1x8_to_f16x2(w[j], q);
+                        e2m1x8_to_f16x2(wd[j], q);
 #pragma unroll
                         for (int e = 0; e < 4; e++) r[4 * j + e] = hmul2_f16(q[e], (j < 2) ? s0 : s1);
                     }
@@ -452,43 +451,44 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
         }
     } else if (warp >= kWarpEpi0) {
         // ===================== epilogue (warps 4..7: TMEM lane quarters 0..3) =======================
-        // one thread = one weight row; a column = one token of the tile.  Lane l keeps the per-token
-        // factors of tokens l, l + 32, l + 64, l + 96 and hands them out by shuffle.
+        // one thread = one weight row of each row tile; a column = one token of the group.  Lane l keeps
+        // the per-token factors of tokens l, l + 32, l + 64, l + 96 and hands them out by shuffle.
         const int quarter = warp & 3;
-        uint32_t tile_seq = 0;
-        for (int u = blockIdx.x; u < n_units && !*s_abort; u += gridDim.x) {
-            const int4 grp = a.groups[u / n_tiles];
-            const int ntt = (grp.z + kTileTok - 1) / kTileTok;
-            const int wrow = (u % n_tiles) * kTileM + quarter * 32 + lane;
-            const float glob = f16_global_to_f32(a.global[(size_t)grp.x * a.N + wrow]);
-            bool ok = true;
-            for (int t = 0; t < ntt && ok; t++, tile_seq++) {
-                const int cnt = min(grp.z - t * kTileTok, kTileTok);
-                const int pos0 = grp.y + t * kTileTok;
-                float fac[4];
+        uint32_t unit_i = 0;
+        for (int u = blockIdx.x; u < n_units && !*s_abort; u += gridDim.x, unit_i++) {
+            const int4 grp = a.groups[u / n_pairs];
+            const int cnt = grp.z, pos0 = grp.y;
+            const int wrow0 = (u % n_pairs) * 2 * kTileM + quarter * 32 + lane;
+            float glob[2];
 #pragma unroll
-                for (int q = 0; q < 4; q++) {
-                    const int i = q * 32 + lane;
-                    float f = 0.f;
-                    if (i < cnt) {
-                        f = a.row_scale[pos0 + i];
-                        if (!GATE_UP) f *= a.route_weight[a.route_idx[pos0 + i]];
-                    }
-                    fac[q] = f;
+            for (int r = 0; r < 2; r++) glob[r] = f16_global_to_f32(a.global[(size_t)grp.x * a.N + wrow0 + r * kTileM]);
+            float fac[4];
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const int i = q * 32 + lane;
+                float f = 0.f;
+                if (i < cnt) {
+                    f = a.row_scale[pos0 + i];
+                    if (!GATE_UP) f *= a.route_weight[a.route_idx[pos0 + i]];
                 }
-                ok = mbar_wait(ACC_FULL(tile_seq & 1), (tile_seq >> 1) & 1, s_abort, a.err);
-                if (!ok) break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + kAccCol0 + (tile_seq & 1) * kTileTok;
-#pragma unroll
-                for (int c0 = 0; c0 < kTileTok; c0 += 16) {
-                    if (c0 < cnt) {     // uniform over the warp
+                fac[q] = f;
+            }
+            if (!mbar_wait(ACC_FULL, unit_i & 1, s_abort, a.err)) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+            for (int r = 0; r < 2; r++) {
+                const int wrow = wrow0 + r * kTileM;
+                const float gl = r ? glob[1] : glob[0];
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + kAccCol0 + r * kTileTok;
+#pragma unroll 1
+                for (int c0 = 0; c0 < cnt; c0 += 16) {      // uniform over the warp
+                    {
                         float v[16];
                         tmem_ld16(taddr + c0, v);
                         tmem_ld_wait();
+                        const float fq = c0 < 32 ? fac[0] : c0 < 64 ? fac[1] : c0 < 96 ? fac[2] : fac[3];
 #pragma unroll
-                        for (int j = 0; j < 16; j++)
-                            v[j] = (v[j] * glob) * __shfl_sync(0xffffffffu, fac[c0 >> 5], (c0 & 31) + j);
+                        for (int j = 0; j < 16; j++) v[j] = (v[j] * gl) * __shfl_sync(0xffffffffu, fq, (c0 & 31) + j);
                         if (GATE_UP || a.y_f32) {
                             float* const dst = GATE_UP ? a.ic1 : reinterpret_cast<float*>(a.y);
 #pragma unroll
@@ -510,10 +510,9 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
                         }
                     }
                 }
-                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                mbar_arrive(ACC_EMPTY(tile_seq & 1));
             }
-            if (!ok) break;
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(ACC_EMPTY);
         }
     }
     // drain: nobody frees tensor memory while another role may still touch it
@@ -541,13 +540,13 @@ EncodeTiledFn encode_tiled() {
     return fn;
 }
 
-// f16 matrix [rows, K] row-major, box = 64 k x 128 rows, 128-byte swizzle
-bool make_act_map(CUtensorMap* map, const void* base, size_t rows, int K) {
+// f16 matrix [rows, K] row-major, box = 64 k x box_rows, 128-byte swizzle
+bool make_act_map(CUtensorMap* map, const void* base, size_t rows, int K, int box_rows) {
     EncodeTiledFn fn = encode_tiled();
     if (!fn) return false;
     cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-    cuuint32_t box[2] = {(cuuint32_t)kStepK, (cuuint32_t)kTileTok};
+    cuuint32_t box[2] = {(cuuint32_t)kStepK, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -643,8 +642,8 @@ int launch_prefill_umma(const BankView& b, const void* x, int x_dtype, const Dec
         nbins = b.slots;
     }
     launches += launch_csr_build(bins_of_route, routes, nbins, sc.seg, sc.route_idx, sc.csr_scratch, sc.csr_flag, c);
-    // 2. passes of <= 256 sorted rows per expert
-    launches += launch_groups_from_csr(sc.seg, nbins, slot_of_bin, b.slots, 2 * kTileTok, sc.groups, sc.n_groups, c);
+    // 2. passes of <= 128 sorted rows per expert
+    launches += launch_groups_from_csr(sc.seg, nbins, slot_of_bin, b.slots, kTileTok, sc.groups, sc.n_groups, c);
     // 3. sorted, scaled f16 activations
     c.begin(K_PERMUTE_ACT);
     prefill_gather_kernel<<<routes, 256, 0, c.s>>>(x, x_dtype, sc.route_idx, sc.seg + nbins, top_k, b.hidden, sc.xg,
@@ -652,10 +651,14 @@ int launch_prefill_umma(const BankView& b, const void* x, int x_dtype, const Dec
     c.end();
     launches++;
 
-    CUtensorMap map_x, map_h, map_gp, map_gs, map_dp, map_ds;
+    XMaps map_x, map_h;
+    CUtensorMap map_gp, map_gs, map_dp, map_ds;
+    for (int q = 0; q < 4; q++)
+        if (!make_act_map(&map_x.m[q], sc.xg, (size_t)routes, b.hidden, 32 * (q + 1)) ||
+            !make_act_map(&map_h.m[q], sc.ic2h, (size_t)routes, b.inter, 32 * (q + 1)))
+            return -1;
     const size_t gu_rows = (size_t)b.slots * 2 * b.inter, dn_rows = (size_t)b.slots * b.hidden;
-    if (!make_act_map(&map_x, sc.xg, (size_t)routes, b.hidden) || !make_act_map(&map_h, sc.ic2h, (size_t)routes, b.inter) ||
-        !make_raw_map(&map_gp, b.gu_packed, gu_rows, b.hidden / 2, 64, kTileM, CU_TENSOR_MAP_SWIZZLE_64B) ||
+    if (!make_raw_map(&map_gp, b.gu_packed, gu_rows, b.hidden / 2, 64, kTileM, CU_TENSOR_MAP_SWIZZLE_64B) ||
         !make_raw_map(&map_gs, b.gu_scale, gu_rows, b.hidden / 16, 16, kTileM, CU_TENSOR_MAP_SWIZZLE_NONE) ||
         !make_raw_map(&map_dp, b.dn_packed, dn_rows, b.inter / 2, 64, kTileM, CU_TENSOR_MAP_SWIZZLE_64B) ||
         !make_raw_map(&map_ds, b.dn_scale, dn_rows, b.inter / 16, 16, kTileM, CU_TENSOR_MAP_SWIZZLE_NONE))
