@@ -7,17 +7,18 @@
 // the f16 row global applied once after the K reduction.
 //
 //   gather    the routes are sorted by expert (CSR); xg[i] = f16(x[token of route_idx[i]] * 2^-e) with a
-//             per-row power-of-two scale (exact, keeps any bf16 / f32 input inside the f16 range)
+//             per-row power-of-two scale (exact, keeps any bf16 / f32 input inside the f16 range); every
+//             8 k are stored as k0 k4 k1 k5 k2 k6 k3 k7, the order the weight unpack produces
 //   gemm      D[128 weight rows, n tokens] per unit = (pass of <= 128 sorted rows of one expert, tile of
 //             128 weight rows); persistent CTAs, 16 warps:
 //               warp 0      TMA: activation tiles [128 tokens x 64 k] f16, 128-byte swizzle (B operand)
 //               warp 2      TMA: packed weight rows (64-byte swizzle) and block scales into a raw ring
-//               warps 8..15 dequantise (hardware e2m1x2 / e4m3x2 -> f16x2, exact product with the block
+//               warps 8..23 dequantise (E2M1 -> f16 by shifts and masks, exact product with the block
 //                           scale) and store the f16 weights into tensor memory (tcgen05.st): they are the
 //                           A operand, one TMEM lane per weight row, so the dequantised weights never
 //                           cross shared memory
-//               warp 1      issues tcgen05.mma (M = 128, N = tokens rounded up to 16, K = 16 per
-//                           instruction, f16 x f16 -> f32 in TMEM), commits to mbarriers
+//               warps 1, 3  issue tcgen05.mma, one warp per row tile (M = 128, N = tokens rounded up to
+//                           16, K = 16 per instruction, f16 x f16 -> f32 in TMEM), commit to mbarriers
 //               warps 4..7  epilogue: tcgen05.ld of one of two accumulator sets while the next unit's
 //                           mainloop runs; a thread owns a weight row, so stores are coalesced over rows
 //             gate_up writes gate and up (globals and row scale applied) as f32; down applies global,
@@ -110,16 +111,23 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// Eight E2M1 codes of one packed word -> four f16x2 by integer operations only.  The hardware
+// conversion (cvt.rn.f16x2.e2m1x2) runs on the 16-lane conversion unit, which saturates long before
+// the tensor cores do; shifts and logic run four to eight times wider.  An E2M1 code s.ee.m placed
+// at f16 bits 15 | 11..9 reads as the code's value times 2^-14 (its 0.5 becomes an f16 subnormal),
+// so the factor 2^14 is applied later (kScaleBoost with the block scale, kAccBoost in the epilogue).
+// One shift serves the codes k_i and k_(i+4) of a word, so q[i] = (k_i, k_(i+4)): the activations are
+// stored in the matching order (kperm8).
 __device__ __forceinline__ void e2m1x8_to_f16x2(uint32_t w, uint32_t (&q)[4]) {
-    asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
-        "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
-        "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t"
-        "cvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
-        "cvt.rn.f16x2.e2m1x2 %2, b2;\n\t"
-        "cvt.rn.f16x2.e2m1x2 %3, b3;\n\t}"
-        : "=r"(q[0]), "=r"(q[1]), "=r"(q[2]), "=r"(q[3])
-        : "r"(w));
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const uint32_t t = (i < 3) ? (w << (9 - 4 * i)) : (w >> 3);
+        q[i] = (t & 0x0E000E00u) | ((t << 3) & 0x80008000u);
+    }
 }
+constexpr uint32_t kScaleBoostH2 = 0x58005800u;   // f16x2 (128, 128): block scales carry 2^7 of the 2^14
+constexpr float kAccBoost = 128.0f;               // the epilogue applies the remaining 2^7
+
 __device__ __forceinline__ uint32_t hmul2_f16(uint32_t a, uint32_t b) {
     uint32_t d;
     asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
@@ -168,15 +176,15 @@ prefill_gather_kernel(const void* __restrict__ x, int x_dtype, const int32_t* __
     for (int k = k0; k < K; k += 2048) {
         __half2 h[4];
 #pragma unroll
-        for (int q = 0; q < 4; q++) h[q] = __floats2half2_rn(v[2 * q] * inv, v[2 * q + 1] * inv);
+        for (int q = 0; q < 4; q++) h[q] = __floats2half2_rn(v[q] * inv, v[q + 4] * inv);   // kperm8
         *reinterpret_cast<uint4*>(xg + (size_t)i * K + k) =
             make_uint4(*reinterpret_cast<uint32_t*>(&h[0]), *reinterpret_cast<uint32_t*>(&h[1]),
                        *reinterpret_cast<uint32_t*>(&h[2]), *reinterpret_cast<uint32_t*>(&h[3]));
     }
 }
 
-// ic1 (f32, sorted rows: gate | up) -> ic2 = silu(gate) * up as f16 with a per-row power-of-two scale.
-// One warp per row; K == 512.
+// ic1 (f32, sorted rows: gate | up) -> ic2 = silu(gate) * up as f16 with a per-row power-of-two scale,
+// every 8 k stored in the order of the weight unpack (kperm8).  One warp per row; K == 512.
 __global__ void __launch_bounds__(256)
 prefill_rescale_kernel(const float* __restrict__ ic1, const int32_t* __restrict__ n_sorted, int K,
                        __half* __restrict__ ic2h, float* __restrict__ row_scale) {
@@ -185,15 +193,20 @@ prefill_rescale_kernel(const float* __restrict__ ic1, const int32_t* __restrict_
     float v[16];
     float m = 0.f;
 #pragma unroll
-    for (int c = 0; c < 4; c++) {
-        const float4 g = *reinterpret_cast<const float4*>(ic1 + (size_t)row * 2 * K + c * 128 + lane * 4);
-        const float4 u = *reinterpret_cast<const float4*>(ic1 + (size_t)row * 2 * K + K + c * 128 + lane * 4);
-        v[4 * c] = (g.x / (1.0f + __expf(-g.x))) * u.x;
-        v[4 * c + 1] = (g.y / (1.0f + __expf(-g.y))) * u.y;
-        v[4 * c + 2] = (g.z / (1.0f + __expf(-g.z))) * u.z;
-        v[4 * c + 3] = (g.w / (1.0f + __expf(-g.w))) * u.w;
+    for (int c = 0; c < 2; c++) {
+        const float* g = ic1 + (size_t)row * 2 * K + c * 256 + lane * 8;
 #pragma unroll
-        for (int q = 0; q < 4; q++) m = fmaxf(m, fabsf(v[4 * c + q]));
+        for (int h = 0; h < 2; h++) {
+            const float4 gv = *reinterpret_cast<const float4*>(g + 4 * h);
+            const float4 uv = *reinterpret_cast<const float4*>(g + K + 4 * h);
+            float* o = v + 8 * c + 4 * h;
+            o[0] = (gv.x / (1.0f + __expf(-gv.x))) * uv.x;
+            o[1] = (gv.y / (1.0f + __expf(-gv.y))) * uv.y;
+            o[2] = (gv.z / (1.0f + __expf(-gv.z))) * uv.z;
+            o[3] = (gv.w / (1.0f + __expf(-gv.w))) * uv.w;
+        }
+#pragma unroll
+        for (int q = 0; q < 8; q++) m = fmaxf(m, fabsf(v[8 * c + q]));
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
@@ -204,11 +217,13 @@ prefill_rescale_kernel(const float* __restrict__ ic1, const int32_t* __restrict_
         sc = __uint_as_float((uint32_t)(127 - 14 + (e - 127)) << 23);
     }
 #pragma unroll
-    for (int c = 0; c < 4; c++) {
-        __half2 a = __floats2half2_rn(v[4 * c] * inv, v[4 * c + 1] * inv);
-        __half2 b = __floats2half2_rn(v[4 * c + 2] * inv, v[4 * c + 3] * inv);
-        *reinterpret_cast<uint2*>(ic2h + (size_t)row * K + c * 128 + lane * 4) =
-            make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+    for (int c = 0; c < 2; c++) {
+        __half2 h[4];
+#pragma unroll
+        for (int q = 0; q < 4; q++) h[q] = __floats2half2_rn(v[8 * c + q] * inv, v[8 * c + q + 4] * inv);   // kperm8
+        *reinterpret_cast<uint4*>(ic2h + (size_t)row * K + c * 256 + lane * 8) =
+            make_uint4(*reinterpret_cast<uint32_t*>(&h[0]), *reinterpret_cast<uint32_t*>(&h[1]),
+                       *reinterpret_cast<uint32_t*>(&h[2]), *reinterpret_cast<uint32_t*>(&h[3]));
     }
     if (lane == 0) row_scale[row] = sc;
 }
@@ -229,7 +244,7 @@ struct UmmaArgs {
 };
 
 // warp roles of the GEMM CTA (24 warps)
-constexpr int kWarpActTma = 0, kWarpMma = 1, kWarpRawTma = 2, kWarpEpi0 = 4, kWarpDeq0 = 8;
+constexpr int kWarpActTma = 0, kWarpMma = 1, kWarpRawTma = 2, kWarpMma1 = 3, kWarpEpi0 = 4, kWarpDeq0 = 8;
 constexpr int kEpiWarps = 4;
 constexpr int kDeqSets = 4;                    // dequantiser sets of 4 warps (128 threads = 128 weight rows)
 constexpr int kRawStages = 6;
@@ -292,7 +307,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
     if (threadIdx.x == 0) {
         for (int s = 0; s < kXStages; s++) {
             mbar_init(X_FULL(s), 1);
-            mbar_init(X_EMPTY(s), 1);
+            mbar_init(X_EMPTY(s), 2);
         }
         for (int s = 0; s < kRawStages; s++) {
             mbar_init(RAW_FULL(s), 1);
@@ -302,7 +317,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
             mbar_init(W_READY(s), 128);
             mbar_init(W_FREE(s), 1);
         }
-        mbar_init(ACC_FULL, 1);
+        mbar_init(ACC_FULL, 2);
         mbar_init(ACC_EMPTY, kEpiWarps * 32);
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -363,10 +378,14 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
                 if (!ok) break;
             }
         }
-    } else if (warp == kWarpMma) {
-        // ===================== MMA issuer ======================================================
+    } else if (warp == kWarpMma || warp == kWarpMma1) {
+        // ===================== MMA issuers: one warp per row tile =================================
+        // issuing a tcgen05.mma costs the issuing thread tens of cycles, more than the math of a small
+        // token tile takes; two issuers on two schedulers keep the tensor pipe fed
         if (lane == 0) {
-            uint32_t it = 0, item = 0, unit_i = 0;
+            const int r = (warp == kWarpMma) ? 0 : 1;
+            const uint32_t d_tmem = tmem_base + kAccCol0 + r * kTileTok;
+            uint32_t it = 0, item = r, unit_i = 0;
             for (int u = blockIdx.x; u < n_units && !*s_abort; u += gridDim.x, unit_i++) {
                 const int4 grp = a.groups[u / n_pairs];
                 const int n_pad = max(16, (grp.z + 15) & ~15);
@@ -374,26 +393,22 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
                 // the accumulators must have been read back
                 bool ok = mbar_wait(ACC_EMPTY, (unit_i & 1) ^ 1, s_abort, a.err);
                 for (int c = 0; c < kChunks && ok; c++, item += 2) {
-                    const int wb0 = item % kWBufs;                 // row tile 0; row tile 1 is the next buffer
-                    ok = mbar_wait(W_READY(wb0), (item / kWBufs) & 1, s_abort, a.err);
-                    if (ok) ok = mbar_wait(W_READY(wb0 + 1), (item / kWBufs) & 1, s_abort, a.err);
+                    const int wb = item % kWBufs;
+                    ok = mbar_wait(W_READY(wb), (item / kWBufs) & 1, s_abort, a.err);
+                    const uint32_t w_addr = tmem_base + wb * kWCols;
                     for (int h = 0; h < 2 && ok; h++, it++) {
                         const int st = it % kXStages;
                         ok = mbar_wait(X_FULL(st), (it / kXStages) & 1, s_abort, a.err);
                         if (!ok) break;
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                        const uint32_t x_addr = smem_u32(x_tiles + (size_t)st * kTileBytes);
+                        const uint64_t xdesc = umma_desc(smem_u32(x_tiles + (size_t)st * kTileBytes));
 #pragma unroll
-                        for (int r = 0; r < 2; r++)
-#pragma unroll
-                            for (int kk = 0; kk < 4; kk++)
-                                umma_f16_ts(tmem_base + kAccCol0 + r * kTileTok, tmem_base + (wb0 + r) * kWCols + (h * 4 + kk) * 8,
-                                            umma_desc(x_addr + kk * 32), idesc, (c > 0 || h > 0 || kk > 0) ? 1u : 0u);
-                        umma_commit(X_EMPTY(st));        // the activation stage is free once these MMAs retire
+                        for (int kk = 0; kk < 4; kk++)
+                            umma_f16_ts(d_tmem, w_addr + (h * 4 + kk) * 8, xdesc + kk * 2, idesc, (c > 0 || h > 0 || kk > 0) ? 1u : 0u);
+                        umma_commit(X_EMPTY(st));        // the activation stage is free once both issuers' MMAs retire
                     }
                     if (!ok) break;
-                    umma_commit(W_FREE(wb0));            // and so are the two weight buffers
-                    umma_commit(W_FREE(wb0 + 1));
+                    umma_commit(W_FREE(wb));             // and so is the weight buffer
                 }
                 if (!ok) break;
                 umma_commit(ACC_FULL);
@@ -430,6 +445,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
                     const uint32_t two = ((g & 2) ? sc8.y : sc8.x) >> ((g & 1) * 16);
                     uint32_t h2;
                     asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"((uint16_t)(two & 0xffffu)));
+                    h2 = hmul2_f16(h2, kScaleBoostH2);
                     const uint32_t s0 = __byte_perm(h2, h2, 0x1010), s1 = __byte_perm(h2, h2, 0x3232);
                     const uint32_t wd[4] = {raw[g].x, raw[g].y, raw[g].z, raw[g].w};
                     uint32_t r[16];
@@ -461,7 +477,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
             const int wrow0 = (u % n_pairs) * 2 * kTileM + quarter * 32 + lane;
             float glob[2];
 #pragma unroll
-            for (int r = 0; r < 2; r++) glob[r] = f16_global_to_f32(a.global[(size_t)grp.x * a.N + wrow0 + r * kTileM]);
+            for (int r = 0; r < 2; r++) glob[r] = kAccBoost * f16_global_to_f32(a.global[(size_t)grp.x * a.N + wrow0 + r * kTileM]);
             float fac[4];
 #pragma unroll
             for (int q = 0; q < 4; q++) {
