@@ -7,13 +7,12 @@
 // the f16 row global applied once after the K reduction.
 //
 //   gather    the routes are sorted by expert (CSR); xg[i] = f16(x[token of route_idx[i]] * 2^-e) with a
-//             per-row power-of-two scale (exact, keeps any bf16 / f32 input inside the f16 range); every
-//             8 k are stored as k0 k4 k1 k5 k2 k6 k3 k7, the order the weight unpack produces
+//             per-row power-of-two scale (exact, keeps any bf16 / f32 input inside the f16 range)
 //   gemm      D[128 weight rows, n tokens] per unit = (pass of <= 128 sorted rows of one expert, tile of
 //             128 weight rows); persistent CTAs, 16 warps:
 //               warp 0      TMA: activation tiles [128 tokens x 64 k] f16, 128-byte swizzle (B operand)
 //               warp 2      TMA: packed weight rows (64-byte swizzle) and block scales into a raw ring
-//               warps 8..23 dequantise (E2M1 -> f16 by shifts and masks, exact product with the block
+//               warps 8..23 dequantise (hardware e2m1x2 / e4m3x2 -> f16x2, exact product with the block
 //                           scale) and store the f16 weights into tensor memory (tcgen05.st): they are the
 //                           A operand, one TMEM lane per weight row, so the dequantised weights never
 //                           cross shared memory
@@ -40,7 +39,7 @@ constexpr int kTileTok = 128; // most tokens per pass (MMA N <= 128, one TMEM co
 constexpr int kStepK = 64;    // k per pipeline step: one 128-byte swizzle atom of f16
 constexpr int kXStages = 8;
 constexpr int kTileBytes = kTileTok * kStepK * 2;  // 16 KiB activation tile
-constexpr int kThreads = 768;
+constexpr int kThreads = 896;
 constexpr uint32_t kSpin = 1u << 20;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -111,23 +110,19 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// Eight E2M1 codes of one packed word -> four f16x2 by integer operations only.  The hardware
-// conversion (cvt.rn.f16x2.e2m1x2) runs on the 16-lane conversion unit, which saturates long before
-// the tensor cores do; shifts and logic run four to eight times wider.  An E2M1 code s.ee.m placed
-// at f16 bits 15 | 11..9 reads as the code's value times 2^-14 (its 0.5 becomes an f16 subnormal),
-// so the factor 2^14 is applied later (kScaleBoost with the block scale, kAccBoost in the epilogue).
-// One shift serves the codes k_i and k_(i+4) of a word, so q[i] = (k_i, k_(i+4)): the activations are
-// stored in the matching order (kperm8).
+// Eight E2M1 codes of one packed word -> four f16x2, one hardware conversion per byte.  Byte b holds
+// k = 2b (low nibble, low half of the result) and k = 2b + 1.  (An integer-only unpack, shifts and masks
+// into the f16 exponent field, was measured: same speed within 3 %, twice the instructions.)
 __device__ __forceinline__ void e2m1x8_to_f16x2(uint32_t w, uint32_t (&q)[4]) {
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        const uint32_t t = (i < 3) ? (w << (9 - 4 * i)) : (w >> 3);
-        q[i] = (t & 0x0E000E00u) | ((t << 3) & 0x80008000u);
-    }
+    asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+        "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %2, b2;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %3, b3;\n\t}"
+        : "=r"(q[0]), "=r"(q[1]), "=r"(q[2]), "=r"(q[3])
+        : "r"(w));
 }
-constexpr uint32_t kScaleBoostH2 = 0x58005800u;   // f16x2 (128, 128): block scales carry 2^7 of the 2^14
-constexpr float kAccBoost = 128.0f;               // the epilogue applies the remaining 2^7
-
 __device__ __forceinline__ uint32_t hmul2_f16(uint32_t a, uint32_t b) {
     uint32_t d;
     asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
@@ -176,15 +171,15 @@ prefill_gather_kernel(const void* __restrict__ x, int x_dtype, const int32_t* __
     for (int k = k0; k < K; k += 2048) {
         __half2 h[4];
 #pragma unroll
-        for (int q = 0; q < 4; q++) h[q] = __floats2half2_rn(v[q] * inv, v[q + 4] * inv);   // kperm8
+        for (int q = 0; q < 4; q++) h[q] = __floats2half2_rn(v[2 * q] * inv, v[2 * q + 1] * inv);
         *reinterpret_cast<uint4*>(xg + (size_t)i * K + k) =
             make_uint4(*reinterpret_cast<uint32_t*>(&h[0]), *reinterpret_cast<uint32_t*>(&h[1]),
                        *reinterpret_cast<uint32_t*>(&h[2]), *reinterpret_cast<uint32_t*>(&h[3]));
     }
 }
 
-// ic1 (f32, sorted rows: gate | up) -> ic2 = silu(gate) * up as f16 with a per-row power-of-two scale,
-// every 8 k stored in the order of the weight unpack (kperm8).  One warp per row; K == 512.
+// ic1 (f32, sorted rows: gate | up) -> ic2 = silu(gate) * up as f16 with a per-row power-of-two scale.
+// One warp per row; K == 512.
 __global__ void __launch_bounds__(256)
 prefill_rescale_kernel(const float* __restrict__ ic1, const int32_t* __restrict__ n_sorted, int K,
                        __half* __restrict__ ic2h, float* __restrict__ row_scale) {
@@ -220,7 +215,7 @@ prefill_rescale_kernel(const float* __restrict__ ic1, const int32_t* __restrict_
     for (int c = 0; c < 2; c++) {
         __half2 h[4];
 #pragma unroll
-        for (int q = 0; q < 4; q++) h[q] = __floats2half2_rn(v[8 * c + q] * inv, v[8 * c + q + 4] * inv);   // kperm8
+        for (int q = 0; q < 4; q++) h[q] = __floats2half2_rn(v[8 * c + 2 * q] * inv, v[8 * c + 2 * q + 1] * inv);
         *reinterpret_cast<uint4*>(ic2h + (size_t)row * K + c * 256 + lane * 8) =
             make_uint4(*reinterpret_cast<uint32_t*>(&h[0]), *reinterpret_cast<uint32_t*>(&h[1]),
                        *reinterpret_cast<uint32_t*>(&h[2]), *reinterpret_cast<uint32_t*>(&h[3]));
@@ -245,7 +240,8 @@ struct UmmaArgs {
 
 // warp roles of the GEMM CTA (24 warps)
 constexpr int kWarpActTma = 0, kWarpMma = 1, kWarpRawTma = 2, kWarpMma1 = 3, kWarpEpi0 = 4, kWarpDeq0 = 8;
-constexpr int kEpiWarps = 4;
+constexpr int kEpiWarps = 8;          // warps 4..7 read row tile 0, warps 24..27 row tile 1
+constexpr int kWarpEpi1 = 24;
 constexpr int kDeqSets = 4;                    // dequantiser sets of 4 warps (128 threads = 128 weight rows)
 constexpr int kRawStages = 6;
 constexpr int kRawPackedBytes = kTileM * 64;   // one chunk of 128 k: 128 weight rows x 64 bytes, 64-byte swizzle
@@ -414,7 +410,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
                 umma_commit(ACC_FULL);
             }
         }
-    } else if (warp >= kWarpDeq0) {
+    } else if (warp >= kWarpDeq0 && warp < kWarpEpi1) {
         // ===================== dequantisers: raw ring -> f16 weights in tensor memory ================
         // Four sets of four warps; set s takes the pieces w = s (mod 4) of every unit (w = 2 * chunk +
         // row tile) and owns weight buffer s.  Warp quarter q may touch TMEM lanes 32q..32q+31; a thread
@@ -445,7 +441,6 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
                     const uint32_t two = ((g & 2) ? sc8.y : sc8.x) >> ((g & 1) * 16);
                     uint32_t h2;
                     asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"((uint16_t)(two & 0xffffu)));
-                    h2 = hmul2_f16(h2, kScaleBoostH2);
                     const uint32_t s0 = __byte_perm(h2, h2, 0x1010), s1 = __byte_perm(h2, h2, 0x3232);
                     const uint32_t wd[4] = {raw[g].x, raw[g].y, raw[g].z, raw[g].w};
                     uint32_t r[16];
@@ -466,18 +461,17 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
             if (!ok) break;
         }
     } else if (warp >= kWarpEpi0) {
-        // ===================== epilogue (warps 4..7: TMEM lane quarters 0..3) =======================
-        // one thread = one weight row of each row tile; a column = one token of the group.  Lane l keeps
+        // ===================== epilogue (warps 4..7 and 24..27: TMEM lane quarters 0..3) ==============
+        // one thread = one weight row of its row tile; a column = one token of the group.  Lane l keeps
         // the per-token factors of tokens l, l + 32, l + 64, l + 96 and hands them out by shuffle.
         const int quarter = warp & 3;
         uint32_t unit_i = 0;
         for (int u = blockIdx.x; u < n_units && !*s_abort; u += gridDim.x, unit_i++) {
             const int4 grp = a.groups[u / n_pairs];
             const int cnt = grp.z, pos0 = grp.y;
-            const int wrow0 = (u % n_pairs) * 2 * kTileM + quarter * 32 + lane;
-            float glob[2];
-#pragma unroll
-            for (int r = 0; r < 2; r++) glob[r] = kAccBoost * f16_global_to_f32(a.global[(size_t)grp.x * a.N + wrow0 + r * kTileM]);
+            const int r = (warp >= kWarpEpi1) ? 1 : 0;
+            const int wrow = (u % n_pairs) * 2 * kTileM + r * kTileM + quarter * 32 + lane;
+            const float gl = f16_global_to_f32(a.global[(size_t)grp.x * a.N + wrow]);
             float fac[4];
 #pragma unroll
             for (int q = 0; q < 4; q++) {
@@ -491,10 +485,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
             }
             if (!mbar_wait(ACC_FULL, unit_i & 1, s_abort, a.err)) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll 1
-            for (int r = 0; r < 2; r++) {
-                const int wrow = wrow0 + r * kTileM;
-                const float gl = r ? glob[1] : glob[0];
+            {
                 const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + kAccCol0 + r * kTileTok;
 #pragma unroll 1
                 for (int c0 = 0; c0 < cnt; c0 += 16) {      // uniform over the warp
