@@ -284,10 +284,127 @@ router_topk_kernel(const float* __restrict__ logits, int tokens, int experts, in
     }
 }
 
+
+// ---- wide variant for large batches --------------------------------------------------------
+// CTA = 4 warps, tile = 64 experts x 32 tokens; a lane owns experts lane and lane + 32, a warp 8 tokens:
+// 16 independent chains per thread and 10 shared-memory loads per 64 FMAs, so the kernel is bound by the
+// FP32 pipe instead of by load issue.  Every chain still walks k in order with one fma per k.
+constexpr int kBE = 64, kBT = 32, kBK = 128;
+constexpr int kBWStride = kBK * 2 + 16;
+
+__global__ void __launch_bounds__(128, 2)
+router_logits_wide_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gate_w,
+                          int tokens, int experts, int hidden, float* __restrict__ logits) {
+    extern __shared__ __align__(16) uint8_t rsm[];
+    uint8_t* const wbuf = rsm;                                               // [2][64][kBWStride]
+    float* const xbuf = reinterpret_cast<float*>(rsm + 2 * kBE * kBWStride);  // [2][kBK][32]
+    const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+    const int e0 = blockIdx.x * kBE, t0 = blockIdx.y * kBT;
+    const int nchunks = hidden / kBK;
+    const uint32_t wbase = (uint32_t)__cvta_generic_to_shared(wbuf);
+
+    auto issue_w = [&](int c, int b) {
+        for (int i = tid; i < kBE * (kBK / 8); i += 128) {
+            const int row = i / (kBK / 8), piece = i % (kBK / 8);
+            const int e = min(e0 + row, experts - 1);
+            cp_async16(wbase + b * kBE * kBWStride + row * kBWStride + piece * 16,
+                       gate_w + (size_t)e * hidden + c * kBK + piece * 8);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    // activations: thread -> token lane, 16-byte pieces warp + 4 * i
+    uint4 xr[4];
+    auto load_x = [&](int c) {
+        const int t = t0 + lane;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            xr[i] = make_uint4(0, 0, 0, 0);
+            if (t < tokens) xr[i] = *reinterpret_cast<const uint4*>(x + (size_t)t * hidden + c * kBK + (warp + 4 * i) * 8);
+        }
+    };
+    auto store_x = [&](int b) {
+        float* xs = xbuf + b * kBK * kBT;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int k = (warp + 4 * i) * 8;
+            const uint32_t w[4] = {xr[i].x, xr[i].y, xr[i].z, xr[i].w};
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const float2 v = bf16x2_to_f32(w[q]);
+                xs[(k + 2 * q) * kBT + lane] = v.x;
+                xs[(k + 2 * q + 1) * kBT + lane] = v.y;
+            }
+        }
+    };
+
+    issue_w(0, 0);
+    load_x(0);
+    store_x(0);
+    float acc[2][8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) acc[0][i] = acc[1][i] = 0.f;
+    for (int c = 0; c < nchunks; c++) {
+        const int b = c & 1;
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        if (c + 1 < nchunks) {
+            issue_w(c + 1, b ^ 1);
+            load_x(c + 1);
+        }
+        const uint32_t wrow = wbase + b * kBE * kBWStride + lane * kBWStride;
+        const float* xs = xbuf + b * kBK * kBT + warp * 8;
+#pragma unroll 4
+        for (int kk = 0; kk < kBK; kk += 4) {
+            uint2 wa, wb;
+            asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(wa.x), "=r"(wa.y) : "r"(wrow + kk * 2));
+            asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(wb.x), "=r"(wb.y) : "r"(wrow + 32 * kBWStride + kk * 2));
+            const float2 a01 = bf16x2_to_f32(wa.x), a23 = bf16x2_to_f32(wa.y);
+            const float2 b01 = bf16x2_to_f32(wb.x), b23 = bf16x2_to_f32(wb.y);
+            const float wa4[4] = {a01.x, a01.y, a23.x, a23.y}, wb4[4] = {b01.x, b01.y, b23.x, b23.y};
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const float4 x0 = *reinterpret_cast<const float4*>(xs + (kk + q) * kBT);
+                const float4 x1 = *reinterpret_cast<const float4*>(xs + (kk + q) * kBT + 4);
+                const float xv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    acc[0][i] = __fmaf_rn(xv[i], wa4[q], acc[0][i]);
+                    acc[1][i] = __fmaf_rn(xv[i], wb4[q], acc[1][i]);
+                }
+            }
+        }
+        if (c + 1 < nchunks) store_x(b ^ 1);
+    }
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        const int e = e0 + lane + 32 * h;
+        if (e < experts) {
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const int t = t0 + warp * 8 + i;
+                if (t < tokens) logits[(size_t)t * experts + e] = acc[h][i];
+            }
+        }
+    }
+}
+
 }  // namespace
 
 int launch_router_logits(const __nv_bfloat16* x, const __nv_bfloat16* gate_w, int tokens, int experts,
                          int hidden, float* logits, const Ctx& c) {
+    if (hidden % kBK == 0 && tokens >= 1024) {
+        dim3 grid((experts + kBE - 1) / kBE, (tokens + kBT - 1) / kBT);
+        const size_t smem = 2 * kBE * kBWStride + 2 * kBK * kBT * sizeof(float);
+        static bool attr3 = false;
+        if (!attr3) {
+            cudaFuncSetAttribute(router_logits_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            attr3 = true;
+        }
+        c.begin(K_ROUTER_LOGITS);
+        router_logits_wide_kernel<<<grid, 128, smem, c.s>>>(x, gate_w, tokens, experts, hidden, logits);
+        c.end();
+        return 1;
+    }
     if (hidden % kKC == 0) {
         dim3 grid((experts + kTileE - 1) / kTileE, (tokens + kTileT - 1) / kTileT);
         const size_t smem = 2 * kTileE * kWStride + 2 * kKC * kTileT * sizeof(float);

@@ -92,7 +92,7 @@ def test_router_ids_bit_exact_small(small, tokens):
     assert np.array_equal(w.cpu().numpy(), want_w), "same operations in the same order: weights are bit-equal too"
 
 
-@pytest.mark.parametrize("tokens", [1, 16, 64, 512])
+@pytest.mark.parametrize("tokens", [1, 16, 64, 512, 1100])
 def test_router_ids_bit_exact_full(full, tokens):
     lay, moe, ol = full
     xb = pkg.synth.make_x(100 + tokens, tokens, lay.hidden)
