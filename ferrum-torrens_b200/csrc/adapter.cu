@@ -802,7 +802,8 @@ static int shared_locked(ftm_handle* h, const void* x, int32_t tokens, const voi
         return fail(h, FTM_ERR_BAD, "moe: shared expert: %d tokens (max_tokens %d)", tokens, h->cfg.max_tokens);
     h->launches += launch_shared_expert((const __nv_bfloat16*)x, tokens, h->cfg.hidden, h->cfg.shared_inter,
                                         (const __nv_bfloat16*)gate_up, (const __nv_bfloat16*)down,
-                                        (const __nv_bfloat16*)shared_gate, h->ic2s, shared_out, se_gate_out, h->ctx(s));
+                                        (const __nv_bfloat16*)shared_gate, h->ic2s, shared_out, se_gate_out, h->flags + 2,
+                                        h->ctx(s));
     CU(h, cudaGetLastError());
     return FTM_OK;
 }

@@ -118,7 +118,12 @@ int launch_prefill_umma(const BankView& b, const void* x, int x_dtype, const Dec
 int launch_shared_expert(const __nv_bfloat16* x, int tokens, int hidden, int shared_inter,
                          const __nv_bfloat16* gate_up, const __nv_bfloat16* down,
                          const __nv_bfloat16* shared_gate, float* ic2s, float* shared_out,
-                         float* se_gate, const Ctx& c);
+                         float* se_gate, int32_t* err, const Ctx& c);
+// shared_umma.cu: the same on tcgen05 tensor cores, for batches of 256 tokens and more
+bool shared_umma_supported(int tokens, int hidden, int shared_inter);
+int launch_shared_umma(const __nv_bfloat16* x, int tokens, int hidden, int shared_inter, const __nv_bfloat16* gate_up,
+                       const __nv_bfloat16* down, const __nv_bfloat16* shared_gate, __nv_bfloat16* ic2b, float* shared_out,
+                       float* se_gate, int32_t* err, const Ctx& c);
 
 // combine.cu
 int launch_sum_routes(const float* yroute, int tokens, int top_k, int hidden, const float* shared,

@@ -29,10 +29,13 @@
 #include <cuda.h>
 
 #include "kernels.cuh"
+#include "umma.cuh"
 
 namespace ftm {
 
 namespace {
+
+using namespace umma;
 
 constexpr int kTileM = 128;   // weight rows per tile (MMA M, one TMEM lane per row)
 constexpr int kTileTok = 128; // most tokens per pass (MMA N <= 128, one TMEM column per token)
@@ -40,75 +43,9 @@ constexpr int kStepK = 64;    // k per pipeline step: one 128-byte swizzle atom 
 constexpr int kXStages = 8;
 constexpr int kTileBytes = kTileTok * kStepK * 2;  // 16 KiB activation tile
 constexpr int kThreads = 896;
-constexpr uint32_t kSpin = 1u << 20;
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// bounded wait: false after kSpin polls or once another role has raised the abort flag
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* err) {
-    for (uint32_t i = 0; i < kSpin; i++) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 1023u) == 1023u && *abort_flag) return false;
-    }
-    *abort_flag = 1;
-    atomicExch(err, 3);
-    return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
-        "l"(map), "r"(c0), "r"(c1), "r"(bar)
-        : "memory");
-}
-
-// shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128 bytes, 8-row groups
-// 1024 bytes apart
-__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((saddr & 0x3ffffu) >> 4);   // start address
-    d |= (uint64_t)1 << 16;                      // leading byte offset (unused with 128B swizzle)
-    d |= (uint64_t)(1024 >> 4) << 32;            // stride byte offset between 8-row groups
-    d |= (uint64_t)1 << 46;                      // descriptor version
-    d |= (uint64_t)2 << 61;                      // 128-byte swizzle
-    return d;
-}
 // instruction descriptor: f16 x f16 -> f32, both operands K-major, M = 128; N (bits 17..22, N >> 3) per unit
 constexpr uint32_t kIdescBase = (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(kTileM >> 4) << 24);
 
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
-    uint32_t r[16];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr));
-#pragma unroll
-    for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Eight E2M1 codes of one packed word -> four f16x2, one hardware conversion per byte.  Byte b holds
 // k = 2b (low nibble, low half of the result) and k = 2b + 1.  (An integer-only unpack, shifts and masks
@@ -250,23 +187,6 @@ constexpr int kRawStageBytes = kRawPackedBytes + kRawScaleBytes;
 constexpr int kWBufs = kDeqSets;               // dequantised weight chunks in tensor memory, 64 columns each
 constexpr int kWCols = 64;
 constexpr int kAccCol0 = kWBufs * kWCols;      // accumulators: a ring of two tiles of 128 f32 columns behind them
-
-__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
-                                            uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
-        "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
-        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
-        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-        : "memory");
-}
 
 // activation tile maps by box height: 32, 64, 96 or 128 token rows, so that a small group does not
 // pull 128 rows through L2
@@ -532,20 +452,6 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
 
 constexpr size_t kUmmaSmem = 1024 + (size_t)kXStages * kTileBytes + (size_t)kRawStages * kRawStageBytes + 40 * 8 + 64;
 static_assert(kUmmaSmem <= 227 * 1024, "shared memory of the grouped GEMM CTA");
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled() {
-    static EncodeTiledFn fn = [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) p = nullptr;
-        return reinterpret_cast<EncodeTiledFn>(p);
-    }();
-    return fn;
-}
 
 // f16 matrix [rows, K] row-major, box = 64 k x box_rows, 128-byte swizzle
 bool make_act_map(CUtensorMap* map, const void* base, size_t rows, int K, int box_rows) {

@@ -253,7 +253,12 @@ shared_phase2_mma_kernel(const __nv_bfloat16* __restrict__ ic2b, int tokens, int
 int launch_shared_expert(const __nv_bfloat16* x, int tokens, int hidden, int shared_inter,
                          const __nv_bfloat16* gate_up, const __nv_bfloat16* down,
                          const __nv_bfloat16* shared_gate, float* ic2s, float* shared_out, float* se_gate,
-                         const Ctx& c) {
+                         int32_t* err, const Ctx& c) {
+    if (shared_umma_supported(tokens, hidden, shared_inter)) {
+        const int n = launch_shared_umma(x, tokens, hidden, shared_inter, gate_up, down, shared_gate,
+                                         reinterpret_cast<__nv_bfloat16*>(ic2s), shared_out, se_gate, err, c);
+        if (n >= 0) return n;
+    }
     // tensor-core path: K splits must be multiples of 32
     if (hidden % 256 == 0 && shared_inter % 64 == 0 && hidden % 16 == 0 && shared_inter % 8 == 0) {
         __nv_bfloat16* ic2b = reinterpret_cast<__nv_bfloat16*>(ic2s);

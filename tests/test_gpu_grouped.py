@@ -2,7 +2,7 @@
 
 Same bars as the decode path: the permutation is exact by construction (the CSR tests cover it), outputs
 are compared with the f32 restatement of the reference's host path (src/domain/expert_kernel.rs:547-618).
-The cases cover: one token, fewer tokens than one accumulator tile, experts cut into several passes of 256
+The cases cover: one token, fewer tokens than one accumulator tile, experts cut into several passes of 128
 rows (tokens all routed to a few experts), experts that are not resident, f32 and bf16 activations and
 outputs, and ids given as i64.
 """
@@ -79,8 +79,8 @@ def test_grouped_path_matches_cpu_path(layer, tokens):
 
 
 def test_hot_experts_take_several_passes_and_tiles(layer):
-    """700 tokens over 12 experts: ~467 routes per expert, i.e. two passes of <= 256 rows, both accumulator
-    tiles in use, ragged last tile."""
+    """700 tokens over 12 experts: ~467 routes per expert, i.e. four passes of <= 128 rows with a ragged last
+    pass."""
     lay, moe, banks = layer
     rng = np.random.default_rng(3)
     tokens = 700
@@ -130,3 +130,44 @@ def test_experts_that_are_not_resident_contribute_nothing():
                                       ids.reshape(-1), w_res.reshape(-1))
     assert rel_l2(got, want) < 1e-3
     moe.close()
+
+
+@pytest.mark.parametrize("tokens", [256, 300, 700])
+def test_shared_expert_on_tensor_memory_path(layer, tokens):
+    """256 tokens and more: the shared expert runs as two tcgen05 GEMMs (ic2 crosses as a bf16 hi + lo pair).
+    Ragged last tile at 300 and 700 tokens."""
+    lay, moe, banks = layer
+    ol = o.Layer(lay.hidden, lay.inter, lay.experts, lay.top_k, lay.shared_inter, lay.gate_w, lay.sh_gate_up,
+                 lay.sh_down, lay.sh_gate, banks)
+    xb = pkg.synth.make_x(1000 + tokens, tokens, lay.hidden)
+    xf = pkg.synth.bf16_bits_to_f32(xb)
+    shared, gate = moe.shared_expert(bf16_dev(xb), bf16_dev(lay.sh_gate_up), bf16_dev(lay.sh_down), bf16_dev(lay.sh_gate))
+    moe.sync_status()
+    want = o.shared_expert(ol, xf)
+    got = shared.cpu().numpy()
+    assert rel_l2(got, want) <= 2e-4
+    assert np.abs(got - want).max() <= 2e-4 * np.abs(want).max()
+    g = o.bf16_gemm(xf, lay.sh_gate, tokens, 1, lay.hidden).reshape(-1)
+    want_gate = 1.0 / (1.0 + np.exp(-g.astype(np.float64)))
+    assert np.abs(gate.cpu().numpy() - want_gate).max() <= 1e-5
+
+
+def test_whole_block_512_tokens_against_cpu_path(layer):
+    """Router, grouped GEMM, tcgen05 shared expert and combine in one call, against the CPU checker's block."""
+    lay, moe, banks = layer
+    ol = o.Layer(lay.hidden, lay.inter, lay.experts, lay.top_k, lay.shared_inter, lay.gate_w, lay.sh_gate_up,
+                 lay.sh_down, lay.sh_gate, banks)
+    tokens = 512
+    xb = pkg.synth.make_x(4243, tokens, lay.hidden)
+    out = torch.empty((tokens, lay.hidden), dtype=torch.bfloat16, device=dev())
+    ids = torch.empty((tokens, lay.top_k), dtype=torch.int32, device=dev())
+    w = torch.empty((tokens, lay.top_k), dtype=torch.float32, device=dev())
+    moe.moe_block(0, bf16_dev(xb), bf16_dev(lay.gate_w), bf16_dev(lay.sh_gate_up), bf16_dev(lay.sh_down),
+                  bf16_dev(lay.sh_gate), out, ids_out=ids, weights_out=w)
+    moe.sync_status()
+    want, want_ids, want_w = o.moe_block(ol, pkg.synth.bf16_bits_to_f32(xb), threads=o.max_threads())
+    assert np.array_equal(ids.cpu().numpy(), want_ids), "routed expert ids must be bit-exact"
+    assert np.abs(w.cpu().numpy() - want_w).max() <= 1e-6
+    got = out.float().cpu().numpy()
+    assert rel_l2(got, want) <= 1e-2
+    assert np.abs(got - want).max() <= 2e-2 * np.abs(want).max()
