@@ -52,6 +52,8 @@ def parse():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--sweep", action="store_true", help="also report T = 1, 8, 512, 2048")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--path", default="auto", choices=["auto", "gemv", "grouped", "scalar"],
+                    help="routed-expert kernels: auto = decode kernels up to 256 tokens, tcgen05 grouped GEMM above")
     return ap.parse_args()
 
 
@@ -183,6 +185,7 @@ def run_b200(args):
         return run_ep(args, pkg, dev, world, rank, local)
 
     T = args.tokens or 64
+    path = {"auto": 0, "gemv": 1, "grouped": 2, "scalar": 3}[args.path]
     nlayers = max(1, args.layers)
     moe = pkg.B200MoE(local, pkg.ExpertShapes(HIDDEN, INTER), EXPERTS * nlayers, experts=EXPERTS, layers=nlayers,
                       top_k=TOP_K, shared_inter=SHARED, max_tokens=max(T, 64))
@@ -198,7 +201,7 @@ def run_b200(args):
     def step(i, x=None):
         l = i % nlayers
         g, su, sd, sg = dense[l]
-        moe.moe_block(l, xs[l] if x is None else x, g, su, sd, sg, out, ids_out=ids, weights_out=wts)
+        moe.moe_block(l, xs[l] if x is None else x, g, su, sd, sg, out, ids_out=ids, weights_out=wts, path=path)
 
     def barrier():
         if world > 1:
@@ -258,10 +261,10 @@ def run_b200(args):
     uniq = [int(torch.unique(i).numel()) for i, _ in routed]
     reqs = [pkg.MoEDeviceRequest(l, HIDDEN, INTER, TOP_K, xs[l], routed[l][0], routed[l][1]) for l in range(nlayers)]
     for i in range(W):
-        moe.grouped_moe_staged(reqs[i % nlayers], out)
+        moe.grouped_moe_staged(reqs[i % nlayers], out, path=path)
     moe.profile(True)
     for i in range(K):
-        moe.grouped_moe_staged(reqs[i % nlayers], out)
+        moe.grouped_moe_staged(reqs[i % nlayers], out, path=path)
     prof = moe.profile_read()
     moe.profile(False)
     # the router and shared-expert kernels, each alone on the stream

@@ -296,9 +296,10 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
         }
     } else if (warp == kWarpMma || warp == kWarpMma1) {
         // ===================== MMA issuers: one warp per row tile =================================
-        // issuing a tcgen05.mma costs the issuing thread tens of cycles, more than the math of a small
-        // token tile takes; two issuers on two schedulers keep the tensor pipe fed
-        if (lane == 0) {
+        // The whole warp walks the loop and one elected lane issues: the code stays warp-uniform.  Two
+        // issuers on two schedulers, because issuing a tcgen05.mma costs more than the math of a small
+        // token tile takes.
+        {
             const int r = (warp == kWarpMma) ? 0 : 1;
             const uint32_t d_tmem = tmem_base + kAccCol0 + r * kTileTok;
             uint32_t it = 0, item = r, unit_i = 0;
@@ -307,27 +308,30 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
                 const int n_pad = max(16, (grp.z + 15) & ~15);
                 const uint32_t idesc = kIdescBase | ((uint32_t)(n_pad >> 3) << 17);
                 // the accumulators must have been read back
-                bool ok = mbar_wait(ACC_EMPTY, (unit_i & 1) ^ 1, s_abort, a.err);
+                bool ok = mbar_wait_warp(ACC_EMPTY, (unit_i & 1) ^ 1, s_abort, a.err);
                 for (int c = 0; c < kChunks && ok; c++, item += 2) {
                     const int wb = item % kWBufs;
-                    ok = mbar_wait(W_READY(wb), (item / kWBufs) & 1, s_abort, a.err);
+                    ok = mbar_wait_warp(W_READY(wb), (item / kWBufs) & 1, s_abort, a.err);
                     const uint32_t w_addr = tmem_base + wb * kWCols;
                     for (int h = 0; h < 2 && ok; h++, it++) {
                         const int st = it % kXStages;
-                        ok = mbar_wait(X_FULL(st), (it / kXStages) & 1, s_abort, a.err);
+                        ok = mbar_wait_warp(X_FULL(st), (it / kXStages) & 1, s_abort, a.err);
                         if (!ok) break;
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                         const uint64_t xdesc = umma_desc(smem_u32(x_tiles + (size_t)st * kTileBytes));
+                        if (elect_one()) {
 #pragma unroll
-                        for (int kk = 0; kk < 4; kk++)
-                            umma_f16_ts(d_tmem, w_addr + (h * 4 + kk) * 8, xdesc + kk * 2, idesc, (c > 0 || h > 0 || kk > 0) ? 1u : 0u);
-                        umma_commit(X_EMPTY(st));        // the activation stage is free once both issuers' MMAs retire
+                            for (int kk = 0; kk < 4; kk++)
+                                umma_f16_ts(d_tmem, w_addr + (h * 4 + kk) * 8, xdesc + kk * 2, idesc, (c > 0 || h > 0 || kk > 0) ? 1u : 0u);
+                            umma_commit(X_EMPTY(st));    // the activation stage is free once both issuers' MMAs retire
+                            if (h == 1) umma_commit(W_FREE(wb));   // and so is the weight buffer
+                        }
+                        __syncwarp();
                     }
-                    if (!ok) break;
-                    umma_commit(W_FREE(wb));             // and so is the weight buffer
                 }
                 if (!ok) break;
-                umma_commit(ACC_FULL);
+                if (elect_one()) umma_commit(ACC_FULL);
+                __syncwarp();
             }
         }
     } else if (warp >= kWarpDeq0 && warp < kWarpEpi1) {
