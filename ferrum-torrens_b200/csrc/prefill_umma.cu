@@ -256,7 +256,8 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
 
     if (warp == kWarpActTma) {
         // ===================== activation tiles: TMA, 128-byte swizzle ============================
-        if (lane == 0) {
+        // (the whole warp walks the loop, one elected lane issues: see elect_one)
+        {
             uint32_t it = 0;
             for (int u = blockIdx.x; u < n_units && !*s_abort; u += gridDim.x) {
                 const int4 grp = a.groups[u / n_pairs];
@@ -265,17 +266,20 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
                 bool ok = true;
                 for (int ks = 0; ks < K / kStepK && ok; ks++, it++) {
                     const int st = it % kXStages;
-                    ok = mbar_wait(X_EMPTY(st), ((it / kXStages) & 1) ^ 1, s_abort, a.err);
+                    ok = mbar_wait_warp(X_EMPTY(st), ((it / kXStages) & 1) ^ 1, s_abort, a.err);
                     if (!ok) break;
-                    mbar_expect_tx(X_FULL(st), bytes);
-                    tma_load_2d(smem_u32(x_tiles + (size_t)st * kTileBytes), &xmaps.m[sel], ks * kStepK, grp.y, X_FULL(st));
+                    if (elect_one()) {
+                        mbar_expect_tx(X_FULL(st), bytes);
+                        tma_load_2d(smem_u32(x_tiles + (size_t)st * kTileBytes), &xmaps.m[sel], ks * kStepK, grp.y, X_FULL(st));
+                    }
+                    __syncwarp();
                 }
                 if (!ok) break;
             }
         }
     } else if (warp == kWarpRawTma) {
         // ===================== packed weights and block scales: TMA into the raw ring ===============
-        if (lane == 0) {
+        {
             uint32_t it = 0;
             for (int u = blockIdx.x; u < n_units && !*s_abort; u += gridDim.x) {
                 const int4 grp = a.groups[u / n_pairs];
@@ -284,12 +288,15 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
                 for (int w = 0; w < kItems && ok; w++, it++) {
                     const int c = w >> 1, r = w & 1;
                     const int st = it % kRawStages;
-                    ok = mbar_wait(RAW_EMPTY(st), ((it / kRawStages) & 1) ^ 1, s_abort, a.err);
+                    ok = mbar_wait_warp(RAW_EMPTY(st), ((it / kRawStages) & 1) ^ 1, s_abort, a.err);
                     if (!ok) break;
-                    const uint32_t dst = smem_u32(raw_ring + (size_t)st * kRawStageBytes);
-                    mbar_expect_tx(RAW_FULL(st), kRawStageBytes);
-                    tma_load_2d(dst, &tmap_packed, c * 64, row0 + r * kTileM, RAW_FULL(st));
-                    tma_load_2d(dst + kRawPackedBytes, &tmap_scale, (c >> 1) * 16, row0 + r * kTileM, RAW_FULL(st));
+                    if (elect_one()) {
+                        const uint32_t dst = smem_u32(raw_ring + (size_t)st * kRawStageBytes);
+                        mbar_expect_tx(RAW_FULL(st), kRawStageBytes);
+                        tma_load_2d(dst, &tmap_packed, c * 64, row0 + r * kTileM, RAW_FULL(st));
+                        tma_load_2d(dst + kRawPackedBytes, &tmap_scale, (c >> 1) * 16, row0 + r * kTileM, RAW_FULL(st));
+                    }
+                    __syncwarp();
                 }
                 if (!ok) break;
             }

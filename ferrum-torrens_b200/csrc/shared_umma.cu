@@ -81,10 +81,13 @@ dense_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     const int n_tile = blockIdx.x, t0 = blockIdx.y * kTile;
 
     if (warp == 0) {
-        if (lane == 0) {
-            for (int ks = 0; ks < a.k_steps; ks++) {
-                const int st = ks % kStages;
-                if (!mbar_wait(EMPTY(st), ((ks / kStages) & 1) ^ 1, s_abort, a.err)) break;
+        // TMA producer: the whole warp walks the loop, one elected lane issues
+        bool ok = true;
+        for (int ks = 0; ks < a.k_steps && ok; ks++) {
+            const int st = ks % kStages;
+            ok = mbar_wait_warp(EMPTY(st), ((ks / kStages) & 1) ^ 1, s_abort, a.err);
+            if (!ok) break;
+            if (elect_one()) {
                 mbar_expect_tx(FULL(st), 2 * kOperandBytes);
                 const int plane = ks / a.k_steps_plane;
                 const int ka = (ks - plane * a.k_steps_plane) * kStepK;
@@ -99,23 +102,27 @@ dense_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     tma_load_2d(bdst, &tmap_b, kb, n_tile * kTile, FULL(st));
                 }
             }
+            __syncwarp();
         }
     } else if (warp == 1) {
-        if (lane == 0) {
-            bool ok = true;
-            for (int ks = 0; ks < a.k_steps && ok; ks++) {
-                const int st = ks % kStages;
-                ok = mbar_wait(FULL(st), (ks / kStages) & 1, s_abort, a.err);
-                if (!ok) break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t adesc = umma_desc(smem_u32(a_tiles + (size_t)st * kOperandBytes));
-                const uint64_t bdesc = umma_desc(smem_u32(b_tiles + (size_t)st * kOperandBytes));
+        // MMA issuer, same shape
+        bool ok = true;
+        for (int ks = 0; ks < a.k_steps && ok; ks++) {
+            const int st = ks % kStages;
+            ok = mbar_wait_warp(FULL(st), (ks / kStages) & 1, s_abort, a.err);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint64_t adesc = umma_desc(smem_u32(a_tiles + (size_t)st * kOperandBytes));
+            const uint64_t bdesc = umma_desc(smem_u32(b_tiles + (size_t)st * kOperandBytes));
+            if (elect_one()) {
 #pragma unroll
                 for (int kk = 0; kk < 4; kk++) umma_f16_ss(tmem_base, adesc + kk * 2, bdesc + kk * 2, kIdesc, (ks > 0 || kk > 0) ? 1u : 0u);
                 umma_commit(EMPTY(st));
             }
-            if (ok) umma_commit(ACC_FULL);
+            __syncwarp();
         }
+        if (ok && elect_one()) umma_commit(ACC_FULL);
+        __syncwarp();
     } else {
         const int quarter = warp & 3;
         const int t = t0 + quarter * 32 + lane;
