@@ -11,7 +11,8 @@
 //   gemm      D[128 weight rows, n tokens] per unit = (pass of <= 128 sorted rows of one expert, tile of
 //             128 weight rows); persistent CTAs, 16 warps:
 //               warp 0      TMA: activation tiles [128 tokens x 64 k] f16, 128-byte swizzle (B operand)
-//               warp 2      TMA: packed weight rows (64-byte swizzle) and block scales into a raw ring
+//               warp 2      TMA: packed weight rows (256 k = one 128-byte line per row, 128-byte swizzle)
+//                           and block scales into a raw ring
 //               warps 8..23 dequantise (hardware e2m1x2 / e4m3x2 -> f16x2, exact product with the block
 //                           scale) and store the f16 weights into tensor memory (tcgen05.st): they are the
 //                           A operand, one TMEM lane per weight row, so the dequantised weights never
@@ -40,7 +41,7 @@ using namespace umma;
 constexpr int kTileM = 128;   // weight rows per tile (MMA M, one TMEM lane per row)
 constexpr int kTileTok = 128; // most tokens per pass (MMA N <= 128, one TMEM column per token)
 constexpr int kStepK = 64;    // k per pipeline step: one 128-byte swizzle atom of f16
-constexpr int kXStages = 8;
+constexpr int kXStages = 6;
 constexpr int kTileBytes = kTileTok * kStepK * 2;  // 16 KiB activation tile
 constexpr int kThreads = 896;
 // instruction descriptor: f16 x f16 -> f32, both operands K-major, M = 128; N (bits 17..22, N >> 3) per unit
@@ -181,8 +182,8 @@ constexpr int kEpiWarps = 8;          // warps 4..7 read row tile 0, warps 24..2
 constexpr int kWarpEpi1 = 24;
 constexpr int kDeqSets = 4;                    // dequantiser sets of 4 warps (128 threads = 128 weight rows)
 constexpr int kRawStages = 6;
-constexpr int kRawPackedBytes = kTileM * 64;   // one chunk of 128 k: 128 weight rows x 64 bytes, 64-byte swizzle
-constexpr int kRawScaleBytes = kTileM * 16;    // 128 rows x 16 scale bytes (256 k: the chunk's half is used)
+constexpr int kRawPackedBytes = kTileM * 128;  // two chunks (256 k): 128 weight rows x 128 bytes, 128-byte swizzle
+constexpr int kRawScaleBytes = kTileM * 16;    // 128 rows x 16 scale bytes (256 k)
 constexpr int kRawStageBytes = kRawPackedBytes + kRawScaleBytes;
 constexpr int kWBufs = kDeqSets;               // dequantised weight chunks in tensor memory, 64 columns each
 constexpr int kWCols = 64;
@@ -227,7 +228,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
         }
         for (int s = 0; s < kRawStages; s++) {
             mbar_init(RAW_FULL(s), 1);
-            mbar_init(RAW_EMPTY(s), 128);
+            mbar_init(RAW_EMPTY(s), 256);
         }
         for (int s = 0; s < kWBufs; s++) {
             mbar_init(W_READY(s), 128);
@@ -285,16 +286,17 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
                 const int4 grp = a.groups[u / n_pairs];
                 const int row0 = grp.x * a.N + (u % n_pairs) * 2 * kTileM;
                 bool ok = true;
-                for (int w = 0; w < kItems && ok; w++, it++) {
-                    const int c = w >> 1, r = w & 1;
+                // a stage = two chunks (256 k) of one row tile: full 128-byte lines per weight row
+                for (int q = 0; q < kChunks && ok; q++, it++) {
+                    const int cp = q >> 1, r = q & 1;
                     const int st = it % kRawStages;
                     ok = mbar_wait_warp(RAW_EMPTY(st), ((it / kRawStages) & 1) ^ 1, s_abort, a.err);
                     if (!ok) break;
                     if (elect_one()) {
                         const uint32_t dst = smem_u32(raw_ring + (size_t)st * kRawStageBytes);
                         mbar_expect_tx(RAW_FULL(st), kRawStageBytes);
-                        tma_load_2d(dst, &tmap_packed, c * 64, row0 + r * kTileM, RAW_FULL(st));
-                        tma_load_2d(dst + kRawPackedBytes, &tmap_scale, (c >> 1) * 16, row0 + r * kTileM, RAW_FULL(st));
+                        tma_load_2d(dst, &tmap_packed, cp * 128, row0 + r * kTileM, RAW_FULL(st));
+                        tma_load_2d(dst + kRawPackedBytes, &tmap_scale, cp * 16, row0 + r * kTileM, RAW_FULL(st));
                     }
                     __syncwarp();
                 }
@@ -348,16 +350,17 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
         // owns one weight row of the piece: 64 packed bytes, eight block scales, 64 columns.
         const int quarter = warp & 3, set = (warp - kWarpDeq0) >> 2;
         const int row = quarter * 32 + lane;
-        const int sw = (row >> 1) & 3;      // 64-byte swizzle of the TMA box: 16-byte chunk index ^ ((row >> 1) & 3)
+        const int sw = row & 7;             // 128-byte swizzle of the TMA box: 16-byte chunk index ^ (row & 7)
         const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + set * kWCols;
-        uint32_t item0 = 0;                 // pieces before this unit
-        for (int u = blockIdx.x; u < n_units && !*s_abort; u += gridDim.x, item0 += kItems) {
+        uint32_t item0 = 0, stage0 = 0;     // pieces and raw stages before this unit
+        for (int u = blockIdx.x; u < n_units && !*s_abort; u += gridDim.x, item0 += kItems, stage0 += kChunks) {
             bool ok = true;
             for (int w = set; w < kItems && ok; w += kDeqSets) {
                 const uint32_t item = item0 + w;
                 const int c = w >> 1;
-                const int st = item % kRawStages;
-                ok = mbar_wait(RAW_FULL(st), (item / kRawStages) & 1, s_abort, a.err);
+                const uint32_t stage = stage0 + 2 * (c >> 1) + (w & 1);      // the raw stage holds chunks c & ~1 and c | 1
+                const int st = stage % kRawStages;
+                ok = mbar_wait(RAW_FULL(st), (stage / kRawStages) & 1, s_abort, a.err);
                 if (ok) ok = mbar_wait(W_FREE(set), ((item / kWBufs) & 1) ^ 1, s_abort, a.err);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -365,7 +368,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
                 const uint2 sc8 = *reinterpret_cast<const uint2*>(rp + kRawPackedBytes + row * 16 + (c & 1) * 8);
                 uint4 raw[4];
 #pragma unroll
-                for (int g = 0; g < 4; g++) raw[g] = *reinterpret_cast<const uint4*>(rp + row * 64 + ((g ^ sw) << 4));
+                for (int g = 0; g < 4; g++) raw[g] = *reinterpret_cast<const uint4*>(rp + row * 128 + ((((c & 1) * 4 + g) ^ sw) << 4));
 #pragma unroll
                 for (int g = 0; g < 4; g++) {
                     // 32 k: two block scales
@@ -582,9 +585,9 @@ int launch_prefill_umma(const BankView& b, const void* x, int x_dtype, const Dec
             !make_act_map(&map_h.m[q], sc.ic2h, (size_t)routes, b.inter, 32 * (q + 1)))
             return -1;
     const size_t gu_rows = (size_t)b.slots * 2 * b.inter, dn_rows = (size_t)b.slots * b.hidden;
-    if (!make_raw_map(&map_gp, b.gu_packed, gu_rows, b.hidden / 2, 64, kTileM, CU_TENSOR_MAP_SWIZZLE_64B) ||
+    if (!make_raw_map(&map_gp, b.gu_packed, gu_rows, b.hidden / 2, 128, kTileM, CU_TENSOR_MAP_SWIZZLE_128B) ||
         !make_raw_map(&map_gs, b.gu_scale, gu_rows, b.hidden / 16, 16, kTileM, CU_TENSOR_MAP_SWIZZLE_NONE) ||
-        !make_raw_map(&map_dp, b.dn_packed, dn_rows, b.inter / 2, 64, kTileM, CU_TENSOR_MAP_SWIZZLE_64B) ||
+        !make_raw_map(&map_dp, b.dn_packed, dn_rows, b.inter / 2, 128, kTileM, CU_TENSOR_MAP_SWIZZLE_128B) ||
         !make_raw_map(&map_ds, b.dn_scale, dn_rows, b.inter / 16, 16, kTileM, CU_TENSOR_MAP_SWIZZLE_NONE))
         return -1;
     static bool attr = false;
