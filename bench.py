@@ -279,16 +279,30 @@ def run_b200(args):
     pk = peaks()
     gate_kind = "expert_gate_up" if "expert_gate_up" in prof else "grouped_gate_up"
     g_ms, g_n = prof[gate_kind]
-    gu_bytes = U * GATE_UP_BYTES + T * HIDDEN * 2
-    # DRAM traffic per algorithmic byte of this kernel from the ncu capture summarised in
-    # profiles/expert_mma_gate_up_T64.md (dram__bytes_read + dram__bytes_write over one launch)
-    NCU_TRAFFIC_RATIO = 1.042
-    achieved = gu_bytes / (g_ms / g_n * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": gate_kind, "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                "frac": achieved / pk["hbm_gbs"], "peak_source": pk["which"], "frac_of_nominal_8000": achieved / 8000.0,
-                "traffic": NCU_TRAFFIC_RATIO * gu_bytes, "distinct_experts": U, "bytes_per_launch": gu_bytes,
-                "us_per_launch": g_ms / g_n * 1e3,
-                "kernels": {k: {"us_per_launch": ms / n * 1e3, "launches": n} for k, (ms, n) in prof.items()}}
+    kernels = {k: {"us_per_launch": ms / n * 1e3, "launches": n} for k, (ms, n) in prof.items()}
+    if gate_kind == "expert_gate_up":
+        # decode kernels: bound by the HBM stream of the routed experts' weights
+        gu_bytes = U * GATE_UP_BYTES + T * HIDDEN * 2
+        # DRAM traffic per algorithmic byte of this kernel, from one ncu capture of it
+        # (dram__bytes_read + dram__bytes_write over one launch at T = 64)
+        NCU_TRAFFIC_RATIO = 1.042
+        achieved = gu_bytes / (g_ms / g_n * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "kernel": gate_kind, "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                    "frac": achieved / pk["hbm_gbs"], "peak_source": pk["which"], "frac_of_nominal_8000": achieved / 8000.0,
+                    "traffic": NCU_TRAFFIC_RATIO * gu_bytes, "distinct_experts": U, "bytes_per_launch": gu_bytes,
+                    "us_per_launch": g_ms / g_n * 1e3, "kernels": kernels}
+    else:
+        # tcgen05 grouped GEMM: useful flops of the routes (padding of ragged groups not counted)
+        flops = T * TOP_K * 2.0 * HIDDEN * (2 * INTER)
+        achieved = flops / (g_ms / g_n * 1e-3) / 1e12
+        roofline = {"bound": "tensor", "kernel": gate_kind, "achieved": achieved, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
+                    "frac": achieved / pk["bf16_tflops"], "peak_source": pk["which"] + " (burst; sustained %.0f)" % pk["bf16_tflops_sustained"],
+                    "traffic": None, "distinct_experts": U, "flops_per_launch": flops, "us_per_launch": g_ms / g_n * 1e3,
+                    "kernels": kernels}
+        if "grouped_down" in prof:
+            d_ms, d_n = prof["grouped_down"]
+            dn = T * TOP_K * 2.0 * INTER * HIDDEN / (d_ms / d_n * 1e-3) / 1e12
+            roofline["down"] = {"achieved": dn, "frac": dn / pk["bf16_tflops"]}
     if "expert_down" in prof:
         d_ms, d_n = prof["expert_down"]
         dn = (U * DOWN_BYTES) / (d_ms / d_n * 1e-3) / 1e9
@@ -300,7 +314,7 @@ def run_b200(args):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
         "ms_per_step": total_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16 activations x NVFP4 (e2m1 + e4m3 block scales) weights, f32 accumulate", "data": "synthetic",
-        "config": {"workload": f"decode T={T} tokens/step, hidden {HIDDEN}, {EXPERTS} resident NVFP4 experts top-{TOP_K}, "
+        "config": {"workload": f"{'decode' if T <= 256 else 'prefill'} T={T} tokens/step, hidden {HIDDEN}, {EXPERTS} resident NVFP4 experts top-{TOP_K}, "
                                f"bf16 shared expert {SHARED}",
                    "l2": f"inputs larger than L2: {nlayers} independently seeded layers "
                          f"({nlayers * EXPERTS * EXPERT_BYTES / 1e6:.0f} MB of banks) cycled step by step",
