@@ -52,6 +52,12 @@ def parse():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--sweep", action="store_true", help="also report T = 1, 8, 512, 2048")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ep-chunks", type=int, default=2,
+                    help="N > 1: expert ranges per owner that are exchanged and computed one after the other, so that "
+                         "exchanges run under compute; 1 = the plain schedule")
+    ap.add_argument("--ep-exchange", default="p2p", choices=["p2p", "nccl"],
+                    help="N > 1: dispatch / return by this library's kernels over peer memory, or by NCCL all-to-all")
+    ap.add_argument("--ep-comm-sms", type=int, default=16, help="N > 1: SMs left to the exchange kernels when overlapping")
     ap.add_argument("--path", default="auto", choices=["auto", "gemv", "grouped", "scalar"],
                     help="routed-expert kernels: auto = decode kernels up to 256 tokens, tcgen05 grouped GEMM above")
     return ap.parse_args()
@@ -362,7 +368,7 @@ def run_ep(args, pkg, dev, world, rank, local):
     nlayers = min(max(1, args.layers), 2)
     per = EXPERTS // world
     be = ep.LibBackend(local, rank, world, pkg.ExpertShapes(HIDDEN, INTER), experts=EXPERTS, layers=nlayers,
-                       top_k=TOP_K, shared_inter=SHARED, max_tokens=T)
+                       top_k=TOP_K, shared_inter=SHARED, max_tokens=T, comm_sms=args.ep_comm_sms if (args.ep_chunks > 1 and args.ep_exchange == "nccl") else 0)
     dense, xs = [], []
     for l in range(nlayers):
         pkg.synth.fill_banks_on_device(be.owner, l, seed=1000 + 977 * rank + l, experts=per, slot0=l * per,
@@ -372,10 +378,20 @@ def run_ep(args, pkg, dev, world, rank, local):
     out = torch.empty((T, HIDDEN), dtype=torch.bfloat16, device=dev)
     layer = ep.ExpertParallelMoE(be, world)
 
-    def step(i, record=None):
+    chunks = max(1, args.ep_chunks)
+    p2p = args.ep_exchange == "p2p"
+    if p2p:
+        be.enable_peer_exchange()
+
+    def step(i, record=None, x=None):
         l = i % nlayers
         g, su, sd, sg = dense[l]
-        layer.forward(l, xs[l], g, su, sd, sg, out, record=record)
+        if p2p:
+            layer.forward_p2p(l, xs[l] if x is None else x, g, su, sd, sg, out, record=record)
+        elif record is None and chunks > 1:
+            layer.forward_overlapped(l, xs[l] if x is None else x, g, su, sd, sg, out, chunks=chunks)
+        else:
+            layer.forward(l, xs[l] if x is None else x, g, su, sd, sg, out, record=record)
 
     def barrier():
         dist.barrier()
@@ -412,8 +428,7 @@ def run_ep(args, pkg, dev, world, rank, local):
     def step_e2e(i):
         l = i % nlayers
         x_stage.copy_(x_host[l], non_blocking=True)
-        g, su, sd, sg = dense[l]
-        layer.forward(l, x_stage, g, su, sd, sg, out)
+        step(i, x=x_stage)
         out_host.copy_(out, non_blocking=True)
 
     for i in range(2):
@@ -460,12 +475,15 @@ def run_ep(args, pkg, dev, world, rank, local):
             "dtype": "bf16 activations x NVFP4 (e2m1 + e4m3 block scales) weights, f32 accumulate",
             "data": "synthetic",
             "config": {"workload": f"expert-parallel layer, T={T} tokens per GPU, {EXPERTS} experts split {per} per GPU, "
-                                   f"top-{TOP_K}, uniform routing, NCCL all-to-all dispatch/combine",
+                                   f"top-{TOP_K}, uniform routing, " +
+                                   ("dispatch / return by peer-memory kernels over NVLink" if p2p else
+                                    f"NCCL all-to-all dispatch/combine, {chunks} overlapped expert range(s) per owner"),
                        "l2": f"inputs larger than L2: {nlayers} layers cycled, {T * TOP_K} routes x 4 KB rows per step",
                        "timed_region": "whole block incl. both all-to-alls, CUDA events, max over ranks"},
             "gpu_launches": int(launches), "clocks": clocks,
-            "ep": {"phases_ms_max_over_ranks": phases,
-                   "exposed_comm_ms": phases["dispatch_a2a_ms"] + phases["return_a2a_ms"],
+            "ep": {"phases_of": "one step, marks after each phase" if p2p else "one step of the plain schedule (every phase waits for the one before)",
+                   "phases_ms_max_over_ranks": phases, "unpipelined_ms_per_step": sum(phases.values()),
+                   "exchange_ms_unpipelined": phases["dispatch_a2a_ms"] + phases["return_a2a_ms"],
                    "max_routes_sent_off_rank": float(sent.item()),
                    "nvlink_bytes_each_way_per_gpu": float(sent.item()) * HIDDEN * 2},
             "e2e": e2e, "roofline": None,

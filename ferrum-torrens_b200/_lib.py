@@ -55,8 +55,12 @@ _PROTOS = {
     "ftm_shared_expert": (_int, [_vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp]),
     "ftm_combine": (_int, [_vp, _vp, _int, _vp, _vp, _i32, _vp, _int, _vp]),
     "ftm_moe_block": (_int, [_vp, _i32, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _int, _vp, _vp, _int, _vp]),
+    "ftm_set_sm_budget": (C.c_int, [_vp, C.c_int32]),
     "ftm_kernel_launches": (C.c_uint64, [_vp]),
     "ftm_ep_pack": (_int, [_vp, _vp, _vp, _vp, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "ftm_ep_plan": (_int, [_vp, _vp, _i32, _i32, _vp, _vp, _vp]),
+    "ftm_ep_dispatch": (_int, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, C.c_int64, _vp]),
+    "ftm_ep_return": (_int, [_vp, _vp, _i32, _i32, _i32, _vp, _vp, C.c_int64, _vp]),
     "ftm_ep_combine": (_int, [_vp, _vp, _int, _vp, _vp, _vp, _i32, _vp, _int, _vp]),
     "ftm_profile_enable": (_int, [_vp, _int]),
     "ftm_profile_read": (_int, [_vp, _int, C.POINTER(C.c_double), C.POINTER(C.c_uint64)]),

@@ -115,7 +115,8 @@ struct ftm_handle {
     float *row_scale = nullptr, *row_scale2 = nullptr;
     int4* groups = nullptr;
     int32_t *sorted_route = nullptr, *n_groups = nullptr;
-    int sm_count = 148;
+    int sm_count = 148;   // CTAs of the persistent kernels (ftm_set_sm_budget)
+    int sm_total = 148;
     std::vector<void*> allocs;
 
     uint64_t steps = 0;
@@ -363,7 +364,8 @@ FTM_API int ftm_create(const ftm_config* c, void* stream, ftm_handle** out) {
     A(dev_alloc(hp, &h->xg, R * H));
     A(dev_alloc(hp, &h->row_scale, R));
     A(dev_alloc(hp, &h->row_scale2, R));
-    cudaDeviceGetAttribute(&h->sm_count, cudaDevAttrMultiProcessorCount, c->ordinal);
+    cudaDeviceGetAttribute(&h->sm_total, cudaDevAttrMultiProcessorCount, c->ordinal);
+    h->sm_count = h->sm_total;
     (void)bins;
     if (rc == FTM_OK) {
         e = cudaMemset(h->d_slot_for_id, 0xff, n_ids * sizeof(int32_t));
@@ -709,6 +711,9 @@ FTM_API int ftm_sync_status(ftm_handle* h, void* stream) {
     CU(h, cudaStreamSynchronize(s));
     if (f[2]) {
         cudaMemsetAsync(h->flags + 2, 0, sizeof(int32_t), s);
+        if (f[2] == 4)
+            return fail(h, FTM_ERR_BAD, "moe: an expert-parallel exchange row fell outside its buffer and was dropped; "
+                                        "the step's output is invalid");
         return fail(h, FTM_ERR_CUDA, "moe: driver: a kernel gave up a bounded wait (code %d); the step's output is invalid",
                     f[2]);
     }
@@ -750,6 +755,14 @@ FTM_API int ftm_profile_read(ftm_handle* h, int kind, double* total_ms, uint64_t
 FTM_API const char* ftm_profile_kind_name(int kind) {
     return (kind >= 0 && kind < K_NUM_KINDS) ? kKindNames[kind] : nullptr;
 }
+FTM_API int ftm_set_sm_budget(ftm_handle* h, int32_t sms) {
+    if (!h) return FTM_ERR_BAD;
+    std::lock_guard<std::mutex> lk(h->mu);
+    if (sms < 0 || sms > h->sm_total) return fail(h, FTM_ERR_BAD, "moe: sm budget %d of %d SMs", sms, h->sm_total);
+    h->sm_count = sms ? sms : h->sm_total;
+    return FTM_OK;
+}
+
 FTM_API uint64_t ftm_kernel_launches(const ftm_handle* h) { return h ? h->launches : 0; }
 
 // ---- expert-parallel dispatch / combine -------------------------------------------------------
@@ -772,6 +785,57 @@ FTM_API int ftm_ep_pack(ftm_handle* h, const void* x_bf16, const int32_t* ids, c
     h->launches += launch_ep_pack((const __nv_bfloat16*)x_bf16, ids, weights, route_idx, h->seg, tokens, h->cfg.top_k,
                                   h->cfg.hidden, h->cfg.experts, ep_size, (__nv_bfloat16*)send_x, send_expert,
                                   send_weight, counts, h->ctx(s));
+    CU(h, cudaGetLastError());
+    return FTM_OK;
+}
+
+FTM_API int ftm_ep_plan(ftm_handle* h, const int32_t* ids, int32_t tokens, int32_t ep_size, int32_t* route_idx,
+                        int32_t* counts, void* stream) {
+    if (!h) return FTM_ERR_BAD;
+    std::lock_guard<std::mutex> lk(h->mu);
+    if (!ids || !route_idx || !counts) return fail(h, FTM_ERR_BAD, "moe: ep_plan: null buffer");
+    if (tokens <= 0 || tokens > h->cfg.max_tokens)
+        return fail(h, FTM_ERR_BAD, "moe: ep_plan: %d tokens (max_tokens %d)", tokens, h->cfg.max_tokens);
+    if (ep_size < 1 || ep_size > 32 || h->cfg.experts % ep_size)
+        return fail(h, FTM_ERR_BAD, "moe: ep_plan: %d experts do not split over %d ranks", h->cfg.experts, ep_size);
+    cudaStream_t s = pick(h, stream);
+    const int routes = tokens * h->cfg.top_k;
+    CU(h, cudaMemsetAsync(h->flags + 1, 0, sizeof(int32_t), s));
+    h->launches += launch_csr_build(ids, routes, h->cfg.experts, h->seg, route_idx, h->csr_scratch, h->flags + 1, h->ctx(s));
+    h->launches += launch_ep_counts(h->seg, h->cfg.experts, ep_size, counts, h->ctx(s));
+    CU(h, cudaGetLastError());
+    return FTM_OK;
+}
+
+FTM_API int ftm_ep_dispatch(ftm_handle* h, const void* x_bf16, const int32_t* ids, const float* weights,
+                            const int32_t* route_idx, int32_t tokens, int32_t ep_size, int32_t ep_rank,
+                            const int32_t* counts_all, const uint64_t* peer_x, const uint64_t* peer_meta,
+                            int64_t capacity_rows, void* stream) {
+    if (!h) return FTM_ERR_BAD;
+    std::lock_guard<std::mutex> lk(h->mu);
+    if (!x_bf16 || !ids || !weights || !route_idx || !counts_all || !peer_x || !peer_meta)
+        return fail(h, FTM_ERR_BAD, "moe: ep_dispatch: null buffer");
+    if (tokens <= 0 || tokens > h->cfg.max_tokens)
+        return fail(h, FTM_ERR_BAD, "moe: ep_dispatch: %d tokens (max_tokens %d)", tokens, h->cfg.max_tokens);
+    if (ep_size < 1 || ep_size > 32 || h->cfg.experts % ep_size || ep_rank < 0 || ep_rank >= ep_size || capacity_rows < 1)
+        return fail(h, FTM_ERR_BAD, "moe: ep_dispatch: rank %d of %d, capacity %lld", ep_rank, ep_size, (long long)capacity_rows);
+    h->launches += launch_ep_dispatch((const __nv_bfloat16*)x_bf16, ids, weights, route_idx, h->seg, tokens, h->cfg.top_k,
+                                      h->cfg.hidden, h->cfg.experts, ep_size, ep_rank, counts_all, peer_x, peer_meta,
+                                      capacity_rows, h->flags + 2, h->ctx(pick(h, stream)));
+    CU(h, cudaGetLastError());
+    return FTM_OK;
+}
+
+FTM_API int ftm_ep_return(ftm_handle* h, const void* y_bf16, int32_t rows, int32_t ep_size, int32_t ep_rank,
+                          const int32_t* counts_all, const uint64_t* peer_back, int64_t capacity_rows, void* stream) {
+    if (!h) return FTM_ERR_BAD;
+    std::lock_guard<std::mutex> lk(h->mu);
+    if (!y_bf16 || !counts_all || !peer_back) return fail(h, FTM_ERR_BAD, "moe: ep_return: null buffer");
+    if (rows < 0 || ep_size < 1 || ep_size > 32 || ep_rank < 0 || ep_rank >= ep_size || capacity_rows < 1)
+        return fail(h, FTM_ERR_BAD, "moe: ep_return: %d rows, rank %d of %d", rows, ep_rank, ep_size);
+    if (rows == 0) return FTM_OK;
+    h->launches += launch_ep_return((const __nv_bfloat16*)y_bf16, rows, h->cfg.hidden, ep_size, ep_rank, counts_all, peer_back,
+                                    capacity_rows, h->flags + 2, h->ctx(pick(h, stream)));
     CU(h, cudaGetLastError());
     return FTM_OK;
 }

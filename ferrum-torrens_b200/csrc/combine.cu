@@ -122,7 +122,84 @@ __global__ void ep_combine_kernel(const void* __restrict__ y, int y_dtype, const
     }
 }
 
+// ---- expert-parallel exchange over peer memory -------------------------------------------------
+// counts_all[s * world + p] = routes that rank s sends to owner p.  An owner's receive buffer holds the
+// sources in rank order, each source's routes in its send order (sorted by expert).
+
+// dispatch: position i of this rank's send order goes straight into the owner's receive buffers
+__global__ void __launch_bounds__(128)
+ep_dispatch_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ ids, const float* __restrict__ weights,
+                   const int32_t* __restrict__ route_idx, const int32_t* __restrict__ seg, int top_k, int H, int per,
+                   int world, int rank, const int32_t* __restrict__ counts_all, const uint64_t* __restrict__ peer_x,
+                   const uint64_t* __restrict__ peer_meta, long long capacity, int32_t* err) {
+    const int i = blockIdx.x;
+    const int r = route_idx[i];
+    const int e = ids[r];
+    const int p = e / per;
+    long long row = i - seg[p * per];
+    for (int s = 0; s < rank; s++) row += counts_all[s * world + p];
+    if (p < 0 || p >= world || row < 0 || row >= capacity) {   // never store outside the owner's buffer
+        if (threadIdx.x == 0) atomicExch(err, 4);
+        return;
+    }
+    const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)(r / top_k) * H);
+    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(peer_x[p]) + (size_t)row * H);
+    for (int c = threadIdx.x; c < H / 8; c += blockDim.x) dst[c] = src[c];
+    if (threadIdx.x == 0)
+        reinterpret_cast<int2*>(peer_meta[p])[row] = make_int2(e, __float_as_int(weights[r]));
+}
+
+// return: row i of the owner's output (receive order) goes to the position its source packed it at
+__global__ void __launch_bounds__(128)
+ep_return_kernel(const __nv_bfloat16* __restrict__ y, int n, int H, int world, int rank,
+                 const int32_t* __restrict__ counts_all, const uint64_t* __restrict__ peer_back, long long capacity,
+                 int32_t* err) {
+    const int i = blockIdx.x;
+    int s = 0, roff = 0;
+    for (; s < world; s++) {
+        const int c = counts_all[s * world + rank];
+        if (i < roff + c) break;
+        roff += c;
+    }
+    long long row = i - roff;
+    if (s < world)
+        for (int p = 0; p < rank; p++) row += counts_all[s * world + p];
+    if (s >= world || row < 0 || row >= capacity) {
+        if (threadIdx.x == 0) atomicExch(err, 4);
+        return;
+    }
+    const uint4* src = reinterpret_cast<const uint4*>(y + (size_t)i * H);
+    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(peer_back[s]) + (size_t)row * H);
+    for (int c = threadIdx.x; c < H / 8; c += blockDim.x) dst[c] = src[c];
+}
+
 }  // namespace
+
+int launch_ep_dispatch(const __nv_bfloat16* x, const int32_t* ids, const float* weights, const int32_t* route_idx,
+                       const int32_t* seg, int tokens, int top_k, int hidden, int experts, int world, int rank,
+                       const int32_t* counts_all, const uint64_t* peer_x, const uint64_t* peer_meta, long long capacity,
+                       int32_t* err, const Ctx& c) {
+    c.begin(K_EP_PACK);
+    ep_dispatch_kernel<<<tokens * top_k, 128, 0, c.s>>>(x, ids, weights, route_idx, seg, top_k, hidden, experts / world, world,
+                                                       rank, counts_all, peer_x, peer_meta, capacity, err);
+    c.end();
+    return 1;
+}
+
+int launch_ep_return(const __nv_bfloat16* y, int n, int hidden, int world, int rank, const int32_t* counts_all,
+                     const uint64_t* peer_back, long long capacity, int32_t* err, const Ctx& c) {
+    c.begin(K_EP_COMBINE);
+    ep_return_kernel<<<n, 128, 0, c.s>>>(y, n, hidden, world, rank, counts_all, peer_back, capacity, err);
+    c.end();
+    return 1;
+}
+
+int launch_ep_counts(const int32_t* seg, int experts, int ranks, int32_t* counts, const Ctx& c) {
+    c.begin(K_EP_PACK);
+    ep_rank_counts_kernel<<<1, 32, 0, c.s>>>(seg, experts, ranks, counts);
+    c.end();
+    return 1;
+}
 
 int launch_sum_routes(const float* yroute, int tokens, int top_k, int hidden, const float* shared,
                       const float* se_gate, void* out, int out_dtype, const Ctx& c) {

@@ -136,6 +136,13 @@ int launch_ep_pack(const __nv_bfloat16* x, const int32_t* ids, const float* weig
 int launch_ep_combine(const void* y, int y_dtype, const int32_t* route_idx, int32_t* pos_scratch, int tokens,
                       int top_k, int hidden, const float* shared, const float* se_gate, void* out, int out_dtype,
                       const Ctx& c);
+int launch_ep_counts(const int32_t* seg, int experts, int ranks, int32_t* counts, const Ctx& c);
+int launch_ep_dispatch(const __nv_bfloat16* x, const int32_t* ids, const float* weights, const int32_t* route_idx,
+                       const int32_t* seg, int tokens, int top_k, int hidden, int experts, int world, int rank,
+                       const int32_t* counts_all, const uint64_t* peer_x, const uint64_t* peer_meta, long long capacity,
+                       int32_t* err, const Ctx& c);
+int launch_ep_return(const __nv_bfloat16* y, int n, int hidden, int world, int rank, const int32_t* counts_all,
+                     const uint64_t* peer_back, long long capacity, int32_t* err, const Ctx& c);
 int launch_cast_to_bf16(const void* src, int src_dtype, size_t n, __nv_bfloat16* dst, const Ctx& c);
 
 }  // namespace ftm

@@ -52,12 +52,37 @@ def all_to_all_rows(send: torch.Tensor, send_counts: list[int], recv_counts: lis
     return out
 
 
+class _Done:
+    def wait(self):
+        return True
+
+
+def all_to_all_views(outs, ins, group=None):
+    """Asynchronous all-to-all of one tensor view per peer (no staging copy with NCCL).  Backends
+    without the list form (gloo, on the CPU tests) go through one contiguous exchange."""
+    if dist.get_backend(group) == "nccl":
+        return dist.all_to_all(outs, ins, group=group, async_op=True)
+    width = 1
+    for d in ins[0].shape[1:]:
+        width *= d
+    flat_in = torch.cat([t.reshape(t.shape[0], width) for t in ins])
+    n_out = sum(t.shape[0] for t in outs)
+    flat_out = flat_in.new_empty((n_out, width))
+    dist.all_to_all_single(flat_out, flat_in, output_split_sizes=[t.shape[0] for t in outs],
+                           input_split_sizes=[t.shape[0] for t in ins], group=group)
+    at = 0
+    for t in outs:
+        t.copy_(flat_out[at:at + t.shape[0]].reshape(t.shape))
+        at += t.shape[0]
+    return _Done()
+
+
 class LibBackend:
     """The CUDA library on both sides of the exchange."""
 
     def __init__(self, device: int, rank: int, world: int, shapes: _moe.ExpertShapes, *, experts: int = 256,
                  layers: int = 1, top_k: int = 8, shared_inter: int = 512, max_tokens: int = 8192,
-                 recv_capacity: int | None = None):
+                 recv_capacity: int | None = None, comm_sms: int = 0):
         if experts % world:
             raise _moe.bad(f"{experts} experts do not split over {world} ranks")
         self.rank, self.world, self.experts, self.layers, self.top_k = rank, world, experts, layers, top_k
@@ -70,6 +95,27 @@ class LibBackend:
         self.recv_capacity = recv_capacity or 4 * max_tokens * top_k
         self.owner = _moe.B200MoE(device, shapes, layers * self.per, experts=experts, layers=layers, top_k=1,
                                   shared_inter=0, max_tokens=self.recv_capacity)
+        # the expert kernels hold one CTA per SM for their whole duration: leave `comm_sms` SMs to the
+        # exchange kernels that should run at the same time (forward_overlapped)
+        if comm_sms:
+            sms = torch.cuda.get_device_properties(device).multi_processor_count
+            self.owner.set_sm_budget(max(1, sms - comm_sms))
+
+    def enable_peer_exchange(self, group=None):
+        """Allocate the receive / back buffers in symmetric memory and exchange their addresses, so that
+        dispatch and return can store straight into a peer's memory over NVLink (forward_p2p).  Collective:
+        every rank of the group calls it."""
+        import torch.distributed._symmetric_memory as symm
+        g = group if group is not None else dist.group.WORLD
+        dev = torch.device("cuda", self.front.device)
+        H = self.shapes.hidden
+        self.send_capacity = self.front.max_tokens * self.top_k
+        self.p2p_recv_x = symm.empty((self.recv_capacity, H), dtype=torch.bfloat16, device=dev)
+        self.p2p_recv_meta = symm.empty((self.recv_capacity, 2), dtype=torch.int32, device=dev)
+        self.p2p_back = symm.empty((self.send_capacity, H), dtype=torch.bfloat16, device=dev)
+        self._symm = [symm.rendezvous(t, g.group_name) for t in (self.p2p_recv_x, self.p2p_recv_meta, self.p2p_back)]
+        self.peer_x, self.peer_meta, self.peer_back = (h.buffer_ptrs_dev for h in self._symm)
+        self._tick = torch.zeros((1,), dtype=torch.int32, device=dev)
 
     def owned(self, expert: int) -> bool:
         return expert // self.per == self.rank
@@ -134,6 +180,125 @@ class ExpertParallelMoE:
         y = b.experts_forward(layer, recv_x, recv_e, recv_w)
         mark("computed")
         back = all_to_all_rows(y, rc, sc, self.group)
+        mark("returned")
+        b.combine(back, route_idx, shared, se_gate, out)
+        mark("combined")
+        return ids, w
+
+    def forward_p2p(self, layer: int, x, gate_w, sh_gate_up, sh_down, sh_gate, out, record=None):
+        """The same block with both exchanges done by this library's own kernels over peer memory: the
+        dispatch kernel reads a token's activation row once and stores it straight into the owner's
+        receive buffer (no send buffer, no collective), the return kernel stores every output row at the
+        position its source expects.  The backend must have called enable_peer_exchange().
+
+            route, plan, all-gather of the counts         one host read-back of the [world, world] counts
+            shared expert (while the host reads back)
+            dispatch kernel (peer stores) | barrier | experts | return kernel (peer stores) | barrier | combine
+        """
+        mark = record or (lambda name: None)
+        b = self.b
+        world = self.world
+        ids, w = b.route(x, gate_w)
+        route_idx, counts = b.front.ep_plan(ids, world)
+        counts_all = torch.empty((world * world,), dtype=torch.int32, device=counts.device)
+        dist.all_gather_into_tensor(counts_all, counts, group=self.group)
+        shared, se_gate = b.shared(x, sh_gate_up, sh_down, sh_gate) if sh_gate_up is not None else (None, None)
+        ca = counts_all.reshape(world, world).tolist()            # the one host read-back
+        sc = ca[b.rank]
+        rc = [ca[s][b.rank] for s in range(world)]
+        self.last_counts = (sc, rc)
+        n = sum(rc)
+        if n > b.recv_capacity:
+            raise _moe.bad(f"{n} routes received, the receive buffer was sized for {b.recv_capacity}")
+        mark("packed")
+        b.front.ep_dispatch(x, ids, w, route_idx, world, b.rank, counts_all, b.peer_x, b.peer_meta, b.recv_capacity)
+        self._barrier(b)
+        mark("dispatched")
+        if n:
+            meta = b.p2p_recv_meta[:n]
+            y = b.experts_forward(layer, b.p2p_recv_x[:n], meta[:, 0].contiguous(), meta[:, 1].contiguous().view(torch.float32))
+            mark("computed")
+            b.owner.ep_return(y, world, b.rank, counts_all, b.peer_back, b.send_capacity)
+        else:
+            mark("computed")
+        self._barrier(b)
+        mark("returned")
+        b.combine(b.p2p_back[:sum(sc)], route_idx, shared, se_gate, out)
+        mark("combined")
+        return ids, w
+
+    def _barrier(self, b):
+        # every rank's stores before this point are complete before any rank goes on
+        dist.all_reduce(b._tick, group=self.group)
+
+    def forward_overlapped(self, layer: int, x, gate_w, sh_gate_up, sh_down, sh_gate, out, chunks: int = 2, record=None):
+        """The same block with the exchanges under the compute.  The send buffers are sorted by (owner,
+        expert), so every owner's experts are cut into `chunks` contiguous ranges and each range is
+        exchanged and computed on its own; an expert's routes stay in one range, so no weight is
+        dequantised twice:
+
+            route, pack, counts per (owner, range)         one host read-back, as in `forward`
+            dispatch of every range (async, in order)      the shared expert runs under the first one
+            range c: wait dispatch | experts | return (async)    experts of c run under dispatch of c + 1
+                                                                  and the return of c - 1
+            wait the returns | combine
+
+        The returned rows land in send order, so the combine is the one of `forward`.  Every rank must
+        pass the same `chunks`; it must divide the experts per rank."""
+        mark = record or (lambda name: None)
+        b = self.b
+        world = self.world
+        per = b.per
+        if chunks < 1 or per % chunks:
+            raise _moe.bad(f"{per} experts per rank cannot be cut into {chunks} ranges")
+        sub = per // chunks
+        ids, w = b.route(x, gate_w)
+        send_x, send_e, send_w, route_idx, _ = b.pack(x, ids, w)
+        # routes per (owner, range): the send buffers are sorted by expert id
+        counts = torch.bincount((send_e // sub).long(), minlength=world * chunks).to(torch.int32)
+        recv_counts = torch.empty_like(counts)
+        dist.all_to_all_single(recv_counts, counts, group=self.group)           # [source][range]
+        sc = counts.reshape(world, chunks).tolist()                             # the one host read-back
+        rc = recv_counts.reshape(world, chunks).tolist()
+        self.last_counts = ([sum(r) for r in sc], [sum(r) for r in rc])
+        mark("packed")
+        # one meta row per route (expert id, weight bits): one exchange instead of two
+        send_m = torch.stack((send_e, send_w.view(torch.int32)), dim=1)
+        soff = [0]
+        for p in range(world):
+            for c in range(chunks):
+                soff.append(soff[-1] + sc[p][c])
+        pending = []
+        for c in range(chunks):
+            n = sum(rc[s][c] for s in range(world))
+            recv_x = send_x.new_empty((n,) + tuple(send_x.shape[1:]))
+            recv_m = send_m.new_empty((n, 2))
+            roff = [0]
+            for s in range(world):
+                roff.append(roff[-1] + rc[s][c])
+            ins_x = [send_x[soff[p * chunks + c]:soff[p * chunks + c + 1]] for p in range(world)]
+            ins_m = [send_m[soff[p * chunks + c]:soff[p * chunks + c + 1]] for p in range(world)]
+            outs_x = [recv_x[roff[s]:roff[s + 1]] for s in range(world)]
+            outs_m = [recv_m[roff[s]:roff[s + 1]] for s in range(world)]
+            works = [all_to_all_views(outs_x, ins_x, self.group), all_to_all_views(outs_m, ins_m, self.group)]
+            pending.append((works, recv_x, recv_m, roff))
+        shared, se_gate = b.shared(x, sh_gate_up, sh_down, sh_gate) if sh_gate_up is not None else (None, None)
+        mark("shared")
+        back = None
+        returns = []
+        for c, (works, recv_x, recv_m, roff) in enumerate(pending):
+            for wk in works:
+                wk.wait()
+            mark(f"dispatched{c}")
+            y = b.experts_forward(layer, recv_x, recv_m[:, 0].contiguous(), recv_m[:, 1].contiguous().view(torch.float32))
+            mark(f"computed{c}")
+            if back is None:
+                back = y.new_empty((soff[-1],) + tuple(y.shape[1:]))
+            ins = [y[roff[s]:roff[s + 1]] for s in range(world)]
+            outs = [back[soff[p * chunks + c]:soff[p * chunks + c + 1]] for p in range(world)]
+            returns.append((all_to_all_views(outs, ins, self.group), y))
+        for wk, _ in returns:
+            wk.wait()
         mark("returned")
         b.combine(back, route_idx, shared, se_gate, out)
         mark("combined")

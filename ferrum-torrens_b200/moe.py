@@ -331,6 +331,10 @@ class B200MoE:
     def kernel_launches(self) -> int:
         return int(self._lib.ftm_kernel_launches(self._h))
 
+    def set_sm_budget(self, sms: int):
+        """SMs the persistent expert kernels may occupy (0 = all): leaves room for exchange kernels."""
+        self._check(self._lib.ftm_set_sm_budget(self._h, int(sms)))
+
     def profile(self, on: bool):
         """Per-kernel CUDA-event timing (FT_PROFILE, src/infrastructure/profile.rs:1-14)."""
         self._check(self._lib.ftm_profile_enable(self._h, 1 if on else 0))
@@ -427,6 +431,32 @@ class B200MoE:
                                           ep_size, _dev(send_x, "send_x"), _dev(send_e, "send_e"), _dev(send_w, "send_w"),
                                           _dev(route_idx, "route_idx"), _dev(counts, "counts"), _stream_ptr(stream)))
         return send_x, send_e, send_w, route_idx, counts
+
+    def ep_plan(self, ids, ep_size: int, stream=None):
+        """Sort this rank's routes by (owner, expert): returns (route_idx [R] i32, counts [ep_size] i32)."""
+        torch = _torch()
+        tokens = ids.numel() // self.top_k
+        route_idx = torch.empty((ids.numel(),), dtype=torch.int32, device=ids.device)
+        counts = torch.empty((ep_size,), dtype=torch.int32, device=ids.device)
+        self._check(self._lib.ftm_ep_plan(self._h, _dev(ids, "ids"), tokens, ep_size, _dev(route_idx, "route_idx"),
+                                          _dev(counts, "counts"), _stream_ptr(stream)))
+        return route_idx, counts
+
+    def ep_dispatch(self, x, ids, weights, route_idx, ep_size: int, ep_rank: int, counts_all, peer_x: int, peer_meta: int,
+                    capacity_rows: int, stream=None):
+        """Store every route's row, expert id and weight into its owner's receive buffers over peer memory.
+        peer_x / peer_meta: device addresses of the arrays of ep_size buffer pointers."""
+        tokens = x.numel() // self.shapes.hidden
+        self._check(self._lib.ftm_ep_dispatch(self._h, _dev(x, "x"), _dev(ids, "ids"), _dev(weights, "weights"),
+                                              _dev(route_idx, "route_idx"), tokens, ep_size, ep_rank,
+                                              _dev(counts_all, "counts_all"), C.c_void_p(peer_x), C.c_void_p(peer_meta),
+                                              capacity_rows, _stream_ptr(stream)))
+
+    def ep_return(self, y, ep_size: int, ep_rank: int, counts_all, peer_back: int, capacity_rows: int, stream=None):
+        """Owner side: store the rows of y (receive order, bf16) into their sources' back buffers."""
+        rows = y.numel() // self.shapes.hidden
+        self._check(self._lib.ftm_ep_return(self._h, _dev(y, "y"), rows, ep_size, ep_rank, _dev(counts_all, "counts_all"),
+                                            C.c_void_p(peer_back), capacity_rows, _stream_ptr(stream)))
 
     def ep_combine(self, y, route_idx, shared, se_gate, out, stream=None):
         """out[t] = se_gate[t] * shared[t] + sum_j y[position of route t*k + j] (weights applied by the owner)."""

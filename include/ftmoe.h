@@ -251,8 +251,34 @@ FTM_API const char* ftm_profile_kind_name(int kind);
 FTM_API int ftm_ep_pack(ftm_handle* h, const void* x_bf16, const int32_t* ids, const float* weights, int32_t tokens,
                         int32_t ep_size, void* send_x, int32_t* send_expert, float* send_weight, int32_t* route_idx,
                         int32_t* counts, void* stream);
+/* The same exchange over peer memory (NVLink loads and stores instead of a collective library).
+ * counts_all [ep_size][ep_size] (device): row s = the counts of rank s, gathered by the caller.
+ *   ftm_ep_plan      sorts this rank's routes by (owner, expert): route_idx [R], counts [ep_size].
+ *   ftm_ep_dispatch  stores every route's activation row, expert id and weight straight into its
+ *                    owner's receive buffers: peer_x / peer_meta are device arrays of ep_size pointers
+ *                    ([capacity_rows, hidden] bf16 and [capacity_rows] (i32 id, f32 bits)); a rank's
+ *                    rows follow those of the ranks before it, in its send order.  Call after
+ *                    ftm_ep_plan on the same handle and stream.
+ *   ftm_ep_return    the owner stores row i of y [rows, hidden] bf16 (receive order) into the source's
+ *                    back buffer (peer_back: ep_size pointers to [capacity_rows, hidden] bf16) at the
+ *                    position the source packed that route.
+ * The caller orders the ranks (a barrier after the dispatch and after the return).  A row that would
+ * fall outside a buffer is not stored and ftm_sync_status reports it. */
+FTM_API int ftm_ep_plan(ftm_handle* h, const int32_t* ids, int32_t tokens, int32_t ep_size, int32_t* route_idx,
+                        int32_t* counts, void* stream);
+FTM_API int ftm_ep_dispatch(ftm_handle* h, const void* x_bf16, const int32_t* ids, const float* weights,
+                            const int32_t* route_idx, int32_t tokens, int32_t ep_size, int32_t ep_rank,
+                            const int32_t* counts_all, const uint64_t* peer_x, const uint64_t* peer_meta,
+                            int64_t capacity_rows, void* stream);
+FTM_API int ftm_ep_return(ftm_handle* h, const void* y_bf16, int32_t rows, int32_t ep_size, int32_t ep_rank,
+                          const int32_t* counts_all, const uint64_t* peer_back, int64_t capacity_rows, void* stream);
 FTM_API int ftm_ep_combine(ftm_handle* h, const void* y, int y_dtype, const int32_t* route_idx, const float* shared,
                            const float* se_gate, int32_t tokens, void* out, int out_dtype, void* stream);
+
+/* SMs that the persistent expert kernels of h may occupy (0 = all of the device).  The expert kernels
+ * run one CTA per SM for their whole duration; an expert-parallel caller that wants its exchange kernels
+ * (NCCL) to run at the same time leaves them a few SMs.  No counterpart in the reference (one GPU). */
+FTM_API int ftm_set_sm_budget(ftm_handle* h, int32_t sms);
 
 /* number of this library's kernels launched on h since creation (a diagnostics counter) */
 FTM_API uint64_t ftm_kernel_launches(const ftm_handle* h);

@@ -80,6 +80,12 @@ def _worker(rank, world, port, tokens_per_rank, q):
         assert np.array_equal(ids.numpy(), want_ids)
         err = np.abs(out.numpy() - want).max() / np.abs(want).max()
         sc, rc = layer.last_counts
+        # the overlapped schedule (expert ranges exchanged and computed one after the other) gives the same block
+        for chunks in (2, 4):
+            out2 = torch.empty_like(out)
+            ids2, _ = layer.forward_overlapped(0, x, None, True, None, None, out2, chunks=chunks)
+            assert np.array_equal(ids2.numpy(), want_ids)
+            assert np.abs(out2.numpy() - out.numpy()).max() <= 1e-6 * np.abs(want).max(), chunks
         q.put((rank, float(err), sc, rc))
     finally:
         dist.destroy_process_group()

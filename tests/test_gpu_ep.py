@@ -50,6 +50,21 @@ def _worker(rank, world, port, tokens, q):
         solo.sync_status()
         same_ids = bool(torch.equal(ids, want_ids))
         rel = float((out - want).norm() / want.norm())
+        # the overlapped schedule (exchanges under compute) gives the same block
+        out2 = torch.empty_like(out)
+        layer.forward_overlapped(0, _bf16(xb, dev), *w, out2, chunks=2)
+        be.front.sync_status()
+        be.owner.sync_status()
+        rel = max(rel, float((out2 - want).norm() / want.norm()))
+        # both exchanges by the library's own kernels over peer memory (two steps: the buffers are reused)
+        be.enable_peer_exchange()
+        for _ in range(2):
+            out3 = torch.zeros_like(out)
+            ids3, _ = layer.forward_p2p(0, _bf16(xb, dev), *w, out3)
+            be.front.sync_status()
+            be.owner.sync_status()
+            same_ids = same_ids and bool(torch.equal(ids3, want_ids))
+            rel = max(rel, float((out3 - want).norm() / want.norm()))
         q.put((rank, same_ids, rel))
         solo.close()
         be.close()
