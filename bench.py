@@ -316,6 +316,25 @@ def run_b200(args):
         both = (U * EXPERT_BYTES) / ((g_ms / g_n + d_ms / d_n) * 1e-3) / 1e9
         roofline["expert_weights_gbs"] = both
 
+    # the same steps replayed from one captured CUDA graph (one block per layer in the graph): what an engine
+    # that captures its decode step gets; reported beside the eager numbers, not instead of them
+    graph_info = None
+    if world == 1:
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            cg = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(cg, stream=side):
+                for l in range(nlayers):
+                    step(l)
+            reps = max(1, K // nlayers)
+            g_ms = timed(lambda i: cg.replay(), reps, 3)
+            moe.sync_status()
+            graph_info = {"layers_per_graph": nlayers, "replays": reps, "us_per_layer_step": g_ms / (reps * nlayers) * 1e3,
+                          "tokens_per_s": T * reps * nlayers / (g_ms * 1e-3)}
+        except Exception as exc:      # a failed capture must not lose the eager line
+            graph_info = {"error": str(exc)[:200]}
+
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
         "ms_per_step": total_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -325,7 +344,7 @@ def run_b200(args):
                    "l2": f"inputs larger than L2: {nlayers} independently seeded layers "
                          f"({nlayers * EXPERTS * EXPERT_BYTES / 1e6:.0f} MB of banks) cycled step by step",
                    "timed_region": "whole block (router, routed experts, shared expert, combine), CUDA events"},
-        "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline, "clocks": clocks,
+        "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline, "clocks": clocks, "graph_replay": graph_info,
     }
 
     if args.sweep and world == 1:

@@ -535,9 +535,14 @@ static int router_locked(ftm_handle* h, const void* x, const void* gate_w, int32
     if (!x || !gate_w || !ids_out || !weights_out) return fail(h, FTM_ERR_BAD, "moe: router: null buffer");
     if (tokens <= 0 || tokens > h->cfg.max_tokens)
         return fail(h, FTM_ERR_BAD, "moe: router: %d tokens (max_tokens %d)", tokens, h->cfg.max_tokens);
-    h->launches += launch_router_logits((const __nv_bfloat16*)x, (const __nv_bfloat16*)gate_w, tokens, h->cfg.experts,
-                                        h->cfg.hidden, h->logits, h->ctx(s));
-    h->launches += launch_router_topk(h->logits, tokens, h->cfg.experts, h->cfg.top_k, ids_out, weights_out, h->ctx(s));
+    if (router_fused_supported(tokens, h->cfg.experts, h->cfg.hidden, h->cfg.top_k)) {
+        h->launches += launch_router_fused((const __nv_bfloat16*)x, (const __nv_bfloat16*)gate_w, tokens, h->cfg.hidden,
+                                           h->cfg.top_k, ids_out, weights_out, h->ctx(s));
+    } else {
+        h->launches += launch_router_logits((const __nv_bfloat16*)x, (const __nv_bfloat16*)gate_w, tokens, h->cfg.experts,
+                                            h->cfg.hidden, h->logits, h->ctx(s));
+        h->launches += launch_router_topk(h->logits, tokens, h->cfg.experts, h->cfg.top_k, ids_out, weights_out, h->ctx(s));
+    }
     CU(h, cudaGetLastError());
     return FTM_OK;
 }

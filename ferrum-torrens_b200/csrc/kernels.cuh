@@ -44,6 +44,11 @@ int launch_router_logits(const __nv_bfloat16* x, const __nv_bfloat16* gate_w, in
 int launch_router_topk(const float* logits, int tokens, int experts, int top_k, int32_t* ids,
                        float* weights, const Ctx& c);
 
+// logits and top-k in one cluster launch (256 experts, fewer than 1024 tokens)
+bool router_fused_supported(int tokens, int experts, int hidden, int top_k);
+int launch_router_fused(const __nv_bfloat16* x, const __nv_bfloat16* gate_w, int tokens, int hidden, int top_k,
+                        int32_t* ids, float* weights, const Ctx& c);
+
 // permute.cu
 // scratch: cta_hist needs csr_scratch_ints(routes, bins) int32 entries
 size_t csr_scratch_ints(int routes, int bins);

@@ -8,6 +8,8 @@
 // The selected ids must equal the host path's bit for bit, so the k-sum is kept sequential:
 // a bf16 x bf16 product is exact in f32, hence fma(x, w, acc) rounds exactly like the host's
 // separate multiply and add, and one thread walks one (token, expert) chain in k order.
+#include <cooperative_groups.h>
+
 #include "kernels.cuh"
 
 namespace ftm {
@@ -213,14 +215,11 @@ router_logits_tiled_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloa
 // is "lowest lane, then lowest position in the lane".
 constexpr int kTopkWarps = 4;
 
+// one warp: softmax over the row's logits, top-k by probability (ties: lowest index), renormalise.
+// `row` may point to global or shared memory.
 template <int PER>
-__global__ void __launch_bounds__(kTopkWarps * 32)
-router_topk_kernel(const float* __restrict__ logits, int tokens, int experts, int top_k,
-                   int32_t* __restrict__ ids, float* __restrict__ weights) {
-    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-    const int t = blockIdx.x * kTopkWarps + warp;
-    if (t >= tokens) return;
-    const float* row = logits + (size_t)t * experts;
+__device__ __forceinline__ void warp_topk_row(const float* row, int experts, int top_k, int lane,
+                                              int32_t* __restrict__ ids_row, float* __restrict__ weights_row) {
     float v[PER];
     float mx = -INFINITY;
 #pragma unroll
@@ -279,10 +278,110 @@ router_topk_kernel(const float* __restrict__ logits, int tokens, int experts, in
     }
     const float inv2 = __fdiv_rn(1.0f, topsum);
     if (lane < top_k) {
-        ids[(size_t)t * top_k + lane] = my_id;
-        weights[(size_t)t * top_k + lane] = __fmul_rn(my_p, inv2);
+        ids_row[lane] = my_id;
+        weights_row[lane] = __fmul_rn(my_p, inv2);
     }
 }
+
+template <int PER>
+__global__ void __launch_bounds__(kTopkWarps * 32)
+router_topk_kernel(const float* __restrict__ logits, int tokens, int experts, int top_k,
+                   int32_t* __restrict__ ids, float* __restrict__ weights) {
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int t = blockIdx.x * kTopkWarps + warp;
+    if (t >= tokens) return;
+    warp_topk_row<PER>(logits + (size_t)t * experts, experts, top_k, lane, ids + (size_t)t * top_k, weights + (size_t)t * top_k);
+}
+
+// ---- fused router for decode batches: logits and top-k in one launch --------------------------
+// 256 experts, hidden % 256 == 0.  A cluster of 8 CTAs covers the 256 experts of 4 tokens: CTA r computes
+// the logits of experts 32r..32r+31 (lane = expert, warp = token, ONE chain per thread, so the launch has
+// tokens/4 x 8 CTAs and the chain of 2048 dependent FMAs is the only long latency), stores them into the
+// first CTA's shared memory (distributed shared memory), and after the cluster barrier the first CTA's four
+// warps run the top-k of the four tokens.  Same arithmetic, same order as the two separate kernels.
+constexpr int kFusedTok = 4, kFusedK = 256;
+constexpr int kFusedWStride = kFusedK * 2 + 16;
+
+__global__ void __cluster_dims__(8, 1, 1) __launch_bounds__(128)
+router_fused_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gate_w, int tokens,
+                    int hidden, int top_k, int32_t* __restrict__ ids, float* __restrict__ weights) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    __shared__ __align__(16) uint8_t wbuf[2][32 * kFusedWStride];
+    __shared__ __align__(16) float xbuf[2][kFusedTok][kFusedK];
+    __shared__ float slog[kFusedTok][256];       // used in the cluster's first CTA
+    const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+    const int rank = (int)cluster.block_rank();   // = blockIdx.x: experts 32 * rank ..
+    const int e0 = rank * 32, t0 = blockIdx.y * kFusedTok;
+    const int nchunks = hidden / kFusedK;
+    const uint32_t wbase = (uint32_t)__cvta_generic_to_shared(&wbuf[0][0]);
+
+    auto issue_w = [&](int c, int b) {
+        for (int i = tid; i < 32 * (kFusedK / 8); i += 128) {
+            const int row = i / (kFusedK / 8), piece = i % (kFusedK / 8);
+            cp_async16(wbase + b * 32 * kFusedWStride + row * kFusedWStride + piece * 16,
+                       gate_w + (size_t)(e0 + row) * hidden + c * kFusedK + piece * 8);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    // activations of the chunk: thread -> token tid / 32, 8 k at lane * 8
+    uint4 xr;
+    auto load_x = [&](int c) {
+        const int t = t0 + warp;
+        xr = make_uint4(0, 0, 0, 0);
+        if (t < tokens) xr = *reinterpret_cast<const uint4*>(x + (size_t)t * hidden + c * kFusedK + lane * 8);
+    };
+    auto store_x = [&](int b) {
+        const uint32_t w[4] = {xr.x, xr.y, xr.z, xr.w};
+        float* dst = &xbuf[b][warp][lane * 8];
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            const float2 v = bf16x2_to_f32(w[q]);
+            dst[2 * q] = v.x;
+            dst[2 * q + 1] = v.y;
+        }
+    };
+    issue_w(0, 0);
+    load_x(0);
+    store_x(0);
+    float acc = 0.f;
+    for (int c = 0; c < nchunks; c++) {
+        const int b = c & 1;
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        if (c + 1 < nchunks) {
+            issue_w(c + 1, b ^ 1);
+            load_x(c + 1);
+        }
+        const uint32_t wrow = wbase + b * 32 * kFusedWStride + lane * kFusedWStride;
+        const float* xs = &xbuf[b][warp][0];
+#pragma unroll 4
+        for (int kk = 0; kk < kFusedK; kk += 8) {
+            uint4 wv;
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(wv.x), "=r"(wv.y), "=r"(wv.z), "=r"(wv.w) : "r"(wrow + kk * 2));
+            const float4 xa = *reinterpret_cast<const float4*>(xs + kk), xb = *reinterpret_cast<const float4*>(xs + kk + 4);
+            const float2 w01 = bf16x2_to_f32(wv.x), w23 = bf16x2_to_f32(wv.y), w45 = bf16x2_to_f32(wv.z), w67 = bf16x2_to_f32(wv.w);
+            acc = __fmaf_rn(xa.x, w01.x, acc);
+            acc = __fmaf_rn(xa.y, w01.y, acc);
+            acc = __fmaf_rn(xa.z, w23.x, acc);
+            acc = __fmaf_rn(xa.w, w23.y, acc);
+            acc = __fmaf_rn(xb.x, w45.x, acc);
+            acc = __fmaf_rn(xb.y, w45.y, acc);
+            acc = __fmaf_rn(xb.z, w67.x, acc);
+            acc = __fmaf_rn(xb.w, w67.y, acc);
+        }
+        if (c + 1 < nchunks) store_x(b ^ 1);
+    }
+    // hand the logit to the cluster's first CTA
+    float* remote = cluster.map_shared_rank(&slog[0][0], 0);
+    remote[warp * 256 + e0 + lane] = acc;
+    cluster.sync();
+    if (rank == 0) {
+        const int t = t0 + warp;
+        if (t < tokens) warp_topk_row<8>(&slog[warp][0], 256, top_k, lane, ids + (size_t)t * top_k, weights + (size_t)t * top_k);
+    }
+}
+
 
 
 // ---- wide variant for large batches --------------------------------------------------------
@@ -440,6 +539,19 @@ int launch_router_logits(const __nv_bfloat16* x, const __nv_bfloat16* gate_w, in
         router_logits_kernel<TT><<<grid, block, smem, c.s>>>(x, gate_w, tokens, experts, hidden, logits);
         c.end();
     }
+    return 1;
+}
+
+bool router_fused_supported(int tokens, int experts, int hidden, int top_k) {
+    return experts == 256 && hidden % kFusedK == 0 && tokens < 1024 && top_k <= 32;
+}
+
+int launch_router_fused(const __nv_bfloat16* x, const __nv_bfloat16* gate_w, int tokens, int hidden, int top_k,
+                        int32_t* ids, float* weights, const Ctx& c) {
+    dim3 grid(8, (tokens + kFusedTok - 1) / kFusedTok);
+    c.begin(K_ROUTER_LOGITS);
+    router_fused_kernel<<<grid, 128, 0, c.s>>>(x, gate_w, tokens, hidden, top_k, ids, weights);
+    c.end();
     return 1;
 }
 
