@@ -284,7 +284,6 @@ struct ExpertArgs {
     float* yroute;              // down out: [routes, hidden] f32, weighted
     int32_t* err;
     int N, top_k;
-    int debug;  // diagnostics: 1 = skip the arithmetic (copy pipeline only), 2 = every group reads slot 0
 };
 
 // GATE_UP: K = hidden, a warp item is 8 gate rows and the 8 matching up rows, so that the
@@ -372,7 +371,7 @@ __global__ void __launch_bounds__(Cfg<GATE_UP, K_, NT>::kThreads, OCC) expert_mm
     // ---- copy issue: piece `half` of item `it` (group descriptor `grp`) into ring position n % D ----
     auto issue = [&](const int4 grp, int it, int half, int n) {
         const int blk = it % blocks;
-        const size_t slot_rows = (a.debug == 2) ? 0 : (size_t)grp.x * a.N;
+        const size_t slot_rows = (size_t)grp.x * a.N;
         const uint32_t bar = full0 + 8u * (n % D);
         uint8_t* const sp = wbase + (size_t)(n % D) * C::kStageBytes;
         uint8_t* const sc = wbase + D * C::kStageBytes + (size_t)((n / SUB) % NSB) * C::kScaleBytes;
@@ -518,7 +517,7 @@ __global__ void __launch_bounds__(Cfg<GATE_UP, K_, NT>::kThreads, OCC) expert_mm
                 const uint32_t row_lo = sp + g8 * RSA + t4 * 16, row_hi = row_lo + 8 * RSA;
                 const uint32_t sc_lo = sc + g8 * RSS + half * (KSUB / 16), sc_hi = sc_lo + 8 * RSS;
                 const uint32_t xa = smem_u32(xtile) + g8 * RSX + t4 * 16 + half * (KSUB * 2);
-                if (a.debug != 1) {
+                {
 #pragma unroll
                     for (int w2 = 0; w2 < WIN / 2; w2++) {
                         // scales of two windows: 16 bytes per row
@@ -558,9 +557,6 @@ __global__ void __launch_bounds__(Cfg<GATE_UP, K_, NT>::kThreads, OCC) expert_mm
                             }
                         }
                     }
-                } else {
-                    const uint4 plo = lds128(row_lo), phi = lds128(row_hi + (WIN - 1) * 64);
-                    acc[0][0][0] = __uint_as_float(plo.x ^ phi.w);
                 }
                 n_done++;
                 // every lane's reads of the buffer have returned (their values fed the MMAs above), so the
@@ -729,8 +725,6 @@ int launch_decode_mma(const BankView& b, const void* x, int x_dtype, const Decod
     }
 
     ExpertArgs a{};
-    static const int debug_mode = [] { const char* e = getenv("FTM_DEBUG_EXPERT"); return e ? atoi(e) : 0; }();
-    a.debug = debug_mode;
     a.groups = sc.groups;
     a.sorted_route = sc.sorted_route;
     a.n_groups = sc.n_groups;
