@@ -399,8 +399,19 @@ def run_ep(args, pkg, dev, world, rank, local):
 
     chunks = max(1, args.ep_chunks)
     p2p = args.ep_exchange == "p2p"
+    exchange_note = None
     if p2p:
-        be.enable_peer_exchange()
+        # symmetric memory must come up on every rank, else every rank takes the NCCL exchange
+        ok = torch.ones((1,), device=dev)
+        try:
+            be.enable_peer_exchange()
+        except Exception as exc:
+            ok.zero_()
+            exchange_note = f"peer exchange unavailable ({str(exc)[:120]}); NCCL all-to-all used"
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if float(ok.item()) == 0.0:
+            p2p = False
+            exchange_note = exchange_note or "peer exchange unavailable on another rank; NCCL all-to-all used"
 
     def step(i, record=None, x=None):
         l = i % nlayers
@@ -500,7 +511,7 @@ def run_ep(args, pkg, dev, world, rank, local):
                        "l2": f"inputs larger than L2: {nlayers} layers cycled, {T * TOP_K} routes x 4 KB rows per step",
                        "timed_region": "whole block incl. both all-to-alls, CUDA events, max over ranks"},
             "gpu_launches": int(launches), "clocks": clocks,
-            "ep": {"phases_of": "one step, marks after each phase" if p2p else "one step of the plain schedule (every phase waits for the one before)",
+            "ep": {"exchange_note": exchange_note,"phases_of": "one step, marks after each phase" if p2p else "one step of the plain schedule (every phase waits for the one before)",
                    "phases_ms_max_over_ranks": phases, "unpipelined_ms_per_step": sum(phases.values()),
                    "exchange_ms_unpipelined": phases["dispatch_a2a_ms"] + phases["return_a2a_ms"],
                    "max_routes_sent_off_rank": float(sent.item()),
