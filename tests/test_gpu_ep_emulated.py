@@ -1,0 +1,113 @@
+"""The peer-memory exchange kernels (ftm_ep_plan / ftm_ep_dispatch / ftm_ep_return / ftm_ep_combine) for
+4 and 8 ranks, emulated on ONE GPU: every "rank" is a pair of adapter handles in this process and the peer
+pointer arrays point at the other ranks' buffers on the same device.  The kernels of different ranks do not
+wait for one another (the ordering between the phases is the host's), so they run one after the other here.
+The result of every rank must equal the block computed by one adapter that holds all experts."""
+import importlib
+
+import numpy as np
+import pytest
+import torch
+
+pkg = importlib.import_module("ferrum-torrens_b200")
+
+pytestmark = pytest.mark.gpu
+
+H, I, E, K, SI = 256, 64, 16, 4, 64
+
+
+def _bf16(bits, dev):
+    return torch.from_numpy(np.ascontiguousarray(bits).view(np.int16)).to(dev).view(torch.bfloat16)
+
+
+@pytest.mark.parametrize("world,tokens", [(4, [37, 5, 64, 1]), (8, [9, 33, 2, 17, 40, 1, 8, 21])])
+def test_peer_exchange_kernels_many_ranks_on_one_gpu(world, tokens):
+    dev = torch.device("cuda:0")
+    lay = pkg.synth.make_layer(91, hidden=H, inter=I, experts=E, top_k=K, shared_inter=SI)
+    shapes = pkg.ExpertShapes(H, I)
+    per = E // world
+    maxtok = max(tokens)
+    cap = sum(tokens) * K
+    dense = [_bf16(a, dev) for a in (lay.gate_w, lay.sh_gate_up, lay.sh_down, lay.sh_gate)]
+
+    solo = pkg.B200MoE(0, shapes, E, experts=E, layers=1, top_k=K, shared_inter=SI, max_tokens=maxtok)
+    for e in range(E):
+        solo.load(0, e, e, lay.fields(e))
+    fronts, owners = [], []
+    for r in range(world):
+        fronts.append(pkg.B200MoE(0, shapes, 1, experts=E, layers=1, top_k=K, shared_inter=SI, max_tokens=maxtok))
+        ow = pkg.B200MoE(0, shapes, per, experts=E, layers=1, top_k=1, shared_inter=0, max_tokens=cap)
+        for e in range(r * per, (r + 1) * per):
+            ow.load(0, e, e - r * per, lay.fields(e))
+        owners.append(ow)
+
+    xs = [_bf16(pkg.synth.make_x(700 + r, tokens[r], H), dev) for r in range(world)]
+    recv_x = [torch.zeros((cap, H), dtype=torch.bfloat16, device=dev) for _ in range(world)]
+    recv_m = [torch.zeros((cap, 2), dtype=torch.int32, device=dev) for _ in range(world)]
+    back = [torch.zeros((tokens[r] * K, H), dtype=torch.bfloat16, device=dev) for r in range(world)]
+    ptrs = lambda ts: torch.tensor([t.data_ptr() for t in ts], dtype=torch.int64, device=dev)
+    peer_x, peer_m, peer_back = ptrs(recv_x), ptrs(recv_m), ptrs(back)
+
+    routed = []
+    for r in range(world):
+        ids, w = fronts[r].router(xs[r], dense[0])
+        route_idx, counts = fronts[r].ep_plan(ids, world)
+        routed.append((ids, w, route_idx, counts))
+    counts_all = torch.cat([c for _, _, _, c in routed]).contiguous()             # the all-gather
+    ca = counts_all.reshape(world, world).cpu().numpy()
+    assert ca.sum(axis=1).tolist() == [t * K for t in tokens]
+    for r in range(world):
+        ids, w, route_idx, _ = routed[r]
+        fronts[r].ep_dispatch(xs[r], ids, w, route_idx, world, r, counts_all, peer_x.data_ptr(), peer_m.data_ptr(), cap)
+    torch.cuda.synchronize()                                                       # the barrier
+    for r in range(world):
+        n = int(ca[:, r].sum())
+        meta = recv_m[r][:n]
+        assert bool(((meta[:, 0] // per) == r).all()), "a rank only receives routes of experts it owns"
+        if n:
+            y = torch.empty((n, H), dtype=torch.bfloat16, device=dev)
+            req = pkg.MoEDeviceRequest(0, H, I, 1, recv_x[r][:n], meta[:, 0].contiguous().reshape(n, 1),
+                                       meta[:, 1].contiguous().view(torch.float32).reshape(n, 1))
+            owners[r].grouped_moe_staged(req, y)
+            owners[r].ep_return(y, world, r, counts_all, peer_back.data_ptr(), min(tokens) * K)
+    torch.cuda.synchronize()                                                       # the barrier
+    # the smallest back buffer was given as the capacity of all: rows beyond it are dropped and reported, so
+    # redo the return with each source's real capacity only when the sizes differ
+    if len(set(tokens)) > 1:
+        statuses = []
+        for r in range(world):
+            try:
+                owners[r].sync_status()
+                statuses.append(True)
+            except pkg.MoEError:
+                statuses.append(False)
+        assert not all(statuses), "rows past the given capacity must be reported, not stored"
+        cap_back = max(tokens) * K
+        back = [torch.zeros((cap_back, H), dtype=torch.bfloat16, device=dev) for _ in range(world)]
+        peer_back = ptrs(back)
+        for r in range(world):
+            n = int(ca[:, r].sum())
+            if n:
+                meta = recv_m[r][:n]
+                y = torch.empty((n, H), dtype=torch.bfloat16, device=dev)
+                req = pkg.MoEDeviceRequest(0, H, I, 1, recv_x[r][:n], meta[:, 0].contiguous().reshape(n, 1),
+                                           meta[:, 1].contiguous().view(torch.float32).reshape(n, 1))
+                owners[r].grouped_moe_staged(req, y)
+                owners[r].ep_return(y, world, r, counts_all, peer_back.data_ptr(), cap_back)
+        torch.cuda.synchronize()
+    for r in range(world):
+        owners[r].sync_status()
+        fronts[r].sync_status()
+        ids, w, route_idx, _ = routed[r]
+        shared, se_gate = fronts[r].shared_expert(xs[r], dense[1], dense[2], dense[3])
+        out = torch.empty((tokens[r], H), dtype=torch.float32, device=dev)
+        fronts[r].ep_combine(back[r][:tokens[r] * K], route_idx, shared, se_gate, out)
+        want = torch.empty((tokens[r], H), dtype=torch.float32, device=dev)
+        want_ids = torch.empty((tokens[r], K), dtype=torch.int32, device=dev)
+        solo.moe_block(0, xs[r], *dense, want, ids_out=want_ids)
+        solo.sync_status()
+        assert torch.equal(ids, want_ids)
+        rel = float((out - want).norm() / want.norm())
+        assert rel < 5e-3, (r, rel)     # one bf16 rounding per returned row
+    for m in fronts + owners + [solo]:
+        m.close()
