@@ -496,6 +496,23 @@ def run_ep(args, pkg, dev, world, rank, local):
     dist.all_reduce(acc, op=dist.ReduceOp.MAX)
     phases = {n: float(v) for n, v in zip(["router_shared_pack_ms", "dispatch_a2a_ms", "experts_ms", "return_a2a_ms",
                                            "combine_ms"], acc.tolist())}
+    # roofline of the dominant kernel (the owner's grouped gate_up GEMM): CUDA events around every launch
+    be.owner.profile(True)
+    for i in range(3):
+        step(W + i)
+    oprof = be.owner.profile_read()
+    be.owner.profile(False)
+    recv_routes = float(sum(layer.last_counts[1]))
+    roofline = None
+    if "grouped_gate_up" in oprof:
+        pk = peaks()
+        g_ms, g_n = oprof["grouped_gate_up"]
+        flops = recv_routes * 2.0 * HIDDEN * (2 * INTER)
+        ach = flops / (g_ms / g_n * 1e-3) / 1e12
+        roofline = {"bound": "tensor", "kernel": "grouped_gate_up (owner side, rank 0)", "achieved": ach, "peak": pk["bf16_tflops"],
+                    "unit": "TFLOP/s", "frac": ach / pk["bf16_tflops"], "peak_source": pk["which"], "traffic": None,
+                    "routes_received": recv_routes, "us_per_launch": g_ms / g_n * 1e3,
+                    "kernels": {k: {"us_per_launch": ms / n * 1e3, "launches": n} for k, (ms, n) in oprof.items()}}
     sent = torch.tensor([sum(layer.last_counts[0]) - layer.last_counts[0][rank]], device=dev, dtype=torch.float32)
     dist.all_reduce(sent, op=dist.ReduceOp.MAX)
     if rank == 0:
@@ -516,7 +533,7 @@ def run_ep(args, pkg, dev, world, rank, local):
                    "exchange_ms_unpipelined": phases["dispatch_a2a_ms"] + phases["return_a2a_ms"],
                    "max_routes_sent_off_rank": float(sent.item()),
                    "nvlink_bytes_each_way_per_gpu": float(sent.item()) * HIDDEN * 2},
-            "e2e": e2e, "roofline": None,
+            "e2e": e2e, "roofline": roofline,
         }
         print(json.dumps(line))
     be.close()

@@ -68,52 +68,64 @@ __device__ __forceinline__ uint32_t hmul2_f16(uint32_t a, uint32_t b) {
 }
 
 // ---- gather: sorted activations as scaled f16 ------------------------------------------------
-// one CTA per sorted position; K % 256 == 0
+// one warp per sorted position (no block-wide synchronisation); K == 2048: a lane holds 8 chunks of 8 k
 __global__ void __launch_bounds__(256)
 prefill_gather_kernel(const void* __restrict__ x, int x_dtype, const int32_t* __restrict__ route_idx,
                       const int32_t* __restrict__ n_sorted, int top_k, int K, __half* __restrict__ xg,
                       float* __restrict__ row_scale) {
-    __shared__ float wmax[8];
-    __shared__ float s_inv;
-    const int i = blockIdx.x;
+    const int i = blockIdx.x * 8 + threadIdx.x / 32, lane = threadIdx.x % 32;
     if (i >= *n_sorted) return;   // routes of unknown experts are in no bucket
     const size_t src = (size_t)(route_idx[i] / top_k) * K;
-    float v[8];
+    constexpr int kChunksPerLane = 8;   // 2048 / (32 lanes * 8 k)
+    float v[kChunksPerLane][8];
     float m = 0.f;
-    const int k0 = threadIdx.x * 8;   // K == 2048: one pass
-    for (int k = k0; k < K; k += 2048) {
+    if (x_dtype == 0) {
+        uint4 raw[kChunksPerLane];
 #pragma unroll
-        for (int q = 0; q < 8; q++) {
-            v[q] = load_act(x, x_dtype, src + k + q);
-            m = fmaxf(m, fabsf(v[q]));
+        for (int c = 0; c < kChunksPerLane; c++)
+            raw[c] = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(x) + src + (c * 32 + lane) * 8);
+#pragma unroll
+        for (int c = 0; c < kChunksPerLane; c++) {
+            const uint32_t w[4] = {raw[c].x, raw[c].y, raw[c].z, raw[c].w};
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const float2 f = bf16x2_to_f32(w[q]);
+                v[c][2 * q] = f.x;
+                v[c][2 * q + 1] = f.y;
+            }
+        }
+    } else {
+#pragma unroll
+        for (int c = 0; c < kChunksPerLane; c++) {
+            const float* p = reinterpret_cast<const float*>(x) + src + (c * 32 + lane) * 8;
+            const float4 f0 = *reinterpret_cast<const float4*>(p), f1 = *reinterpret_cast<const float4*>(p + 4);
+            v[c][0] = f0.x; v[c][1] = f0.y; v[c][2] = f0.z; v[c][3] = f0.w;
+            v[c][4] = f1.x; v[c][5] = f1.y; v[c][6] = f1.z; v[c][7] = f1.w;
         }
     }
+#pragma unroll
+    for (int c = 0; c < kChunksPerLane; c++)
+#pragma unroll
+        for (int q = 0; q < 8; q++) m = fmaxf(m, fabsf(v[c][q]));
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    if ((threadIdx.x & 31) == 0) wmax[threadIdx.x >> 5] = m;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        float mm = 0.f;
-        for (int w = 0; w < 8; w++) mm = fmaxf(mm, wmax[w]);
-        const int e = max((int)((__float_as_uint(mm) >> 23) & 0xff), 15);
-        float inv = 1.0f, sc = 1.0f;
-        if (e < 255) {
-            inv = __uint_as_float((uint32_t)(127 + 14 - (e - 127)) << 23);
-            sc = __uint_as_float((uint32_t)(127 - 14 + (e - 127)) << 23);
-        }
-        s_inv = inv;
-        row_scale[i] = sc;
+    // largest magnitude into [2^14, 2^15): exact power-of-two scaling
+    const int e = max((int)((__float_as_uint(m) >> 23) & 0xff), 15);
+    float inv = 1.0f, sc = 1.0f;
+    if (e < 255) {
+        inv = __uint_as_float((uint32_t)(127 + 14 - (e - 127)) << 23);
+        sc = __uint_as_float((uint32_t)(127 - 14 + (e - 127)) << 23);
     }
-    __syncthreads();
-    const float inv = s_inv;
-    for (int k = k0; k < K; k += 2048) {
+#pragma unroll
+    for (int c = 0; c < kChunksPerLane; c++) {
         __half2 h[4];
 #pragma unroll
-        for (int q = 0; q < 4; q++) h[q] = __floats2half2_rn(v[2 * q] * inv, v[2 * q + 1] * inv);
-        *reinterpret_cast<uint4*>(xg + (size_t)i * K + k) =
+        for (int q = 0; q < 4; q++) h[q] = __floats2half2_rn(v[c][2 * q] * inv, v[c][2 * q + 1] * inv);
+        *reinterpret_cast<uint4*>(xg + (size_t)i * K + (c * 32 + lane) * 8) =
             make_uint4(*reinterpret_cast<uint32_t*>(&h[0]), *reinterpret_cast<uint32_t*>(&h[1]),
                        *reinterpret_cast<uint32_t*>(&h[2]), *reinterpret_cast<uint32_t*>(&h[3]));
     }
+    if (lane == 0) row_scale[i] = sc;
 }
 
 // ic1 (f32, sorted rows: gate | up) -> ic2 = silu(gate) * up as f16 with a per-row power-of-two scale.
@@ -573,7 +585,7 @@ int launch_prefill_umma(const BankView& b, const void* x, int x_dtype, const Dec
     launches += launch_groups_from_csr(sc.seg, nbins, slot_of_bin, b.slots, kTileTok, sc.groups, sc.n_groups, c);
     // 3. sorted, scaled f16 activations
     c.begin(K_PERMUTE_ACT);
-    prefill_gather_kernel<<<routes, 256, 0, c.s>>>(x, x_dtype, sc.route_idx, sc.seg + nbins, top_k, b.hidden, sc.xg,
+    prefill_gather_kernel<<<(routes + 7) / 8, 256, 0, c.s>>>(x, x_dtype, sc.route_idx, sc.seg + nbins, top_k, b.hidden, sc.xg,
                                                    sc.row_scale);
     c.end();
     launches++;
