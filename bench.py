@@ -58,6 +58,11 @@ def parse():
     ap.add_argument("--ep-exchange", default="p2p", choices=["p2p", "nccl"],
                     help="N > 1: dispatch / return by this library's kernels over peer memory, or by NCCL all-to-all")
     ap.add_argument("--ep-comm-sms", type=int, default=16, help="N > 1: SMs left to the exchange kernels when overlapping")
+    ap.add_argument("--zipf", type=float, default=None,
+                    help="add a per-expert Zipf(alpha) popularity bias to the router logits (skewed expert counts)")
+    ap.add_argument("--stack", action="store_true",
+                    help="N = 1: one step = a pass through --layers MoE blocks with a residual add between them "
+                         "(the 40-layer stack of the benchmark configs: --layers 40 --stack)")
     ap.add_argument("--path", default="auto", choices=["auto", "gemv", "grouped", "scalar"],
                     help="routed-expert kernels: auto = decode kernels up to 256 tokens, tcgen05 grouped GEMM above")
     return ap.parse_args()
@@ -196,10 +201,14 @@ def run_b200(args):
     moe = pkg.B200MoE(local, pkg.ExpertShapes(HIDDEN, INTER), EXPERTS * nlayers, experts=EXPERTS, layers=nlayers,
                       top_k=TOP_K, shared_inter=SHARED, max_tokens=max(T, 64))
     dense, xs = [], []
+    # a stack feeds every block's output back into the residual stream: row globals 2^-6 / 2^-10 keep it O(1)
+    gbits = (0x2400, 0x1400) if args.stack else (0x3C00, 0x3C00)
     for l in range(nlayers):
-        pkg.synth.fill_banks_on_device(moe, l, seed=1000 + 17 * rank + l, slot0=l * EXPERTS)
-        dense.append(pkg.synth.device_dense_weights(2000 + 17 * rank + l, dev))
-        xs.append(pkg.synth.device_x(3000 + 17 * rank + l, T, HIDDEN, dev))
+        pkg.synth.fill_banks_on_device(moe, l, seed=1000 + 17 * rank + l, slot0=l * EXPERTS, global_bits=gbits)
+        dense.append(pkg.synth.device_dense_weights(2000 + 17 * rank + l, dev, zipf_alpha=args.zipf))
+        xs.append(pkg.synth.device_x(3000 + 17 * rank + l, T, HIDDEN, dev, biased=args.zipf is not None))
+    if args.stack and world == 1:
+        return run_stack(args, pkg, moe, dense, xs[0], dev, T, nlayers, path)
     out = torch.empty((T, HIDDEN), dtype=torch.bfloat16, device=dev)
     ids = torch.empty((T, TOP_K), dtype=torch.int32, device=dev)
     wts = torch.empty((T, TOP_K), dtype=torch.float32, device=dev)
@@ -340,7 +349,7 @@ def run_b200(args):
         "ms_per_step": total_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16 activations x NVFP4 (e2m1 + e4m3 block scales) weights, f32 accumulate", "data": "synthetic",
         "config": {"workload": f"{'decode' if T <= 256 else 'prefill'} T={T} tokens/step, hidden {HIDDEN}, {EXPERTS} resident NVFP4 experts top-{TOP_K}, "
-                               f"bf16 shared expert {SHARED}",
+                               f"bf16 shared expert {SHARED}, {'uniform' if args.zipf is None else f'Zipf({args.zipf})-skewed'} routing",
                    "l2": f"inputs larger than L2: {nlayers} independently seeded layers "
                          f"({nlayers * EXPERTS * EXPERT_BYTES / 1e6:.0f} MB of banks) cycled step by step",
                    "timed_region": "whole block (router, routed experts, shared expert, combine), CUDA events"},
@@ -376,6 +385,71 @@ def run_b200(args):
         dist.destroy_process_group()
 
 
+def run_stack(args, pkg, moe, dense, x0, dev, T, nlayers, path):
+    """One step = a pass through `nlayers` MoE blocks, x <- x + block(x) between them (the 40-layer stack of the
+    benchmark configs).  Prints one JSON line: tokens/s through the whole stack, eager and from one CUDA graph."""
+    import torch
+    out = torch.empty((T, HIDDEN), dtype=torch.bfloat16, device=dev)
+    xa, xb = torch.empty_like(x0), torch.empty_like(x0)
+
+    def stack_pass(i=0):
+        xa.copy_(x0)
+        cur, nxt = xa, xb
+        for l in range(nlayers):
+            g, su, sd, sg = dense[l]
+            moe.moe_block(l, cur, g, su, sd, sg, out, path=path)
+            torch.add(cur, out, out=nxt)
+            cur, nxt = nxt, cur
+        return cur
+
+    def timed(fn, steps, warmup):
+        for i in range(warmup):
+            fn(i)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            fn(i)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1)
+
+    W, K = max(3, args.warmup), max(1, args.steps)
+    last = stack_pass()
+    moe.sync_status()
+    finite = bool(torch.isfinite(last.float()).all())
+    rms = float(last.float().pow(2).mean().sqrt())
+    sampler = ClockSampler(dev.index or 0)
+    sampler.start()
+    ms = timed(stack_pass, K, W)
+    clocks = sampler.stop()
+    graph = None
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        cg = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(cg, stream=side):
+            stack_pass()
+        g_ms = timed(lambda i: cg.replay(), K, 3)
+        moe.sync_status()
+        graph = {"ms_per_pass": g_ms / K, "tokens_per_s": T * K / (g_ms * 1e-3)}
+    except Exception as exc:
+        graph = {"error": str(exc)[:200]}
+    print(json.dumps({
+        "metric": METRIC, "value": T * K / (ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": K, "warmup": W,
+        "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16 activations x NVFP4 (e2m1 + e4m3 block scales) weights, f32 accumulate", "data": "synthetic",
+        "config": {"workload": f"{nlayers}-layer MoE-only stack, T={T}, residual add between the blocks, "
+                               f"{nlayers * EXPERTS * EXPERT_BYTES / 1e9:.1f} GB of expert banks, independent seeds per layer; "
+                               "one step = one pass through all layers; value = tokens/s through the whole stack",
+                   "l2": "every layer's banks are read once per pass (banks far larger than L2)",
+                   "residual_rms_after_last_layer": rms, "finite": finite},
+        "layer_steps_per_s": nlayers * K / (ms * 1e-3), "us_per_layer": ms / K / nlayers * 1e3,
+        "graph_replay": graph, "clocks": clocks,
+    }))
+    moe.close()
+
+
 def run_ep(args, pkg, dev, world, rank, local):
     """N > 1: the expert-parallel layer (256 experts split over the ranks, T = 8192 tokens per GPU,
     dispatch / combine by NCCL all-to-all).  Weak scaling: per-GPU tokens are fixed."""
@@ -392,8 +466,8 @@ def run_ep(args, pkg, dev, world, rank, local):
     for l in range(nlayers):
         pkg.synth.fill_banks_on_device(be.owner, l, seed=1000 + 977 * rank + l, experts=per, slot0=l * per,
                                        expert0=rank * per)
-        dense.append(pkg.synth.device_dense_weights(2000 + l, dev))          # replicated: same seed on every rank
-        xs.append(pkg.synth.device_x(3000 + 17 * rank + l, T, HIDDEN, dev))
+        dense.append(pkg.synth.device_dense_weights(2000 + l, dev, zipf_alpha=args.zipf))   # replicated: same seed on every rank
+        xs.append(pkg.synth.device_x(3000 + 17 * rank + l, T, HIDDEN, dev, biased=args.zipf is not None))
     out = torch.empty((T, HIDDEN), dtype=torch.bfloat16, device=dev)
     layer = ep.ExpertParallelMoE(be, world)
 
@@ -522,7 +596,7 @@ def run_ep(args, pkg, dev, world, rank, local):
             "dtype": "bf16 activations x NVFP4 (e2m1 + e4m3 block scales) weights, f32 accumulate",
             "data": "synthetic",
             "config": {"workload": f"expert-parallel layer, T={T} tokens per GPU, {EXPERTS} experts split {per} per GPU, "
-                                   f"top-{TOP_K}, uniform routing, " +
+                                   f"top-{TOP_K}, {'uniform' if args.zipf is None else f'Zipf({args.zipf})-skewed'} routing, " +
                                    ("dispatch / return by peer-memory kernels over NVLink" if p2p else
                                     f"NCCL all-to-all dispatch/combine, {chunks} overlapped expert range(s) per owner"),
                        "l2": f"inputs larger than L2: {nlayers} layers cycled, {T * TOP_K} routes x 4 KB rows per step",

@@ -108,9 +108,11 @@ def make_x(seed: int, tokens: int, hidden: int, biased: bool = False) -> np.ndar
 # ---- device-side generation for the benchmark --------------------------------------------------
 
 def fill_banks_on_device(moe, layer: int, seed: int, experts: int | None = None, slot0: int = 0, chunk: int = 64,
-                         expert0: int = 0):
+                         expert0: int = 0, global_bits=(0x3C00, 0x3C00)):
     """Draws `experts` experts of `layer` (ids expert0, expert0 + 1, ..) straight into the adapter's banks
-    (slot = slot0 + i) and marks them resident.  Same distributions as make_layer."""
+    (slot = slot0 + i) and marks them resident.  Same distributions as make_layer.  `global_bits`: f16 bit
+    patterns of the gate_up and down row globals (1.0 by default; a multi-layer stack uses smaller ones so that
+    the residual stream stays O(1))."""
     import torch
     experts = experts if experts is not None else moe.experts
     g = torch.Generator(device=f"cuda:{moe.device}").manual_seed(seed)
@@ -126,7 +128,7 @@ def fill_banks_on_device(moe, layer: int, seed: int, experts: int | None = None,
                 u = torch.rand(part.shape, generator=g, device=part.device) * -6.0
                 part.copy_(torch.exp2(u).to(torch.float8_e4m3fn).view(torch.uint8))
             else:
-                part.view(torch.int16).fill_(0x3C00)
+                part.view(torch.int16).fill_(global_bits[b // 3])
     torch.cuda.synchronize()
     for e in range(experts):
         moe.adopt(layer, expert0 + e, slot0 + e)
