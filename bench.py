@@ -134,7 +134,13 @@ def host_layer_for_cpu(seed: int):
 def time_cpu(tokens_sample: int, steps: int, warmup: int, seed: int = 2024):
     """tokens/s of the CPU restatement of the reference's host path, all host threads."""
     pkg, o, lay, ol = host_layer_for_cpu(seed)
-    threads = o.max_threads()
+    # every core this process may run on: a launcher's OMP_NUM_THREADS=1 (torchrun sets it) must not shrink
+    # the CPU arm to one thread
+    try:
+        threads = len(os.sched_getaffinity(0))
+    except AttributeError:
+        threads = os.cpu_count() or 1
+    threads = max(threads, o.max_threads())
     times = []
     for i in range(warmup + steps):
         x = pkg.synth.bf16_bits_to_f32(pkg.synth.make_x(seed + i, tokens_sample, HIDDEN))
