@@ -202,7 +202,16 @@ class ExpertParallelMoE:
         route_idx, counts = b.front.ep_plan(ids, world)
         counts_all = torch.empty((world * world,), dtype=torch.int32, device=counts.device)
         dist.all_gather_into_tensor(counts_all, counts, group=self.group)
-        shared, se_gate = b.shared(x, sh_gate_up, sh_down, sh_gate) if sh_gate_up is not None else (None, None)
+        # the shared expert (tensor cores) runs on a side stream under the dispatch (NVLink stores)
+        shared = se_gate = None
+        side = None
+        if sh_gate_up is not None and x.is_cuda:
+            side = self._side_stream(x.device)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                shared, se_gate = b.shared(x, sh_gate_up, sh_down, sh_gate)
+        elif sh_gate_up is not None:
+            shared, se_gate = b.shared(x, sh_gate_up, sh_down, sh_gate)
         ca = counts_all.reshape(world, world).tolist()            # the one host read-back
         sc = ca[b.rank]
         rc = [ca[s][b.rank] for s in range(world)]
@@ -223,9 +232,19 @@ class ExpertParallelMoE:
             mark("computed")
         self._barrier(b)
         mark("returned")
+        if side is not None:
+            cur = torch.cuda.current_stream()
+            cur.wait_stream(side)
+            shared.record_stream(cur)       # allocated on the side stream, read on this one
+            se_gate.record_stream(cur)
         b.combine(b.p2p_back[:sum(sc)], route_idx, shared, se_gate, out)
         mark("combined")
         return ids, w
+
+    def _side_stream(self, device):
+        if getattr(self, "_side", None) is None:
+            self._side = torch.cuda.Stream(device=device)
+        return self._side
 
     def _barrier(self, b):
         # every rank's stores before this point are complete before any rank goes on
