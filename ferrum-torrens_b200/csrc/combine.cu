@@ -132,7 +132,11 @@ ep_dispatch_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restric
                    const int32_t* __restrict__ route_idx, const int32_t* __restrict__ seg, int top_k, int H, int per,
                    int world, int rank, const int32_t* __restrict__ counts_all, const uint64_t* __restrict__ peer_x,
                    const uint64_t* __restrict__ peer_meta, long long capacity, int32_t* err) {
-    const int i = blockIdx.x;
+    // CTAs walk the send order starting at the next rank's block, so that at any time every owner is written
+    // by one source (all ranks starting at owner 0 would share that owner's ingress bandwidth)
+    const int routes = gridDim.x;
+    int i = blockIdx.x + seg[((rank + 1) % world) * per];
+    if (i >= routes) i -= routes;
     const int r = route_idx[i];
     const int e = ids[r];
     const int p = e / per;
@@ -154,7 +158,11 @@ __global__ void __launch_bounds__(128)
 ep_return_kernel(const __nv_bfloat16* __restrict__ y, int n, int H, int world, int rank,
                  const int32_t* __restrict__ counts_all, const uint64_t* __restrict__ peer_back, long long capacity,
                  int32_t* err) {
-    const int i = blockIdx.x;
+    // rows are walked starting at the next rank's block (see ep_dispatch_kernel)
+    int first = 0;
+    for (int q = 0; q < (rank + 1) % world; q++) first += counts_all[q * world + rank];
+    int i = blockIdx.x + first;
+    if (i >= n) i -= n;
     int s = 0, roff = 0;
     for (; s < world; s++) {
         const int c = counts_all[s * world + rank];
