@@ -1,5 +1,5 @@
 """Expert parallelism on real GPUs (needs at least two): the n-rank result equals the single-GPU result
-on the same seeded inputs.  Run by hand with `gpurun --gpus 2`; skipped on a one-GPU box."""
+on the same seeded inputs.  Needs two GPUs; skipped on a one-GPU box."""
 import importlib
 import os
 import socket
