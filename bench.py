@@ -254,7 +254,6 @@ def run_b200(args):
     l0 = moe.kernel_launches()
     total_ms = timed(step, K, W)
     launches = (moe.kernel_launches() - l0) * K // (K + W)
-    clocks = sampler.stop() if rank == 0 else None
     value = world * T * K / (total_ms * 1e-3)
 
     # end to end: pinned host x in, block, result out, every step
@@ -330,6 +329,9 @@ def run_b200(args):
         roofline["down"] = {"achieved": dn, "frac": dn / pk["hbm_gbs"]}
         both = (U * EXPERT_BYTES) / ((g_ms / g_n + d_ms / d_n) * 1e-3) / 1e9
         roofline["expert_weights_gbs"] = both
+
+    # the sampler ran through the timed steps, the end-to-end steps and the per-kernel passes (all GPU-busy)
+    clocks = sampler.stop() if rank == 0 else None
 
     # the same steps replayed from one captured CUDA graph (one block per layer in the graph): what an engine
     # that captures its decode step gets; reported beside the eager numbers, not instead of them
