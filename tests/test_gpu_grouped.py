@@ -171,3 +171,32 @@ def test_whole_block_512_tokens_against_cpu_path(layer):
     got = out.float().cpu().numpy()
     assert rel_l2(got, want) <= 1e-2
     assert np.abs(got - want).max() <= 2e-2 * np.abs(want).max()
+
+
+def test_grouped_path_second_layer_and_slot_offsets():
+    """Two layers in one adapter, the second one's experts stored in reverse slot order: the grouped GEMM must find
+    every expert's rows through the residency table (bank row = slot, not expert id)."""
+    E2 = 32
+    lays = [pkg.synth.make_layer(300 + l, experts=E2) for l in range(2)]
+    shapes = pkg.ExpertShapes(lays[0].hidden, lays[0].inter)
+    moe = pkg.B200MoE(0, shapes, 2 * E2, experts=E2, layers=2, top_k=lays[0].top_k, shared_inter=0, max_tokens=512)
+    for e in range(E2):
+        moe.load(0, e, e, lays[0].fields(e))
+        moe.load(1, e, 2 * E2 - 1 - e, lays[1].fields(e))
+    lay = lays[1]
+    banks = o.HostBanks(*lay.banks, slots=E2, gu_rows=2 * lay.inter, gu_cols=lay.hidden, dn_rows=lay.hidden,
+                        dn_cols=lay.inter)
+    rng = np.random.default_rng(8)
+    tokens = 400
+    xb = pkg.synth.make_x(13, tokens, lay.hidden)
+    ids = _ids(rng, tokens, E2, lay.top_k)
+    w = rng.uniform(0.05, 0.5, ids.shape).astype(np.float32)
+    out = torch.empty((tokens, lay.hidden), dtype=torch.float32, device=dev())
+    req = pkg.MoEDeviceRequest(1, lay.hidden, lay.inter, lay.top_k, bf16_dev(xb), torch.from_numpy(ids).to(dev()),
+                               torch.from_numpy(w).to(dev()))
+    moe.grouped_moe_staged(req, out)          # 3200 routes: AUTO takes the grouped GEMM
+    moe.sync_status()
+    want = o.grouped_moe_reference_mt(banks, lay.hidden, lay.inter, pkg.synth.bf16_bits_to_f32(xb), lay.top_k,
+                                      ids.reshape(-1), w.reshape(-1))
+    assert rel_l2(out.cpu().numpy(), want) < 1e-3
+    moe.close()
