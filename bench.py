@@ -219,10 +219,11 @@ def run_b200(args):
     ids = torch.empty((T, TOP_K), dtype=torch.int32, device=dev)
     wts = torch.empty((T, TOP_K), dtype=torch.float32, device=dev)
 
-    def step(i, x=None):
+    def step(i, x=None, o=None):
         l = i % nlayers
         g, su, sd, sg = dense[l]
-        moe.moe_block(l, xs[l] if x is None else x, g, su, sd, sg, out, ids_out=ids, weights_out=wts, path=path)
+        moe.moe_block(l, xs[l] if x is None else x, g, su, sd, sg, out if o is None else o, ids_out=ids, weights_out=wts,
+                      path=path)
 
     def barrier():
         if world > 1:
@@ -256,19 +257,71 @@ def run_b200(args):
     launches = (moe.kernel_launches() - l0) * K // (K + W)
     value = world * T * K / (total_ms * 1e-3)
 
-    # end to end: pinned host x in, block, result out, every step
+    # end to end: every step's activations come from pinned host memory and its result goes back to pinned host
+    # memory.  The copies run on a copy stream with two staging buffers each way, so the H2D of step i + 1 and the
+    # D2H of step i overlap the compute of a neighbouring step, as a serving loop would run them.
     x_host = [x.cpu().pin_memory() for x in xs]
-    x_stage = torch.empty_like(xs[0])
-    out_host = torch.empty((T, HIDDEN), dtype=torch.bfloat16).pin_memory()
+    x_stage = [torch.empty_like(xs[0]) for _ in range(2)]
+    out_dev = [torch.empty_like(out) for _ in range(2)]
+    out_host = [torch.empty((T, HIDDEN), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    copy_s = torch.cuda.Stream()
+    ev_h2d = [torch.cuda.Event() for _ in range(2)]
+    ev_comp = [torch.cuda.Event() for _ in range(2)]
+    ev_d2h = [torch.cuda.Event() for _ in range(2)]
+    primed = [False]
 
     def step_e2e(i):
-        x_stage.copy_(x_host[i % nlayers], non_blocking=True)
-        step(i, x_stage)
-        out_host.copy_(out, non_blocking=True)
+        cur = torch.cuda.current_stream()
+        b = i & 1
+        if not primed[0]:                      # the first step's input
+            with torch.cuda.stream(copy_s):
+                x_stage[b].copy_(x_host[i % nlayers], non_blocking=True)
+                ev_h2d[b].record(copy_s)
+            for e in ev_comp + ev_d2h:
+                e.record(cur)
+            primed[0] = True
+        cur.wait_event(ev_h2d[b])              # this step's input has arrived
+        cur.wait_event(ev_d2h[b])              # the result buffer's previous content has left
+        step(i, x=x_stage[b], o=out_dev[b])
+        ev_comp[b].record(cur)
+        with torch.cuda.stream(copy_s):
+            copy_s.wait_event(ev_comp[b ^ 1])  # the other input buffer was read by the previous step
+            x_stage[b ^ 1].copy_(x_host[(i + 1) % nlayers], non_blocking=True)
+            ev_h2d[b ^ 1].record(copy_s)
+            copy_s.wait_event(ev_comp[b])
+            out_host[b].copy_(out_dev[b], non_blocking=True)
+            ev_d2h[b].record(copy_s)
 
-    e2e_ms = timed(step_e2e, K, W)
+    def timed_e2e():
+        for i in range(W):
+            step_e2e(i)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(K):
+            step_e2e(W + i)
+        torch.cuda.current_stream().wait_event(ev_d2h[(W + K - 1) & 1])    # the last result has reached the host buffer
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    e2e_ms = timed_e2e()
+
+    # the same without any overlap: copy in, block, copy out on one stream
+    def step_serial(i):
+        x_stage[0].copy_(x_host[i % nlayers], non_blocking=True)
+        step(i, x=x_stage[0], o=out_dev[0])
+        out_host[0].copy_(out_dev[0], non_blocking=True)
+
+    serial_ms = timed(step_serial, K, W)
     e2e = {"value": world * T * K / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": T * HIDDEN * 2,
-           "d2h_bytes_per_step": T * HIDDEN * 2}
+           "d2h_bytes_per_step": T * HIDDEN * 2,
+           "how": "pinned host buffers; H2D of step i + 1 and D2H of step i on a copy stream (two staging buffers each "
+                  "way) under the compute of the neighbouring step",
+           "serial_value": world * T * K / (serial_ms * 1e-3)}
 
     # per-kernel profile pass (CUDA events around every launch) for the roofline of the dominant kernel.
     # The routed half runs alone here (serving call with the router's ids), so that the shared expert,
@@ -495,15 +548,16 @@ def run_ep(args, pkg, dev, world, rank, local):
             p2p = False
             exchange_note = exchange_note or "peer exchange unavailable on another rank; NCCL all-to-all used"
 
-    def step(i, record=None, x=None):
+    def step(i, record=None, x=None, o=None):
         l = i % nlayers
         g, su, sd, sg = dense[l]
+        xin, dst = (xs[l] if x is None else x), (out if o is None else o)
         if p2p:
-            layer.forward_p2p(l, xs[l] if x is None else x, g, su, sd, sg, out, record=record)
+            layer.forward_p2p(l, xin, g, su, sd, sg, dst, record=record)
         elif record is None and chunks > 1:
-            layer.forward_overlapped(l, xs[l] if x is None else x, g, su, sd, sg, out, chunks=chunks)
+            layer.forward_overlapped(l, xin, g, su, sd, sg, dst, chunks=chunks)
         else:
-            layer.forward(l, xs[l] if x is None else x, g, su, sd, sg, out, record=record)
+            layer.forward(l, xin, g, su, sd, sg, dst, record=record)
 
     def barrier():
         dist.barrier()
@@ -532,23 +586,47 @@ def run_ep(args, pkg, dev, world, rank, local):
     total_ms = float(ms.item())
     clocks = sampler.stop() if rank == 0 else None
 
-    # end to end: pinned host activations in, the result out, every step
+    # end to end: pinned host activations in, the result out, every step; the copies run on a copy stream with two
+    # staging buffers each way, so they overlap the neighbouring steps' compute as in a serving loop
     x_host = [x.cpu().pin_memory() for x in xs]
-    x_stage = torch.empty_like(xs[0])
-    out_host = torch.empty((T, HIDDEN), dtype=torch.bfloat16).pin_memory()
+    x_stage = [torch.empty_like(xs[0]) for _ in range(2)]
+    out_dev = [torch.empty_like(out) for _ in range(2)]
+    out_host = [torch.empty((T, HIDDEN), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    copy_s = torch.cuda.Stream()
+    ev_h2d = [torch.cuda.Event() for _ in range(2)]
+    ev_comp = [torch.cuda.Event() for _ in range(2)]
+    ev_d2h = [torch.cuda.Event() for _ in range(2)]
+    primed = [False]
 
     def step_e2e(i):
-        l = i % nlayers
-        x_stage.copy_(x_host[l], non_blocking=True)
-        step(i, x=x_stage)
-        out_host.copy_(out, non_blocking=True)
+        cur = torch.cuda.current_stream()
+        b = i & 1
+        if not primed[0]:
+            with torch.cuda.stream(copy_s):
+                x_stage[b].copy_(x_host[i % nlayers], non_blocking=True)
+                ev_h2d[b].record(copy_s)
+            for e in ev_comp + ev_d2h:
+                e.record(cur)
+            primed[0] = True
+        cur.wait_event(ev_h2d[b])
+        cur.wait_event(ev_d2h[b])
+        step(i, x=x_stage[b], o=out_dev[b])
+        ev_comp[b].record(cur)
+        with torch.cuda.stream(copy_s):
+            copy_s.wait_event(ev_comp[b ^ 1])
+            x_stage[b ^ 1].copy_(x_host[(i + 1) % nlayers], non_blocking=True)
+            ev_h2d[b ^ 1].record(copy_s)
+            copy_s.wait_event(ev_comp[b])
+            out_host[b].copy_(out_dev[b], non_blocking=True)
+            ev_d2h[b].record(copy_s)
 
     for i in range(2):
         step_e2e(i)
     barrier()
     e0.record()
     for i in range(K):
-        step_e2e(W + i)
+        step_e2e(2 + i)
+    torch.cuda.current_stream().wait_event(ev_d2h[(2 + K - 1) & 1])
     e1.record()
     barrier()
     ms2 = torch.tensor([e0.elapsed_time(e1)], device=dev)
