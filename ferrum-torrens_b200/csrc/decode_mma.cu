@@ -70,6 +70,8 @@ struct PlanArgs {
 };
 
 __global__ void __launch_bounds__(kPlanThreads) decode_plan_kernel(PlanArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();     // the router's ids
     extern __shared__ int psm[];
     int* const cnt = psm;                 // [slots]
     int* const pos_base = cnt + a.slots;  // [slots]
@@ -359,6 +361,8 @@ __global__ void __launch_bounds__(Cfg<GATE_UP, K_, NT>::kThreads, OCC) expert_mm
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
+    pdl_launch_dependents();
+    pdl_wait();     // the plan (groups, sorted routes) and, for the down kernel, ic2
 
     // contiguous item range of this CTA: item = group * blocks + block
     const int n_groups = *a.n_groups;
@@ -594,8 +598,13 @@ __global__ void __launch_bounds__(Cfg<GATE_UP, K_, NT>::kThreads, OCC) expert_mm
     }
 }
 
+// latency-bound steps (a handful of tokens) chain their kernels with programmatic dependent launch: measured
+// 49 -> 43 us per block at one token; at 64 tokens the early-resident CTAs only get in the way of the shared
+// expert that runs beside them, so larger steps launch the ordinary way
+constexpr int kPdlMaxRoutes = 128;
+
 template <bool GATE_UP, int K_, int NT, int OCC>
-void launch_expert(ExpertArgs a, int sm_count, cudaStream_t s) {
+void launch_expert(ExpertArgs a, int sm_count, cudaStream_t s, bool pdl) {
     using C = Cfg<GATE_UP, K_, NT>;
     static bool attr = false;
     if (!attr) {
@@ -603,7 +612,10 @@ void launch_expert(ExpertArgs a, int sm_count, cudaStream_t s) {
                              (int)C::kSmem);
         attr = true;
     }
-    expert_mma_kernel<GATE_UP, K_, NT, OCC><<<sm_count * OCC, C::kThreads, C::kSmem, s>>>(a);
+    if (pdl)
+        launch_pdl(expert_mma_kernel<GATE_UP, K_, NT, OCC>, dim3(sm_count * OCC), dim3(C::kThreads), C::kSmem, s, a);
+    else
+        expert_mma_kernel<GATE_UP, K_, NT, OCC><<<sm_count * OCC, C::kThreads, C::kSmem, s>>>(a);
 }
 
 // Large batches: the routes are bucketed by the multi-CTA CSR build (seg / route_idx); this turns every
@@ -697,7 +709,10 @@ int launch_decode_mma(const BankView& b, const void* x, int x_dtype, const Decod
             pattr = true;
         }
         c.begin(K_DECODE_PLAN);
-        decode_plan_kernel<<<1, kPlanThreads, psmem, c.s>>>(pa);
+        if (routes <= kPdlMaxRoutes)
+            launch_pdl(decode_plan_kernel, dim3(1), dim3(kPlanThreads), psmem, c.s, pa);
+        else
+            decode_plan_kernel<<<1, kPlanThreads, psmem, c.s>>>(pa);
         c.end();
         launches += 1;
     } else {
@@ -735,18 +750,18 @@ int launch_decode_mma(const BankView& b, const void* x, int x_dtype, const Decod
     a.act = x; a.act_dtype = x_dtype; a.ic2 = sc.ic2p; a.N = 2 * b.inter;
     c.begin(K_EXPERT_GATE_UP);
     if (small)
-        launch_expert<true, 2048, 1, 1>(a, sm_count, c.s);
+        launch_expert<true, 2048, 1, 1>(a, sm_count, c.s, routes <= kPdlMaxRoutes);
     else
-        launch_expert<true, 2048, 2, 1>(a, sm_count, c.s);
+        launch_expert<true, 2048, 2, 1>(a, sm_count, c.s, false);
     c.end();
     // down: K = inter, N = hidden rows
     a.packed = b.dn_packed; a.scale = b.dn_scale; a.global = b.dn_global;
     a.act = sc.ic2p; a.act_dtype = 1; a.yroute = sc.yroute; a.route_weight = route_weight; a.N = b.hidden;
     c.begin(K_EXPERT_DOWN);
     if (small)
-        launch_expert<false, 512, 1, 1>(a, sm_count, c.s);
+        launch_expert<false, 512, 1, 1>(a, sm_count, c.s, routes <= kPdlMaxRoutes);
     else
-        launch_expert<false, 512, 2, 1>(a, sm_count, c.s);
+        launch_expert<false, 512, 2, 1>(a, sm_count, c.s, false);
     c.end();
     return launches + 2;
 }

@@ -310,6 +310,7 @@ router_fused_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
     __shared__ __align__(16) uint8_t wbuf[2][32 * kFusedWStride];
     __shared__ __align__(16) float xbuf[2][kFusedTok][kFusedK];
     __shared__ float slog[kFusedTok][256];       // used in the cluster's first CTA
+    pdl_launch_dependents();
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
     const int rank = (int)cluster.block_rank();   // = blockIdx.x: experts 32 * rank ..
     const int e0 = rank * 32, t0 = blockIdx.y * kFusedTok;
