@@ -115,6 +115,7 @@ struct ftm_handle {
     float *row_scale = nullptr, *row_scale2 = nullptr;
     int4* groups = nullptr;
     int32_t *sorted_route = nullptr, *n_groups = nullptr;
+    PrefillMaps maps;     // tensor maps of the grouped GEMMs (fixed addresses: encoded once)
     int sm_count = 148;   // CTAs of the persistent kernels (ftm_set_sm_budget)
     int sm_total = 148;
     std::vector<void*> allocs;
@@ -126,6 +127,21 @@ struct ftm_handle {
 };
 
 namespace {
+
+// Makes the adapter's device current for one call and restores the caller's on the way out: a host
+// thread that drives adapters on several devices need not switch devices itself.
+struct DeviceGuard {
+    int prev = -1;
+    bool switched = false;
+    explicit DeviceGuard(int want) {
+        if (cudaGetDevice(&prev) == cudaSuccess && prev != want) switched = cudaSetDevice(want) == cudaSuccess;
+    }
+    ~DeviceGuard() {
+        if (switched) cudaSetDevice(prev);
+    }
+    DeviceGuard(const DeviceGuard&) = delete;
+    DeviceGuard& operator=(const DeviceGuard&) = delete;
+};
 
 int fail(const ftm_handle* h, int code, const char* fmt, ...) {
     char buf[512];
@@ -194,6 +210,15 @@ BankView bank_view(const ftm_handle* h) {
     return v;
 }
 
+// (re)encodes the grouped GEMM's tensor maps; the shapes the tcgen05 path does not cover need none
+void build_maps(ftm_handle* h) {
+    h->maps.ok = false;
+    if (!h->resident || !h->xg || !h->ic2) return;
+    if (!prefill_umma_supported(h->cfg.hidden, h->cfg.inter, 1, 1, true)) return;
+    prefill_build_maps(bank_view(h), h->xg, reinterpret_cast<const __half*>(h->ic2),
+                       (size_t)h->cfg.max_tokens * h->cfg.top_k, &h->maps);
+}
+
 void clear_residency(ftm_handle* h) {
     std::fill(h->slot_for_id.begin(), h->slot_for_id.end(), -1);
     std::fill(h->id_of_slot.begin(), h->id_of_slot.end(), -1);
@@ -228,7 +253,7 @@ int run_routed(ftm_handle* h, const void* x, int x_dtype, const void* expert_ids
     BankView b = bank_view(h);
     const int routes = tokens * h->cfg.top_k;
     // large batches (or FTM_PATH_GROUPED): the tcgen05 grouped GEMM, which also does the combine
-    if ((path == FTM_PATH_GROUPED || (path == FTM_PATH_AUTO && routes > kGroupedMinRoutes)) &&
+    if ((path == FTM_PATH_GROUPED || (path == FTM_PATH_AUTO && routes > kGroupedMinRoutes)) && h->maps.ok &&
         prefill_umma_supported(h->cfg.hidden, h->cfg.inter, h->cfg.slots, h->cfg.experts, expert_ids != nullptr)) {
         PrefillScratch sc{};
         sc.route_bin = h->route_expert; sc.seg = h->seg; sc.route_idx = h->sorted_route; sc.pos_of_route = h->route_idx;
@@ -238,7 +263,7 @@ int run_routed(ftm_handle* h, const void* x, int x_dtype, const void* expert_ids
         DecodeRoutes rt{expert_ids ? nullptr : h->route_slot, expert_ids, ids_dtype, layer, h->cfg.experts,
                         (int)h->slot_for_id.size(), h->d_slot_for_id, h->route_slot, h->flags + 1};
         int n = launch_prefill_umma(b, x, x_dtype, rt, weights, tokens, h->cfg.top_k, sc, h->sm_count, shared, se_gate, join,
-                                    out, out_dtype, h->ctx(s));
+                                    out, out_dtype, h->maps, h->ctx(s));
         if (n < 0) return fail(h, FTM_ERR_CUDA, "moe: driver: cuTensorMapEncodeTiled failed");
         h->launches += n;
         return FTM_OK;
@@ -309,8 +334,11 @@ FTM_API int ftm_create(const ftm_config* c, void* stream, ftm_handle** out) {
                     cudaGetErrorString(e));
     if (c->ordinal < 0 || c->ordinal >= ndev)
         return fail(nullptr, FTM_ERR_BAD, "moe: device ordinal %d of %d", c->ordinal, ndev);
-    e = cudaSetDevice(c->ordinal);
-    if (e != cudaSuccess) return cuda_fail(nullptr, e, "cudaSetDevice");
+    DeviceGuard dg(c->ordinal);
+    int cur = -1;
+    e = cudaGetDevice(&cur);
+    if (e != cudaSuccess || cur != c->ordinal)
+        return cuda_fail(nullptr, e == cudaSuccess ? cudaErrorInvalidDevice : e, "cudaSetDevice");
 
     std::unique_ptr<ftm_handle> h(new ftm_handle);
     h->cfg = *c;
@@ -375,6 +403,7 @@ FTM_API int ftm_create(const ftm_config* c, void* stream, ftm_handle** out) {
         if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->ev_join, cudaEventDisableTiming);
         if (e != cudaSuccess) rc = cuda_fail(hp, e, "adapter setup");
     }
+    if (rc == FTM_OK) build_maps(hp);
     if (rc != FTM_OK) {
         g_create_error = h->err;
         ftm_destroy(h.release());
@@ -386,7 +415,7 @@ FTM_API int ftm_create(const ftm_config* c, void* stream, ftm_handle** out) {
 
 FTM_API void ftm_destroy(ftm_handle* h) {
     if (!h) return;
-    cudaSetDevice(h->cfg.ordinal);
+    DeviceGuard dg(h->cfg.ordinal);
     cudaDeviceSynchronize();
     for (void* p : h->allocs) cudaFree(p);
     for (int b = 0; b < FTM_NUM_BANKS; b++)
@@ -403,6 +432,7 @@ static int load_common(ftm_handle* h, int32_t layer, int32_t expert, int32_t slo
                        const size_t lens[], cudaMemcpyKind kind) {
     if (!h) return FTM_ERR_BAD;
     std::lock_guard<std::mutex> lk(h->mu);
+    DeviceGuard dg(h->cfg.ordinal);
     if (!h->resident) return fail(h, FTM_ERR_BAD, "moe: load while the expert banks are released");
     if (layer < 0 || layer >= h->cfg.layers || expert < 0 || expert >= h->cfg.experts)
         return fail(h, FTM_ERR_MISSING, "moe: no expert bank entry L%05d expert %d", layer, expert);
@@ -415,7 +445,6 @@ static int load_common(ftm_handle* h, int32_t layer, int32_t expert, int32_t slo
             return fail(h, FTM_ERR_BAD, "moe: expert field %d has %zu bytes, the bank row is %zu", b, lens[b],
                         h->row_bytes[b]);
     }
-    CU(h, cudaSetDevice(h->cfg.ordinal));
     for (int b = 0; b < FTM_NUM_BANKS; b++) {
         uint8_t* dst = (uint8_t*)h->banks[b] + (size_t)slot * h->row_bytes[b];
         if (fields[b] == dst) continue;  // the bytes were written in place through ftm_bank_ptrs
@@ -457,8 +486,8 @@ FTM_API int ftm_slots(const ftm_handle* h) { return h ? h->cfg.slots : 0; }
 FTM_API int ftm_release_banks(ftm_handle* h) {
     if (!h) return FTM_ERR_BAD;
     std::lock_guard<std::mutex> lk(h->mu);
+    DeviceGuard dg(h->cfg.ordinal);
     if (!h->resident) return FTM_OK;
-    CU(h, cudaSetDevice(h->cfg.ordinal));
     CU(h, cudaDeviceSynchronize());
     for (int b = 0; b < FTM_NUM_BANKS; b++) {
         CU(h, cudaFree(h->banks[b]));
@@ -473,9 +502,11 @@ FTM_API int ftm_release_banks(ftm_handle* h) {
 FTM_API int ftm_rehydrate_banks(ftm_handle* h) {
     if (!h) return FTM_ERR_BAD;
     std::lock_guard<std::mutex> lk(h->mu);
+    DeviceGuard dg(h->cfg.ordinal);
     if (h->resident) return FTM_OK;
-    CU(h, cudaSetDevice(h->cfg.ordinal));
-    return alloc_banks(h);
+    int rc = alloc_banks(h);
+    if (rc == FTM_OK) build_maps(h);   // the banks have new addresses
+    return rc;
 }
 
 FTM_API int ftm_banks_resident(const ftm_handle* h) { return h && h->resident ? 1 : 0; }
@@ -494,6 +525,7 @@ FTM_API size_t ftm_bank_row_bytes(const ftm_handle* h, int bank) {
 FTM_API int32_t ftm_slot_of(const ftm_handle* h, int32_t layer, int32_t expert) {
     if (!h || layer < 0 || layer >= h->cfg.layers || expert < 0 || expert >= h->cfg.experts) return -1;
     std::lock_guard<std::mutex> lk(h->mu);
+    DeviceGuard dg(h->cfg.ordinal);
     return h->slot_for_id[(size_t)layer * h->cfg.experts + expert];
 }
 
@@ -501,6 +533,7 @@ FTM_API int ftm_ensure_experts(ftm_handle* h, int32_t layer, const uint32_t* rou
                        uint32_t* write_slots, int32_t* rewrites, size_t* n_miss) {
     if (!h) return FTM_ERR_BAD;
     std::lock_guard<std::mutex> lk(h->mu);
+    DeviceGuard dg(h->cfg.ordinal);
     if (layer < 0 || layer >= h->cfg.layers) return fail(h, FTM_ERR_BAD, "moe: layer %d of %d", layer, h->cfg.layers);
     if ((n && !routed) || !n_miss) return fail(h, FTM_ERR_BAD, "moe: null routed ids");
     for (size_t i = 0; i < n; i++)
@@ -523,6 +556,7 @@ FTM_API int ftm_router_from_logits(ftm_handle* h, const float* logits, int32_t t
                            float* weights_out, void* stream) {
     if (!h) return FTM_ERR_BAD;
     std::lock_guard<std::mutex> lk(h->mu);
+    DeviceGuard dg(h->cfg.ordinal);
     if (!logits || !ids_out || !weights_out) return fail(h, FTM_ERR_BAD, "moe: router: null buffer");
     if (tokens <= 0) return fail(h, FTM_ERR_BAD, "moe: router: %d tokens", tokens);
     h->launches += launch_router_topk(logits, tokens, h->cfg.experts, h->cfg.top_k, ids_out, weights_out, h->ctx(pick(h, stream)));
@@ -551,6 +585,7 @@ FTM_API int ftm_router(ftm_handle* h, const void* x_bf16, const void* gate_w_bf1
                float* weights_out, void* stream) {
     if (!h) return FTM_ERR_BAD;
     std::lock_guard<std::mutex> lk(h->mu);
+    DeviceGuard dg(h->cfg.ordinal);
     return router_locked(h, x_bf16, gate_w_bf16, tokens, ids_out, weights_out, pick(h, stream));
 }
 
@@ -560,6 +595,7 @@ FTM_API int ftm_csr_build(ftm_handle* h, const int32_t* route_slot, int32_t rout
                   int32_t* route_idx_out, void* stream) {
     if (!h) return FTM_ERR_BAD;
     std::lock_guard<std::mutex> lk(h->mu);
+    DeviceGuard dg(h->cfg.ordinal);
     if (!route_slot || !seg_out || !route_idx_out) return fail(h, FTM_ERR_BAD, "moe: csr: null buffer");
     if (routes <= 0 || (int64_t)routes > (int64_t)h->cfg.max_tokens * h->cfg.top_k)
         return fail(h, FTM_ERR_BAD, "moe: csr: %d routes (cap %lld)", routes,
@@ -575,6 +611,7 @@ FTM_API int ftm_csr_build(ftm_handle* h, const int32_t* route_slot, int32_t rout
 FTM_API int ftm_csr_bad(ftm_handle* h, void* stream, int32_t* bad_out) {
     if (!h || !bad_out) return FTM_ERR_BAD;
     std::lock_guard<std::mutex> lk(h->mu);
+    DeviceGuard dg(h->cfg.ordinal);
     cudaStream_t s = pick(h, stream);
     CU(h, cudaMemcpyAsync(bad_out, h->flags, sizeof(int32_t), cudaMemcpyDeviceToHost, s));
     CU(h, cudaStreamSynchronize(s));
@@ -595,6 +632,7 @@ FTM_API int ftm_grouped_moe_host(ftm_handle* h, const float* x, size_t x_len, in
                          size_t routes_len, const float* weights, size_t weights_len, float* out, size_t out_len) {
     if (!h) return FTM_ERR_BAD;
     std::lock_guard<std::mutex> lk(h->mu);
+    DeviceGuard dg(h->cfg.ordinal);
     if (!x || !routes || !weights || !out) return fail(h, FTM_ERR_BAD, "moe: grouped_moe: null buffer");
     const size_t H = h->cfg.hidden;
     if (x_len == 0 || x_len % H) return fail(h, FTM_ERR_BAD, "moe: grouped_moe: %zu activations for hidden %zu", x_len, H);
@@ -607,7 +645,6 @@ FTM_API int ftm_grouped_moe_host(ftm_handle* h, const float* x, size_t x_len, in
                     routes_len, weights_len, tokens, top_k);
     if (out_len < tokens * H) return fail(h, FTM_ERR_BAD, "moe: grouped_moe: out holds %zu, needs %zu", out_len, tokens * H);
     if ((rc = check_host_routes(h, routes, R)) != FTM_OK) return rc;
-    CU(h, cudaSetDevice(h->cfg.ordinal));
     cudaStream_t s = h->stream;
     // narrow to bf16 on the host, as the reference adapter does before its upload
     std::vector<uint16_t> xb(x_len);
@@ -630,6 +667,7 @@ FTM_API int ftm_grouped_moe_dev(ftm_handle* h, const void* x, int x_dtype, int32
                         int out_dtype, void* stream) {
     if (!h) return FTM_ERR_BAD;
     std::lock_guard<std::mutex> lk(h->mu);
+    DeviceGuard dg(h->cfg.ordinal);
     if (!x || !routes_host || !weights_dev || !out) return fail(h, FTM_ERR_BAD, "moe: grouped_moe_dev: null buffer");
     int rc = check_tokens(h, tokens, top_k);
     if (rc != FTM_OK) return rc;
@@ -676,6 +714,7 @@ FTM_API int ftm_moe_layer_staged(ftm_handle* h, int32_t layer, const void* x, in
                          void* stream) {
     if (!h) return FTM_ERR_BAD;
     std::lock_guard<std::mutex> lk(h->mu);
+    DeviceGuard dg(h->cfg.ordinal);
     return staged_locked(h, layer, x, x_dtype, expert_ids, ids_dtype, weights, tokens, nullptr, nullptr, nullptr,
                          out, out_dtype, path, pick(h, stream));
 }
@@ -683,6 +722,7 @@ FTM_API int ftm_moe_layer_staged(ftm_handle* h, int32_t layer, const void* x, in
 FTM_API int ftm_moe_begin(ftm_handle* h, int32_t, const void*, int, const void*, int, const float*, int32_t, void*) {
     if (!h) return FTM_ERR_BAD;
     std::lock_guard<std::mutex> lk(h->mu);
+    DeviceGuard dg(h->cfg.ordinal);
     return fail(h, FTM_ERR_NOT_SUPPORTED,
                 "moe: no overlapped path: every expert is resident, call ftm_moe_layer_staged");
 }
@@ -690,6 +730,7 @@ FTM_API int ftm_moe_begin(ftm_handle* h, int32_t, const void*, int, const void*,
 FTM_API int ftm_moe_finish(ftm_handle* h, void*, int, void*) {
     if (!h) return FTM_ERR_BAD;
     std::lock_guard<std::mutex> lk(h->mu);
+    DeviceGuard dg(h->cfg.ordinal);
     return fail(h, FTM_ERR_NOT_SUPPORTED, "moe: no pending step");
 }
 
@@ -698,8 +739,8 @@ FTM_API size_t ftm_route_cap(const ftm_handle* h) { return h ? (size_t)h->cfg.ma
 FTM_API int ftm_reset_staging(ftm_handle* h) {
     if (!h) return FTM_ERR_BAD;
     std::lock_guard<std::mutex> lk(h->mu);
+    DeviceGuard dg(h->cfg.ordinal);
     clear_residency(h);
-    CU(h, cudaSetDevice(h->cfg.ordinal));
     CU(h, cudaMemsetAsync(h->d_slot_for_id, 0xff, h->slot_for_id.size() * sizeof(int32_t), h->stream));
     CU(h, cudaStreamSynchronize(h->stream));
     return FTM_OK;
@@ -710,6 +751,7 @@ FTM_API uint64_t ftm_steps(const ftm_handle* h) { return h ? h->steps : 0; }
 FTM_API int ftm_sync_status(ftm_handle* h, void* stream) {
     if (!h) return FTM_ERR_BAD;
     std::lock_guard<std::mutex> lk(h->mu);
+    DeviceGuard dg(h->cfg.ordinal);
     cudaStream_t s = pick(h, stream);
     int32_t f[8] = {};
     CU(h, cudaMemcpyAsync(f, h->flags, sizeof f, cudaMemcpyDeviceToHost, s));
@@ -732,7 +774,7 @@ FTM_API int ftm_sync_status(ftm_handle* h, void* stream) {
 FTM_API int ftm_profile_enable(ftm_handle* h, int on) {
     if (!h) return FTM_ERR_BAD;
     std::lock_guard<std::mutex> lk(h->mu);
-    CU(h, cudaSetDevice(h->cfg.ordinal));
+    DeviceGuard dg(h->cfg.ordinal);
     CU(h, cudaDeviceSynchronize());
     h->prof.drain();
     if (on) {
@@ -748,8 +790,8 @@ FTM_API int ftm_profile_enable(ftm_handle* h, int on) {
 FTM_API int ftm_profile_read(ftm_handle* h, int kind, double* total_ms, uint64_t* launches) {
     if (!h) return FTM_ERR_BAD;
     std::lock_guard<std::mutex> lk(h->mu);
+    DeviceGuard dg(h->cfg.ordinal);
     if (kind < 0 || kind >= K_NUM_KINDS) return fail(h, FTM_ERR_BAD, "moe: profile kind %d", kind);
-    CU(h, cudaSetDevice(h->cfg.ordinal));
     CU(h, cudaDeviceSynchronize());
     h->prof.drain();
     if (total_ms) *total_ms = h->prof.total_ms[kind];
@@ -763,6 +805,7 @@ FTM_API const char* ftm_profile_kind_name(int kind) {
 FTM_API int ftm_set_sm_budget(ftm_handle* h, int32_t sms) {
     if (!h) return FTM_ERR_BAD;
     std::lock_guard<std::mutex> lk(h->mu);
+    DeviceGuard dg(h->cfg.ordinal);
     if (sms < 0 || sms > h->sm_total) return fail(h, FTM_ERR_BAD, "moe: sm budget %d of %d SMs", sms, h->sm_total);
     h->sm_count = sms ? sms : h->sm_total;
     return FTM_OK;
@@ -777,6 +820,7 @@ FTM_API int ftm_ep_pack(ftm_handle* h, const void* x_bf16, const int32_t* ids, c
                         int32_t* counts, void* stream) {
     if (!h) return FTM_ERR_BAD;
     std::lock_guard<std::mutex> lk(h->mu);
+    DeviceGuard dg(h->cfg.ordinal);
     if (!x_bf16 || !ids || !weights || !send_x || !send_expert || !send_weight || !route_idx || !counts)
         return fail(h, FTM_ERR_BAD, "moe: ep_pack: null buffer");
     if (tokens <= 0 || tokens > h->cfg.max_tokens)
@@ -786,6 +830,8 @@ FTM_API int ftm_ep_pack(ftm_handle* h, const void* x_bf16, const int32_t* ids, c
     cudaStream_t s = pick(h, stream);
     const int routes = tokens * h->cfg.top_k;
     CU(h, cudaMemsetAsync(h->flags + 1, 0, sizeof(int32_t), s));
+    // positions the permutation build leaves unwritten (a route whose expert id is out of range) read as -1
+    CU(h, cudaMemsetAsync(route_idx, 0xff, (size_t)routes * sizeof(int32_t), s));
     h->launches += launch_csr_build(ids, routes, h->cfg.experts, h->seg, route_idx, h->csr_scratch, h->flags + 1, h->ctx(s));
     h->launches += launch_ep_pack((const __nv_bfloat16*)x_bf16, ids, weights, route_idx, h->seg, tokens, h->cfg.top_k,
                                   h->cfg.hidden, h->cfg.experts, ep_size, (__nv_bfloat16*)send_x, send_expert,
@@ -798,6 +844,7 @@ FTM_API int ftm_ep_plan(ftm_handle* h, const int32_t* ids, int32_t tokens, int32
                         int32_t* counts, void* stream) {
     if (!h) return FTM_ERR_BAD;
     std::lock_guard<std::mutex> lk(h->mu);
+    DeviceGuard dg(h->cfg.ordinal);
     if (!ids || !route_idx || !counts) return fail(h, FTM_ERR_BAD, "moe: ep_plan: null buffer");
     if (tokens <= 0 || tokens > h->cfg.max_tokens)
         return fail(h, FTM_ERR_BAD, "moe: ep_plan: %d tokens (max_tokens %d)", tokens, h->cfg.max_tokens);
@@ -806,6 +853,8 @@ FTM_API int ftm_ep_plan(ftm_handle* h, const int32_t* ids, int32_t tokens, int32
     cudaStream_t s = pick(h, stream);
     const int routes = tokens * h->cfg.top_k;
     CU(h, cudaMemsetAsync(h->flags + 1, 0, sizeof(int32_t), s));
+    // positions the permutation build leaves unwritten (a route whose expert id is out of range) read as -1
+    CU(h, cudaMemsetAsync(route_idx, 0xff, (size_t)routes * sizeof(int32_t), s));
     h->launches += launch_csr_build(ids, routes, h->cfg.experts, h->seg, route_idx, h->csr_scratch, h->flags + 1, h->ctx(s));
     h->launches += launch_ep_counts(h->seg, h->cfg.experts, ep_size, counts, h->ctx(s));
     CU(h, cudaGetLastError());
@@ -818,6 +867,7 @@ FTM_API int ftm_ep_dispatch(ftm_handle* h, const void* x_bf16, const int32_t* id
                             int64_t capacity_rows, void* stream) {
     if (!h) return FTM_ERR_BAD;
     std::lock_guard<std::mutex> lk(h->mu);
+    DeviceGuard dg(h->cfg.ordinal);
     if (!x_bf16 || !ids || !weights || !route_idx || !counts_all || !peer_x || !peer_meta)
         return fail(h, FTM_ERR_BAD, "moe: ep_dispatch: null buffer");
     if (tokens <= 0 || tokens > h->cfg.max_tokens)
@@ -835,6 +885,7 @@ FTM_API int ftm_ep_return(ftm_handle* h, const void* y_bf16, int32_t rows, int32
                           const int32_t* counts_all, const uint64_t* peer_back, int64_t capacity_rows, void* stream) {
     if (!h) return FTM_ERR_BAD;
     std::lock_guard<std::mutex> lk(h->mu);
+    DeviceGuard dg(h->cfg.ordinal);
     if (!y_bf16 || !counts_all || !peer_back) return fail(h, FTM_ERR_BAD, "moe: ep_return: null buffer");
     if (rows < 0 || ep_size < 1 || ep_size > 32 || ep_rank < 0 || ep_rank >= ep_size || capacity_rows < 1)
         return fail(h, FTM_ERR_BAD, "moe: ep_return: %d rows, rank %d of %d", rows, ep_rank, ep_size);
@@ -849,6 +900,7 @@ FTM_API int ftm_ep_combine(ftm_handle* h, const void* y, int y_dtype, const int3
                            const float* se_gate, int32_t tokens, void* out, int out_dtype, void* stream) {
     if (!h) return FTM_ERR_BAD;
     std::lock_guard<std::mutex> lk(h->mu);
+    DeviceGuard dg(h->cfg.ordinal);
     if (!y || !route_idx || !out || (shared && !se_gate)) return fail(h, FTM_ERR_BAD, "moe: ep_combine: null buffer");
     if (tokens <= 0 || tokens > h->cfg.max_tokens)
         return fail(h, FTM_ERR_BAD, "moe: ep_combine: %d tokens (max_tokens %d)", tokens, h->cfg.max_tokens);
@@ -882,6 +934,7 @@ FTM_API int ftm_shared_expert(ftm_handle* h, const void* x_bf16, int32_t tokens,
                       void* stream) {
     if (!h) return FTM_ERR_BAD;
     std::lock_guard<std::mutex> lk(h->mu);
+    DeviceGuard dg(h->cfg.ordinal);
     return shared_locked(h, x_bf16, tokens, gate_up_bf16, down_bf16, shared_gate_bf16, shared_out, se_gate_out,
                          pick(h, stream));
 }
@@ -890,6 +943,7 @@ FTM_API int ftm_combine(ftm_handle* h, const void* routed, int routed_dtype, con
                 int32_t tokens, void* out, int out_dtype, void* stream) {
     if (!h) return FTM_ERR_BAD;
     std::lock_guard<std::mutex> lk(h->mu);
+    DeviceGuard dg(h->cfg.ordinal);
     if (!routed || !shared || !se_gate || !out) return fail(h, FTM_ERR_BAD, "moe: combine: null buffer");
     if (tokens <= 0) return fail(h, FTM_ERR_BAD, "moe: combine: %d tokens", tokens);
     if ((routed_dtype != FTM_BF16 && routed_dtype != FTM_F32) || (out_dtype != FTM_BF16 && out_dtype != FTM_F32))
@@ -904,6 +958,7 @@ FTM_API int ftm_moe_block(ftm_handle* h, int32_t layer, const void* x_bf16, int3
                   int out_dtype, int32_t* ids_out, float* weights_out, int path, void* stream) {
     if (!h) return FTM_ERR_BAD;
     std::lock_guard<std::mutex> lk(h->mu);
+    DeviceGuard dg(h->cfg.ordinal);
     cudaStream_t s = pick(h, stream);
     if (!x_bf16 || !out) return fail(h, FTM_ERR_BAD, "moe: moe_block: null buffer");
     int rc = check_tokens(h, tokens, h->cfg.top_k);

@@ -64,6 +64,7 @@ __global__ void ep_pack_kernel(const __nv_bfloat16* __restrict__ x, const int32_
                                float* __restrict__ send_weight) {
     const int i = blockIdx.x;
     const int r = route_idx[i];
+    if (r < 0 || r >= routes) return;   // a route the permutation build dropped (expert id out of range, flagged there)
     const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)(r / top_k) * H);
     uint4* dst = reinterpret_cast<uint4*>(send_x + (size_t)i * H);
     for (int c = threadIdx.x; c < H / 8; c += blockDim.x) dst[c] = src[c];
@@ -129,20 +130,26 @@ __global__ void ep_combine_kernel(const void* __restrict__ y, int y_dtype, const
 // dispatch: position i of this rank's send order goes straight into the owner's receive buffers
 __global__ void __launch_bounds__(128)
 ep_dispatch_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ ids, const float* __restrict__ weights,
-                   const int32_t* __restrict__ route_idx, const int32_t* __restrict__ seg, int top_k, int H, int per,
-                   int world, int rank, const int32_t* __restrict__ counts_all, const uint64_t* __restrict__ peer_x,
-                   const uint64_t* __restrict__ peer_meta, long long capacity, int32_t* err) {
+                   const int32_t* __restrict__ route_idx, const int32_t* __restrict__ seg, int routes, int top_k, int H,
+                   int per, int world, int rank, const int32_t* __restrict__ counts_all,
+                   const uint64_t* __restrict__ peer_x, const uint64_t* __restrict__ peer_meta, long long capacity,
+                   int32_t* err) {
     // CTAs walk the send order starting at the next rank's block, so that at any time every owner is written
     // by one source (all ranks starting at owner 0 would share that owner's ingress bandwidth)
-    const int routes = gridDim.x;
     int i = blockIdx.x + seg[((rank + 1) % world) * per];
     if (i >= routes) i -= routes;
-    const int r = route_idx[i];
-    const int e = ids[r];
+    // every index is checked before the load that depends on it: a route the permutation build dropped
+    // (route_idx left at -1) or an expert id outside the layer raises the error flag, it is never followed
+    const int r = (i >= 0 && i < routes) ? route_idx[i] : -1;
+    const int e = (r >= 0 && r < routes) ? ids[r] : -1;
+    if (e < 0 || e >= per * world) {
+        if (threadIdx.x == 0) atomicExch(err, 4);
+        return;
+    }
     const int p = e / per;
     long long row = i - seg[p * per];
     for (int s = 0; s < rank; s++) row += counts_all[s * world + p];
-    if (p < 0 || p >= world || row < 0 || row >= capacity) {   // never store outside the owner's buffer
+    if (row < 0 || row >= capacity) {   // never store outside the owner's buffer
         if (threadIdx.x == 0) atomicExch(err, 4);
         return;
     }
@@ -188,8 +195,9 @@ int launch_ep_dispatch(const __nv_bfloat16* x, const int32_t* ids, const float* 
                        const int32_t* counts_all, const uint64_t* peer_x, const uint64_t* peer_meta, long long capacity,
                        int32_t* err, const Ctx& c) {
     c.begin(K_EP_PACK);
-    ep_dispatch_kernel<<<tokens * top_k, 128, 0, c.s>>>(x, ids, weights, route_idx, seg, top_k, hidden, experts / world, world,
-                                                       rank, counts_all, peer_x, peer_meta, capacity, err);
+    ep_dispatch_kernel<<<tokens * top_k, 128, 0, c.s>>>(x, ids, weights, route_idx, seg, tokens * top_k, top_k, hidden,
+                                                       experts / world, world, rank, counts_all, peer_x, peer_meta, capacity,
+                                                       err);
     c.end();
     return 1;
 }

@@ -606,12 +606,8 @@ constexpr int kPdlMaxRoutes = 128;
 template <bool GATE_UP, int K_, int NT, int OCC>
 void launch_expert(ExpertArgs a, int sm_count, cudaStream_t s, bool pdl) {
     using C = Cfg<GATE_UP, K_, NT>;
-    static bool attr = false;
-    if (!attr) {
-        cudaFuncSetAttribute(expert_mma_kernel<GATE_UP, K_, NT, OCC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)C::kSmem);
-        attr = true;
-    }
+    static PerDeviceOnce once;   // one per instantiation
+    allow_dyn_smem(once, expert_mma_kernel<GATE_UP, K_, NT, OCC>, C::kSmem);
     if (pdl)
         launch_pdl(expert_mma_kernel<GATE_UP, K_, NT, OCC>, dim3(sm_count * OCC), dim3(C::kThreads), C::kSmem, s, a);
     else
@@ -703,11 +699,8 @@ int launch_decode_mma(const BankView& b, const void* x, int x_dtype, const Decod
         pa.groups = sc.groups; pa.sorted_route = sc.sorted_route; pa.n_groups = sc.n_groups; pa.yroute = sc.yroute;
         pa.bad_flag = rt.bad_flag;
         const size_t psmem = decode_plan_smem(b.slots);
-        static bool pattr = false;
-        if (!pattr) {
-            cudaFuncSetAttribute(decode_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-            pattr = true;
-        }
+        static PerDeviceOnce once;
+        allow_dyn_smem(once, decode_plan_kernel, 200 * 1024);
         c.begin(K_DECODE_PLAN);
         if (routes <= kPdlMaxRoutes)
             launch_pdl(decode_plan_kernel, dim3(1), dim3(kPlanThreads), psmem, c.s, pa);

@@ -1,6 +1,10 @@
 // Launchers of the MoE kernels; each returns the number of kernel launches it enqueued.
 #pragma once
 
+#include <cuda.h>
+
+#include <atomic>
+
 #include "common.cuh"
 
 namespace ftm {
@@ -57,6 +61,25 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
     cfg.attrs = at;
     cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+// The opt-in to more than 48 KB of dynamic shared memory is a per-device property of a kernel, and one
+// process may hold adapters on several devices: every launcher remembers, per device ordinal, whether
+// the current device has been opted in.  Safe to call from several threads (the attribute call is
+// idempotent; the mask only saves repeating it).
+struct PerDeviceOnce {
+    std::atomic<uint64_t> mask{0};
+};
+template <typename KernelT>
+inline cudaError_t allow_dyn_smem(PerDeviceOnce& once, KernelT kernel, size_t bytes) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    const uint64_t bit = 1ull << (dev & 63);
+    if (once.mask.load(std::memory_order_acquire) & bit) return cudaSuccess;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e == cudaSuccess) once.mask.fetch_or(bit, std::memory_order_release);
+    return e;
 }
 
 // router.cu
@@ -134,11 +157,17 @@ struct PrefillScratch {
     void* y;                 // [routes, hidden] weighted expert outputs, sorted rows: bf16, or f32 for f32 outputs
     int32_t* err;
 };
+// tensor maps of the grouped GEMMs, encoded once per adapter (activation boxes of 32 / 64 / 96 / 128 rows)
+struct PrefillMaps {
+    CUtensorMap x[4], h[4], gp, gs, dp, ds;
+    bool ok = false;
+};
 bool prefill_umma_supported(int hidden, int inter, int slots, int experts, bool have_expert_ids);
+bool prefill_build_maps(const BankView& b, const __half* xg, const __half* ic2h, size_t rows, PrefillMaps* out);
 int launch_prefill_umma(const BankView& b, const void* x, int x_dtype, const DecodeRoutes& rt,
                         const float* route_weight, int tokens, int top_k, PrefillScratch sc, int sm_count,
                         const float* shared, const float* se_gate, cudaEvent_t join, void* out, int out_dtype,
-                        const Ctx& c);
+                        const PrefillMaps& maps, const Ctx& c);
 
 // shared_expert.cu
 int launch_shared_expert(const __nv_bfloat16* x, int tokens, int hidden, int shared_inter,

@@ -551,6 +551,28 @@ bool make_raw_map(CUtensorMap* map, const void* base, size_t rows, int row_bytes
 
 }  // namespace
 
+// The tensor maps of the two grouped GEMMs.  Every address they hold (the sorted-activation scratch, the
+// f16 intermediate, the four packed / scale banks) is fixed for the adapter's life, so they are encoded
+// when the adapter is created (and again when its banks are reallocated), never per call.  `rows` is the
+// scratch capacity in routes: a call with fewer routes reads stale rows past its own, whose columns the
+// epilogue never stores.
+bool prefill_build_maps(const BankView& b, const __half* xg, const __half* ic2h, size_t rows, PrefillMaps* out) {
+    out->ok = false;
+    if (!encode_tiled() || !b.gu_packed) return false;
+    for (int q = 0; q < 4; q++)
+        if (!make_act_map(&out->x[q], xg, rows, b.hidden, 32 * (q + 1)) ||
+            !make_act_map(&out->h[q], ic2h, rows, b.inter, 32 * (q + 1)))
+            return false;
+    const size_t gu_rows = (size_t)b.slots * 2 * b.inter, dn_rows = (size_t)b.slots * b.hidden;
+    if (!make_raw_map(&out->gp, b.gu_packed, gu_rows, b.hidden / 2, 128, kTileM, CU_TENSOR_MAP_SWIZZLE_128B) ||
+        !make_raw_map(&out->gs, b.gu_scale, gu_rows, b.hidden / 16, 16, kTileM, CU_TENSOR_MAP_SWIZZLE_NONE) ||
+        !make_raw_map(&out->dp, b.dn_packed, dn_rows, b.inter / 2, 128, kTileM, CU_TENSOR_MAP_SWIZZLE_128B) ||
+        !make_raw_map(&out->ds, b.dn_scale, dn_rows, b.inter / 16, 16, kTileM, CU_TENSOR_MAP_SWIZZLE_NONE))
+        return false;
+    out->ok = true;
+    return true;
+}
+
 bool prefill_umma_supported(int hidden, int inter, int slots, int experts, bool have_expert_ids) {
     if (hidden != 2048 || inter != 512) return false;
     if ((have_expert_ids ? experts : slots) > 1024) return false;
@@ -560,7 +582,7 @@ bool prefill_umma_supported(int hidden, int inter, int slots, int experts, bool 
 int launch_prefill_umma(const BankView& b, const void* x, int x_dtype, const DecodeRoutes& rt,
                         const float* route_weight, int tokens, int top_k, PrefillScratch sc, int sm_count,
                         const float* shared, const float* se_gate, cudaEvent_t join, void* out, int out_dtype,
-                        const Ctx& c) {
+                        const PrefillMaps& maps, const Ctx& c) {
     const int routes = tokens * top_k;
     int launches = 0;
     // 1. buckets, stable: by expert id of the layer (serving call) or by slot id
@@ -590,24 +612,16 @@ int launch_prefill_umma(const BankView& b, const void* x, int x_dtype, const Dec
     c.end();
     launches++;
 
+    if (!maps.ok) return -1;
     XMaps map_x, map_h;
-    CUtensorMap map_gp, map_gs, map_dp, map_ds;
-    for (int q = 0; q < 4; q++)
-        if (!make_act_map(&map_x.m[q], sc.xg, (size_t)routes, b.hidden, 32 * (q + 1)) ||
-            !make_act_map(&map_h.m[q], sc.ic2h, (size_t)routes, b.inter, 32 * (q + 1)))
-            return -1;
-    const size_t gu_rows = (size_t)b.slots * 2 * b.inter, dn_rows = (size_t)b.slots * b.hidden;
-    if (!make_raw_map(&map_gp, b.gu_packed, gu_rows, b.hidden / 2, 128, kTileM, CU_TENSOR_MAP_SWIZZLE_128B) ||
-        !make_raw_map(&map_gs, b.gu_scale, gu_rows, b.hidden / 16, 16, kTileM, CU_TENSOR_MAP_SWIZZLE_NONE) ||
-        !make_raw_map(&map_dp, b.dn_packed, dn_rows, b.inter / 2, 128, kTileM, CU_TENSOR_MAP_SWIZZLE_128B) ||
-        !make_raw_map(&map_ds, b.dn_scale, dn_rows, b.inter / 16, 16, kTileM, CU_TENSOR_MAP_SWIZZLE_NONE))
-        return -1;
-    static bool attr = false;
-    if (!attr) {
-        cudaFuncSetAttribute(umma_grouped_gemm_kernel<true, 2048>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kUmmaSmem);
-        cudaFuncSetAttribute(umma_grouped_gemm_kernel<false, 512>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kUmmaSmem);
-        attr = true;
+    for (int q = 0; q < 4; q++) {
+        map_x.m[q] = maps.x[q];
+        map_h.m[q] = maps.h[q];
     }
+    const CUtensorMap &map_gp = maps.gp, &map_gs = maps.gs, &map_dp = maps.dp, &map_ds = maps.ds;
+    static PerDeviceOnce once_gu, once_dn;
+    allow_dyn_smem(once_gu, umma_grouped_gemm_kernel<true, 2048>, kUmmaSmem);
+    allow_dyn_smem(once_dn, umma_grouped_gemm_kernel<false, 512>, kUmmaSmem);
     UmmaArgs a{};
     a.groups = sc.groups; a.n_groups = sc.n_groups; a.route_idx = sc.route_idx; a.err = sc.err;
     a.global = b.gu_global; a.row_scale = sc.row_scale;

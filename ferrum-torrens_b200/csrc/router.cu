@@ -495,11 +495,8 @@ int launch_router_logits(const __nv_bfloat16* x, const __nv_bfloat16* gate_w, in
     if (hidden % kBK == 0 && tokens >= 1024) {
         dim3 grid((experts + kBE - 1) / kBE, (tokens + kBT - 1) / kBT);
         const size_t smem = 2 * kBE * kBWStride + 2 * kBK * kBT * sizeof(float);
-        static bool attr3 = false;
-        if (!attr3) {
-            cudaFuncSetAttribute(router_logits_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            attr3 = true;
-        }
+        static PerDeviceOnce once;
+        allow_dyn_smem(once, router_logits_wide_kernel, smem);
         c.begin(K_ROUTER_LOGITS);
         router_logits_wide_kernel<<<grid, 128, smem, c.s>>>(x, gate_w, tokens, experts, hidden, logits);
         c.end();
@@ -508,11 +505,8 @@ int launch_router_logits(const __nv_bfloat16* x, const __nv_bfloat16* gate_w, in
     if (hidden % kKC == 0) {
         dim3 grid((experts + kTileE - 1) / kTileE, (tokens + kTileT - 1) / kTileT);
         const size_t smem = 2 * kTileE * kWStride + 2 * kKC * kTileT * sizeof(float);
-        static bool attr2 = false;
-        if (!attr2) {
-            cudaFuncSetAttribute(router_logits_tiled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            attr2 = true;
-        }
+        static PerDeviceOnce once;
+        allow_dyn_smem(once, router_logits_tiled_kernel, smem);
         c.begin(K_ROUTER_LOGITS);
         router_logits_tiled_kernel<<<grid, 128, smem, c.s>>>(x, gate_w, tokens, experts, hidden, logits);
         c.end();
@@ -530,12 +524,8 @@ int launch_router_logits(const __nv_bfloat16* x, const __nv_bfloat16* gate_w, in
         constexpr int TT = 4;
         dim3 grid(etiles, (tokens + kTokGroups * TT - 1) / (kTokGroups * TT));
         size_t smem = (size_t)kTokGroups * TT * kChunk * sizeof(float);
-        static bool attr = false;
-        if (!attr) {
-            cudaFuncSetAttribute(router_logits_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)smem);
-            attr = true;
-        }
+        static PerDeviceOnce once;
+        allow_dyn_smem(once, router_logits_kernel<TT>, smem);
         c.begin(K_ROUTER_LOGITS);
         router_logits_kernel<TT><<<grid, block, smem, c.s>>>(x, gate_w, tokens, experts, hidden, logits);
         c.end();

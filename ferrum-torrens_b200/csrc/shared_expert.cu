@@ -275,12 +275,9 @@ int launch_shared_expert(const __nv_bfloat16* x, int tokens, int hidden, int sha
     const int ttiles = (tokens + kTokTile - 1) / kTokTile;
     const int r1 = 16, r2 = 64;
     size_t sm1 = (size_t)kTokTile * hidden * sizeof(float), sm2 = (size_t)kTokTile * shared_inter * sizeof(float);
-    static bool attr = false;
-    if (!attr) {
-        cudaFuncSetAttribute(shared_phase1_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        cudaFuncSetAttribute(shared_phase2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        attr = true;
-    }
+    static PerDeviceOnce once1, once2;
+    allow_dyn_smem(once1, shared_phase1_kernel, 200 * 1024);
+    allow_dyn_smem(once2, shared_phase2_kernel, 200 * 1024);
     dim3 g1(ttiles, (shared_inter + r1 - 1) / r1);
     c.begin(K_SHARED_PHASE1);
     shared_phase1_kernel<<<g1, kThreads, sm1, c.s>>>(x, tokens, hidden, shared_inter, gate_up, shared_gate, r1, ic2s,

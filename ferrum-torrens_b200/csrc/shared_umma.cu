@@ -231,12 +231,9 @@ int launch_shared_umma(const __nv_bfloat16* x, int tokens, int hidden, int share
         !make_bf16_map(&map_ic2, ic2b, (size_t)2 * tokens, shared_inter, kTile) ||
         !make_bf16_map(&map_dn, down, (size_t)hidden, shared_inter, kTile))
         return -1;
-    static bool attr = false;
-    if (!attr) {
-        cudaFuncSetAttribute(dense_umma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDenseSmem);
-        cudaFuncSetAttribute(dense_umma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDenseSmem);
-        attr = true;
-    }
+    static PerDeviceOnce once_gu, once_dn;
+    allow_dyn_smem(once_gu, dense_umma_kernel<true>, kDenseSmem);
+    allow_dyn_smem(once_dn, dense_umma_kernel<false>, kDenseSmem);
     const int ttiles = (tokens + kTile - 1) / kTile;
     DenseArgs a{};
     a.tokens = tokens; a.err = err;

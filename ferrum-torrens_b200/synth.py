@@ -74,22 +74,26 @@ class HostLayer:
 
 
 def make_layer(seed: int, hidden: int = 2048, inter: int = 512, experts: int = 256, top_k: int = 8,
-               shared_inter: int = 512, zipf_alpha: float | None = None, global_scale: float = 1.0) -> HostLayer:
+               shared_inter: int = 512, zipf_alpha: float | None = None, global_scale=1.0) -> HostLayer:
+    """`global_scale`: the f16 row global of every expert row, one value or a (gate_up, down) pair.  The
+    benchmark configs use 1.0; (2^-6, 2^-10) gives layer outputs of magnitude O(0.1 .. 1), as real
+    checkpoints have and as a multi-layer stack needs to keep its residual stream bounded."""
     rng = np.random.default_rng(seed)
     gate = rng.normal(0.0, 0.02, (experts, hidden)).astype(np.float32)
     if zipf_alpha is not None:
         gate[:, 0] = zipf_bias(rng, experts, zipf_alpha)
-    f16 = np.array([global_scale], np.float16).view(np.uint16)[0]
+    gs = global_scale if isinstance(global_scale, (tuple, list)) else (global_scale, global_scale)
+    f16s = [np.array([g], np.float16).view(np.uint16)[0] for g in gs]
 
-    def bank(rows, cols):
+    def bank(rows, cols, f16):
         packed = rng.integers(0, 256, (experts, rows * cols // 2), dtype=np.uint8)
         u = rng.uniform(-6.0, 0.0, (experts, rows * cols // 16))
         scale = nearest_e4m3(np.exp2(u))
         glob = np.full((experts, rows), f16, np.uint16).view(np.uint8).reshape(experts, rows * 2)
         return packed, scale, glob
 
-    gu = bank(2 * inter, hidden)
-    dn = bank(hidden, inter)
+    gu = bank(2 * inter, hidden, f16s[0])
+    dn = bank(hidden, inter, f16s[1])
     n = lambda *s: f32_to_bf16_bits(rng.normal(0.0, 0.02, s).astype(np.float32))
     return HostLayer(hidden, inter, experts, top_k, shared_inter, f32_to_bf16_bits(gate),
                      n(2 * shared_inter, hidden), n(hidden, shared_inter), n(1, hidden), [*gu, *dn],

@@ -68,8 +68,9 @@ class OracleBackend:
 
 
 def _worker(rank, world, port, tokens_per_rank, q):
+    import datetime
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=90))
     try:
         lay = pkg.synth.make_layer(21, hidden=H, inter=I, experts=E, top_k=K, shared_inter=SI)
         x = torch.from_numpy(pkg.synth.bf16_bits_to_f32(pkg.synth.make_x(100 + rank, tokens_per_rank[rank], H)))
@@ -86,9 +87,15 @@ def _worker(rank, world, port, tokens_per_rank, q):
             ids2, _ = layer.forward_overlapped(0, x, None, True, None, None, out2, chunks=chunks)
             assert np.array_equal(ids2.numpy(), want_ids)
             assert np.abs(out2.numpy() - out.numpy()).max() <= 1e-6 * np.abs(want).max(), chunks
-        q.put((rank, float(err), sc, rc))
+        q.put((rank, float(err), sc, rc, None))
+    except BaseException as exc:   # the parent fails fast instead of waiting for the queue
+        q.put((rank, float("inf"), [], [], repr(exc)[:500]))
+        raise
     finally:
-        dist.destroy_process_group()
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
 
 
 @pytest.mark.parametrize("tokens_per_rank", [(5, 9), (1, 0 + 3)])
@@ -100,12 +107,28 @@ def test_two_ranks_match_single_rank(tokens_per_rank):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     procs = [ctx.Process(target=_worker, args=(r, 2, port, tokens_per_rank, q)) for r in range(2)]
+    res = []
+    try:
+        for p in procs:
+            p.start()
+        for _ in procs:
+            r = q.get(timeout=120)
+            res.append(r)
+            if r[4] is not None:
+                break
+        if all(r[4] is None for r in res):
+            for p in procs:
+                p.join(60)
+    finally:
+        for p in procs:   # no worker outlives the test
+            if p.is_alive():
+                p.kill()
+                p.join(10)
+    for r in res:
+        assert r[4] is None, f"rank {r[0]} raised: {r[4]}"
     for p in procs:
-        p.start()
-    res = sorted(q.get(timeout=120) for _ in procs)
-    for p in procs:
-        p.join(60)
         assert p.exitcode == 0
+    res = sorted(r[:4] for r in res)
     for rank, err, sc, rc in res:
         assert err < 1e-5, (rank, err)
         assert sum(sc) == tokens_per_rank[rank] * K

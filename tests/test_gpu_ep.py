@@ -19,12 +19,18 @@ def _bf16(bits, dev):
 
 
 def _worker(rank, world, port, tokens, q):
+    import datetime
     import torch.distributed as dist
     ep = importlib.import_module("ferrum-torrens_b200.ep")
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    # plain peer stores only: no NVLink multicast object is bound to the symmetric buffers, so a rank that
+    # dies leaves nothing behind on its peers' GPUs
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                      TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
     torch.cuda.set_device(rank)
     dev = torch.device(f"cuda:{rank}")
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    # a short collective timeout: if the other rank raised before a collective, this one errors out of it
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
+                            timeout=datetime.timedelta(seconds=120))
     try:
         lay = pkg.synth.make_layer(77, hidden=H, inter=I, experts=E, top_k=K, shared_inter=SI)
         xb = pkg.synth.make_x(500 + rank, tokens, H)
@@ -65,11 +71,17 @@ def _worker(rank, world, port, tokens, q):
             be.owner.sync_status()
             same_ids = same_ids and bool(torch.equal(ids3, want_ids))
             rel = max(rel, float((out3 - want).norm() / want.norm()))
-        q.put((rank, same_ids, rel))
+        q.put((rank, same_ids, rel, None))
         solo.close()
         be.close()
+    except BaseException as exc:   # the parent fails fast instead of waiting for the queue
+        q.put((rank, False, float("inf"), repr(exc)[:500]))
+        raise
     finally:
-        dist.destroy_process_group()
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
@@ -83,13 +95,30 @@ def test_two_gpu_expert_parallel_matches_single_gpu(tokens):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     procs = [ctx.Process(target=_worker, args=(r, 2, port, tokens, q)) for r in range(2)]
+    res = []
+    try:
+        for p in procs:
+            p.start()
+        for _ in procs:
+            r = q.get(timeout=300)
+            res.append(r)
+            if r[3] is not None:   # a rank raised: do not wait for the other, it is killed below
+                break
+        if all(r[3] is None for r in res):
+            for p in procs:
+                p.join(60)
+    finally:
+        # no worker outlives the test: a rank left inside a collective would keep spinning on its GPU
+        for p in procs:
+            if p.is_alive():
+                p.kill()
+                p.join(10)
+    for r in res:
+        assert r[3] is None, f"rank {r[0]} raised: {r[3]}"
+    assert len(res) == len(procs)
     for p in procs:
-        p.start()
-    res = [q.get(timeout=300) for _ in procs]
-    for p in procs:
-        p.join(60)
         assert p.exitcode == 0
-    for rank, same_ids, rel in res:
+    for rank, same_ids, rel, _ in res:
         assert same_ids
         # the owner returns bf16 rows (half the NVLink bytes); one rounding per route
         assert rel < 5e-3, (rank, rel)

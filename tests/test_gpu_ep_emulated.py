@@ -111,3 +111,43 @@ def test_peer_exchange_kernels_many_ranks_on_one_gpu(world, tokens):
         assert rel < 5e-3, (r, rel)     # one bf16 rounding per returned row
     for m in fronts + owners + [solo]:
         m.close()
+
+
+def test_dispatch_reports_an_expert_id_outside_the_layer_instead_of_following_it():
+    """An id outside [0, experts) reaches ftm_ep_plan / ftm_ep_dispatch: the permutation build flags it and
+    leaves that route's position unwritten, and the dispatch kernel must raise the error status without
+    indexing anything with it (every index is checked before the load that depends on it)."""
+    dev = torch.device("cuda:0")
+    world, tokens = 4, 6
+    lay = pkg.synth.make_layer(92, hidden=H, inter=I, experts=E, top_k=K, shared_inter=SI)
+    front = pkg.B200MoE(0, pkg.ExpertShapes(H, I), 1, experts=E, layers=1, top_k=K, shared_inter=SI, max_tokens=tokens)
+    x = _bf16(pkg.synth.make_x(5, tokens, H), dev)
+    ids, w = front.router(x, _bf16(lay.gate_w, dev))
+    front.sync_status()
+    cap = tokens * K
+    recv_x = [torch.zeros((cap, H), dtype=torch.bfloat16, device=dev) for _ in range(world)]
+    recv_m = [torch.zeros((cap, 2), dtype=torch.int32, device=dev) for _ in range(world)]
+    ptrs = lambda ts: torch.tensor([t.data_ptr() for t in ts], dtype=torch.int64, device=dev)
+    peer_x, peer_m = ptrs(recv_x), ptrs(recv_m)
+    for bad in (-1, E + 3):
+        bad_ids = ids.clone()
+        bad_ids[2, 1] = bad
+        route_idx, counts = front.ep_plan(bad_ids, world)
+        counts_all = torch.zeros((world * world,), dtype=torch.int32, device=dev)
+        counts_all[:world] = counts                 # this "rank" is rank 0, the others send nothing
+        front.ep_dispatch(x, bad_ids, w, route_idx, world, 0, counts_all, peer_x.data_ptr(), peer_m.data_ptr(), cap)
+        with pytest.raises(pkg.MoEError):
+            front.sync_status()
+        try:                                         # both flags (bad id, dropped row) may be pending: drain them
+            front.sync_status()
+        except pkg.MoEError:
+            pass
+        front.sync_status()
+    # a clean step after the bad ones still works
+    route_idx, counts = front.ep_plan(ids, world)
+    counts_all = torch.zeros((world * world,), dtype=torch.int32, device=dev)
+    counts_all[:world] = counts
+    front.ep_dispatch(x, ids, w, route_idx, world, 0, counts_all, peer_x.data_ptr(), peer_m.data_ptr(), cap)
+    front.sync_status()
+    assert int(sum(int(m[:, 0].ge(0).sum()) for m in recv_m)) > 0
+    front.close()

@@ -3,10 +3,13 @@
 Bars (from the build's target):
 * routed expert ids and the permutation: bit-exact (ties to the lowest expert index);
 * router weights: within 1e-6 of the CPU path (tests/cudarc_forward.rs:253-254 of the reference);
-* layer outputs: relative L2 <= 1e-2, and max |diff| <= 2e-2 of the largest reference magnitude.
-  The synthetic experts (unit globals, block scales up to 1) produce outputs of magnitude ~1e4,
-  where a bf16 ulp alone is 64, so the max-abs bound is taken relative to max |reference| -- the
-  same normalisation the reference's kernel gate uses (python/ferrum_kernel/selftest.py:936).
+* layer outputs: relative L2 <= 1e-2 and max |diff| <= 2e-2.
+  The benchmark's synthetic experts (unit globals, block scales up to 1) produce outputs of magnitude
+  ~1e4, where a bf16 ulp alone is 64; for those fixtures the max-abs bound is taken relative to
+  max |reference| (`check_close`), the same normalisation the reference's kernel gate uses
+  (python/ferrum_kernel/selftest.py:936).  The ABSOLUTE bound is asserted on layers whose row globals
+  (2^-6 gate_up, 2^-10 down) give outputs of magnitude O(0.1 .. 1), as real checkpoints have
+  (`check_close_abs`): decode, grouped GEMM, whole block and a four-layer stack.
 """
 import importlib
 import os
@@ -39,6 +42,18 @@ def check_close(got: np.ndarray, want: np.ndarray, rel_l2=REL_L2, max_abs_rel=MA
     mx = np.abs(got - want).max() / max(np.abs(want).max(), 1e-30)
     assert rel <= rel_l2, f"relative L2 {rel:.3e}"
     assert mx <= max_abs_rel, f"max abs (relative to max |ref|) {mx:.3e}"
+    return rel, mx
+
+
+MAX_ABS = 2e-2
+
+
+def check_close_abs(got: np.ndarray, want: np.ndarray, rel_l2=REL_L2, max_abs=MAX_ABS):
+    """The stated bar as written: relative L2 and ABSOLUTE max |diff|."""
+    rel = np.linalg.norm(got - want) / max(np.linalg.norm(want), 1e-30)
+    mx = np.abs(got - want).max()
+    assert rel <= rel_l2, f"relative L2 {rel:.3e}"
+    assert mx <= max_abs, f"max abs {mx:.3e}"
     return rel, mx
 
 
@@ -584,8 +599,8 @@ def _zipf_ids(rng, tokens, experts, top_k, alpha):
 
 @pytest.mark.parametrize("tokens", [300, 512])
 def test_large_batch_path_matches_cpu_path(full, tokens):
-    """More than 2048 routes: CSR buckets cut into groups of 16 tokens (Zipf 1.1 skew: some experts get
-    no token, hot ones many groups)."""
+    """More than 2048 routes take the tcgen05 grouped GEMM: CSR buckets cut into passes of at most 128 sorted
+    rows per expert (Zipf 1.1 skew: some experts get no token, hot ones several passes)."""
     lay, moe, ol = full
     rng = np.random.default_rng(tokens)
     xb = pkg.synth.make_x(31 + tokens, tokens, lay.hidden)
@@ -634,3 +649,123 @@ def test_prefill_2048_tokens_paths_agree_and_block_properties(full):
     assert np.array_equal(got_ids.cpu().numpy(), want_ids)
     assert np.abs(got_w.cpu().numpy() - want_w).max() <= 1e-6
     assert torch.isfinite(out.float()).all()
+
+
+# ------------------------------------------------------------------ config 3 through the real router
+@pytest.mark.parametrize("tokens", [512, 2048])
+def test_config3_whole_block_zipf_through_the_router_matches_cpu_path(tokens):
+    """Prefill sizes with a Zipf(1.1) popularity bias carried through the real router (hidden column 0 of the
+    gate weight, x[:, 0] = 1): ids bit-exact, outputs against the CPU path directly (not against another CUDA
+    path).  Some experts get no token, hot ones are cut into several passes of the grouped GEMM."""
+    lay = pkg.synth.make_layer(3033, zipf_alpha=1.1)
+    moe = make_moe(lay, max_tokens=tokens)
+    load_all(moe, lay)
+    ol = oracle_layer(lay)
+    xb = pkg.synth.make_x(600 + tokens, tokens, lay.hidden, biased=True)
+    out = torch.empty((tokens, lay.hidden), dtype=torch.bfloat16, device=dev())
+    ids = torch.empty((tokens, lay.top_k), dtype=torch.int32, device=dev())
+    w = torch.empty((tokens, lay.top_k), dtype=torch.float32, device=dev())
+    moe.moe_block(0, bf16_dev(xb), bf16_dev(lay.gate_w), bf16_dev(lay.sh_gate_up), bf16_dev(lay.sh_down),
+                  bf16_dev(lay.sh_gate), out, ids_out=ids, weights_out=w)
+    moe.sync_status()
+    want, want_ids, want_w = o.moe_block(ol, pkg.synth.bf16_bits_to_f32(xb), threads=o.max_threads())
+    assert np.array_equal(ids.cpu().numpy(), want_ids), "routed expert ids must be bit-exact"
+    assert np.abs(w.cpu().numpy() - want_w).max() <= 1e-6
+    rel, _ = check_close(out.float().cpu().numpy(), want)
+    assert rel < 5e-3, rel
+    counts = np.bincount(want_ids.reshape(-1), minlength=lay.experts)
+    if tokens == 2048:
+        assert counts.min() == 0 and counts.max() > 200, "config 3: some experts idle, hot ones above 200 tokens"
+    # the permutation of these routes, bit-exact
+    seg, idx, badf = moe.csr_build(ids.reshape(-1), lay.experts)
+    want_seg, want_idx = o.build_grouped_csr(want_ids.reshape(-1), lay.experts)
+    assert np.array_equal(seg.cpu().numpy(), want_seg) and np.array_equal(idx.cpu().numpy(), want_idx) and badf == 0
+    moe.close()
+
+
+# ------------------------------------------------------------------ the absolute max-abs bar
+SMALL_GLOBALS = (2.0 ** -6, 2.0 ** -10)
+
+
+@pytest.fixture(scope="module")
+def unit_scale():
+    """The benchmark layer with row globals 2^-6 / 2^-10: outputs of magnitude O(0.1 .. 1)."""
+    lay = pkg.synth.make_layer(4141, global_scale=SMALL_GLOBALS)
+    moe = make_moe(lay, max_tokens=512)
+    load_all(moe, lay)
+    yield lay, moe, oracle_layer(lay)
+    moe.close()
+
+
+@pytest.mark.parametrize("tokens,odt", [(1, "bf16"), (8, "bf16"), (64, "bf16"), (64, "f32"), (300, "bf16")])
+def test_whole_block_meets_the_absolute_bar(unit_scale, tokens, odt):
+    """rel-L2 <= 1e-2 AND max |diff| <= 2e-2 in absolute terms: decode kernels (1, 8, 64 tokens) and the
+    tcgen05 grouped GEMM (300 tokens = 2400 routes)."""
+    lay, moe, ol = unit_scale
+    xb = pkg.synth.make_x(5150 + tokens, tokens, lay.hidden)
+    out = torch.empty((tokens, lay.hidden), dtype=torch.bfloat16 if odt == "bf16" else torch.float32, device=dev())
+    ids = torch.empty((tokens, lay.top_k), dtype=torch.int32, device=dev())
+    moe.moe_block(0, bf16_dev(xb), bf16_dev(lay.gate_w), bf16_dev(lay.sh_gate_up), bf16_dev(lay.sh_down),
+                  bf16_dev(lay.sh_gate), out, ids_out=ids)
+    moe.sync_status()
+    want, want_ids, _ = o.moe_block(ol, pkg.synth.bf16_bits_to_f32(xb), threads=o.max_threads())
+    assert np.array_equal(ids.cpu().numpy(), want_ids)
+    assert 0.05 < np.abs(want).max() < 4.0, "the case must have outputs where the absolute bar means something"
+    check_close_abs(out.float().cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("path", ["gemv", "grouped"])
+def test_routed_half_meets_the_absolute_bar_on_both_expert_paths(unit_scale, path):
+    """The serving call with given ids on the decode kernels and on the grouped GEMM (forced), 320 tokens."""
+    lay, moe, ol = unit_scale
+    tokens = 320
+    rng = np.random.default_rng(12)
+    xb = pkg.synth.make_x(6160, tokens, lay.hidden)
+    ids = _zipf_ids(rng, tokens, lay.experts, lay.top_k, 1.1)
+    w = rng.uniform(0.05, 0.5, (tokens, lay.top_k)).astype(np.float32)
+    out = torch.empty((tokens, lay.hidden), dtype=torch.bfloat16, device=dev())
+    req = pkg.MoEDeviceRequest(0, lay.hidden, lay.inter, lay.top_k, bf16_dev(xb), torch.from_numpy(ids).to(dev()),
+                               torch.from_numpy(w).to(dev()))
+    moe.grouped_moe_staged(req, out, path=pkg._lib.PATH_GEMV if path == "gemv" else pkg._lib.PATH_GROUPED)
+    moe.sync_status()
+    want = o.grouped_moe_reference_mt(ol.banks, lay.hidden, lay.inter, pkg.synth.bf16_bits_to_f32(xb), lay.top_k,
+                                      ids.reshape(-1), w.reshape(-1))
+    check_close_abs(out.float().cpu().numpy(), want)
+
+
+# ------------------------------------------------------------------ config 4 in small: a stack of blocks
+def test_four_layer_stack_matches_the_chained_cpu_path():
+    """x <- x + block_l(x) over four independently seeded layers (bf16 residual stream, as the stack benchmark
+    runs it).  Every layer is checked against the CPU path fed the SAME input bits (ids bit-exact, outputs to
+    the absolute bar), and the free-running CPU chain is compared at the end."""
+    L, tokens = 4, 48
+    lays = [pkg.synth.make_layer(7000 + l, global_scale=SMALL_GLOBALS) for l in range(L)]
+    moe = make_moe(lays[0], max_tokens=tokens, layers=L)
+    for l, lay in enumerate(lays):
+        load_all(moe, lay, layer=l, slot0=l * lay.experts)
+    H = lays[0].hidden
+    xb = pkg.synth.make_x(7100, tokens, H)
+    cur = bf16_dev(xb).clone()
+    chain = pkg.synth.bf16_bits_to_f32(xb)          # the CPU chain, free-running
+    chain_ok = True
+    for l, lay in enumerate(lays):
+        ol = oracle_layer(lay)
+        out = torch.empty((tokens, H), dtype=torch.bfloat16, device=dev())
+        ids = torch.empty((tokens, lay.top_k), dtype=torch.int32, device=dev())
+        moe.moe_block(l, cur, bf16_dev(lay.gate_w), bf16_dev(lay.sh_gate_up), bf16_dev(lay.sh_down),
+                      bf16_dev(lay.sh_gate), out, ids_out=ids)
+        moe.sync_status()
+        x_in = cur.float().cpu().numpy()
+        want, want_ids, _ = o.moe_block(ol, x_in, threads=o.max_threads())
+        assert np.array_equal(ids.cpu().numpy(), want_ids), f"layer {l}: ids"
+        check_close_abs(out.float().cpu().numpy(), want)
+        cur = cur + out                              # bf16 residual add
+        c_out, c_ids, _ = o.moe_block(ol, chain, threads=o.max_threads())
+        chain_ok = chain_ok and np.array_equal(c_ids, want_ids)
+        chain = pkg.synth.bf16_bits_to_f32(pkg.synth.f32_to_bf16_bits(
+            chain + pkg.synth.bf16_bits_to_f32(pkg.synth.f32_to_bf16_bits(c_out))))
+    got = cur.float().cpu().numpy()
+    assert np.isfinite(got).all()
+    if chain_ok:   # a routing tie broken differently by a one-ulp input difference would fork the two chains
+        check_close_abs(got, chain, rel_l2=1e-2, max_abs=5e-2)
+    moe.close()
