@@ -40,6 +40,8 @@ GATE_UP_BYTES = 1048576 + 131072 + 2048     # packed + scales + globals of gate_
 DOWN_BYTES = 524288 + 65536 + 4096
 METRIC = "moe_layer_tokens_per_s"
 UNIT = "tokens/s"
+UNIT_S = UNIT
+DTYPE = "bf16 activations x NVFP4 (e2m1 + e4m3 block scales) weights, f32 accumulate"
 
 
 def parse():
@@ -50,7 +52,10 @@ def parse():
     ap.add_argument("--tokens", type=int, default=0, help="tokens per step (default: 64 at N=1)")
     ap.add_argument("--layers", type=int, default=4, help="independent layers cycled through")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--sweep", action="store_true", help="also report T = 1, 8, 512, 2048")
+    ap.add_argument("--no-sweep", action="store_true",
+                    help="N = 1: leave out the other batch sizes (T = 1, 8, 512, 2048) and the 40-layer stack that the "
+                         "default line carries beside the T = 64 headline")
+    ap.add_argument("--stack-layers", type=int, default=40, help="layers of the stack reported by the default line")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ep-chunks", type=int, default=2,
                     help="N > 1: expert ranges per owner that are exchanged and computed one after the other, so that "
@@ -155,16 +160,22 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    tokens = args.tokens or 64
+    ep = args.gpus > 1
+    tokens = args.tokens or (8192 if ep else 64)
     sample = min(tokens, 16)
     steps, warmup = max(1, min(args.steps, 8)), max(1, min(args.warmup, 2))
     tps, threads, sec = time_cpu(sample, steps, warmup)
+    workload = (f"expert-parallel layer, T={tokens} tokens per GPU on {args.gpus} GPUs" if ep else f"decode T={tokens}") + \
+        f", hidden {HIDDEN}, {EXPERTS} NVFP4 experts top-{TOP_K}, shared {SHARED}"
     line = {
         "impl": "reference", "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
         "warmup": warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"decode T={tokens}, hidden {HIDDEN}, {EXPERTS} NVFP4 experts top-{TOP_K}, shared {SHARED}",
-                   "sample": f"{sample} tokens per step"},
+        "config": {"workload": workload, "sample": f"{sample} tokens per step",
+                   "sample_reason": "the CPU path costs the same per (token, route) whatever the batch size or the number "
+                                    "of GPUs it is compared with, about 5 ms per token on 16 cores: the whole batch for the "
+                                    "requested steps would take minutes, so a step is a 16-token sample of the batch and "
+                                    "steps / warm-up are capped at 8 / 2; tokens/s is unaffected by the cut"},
         "cpu_baseline": {"value": tps, "unit": UNIT, "cores": threads, "kind": "port",
                          "sample": f"{sample} tokens of the T={tokens} batch per step, whole block, "
                                    f"{steps} steps; C restatement of the reference's host path (the Rust "
@@ -189,7 +200,9 @@ def run_b200(args):
     torch.cuda.set_device(local)
     dev = torch.device(f"cuda:{local}")
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        # a rank that fails before a collective must not leave the others inside it for long
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=300))
 
     import __graft_entry__ as ge
     if rank == 0:
@@ -201,61 +214,212 @@ def run_b200(args):
     if world > 1:
         return run_ep(args, pkg, dev, world, rank, local)
 
+    return run_single(args, pkg, dev, local)
+
+
+L2_BYTES = 126e6
+
+
+def timed_steps(torch, fn, steps, warmup):
+    """CUDA-event time of `steps` calls of fn(i) after `warmup` untimed ones, synchronised on both sides (ms)."""
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        fn(warmup + i)
+    e1.record()
+    torch.cuda.synchronize()
+    return float(e0.elapsed_time(e1))
+
+
+class Workload:
+    """One batch size of the whole block on one adapter: `nl` independently seeded layers cycled step by step."""
+
+    def __init__(self, pkg, moe, dense, dev, T, nl, biased, path):
+        import torch
+        self.torch, self.pkg, self.moe, self.dense, self.T, self.nl, self.path = torch, pkg, moe, dense, T, nl, path
+        self.xs = [pkg.synth.device_x(3000 + l, T, HIDDEN, dev, biased=biased) for l in range(nl)]
+        self.out = torch.empty((T, HIDDEN), dtype=torch.bfloat16, device=dev)
+        self.ids = torch.empty((T, TOP_K), dtype=torch.int32, device=dev)
+        self.wts = torch.empty((T, TOP_K), dtype=torch.float32, device=dev)
+
+    def step(self, i, x=None, o=None):
+        l = i % self.nl
+        g, su, sd, sg = self.dense[l]
+        self.moe.moe_block(l, self.xs[l] if x is None else x, g, su, sd, sg, self.out if o is None else o,
+                           ids_out=self.ids, weights_out=self.wts, path=self.path)
+
+    def time_block(self, K, W):
+        self.step(0)
+        self.moe.sync_status()      # a kernel that gave up a bounded wait fails here, before anything is timed
+        l0 = self.moe.kernel_launches()
+        ms = timed_steps(self.torch, self.step, K, W)
+        launches = (self.moe.kernel_launches() - l0) * K // (K + W)
+        return ms, launches
+
+    def profile(self, K, W):
+        """Per-kernel CUDA-event pass.  The routed half runs alone (serving call with the router's ids), so that
+        the shared expert, which the whole block overlaps on a second stream, does not share the SMs with the
+        timed kernels; router and shared expert are then timed each alone.  Returns (kernels, mean distinct
+        experts per step)."""
+        torch, moe, pkg = self.torch, self.moe, self.pkg
+        routed = []
+        for l in range(self.nl):
+            self.step(l)
+            torch.cuda.synchronize()
+            routed.append((self.ids.clone(), self.wts.clone()))
+        uniq = [int(torch.unique(i).numel()) for i, _ in routed]
+        reqs = [pkg.MoEDeviceRequest(l, HIDDEN, INTER, TOP_K, self.xs[l], routed[l][0], routed[l][1]) for l in range(self.nl)]
+        for i in range(W):
+            moe.grouped_moe_staged(reqs[i % self.nl], self.out, path=self.path)
+        moe.profile(True)
+        for i in range(K):
+            moe.grouped_moe_staged(reqs[i % self.nl], self.out, path=self.path)
+        prof = moe.profile_read()
+        moe.profile(False)
+        moe.profile(True)
+        for i in range(K):
+            g, su, sd, sg = self.dense[i % self.nl]
+            moe.router(self.xs[i % self.nl], g)
+            moe.shared_expert(self.xs[i % self.nl], su, sd, sg)
+        prof.update(moe.profile_read())
+        moe.profile(False)
+        return prof, sum(uniq) / len(uniq)
+
+
+def roofline_of(prof, U, T, nl, pk):
+    """`roofline` object of the dominant routed-expert kernel from a per-kernel profile."""
+    gate_kind = "expert_gate_up" if "expert_gate_up" in prof else "grouped_gate_up"
+    g_ms, g_n = prof[gate_kind]
+    us = g_ms / g_n * 1e3
+    kernels = {k: {"us_per_launch": ms / n * 1e3, "launches": n} for k, (ms, n) in prof.items()}
+    if gate_kind == "expert_gate_up":
+        # decode kernels: bound by the stream of the routed experts' weights
+        gu_bytes = U * GATE_UP_BYTES + T * HIDDEN * 2
+        achieved = gu_bytes / (us * 1e-6) / 1e9
+        touched = nl * U * EXPERT_BYTES
+        resident = touched < 2 * L2_BYTES
+        r = {"bound": "L2 (the cycled experts fit the 126 MB L2)" if resident else "hbm", "kernel": gate_kind,
+             "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
+             "peak_source": pk["which"], "frac_of_nominal_8000": achieved / 8000.0,
+             "traffic": None,
+             "traffic_source": "not captured in this run; profiles/expert_mma_gate_up_T64.md holds the ncu capture of this "
+                               "kernel (dram bytes read + written against the algorithmic bytes of the same launch)",
+             "distinct_experts": U, "bytes_per_launch": gu_bytes, "us_per_launch": us,
+             "expert_bytes_touched_per_cycle": touched, "l2_resident": resident, "kernels": kernels}
+        if "expert_down" in prof:
+            d_ms, d_n = prof["expert_down"]
+            dn = (U * DOWN_BYTES) / (d_ms / d_n * 1e-3) / 1e9
+            r["down"] = {"achieved": dn, "frac": dn / pk["hbm_gbs"], "us_per_launch": d_ms / d_n * 1e3}
+            r["expert_weights_gbs"] = (U * EXPERT_BYTES) / ((g_ms / g_n + d_ms / d_n) * 1e-3) / 1e9
+        return r
+    # tcgen05 grouped GEMM: useful flops of the routes (padding of ragged groups not counted)
+    flops = T * TOP_K * 2.0 * HIDDEN * (2 * INTER)
+    achieved = flops / (us * 1e-6) / 1e12
+    r = {"bound": "tensor", "kernel": gate_kind, "achieved": achieved, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
+         "frac": achieved / pk["bf16_tflops"],
+         "peak_source": pk["which"] + " (burst; sustained %.0f)" % pk["bf16_tflops_sustained"], "traffic": None,
+         "distinct_experts": U, "flops_per_launch": flops, "us_per_launch": us,
+         "weight_stream_gbs": U * GATE_UP_BYTES / (us * 1e-6) / 1e9, "kernels": kernels}
+    if "grouped_down" in prof:
+        d_ms, d_n = prof["grouped_down"]
+        dn = T * TOP_K * 2.0 * INTER * HIDDEN / (d_ms / d_n * 1e-3) / 1e12
+        r["down"] = {"achieved": dn, "frac": dn / pk["bf16_tflops"], "us_per_launch": d_ms / d_n * 1e3}
+    return r
+
+
+def stack_pass_fn(torch, moe, dense, x0, nlayers, path):
+    """One pass through `nlayers` MoE blocks with a bf16 residual add between them."""
+    T = x0.shape[0]
+    out = torch.empty((T, HIDDEN), dtype=torch.bfloat16, device=x0.device)
+    xa, xb = torch.empty_like(x0), torch.empty_like(x0)
+
+    def stack_pass(i=0):
+        xa.copy_(x0)
+        cur, nxt = xa, xb
+        for l in range(nlayers):
+            g, su, sd, sg = dense[l]
+            moe.moe_block(l, cur, g, su, sd, sg, out, path=path)
+            torch.add(cur, out, out=nxt)
+            cur, nxt = nxt, cur
+        return cur
+    return stack_pass
+
+
+def measure_stack(torch, moe, dense, x0, nlayers, path, K, W):
+    """tokens/s through the whole stack, eager and replayed from one CUDA graph."""
+    T = x0.shape[0]
+    fn = stack_pass_fn(torch, moe, dense, x0, nlayers, path)
+    last = fn()
+    moe.sync_status()
+    finite = bool(torch.isfinite(last.float()).all())
+    rms = float(last.float().pow(2).mean().sqrt())
+    ms = timed_steps(torch, fn, K, W)
+    res = {"layers": nlayers, "tokens": T, "ms_per_pass": ms / K, "tokens_per_s": T * K / (ms * 1e-3),
+           "us_per_layer": ms / K / nlayers * 1e3, "residual_rms_after_last_layer": rms, "finite": finite,
+           "expert_bank_gb": nlayers * EXPERTS * EXPERT_BYTES / 1e9}
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        cg = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(cg, stream=side):
+            fn()
+        g_ms = timed_steps(torch, lambda i: cg.replay(), K, 3)
+        moe.sync_status()
+        res["graph_replay"] = {"ms_per_pass": g_ms / K, "tokens_per_s": T * K / (g_ms * 1e-3)}
+    except Exception as exc:
+        res["graph_replay"] = {"error": str(exc)[:200]}
+    return res
+
+
+def run_single(args, pkg, dev, local):
+    import torch
     T = args.tokens or 64
     path = {"auto": 0, "gemv": 1, "grouped": 2, "scalar": 3}[args.path]
-    nlayers = max(1, args.layers)
-    moe = pkg.B200MoE(local, pkg.ExpertShapes(HIDDEN, INTER), EXPERTS * nlayers, experts=EXPERTS, layers=nlayers,
-                      top_k=TOP_K, shared_inter=SHARED, max_tokens=max(T, 64))
-    dense, xs = [], []
-    # a stack feeds every block's output back into the residual stream: row globals 2^-6 / 2^-10 keep it O(1)
-    gbits = (0x2400, 0x1400) if args.stack else (0x3C00, 0x3C00)
-    for l in range(nlayers):
-        pkg.synth.fill_banks_on_device(moe, l, seed=1000 + 17 * rank + l, slot0=l * EXPERTS, global_bits=gbits)
-        dense.append(pkg.synth.device_dense_weights(2000 + 17 * rank + l, dev, zipf_alpha=args.zipf))
-        xs.append(pkg.synth.device_x(3000 + 17 * rank + l, T, HIDDEN, dev, biased=args.zipf is not None))
-    if args.stack and world == 1:
-        return run_stack(args, pkg, moe, dense, xs[0], dev, T, nlayers, path)
-    out = torch.empty((T, HIDDEN), dtype=torch.bfloat16, device=dev)
-    ids = torch.empty((T, TOP_K), dtype=torch.int32, device=dev)
-    wts = torch.empty((T, TOP_K), dtype=torch.float32, device=dev)
-
-    def step(i, x=None, o=None):
-        l = i % nlayers
-        g, su, sd, sg = dense[l]
-        moe.moe_block(l, xs[l] if x is None else x, g, su, sd, sg, out if o is None else o, ids_out=ids, weights_out=wts,
-                      path=path)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def timed(fn, steps, warmup):
-        for i in range(warmup):
-            fn(i)
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for i in range(steps):
-            fn(warmup + i)
-        e1.record()
-        barrier()
-        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
-        if world > 1:
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return float(ms.item())
-
+    cycle = max(1, args.layers)
+    # the default line also carries the other batch sizes of the metric (T = 1, 8, 512, 2048) and the 40-layer
+    # stack; a run asked for one particular workload (--tokens / --zipf / --path / --stack) reports only that
+    default_line = not (args.tokens or args.zipf is not None or args.path != "auto" or args.stack) and not args.no_sweep
+    # --stack --layers N runs a stack of N layers; the default line keeps --stack-layers layers resident
+    total_layers = max(cycle, args.stack_layers) if default_line else cycle
+    max_tokens = max(T, 64, 2048 if default_line else 0)
+    moe = pkg.B200MoE(local, pkg.ExpertShapes(HIDDEN, INTER), EXPERTS * total_layers, experts=EXPERTS, layers=total_layers,
+                      top_k=TOP_K, shared_inter=SHARED, max_tokens=max_tokens)
+    G_SMALL = (0x2400, 0x1400)    # f16 row globals 2^-6 / 2^-10: a stack's residual stream stays O(1)
+    G_ONE = (0x3C00, 0x3C00)      # 1.0, the benchmark configs' global scale
+    for l in range(total_layers):
+        pkg.synth.fill_banks_on_device(moe, l, seed=1000 + l, slot0=l * EXPERTS, global_bits=G_SMALL if args.stack else G_ONE)
+    dense = [pkg.synth.device_dense_weights(2000 + l, dev, zipf_alpha=args.zipf) for l in range(total_layers)]
     W, K = max(3, args.warmup), max(1, args.steps)
-    # one checked step before anything is timed: a kernel that gave up a bounded wait fails here
-    step(0)
-    moe.sync_status()
-    sampler = ClockSampler(local)
-    if rank == 0:
+    pk = peaks()
+
+    if args.stack:
+        x0 = pkg.synth.device_x(3000, T, HIDDEN, dev, biased=args.zipf is not None)
+        sampler = ClockSampler(local)
         sampler.start()
-    l0 = moe.kernel_launches()
-    total_ms = timed(step, K, W)
-    launches = (moe.kernel_launches() - l0) * K // (K + W)
-    value = world * T * K / (total_ms * 1e-3)
+        st = measure_stack(torch, moe, dense, x0, total_layers, path, K, W)
+        clocks = sampler.stop()
+        print(json.dumps({
+            "metric": METRIC, "value": st["tokens_per_s"], "unit": UNIT_S, "n_gpus": 1, "steps": K, "warmup": W,
+            "ms_per_step": st["ms_per_pass"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": DTYPE, "data": "synthetic",
+            "config": {"workload": f"{total_layers}-layer MoE-only stack, T={T}, residual add between the blocks, "
+                                   f"{st['expert_bank_gb']:.1f} GB of expert banks, independent seeds per layer; "
+                                   "one step = one pass through all layers; value = tokens/s through the whole stack",
+                       "l2": "every layer's banks are read once per pass (banks far larger than L2)"},
+            "stack": st, "clocks": clocks}))
+        moe.close()
+        return
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    wl = Workload(pkg, moe, dense, dev, T, cycle, args.zipf is not None, path)
+    total_ms, launches = wl.time_block(K, W)
+    value = T * K / (total_ms * 1e-3)
+    step, xs, out = wl.step, wl.xs, wl.out
+    nlayers = cycle
 
     # end to end: every step's activations come from pinned host memory and its result goes back to pinned host
     # memory.  The copies run on a copy stream with two staging buffers each way, so the H2D of step i + 1 and the
@@ -292,23 +456,17 @@ def run_b200(args):
             out_host[b].copy_(out_dev[b], non_blocking=True)
             ev_d2h[b].record(copy_s)
 
-    def timed_e2e():
-        for i in range(W):
-            step_e2e(i)
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for i in range(K):
-            step_e2e(W + i)
-        torch.cuda.current_stream().wait_event(ev_d2h[(W + K - 1) & 1])    # the last result has reached the host buffer
-        e1.record()
-        barrier()
-        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
-        if world > 1:
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return float(ms.item())
-
-    e2e_ms = timed_e2e()
+    for i in range(W):
+        step_e2e(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(K):
+        step_e2e(W + i)
+    torch.cuda.current_stream().wait_event(ev_d2h[(W + K - 1) & 1])    # the last result has reached the host buffer
+    e1.record()
+    torch.cuda.synchronize()
+    e2e_ms = float(e0.elapsed_time(e1))
 
     # the same without any overlap: copy in, block, copy out on one stream
     def step_serial(i):
@@ -316,198 +474,95 @@ def run_b200(args):
         step(i, x=x_stage[0], o=out_dev[0])
         out_host[0].copy_(out_dev[0], non_blocking=True)
 
-    serial_ms = timed(step_serial, K, W)
-    e2e = {"value": world * T * K / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": T * HIDDEN * 2,
+    serial_ms = timed_steps(torch, step_serial, K, W)
+    e2e = {"value": T * K / (e2e_ms * 1e-3), "unit": UNIT_S, "h2d_bytes_per_step": T * HIDDEN * 2,
            "d2h_bytes_per_step": T * HIDDEN * 2,
            "how": "pinned host buffers; H2D of step i + 1 and D2H of step i on a copy stream (two staging buffers each "
                   "way) under the compute of the neighbouring step",
-           "serial_value": world * T * K / (serial_ms * 1e-3)}
+           "serial_value": T * K / (serial_ms * 1e-3)}
 
-    # per-kernel profile pass (CUDA events around every launch) for the roofline of the dominant kernel.
-    # The routed half runs alone here (serving call with the router's ids), so that the shared expert,
-    # which the whole block overlaps on a second stream, does not share the SMs with the timed kernels.
-    routed = []
-    for l in range(nlayers):
-        step(l)
-        torch.cuda.synchronize()
-        routed.append((ids.clone(), wts.clone()))
-    uniq = [int(torch.unique(i).numel()) for i, _ in routed]
-    reqs = [pkg.MoEDeviceRequest(l, HIDDEN, INTER, TOP_K, xs[l], routed[l][0], routed[l][1]) for l in range(nlayers)]
-    for i in range(W):
-        moe.grouped_moe_staged(reqs[i % nlayers], out, path=path)
-    moe.profile(True)
-    for i in range(K):
-        moe.grouped_moe_staged(reqs[i % nlayers], out, path=path)
-    prof = moe.profile_read()
-    moe.profile(False)
-    # the router and shared-expert kernels, each alone on the stream
-    moe.profile(True)
-    for i in range(K):
-        g, su, sd, sg = dense[i % nlayers]
-        moe.router(xs[i % nlayers], g)
-        moe.shared_expert(xs[i % nlayers], su, sd, sg)
-    prof.update(moe.profile_read())
-    moe.profile(False)
-    U = sum(uniq) / len(uniq)
-    pk = peaks()
-    gate_kind = "expert_gate_up" if "expert_gate_up" in prof else "grouped_gate_up"
-    g_ms, g_n = prof[gate_kind]
-    kernels = {k: {"us_per_launch": ms / n * 1e3, "launches": n} for k, (ms, n) in prof.items()}
-    if gate_kind == "expert_gate_up":
-        # decode kernels: bound by the HBM stream of the routed experts' weights
-        gu_bytes = U * GATE_UP_BYTES + T * HIDDEN * 2
-        # DRAM traffic per algorithmic byte of this kernel, from one ncu capture of it
-        # (dram__bytes_read + dram__bytes_write over one launch at T = 64)
-        NCU_TRAFFIC_RATIO = 1.042
-        achieved = gu_bytes / (g_ms / g_n * 1e-3) / 1e9
-        roofline = {"bound": "hbm", "kernel": gate_kind, "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                    "frac": achieved / pk["hbm_gbs"], "peak_source": pk["which"], "frac_of_nominal_8000": achieved / 8000.0,
-                    "traffic": NCU_TRAFFIC_RATIO * gu_bytes, "distinct_experts": U, "bytes_per_launch": gu_bytes,
-                    "us_per_launch": g_ms / g_n * 1e3, "kernels": kernels}
-    else:
-        # tcgen05 grouped GEMM: useful flops of the routes (padding of ragged groups not counted)
-        flops = T * TOP_K * 2.0 * HIDDEN * (2 * INTER)
-        achieved = flops / (g_ms / g_n * 1e-3) / 1e12
-        roofline = {"bound": "tensor", "kernel": gate_kind, "achieved": achieved, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
-                    "frac": achieved / pk["bf16_tflops"], "peak_source": pk["which"] + " (burst; sustained %.0f)" % pk["bf16_tflops_sustained"],
-                    "traffic": None, "distinct_experts": U, "flops_per_launch": flops, "us_per_launch": g_ms / g_n * 1e3,
-                    "kernels": kernels}
-        if "grouped_down" in prof:
-            d_ms, d_n = prof["grouped_down"]
-            dn = T * TOP_K * 2.0 * INTER * HIDDEN / (d_ms / d_n * 1e-3) / 1e12
-            roofline["down"] = {"achieved": dn, "frac": dn / pk["bf16_tflops"]}
-    if "expert_down" in prof:
-        d_ms, d_n = prof["expert_down"]
-        dn = (U * DOWN_BYTES) / (d_ms / d_n * 1e-3) / 1e9
-        roofline["down"] = {"achieved": dn, "frac": dn / pk["hbm_gbs"]}
-        both = (U * EXPERT_BYTES) / ((g_ms / g_n + d_ms / d_n) * 1e-3) / 1e9
-        roofline["expert_weights_gbs"] = both
-
-    # the sampler ran through the timed steps, the end-to-end steps and the per-kernel passes (all GPU-busy)
-    clocks = sampler.stop() if rank == 0 else None
+    prof, U = wl.profile(K, W)
+    roofline = roofline_of(prof, U, T, nlayers, pk)
 
     # the same steps replayed from one captured CUDA graph (one block per layer in the graph): what an engine
     # that captures its decode step gets; reported beside the eager numbers, not instead of them
     graph_info = None
-    if world == 1:
-        try:
-            side = torch.cuda.Stream()
-            side.wait_stream(torch.cuda.current_stream())
-            cg = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(cg, stream=side):
-                for l in range(nlayers):
-                    step(l)
-            reps = max(1, K // nlayers)
-            g_ms = timed(lambda i: cg.replay(), reps, 3)
-            moe.sync_status()
-            graph_info = {"layers_per_graph": nlayers, "replays": reps, "us_per_layer_step": g_ms / (reps * nlayers) * 1e3,
-                          "tokens_per_s": T * reps * nlayers / (g_ms * 1e-3)}
-        except Exception as exc:      # a failed capture must not lose the eager line
-            graph_info = {"error": str(exc)[:200]}
-
-    line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
-        "ms_per_step": total_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16 activations x NVFP4 (e2m1 + e4m3 block scales) weights, f32 accumulate", "data": "synthetic",
-        "config": {"workload": f"{'decode' if T <= 256 else 'prefill'} T={T} tokens/step, hidden {HIDDEN}, {EXPERTS} resident NVFP4 experts top-{TOP_K}, "
-                               f"bf16 shared expert {SHARED}, {'uniform' if args.zipf is None else f'Zipf({args.zipf})-skewed'} routing",
-                   "l2": f"inputs larger than L2: {nlayers} independently seeded layers "
-                         f"({nlayers * EXPERTS * EXPERT_BYTES / 1e6:.0f} MB of banks) cycled step by step",
-                   "timed_region": "whole block (router, routed experts, shared expert, combine), CUDA events"},
-        "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline, "clocks": clocks, "graph_replay": graph_info,
-    }
-
-    if args.sweep and world == 1:
-        sweep = {}
-        for t in (1, 8, 512, 2048):
-            if t > moe.max_tokens:
-                continue
-            xt = [pkg.synth.device_x(4000 + l, t, HIDDEN, dev) for l in range(nlayers)]
-            o2 = torch.empty((t, HIDDEN), dtype=torch.bfloat16, device=dev)
-
-            def st(i, t=t, xt=xt, o2=o2):
-                l = i % nlayers
-                g, su, sd, sg = dense[l]
-                moe.moe_block(l, xt[l], g, su, sd, sg, o2)
-            ms = timed(st, K, W)
-            sweep[f"T={t}"] = {"tokens_per_s": t * K / (ms * 1e-3), "us_per_step": ms / K * 1e3}
-        line["sweep"] = sweep
-
-    if rank == 0 and not args.no_cpu_baseline:
-        sample = min(T, 16)
-        tps, threads, sec = time_cpu(sample, 3, 1)
-        line["cpu_baseline"] = {"value": tps, "unit": UNIT, "cores": threads, "kind": "port",
-                                "sample": f"{sample} tokens of the same block per step, 3 steps, all host threads; "
-                                          f"C restatement of the reference's host path"}
-    if rank == 0:
-        print(json.dumps(line))
-    moe.close()
-    if world > 1:
-        dist.destroy_process_group()
-
-
-def run_stack(args, pkg, moe, dense, x0, dev, T, nlayers, path):
-    """One step = a pass through `nlayers` MoE blocks, x <- x + block(x) between them (the 40-layer stack of the
-    benchmark configs).  Prints one JSON line: tokens/s through the whole stack, eager and from one CUDA graph."""
-    import torch
-    out = torch.empty((T, HIDDEN), dtype=torch.bfloat16, device=dev)
-    xa, xb = torch.empty_like(x0), torch.empty_like(x0)
-
-    def stack_pass(i=0):
-        xa.copy_(x0)
-        cur, nxt = xa, xb
-        for l in range(nlayers):
-            g, su, sd, sg = dense[l]
-            moe.moe_block(l, cur, g, su, sd, sg, out, path=path)
-            torch.add(cur, out, out=nxt)
-            cur, nxt = nxt, cur
-        return cur
-
-    def timed(fn, steps, warmup):
-        for i in range(warmup):
-            fn(i)
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for i in range(steps):
-            fn(i)
-        e1.record()
-        torch.cuda.synchronize()
-        return e0.elapsed_time(e1)
-
-    W, K = max(3, args.warmup), max(1, args.steps)
-    last = stack_pass()
-    moe.sync_status()
-    finite = bool(torch.isfinite(last.float()).all())
-    rms = float(last.float().pow(2).mean().sqrt())
-    sampler = ClockSampler(dev.index or 0)
-    sampler.start()
-    ms = timed(stack_pass, K, W)
-    clocks = sampler.stop()
-    graph = None
     try:
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         cg = torch.cuda.CUDAGraph()
         with torch.cuda.graph(cg, stream=side):
-            stack_pass()
-        g_ms = timed(lambda i: cg.replay(), K, 3)
+            for l in range(nlayers):
+                step(l)
+        reps = max(1, K // nlayers)
+        g_ms = timed_steps(torch, lambda i: cg.replay(), reps, 3)
         moe.sync_status()
-        graph = {"ms_per_pass": g_ms / K, "tokens_per_s": T * K / (g_ms * 1e-3)}
-    except Exception as exc:
-        graph = {"error": str(exc)[:200]}
-    print(json.dumps({
-        "metric": METRIC, "value": T * K / (ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": K, "warmup": W,
-        "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16 activations x NVFP4 (e2m1 + e4m3 block scales) weights, f32 accumulate", "data": "synthetic",
-        "config": {"workload": f"{nlayers}-layer MoE-only stack, T={T}, residual add between the blocks, "
-                               f"{nlayers * EXPERTS * EXPERT_BYTES / 1e9:.1f} GB of expert banks, independent seeds per layer; "
-                               "one step = one pass through all layers; value = tokens/s through the whole stack",
-                   "l2": "every layer's banks are read once per pass (banks far larger than L2)",
-                   "residual_rms_after_last_layer": rms, "finite": finite},
-        "layer_steps_per_s": nlayers * K / (ms * 1e-3), "us_per_layer": ms / K / nlayers * 1e3,
-        "graph_replay": graph, "clocks": clocks,
-    }))
+        graph_info = {"layers_per_graph": nlayers, "replays": reps, "us_per_layer_step": g_ms / (reps * nlayers) * 1e3,
+                      "tokens_per_s": T * reps * nlayers / (g_ms * 1e-3)}
+    except Exception as exc:      # a failed capture must not lose the eager line
+        graph_info = {"error": str(exc)[:200]}
+
+    routing = "uniform" if args.zipf is None else f"Zipf({args.zipf})-skewed"
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT_S, "n_gpus": 1, "steps": K, "warmup": W,
+        "ms_per_step": total_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": DTYPE, "data": "synthetic",
+        "config": {"workload": f"{'decode' if T <= 256 else 'prefill'} T={T} tokens/step, hidden {HIDDEN}, {EXPERTS} resident NVFP4 "
+                               f"experts top-{TOP_K}, bf16 shared expert {SHARED}, {routing} routing",
+                   "l2": f"inputs larger than L2: {nlayers} independently seeded layers cycled step by step, "
+                         f"{nlayers * U * EXPERT_BYTES / 1e6:.0f} MB of routed expert bytes touched per cycle (L2 is 126 MB)",
+                   "timed_region": "whole block (router, routed experts, shared expert, combine), CUDA events"},
+        "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline, "graph_replay": graph_info,
+    }
+
+    if default_line:
+        # the other batch sizes the metric is quoted on.  Decode sizes cycle every resident layer so that the few
+        # experts a step touches are not served from L2; prefill sizes route with the Zipf(1.1) bias of config 3.
+        sweep = {}
+        dense_zipf = [pkg.synth.device_dense_weights(2000 + l, dev, zipf_alpha=1.1) for l in range(cycle)]
+        for t, zipf in ((1, None), (8, None), (512, 1.1), (2048, 1.1)):
+            nl = total_layers if zipf is None else cycle
+            w2 = Workload(pkg, moe, dense if zipf is None else dense_zipf, dev, t, nl, zipf is not None, 0)
+            k2 = K if t <= 64 else max(8, K // 2)
+            ms, _ = w2.time_block(k2, W)
+            entry = {"tokens_per_s": t * k2 / (ms * 1e-3), "ms_per_step": ms / k2, "layers_cycled": nl,
+                     "routing": "uniform" if zipf is None else f"Zipf({zipf}) bias through the router"}
+            p2, u2 = w2.profile(k2, W)
+            entry["roofline"] = roofline_of(p2, u2, t, nl, pk)
+            if t == 1:
+                try:
+                    side = torch.cuda.Stream()
+                    side.wait_stream(torch.cuda.current_stream())
+                    cg = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(cg, stream=side):
+                        for l in range(nl):
+                            w2.step(l)
+                    g_ms = timed_steps(torch, lambda i: cg.replay(), 3, 2)
+                    moe.sync_status()
+                    entry["graph_replay_us_per_step"] = g_ms / (3 * nl) * 1e3
+                except Exception as exc:
+                    entry["graph_replay_us_per_step"] = str(exc)[:120]
+            sweep[f"T={t}"] = entry
+            del w2
+        line["sweep"] = sweep
+        # config 4: the 40-layer stack (row globals 2^-6 / 2^-10 so that the residual stream stays O(1))
+        pkg.synth.set_global_bits_on_device(moe, 0, EXPERTS * total_layers, G_SMALL)
+        stack = {}
+        for t in (1, 2048):
+            x0 = pkg.synth.device_x(3500 + t, t, HIDDEN, dev)
+            stack[f"T={t}"] = measure_stack(torch, moe, dense, x0, total_layers, 0, max(4, K // 4), 3)
+        line["stack40"] = stack
+        pkg.synth.set_global_bits_on_device(moe, 0, EXPERTS * total_layers, G_ONE)
+
+    # the sampler ran through every timed region above (all GPU-busy)
+    line["clocks"] = sampler.stop()
+    if not args.no_cpu_baseline:
+        sample = min(T, 16)
+        tps, threads, sec = time_cpu(sample, 3, 1)
+        line["cpu_baseline"] = {"value": tps, "unit": UNIT_S, "cores": threads, "kind": "port",
+                                "sample": f"{sample} tokens of the same block per step, 3 steps, all host threads; "
+                                          f"C restatement of the reference's host path"}
+    print(json.dumps(line))
     moe.close()
 
 
@@ -553,20 +608,66 @@ def run_ep(args, pkg, dev, world, rank, local):
         g, su, sd, sg = dense[l]
         xin, dst = (xs[l] if x is None else x), (out if o is None else o)
         if p2p:
-            layer.forward_p2p(l, xin, g, su, sd, sg, dst, record=record)
-        elif record is None and chunks > 1:
-            layer.forward_overlapped(l, xin, g, su, sd, sg, dst, chunks=chunks)
-        else:
-            layer.forward(l, xin, g, su, sd, sg, dst, record=record)
+            return layer.forward_p2p(l, xin, g, su, sd, sg, dst, record=record)
+        if record is None and chunks > 1:
+            return layer.forward_overlapped(l, xin, g, su, sd, sg, dst, chunks=chunks)
+        return layer.forward(l, xin, g, su, sd, sg, dst, record=record)
 
     def barrier():
         dist.barrier()
         torch.cuda.synchronize()
 
     W, K = max(3, args.warmup), max(1, args.steps)
-    step(0)
+    ep_ids, _ = step(0)
     be.front.sync_status()
     be.owner.sync_status()
+
+    # Before anything is timed: (1) the expert-parallel result of rank 0's first 256 tokens against one adapter on
+    # this GPU that holds all 256 experts (the banks are regenerated from every owner's seed), and (2) the same
+    # 8192-token block on that one GPU alone, so that the N-GPU figure has a same-workload one-GPU reference.
+    parity = {"checked": False}
+    single_tps = None
+    if rank == 0:
+        solo = pkg.B200MoE(local, pkg.ExpertShapes(HIDDEN, INTER), EXPERTS * nlayers, experts=EXPERTS, layers=nlayers,
+                           top_k=TOP_K, shared_inter=SHARED, max_tokens=T)
+        for l in range(nlayers):
+            for r in range(world):
+                pkg.synth.fill_banks_on_device(solo, l, seed=1000 + 977 * r + l, experts=per, slot0=l * EXPERTS + r * per,
+                                               expert0=r * per)
+        n_chk = min(256, T)
+        want = torch.empty((n_chk, HIDDEN), dtype=torch.bfloat16, device=dev)
+        want_ids = torch.empty((n_chk, TOP_K), dtype=torch.int32, device=dev)
+        g, su, sd, sg = dense[0]
+        solo.moe_block(0, xs[0][:n_chk].contiguous(), g, su, sd, sg, want, ids_out=want_ids)
+        solo.sync_status()
+        got = out[:n_chk].float()
+        rel = float((got - want.float()).norm() / want.float().norm())
+        parity = {"checked": True, "tokens": n_chk, "ids_equal": bool(torch.equal(ep_ids[:n_chk], want_ids)),
+                  "parity_rel_l2": rel, "bar_rel_l2": 1e-2,
+                  "against": "one adapter on rank 0's GPU holding all experts, same seeded banks and inputs"}
+        o1 = torch.empty((T, HIDDEN), dtype=torch.bfloat16, device=dev)
+
+        def solo_step(i):
+            l = i % nlayers
+            g, su, sd, sg = dense[l]
+            solo.moe_block(l, xs[l], g, su, sd, sg, o1)
+        ms1 = timed_steps(torch, solo_step, max(4, K // 2), 3)
+        solo.sync_status()
+        single_tps = T * max(4, K // 2) / (ms1 * 1e-3)
+        solo.close()
+        del solo, o1
+        torch.cuda.empty_cache()
+    bad = torch.zeros((1,), device=dev)
+    if rank == 0 and not (parity["ids_equal"] and parity["parity_rel_l2"] <= 1e-2):
+        bad.fill_(1.0)
+    dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+    if float(bad.item()) != 0.0:
+        if rank == 0:
+            print(json.dumps({"error": "expert-parallel parity check failed", "ep": parity}))
+        be.close()
+        dist.destroy_process_group()
+        raise SystemExit(3)
+
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -688,7 +789,12 @@ def run_ep(args, pkg, dev, world, rank, local):
                        "l2": f"inputs larger than L2: {nlayers} layers cycled, {T * TOP_K} routes x 4 KB rows per step",
                        "timed_region": "whole block incl. both all-to-alls, CUDA events, max over ranks"},
             "gpu_launches": int(launches), "clocks": clocks,
-            "ep": {"exchange_note": exchange_note,"phases_of": "one step, marks after each phase" if p2p else "one step of the plain schedule (every phase waits for the one before)",
+            "ep": {"parity": parity, "parity_rel_l2": parity.get("parity_rel_l2"), "ids_equal": parity.get("ids_equal"),
+                   "single_gpu_same_block_tokens_per_s": single_tps,
+                   "efficiency_vs_1gpu": (world * T * K / (total_ms * 1e-3) / world / single_tps) if single_tps else None,
+                   "efficiency_note": "tokens/s per GPU of this run over tokens/s of the same 8192-token block on one GPU "
+                                      "with all 256 experts resident (rank 0, measured in this run before the timed steps)",
+                   "exchange_note": exchange_note,"phases_of": "one step, marks after each phase" if p2p else "one step of the plain schedule (every phase waits for the one before)",
                    "phases_ms_max_over_ranks": phases, "unpipelined_ms_per_step": sum(phases.values()),
                    "exchange_ms_unpipelined": phases["dispatch_a2a_ms"] + phases["return_a2a_ms"],
                    "max_routes_sent_off_rank": float(sent.item()),

@@ -4,20 +4,22 @@
 // src/domain/expert_kernel.rs:547-618, python/ferrum_kernel/nvfp4_moe.py:186-294), organised so
 // that every expert byte is read from HBM once per step however many tokens route to it:
 //
-//   plan      one CTA sorts the routes by slot (stable), cuts every slot's run into groups of at
-//             most 8 routes and writes the group list.  No host round trip: the expert kernels
-//             read the group count from device memory.
-//   permute   activations are copied once into a k-permuted bf16 matrix whose rows can be fetched
-//             with one bulk copy and read as tensor-core B fragments without bank conflicts.
-//   experts   persistent CTAs, one per SM, each owning a contiguous range of (group, row-block)
-//             items.  A producer warp streams the packed E2M1 rows and E4M3 scales of an item into
-//             a ring of shared-memory stages with bulk async copies (TMA engine, mbarrier
-//             completion); eight consumer warps read 128-bit fragments, dequantise in registers
-//             (bit-placement E2M1 -> bf16, times the block scale, exact) and feed
-//             mma.sync.m16n8k16 with the group's (<= 8) tokens as the N dimension, f32 accumulate.
-//             K is split across the warps of a row tile and reduced through shared memory.
-//             gate_up fuses global scale + silu(gate) * up and writes ic2 (bf16, k-permuted for the
-//             down pass); down fuses global scale and route weight and writes one f32 row per route.
+//   plan      one CTA sorts the routes by slot (counting sort), cuts every slot's run into groups of at
+//             most 8 routes and writes the group list.  No host round trip: the expert kernels read
+//             the group count from device memory.  Batches of more than 2048 routes take the multi-CTA
+//             permutation build of permute.cu and groups of 16.
+//   experts   persistent CTAs, one per SM, each owning a contiguous range of (group, row-block) items.
+//             Every warp is an independent worker on one item at a time: it issues the bulk async
+//             copies (TMA engine, mbarrier transaction count) of its own packed E2M1 rows and E4M3
+//             scales into a private double-buffered ring, reads 128-bit fragments from there, converts
+//             in registers with the hardware conversions (e2m1x2 -> f16x2, e4m3x2 -> f16x2; the product
+//             with the block scale is exact in f16) and feeds mma.sync.m16n8k16 with the group's tokens
+//             as the N dimension, f32 accumulate.  There is no producer warp and no cross-warp
+//             reduction; the warps of a CTA share only the group's activation tile (f16, scaled per
+//             token by a power of two, k-permuted so that B fragments are conflict-free 128-bit loads).
+//             gate_up pairs 8 gate rows with their 8 up rows in one tile, so global scale and
+//             silu(gate) * up are a per-thread epilogue that writes ic2 (f32); down applies global scale
+//             and route weight and writes one f32 row per route.
 //
 // The weights stay in the reference's bank layout (row-major packed nibbles, low nibble = even k).
 #include <cstdlib>
@@ -236,6 +238,15 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
     return v;
 }
+// The same MMA and shared load without `volatile`: the compiler may then move them freely between the
+// ordering points that matter (the mbarrier wait before a piece and the refill after it, both volatile
+// with a memory clobber), hoisting the next step's fragment loads above the current step's MMAs.
+__device__ __forceinline__ void mma_f16_free(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                             uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
 
 // Eight E2M1 codes of one packed word -> four f16x2, one hardware conversion per byte.  Byte b holds
 // k = 2b (low nibble, low half of the result) and k = 2b + 1.  The values 0, 0.5 .. 6 are exact.
@@ -288,6 +299,72 @@ struct ExpertArgs {
     int N, top_k;
 };
 
+// The group's activation tile: warp t converts token t (t, t + kWarps, ..) of the group into shared memory as
+// f16, scaled per token by a power of two so that its largest magnitude lies in [2^14, 2^15) (exact: f16 keeps
+// every bit of a bf16 input and 11 bits of an f32 one), in the k-permuted order of perm_k.  Also notes the
+// token's scale, route and (down projection) route weight.
+template <bool GATE_UP, int K, int kWarps>
+__device__ __forceinline__ void convert_group_tokens(const ExpertArgs& a, const int4 grp, uint8_t* xtile, int RSX,
+                                                     float* s_xscale, int* s_route, float* s_factor, int warp, int lane) {
+    for (int tk = warp; tk < grp.z; tk += kWarps) {
+        const int route = a.sorted_route[grp.y + tk];
+        const size_t row = GATE_UP ? (size_t)(route / a.top_k) : (size_t)route;
+        const bool is_bf16 = GATE_UP && a.act_dtype == 0;
+        // the lane's K / 32 values, eight consecutive k at a time, kept in registers
+        float v[K / 256][8];
+#pragma unroll
+        for (int c8 = 0; c8 < K / 256; c8++) {
+            const size_t k = row * K + c8 * 256 + lane * 8;
+            if (is_bf16) {
+                const uint4 u = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.act) + k);
+                const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    const float2 f = bf16x2_to_f32(w[q]);
+                    v[c8][2 * q] = f.x;
+                    v[c8][2 * q + 1] = f.y;
+                }
+            } else {
+                const float4 f0 = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.act) + k);
+                const float4 f1 = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.act) + k + 4);
+                v[c8][0] = f0.x; v[c8][1] = f0.y; v[c8][2] = f0.z; v[c8][3] = f0.w;
+                v[c8][4] = f1.x; v[c8][5] = f1.y; v[c8][6] = f1.z; v[c8][7] = f1.w;
+            }
+        }
+        float m = 0.f;
+#pragma unroll
+        for (int c8 = 0; c8 < K / 256; c8++)
+#pragma unroll
+            for (int q = 0; q < 8; q++) m = fmaxf(m, fabsf(v[c8][q]));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        // largest magnitude into [2^14, 2^15): exact power-of-two scaling, f16 keeps every bit of
+        // a bf16 input and 11 bits of an f32 one
+        const int e = (int)((__float_as_uint(m) >> 23) & 0xff);
+        float inv = 1.0f, sc = 1.0f;
+        if (e > 0 && e < 255) {
+            inv = __uint_as_float((uint32_t)(127 + 14 - (e - 127)) << 23);
+            sc = __uint_as_float((uint32_t)(127 - 14 + (e - 127)) << 23);
+        }
+        __half* xrow = reinterpret_cast<__half*>(xtile + (size_t)tk * RSX);
+#pragma unroll
+        for (int c8 = 0; c8 < K / 256; c8++) {
+            __half2 h[4];
+#pragma unroll
+            for (int q = 0; q < 4; q++) h[q] = __floats2half2_rn(v[c8][2 * q] * inv, v[c8][2 * q + 1] * inv);
+            // eight consecutive k are one 16-byte chunk of the k-permuted row
+            *reinterpret_cast<uint4*>(xrow + perm_k(c8 * 256 + lane * 8)) =
+                make_uint4(*reinterpret_cast<uint32_t*>(&h[0]), *reinterpret_cast<uint32_t*>(&h[1]),
+                           *reinterpret_cast<uint32_t*>(&h[2]), *reinterpret_cast<uint32_t*>(&h[3]));
+        }
+        if (lane == 0) {
+            s_xscale[tk] = sc;
+            s_route[tk] = route;
+            s_factor[tk] = GATE_UP ? 1.0f : a.route_weight[route];
+        }
+    }
+}
+
 // GATE_UP: K = hidden, a warp item is 8 gate rows and the 8 matching up rows, so that the
 // silu(gate) * up epilogue stays inside one thread; K is streamed in SUB pieces.  Otherwise
 // K = inter and a warp item is 16 consecutive rows in one piece.
@@ -339,7 +416,7 @@ struct ItemIter {
     }
 };
 
-template <bool GATE_UP, int K_, int NT, int OCC>
+template <bool GATE_UP, int K_, int NT, int OCC, int VAR>
 __global__ void __launch_bounds__(Cfg<GATE_UP, K_, NT>::kThreads, OCC) expert_mma_kernel(ExpertArgs a) {
     using C = Cfg<GATE_UP, K_, NT>;
     constexpr int kWarps = C::kWarps;
@@ -347,6 +424,7 @@ __global__ void __launch_bounds__(Cfg<GATE_UP, K_, NT>::kThreads, OCC) expert_mm
     constexpr int K = C::K, SUB = C::SUB, D = C::D, NSB = C::NSB, KSUB = C::KSUB, WIN = C::WIN, RSA = C::RSA, RSS = C::RSS,
                   RSX = C::RSX;
     extern __shared__ __align__(128) uint8_t smem[];
+    const uint32_t smem_base = smem_u32(smem);
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int g8 = lane >> 2, t4 = lane & 3;
     uint8_t* const wbase = smem + (size_t)warp * C::kWarpBytes;   // [2 stages | 2 scale buffers]
@@ -429,63 +507,7 @@ __global__ void __launch_bounds__(Cfg<GATE_UP, K_, NT>::kThreads, OCC) expert_mm
         const int4 grp = a.groups[g];
         // ---- the group's activation tile: warp t converts token t ----
         __syncthreads();  // every warp is done with the previous group's tile
-        for (int tk = warp; tk < grp.z; tk += kWarps) {
-            const int route = a.sorted_route[grp.y + tk];
-            const size_t row = GATE_UP ? (size_t)(route / a.top_k) : (size_t)route;
-            const bool is_bf16 = GATE_UP && a.act_dtype == 0;
-            // the lane's K / 32 values, eight consecutive k at a time, kept in registers
-            float v[K / 256][8];
-#pragma unroll
-            for (int c8 = 0; c8 < K / 256; c8++) {
-                const size_t k = row * K + c8 * 256 + lane * 8;
-                if (is_bf16) {
-                    const uint4 u = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.act) + k);
-                    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-                    for (int q = 0; q < 4; q++) {
-                        const float2 f = bf16x2_to_f32(w[q]);
-                        v[c8][2 * q] = f.x;
-                        v[c8][2 * q + 1] = f.y;
-                    }
-                } else {
-                    const float4 f0 = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.act) + k);
-                    const float4 f1 = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.act) + k + 4);
-                    v[c8][0] = f0.x; v[c8][1] = f0.y; v[c8][2] = f0.z; v[c8][3] = f0.w;
-                    v[c8][4] = f1.x; v[c8][5] = f1.y; v[c8][6] = f1.z; v[c8][7] = f1.w;
-                }
-            }
-            float m = 0.f;
-#pragma unroll
-            for (int c8 = 0; c8 < K / 256; c8++)
-#pragma unroll
-                for (int q = 0; q < 8; q++) m = fmaxf(m, fabsf(v[c8][q]));
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-            // largest magnitude into [2^14, 2^15): exact power-of-two scaling, f16 keeps every bit of
-            // a bf16 input and 11 bits of an f32 one
-            const int e = (int)((__float_as_uint(m) >> 23) & 0xff);
-            float inv = 1.0f, sc = 1.0f;
-            if (e > 0 && e < 255) {
-                inv = __uint_as_float((uint32_t)(127 + 14 - (e - 127)) << 23);
-                sc = __uint_as_float((uint32_t)(127 - 14 + (e - 127)) << 23);
-            }
-            __half* xrow = reinterpret_cast<__half*>(xtile + (size_t)tk * RSX);
-#pragma unroll
-            for (int c8 = 0; c8 < K / 256; c8++) {
-                __half2 h[4];
-#pragma unroll
-                for (int q = 0; q < 4; q++) h[q] = __floats2half2_rn(v[c8][2 * q] * inv, v[c8][2 * q + 1] * inv);
-                // eight consecutive k are one 16-byte chunk of the k-permuted row
-                *reinterpret_cast<uint4*>(xrow + perm_k(c8 * 256 + lane * 8)) =
-                    make_uint4(*reinterpret_cast<uint32_t*>(&h[0]), *reinterpret_cast<uint32_t*>(&h[1]),
-                               *reinterpret_cast<uint32_t*>(&h[2]), *reinterpret_cast<uint32_t*>(&h[3]));
-            }
-            if (lane == 0) {
-                s_xscale[tk] = sc;
-                s_route[tk] = route;
-                s_factor[tk] = GATE_UP ? 1.0f : a.route_weight[route];
-            }
-        }
+        convert_group_tokens<GATE_UP, K, kWarps>(a, grp, xtile, RSX, s_xscale, s_route, s_factor, warp, lane);
         __syncthreads();
 
         // ---- this warp's items of the group ----
@@ -516,21 +538,27 @@ __global__ void __launch_bounds__(Cfg<GATE_UP, K_, NT>::kThreads, OCC) expert_mm
                     dead = true;
                     break;
                 }
-                const uint32_t sp = smem_u32(wbase + (size_t)(n % D) * C::kStageBytes);
-                const uint32_t sc = smem_u32(wbase + D * C::kStageBytes + (size_t)((n / SUB) % NSB) * C::kScaleBytes);
-                const uint32_t row_lo = sp + g8 * RSA + t4 * 16, row_hi = row_lo + 8 * RSA;
-                const uint32_t sc_lo = sc + g8 * RSS + half * (KSUB / 16), sc_hi = sc_lo + 8 * RSS;
-                const uint32_t xa = smem_u32(xtile) + g8 * RSX + t4 * 16 + half * (KSUB * 2);
+                // byte offsets inside the CTA's shared memory of this lane's fragments
+                const uint32_t o_sp = (uint32_t)(warp * C::kWarpBytes + (n % D) * C::kStageBytes);
+                const uint32_t o_sc = (uint32_t)(warp * C::kWarpBytes + D * C::kStageBytes + ((n / SUB) % NSB) * C::kScaleBytes);
+                const uint32_t row_lo = o_sp + g8 * RSA + t4 * 16, row_hi = row_lo + 8 * RSA;
+                const uint32_t sc_lo = o_sc + g8 * RSS + half * (KSUB / 16), sc_hi = sc_lo + 8 * RSS;
+                const uint32_t xa = (uint32_t)(kWarps * C::kWarpBytes) + g8 * RSX + t4 * 16 + half * (KSUB * 2);
+                // VAR bit 0: ordinary loads and a non-volatile MMA, which the compiler may reorder inside the piece
+                auto LD = [&](uint32_t off) -> uint4 {
+                    if (VAR & 1) return *reinterpret_cast<const uint4*>(smem + off);
+                    return lds128(smem_base + off);
+                };
                 {
 #pragma unroll
                     for (int w2 = 0; w2 < WIN / 2; w2++) {
                         // scales of two windows: 16 bytes per row
-                        const uint4 sl4 = lds128(sc_lo + w2 * 16), sh4 = lds128(sc_hi + w2 * 16);
+                        const uint4 sl4 = LD(sc_lo + w2 * 16), sh4 = LD(sc_hi + w2 * 16);
                         const uint32_t slw[4] = {sl4.x, sl4.y, sl4.z, sl4.w}, shw[4] = {sh4.x, sh4.y, sh4.z, sh4.w};
 #pragma unroll
                         for (int wq = 0; wq < 2; wq++) {
                             const int wi = w2 * 2 + wq;
-                            const uint4 plo = lds128(row_lo + wi * 64), phi = lds128(row_hi + wi * 64);
+                            const uint4 plo = LD(row_lo + wi * 64), phi = LD(row_hi + wi * 64);
                             // the lane's two scale bytes of this window: bytes 2*t4, 2*t4+1 of the window's eight
                             const uint32_t wl2 = (t4 & 2) ? slw[wq * 2 + 1] : slw[wq * 2];
                             const uint32_t wh2 = (t4 & 2) ? shw[wq * 2 + 1] : shw[wq * 2];
@@ -539,6 +567,14 @@ __global__ void __launch_bounds__(Cfg<GATE_UP, K_, NT>::kThreads, OCC) expert_mm
                             e4m3x2_to_f16_scales((t4 & 1) ? (wh2 >> 16) : (wh2 & 0xffffu), shi0, shi1);
                             const uint32_t wl[4] = {plo.x, plo.y, plo.z, plo.w};
                             const uint32_t wh[4] = {phi.x, phi.y, phi.z, phi.w};
+                            // VAR bit 1: the window's activation fragments are requested before its conversions
+                            uint4 xpre[NT][4];
+                            if (VAR & 2) {
+#pragma unroll
+                                for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+                                    for (int j = 0; j < 4; j++) xpre[nt][j] = LD(xa + nt * 8 * RSX + wi * 256 + j * 64);
+                            }
 #pragma unroll
                             for (int j = 0; j < 4; j++) {
                                 uint32_t ql[4], qh[4];
@@ -554,9 +590,14 @@ __global__ void __launch_bounds__(Cfg<GATE_UP, K_, NT>::kThreads, OCC) expert_mm
                                 // the dequantised fragments serve every token tile of the group
 #pragma unroll
                                 for (int nt = 0; nt < NT; nt++) {
-                                    const uint4 xb = lds128(xa + nt * 8 * RSX + wi * 256 + j * 64);
-                                    mma_f16(acc[nt][(j & 1) * 2], ql[0], qh[0], ql[1], qh[1], xb.x, xb.y);
-                                    mma_f16(acc[nt][(j & 1) * 2 + 1], ql[2], qh[2], ql[3], qh[3], xb.z, xb.w);
+                                    const uint4 xb = (VAR & 2) ? xpre[nt][j] : LD(xa + nt * 8 * RSX + wi * 256 + j * 64);
+                                    if (VAR & 1) {
+                                        mma_f16_free(acc[nt][(j & 1) * 2], ql[0], qh[0], ql[1], qh[1], xb.x, xb.y);
+                                        mma_f16_free(acc[nt][(j & 1) * 2 + 1], ql[2], qh[2], ql[3], qh[3], xb.z, xb.w);
+                                    } else {
+                                        mma_f16(acc[nt][(j & 1) * 2], ql[0], qh[0], ql[1], qh[1], xb.x, xb.y);
+                                        mma_f16(acc[nt][(j & 1) * 2 + 1], ql[2], qh[2], ql[3], qh[3], xb.z, xb.w);
+                                    }
                                 }
                             }
                         }
@@ -598,20 +639,212 @@ __global__ void __launch_bounds__(Cfg<GATE_UP, K_, NT>::kThreads, OCC) expert_mm
     }
 }
 
+// ------------------------------------------------------------------------------------------
+// the expert kernel, register-streaming form
+//
+// Same items, same fragments, same arithmetic and epilogue as expert_mma_kernel, but no shared-memory
+// ring: every lane fetches its own fragments of the packed rows straight from global memory with 128-bit
+// loads (a warp-wide load covers 8 rows x 64 contiguous bytes) and its block scales with 32-bit loads,
+// kPre windows ahead of the window it is converting, in a rotating register buffer.  Nothing waits on a
+// barrier, the only shared memory is the group's activation tile, so two CTAs (16 warps) fit an SM and
+// the conversions of one warp run under the memory latency of the others.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint4 ldg_stream128(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.L2::128B.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint32_t ldg_u32(const void* p) {
+    uint32_t v;
+    asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+
+template <bool GATE_UP, int K_, int NT_>
+struct LdgCfg {
+    static constexpr int K = K_, NT = NT_;
+    static constexpr int kWarps = 8, kThreads = 256;
+    static constexpr int WINS = K / 128;
+    static constexpr int kPre = WINS < 4 ? WINS : 4;     // windows in flight per warp
+    static constexpr int RSX = K * 2 + 64;
+    static constexpr int kXBytes = kGroupTokens * NT * RSX;
+    static constexpr size_t kSmem = (size_t)kXBytes + 96 * NT + 32;
+};
+
+template <bool GATE_UP, int K_, int NT, int OCC>
+__global__ void __launch_bounds__(256, OCC) expert_ldg_kernel(ExpertArgs a) {
+    using C = LdgCfg<GATE_UP, K_, NT>;
+    constexpr int kWarps = C::kWarps, kTok = kGroupTokens * NT, K = C::K, WINS = C::WINS, P = C::kPre, RSX = C::RSX;
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int g8 = lane >> 2, t4 = lane & 3;
+    uint8_t* const xtile = smem;
+    float* const s_xscale = reinterpret_cast<float*>(xtile + C::kXBytes);
+    float* const s_factor = s_xscale + kTok;
+    int* const s_route = reinterpret_cast<int*>(s_factor + kTok);
+    pdl_launch_dependents();
+    pdl_wait();     // the plan (groups, sorted routes) and, for the down kernel, ic2
+
+    const int n_groups = *a.n_groups;
+    const int blocks = (GATE_UP ? a.N / 2 : a.N) / (GATE_UP ? 8 : 16);
+    const long long total = (long long)n_groups * blocks;
+    const int ib = (int)(total * blockIdx.x / gridDim.x);
+    const int ie = (int)(total * (blockIdx.x + 1) / gridDim.x);
+    if (ib >= ie) return;
+    ItemIter cur;
+    cur.start(ib, ie, blocks, warp, kWarps);
+    const int g_first = ib / blocks, g_last = (ie - 1) / blocks;
+    for (int g = g_first; g <= g_last; g++) {
+        const int4 grp = a.groups[g];
+        __syncthreads();  // every warp is done with the previous group's tile
+        convert_group_tokens<GATE_UP, K, kWarps>(a, grp, xtile, RSX, s_xscale, s_route, s_factor, warp, lane);
+        __syncthreads();
+        const int seg_end = min(ie, (g + 1) * blocks);
+        while (cur.valid() && cur.g == g && cur.it < seg_end) {
+            const int blk = cur.it % blocks;
+            const size_t slot_rows = (size_t)grp.x * a.N;
+            // rows g8 (fragment rows 0..7) and g8 + 8 of the tile
+            const size_t r_lo = slot_rows + (GATE_UP ? blk * 8 + g8 : blk * 16 + g8);
+            const size_t r_hi = slot_rows + (GATE_UP ? a.N / 2 + blk * 8 + g8 : blk * 16 + 8 + g8);
+            const uint8_t* const p_lo = a.packed + r_lo * (size_t)(K / 2) + t4 * 16;
+            const uint8_t* const p_hi = a.packed + r_hi * (size_t)(K / 2) + t4 * 16;
+            // the lane's two scale bytes of a window are bytes 2*t4, 2*t4+1 of the window's eight
+            const uint8_t* const s_lo = a.scale + r_lo * (size_t)(K / 16) + (t4 >> 1) * 4;
+            const uint8_t* const s_hi = a.scale + r_hi * (size_t)(K / 16) + (t4 >> 1) * 4;
+            uint4 bl[P], bh[P];
+            uint32_t cl[P], ch[P];
+#pragma unroll
+            for (int p = 0; p < P; p++) {
+                bl[p] = ldg_stream128(p_lo + p * 64);
+                bh[p] = ldg_stream128(p_hi + p * 64);
+                cl[p] = ldg_u32(s_lo + p * 8);
+                ch[p] = ldg_u32(s_hi + p * 8);
+            }
+            const uint16_t graw_a = a.global[r_lo], graw_b = a.global[r_hi];
+            float acc[NT][4][4];
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+                for (int q = 0; q < 4; q++)
+#pragma unroll
+                    for (int r = 0; r < 4; r++) acc[nt][q][r] = 0.f;
+            const uint8_t* const xa = xtile + g8 * RSX + t4 * 16;
+#pragma unroll
+            for (int wi = 0; wi < WINS; wi++) {
+                const int sl = wi % P;
+                const uint4 plo = bl[sl], phi = bh[sl];
+                const uint32_t wl2 = cl[sl], wh2 = ch[sl];
+                if (wi + P < WINS) {   // refill the slot with the window kPre ahead
+                    bl[sl] = ldg_stream128(p_lo + (wi + P) * 64);
+                    bh[sl] = ldg_stream128(p_hi + (wi + P) * 64);
+                    cl[sl] = ldg_u32(s_lo + (wi + P) * 8);
+                    ch[sl] = ldg_u32(s_hi + (wi + P) * 8);
+                }
+                uint32_t slo0, slo1, shi0, shi1;
+                e4m3x2_to_f16_scales((t4 & 1) ? (wl2 >> 16) : (wl2 & 0xffffu), slo0, slo1);
+                e4m3x2_to_f16_scales((t4 & 1) ? (wh2 >> 16) : (wh2 & 0xffffu), shi0, shi1);
+                const uint32_t wl[4] = {plo.x, plo.y, plo.z, plo.w};
+                const uint32_t wh[4] = {phi.x, phi.y, phi.z, phi.w};
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    uint32_t ql[4], qh[4];
+                    e2m1x8_to_f16x2(wl[j], ql);
+                    e2m1x8_to_f16x2(wh[j], qh);
+                    const uint32_t s0 = (j < 2) ? slo0 : slo1, s1 = (j < 2) ? shi0 : shi1;
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        ql[q] = hmul2_f16(ql[q], s0);
+                        qh[q] = hmul2_f16(qh[q], s1);
+                    }
+#pragma unroll
+                    for (int nt = 0; nt < NT; nt++) {
+                        const uint4 xb = *reinterpret_cast<const uint4*>(xa + nt * 8 * RSX + wi * 256 + j * 64);
+                        mma_f16_free(acc[nt][(j & 1) * 2], ql[0], qh[0], ql[1], qh[1], xb.x, xb.y);
+                        mma_f16_free(acc[nt][(j & 1) * 2 + 1], ql[2], qh[2], ql[3], qh[3], xb.z, xb.w);
+                    }
+                }
+            }
+            // ---- epilogue: rows g8 (acc[.][0..1]) and g8 + 8 (acc[.][2..3]), tokens 2*t4, 2*t4 + 1 ----
+            const float ga = f16_global_to_f32(graw_a), gb = f16_global_to_f32(graw_b);
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                float c4[4];
+#pragma unroll
+                for (int r = 0; r < 4; r++) c4[r] = (acc[nt][0][r] + acc[nt][1][r]) + (acc[nt][2][r] + acc[nt][3][r]);
+#pragma unroll
+                for (int c = 0; c < 2; c++) {
+                    const int tok = nt * 8 + 2 * t4 + c;
+                    if (tok < grp.z) {
+                        const float ts = s_xscale[tok];
+                        const int route = s_route[tok];
+                        if (GATE_UP) {
+                            const float gate = c4[c] * ga * ts, up = c4[2 + c] * gb * ts;
+                            a.ic2[(size_t)route * (a.N / 2) + blk * 8 + g8] = (gate / (1.0f + __expf(-gate))) * up;
+                        } else {
+                            const float wr = s_factor[tok];
+                            a.yroute[(size_t)route * a.N + blk * 16 + g8] = wr * ((c4[c] * ts) * ga);
+                            a.yroute[(size_t)route * a.N + blk * 16 + 8 + g8] = wr * ((c4[2 + c] * ts) * gb);
+                        }
+                    }
+                }
+            }
+            cur.next(ib);
+        }
+    }
+}
+
+template <bool GATE_UP, int K_, int NT, int OCC>
+void launch_expert_ldg(ExpertArgs a, int sm_count, cudaStream_t s, bool pdl) {
+    using C = LdgCfg<GATE_UP, K_, NT>;
+    static PerDeviceOnce once;
+    allow_dyn_smem(once, expert_ldg_kernel<GATE_UP, K_, NT, OCC>, C::kSmem);
+    if (pdl)
+        launch_pdl(expert_ldg_kernel<GATE_UP, K_, NT, OCC>, dim3(sm_count * OCC), dim3(C::kThreads), C::kSmem, s, a);
+    else
+        expert_ldg_kernel<GATE_UP, K_, NT, OCC><<<sm_count * OCC, C::kThreads, C::kSmem, s>>>(a);
+}
+
 // latency-bound steps (a handful of tokens) chain their kernels with programmatic dependent launch: measured
 // 49 -> 43 us per block at one token; at 64 tokens the early-resident CTAs only get in the way of the shared
 // expert that runs beside them, so larger steps launch the ordinary way
 constexpr int kPdlMaxRoutes = 128;
+constexpr int kDefaultVariant = 0;
+
+template <bool GATE_UP, int K_, int NT, int OCC, int VAR>
+void launch_expert_var(ExpertArgs a, int sm_count, cudaStream_t s, bool pdl) {
+    using C = Cfg<GATE_UP, K_, NT>;
+    static PerDeviceOnce once;   // one per instantiation
+    allow_dyn_smem(once, expert_mma_kernel<GATE_UP, K_, NT, OCC, VAR>, C::kSmem);
+    if (pdl)
+        launch_pdl(expert_mma_kernel<GATE_UP, K_, NT, OCC, VAR>, dim3(sm_count * OCC), dim3(C::kThreads), C::kSmem, s, a);
+    else
+        expert_mma_kernel<GATE_UP, K_, NT, OCC, VAR><<<sm_count * OCC, C::kThreads, C::kSmem, s>>>(a);
+}
+
+// instruction-scheduling variant of the expert kernels (see VAR in the kernel); FTM_DECODE_VARIANT overrides
+// the default for experiments
+int decode_variant() {
+    static const int v = [] {
+        const char* e = getenv("FTM_DECODE_VARIANT");
+        return e ? atoi(e) & 7 : kDefaultVariant;
+    }();
+    return v;
+}
 
 template <bool GATE_UP, int K_, int NT, int OCC>
 void launch_expert(ExpertArgs a, int sm_count, cudaStream_t s, bool pdl) {
-    using C = Cfg<GATE_UP, K_, NT>;
-    static PerDeviceOnce once;   // one per instantiation
-    allow_dyn_smem(once, expert_mma_kernel<GATE_UP, K_, NT, OCC>, C::kSmem);
-    if (pdl)
-        launch_pdl(expert_mma_kernel<GATE_UP, K_, NT, OCC>, dim3(sm_count * OCC), dim3(C::kThreads), C::kSmem, s, a);
-    else
-        expert_mma_kernel<GATE_UP, K_, NT, OCC><<<sm_count * OCC, C::kThreads, C::kSmem, s>>>(a);
+    if (decode_variant() & 4) {   // register-streaming kernels, two CTAs per SM
+        launch_expert_ldg<GATE_UP, K_, NT, 2>(a, sm_count, s, pdl);
+        return;
+    }
+    switch (decode_variant()) {
+        case 1: launch_expert_var<GATE_UP, K_, NT, OCC, 1>(a, sm_count, s, pdl); break;
+        case 2: launch_expert_var<GATE_UP, K_, NT, OCC, 2>(a, sm_count, s, pdl); break;
+        case 3: launch_expert_var<GATE_UP, K_, NT, OCC, 3>(a, sm_count, s, pdl); break;
+        default: launch_expert_var<GATE_UP, K_, NT, OCC, 0>(a, sm_count, s, pdl); break;
+    }
 }
 
 // Large batches: the routes are bucketed by the multi-CTA CSR build (seg / route_idx); this turns every

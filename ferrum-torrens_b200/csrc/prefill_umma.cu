@@ -8,19 +8,21 @@
 //
 //   gather    the routes are sorted by expert (CSR); xg[i] = f16(x[token of route_idx[i]] * 2^-e) with a
 //             per-row power-of-two scale (exact, keeps any bf16 / f32 input inside the f16 range)
-//   gemm      D[128 weight rows, n tokens] per unit = (pass of <= 128 sorted rows of one expert, tile of
-//             128 weight rows); persistent CTAs, 16 warps:
-//               warp 0      TMA: activation tiles [128 tokens x 64 k] f16, 128-byte swizzle (B operand)
-//               warp 2      TMA: packed weight rows (256 k = one 128-byte line per row, 128-byte swizzle)
-//                           and block scales into a raw ring
-//               warps 8..23 dequantise (hardware e2m1x2 / e4m3x2 -> f16x2, exact product with the block
-//                           scale) and store the f16 weights into tensor memory (tcgen05.st): they are the
-//                           A operand, one TMEM lane per weight row, so the dequantised weights never
-//                           cross shared memory
-//               warps 1, 3  issue tcgen05.mma, one warp per row tile (M = 128, N = tokens rounded up to
-//                           16, K = 16 per instruction, f16 x f16 -> f32 in TMEM), commit to mbarriers
-//               warps 4..7  epilogue: tcgen05.ld of one of two accumulator sets while the next unit's
-//                           mainloop runs; a thread owns a weight row, so stores are coalesced over rows
+//   gemm      unit = (pass of <= 128 sorted rows of one expert, 256 weight rows = two tiles of 128);
+//             persistent CTAs of 28 warps:
+//               warp 0       TMA: activation tiles [32..128 tokens x 64 k] f16, 128-byte swizzle (B operand)
+//               warp 2       TMA: packed weight rows (256 k = one 128-byte line per row, 128-byte swizzle)
+//                            and block scales into a raw ring
+//               warps 8..23  four dequantiser sets of four warps: hardware e2m1x2 / e4m3x2 -> f16x2, exact
+//                            product with the block scale, stored into tensor memory (tcgen05.st).  The
+//                            weights are the A operand, one TMEM lane per weight row, so the dequantised
+//                            weights never cross shared memory
+//               warps 1, 3   issue tcgen05.mma (TS form), one warp per row tile (M = 128, N = tokens
+//                            rounded up to 16, K = 16 per instruction, f16 x f16 -> f32 in TMEM), commit
+//                            to mbarriers
+//               warps 4..7, 24..27  epilogue, one set per row tile: tcgen05.ld of the accumulators while
+//                            the next unit's mainloop runs; a thread owns a weight row, so stores are
+//                            coalesced over rows
 //             gate_up writes gate and up (globals and row scale applied) as f32; down applies global,
 //             row scale and route weight and writes one row per route (bf16, or f32 for f32 outputs).
 //   rescale   silu(gate) * up -> f16 with a per-route power-of-two scale, between the two GEMMs
@@ -188,7 +190,7 @@ struct UmmaArgs {
     int N;                     // rows of the weight matrix (2 * inter or hidden)
 };
 
-// warp roles of the GEMM CTA (24 warps)
+// warp roles of the GEMM CTA (28 warps)
 constexpr int kWarpActTma = 0, kWarpMma = 1, kWarpRawTma = 2, kWarpMma1 = 3, kWarpEpi0 = 4, kWarpDeq0 = 8;
 constexpr int kEpiWarps = 8;          // warps 4..7 read row tile 0, warps 24..27 row tile 1
 constexpr int kWarpEpi1 = 24;

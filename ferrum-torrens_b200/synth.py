@@ -138,6 +138,15 @@ def fill_banks_on_device(moe, layer: int, seed: int, experts: int | None = None,
         moe.adopt(layer, expert0 + e, slot0 + e)
 
 
+def set_global_bits_on_device(moe, slot0: int, slots: int, global_bits=(0x3C00, 0x3C00)):
+    """Overwrites the f16 row globals of `slots` slots starting at slot0 (gate_up, down bit patterns)."""
+    import torch
+    banks = moe.bank_tensors()
+    for b in (2, 5):
+        banks[b][slot0:slot0 + slots].view(torch.int16).fill_(global_bits[b // 3])
+    torch.cuda.synchronize()
+
+
 def device_dense_weights(seed: int, device, hidden: int = 2048, experts: int = 256, shared_inter: int = 512,
                          zipf_alpha: float | None = None):
     """Router and shared-expert weights as bf16 CUDA tensors: (gate_w, sh_gate_up, sh_down, sh_gate)."""
