@@ -96,6 +96,10 @@ struct ftm_handle {
 
     size_t row_bytes[FTM_NUM_BANKS]{};
     void* banks[FTM_NUM_BANKS]{};
+    // the block scales of both projections once more, in the order the decode kernels' lanes read them
+    // (same bytes, reordered by launch_scale_repack whenever a slot is loaded); null for shapes those
+    // kernels do not take
+    void* scale_frag[2]{};
     bool resident = false;
 
     std::vector<int32_t> slot_for_id;  // host mirror, [layers * experts]
@@ -179,6 +183,17 @@ int dev_alloc(ftm_handle* h, T** out, size_t count) {
     return FTM_OK;
 }
 
+void free_banks(ftm_handle* h) {
+    for (int b = 0; b < FTM_NUM_BANKS; b++) {
+        if (h->banks[b]) cudaFree(h->banks[b]);
+        h->banks[b] = nullptr;
+    }
+    for (int q = 0; q < 2; q++) {
+        if (h->scale_frag[q]) cudaFree(h->scale_frag[q]);
+        h->scale_frag[q] = nullptr;
+    }
+}
+
 int alloc_banks(ftm_handle* h) {
     for (int b = 0; b < FTM_NUM_BANKS; b++) {
         size_t bytes = h->row_bytes[b] * (size_t)h->cfg.slots;
@@ -190,6 +205,16 @@ int alloc_banks(ftm_handle* h) {
             }
             h->banks[b] = nullptr;
             return cuda_fail(h, e, "cudaMalloc(expert bank)");
+        }
+    }
+    // fragment-ordered scale copies (11 % more device memory) for the shapes the decode kernels take
+    if (h->cfg.hidden % 512 == 0 && h->cfg.inter % 512 == 0) {
+        for (int q = 0; q < 2; q++) {
+            cudaError_t e = cudaMalloc(&h->scale_frag[q], h->row_bytes[q ? 4 : 1] * (size_t)h->cfg.slots);
+            if (e != cudaSuccess) {
+                free_banks(h);
+                return cuda_fail(h, e, "cudaMalloc(expert scale copy)");
+            }
         }
     }
     h->resident = true;
@@ -204,6 +229,8 @@ BankView bank_view(const ftm_handle* h) {
     v.dn_packed = (const uint8_t*)h->banks[3];
     v.dn_scale = (const uint8_t*)h->banks[4];
     v.dn_global = (const uint16_t*)h->banks[5];
+    v.gu_scale_frag = (const uint8_t*)h->scale_frag[0];
+    v.dn_scale_frag = (const uint8_t*)h->scale_frag[1];
     v.hidden = h->cfg.hidden;
     v.inter = h->cfg.inter;
     v.slots = h->cfg.slots;
@@ -418,8 +445,7 @@ FTM_API void ftm_destroy(ftm_handle* h) {
     DeviceGuard dg(h->cfg.ordinal);
     cudaDeviceSynchronize();
     for (void* p : h->allocs) cudaFree(p);
-    for (int b = 0; b < FTM_NUM_BANKS; b++)
-        if (h->banks[b]) cudaFree(h->banks[b]);
+    free_banks(h);
     if (h->aux) cudaStreamDestroy(h->aux);
     if (h->ev_fork) cudaEventDestroy(h->ev_fork);
     if (h->ev_join) cudaEventDestroy(h->ev_join);
@@ -449,6 +475,11 @@ static int load_common(ftm_handle* h, int32_t layer, int32_t expert, int32_t slo
         uint8_t* dst = (uint8_t*)h->banks[b] + (size_t)slot * h->row_bytes[b];
         if (fields[b] == dst) continue;  // the bytes were written in place through ftm_bank_ptrs
         CU(h, cudaMemcpyAsync(dst, fields[b], lens[b], kind, h->stream));
+    }
+    if (h->scale_frag[0]) {
+        h->launches += launch_scale_repack(bank_view(h), slot, (uint8_t*)h->scale_frag[0], (uint8_t*)h->scale_frag[1],
+                                           h->ctx(h->stream));
+        CU(h, cudaGetLastError());
     }
     // residency: the slot's previous occupant leaves, the expert's previous slot empties
     const int32_t id = layer * h->cfg.experts + expert;
@@ -489,10 +520,7 @@ FTM_API int ftm_release_banks(ftm_handle* h) {
     DeviceGuard dg(h->cfg.ordinal);
     if (!h->resident) return FTM_OK;
     CU(h, cudaDeviceSynchronize());
-    for (int b = 0; b < FTM_NUM_BANKS; b++) {
-        CU(h, cudaFree(h->banks[b]));
-        h->banks[b] = nullptr;
-    }
+    free_banks(h);
     h->resident = false;
     clear_residency(h);
     CU(h, cudaMemset(h->d_slot_for_id, 0xff, h->slot_for_id.size() * sizeof(int32_t)));

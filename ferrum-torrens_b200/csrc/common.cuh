@@ -75,6 +75,10 @@ struct BankView {
     const uint8_t* dn_packed;  // [slots, H, I/2]
     const uint8_t* dn_scale;   // [slots, H, I/16]
     const uint16_t* dn_global; // [slots, H]
+    // the block scales once more, in the order the decode kernels' lanes consume them (see decode_mma.cu,
+    // "fragment-ordered scales"); null when the adapter keeps no such copy
+    const uint8_t* gu_scale_frag = nullptr;  // [slots, 2I * H / 16]
+    const uint8_t* dn_scale_frag = nullptr;  // [slots, H * I / 16]
     int hidden, inter, slots;
 };
 

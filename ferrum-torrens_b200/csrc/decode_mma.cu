@@ -286,6 +286,7 @@ constexpr int kGroupTokens = 8;
 struct ExpertArgs {
     const uint8_t* packed;      // bank base [slots, N, K/2]
     const uint8_t* scale;       // [slots, N, K/16]
+    const uint8_t* scale_frag;  // the same scales in fragment order (register-streaming kernel), or null
     const uint16_t* global;     // [slots, N]
     const void* act;            // gate_up: the layer input [tokens, K] (bf16 or f32); down: ic2 f32 [routes, K]
     int act_dtype;
@@ -656,6 +657,19 @@ __device__ __forceinline__ uint4 ldg_stream128(const void* p) {
                  : "l"(p));
     return v;
 }
+// the same with a 256-byte L2 fill: a miss brings the row's next three 64-byte windows along
+__device__ __forceinline__ uint4 ldg_stream128_wide(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.L2::256B.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint4 ldg_nc128(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
 __device__ __forceinline__ uint32_t ldg_u32(const void* p) {
     uint32_t v;
     asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(v) : "l"(p));
@@ -673,7 +687,7 @@ struct LdgCfg {
     static constexpr size_t kSmem = (size_t)kXBytes + 96 * NT + 32;
 };
 
-template <bool GATE_UP, int K_, int NT, int OCC>
+template <bool GATE_UP, int K_, int NT, int OCC, int LV>
 __global__ void __launch_bounds__(256, OCC) expert_ldg_kernel(ExpertArgs a) {
     using C = LdgCfg<GATE_UP, K_, NT>;
     constexpr int kWarps = C::kWarps, kTok = kGroupTokens * NT, K = C::K, WINS = C::WINS, P = C::kPre, RSX = C::RSX;
@@ -693,8 +707,53 @@ __global__ void __launch_bounds__(256, OCC) expert_ldg_kernel(ExpertArgs a) {
     const int ib = (int)(total * blockIdx.x / gridDim.x);
     const int ie = (int)(total * (blockIdx.x + 1) / gridDim.x);
     if (ib >= ie) return;
+
+    // this lane's fragment rows of an item: rows g8 and g8 + 8 of the tile, as row indices into the bank (they
+    // fit 32 bits; the 64-bit addresses are formed where they are used, which keeps the register count down)
+    auto rows_of = [&](int slot, int it, int& r_lo, int& r_hi) {
+        const int blk = it % blocks;
+        const int slot_rows = slot * a.N;
+        r_lo = slot_rows + (GATE_UP ? blk * 8 + g8 : blk * 16 + g8);
+        r_hi = slot_rows + (GATE_UP ? a.N / 2 + blk * 8 + g8 : blk * 16 + 8 + g8);
+    };
+    uint4 bl[P], bh[P];
+    uint32_t cl[P], ch[P];
+    // LV bit 0: the scales of two windows (16 bytes per row) come with one 128-bit load per row instead of a
+    // 32-bit load per row and window: half the requests to the L1, where a load that touches eight rows costs
+    // eight tag look-ups whatever its width.  LV bit 1: 256-byte L2 fill on the packed rows.
+    // LV bit 2: fragment-ordered scales.  The adapter keeps a second copy of every expert's block scales in
+    // the order this kernel's lanes consume them: for tile t of a slot and every group of four windows
+    // (512 k), 32 lanes x 16 bytes, lane (g8, t4) holding for each of the four windows the two scale bytes
+    // of its low row (blocks 2*t4, 2*t4 + 1 of the window) and the two of its high row.  One fully coalesced
+    // 128-bit load per lane then serves four windows of both rows: a quarter of a load instruction and one
+    // L1 tag look-up per window instead of two loads that each touch eight rows.
+    constexpr bool kFragScales = (LV & 4) != 0;
+    constexpr bool kPairScales = (LV & 1) != 0 && !kFragScales;
+    constexpr int kGroups = WINS / 4;     // groups of four windows per item
+    uint4 dl[P / 2 > 0 ? P / 2 : 1], dh[P / 2 > 0 ? P / 2 : 1];
+    uint4 sf[2];
+    // window w of the item whose fragment rows are r_lo / r_hi into slot sl: 16 bytes per 64-byte window step
+    // of each packed row, and the 32-bit word holding scale bytes 2*t4, 2*t4 + 1 of the window's eight
+    auto fetch = [&](int r_lo, int r_hi, int w, int sl) {
+        const uint8_t* const q_lo = a.packed + (size_t)r_lo * (K / 2) + t4 * 16 + w * 64;
+        const uint8_t* const q_hi = a.packed + (size_t)r_hi * (K / 2) + t4 * 16 + w * 64;
+        bl[sl] = (LV & 2) ? ldg_stream128_wide(q_lo) : ldg_stream128(q_lo);
+        bh[sl] = (LV & 2) ? ldg_stream128_wide(q_hi) : ldg_stream128(q_hi);
+        if (kFragScales) {
+            // loaded per group of four windows, see the item loop
+        } else if (!kPairScales) {
+            cl[sl] = ldg_u32(a.scale + (size_t)r_lo * (K / 16) + (t4 >> 1) * 4 + w * 8);
+            ch[sl] = ldg_u32(a.scale + (size_t)r_hi * (K / 16) + (t4 >> 1) * 4 + w * 8);
+        } else if ((w & 1) == 1) {
+            // with the pair's second window: by then the pair that held these registers has been consumed
+            dl[(sl >> 1)] = ldg_nc128(a.scale + (size_t)r_lo * (K / 16) + (w - 1) * 8);
+            dh[(sl >> 1)] = ldg_nc128(a.scale + (size_t)r_hi * (K / 16) + (w - 1) * 8);
+        }
+    };
+
     ItemIter cur;
     cur.start(ib, ie, blocks, warp, kWarps);
+    int cr_lo = 0, cr_hi = 0;
     const int g_first = ib / blocks, g_last = (ie - 1) / blocks;
     for (int g = g_first; g <= g_last; g++) {
         const int4 grp = a.groups[g];
@@ -704,25 +763,15 @@ __global__ void __launch_bounds__(256, OCC) expert_ldg_kernel(ExpertArgs a) {
         const int seg_end = min(ie, (g + 1) * blocks);
         while (cur.valid() && cur.g == g && cur.it < seg_end) {
             const int blk = cur.it % blocks;
-            const size_t slot_rows = (size_t)grp.x * a.N;
-            // rows g8 (fragment rows 0..7) and g8 + 8 of the tile
-            const size_t r_lo = slot_rows + (GATE_UP ? blk * 8 + g8 : blk * 16 + g8);
-            const size_t r_hi = slot_rows + (GATE_UP ? a.N / 2 + blk * 8 + g8 : blk * 16 + 8 + g8);
-            const uint8_t* const p_lo = a.packed + r_lo * (size_t)(K / 2) + t4 * 16;
-            const uint8_t* const p_hi = a.packed + r_hi * (size_t)(K / 2) + t4 * 16;
-            // the lane's two scale bytes of a window are bytes 2*t4, 2*t4+1 of the window's eight
-            const uint8_t* const s_lo = a.scale + r_lo * (size_t)(K / 16) + (t4 >> 1) * 4;
-            const uint8_t* const s_hi = a.scale + r_hi * (size_t)(K / 16) + (t4 >> 1) * 4;
-            uint4 bl[P], bh[P];
-            uint32_t cl[P], ch[P];
+            rows_of(grp.x, cur.it, cr_lo, cr_hi);
 #pragma unroll
-            for (int p = 0; p < P; p++) {
-                bl[p] = ldg_stream128(p_lo + p * 64);
-                bh[p] = ldg_stream128(p_hi + p * 64);
-                cl[p] = ldg_u32(s_lo + p * 8);
-                ch[p] = ldg_u32(s_hi + p * 8);
+            for (int p = 0; p < P; p++) fetch(cr_lo, cr_hi, p, p);
+            const uint8_t* const fr = a.scale_frag + ((size_t)grp.x * blocks + blk) * (size_t)(kGroups * 512) + lane * 16;
+            if (kFragScales) {
+                sf[0] = ldg_nc128(fr);
+                if (kGroups > 1) sf[1] = ldg_nc128(fr + 512);
             }
-            const uint16_t graw_a = a.global[r_lo], graw_b = a.global[r_hi];
+            const uint16_t graw_a = a.global[cr_lo], graw_b = a.global[cr_hi];
             float acc[NT][4][4];
 #pragma unroll
             for (int nt = 0; nt < NT; nt++)
@@ -735,16 +784,33 @@ __global__ void __launch_bounds__(256, OCC) expert_ldg_kernel(ExpertArgs a) {
             for (int wi = 0; wi < WINS; wi++) {
                 const int sl = wi % P;
                 const uint4 plo = bl[sl], phi = bh[sl];
-                const uint32_t wl2 = cl[sl], wh2 = ch[sl];
-                if (wi + P < WINS) {   // refill the slot with the window kPre ahead
-                    bl[sl] = ldg_stream128(p_lo + (wi + P) * 64);
-                    bh[sl] = ldg_stream128(p_hi + (wi + P) * 64);
-                    cl[sl] = ldg_u32(s_lo + (wi + P) * 8);
-                    ch[sl] = ldg_u32(s_hi + (wi + P) * 8);
+                uint32_t wl2 = 0, wh2 = 0, lo16, hi16;   // the lane's two scale bytes of the low and of the high row
+                if (kFragScales) {
+                    // word wi % 4 of the group's sixteen bytes: low row's two bytes | high row's two bytes
+                    const uint4 g4 = sf[(wi >> 2) & 1];
+                    const uint32_t word = (wi & 3) == 0 ? g4.x : (wi & 3) == 1 ? g4.y : (wi & 3) == 2 ? g4.z : g4.w;
+                    lo16 = word;
+                    hi16 = word >> 16;
+                    // the group after next, once this group's last window has taken its word
+                    if ((wi & 3) == 3 && (wi >> 2) + 2 < kGroups) sf[(wi >> 2) & 1] = ldg_nc128(fr + ((wi >> 2) + 2) * 512);
+                } else if (!kPairScales) {
+                    wl2 = cl[sl];
+                    wh2 = ch[sl];
+                } else {
+                    // word (wi & 1) * 2 + (t4 >> 1) of the pair's sixteen bytes
+                    const uint4 ql4 = dl[sl >> 1], qh4 = dh[sl >> 1];
+                    wl2 = (wi & 1) ? ((t4 & 2) ? ql4.w : ql4.z) : ((t4 & 2) ? ql4.y : ql4.x);
+                    wh2 = (wi & 1) ? ((t4 & 2) ? qh4.w : qh4.z) : ((t4 & 2) ? qh4.y : qh4.x);
+                }
+                // refill the slot with the window kPre ahead
+                if (wi + P < WINS) fetch(cr_lo, cr_hi, wi + P, sl);
+                if (!kFragScales) {
+                    lo16 = (t4 & 1) ? (wl2 >> 16) : wl2;
+                    hi16 = (t4 & 1) ? (wh2 >> 16) : wh2;
                 }
                 uint32_t slo0, slo1, shi0, shi1;
-                e4m3x2_to_f16_scales((t4 & 1) ? (wl2 >> 16) : (wl2 & 0xffffu), slo0, slo1);
-                e4m3x2_to_f16_scales((t4 & 1) ? (wh2 >> 16) : (wh2 & 0xffffu), shi0, shi1);
+                e4m3x2_to_f16_scales(lo16, slo0, slo1);   // (the conversion reads the low 16 bits)
+                e4m3x2_to_f16_scales(hi16, shi0, shi1);
                 const uint32_t wl[4] = {plo.x, plo.y, plo.z, plo.w};
                 const uint32_t wh[4] = {phi.x, phi.y, phi.z, phi.w};
 #pragma unroll
@@ -795,22 +861,52 @@ __global__ void __launch_bounds__(256, OCC) expert_ldg_kernel(ExpertArgs a) {
     }
 }
 
-template <bool GATE_UP, int K_, int NT, int OCC>
+template <bool GATE_UP, int K_, int NT, int OCC, int LV>
 void launch_expert_ldg(ExpertArgs a, int sm_count, cudaStream_t s, bool pdl) {
     using C = LdgCfg<GATE_UP, K_, NT>;
     static PerDeviceOnce once;
-    allow_dyn_smem(once, expert_ldg_kernel<GATE_UP, K_, NT, OCC>, C::kSmem);
+    allow_dyn_smem(once, expert_ldg_kernel<GATE_UP, K_, NT, OCC, LV>, C::kSmem);
     if (pdl)
-        launch_pdl(expert_ldg_kernel<GATE_UP, K_, NT, OCC>, dim3(sm_count * OCC), dim3(C::kThreads), C::kSmem, s, a);
+        launch_pdl(expert_ldg_kernel<GATE_UP, K_, NT, OCC, LV>, dim3(sm_count * OCC), dim3(C::kThreads), C::kSmem, s, a);
     else
-        expert_ldg_kernel<GATE_UP, K_, NT, OCC><<<sm_count * OCC, C::kThreads, C::kSmem, s>>>(a);
+        expert_ldg_kernel<GATE_UP, K_, NT, OCC, LV><<<sm_count * OCC, C::kThreads, C::kSmem, s>>>(a);
+}
+
+// ------------------------------------------------------------------------------------------
+// fragment-ordered scales: the copy of a slot's block scales that expert_ldg_kernel reads
+//
+// dst[((tile * groups + q) * 32 + lane) * 16 + 4 * w + {0, 1, 2, 3}] =
+//   scale[row_lo][8 * (4q + w) + 2 * t4 + {0, 1}], scale[row_hi][8 * (4q + w) + 2 * t4 + {0, 1}]
+// with lane = 4 * g8 + t4 and (row_lo, row_hi) the two rows lane's fragments belong to: gate row 8 * tile + g8
+// and its up row for gate_up, rows 16 * tile + g8 and + 8 for down.  One CTA per tile, one thread per
+// (group, lane).  Same bytes as the bank's scale rows, only reordered.
+// ------------------------------------------------------------------------------------------
+template <bool GATE_UP>
+__global__ void scale_repack_kernel(const uint8_t* __restrict__ scale /* the slot's [N, K/16] */, int N, int K,
+                                    uint8_t* __restrict__ dst /* the slot's fragment-ordered copy */) {
+    const int tile = blockIdx.x, groups = K / 512;
+    const int q = threadIdx.x / 32, lane = threadIdx.x % 32;
+    if (q >= groups) return;
+    const int g8 = lane >> 2, t4 = lane & 3;
+    const int r_lo = GATE_UP ? tile * 8 + g8 : tile * 16 + g8;
+    const int r_hi = GATE_UP ? N / 2 + tile * 8 + g8 : tile * 16 + 8 + g8;
+    const int rs = K / 16;
+    uint32_t w4[4];
+#pragma unroll
+    for (int w = 0; w < 4; w++) {
+        const int off = 8 * (4 * q + w) + 2 * t4;
+        const uint32_t lo = *reinterpret_cast<const uint16_t*>(scale + (size_t)r_lo * rs + off);
+        const uint32_t hi = *reinterpret_cast<const uint16_t*>(scale + (size_t)r_hi * rs + off);
+        w4[w] = lo | (hi << 16);
+    }
+    *reinterpret_cast<uint4*>(dst + ((size_t)(tile * groups + q) * 32 + lane) * 16) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
 }
 
 // latency-bound steps (a handful of tokens) chain their kernels with programmatic dependent launch: measured
 // 49 -> 43 us per block at one token; at 64 tokens the early-resident CTAs only get in the way of the shared
 // expert that runs beside them, so larger steps launch the ordinary way
 constexpr int kPdlMaxRoutes = 128;
-constexpr int kDefaultVariant = 0;
+constexpr int kDefaultVariant = 14;   // register-streaming kernels, fragment-ordered scales, 256-byte L2 fill
 
 template <bool GATE_UP, int K_, int NT, int OCC, int VAR>
 void launch_expert_var(ExpertArgs a, int sm_count, cudaStream_t s, bool pdl) {
@@ -828,18 +924,28 @@ void launch_expert_var(ExpertArgs a, int sm_count, cudaStream_t s, bool pdl) {
 int decode_variant() {
     static const int v = [] {
         const char* e = getenv("FTM_DECODE_VARIANT");
-        return e ? atoi(e) & 7 : kDefaultVariant;
+        return e ? atoi(e) & 15 : kDefaultVariant;
     }();
     return v;
 }
 
 template <bool GATE_UP, int K_, int NT, int OCC>
 void launch_expert(ExpertArgs a, int sm_count, cudaStream_t s, bool pdl) {
-    if (decode_variant() & 4) {   // register-streaming kernels, two CTAs per SM
-        launch_expert_ldg<GATE_UP, K_, NT, 2>(a, sm_count, s, pdl);
+    if (decode_variant() & 4) {
+        // register-streaming kernels, two CTAs per SM; bit 0: paired scale loads, bit 3: 256-byte L2 fill,
+        // bit 1: fragment-ordered scales (when the adapter keeps that copy)
+        const bool frag = (decode_variant() & 2) && a.scale_frag != nullptr;
+        switch (((decode_variant() >> 3) & 1) * 2 + (decode_variant() & 1) + (frag ? 4 : 0)) {
+            case 1: launch_expert_ldg<GATE_UP, K_, NT, 2, 1>(a, sm_count, s, pdl); break;
+            case 2: launch_expert_ldg<GATE_UP, K_, NT, 2, 2>(a, sm_count, s, pdl); break;
+            case 3: launch_expert_ldg<GATE_UP, K_, NT, 2, 3>(a, sm_count, s, pdl); break;
+            case 4: case 5: launch_expert_ldg<GATE_UP, K_, NT, 2, 4>(a, sm_count, s, pdl); break;
+            case 6: case 7: launch_expert_ldg<GATE_UP, K_, NT, 2, 6>(a, sm_count, s, pdl); break;
+            default: launch_expert_ldg<GATE_UP, K_, NT, 2, 0>(a, sm_count, s, pdl); break;
+        }
         return;
     }
-    switch (decode_variant()) {
+    switch (decode_variant() & 3) {
         case 1: launch_expert_var<GATE_UP, K_, NT, OCC, 1>(a, sm_count, s, pdl); break;
         case 2: launch_expert_var<GATE_UP, K_, NT, OCC, 2>(a, sm_count, s, pdl); break;
         case 3: launch_expert_var<GATE_UP, K_, NT, OCC, 3>(a, sm_count, s, pdl); break;
@@ -904,6 +1010,19 @@ int launch_groups_from_csr(const int32_t* seg, int bins, const int32_t* slot_of_
     groups_from_csr_kernel<<<1, 1024, 0, c.s>>>(seg, bins, slot_of_bin, slots, group, groups, n_groups);
     c.end();
     return 1;
+}
+
+int launch_scale_repack(const BankView& b, int slot, uint8_t* gu_scale_frag, uint8_t* dn_scale_frag, const Ctx& c) {
+    const int N1 = 2 * b.inter, K1 = b.hidden, N2 = b.hidden, K2 = b.inter;
+    if (K1 % 512 || K2 % 512 || N1 % 16 || N2 % 16) return 0;   // shapes the register-streaming kernels do not take
+    const size_t s1 = (size_t)N1 * K1 / 16, s2 = (size_t)N2 * K2 / 16;
+    c.begin(K_CAST);
+    scale_repack_kernel<true><<<N1 / 16, 32 * (K1 / 512), 0, c.s>>>(b.gu_scale + (size_t)slot * s1, N1, K1,
+                                                                     gu_scale_frag + (size_t)slot * s1);
+    scale_repack_kernel<false><<<N2 / 16, 32 * (K2 / 512), 0, c.s>>>(b.dn_scale + (size_t)slot * s2, N2, K2,
+                                                                      dn_scale_frag + (size_t)slot * s2);
+    c.end();
+    return 2;
 }
 
 size_t decode_plan_smem(int slots) { return (size_t)3 * slots * sizeof(int); }
@@ -972,7 +1091,7 @@ int launch_decode_mma(const BankView& b, const void* x, int x_dtype, const Decod
     a.err = sc.err;
     a.top_k = top_k;
     // gate_up: K = hidden, N = 2 * inter rows
-    a.packed = b.gu_packed; a.scale = b.gu_scale; a.global = b.gu_global;
+    a.packed = b.gu_packed; a.scale = b.gu_scale; a.scale_frag = b.gu_scale_frag; a.global = b.gu_global;
     a.act = x; a.act_dtype = x_dtype; a.ic2 = sc.ic2p; a.N = 2 * b.inter;
     c.begin(K_EXPERT_GATE_UP);
     if (small)
@@ -981,7 +1100,7 @@ int launch_decode_mma(const BankView& b, const void* x, int x_dtype, const Decod
         launch_expert<true, 2048, 2, 1>(a, sm_count, c.s, false);
     c.end();
     // down: K = inter, N = hidden rows
-    a.packed = b.dn_packed; a.scale = b.dn_scale; a.global = b.dn_global;
+    a.packed = b.dn_packed; a.scale = b.dn_scale; a.scale_frag = b.dn_scale_frag; a.global = b.dn_global;
     a.act = sc.ic2p; a.act_dtype = 1; a.yroute = sc.yroute; a.route_weight = route_weight; a.N = b.hidden;
     c.begin(K_EXPERT_DOWN);
     if (small)

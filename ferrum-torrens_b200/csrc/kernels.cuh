@@ -136,6 +136,9 @@ int launch_decode_mma(const BankView& b, const void* x, int x_dtype, const Decod
                       const float* route_weight, int tokens, int top_k, DecodeScratch sc, int sm_count,
                       const Ctx& c);
 
+// fragment-ordered copy of one slot's block scales (both projections), after the slot's bytes have landed
+int launch_scale_repack(const BankView& b, int slot, uint8_t* gu_scale_frag, uint8_t* dn_scale_frag, const Ctx& c);
+
 int launch_groups_from_csr(const int32_t* seg, int bins, const int32_t* slot_of_bin, int slots, int group,
                            int4* groups, int32_t* n_groups, const Ctx& c);
 
