@@ -55,6 +55,10 @@ _PROTOS = {
     "ftm_shared_expert": (_int, [_vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp]),
     "ftm_combine": (_int, [_vp, _vp, _int, _vp, _vp, _i32, _vp, _int, _vp]),
     "ftm_moe_block": (_int, [_vp, _i32, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _int, _vp, _vp, _int, _vp]),
+    "ftm_add_rmsnorm": (_int, [_vp, _vp, _vp, _vp, C.c_float, _i32, _vp, _vp, _vp]),
+    "ftm_moe_block_prenorm": (_int, [_vp, _i32, _vp, _vp, _vp, C.c_float, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _int,
+                                     _vp, _vp, _int, _vp]),
+    "ftm_dense_gemv": (_int, [_vp, _vp, _int, _vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp]),
     "ftm_set_sm_budget": (C.c_int, [_vp, C.c_int32]),
     "ftm_kernel_launches": (C.c_uint64, [_vp]),
     "ftm_ep_pack": (_int, [_vp, _vp, _vp, _vp, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp]),

@@ -27,7 +27,8 @@ thread_local std::string g_create_error;
 const char* const kKindNames[K_NUM_KINDS] = {
     "router_logits", "router_topk", "slot_rewrite", "csr_build", "expert_gate_up", "expert_down", "sum_routes",
     "shared_phase1", "shared_phase2", "cast_bf16",   "combine",  "grouped_gate_up", "grouped_down",
-    "permute_act",   "decode_plan",   "ep_pack",         "ep_combine", "prefill_rescale"};
+    "permute_act",   "decode_plan",   "ep_pack",         "ep_combine", "prefill_rescale", "dense_gemv",
+    "add_rmsnorm"};
 
 }  // namespace
 
@@ -981,21 +982,14 @@ FTM_API int ftm_combine(ftm_handle* h, const void* routed, int routed_dtype, con
     return FTM_OK;
 }
 
-FTM_API int ftm_moe_block(ftm_handle* h, int32_t layer, const void* x_bf16, int32_t tokens, const void* gate_w_bf16,
-                  const void* sh_gate_up_bf16, const void* sh_down_bf16, const void* sh_gate_bf16, void* out,
-                  int out_dtype, int32_t* ids_out, float* weights_out, int path, void* stream) {
-    if (!h) return FTM_ERR_BAD;
-    std::lock_guard<std::mutex> lk(h->mu);
-    DeviceGuard dg(h->cfg.ordinal);
-    cudaStream_t s = pick(h, stream);
-    if (!x_bf16 || !out) return fail(h, FTM_ERR_BAD, "moe: moe_block: null buffer");
-    int rc = check_tokens(h, tokens, h->cfg.top_k);
-    if (rc != FTM_OK) return rc;
+static int block_locked(ftm_handle* h, int32_t layer, const void* x_bf16, int32_t tokens, const void* gate_w_bf16,
+                        const void* sh_gate_up_bf16, const void* sh_down_bf16, const void* sh_gate_bf16, void* out,
+                        int out_dtype, int32_t* ids_out, float* weights_out, int path, cudaStream_t s) {
     // shared expert on the second stream, forked from and joined back into s
     CU(h, cudaEventRecord(h->ev_fork, s));
     CU(h, cudaStreamWaitEvent(h->aux, h->ev_fork, 0));
-    rc = shared_locked(h, x_bf16, tokens, sh_gate_up_bf16, sh_down_bf16, sh_gate_bf16, h->shared_out, h->se_gate,
-                       h->aux);
+    int rc = shared_locked(h, x_bf16, tokens, sh_gate_up_bf16, sh_down_bf16, sh_gate_bf16, h->shared_out, h->se_gate,
+                           h->aux);
     CU(h, cudaEventRecord(h->ev_join, h->aux));
     if (rc != FTM_OK) {
         cudaStreamWaitEvent(s, h->ev_join, 0);
@@ -1009,6 +1003,84 @@ FTM_API int ftm_moe_block(ftm_handle* h, int32_t layer, const void* x_bf16, int3
                            h->ev_join, out, out_dtype, path, s);
     if (rc != FTM_OK) cudaStreamWaitEvent(s, h->ev_join, 0);  // never leave the fork unjoined
     return rc;
+}
+
+FTM_API int ftm_moe_block(ftm_handle* h, int32_t layer, const void* x_bf16, int32_t tokens, const void* gate_w_bf16,
+                  const void* sh_gate_up_bf16, const void* sh_down_bf16, const void* sh_gate_bf16, void* out,
+                  int out_dtype, int32_t* ids_out, float* weights_out, int path, void* stream) {
+    if (!h) return FTM_ERR_BAD;
+    std::lock_guard<std::mutex> lk(h->mu);
+    DeviceGuard dg(h->cfg.ordinal);
+    cudaStream_t s = pick(h, stream);
+    if (!x_bf16 || !out) return fail(h, FTM_ERR_BAD, "moe: moe_block: null buffer");
+    int rc = check_tokens(h, tokens, h->cfg.top_k);
+    if (rc != FTM_OK) return rc;
+    return block_locked(h, layer, x_bf16, tokens, gate_w_bf16, sh_gate_up_bf16, sh_down_bf16, sh_gate_bf16, out,
+                        out_dtype, ids_out, weights_out, path, s);
+}
+
+// ---- the steps either side of the block -----------------------------------------------------
+
+static int add_rmsnorm_locked(ftm_handle* h, const void* x, const void* r, const void* w, float eps, int32_t tokens,
+                              void* sum_out, void* out, cudaStream_t s) {
+    if (!x || !r || !w || !sum_out || !out) return fail(h, FTM_ERR_BAD, "moe: add_rmsnorm: null buffer");
+    if (tokens <= 0) return fail(h, FTM_ERR_BAD, "moe: add_rmsnorm: %d tokens", tokens);
+    if (h->cfg.hidden % 8 || h->cfg.hidden > 4096)
+        return fail(h, FTM_ERR_BAD, "moe: add_rmsnorm: hidden %d (a multiple of 8, at most 4096)", h->cfg.hidden);
+    if (!(eps >= 0.f)) return fail(h, FTM_ERR_BAD, "moe: add_rmsnorm: eps %g", (double)eps);
+    h->launches += launch_add_rmsnorm((const __nv_bfloat16*)x, (const __nv_bfloat16*)r, (const __nv_bfloat16*)w, eps, tokens,
+                                      h->cfg.hidden, (__nv_bfloat16*)sum_out, (__nv_bfloat16*)out, h->ctx(s));
+    CU(h, cudaGetLastError());
+    return FTM_OK;
+}
+
+FTM_API int ftm_add_rmsnorm(ftm_handle* h, const void* x_bf16, const void* residual_bf16, const void* norm_w_bf16, float eps,
+                            int32_t tokens, void* sum_out_bf16, void* out_bf16, void* stream) {
+    if (!h) return FTM_ERR_BAD;
+    std::lock_guard<std::mutex> lk(h->mu);
+    DeviceGuard dg(h->cfg.ordinal);
+    return add_rmsnorm_locked(h, x_bf16, residual_bf16, norm_w_bf16, eps, tokens, sum_out_bf16, out_bf16, pick(h, stream));
+}
+
+FTM_API int ftm_moe_block_prenorm(ftm_handle* h, int32_t layer, const void* attn_out_bf16, const void* residual_bf16,
+                                  const void* norm_w_bf16, float eps, int32_t tokens, const void* gate_w_bf16,
+                                  const void* sh_gate_up_bf16, const void* sh_down_bf16, const void* sh_gate_bf16,
+                                  void* sum_out_bf16, void* h2_out_bf16, void* out, int out_dtype, int32_t* ids_out,
+                                  float* weights_out, int path, void* stream) {
+    if (!h) return FTM_ERR_BAD;
+    std::lock_guard<std::mutex> lk(h->mu);
+    DeviceGuard dg(h->cfg.ordinal);
+    cudaStream_t s = pick(h, stream);
+    if (!out) return fail(h, FTM_ERR_BAD, "moe: moe_block_prenorm: null buffer");
+    int rc = check_tokens(h, tokens, h->cfg.top_k);
+    if (rc != FTM_OK) return rc;
+    // the normalised rows go to the adapter's own scratch (or to the caller's buffer when it wants them): at
+    // decode sizes they never leave L2 before the router, the expert kernels and the shared expert read them
+    void* h2 = h2_out_bf16 ? h2_out_bf16 : (void*)h->x_bf16;
+    rc = add_rmsnorm_locked(h, attn_out_bf16, residual_bf16, norm_w_bf16, eps, tokens, sum_out_bf16, h2, s);
+    if (rc != FTM_OK) return rc;
+    return block_locked(h, layer, h2, tokens, gate_w_bf16, sh_gate_up_bf16, sh_down_bf16, sh_gate_bf16, out, out_dtype,
+                        ids_out, weights_out, path, s);
+}
+
+// ---- dense NVFP4 GEMV of the decode tail ----------------------------------------------------
+
+FTM_API int ftm_dense_gemv(ftm_handle* h, const void* a, int a_dtype, const void* packed_kmajor_i32, const void* scale_kmajor_u8,
+                           const void* global_f16, int32_t m, int32_t n, int32_t k, float* c, void* stream) {
+    if (!h) return FTM_ERR_BAD;
+    std::lock_guard<std::mutex> lk(h->mu);
+    DeviceGuard dg(h->cfg.ordinal);
+    const char* shapes = "the dense gemv kernel was built for %s, not the shapes handed in";
+    if (!a || !packed_kmajor_i32 || !scale_kmajor_u8 || !global_f16 || !c)
+        return fail(h, FTM_ERR_BAD, "moe: dense gemv: null buffer");
+    if (a_dtype != FTM_BF16 && a_dtype != FTM_F32) return fail(h, FTM_ERR_BAD, "moe: dense gemv: activations cannot be dtype %d", a_dtype);
+    if (m <= 0 || n <= 0 || k <= 0) return fail(h, FTM_ERR_BAD, shapes, "a = [M, K] and packed = [K // 8, N]");
+    if (!dense_gemv_supported(n, k))
+        return fail(h, FTM_ERR_BAD, shapes, "N a multiple of 4 and K a multiple of 32 (at most 3136)");
+    h->launches += launch_dense_gemv(a, a_dtype, (const uint32_t*)packed_kmajor_i32, (const uint8_t*)scale_kmajor_u8,
+                                     (const uint16_t*)global_f16, m, n, k, c, h->sm_count, h->ctx(pick(h, stream)));
+    CU(h, cudaGetLastError());
+    return FTM_OK;
 }
 
 }  // extern "C"

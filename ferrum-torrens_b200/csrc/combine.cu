@@ -55,6 +55,66 @@ __global__ void cast_to_bf16_kernel(const void* __restrict__ src, int src_dtype,
     if (i < n) dst[i] = __float2bfloat16_rn(load_act(src, src_dtype, i));
 }
 
+// ---- fused residual add + RMSNorm in front of the block -------------------------------------
+// Reference: python/ferrum_kernel/norm.py:35-110 (`_add_rmsnorm_kernel`, `add_rmsnorm_reference`), the
+// post-attention site src/models/qwen3_6/forward.rs:942-953:
+//   s = bf16(f32(x) + f32(r))                    the new residual, bf16 like the stream
+//   var = mean(f32(s)^2)                         f32
+//   y = bf16((f32(s) * (1 / sqrt(var + eps))) * f32(w))      w is the baked 1 + weight vector
+// One warp per row; a lane keeps its elements in registers between the two passes.
+template <int kPerLane>
+__global__ void __launch_bounds__(128)
+add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ r,
+                   const __nv_bfloat16* __restrict__ w, float eps, int tokens, int H,
+                   __nv_bfloat16* __restrict__ sum_out, __nv_bfloat16* __restrict__ out) {
+    const int row = blockIdx.x * 4 + threadIdx.x / 32, lane = threadIdx.x % 32;
+    if (row >= tokens) return;
+    // chunk c of the lane: eight consecutive elements at (c * 32 + lane) * 8
+    float sf[kPerLane][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < kPerLane; c++) {
+        const int k = (c * 32 + lane) * 8;
+        if (k < H) {
+            const uint4 xv = *reinterpret_cast<const uint4*>(x + (size_t)row * H + k);
+            const uint4 rv = *reinterpret_cast<const uint4*>(r + (size_t)row * H + k);
+            const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w}, rw[4] = {rv.x, rv.y, rv.z, rv.w};
+            uint32_t sw[4];
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const float2 a = bf16x2_to_f32(xw[q]), b = bf16x2_to_f32(rw[q]);
+                const __nv_bfloat162 s2 = __floats2bfloat162_rn(a.x + b.x, a.y + b.y);
+                sw[q] = *reinterpret_cast<const uint32_t*>(&s2);
+                const float2 f = bf16x2_to_f32(sw[q]);
+                sf[c][2 * q] = f.x;
+                sf[c][2 * q + 1] = f.y;
+                ss += f.x * f.x;
+                ss += f.y * f.y;
+            }
+            *reinterpret_cast<uint4*>(sum_out + (size_t)row * H + k) = make_uint4(sw[0], sw[1], sw[2], sw[3]);
+        }
+    }
+    ss = warp_sum(ss);
+    const float var = ss * (1.0f / (float)H);
+    const float recip = 1.0f / sqrtf(var + eps);
+#pragma unroll
+    for (int c = 0; c < kPerLane; c++) {
+        const int k = (c * 32 + lane) * 8;
+        if (k < H) {
+            const uint4 wv = *reinterpret_cast<const uint4*>(w + k);
+            const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+            uint32_t yw[4];
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const float2 g = bf16x2_to_f32(ww[q]);
+                const __nv_bfloat162 y2 = __floats2bfloat162_rn((sf[c][2 * q] * recip) * g.x, (sf[c][2 * q + 1] * recip) * g.y);
+                yw[q] = *reinterpret_cast<const uint32_t*>(&y2);
+            }
+            *reinterpret_cast<uint4*>(out + (size_t)row * H + k) = make_uint4(yw[0], yw[1], yw[2], yw[3]);
+        }
+    }
+}
+
 // ---- expert-parallel dispatch / combine ----------------------------------------------------
 // pack: position i of the send buffers takes route r = route_idx[i] (routes sorted by global expert
 // id, hence by owning rank): the token's activation row, the expert id and the route weight
@@ -233,6 +293,20 @@ int launch_combine(const void* routed, int routed_dtype, const float* shared, co
     c.begin(K_COMBINE);
     combine_kernel<<<(unsigned)((n + 255) / 256), 256, 0, c.s>>>(routed, routed_dtype, shared, se_gate, tokens, hidden,
                                                                out, out_dtype);
+    c.end();
+    return 1;
+}
+
+int launch_add_rmsnorm(const __nv_bfloat16* x, const __nv_bfloat16* r, const __nv_bfloat16* w, float eps, int tokens,
+                       int hidden, __nv_bfloat16* sum_out, __nv_bfloat16* out, const Ctx& c) {
+    // hidden is a multiple of 8 and at most 4096 (32 lanes x 8 elements x 16 chunks), checked by the caller
+    const int chunks = (hidden + 255) / 256;
+    const int grid = (tokens + 3) / 4;
+    c.begin(K_ADD_RMSNORM);
+    if (chunks <= 8)
+        add_rmsnorm_kernel<8><<<grid, 128, 0, c.s>>>(x, r, w, eps, tokens, hidden, sum_out, out);
+    else
+        add_rmsnorm_kernel<16><<<grid, 128, 0, c.s>>>(x, r, w, eps, tokens, hidden, sum_out, out);
     c.end();
     return 1;
 }

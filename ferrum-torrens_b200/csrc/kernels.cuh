@@ -29,6 +29,8 @@ enum Kind {
     K_EP_PACK,
     K_EP_COMBINE,
     K_PREFILL_RESCALE,
+    K_DENSE_GEMV,
+    K_ADD_RMSNORM,
     K_NUM_KINDS
 };
 
@@ -202,5 +204,13 @@ int launch_ep_dispatch(const __nv_bfloat16* x, const int32_t* ids, const float* 
 int launch_ep_return(const __nv_bfloat16* y, int n, int hidden, int world, int rank, const int32_t* counts_all,
                      const uint64_t* peer_back, long long capacity, int32_t* err, const Ctx& c);
 int launch_cast_to_bf16(const void* src, int src_dtype, size_t n, __nv_bfloat16* dst, const Ctx& c);
+// fused residual add + RMSNorm in front of the block: sum_out = bf16(x + r), out = bf16(sum * rsqrt(mean(sum^2) + eps) * w)
+int launch_add_rmsnorm(const __nv_bfloat16* x, const __nv_bfloat16* r, const __nv_bfloat16* w, float eps, int tokens,
+                       int hidden, __nv_bfloat16* sum_out, __nv_bfloat16* out, const Ctx& c);
+
+// dense_gemv.cu: K-major NVFP4 GEMV of the decode tail (lm_head)
+bool dense_gemv_supported(int N, int K);
+int launch_dense_gemv(const void* a, int a_dtype, const uint32_t* packed, const uint8_t* scale, const uint16_t* global,
+                      int M, int N, int K, float* c, int sm_count, const Ctx& ctx);
 
 }  // namespace ftm

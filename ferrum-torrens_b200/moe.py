@@ -481,6 +481,61 @@ class B200MoE:
             _dev(weights_out, "weights") if weights_out is not None else null, path, _stream_ptr(stream)))
 
 
+    # -- the steps either side of the block -----------------------------------------------------
+    def add_rmsnorm(self, x, residual, norm_w, eps: float, stream=None):
+        """Fused residual add + RMSNorm (norm.py `add_rmsnorm`): returns (sum_out, out), both [T, hidden] bf16."""
+        torch = _torch()
+        for t, n in ((x, "x"), (residual, "residual"), (norm_w, "norm_w")):
+            if t.dtype != torch.bfloat16:
+                raise bad(f"add_rmsnorm {n} must be bf16")
+        tokens = x.numel() // self.shapes.hidden
+        if residual.numel() != x.numel() or norm_w.numel() != self.shapes.hidden:
+            raise bad(f"add_rmsnorm: x {x.numel()}, residual {residual.numel()}, norm_w {norm_w.numel()}")
+        s, y = torch.empty_like(x), torch.empty_like(x)
+        self._check(self._lib.ftm_add_rmsnorm(self._h, _dev(x, "x"), _dev(residual, "residual"), _dev(norm_w, "norm_w"),
+                                              C.c_float(eps), tokens, _dev(s, "sum_out"), _dev(y, "out"),
+                                              _stream_ptr(stream)))
+        return s, y
+
+    def moe_block_prenorm(self, layer: int, attn_out, residual, norm_w, eps: float, gate_w, sh_gate_up, sh_down, sh_gate,
+                          sum_out, out, *, h2_out=None, ids_out=None, weights_out=None, path: int = L.PATH_AUTO,
+                          stream=None):
+        """sum_out = attn_out + residual, h2 = rms_norm(sum_out), out = moe_block(h2) (forward.rs:942-953)."""
+        tokens = attn_out.numel() // self.shapes.hidden
+        if out.numel() != tokens * self.shapes.hidden or sum_out.numel() != attn_out.numel():
+            raise bad(f"out holds {out.numel()}, the block produces {tokens * self.shapes.hidden}")
+        null = C.c_void_p(0)
+        opt = lambda t, n: _dev(t, n) if t is not None else null
+        self._check(self._lib.ftm_moe_block_prenorm(
+            self._h, layer, _dev(attn_out, "attn_out"), _dev(residual, "residual"), _dev(norm_w, "norm_w"), C.c_float(eps),
+            tokens, _dev(gate_w, "gate"), _dev(sh_gate_up, "sh_gate_up"), _dev(sh_down, "sh_down"), _dev(sh_gate, "sh_gate"),
+            _dev(sum_out, "sum_out"), opt(h2_out, "h2"), _dev(out, "out"), _dtype_code(out), opt(ids_out, "ids"),
+            opt(weights_out, "weights"), path, _stream_ptr(stream)))
+
+    def dense_gemv(self, a, packed_kmajor, scale_kmajor, glob, c=None, stream=None):
+        """DenseGemv::gemv (cuda_linear.rs:48-175): c [M, N] f32 = a [M, K] @ dequant(W)^T for the K-major bank
+        packed [K/8, N] int32, scale [K/16, N] uint8, global [N] f16 (as int16 / uint8 bytes)."""
+        torch = _torch()
+        if a.dim() != 2 or packed_kmajor.dim() != 2:
+            raise bad("the dense gemv kernel was built for a = [M, K] and packed = [K // 8, N], not the shapes handed in")
+        m, k = a.shape
+        kw, n = packed_kmajor.shape
+        if kw * 8 != k or packed_kmajor.dtype != torch.int32:
+            raise bad("the dense gemv kernel was built for packed = [K // 8, N], not the shapes handed in")
+        if tuple(scale_kmajor.shape) != (k // 16, n) or scale_kmajor.element_size() != 1:
+            raise bad("the dense gemv kernel was built for scale = [K // 16, N], not the shapes handed in")
+        if glob.numel() * glob.element_size() != n * 2:
+            raise bad("the dense gemv kernel was built for global = [N] f16 (N * 2 bytes), not the shapes handed in")
+        if c is None:
+            c = torch.empty((m, n), dtype=torch.float32, device=a.device)
+        elif tuple(c.shape) != (m, n) or c.dtype != torch.float32:
+            raise bad("the dense gemv kernel was built for c = [M, N], not the shapes handed in")
+        self._check(self._lib.ftm_dense_gemv(self._h, _dev(a, "a"), _dtype_code(a), _dev(packed_kmajor, "packed"),
+                                             _dev(scale_kmajor, "scale"), _dev(glob, "global"), m, n, k, _dev(c, "c"),
+                                             _stream_ptr(stream)))
+        return c
+
+
 def _check_device_step(step: MoEDeviceRequest) -> int:
     """check_device_step (src/application/run_experts.rs:251-268): element counts only."""
     hidden, top_k = step.hidden, step.top_k

@@ -228,6 +228,33 @@ FTM_API int ftm_moe_block(ftm_handle* h, int32_t layer, const void* x_bf16, int3
                   const void* sh_gate_bf16, void* out, int out_dtype, int32_t* ids_out,
                   float* weights_out, int path, void* stream);
 
+/* ---- the steps either side of the block ------------------------------------------------------- */
+/* Fused residual add + RMSNorm (python/ferrum_kernel/norm.py:35-110 `_add_rmsnorm_kernel`; the
+ * post-attention site src/models/qwen3_6/forward.rs:942-953): per row of `hidden` elements
+ *   sum_out = bf16(f32(x) + f32(residual)),   out = bf16(f32(sum_out) * (1 / sqrt(mean(sum_out^2) + eps)) * f32(norm_w))
+ * x, residual, sum_out, out [T, hidden] bf16 dev, norm_w [hidden] bf16 dev (the baked 1 + weight vector).
+ * sum_out is the next layer's residual.  hidden a multiple of 8, at most 4096.  Asynchronous. */
+FTM_API int ftm_add_rmsnorm(ftm_handle* h, const void* x_bf16, const void* residual_bf16, const void* norm_w_bf16, float eps,
+                            int32_t tokens, void* sum_out_bf16, void* out_bf16, void* stream);
+/* The post-attention norm and the block in one call (forward.rs:942-953 then moe_block(&h2), :716-791):
+ * sum_out = attn_out + residual, h2 = rms_norm(sum_out), out = moe_block(h2).  The normalised rows are
+ * written once to the adapter's scratch (or to h2_out when it is not NULL), which at decode sizes stays
+ * in L2 until the router, the expert kernels and the shared expert have read it; the caller never
+ * materialises h2 or runs a separate norm launch chain.  Other arguments as ftm_moe_block. */
+FTM_API int ftm_moe_block_prenorm(ftm_handle* h, int32_t layer, const void* attn_out_bf16, const void* residual_bf16,
+                                  const void* norm_w_bf16, float eps, int32_t tokens, const void* gate_w_bf16,
+                                  const void* sh_gate_up_bf16, const void* sh_down_bf16, const void* sh_gate_bf16,
+                                  void* sum_out_bf16, void* h2_out_bf16, void* out, int out_dtype, int32_t* ids_out,
+                                  float* weights_out, int path, void* stream);
+/* DenseGemv::gemv (src/infrastructure/cuda_linear.rs:48-175; kernel python/ferrum_kernel/linear.py:41-150):
+ * c = a @ dequant(packed, scale, global)^T for the lm_head.  a [M, K] bf16 or f32 dev; the weight is the
+ * engine's K-major resident bank: packed [K/8, N] int32 (word (w, n) = the eight e2m1 codes k = 8w .. 8w+7
+ * of row n, nibble j -> k = 8w + j), scale [K/16, N] uint8 (e4m3), global [N] f16; c [M, N] f32 dev, fully
+ * overwritten.  N a multiple of 4, K a multiple of 32.  The weight is streamed once per sixteen rows of a.
+ * Asynchronous. */
+FTM_API int ftm_dense_gemv(ftm_handle* h, const void* a, int a_dtype, const void* packed_kmajor_i32, const void* scale_kmajor_u8,
+                           const void* global_f16, int32_t m, int32_t n, int32_t k, float* c, void* stream);
+
 /* ---- per-kernel timing (the reference's FT_PROFILE stage timer, src/infrastructure/profile.rs:1-14) */
 /* While enabled, every kernel launch of h is bracketed by CUDA events on its stream.  Enabling
  * resets the accumulators; both calls synchronise the device.  Not for use under stream capture. */

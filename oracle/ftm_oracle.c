@@ -17,6 +17,68 @@
 #include <omp.h>
 #endif
 
+/* ---- the steps either side of the block ------------------------------------------------------- */
+
+/* src/models/qwen3_6/forward.rs:48-61 */
+void ftmo_rms_norm(const float* x, const float* w, float eps, size_t rows, size_t row_len, float* out) {
+    float inv_rowlen = 1.0f / (float)row_len;
+    for (size_t r = 0; r < rows; r++) {
+        const float* row = x + r * row_len;
+        float sum = 0.0f;
+        for (size_t j = 0; j < row_len; j++) sum = sum + row[j] * row[j];
+        float mean = sum * inv_rowlen;
+        float inv = 1.0f / sqrtf(mean + eps);
+        for (size_t j = 0; j < row_len; j++) out[r * row_len + j] = row[j] * inv * w[j];
+    }
+}
+
+/* python/ferrum_kernel/norm.py:35-110: the bf16 stream's rounding points, the tower's reduction order */
+void ftmo_add_rmsnorm(const uint16_t* x, const uint16_t* r, const uint16_t* w, float eps, size_t rows,
+                      size_t hidden, uint16_t* sum_out, uint16_t* out) {
+    float inv_rowlen = 1.0f / (float)hidden;
+    for (size_t t = 0; t < rows; t++) {
+        float sum = 0.0f;
+        for (size_t j = 0; j < hidden; j++) {
+            float s = ftmo_bf16_to_f32(x[t * hidden + j]) + ftmo_bf16_to_f32(r[t * hidden + j]);
+            uint16_t sb = ftmo_f32_to_bf16(s);
+            sum_out[t * hidden + j] = sb;
+            float sf = ftmo_bf16_to_f32(sb);
+            sum = sum + sf * sf;
+        }
+        float var = sum * inv_rowlen;
+        float recip = 1.0f / sqrtf(var + eps);
+        for (size_t j = 0; j < hidden; j++) {
+            float sf = ftmo_bf16_to_f32(sum_out[t * hidden + j]);
+            out[t * hidden + j] = ftmo_f32_to_bf16((sf * recip) * ftmo_bf16_to_f32(w[j]));
+        }
+    }
+}
+
+/* python/ferrum_kernel/linear.py:152-168 on the K-major bank of src/infrastructure/cuda_linear.rs:103-111 */
+void ftmo_nvfp4_dense_gemv(const float* a, const uint32_t* packed_kmajor, const uint8_t* scale_kmajor,
+                           const uint16_t* global, size_t m, size_t n, size_t k, float* c, int threads) {
+    if (threads < 1) threads = 1;
+#pragma omp parallel for num_threads(threads) schedule(static)
+    for (long long row = 0; row < (long long)n; row++) {
+        float g = ftmo_f16_to_f32(global[row]);
+        /* w[row, kk] = (lut[code] * scale) * global, as the oracle widens it before the matmul */
+        float* wrow = (float*)malloc(sizeof(float) * k);
+        for (size_t kk = 0; kk < k; kk++) {
+            uint32_t word = packed_kmajor[(kk / 8) * n + (size_t)row];
+            uint8_t code = (uint8_t)((word >> (4 * (kk % 8))) & 0xF);
+            float v = ftmo_fp4_nibble(code, 0);
+            float sc = ftmo_e4m3fn_to_f32(scale_kmajor[(kk / 16) * n + (size_t)row]);
+            wrow[kk] = (v * sc) * g;
+        }
+        for (size_t t = 0; t < m; t++) {
+            float acc = 0.0f;
+            for (size_t kk = 0; kk < k; kk++) acc = acc + a[t * k + kk] * wrow[kk];
+            c[t * n + (size_t)row] = acc;
+        }
+        free(wrow);
+    }
+}
+
 int ftmo_max_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -135,6 +135,24 @@ int32_t ftmo_cache_id_of_slot(const ftmo_cache* c, size_t slot);
 size_t ftmo_cache_ensure(ftmo_cache* c, size_t layer, const uint32_t* routed, size_t n,
                          uint32_t* misses, uint32_t* write_slots, int32_t* rewrites);
 
+/* ---- the steps either side of the block ---- */
+/* Fused residual add + RMSNorm on the bf16 stream: python/ferrum_kernel/norm.py:35-110
+ * (`_add_rmsnorm_kernel`, `add_rmsnorm_reference`) with the row reduction in the order of the host tower's
+ * rms_norm (src/models/qwen3_6/forward.rs:48-61: squares summed left to right, times 1 / row_len, then
+ * 1 / sqrt(mean + eps)).  x, r, w are bf16 bit patterns; sum_out and out receive bf16 bit patterns. */
+void ftmo_add_rmsnorm(const uint16_t* x, const uint16_t* r, const uint16_t* w, float eps, size_t rows,
+                      size_t hidden, uint16_t* sum_out, uint16_t* out);
+/* the host tower's f32 rms_norm itself: src/models/qwen3_6/forward.rs:48-61 */
+void ftmo_rms_norm(const float* x, const float* w, float eps, size_t rows, size_t row_len, float* out);
+
+/* Dense NVFP4 GEMV of the decode tail: python/ferrum_kernel/linear.py:152-168
+ * (`nvfp4_dense_gemv_reference`: widen the whole weight, global included, then one f32 matmul), on the
+ * K-major bank the launcher takes (src/infrastructure/cuda_linear.rs:103-111): packed [K/8, N] int32 with
+ * nibble j of word (w, n) = code k = 8w + j of row n, scale [K/16, N] e4m3, global [N] f16.
+ * a [M, K] f32, c [M, N] f32; sums over k left to right. */
+void ftmo_nvfp4_dense_gemv(const float* a, const uint32_t* packed_kmajor, const uint8_t* scale_kmajor,
+                           const uint16_t* global, size_t m, size_t n, size_t k, float* c, int threads);
+
 int ftmo_max_threads(void);
 
 #ifdef __cplusplus

@@ -60,6 +60,9 @@ def lib() -> C.CDLL:
         _lib.ftmo_silu.argtypes = [f32]
         _lib.ftmo_sigmoid.restype = f32
         _lib.ftmo_sigmoid.argtypes = [f32]
+        _lib.ftmo_add_rmsnorm.restype = None
+        _lib.ftmo_rms_norm.restype = None
+        _lib.ftmo_nvfp4_dense_gemv.restype = None
         _lib.ftmo_cache_new.restype = C.c_void_p
         _lib.ftmo_cache_new.argtypes = [C.c_size_t] * 3
         _lib.ftmo_cache_free.argtypes = [C.c_void_p]
@@ -355,6 +358,40 @@ def moe_block(layer: Layer, x, threads: int = 1, form: str = "gemv"):
     if rc != OK:
         raise OracleError("Bad", "moe_block: bad layer shapes")
     return out, ids, w
+
+
+# ---- the steps either side of the block ---------------------------------------
+def add_rmsnorm(x_bits, r_bits, w_bits, eps: float):
+    """Fused residual add + RMSNorm on bf16 bit patterns: returns (sum_out, out) as bf16 bit patterns."""
+    x, r, w = _c(x_bits, np.uint16), _c(r_bits, np.uint16), _c(w_bits, np.uint16).reshape(-1)
+    rows, hidden = x.shape
+    s = np.empty_like(x)
+    y = np.empty_like(x)
+    lib().ftmo_add_rmsnorm(_p(x), _p(r), _p(w), C.c_float(eps), C.c_size_t(rows), C.c_size_t(hidden), _p(s), _p(y))
+    return s, y
+
+
+def rms_norm(x, w, eps: float) -> np.ndarray:
+    """The host tower's f32 rms_norm (forward.rs:48-61)."""
+    x, w = _c(x, np.float32), _c(w, np.float32).reshape(-1)
+    out = np.empty_like(x)
+    lib().ftmo_rms_norm(_p(x), _p(w), C.c_float(eps), C.c_size_t(x.shape[0]), C.c_size_t(x.shape[1]), _p(out))
+    return out
+
+
+def nvfp4_dense_gemv(a, packed_kmajor, scale_kmajor, glob, threads: int | None = None) -> np.ndarray:
+    """nvfp4_dense_gemv_reference on the K-major bank: packed [K/8, N] int32, scale [K/16, N] u8, global [N] f16."""
+    a = _c(a, np.float32)
+    packed = _c(packed_kmajor, np.uint32)
+    scale = _c(scale_kmajor, np.uint8)
+    g = _c(glob, np.uint16).reshape(-1)
+    m, k = a.shape
+    n = packed.shape[1]
+    assert packed.shape == (k // 8, n) and scale.shape == (k // 16, n) and g.size == n
+    c = np.empty((m, n), np.float32)
+    lib().ftmo_nvfp4_dense_gemv(_p(a), _p(packed), _p(scale), _p(g), C.c_size_t(m), C.c_size_t(n), C.c_size_t(k), _p(c),
+                                C.c_int(threads or max_threads()))
+    return c
 
 
 # ---- expert-slot LRU --------------------------------------------------------
