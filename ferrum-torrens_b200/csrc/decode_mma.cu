@@ -684,7 +684,7 @@ struct LdgCfg {
     static constexpr int kPre = WINS < 4 ? WINS : 4;     // windows in flight per warp
     static constexpr int RSX = K * 2 + 64;
     static constexpr int kXBytes = kGroupTokens * NT * RSX;
-    static constexpr size_t kSmem = (size_t)kXBytes + 96 * NT + 32;
+    static constexpr size_t kSmem = (size_t)kXBytes + 96 * NT + 32;    // the group's activation tile and its per-token notes
 };
 
 template <bool GATE_UP, int K_, int NT, int OCC, int LV>
@@ -864,12 +864,13 @@ __global__ void __launch_bounds__(256, OCC) expert_ldg_kernel(ExpertArgs a) {
 template <bool GATE_UP, int K_, int NT, int OCC, int LV>
 void launch_expert_ldg(ExpertArgs a, int sm_count, cudaStream_t s, bool pdl) {
     using C = LdgCfg<GATE_UP, K_, NT>;
+    const size_t smem = C::kSmem;
     static PerDeviceOnce once;
-    allow_dyn_smem(once, expert_ldg_kernel<GATE_UP, K_, NT, OCC, LV>, C::kSmem);
+    allow_dyn_smem(once, expert_ldg_kernel<GATE_UP, K_, NT, OCC, LV>, smem);
     if (pdl)
-        launch_pdl(expert_ldg_kernel<GATE_UP, K_, NT, OCC, LV>, dim3(sm_count * OCC), dim3(C::kThreads), C::kSmem, s, a);
+        launch_pdl(expert_ldg_kernel<GATE_UP, K_, NT, OCC, LV>, dim3(sm_count * OCC), dim3(C::kThreads), smem, s, a);
     else
-        expert_ldg_kernel<GATE_UP, K_, NT, OCC, LV><<<sm_count * OCC, C::kThreads, C::kSmem, s>>>(a);
+        expert_ldg_kernel<GATE_UP, K_, NT, OCC, LV><<<sm_count * OCC, C::kThreads, smem, s>>>(a);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -932,25 +933,21 @@ int decode_variant() {
 template <bool GATE_UP, int K_, int NT, int OCC>
 void launch_expert(ExpertArgs a, int sm_count, cudaStream_t s, bool pdl) {
     if (decode_variant() & 4) {
-        // register-streaming kernels, two CTAs per SM; bit 0: paired scale loads, bit 3: 256-byte L2 fill,
-        // bit 1: fragment-ordered scales (when the adapter keeps that copy)
-        const bool frag = (decode_variant() & 2) && a.scale_frag != nullptr;
-        switch (((decode_variant() >> 3) & 1) * 2 + (decode_variant() & 1) + (frag ? 4 : 0)) {
+        // register-streaming kernels, two CTAs per SM.  Variant bits: 1 = paired scale loads, 2 = fragment-ordered
+        // scales (when the adapter keeps that copy), 8 = 256-byte L2 fill
+        const int v = decode_variant();
+        const bool frag = (v & 2) && a.scale_frag != nullptr;
+        const int lv = (frag ? 4 : (v & 1)) | ((v & 8) ? 2 : 0);
+        switch (lv) {
             case 1: launch_expert_ldg<GATE_UP, K_, NT, 2, 1>(a, sm_count, s, pdl); break;
-            case 2: launch_expert_ldg<GATE_UP, K_, NT, 2, 2>(a, sm_count, s, pdl); break;
             case 3: launch_expert_ldg<GATE_UP, K_, NT, 2, 3>(a, sm_count, s, pdl); break;
-            case 4: case 5: launch_expert_ldg<GATE_UP, K_, NT, 2, 4>(a, sm_count, s, pdl); break;
-            case 6: case 7: launch_expert_ldg<GATE_UP, K_, NT, 2, 6>(a, sm_count, s, pdl); break;
+            case 4: launch_expert_ldg<GATE_UP, K_, NT, 2, 4>(a, sm_count, s, pdl); break;
+            case 6: launch_expert_ldg<GATE_UP, K_, NT, 2, 6>(a, sm_count, s, pdl); break;
             default: launch_expert_ldg<GATE_UP, K_, NT, 2, 0>(a, sm_count, s, pdl); break;
         }
         return;
     }
-    switch (decode_variant() & 3) {
-        case 1: launch_expert_var<GATE_UP, K_, NT, OCC, 1>(a, sm_count, s, pdl); break;
-        case 2: launch_expert_var<GATE_UP, K_, NT, OCC, 2>(a, sm_count, s, pdl); break;
-        case 3: launch_expert_var<GATE_UP, K_, NT, OCC, 3>(a, sm_count, s, pdl); break;
-        default: launch_expert_var<GATE_UP, K_, NT, OCC, 0>(a, sm_count, s, pdl); break;
-    }
+    launch_expert_var<GATE_UP, K_, NT, OCC, 0>(a, sm_count, s, pdl);   // the shared-memory ring kernels (variant 0)
 }
 
 // Large batches: the routes are bucketed by the multi-CTA CSR build (seg / route_idx); this turns every
