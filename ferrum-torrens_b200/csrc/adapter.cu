@@ -919,8 +919,48 @@ FTM_API int ftm_ep_return(ftm_handle* h, const void* y_bf16, int32_t rows, int32
     if (rows < 0 || ep_size < 1 || ep_size > 32 || ep_rank < 0 || ep_rank >= ep_size || capacity_rows < 1)
         return fail(h, FTM_ERR_BAD, "moe: ep_return: %d rows, rank %d of %d", rows, ep_rank, ep_size);
     if (rows == 0) return FTM_OK;
-    h->launches += launch_ep_return((const __nv_bfloat16*)y_bf16, rows, h->cfg.hidden, ep_size, ep_rank, counts_all, peer_back,
+    h->launches += launch_ep_return((const __nv_bfloat16*)y_bf16, nullptr, nullptr, rows, h->cfg.hidden, ep_size, ep_rank, counts_all, peer_back,
                                     capacity_rows, h->flags + 2, h->ctx(pick(h, stream)));
+    CU(h, cudaGetLastError());
+    return FTM_OK;
+}
+
+FTM_API int ftm_ep_experts_sorted(ftm_handle* h, int32_t layer, const void* x_bf16, const int32_t* expert_ids,
+                                  const float* weights, int32_t rows, void* stream) {
+    if (!h) return FTM_ERR_BAD;
+    std::lock_guard<std::mutex> lk(h->mu);
+    DeviceGuard dg(h->cfg.ordinal);
+    if (!x_bf16 || !expert_ids || !weights) return fail(h, FTM_ERR_BAD, "moe: ep_experts_sorted: null buffer");
+    if (layer < 0 || layer >= h->cfg.layers) return fail(h, FTM_ERR_BAD, "moe: layer %d of %d", layer, h->cfg.layers);
+    if (h->cfg.top_k != 1)
+        return fail(h, FTM_ERR_BAD, "moe: ep_experts_sorted needs an owner adapter (top_k 1), this one has top_k %d", h->cfg.top_k);
+    int rc = check_tokens(h, rows, 1);
+    if (rc != FTM_OK) return rc;
+    // only the grouped GEMM leaves its rows sorted; small steps take the ordinary call and ftm_ep_return
+    if (rows <= kGroupedMinRoutes || !h->maps.ok ||
+        !prefill_umma_supported(h->cfg.hidden, h->cfg.inter, h->cfg.slots, h->cfg.experts, true))
+        return fail(h, FTM_ERR_NOT_SUPPORTED, "moe: ep_experts_sorted: %d rows take the ordinary staged call", rows);
+    rc = run_routed(h, x_bf16, FTM_BF16, expert_ids, FTM_I32, layer, weights, rows, nullptr, nullptr, nullptr, nullptr,
+                    FTM_BF16, FTM_PATH_GROUPED, pick(h, stream));
+    if (rc != FTM_OK) return rc;
+    CU(h, cudaGetLastError());
+    h->steps++;
+    return FTM_OK;
+}
+
+FTM_API int ftm_ep_return_sorted(ftm_handle* h, int32_t rows, int32_t ep_size, int32_t ep_rank, const int32_t* counts_all,
+                                 const uint64_t* peer_back, int64_t capacity_rows, void* stream) {
+    if (!h) return FTM_ERR_BAD;
+    std::lock_guard<std::mutex> lk(h->mu);
+    DeviceGuard dg(h->cfg.ordinal);
+    if (!counts_all || !peer_back) return fail(h, FTM_ERR_BAD, "moe: ep_return_sorted: null buffer");
+    if (rows <= 0 || rows > h->cfg.max_tokens || ep_size < 1 || ep_size > 32 || ep_rank < 0 || ep_rank >= ep_size ||
+        capacity_rows < 1 || h->cfg.top_k != 1)
+        return fail(h, FTM_ERR_BAD, "moe: ep_return_sorted: %d rows, rank %d of %d", rows, ep_rank, ep_size);
+    // the rows ftm_ep_experts_sorted left in the adapter: y sorted by expert, the position of every received row,
+    // and its slot (a row whose expert is not resident returns zeros)
+    h->launches += launch_ep_return((const __nv_bfloat16*)h->yroute, h->route_idx, h->route_slot, rows, h->cfg.hidden, ep_size,
+                                    ep_rank, counts_all, peer_back, capacity_rows, h->flags + 2, h->ctx(pick(h, stream)));
     CU(h, cudaGetLastError());
     return FTM_OK;
 }

@@ -187,6 +187,11 @@ __global__ void ep_combine_kernel(const void* __restrict__ y, int y_dtype, const
 // counts_all[s * world + p] = routes that rank s sends to owner p.  An owner's receive buffer holds the
 // sources in rank order, each source's routes in its send order (sorted by expert).
 
+// Both kernels move whole rows between GPUs with plain 16-byte peer stores.  A CTA takes kEpRows rows and
+// issues all their loads before the first store, so that every thread keeps several stores in flight on the
+// link (one row per CTA reached 0.71 of the measured peer-copy rate).
+constexpr int kEpRows = 4;
+
 // dispatch: position i of this rank's send order goes straight into the owner's receive buffers
 __global__ void __launch_bounds__(128)
 ep_dispatch_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ ids, const float* __restrict__ weights,
@@ -196,56 +201,104 @@ ep_dispatch_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restric
                    int32_t* err) {
     // CTAs walk the send order starting at the next rank's block, so that at any time every owner is written
     // by one source (all ranks starting at owner 0 would share that owner's ingress bandwidth)
-    int i = blockIdx.x + seg[((rank + 1) % world) * per];
-    if (i >= routes) i -= routes;
-    // every index is checked before the load that depends on it: a route the permutation build dropped
-    // (route_idx left at -1) or an expert id outside the layer raises the error flag, it is never followed
-    const int r = (i >= 0 && i < routes) ? route_idx[i] : -1;
-    const int e = (r >= 0 && r < routes) ? ids[r] : -1;
-    if (e < 0 || e >= per * world) {
-        if (threadIdx.x == 0) atomicExch(err, 4);
-        return;
+    const int first = seg[((rank + 1) % world) * per];
+    const uint4* src[kEpRows];
+    uint4* dst[kEpRows];
+#pragma unroll
+    for (int q = 0; q < kEpRows; q++) {
+        src[q] = nullptr;
+        dst[q] = nullptr;
+        int i = blockIdx.x * kEpRows + q;
+        if (i >= routes) continue;
+        i += first;
+        if (i >= routes) i -= routes;
+        // every index is checked before the load that depends on it: a route the permutation build dropped
+        // (route_idx left at -1) or an expert id outside the layer raises the error flag, it is never followed
+        const int r = (i >= 0 && i < routes) ? route_idx[i] : -1;
+        const int e = (r >= 0 && r < routes) ? ids[r] : -1;
+        if (e < 0 || e >= per * world) {
+            if (threadIdx.x == 0) atomicExch(err, 4);
+            continue;
+        }
+        const int p = e / per;
+        long long row = i - seg[p * per];
+        for (int s = 0; s < rank; s++) row += counts_all[s * world + p];
+        if (row < 0 || row >= capacity) {   // never store outside the owner's buffer
+            if (threadIdx.x == 0) atomicExch(err, 4);
+            continue;
+        }
+        src[q] = reinterpret_cast<const uint4*>(x + (size_t)(r / top_k) * H);
+        dst[q] = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(peer_x[p]) + (size_t)row * H);
+        if (threadIdx.x == 0)
+            reinterpret_cast<int2*>(peer_meta[p])[row] = make_int2(e, __float_as_int(weights[r]));
     }
-    const int p = e / per;
-    long long row = i - seg[p * per];
-    for (int s = 0; s < rank; s++) row += counts_all[s * world + p];
-    if (row < 0 || row >= capacity) {   // never store outside the owner's buffer
-        if (threadIdx.x == 0) atomicExch(err, 4);
-        return;
+    for (int c = threadIdx.x; c < H / 8; c += blockDim.x) {
+        uint4 v[kEpRows];
+#pragma unroll
+        for (int q = 0; q < kEpRows; q++)
+            if (src[q]) v[q] = src[q][c];
+#pragma unroll
+        for (int q = 0; q < kEpRows; q++)
+            if (dst[q]) dst[q][c] = v[q];
     }
-    const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)(r / top_k) * H);
-    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(peer_x[p]) + (size_t)row * H);
-    for (int c = threadIdx.x; c < H / 8; c += blockDim.x) dst[c] = src[c];
-    if (threadIdx.x == 0)
-        reinterpret_cast<int2*>(peer_meta[p])[row] = make_int2(e, __float_as_int(weights[r]));
 }
 
-// return: row i of the owner's output (receive order) goes to the position its source packed it at
+// return: row i of the owner's output (receive order) goes to the position its source packed it at.  With
+// pos_of_route the owner's rows are still sorted by expert (y row pos_of_route[i] belongs to received row i,
+// a received row whose expert is not resident returns zeros): the un-permute pass and its extra read and
+// write of every row are skipped.
 __global__ void __launch_bounds__(128)
-ep_return_kernel(const __nv_bfloat16* __restrict__ y, int n, int H, int world, int rank,
+ep_return_kernel(const __nv_bfloat16* __restrict__ y, const int32_t* __restrict__ pos_of_route,
+                 const int32_t* __restrict__ route_slot, int n, int H, int world, int rank,
                  const int32_t* __restrict__ counts_all, const uint64_t* __restrict__ peer_back, long long capacity,
                  int32_t* err) {
     // rows are walked starting at the next rank's block (see ep_dispatch_kernel)
     int first = 0;
     for (int q = 0; q < (rank + 1) % world; q++) first += counts_all[q * world + rank];
-    int i = blockIdx.x + first;
-    if (i >= n) i -= n;
-    int s = 0, roff = 0;
-    for (; s < world; s++) {
-        const int c = counts_all[s * world + rank];
-        if (i < roff + c) break;
-        roff += c;
+    const uint4* src[kEpRows];
+    uint4* dst[kEpRows];
+    bool zero[kEpRows];
+#pragma unroll
+    for (int q = 0; q < kEpRows; q++) {
+        src[q] = nullptr;
+        dst[q] = nullptr;
+        zero[q] = false;
+        int i = blockIdx.x * kEpRows + q;
+        if (i >= n) continue;
+        i += first;
+        if (i >= n) i -= n;
+        int s = 0, roff = 0;
+        for (; s < world; s++) {
+            const int c = counts_all[s * world + rank];
+            if (i < roff + c) break;
+            roff += c;
+        }
+        long long row = i - roff;
+        if (s < world)
+            for (int p = 0; p < rank; p++) row += counts_all[s * world + p];
+        if (s >= world || row < 0 || row >= capacity) {
+            if (threadIdx.x == 0) atomicExch(err, 4);
+            continue;
+        }
+        long long from = i;
+        if (pos_of_route) {
+            if (route_slot[i] < 0)
+                zero[q] = true;
+            else
+                from = pos_of_route[i];
+        }
+        src[q] = reinterpret_cast<const uint4*>(y + (size_t)from * H);
+        dst[q] = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(peer_back[s]) + (size_t)row * H);
     }
-    long long row = i - roff;
-    if (s < world)
-        for (int p = 0; p < rank; p++) row += counts_all[s * world + p];
-    if (s >= world || row < 0 || row >= capacity) {
-        if (threadIdx.x == 0) atomicExch(err, 4);
-        return;
+    for (int c = threadIdx.x; c < H / 8; c += blockDim.x) {
+        uint4 v[kEpRows];
+#pragma unroll
+        for (int q = 0; q < kEpRows; q++)
+            if (src[q]) v[q] = zero[q] ? make_uint4(0, 0, 0, 0) : src[q][c];
+#pragma unroll
+        for (int q = 0; q < kEpRows; q++)
+            if (dst[q]) dst[q][c] = v[q];
     }
-    const uint4* src = reinterpret_cast<const uint4*>(y + (size_t)i * H);
-    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(peer_back[s]) + (size_t)row * H);
-    for (int c = threadIdx.x; c < H / 8; c += blockDim.x) dst[c] = src[c];
 }
 
 }  // namespace
@@ -255,17 +308,19 @@ int launch_ep_dispatch(const __nv_bfloat16* x, const int32_t* ids, const float* 
                        const int32_t* counts_all, const uint64_t* peer_x, const uint64_t* peer_meta, long long capacity,
                        int32_t* err, const Ctx& c) {
     c.begin(K_EP_PACK);
-    ep_dispatch_kernel<<<tokens * top_k, 128, 0, c.s>>>(x, ids, weights, route_idx, seg, tokens * top_k, top_k, hidden,
+    ep_dispatch_kernel<<<(tokens * top_k + kEpRows - 1) / kEpRows, 128, 0, c.s>>>(x, ids, weights, route_idx, seg, tokens * top_k, top_k, hidden,
                                                        experts / world, world, rank, counts_all, peer_x, peer_meta, capacity,
                                                        err);
     c.end();
     return 1;
 }
 
-int launch_ep_return(const __nv_bfloat16* y, int n, int hidden, int world, int rank, const int32_t* counts_all,
-                     const uint64_t* peer_back, long long capacity, int32_t* err, const Ctx& c) {
+int launch_ep_return(const __nv_bfloat16* y, const int32_t* pos_of_route, const int32_t* route_slot, int n, int hidden,
+                     int world, int rank, const int32_t* counts_all, const uint64_t* peer_back, long long capacity,
+                     int32_t* err, const Ctx& c) {
     c.begin(K_EP_COMBINE);
-    ep_return_kernel<<<n, 128, 0, c.s>>>(y, n, hidden, world, rank, counts_all, peer_back, capacity, err);
+    ep_return_kernel<<<(n + kEpRows - 1) / kEpRows, 128, 0, c.s>>>(y, pos_of_route, route_slot, n, hidden, world, rank, counts_all,
+                                                                  peer_back, capacity, err);
     c.end();
     return 1;
 }

@@ -201,8 +201,10 @@ int launch_ep_dispatch(const __nv_bfloat16* x, const int32_t* ids, const float* 
                        const int32_t* seg, int tokens, int top_k, int hidden, int experts, int world, int rank,
                        const int32_t* counts_all, const uint64_t* peer_x, const uint64_t* peer_meta, long long capacity,
                        int32_t* err, const Ctx& c);
-int launch_ep_return(const __nv_bfloat16* y, int n, int hidden, int world, int rank, const int32_t* counts_all,
-                     const uint64_t* peer_back, long long capacity, int32_t* err, const Ctx& c);
+// pos_of_route / route_slot null: y is in receive order; else y is still sorted by expert (see the kernel)
+int launch_ep_return(const __nv_bfloat16* y, const int32_t* pos_of_route, const int32_t* route_slot, int n, int hidden,
+                     int world, int rank, const int32_t* counts_all, const uint64_t* peer_back, long long capacity,
+                     int32_t* err, const Ctx& c);
 int launch_cast_to_bf16(const void* src, int src_dtype, size_t n, __nv_bfloat16* dst, const Ctx& c);
 // fused residual add + RMSNorm in front of the block: sum_out = bf16(x + r), out = bf16(sum * rsqrt(mean(sum^2) + eps) * w)
 int launch_add_rmsnorm(const __nv_bfloat16* x, const __nv_bfloat16* r, const __nv_bfloat16* w, float eps, int tokens,

@@ -640,15 +640,19 @@ int launch_prefill_umma(const BankView& b, const void* x, int x_dtype, const Dec
     umma_grouped_gemm_kernel<false, 512><<<sm_count, kThreads, kUmmaSmem, c.s>>>(map_h, map_dp, map_ds, a);
     c.end();
     launches += 3;
-    // 4. un-permute and sum in route order; routes of experts that are not resident are skipped
+    // 4. un-permute and sum in route order; routes of experts that are not resident are skipped.  Without `out`
+    // the rows stay sorted by expert (sc.y, with sc.pos_of_route to find them): the expert-parallel owner hands
+    // them to the return kernel as they are.
     if (join) cudaStreamWaitEvent(c.s, join, 0);
     c.begin(K_SUM_ROUTES);
     prefill_invert_kernel<<<(routes + 255) / 256, 256, 0, c.s>>>(sc.route_idx, sc.seg + nbins, sc.pos_of_route);
-    dim3 grid(tokens, (b.hidden / 4 + 127) / 128);
-    prefill_combine_kernel<<<grid, 128, 0, c.s>>>(sc.y, out_dtype == 1, sc.pos_of_route, route_slot, b.slots, top_k, b.hidden, shared, se_gate,
-                                                  out, out_dtype);
+    if (out) {
+        dim3 grid(tokens, (b.hidden / 4 + 127) / 128);
+        prefill_combine_kernel<<<grid, 128, 0, c.s>>>(sc.y, out_dtype == 1, sc.pos_of_route, route_slot, b.slots, top_k, b.hidden, shared,
+                                                      se_gate, out, out_dtype);
+    }
     c.end();
-    return launches + 2;
+    return launches + (out ? 2 : 1);
 }
 
 }  // namespace ftm

@@ -225,9 +225,15 @@ class ExpertParallelMoE:
         mark("dispatched")
         if n:
             meta = b.p2p_recv_meta[:n]
-            y = b.experts_forward(layer, b.p2p_recv_x[:n], meta[:, 0].contiguous(), meta[:, 1].contiguous().view(torch.float32))
-            mark("computed")
-            b.owner.ep_return(y, world, b.rank, counts_all, b.peer_back, b.send_capacity)
+            rids, rw = meta[:, 0].contiguous(), meta[:, 1].contiguous().view(torch.float32)
+            # large steps: the return kernel reads the rows where the grouped GEMM left them (sorted by expert)
+            if b.owner.ep_experts_sorted(layer, b.p2p_recv_x[:n], rids, rw):
+                mark("computed")
+                b.owner.ep_return_sorted(n, world, b.rank, counts_all, b.peer_back, b.send_capacity)
+            else:
+                y = b.experts_forward(layer, b.p2p_recv_x[:n], rids, rw)
+                mark("computed")
+                b.owner.ep_return(y, world, b.rank, counts_all, b.peer_back, b.send_capacity)
         else:
             mark("computed")
         self._barrier(b)

@@ -458,6 +458,23 @@ class B200MoE:
         self._check(self._lib.ftm_ep_return(self._h, _dev(y, "y"), rows, ep_size, ep_rank, _dev(counts_all, "counts_all"),
                                             C.c_void_p(peer_back), capacity_rows, _stream_ptr(stream)))
 
+    def ep_experts_sorted(self, layer: int, x, expert_ids, weights, stream=None) -> bool:
+        """Owner side: the grouped GEMMs on the received rows, results left sorted by expert inside the adapter for
+        ep_return_sorted.  False when the step is too small for that path (use grouped_moe_staged + ep_return)."""
+        rows = x.numel() // self.shapes.hidden
+        rc = self._lib.ftm_ep_experts_sorted(self._h, layer, _dev(x, "x"), _dev(expert_ids, "ids"), _dev(weights, "weights"),
+                                             rows, _stream_ptr(stream))
+        if rc == L.ERR_NOT_SUPPORTED:
+            return False
+        self._check(rc)
+        return True
+
+    def ep_return_sorted(self, rows: int, ep_size: int, ep_rank: int, counts_all, peer_back: int, capacity_rows: int,
+                         stream=None):
+        """Owner side: store the rows ep_experts_sorted left in the adapter into their sources' back buffers."""
+        self._check(self._lib.ftm_ep_return_sorted(self._h, rows, ep_size, ep_rank, _dev(counts_all, "counts_all"),
+                                                   C.c_void_p(peer_back), capacity_rows, _stream_ptr(stream)))
+
     def ep_combine(self, y, route_idx, shared, se_gate, out, stream=None):
         """out[t] = se_gate[t] * shared[t] + sum_j y[position of route t*k + j] (weights applied by the owner)."""
         tokens = out.numel() // self.shapes.hidden

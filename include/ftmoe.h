@@ -299,6 +299,16 @@ FTM_API int ftm_ep_dispatch(ftm_handle* h, const void* x_bf16, const int32_t* id
                             int64_t capacity_rows, void* stream);
 FTM_API int ftm_ep_return(ftm_handle* h, const void* y_bf16, int32_t rows, int32_t ep_size, int32_t ep_rank,
                           const int32_t* counts_all, const uint64_t* peer_back, int64_t capacity_rows, void* stream);
+/* The owner's step without its last pass.  ftm_moe_layer_staged on an owner adapter (top_k = 1) sorts the
+ * received rows by expert, runs the grouped GEMMs and copies the results back into receive order; that copy
+ * is only there to be read again by ftm_ep_return.  ftm_ep_experts_sorted stops before it (x [rows, hidden]
+ * bf16, expert_ids / weights [rows], all device) and ftm_ep_return_sorted stores every row from where the GEMM
+ * left it straight into its source's back buffer.  FTM_ERR_NOT_SUPPORTED for steps too small for the grouped
+ * GEMM (at most 2048 rows): use ftm_moe_layer_staged and ftm_ep_return there.  Both asynchronous, same stream. */
+FTM_API int ftm_ep_experts_sorted(ftm_handle* h, int32_t layer, const void* x_bf16, const int32_t* expert_ids,
+                                  const float* weights, int32_t rows, void* stream);
+FTM_API int ftm_ep_return_sorted(ftm_handle* h, int32_t rows, int32_t ep_size, int32_t ep_rank, const int32_t* counts_all,
+                                 const uint64_t* peer_back, int64_t capacity_rows, void* stream);
 FTM_API int ftm_ep_combine(ftm_handle* h, const void* y, int y_dtype, const int32_t* route_idx, const float* shared,
                            const float* se_gate, int32_t tokens, void* out, int out_dtype, void* stream);
 

@@ -151,3 +151,84 @@ def test_dispatch_reports_an_expert_id_outside_the_layer_instead_of_following_it
     front.sync_status()
     assert int(sum(int(m[:, 0].ge(0).sum()) for m in recv_m)) > 0
     front.close()
+
+
+def test_sorted_return_on_the_grouped_gemm_path_emulated():
+    """Steps large enough for the grouped GEMM (more than 2048 received rows per owner, production expert shape):
+    the owner leaves its rows sorted by expert and the return kernel stores them from there
+    (ftm_ep_experts_sorted + ftm_ep_return_sorted).  Two ranks on one GPU; every rank's result must equal the
+    block computed by one adapter that holds all experts, and the ordinary return path on the same step."""
+    dev = torch.device("cuda:0")
+    Hh, Ii, Ee, Kk, Ss = 2048, 512, 16, 4, 512
+    world, tokens = 2, [700, 650]
+    lay = pkg.synth.make_layer(93, hidden=Hh, inter=Ii, experts=Ee, top_k=Kk, shared_inter=Ss)
+    shapes = pkg.ExpertShapes(Hh, Ii)
+    per = Ee // world
+    cap = sum(tokens) * Kk
+    dense = [_bf16(a, dev) for a in (lay.gate_w, lay.sh_gate_up, lay.sh_down, lay.sh_gate)]
+    solo = pkg.B200MoE(0, shapes, Ee, experts=Ee, layers=1, top_k=Kk, shared_inter=Ss, max_tokens=max(tokens))
+    for e in range(Ee):
+        solo.load(0, e, e, lay.fields(e))
+    fronts, owners = [], []
+    for r in range(world):
+        fronts.append(pkg.B200MoE(0, shapes, 1, experts=Ee, layers=1, top_k=Kk, shared_inter=Ss, max_tokens=max(tokens)))
+        ow = pkg.B200MoE(0, shapes, per, experts=Ee, layers=1, top_k=1, shared_inter=0, max_tokens=cap)
+        for e in range(r * per, (r + 1) * per):
+            ow.load(0, e, e - r * per, lay.fields(e))
+        owners.append(ow)
+    xs = [_bf16(pkg.synth.make_x(800 + r, tokens[r], Hh), dev) for r in range(world)]
+    recv_x = [torch.zeros((cap, Hh), dtype=torch.bfloat16, device=dev) for _ in range(world)]
+    recv_m = [torch.zeros((cap, 2), dtype=torch.int32, device=dev) for _ in range(world)]
+    ptrs = lambda ts: torch.tensor([t.data_ptr() for t in ts], dtype=torch.int64, device=dev)
+    peer_x, peer_m = ptrs(recv_x), ptrs(recv_m)
+    routed = []
+    for r in range(world):
+        ids, w = fronts[r].router(xs[r], dense[0])
+        route_idx, counts = fronts[r].ep_plan(ids, world)
+        routed.append((ids, w, route_idx, counts))
+    counts_all = torch.cat([c for _, _, _, c in routed]).contiguous()
+    ca = counts_all.reshape(world, world).cpu().numpy()
+    for r in range(world):
+        ids, w, route_idx, _ = routed[r]
+        fronts[r].ep_dispatch(xs[r], ids, w, route_idx, world, r, counts_all, peer_x.data_ptr(), peer_m.data_ptr(), cap)
+    torch.cuda.synchronize()
+    results = {}
+    for mode in ("sorted", "plain"):
+        back = [torch.zeros((tokens[r] * Kk, Hh), dtype=torch.bfloat16, device=dev) for r in range(world)]
+        peer_back = ptrs(back)
+        for r in range(world):
+            n = int(ca[:, r].sum())
+            assert n > 2048, "the case must reach the grouped GEMM"
+            meta = recv_m[r][:n]
+            rids, rw = meta[:, 0].contiguous(), meta[:, 1].contiguous().view(torch.float32)
+            if mode == "sorted":
+                assert owners[r].ep_experts_sorted(0, recv_x[r][:n], rids, rw)
+                owners[r].ep_return_sorted(n, world, r, counts_all, peer_back.data_ptr(), max(tokens) * Kk)
+            else:
+                y = torch.empty((n, Hh), dtype=torch.bfloat16, device=dev)
+                owners[r].grouped_moe_staged(pkg.MoEDeviceRequest(0, Hh, Ii, 1, recv_x[r][:n], rids.reshape(n, 1),
+                                                                  rw.reshape(n, 1)), y)
+                owners[r].ep_return(y, world, r, counts_all, peer_back.data_ptr(), max(tokens) * Kk)
+        torch.cuda.synchronize()
+        for r in range(world):
+            owners[r].sync_status()
+        results[mode] = back
+    for r in range(world):
+        assert torch.equal(results["sorted"][r], results["plain"][r]), "the same rows, whichever pass stored them"
+        ids, w, route_idx, _ = routed[r]
+        shared, se_gate = fronts[r].shared_expert(xs[r], dense[1], dense[2], dense[3])
+        out = torch.empty((tokens[r], Hh), dtype=torch.float32, device=dev)
+        fronts[r].ep_combine(results["sorted"][r], route_idx, shared, se_gate, out)
+        want = torch.empty((tokens[r], Hh), dtype=torch.float32, device=dev)
+        want_ids = torch.empty((tokens[r], Kk), dtype=torch.int32, device=dev)
+        solo.moe_block(0, xs[r], *dense, want, ids_out=want_ids)
+        solo.sync_status()
+        assert torch.equal(ids, want_ids)
+        rel = float((out - want).norm() / want.norm())
+        assert rel < 5e-3, (r, rel)
+    # a step of at most 2048 rows is not taken by this path
+    n_small = 100
+    assert owners[0].ep_experts_sorted(0, recv_x[0][:n_small], recv_m[0][:n_small, 0].contiguous(),
+                                       recv_m[0][:n_small, 1].contiguous().view(torch.float32)) is False
+    for m in fronts + owners + [solo]:
+        m.close()
