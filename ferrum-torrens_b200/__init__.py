@@ -5,7 +5,8 @@ The directory name is not a Python identifier; import it with
 """
 from .moe import (B200MoE, CachedExperts, ExpertCache, ExpertShapes, MoEDeviceRequest, MoEError, MoEGroup,
                   BANKS, route_lists, run_experts)
-from . import _lib, synth
+from . import _lib, ftw, synth
+from .ftw import FtwBanks, FtwIndex
 
 __all__ = ["B200MoE", "CachedExperts", "ExpertCache", "ExpertShapes", "MoEDeviceRequest", "MoEError", "MoEGroup",
-           "BANKS", "route_lists", "run_experts", "synth", "_lib"]
+           "BANKS", "route_lists", "run_experts", "synth", "_lib", "ftw", "FtwBanks", "FtwIndex"]

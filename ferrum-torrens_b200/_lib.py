@@ -59,6 +59,20 @@ _PROTOS = {
     "ftm_moe_block_prenorm": (_int, [_vp, _i32, _vp, _vp, _vp, C.c_float, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _int,
                                      _vp, _vp, _int, _vp]),
     "ftm_dense_gemv": (_int, [_vp, _vp, _int, _vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp]),
+    "ftm_ftw_open": (_int, [C.c_char_p, C.POINTER(_vp)]),
+    "ftm_ftw_parse": (_int, [C.c_char_p, C.POINTER(_vp)]),
+    "ftm_ftw_close": (None, [_vp]),
+    "ftm_ftw_last_error": (C.c_char_p, [_vp]),
+    "ftm_ftw_tensor_count": (C.c_int64, [_vp]),
+    "ftm_ftw_shard_count": (C.c_int64, [_vp]),
+    "ftm_ftw_total_bytes": (C.c_uint64, [_vp]),
+    "ftm_ftw_entry": (_int, [_vp, C.c_char_p, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64),
+                             C.POINTER(_i32), C.POINTER(_i32)]),
+    "ftm_ftw_pieces": (_int, [_vp, C.c_uint64, C.c_uint64, _i32, _vp, _vp, _vp, _vp, C.POINTER(_i32)]),
+    "ftm_ftw_read_range": (_int, [_vp, C.c_uint64, C.c_uint64, _vp, _sz]),
+    "ftm_ftw_expert_slab": (_int, [_vp, C.c_char_p, _i32, C.c_uint32, _i32, _vp, _vp, _vp, C.POINTER(_sz), C.POINTER(_sz),
+                                   C.POINTER(_i32), C.POINTER(_i32)]),
+    "ftm_load_layer_from_ftw": (_int, [_vp, _vp, C.c_char_p, _i32, _i32, _i32, _i32]),
     "ftm_set_sm_budget": (C.c_int, [_vp, C.c_int32]),
     "ftm_kernel_launches": (C.c_uint64, [_vp]),
     "ftm_ep_pack": (_int, [_vp, _vp, _vp, _vp, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp]),

@@ -255,6 +255,49 @@ FTM_API int ftm_moe_block_prenorm(ftm_handle* h, int32_t layer, const void* attn
 FTM_API int ftm_dense_gemv(ftm_handle* h, const void* a, int a_dtype, const void* packed_kmajor_i32, const void* scale_kmajor_u8,
                            const void* global_f16, int32_t m, int32_t n, int32_t k, float* c, void* stream);
 
+/* ---- FTW checkpoint: index and expert banks ---------------------------------------------------
+ * The checkpoint the reference engine loads (src/infrastructure/ftw.rs): a JSON index
+ * `freetoken_weight.json` over one logical byte region cut into shard files.  Host code only; none of
+ * these calls needs a CUDA device except ftm_load_layer_from_ftw. */
+typedef struct ftm_ftw ftm_ftw;
+/* FtwReader::open (ftw.rs:397-440): parses `dir`/freetoken_weight.json (FtwIndex::parse, ftw.rs:95-252: format
+ * tag, version 1, 4096 alignment, contiguous shards covering total_bytes, every tensor aligned, non-empty,
+ * in range and shape * element size == nbytes) and opens every shard (a shard shorter than the index says is
+ * refused).  Errors: FTM_ERR_READ for I/O and JSON syntax, FTM_ERR_BAD for an invalid index. */
+FTM_API int ftm_ftw_open(const char* dir, ftm_ftw** out);
+/* FtwIndex::parse alone, from the document text: entry / pieces work, reads fail (no shard is open) */
+FTM_API int ftm_ftw_parse(const char* json_doc, ftm_ftw** out);
+FTM_API void ftm_ftw_close(ftm_ftw* f);
+/* message of the last failed call on f; ftm_ftw_last_error(NULL): of the last failed open / parse on this thread */
+FTM_API const char* ftm_ftw_last_error(const ftm_ftw* f);
+FTM_API int64_t ftm_ftw_tensor_count(const ftm_ftw* f);
+FTM_API int64_t ftm_ftw_shard_count(const ftm_ftw* f);
+FTM_API uint64_t ftm_ftw_total_bytes(const ftm_ftw* f);
+/* FtwIndex::entry (ftw.rs:254-256): FTM_ERR_MISSING when the index has no such tensor.  shape receives at most
+ * eight dimensions; is_experts_bank = the entry's kind is "experts_bank". */
+FTM_API int ftm_ftw_entry(const ftm_ftw* f, const char* name, uint64_t* global_off, uint64_t* nbytes, uint64_t shape[8],
+                          int32_t* ndim, int32_t* is_experts_bank);
+/* FtwIndex::pieces (ftw.rs:262-302): the per-shard copies of the byte range [global_off, global_off + nbytes);
+ * *n_pieces receives their number, the arrays at most max_pieces of them. */
+FTM_API int ftm_ftw_pieces(const ftm_ftw* f, uint64_t global_off, uint64_t nbytes, int32_t max_pieces, int32_t* shard_index,
+                           uint64_t* file_off, uint64_t* dest_off, uint64_t* length, int32_t* n_pieces);
+/* WeightsReader::read_range (ftw.rs:505-520) */
+FTM_API int ftm_ftw_read_range(ftm_ftw* f, uint64_t global_off, uint64_t nbytes, void* dst, size_t dst_len);
+/* FtwBanks::slab (src/infrastructure/banks.rs:95-199): one expert's packed / scale / global bytes of
+ * `{prefix}{gate_up|down}_{packed,scale,global}#L{layer:05}` (part 0 = gate_up, 1 = down; prefix NULL or ""
+ * for the target's layers, "draft_" for the MTP draft's).  cap / lens: capacity of the three buffers and the
+ * bytes written.  FTM_ERR_MISSING for a layer without entries, FTM_ERR_BAD when the expert is past the bank
+ * or the three entries do not agree with the packed entry's shape, FTM_ERR_READ for a failed read. */
+FTM_API int ftm_ftw_expert_slab(ftm_ftw* f, const char* bank_prefix, int32_t layer, uint32_t expert, int32_t part,
+                                uint8_t* packed, uint8_t* scale, uint8_t* global, const size_t cap[3], size_t lens[3],
+                                int32_t* rows_out, int32_t* cols_out);
+/* Experts first_expert .. first_expert + n_experts - 1 of `layer` straight from the checkpoint into slots
+ * slot0, slot0 + 1, ..: FtwBanks::slab for both parts, then ExpertSlotStore::load (cuda_moe.rs:552-576).
+ * Synchronous.  The reference stages experts on demand because they do not fit its card; with every expert
+ * resident this is the whole load path. */
+FTM_API int ftm_load_layer_from_ftw(ftm_handle* h, ftm_ftw* f, const char* bank_prefix, int32_t layer, int32_t first_expert,
+                                    int32_t n_experts, int32_t slot0);
+
 /* ---- per-kernel timing (the reference's FT_PROFILE stage timer, src/infrastructure/profile.rs:1-14) */
 /* While enabled, every kernel launch of h is bracketed by CUDA events on its stream.  Enabling
  * resets the accumulators; both calls synchronise the device.  Not for use under stream capture. */
