@@ -305,8 +305,8 @@ def roofline_of(prof, U, T, nl, pk):
              "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
              "peak_source": pk["which"], "frac_of_nominal_8000": achieved / 8000.0,
              "traffic": None,
-             "traffic_source": "not captured in this run; profiles/expert_mma_gate_up_T64.md holds the ncu capture of this "
-                               "kernel (dram bytes read + written against the algorithmic bytes of the same launch)",
+             "traffic_source": "not captured in this run; profiles/expert_ldg_T64.md holds the ncu capture of this "
+                               "kernel (dram bytes read + written against the algorithmic bytes of the same launch: 1.04x)",
              "distinct_experts": U, "bytes_per_launch": gu_bytes, "us_per_launch": us,
              "expert_bytes_touched_per_cycle": touched, "l2_resident": resident, "kernels": kernels}
         if "expert_down" in prof:
