@@ -769,3 +769,35 @@ def test_four_layer_stack_matches_the_chained_cpu_path():
     if chain_ok:   # a routing tie broken differently by a one-ulp input difference would fork the two chains
         check_close_abs(got, chain, rel_l2=1e-2, max_abs=5e-2)
     moe.close()
+
+
+# ------------------------------------------------------------------ steps of one or two tokens
+@pytest.mark.parametrize("case", ["one-token", "two-tokens-shared-experts", "sixteen-routes-one-slot", "missing-slots"])
+def test_small_steps_build_their_plan_inside_the_expert_kernels(full, case):
+    """At most 16 routes: no plan kernel, every CTA ranks the routes itself and four warps split K.  Routes that
+    share an expert (two tokens per group), a slot with more than eight routes (two groups of one slot) and
+    routes without a resident expert, against the CPU path and against the per-route scalar kernels."""
+    lay, moe, ol = full
+    rng = np.random.default_rng(17)
+    tokens = 1 if case == "one-token" else 2
+    xb = pkg.synth.make_x(8800 + tokens, tokens, lay.hidden)
+    xf = pkg.synth.bf16_bits_to_f32(xb)
+    if case == "one-token":
+        routes = rng.permutation(lay.experts)[:lay.top_k].astype(np.int32)
+    elif case == "two-tokens-shared-experts":
+        first = rng.permutation(lay.experts)[:lay.top_k].astype(np.int32)
+        second = first.copy()
+        second[:3] = (first[:3] + 100) % lay.experts         # five experts shared by both tokens
+        routes = np.concatenate([first, second[::-1]])
+    elif case == "sixteen-routes-one-slot":
+        routes = np.full(16, 5, np.int32)                      # slot ids are not required to differ per token here
+    else:
+        routes = rng.permutation(lay.experts)[:16].astype(np.int32)
+        routes[[0, 7, 9]] = -1
+    w = rng.uniform(0.05, 0.5, routes.size).astype(np.float32)
+    out = torch.empty((tokens, lay.hidden), dtype=torch.float32, device=dev())
+    moe.grouped_moe_dev(lay.hidden, lay.inter, lay.top_k, bf16_dev(xb), routes, torch.from_numpy(w).to(dev()), out)
+    moe.sync_status()
+    want = o.grouped_moe_reference(ol.banks, lay.hidden, lay.inter, xf, lay.top_k, routes, w)
+    rel, _ = check_close(out.cpu().numpy(), want)
+    assert rel < 5e-3, rel
