@@ -62,6 +62,10 @@ def parse():
                          "exchanges run under compute; 1 = the plain schedule")
     ap.add_argument("--ep-exchange", default="p2p", choices=["p2p", "nccl"],
                     help="N > 1: dispatch / return by this library's kernels over peer memory, or by NCCL all-to-all")
+    ap.add_argument("--ep-fused-return", action="store_true",
+                    help="N > 1, peer-memory exchange: the owner's down GEMM stores its rows into the sources' buffers itself")
+    ap.add_argument("--ep-micro", type=int, default=1,
+                    help="N > 1, peer-memory exchange: micro-batches per step (dispatch of one under the experts of the one before)")
     ap.add_argument("--ep-comm-sms", type=int, default=16, help="N > 1: SMs left to the exchange kernels when overlapping")
     ap.add_argument("--zipf", type=float, default=None,
                     help="add a per-expert Zipf(alpha) popularity bias to the router logits (skewed expert counts)")
@@ -577,7 +581,8 @@ def run_ep(args, pkg, dev, world, rank, local):
     nlayers = min(max(1, args.layers), 2)
     per = EXPERTS // world
     be = ep.LibBackend(local, rank, world, pkg.ExpertShapes(HIDDEN, INTER), experts=EXPERTS, layers=nlayers,
-                       top_k=TOP_K, shared_inter=SHARED, max_tokens=T, comm_sms=args.ep_comm_sms if (args.ep_chunks > 1 and args.ep_exchange == "nccl") else 0)
+                       top_k=TOP_K, shared_inter=SHARED, max_tokens=T, comm_sms=args.ep_comm_sms if ((args.ep_chunks > 1 and args.ep_exchange == "nccl") or
+                                                    (args.ep_micro > 1 and args.ep_exchange == "p2p")) else 0)
     dense, xs = [], []
     for l in range(nlayers):
         pkg.synth.fill_banks_on_device(be.owner, l, seed=1000 + 977 * rank + l, experts=per, slot0=l * per,
@@ -603,12 +608,16 @@ def run_ep(args, pkg, dev, world, rank, local):
             p2p = False
             exchange_note = exchange_note or "peer exchange unavailable on another rank; NCCL all-to-all used"
 
+    micro = max(1, args.ep_micro)
+
     def step(i, record=None, x=None, o=None):
         l = i % nlayers
         g, su, sd, sg = dense[l]
         xin, dst = (xs[l] if x is None else x), (out if o is None else o)
         if p2p:
-            return layer.forward_p2p(l, xin, g, su, sd, sg, dst, record=record)
+            # the phase breakdown (record set) runs the step as one batch, every phase after the one before
+            return layer.forward_p2p(l, xin, g, su, sd, sg, dst, record=record, micro=1 if record else micro,
+                                     fused_return=args.ep_fused_return)
         if record is None and chunks > 1:
             return layer.forward_overlapped(l, xin, g, su, sd, sg, dst, chunks=chunks)
         return layer.forward(l, xin, g, su, sd, sg, dst, record=record)
@@ -784,7 +793,10 @@ def run_ep(args, pkg, dev, world, rank, local):
             "data": "synthetic",
             "config": {"workload": f"expert-parallel layer, T={T} tokens per GPU, {EXPERTS} experts split {per} per GPU, "
                                    f"top-{TOP_K}, {'uniform' if args.zipf is None else f'Zipf({args.zipf})-skewed'} routing, " +
-                                   ("dispatch / return by peer-memory kernels over NVLink" if p2p else
+                                   (f"dispatch by a peer-memory kernel, return by {'the down GEMM itself' if args.ep_fused_return else 'a kernel reading the GEMM rows in place'} "
+                                    f"(plain peer stores over NVLink), {micro} micro-batch(es) "
+                                    f"per step (dispatch of one under the experts of the one before, {args.ep_comm_sms if micro > 1 else 0} SMs "
+                                    f"left to the exchange)" if p2p else
                                     f"NCCL all-to-all dispatch/combine, {chunks} overlapped expert range(s) per owner"),
                        "l2": f"inputs larger than L2: {nlayers} layers cycled, {T * TOP_K} routes x 4 KB rows per step",
                        "timed_region": "whole block incl. both all-to-alls, CUDA events, max over ranks"},
@@ -794,7 +806,7 @@ def run_ep(args, pkg, dev, world, rank, local):
                    "efficiency_vs_1gpu": (world * T * K / (total_ms * 1e-3) / world / single_tps) if single_tps else None,
                    "efficiency_note": "tokens/s per GPU of this run over tokens/s of the same 8192-token block on one GPU "
                                       "with all 256 experts resident (rank 0, measured in this run before the timed steps)",
-                   "exchange_note": exchange_note,"phases_of": "one step, marks after each phase" if p2p else "one step of the plain schedule (every phase waits for the one before)",
+                   "exchange_note": exchange_note,"phases_of": "one step run as ONE batch, marks after each phase" if p2p else "one step of the plain schedule (every phase waits for the one before)",
                    "phases_ms_max_over_ranks": phases, "unpipelined_ms_per_step": sum(phases.values()),
                    "exchange_ms_unpipelined": phases["dispatch_a2a_ms"] + phases["return_a2a_ms"],
                    "max_routes_sent_off_rank": float(sent.item()),

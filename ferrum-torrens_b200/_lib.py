@@ -80,6 +80,7 @@ _PROTOS = {
     "ftm_ep_dispatch": (_int, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, C.c_int64, _vp]),
     "ftm_ep_return": (_int, [_vp, _vp, _i32, _i32, _i32, _vp, _vp, C.c_int64, _vp]),
     "ftm_ep_experts_sorted": (_int, [_vp, _i32, _vp, _vp, _vp, _i32, _vp]),
+    "ftm_ep_experts_return": (_int, [_vp, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp, C.c_int64, _vp]),
     "ftm_ep_return_sorted": (_int, [_vp, _i32, _i32, _i32, _vp, _vp, C.c_int64, _vp]),
     "ftm_ep_combine": (_int, [_vp, _vp, _int, _vp, _vp, _vp, _i32, _vp, _int, _vp]),
     "ftm_profile_enable": (_int, [_vp, _int]),

@@ -277,7 +277,7 @@ constexpr int kGroupedMinRoutes = 2048;
 // `join`, when set, is waited on just before the pass that reads `shared`.
 int run_routed(ftm_handle* h, const void* x, int x_dtype, const void* expert_ids, int ids_dtype, int layer,
                const float* weights, int tokens, const float* shared, const float* se_gate, cudaEvent_t join,
-               void* out, int out_dtype, int path, cudaStream_t s) {
+               void* out, int out_dtype, int path, cudaStream_t s, const EpReturnTo* ret = nullptr) {
     BankView b = bank_view(h);
     const int routes = tokens * h->cfg.top_k;
     // large batches (or FTM_PATH_GROUPED): the tcgen05 grouped GEMM, which also does the combine
@@ -291,7 +291,7 @@ int run_routed(ftm_handle* h, const void* x, int x_dtype, const void* expert_ids
         DecodeRoutes rt{expert_ids ? nullptr : h->route_slot, expert_ids, ids_dtype, layer, h->cfg.experts,
                         (int)h->slot_for_id.size(), h->d_slot_for_id, h->route_slot, h->flags + 1};
         int n = launch_prefill_umma(b, x, x_dtype, rt, weights, tokens, h->cfg.top_k, sc, h->sm_count, shared, se_gate, join,
-                                    out, out_dtype, h->maps, h->ctx(s));
+                                    out, out_dtype, h->maps, h->ctx(s), ret);
         if (n < 0) return fail(h, FTM_ERR_CUDA, "moe: driver: cuTensorMapEncodeTiled failed");
         h->launches += n;
         return FTM_OK;
@@ -942,6 +942,35 @@ FTM_API int ftm_ep_experts_sorted(ftm_handle* h, int32_t layer, const void* x_bf
         return fail(h, FTM_ERR_NOT_SUPPORTED, "moe: ep_experts_sorted: %d rows take the ordinary staged call", rows);
     rc = run_routed(h, x_bf16, FTM_BF16, expert_ids, FTM_I32, layer, weights, rows, nullptr, nullptr, nullptr, nullptr,
                     FTM_BF16, FTM_PATH_GROUPED, pick(h, stream));
+    if (rc != FTM_OK) return rc;
+    CU(h, cudaGetLastError());
+    h->steps++;
+    return FTM_OK;
+}
+
+FTM_API int ftm_ep_experts_return(ftm_handle* h, int32_t layer, const void* x_bf16, const int32_t* expert_ids,
+                                  const float* weights, int32_t rows, int32_t ep_size, int32_t ep_rank,
+                                  const int32_t* counts_all, const uint64_t* peer_back, int64_t capacity_rows,
+                                  void* stream) {
+    if (!h) return FTM_ERR_BAD;
+    std::lock_guard<std::mutex> lk(h->mu);
+    DeviceGuard dg(h->cfg.ordinal);
+    if (!x_bf16 || !expert_ids || !weights || !counts_all || !peer_back)
+        return fail(h, FTM_ERR_BAD, "moe: ep_experts_return: null buffer");
+    if (layer < 0 || layer >= h->cfg.layers) return fail(h, FTM_ERR_BAD, "moe: layer %d of %d", layer, h->cfg.layers);
+    if (h->cfg.top_k != 1)
+        return fail(h, FTM_ERR_BAD, "moe: ep_experts_return needs an owner adapter (top_k 1), this one has top_k %d", h->cfg.top_k);
+    if (ep_size < 1 || ep_size > 32 || ep_rank < 0 || ep_rank >= ep_size || capacity_rows < 1)
+        return fail(h, FTM_ERR_BAD, "moe: ep_experts_return: rank %d of %d, capacity %lld", ep_rank, ep_size, (long long)capacity_rows);
+    int rc = check_tokens(h, rows, 1);
+    if (rc != FTM_OK) return rc;
+    // only the grouped GEMM's epilogue stores to the source ranks; small steps take the ordinary call and ftm_ep_return
+    if (rows <= kGroupedMinRoutes || !h->maps.ok ||
+        !prefill_umma_supported(h->cfg.hidden, h->cfg.inter, h->cfg.slots, h->cfg.experts, true))
+        return fail(h, FTM_ERR_NOT_SUPPORTED, "moe: ep_experts_return: %d rows take the ordinary staged call", rows);
+    EpReturnTo ret{ep_size, ep_rank, counts_all, peer_back, (long long)capacity_rows};
+    rc = run_routed(h, x_bf16, FTM_BF16, expert_ids, FTM_I32, layer, weights, rows, nullptr, nullptr, nullptr, nullptr,
+                    FTM_BF16, FTM_PATH_GROUPED, pick(h, stream), &ret);
     if (rc != FTM_OK) return rc;
     CU(h, cudaGetLastError());
     h->steps++;

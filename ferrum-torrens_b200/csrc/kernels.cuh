@@ -167,12 +167,21 @@ struct PrefillMaps {
     CUtensorMap x[4], h[4], gp, gs, dp, ds;
     bool ok = false;
 };
+// expert-parallel owner: where the down GEMM stores its finished rows instead of the adapter's own scratch.
+// Received row i came from source rank s at row r of that rank's send order; its output row goes to row r of
+// peer_back[s] ([capacity, hidden] bf16 in that rank's memory), by plain stores of the GEMM's epilogue.
+struct EpReturnTo {
+    int world, rank;
+    const int32_t* counts_all;   // [world, world] routes source -> owner
+    const uint64_t* peer_back;   // [world] base addresses of the back buffers
+    long long capacity;          // rows of every back buffer
+};
 bool prefill_umma_supported(int hidden, int inter, int slots, int experts, bool have_expert_ids);
 bool prefill_build_maps(const BankView& b, const __half* xg, const __half* ic2h, size_t rows, PrefillMaps* out);
 int launch_prefill_umma(const BankView& b, const void* x, int x_dtype, const DecodeRoutes& rt,
                         const float* route_weight, int tokens, int top_k, PrefillScratch sc, int sm_count,
                         const float* shared, const float* se_gate, cudaEvent_t join, void* out, int out_dtype,
-                        const PrefillMaps& maps, const Ctx& c);
+                        const PrefillMaps& maps, const Ctx& c, const EpReturnTo* ret = nullptr);
 
 // shared_expert.cu
 int launch_shared_expert(const __nv_bfloat16* x, int tokens, int hidden, int shared_inter,

@@ -186,6 +186,7 @@ struct UmmaArgs {
     float* ic1;                // gate_up out [rows, 2 * inter] f32 (sorted rows): gate | up, before silu
     void* y;                   // down out [rows, hidden], bf16 or f32 (sorted rows)
     int y_f32;
+    const uint64_t* row_dest;  // down only, optional: address of the bf16 output row of every sorted row (0 = none)
     int32_t* err;
     int N;                     // rows of the weight matrix (2 * inter or hidden)
 };
@@ -459,8 +460,11 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
                                 const float got = __shfl_xor_sync(0xffffffffu, give, 1);
                                 const int tok = c0 + j + (lane & 1);
                                 const __nv_bfloat162 pr = (lane & 1) ? __floats2bfloat162_rn(got, mine) : __floats2bfloat162_rn(mine, got);
-                                if (tok < cnt)
-                                    *reinterpret_cast<__nv_bfloat162*>(dst + (size_t)(pos0 + tok) * a.N + (wrow & ~1)) = pr;
+                                if (tok < cnt) {
+                                    __nv_bfloat16* row = dst + (size_t)(pos0 + tok) * a.N;
+                                    if (a.row_dest) row = reinterpret_cast<__nv_bfloat16*>(__ldg(a.row_dest + pos0 + tok));
+                                    if (row) *reinterpret_cast<__nv_bfloat162*>(row + (wrow & ~1)) = pr;
+                                }
                             }
                         }
                     }
@@ -498,6 +502,46 @@ __global__ void prefill_invert_kernel(const int32_t* __restrict__ route_idx, con
                                       int32_t* __restrict__ pos_of_route) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < *n_sorted) pos_of_route[route_idx[i]] = i;
+}
+
+// Expert-parallel owner, one thread per received row i: the address of its output row in the source rank's back
+// buffer goes into row_dest at the row's sorted position, where the down GEMM's epilogue finds it.  A row whose
+// expert is not resident takes no part in the GEMM: its output row is zero-filled here.
+__global__ void __launch_bounds__(128)
+ep_row_dest_kernel(const int32_t* __restrict__ pos_of_route, const int32_t* __restrict__ route_slot, int n, int H,
+                   int world, int rank, const int32_t* __restrict__ counts_all, const uint64_t* __restrict__ peer_back,
+                   long long capacity, uint64_t* __restrict__ row_dest, int32_t* err) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    const int lane = threadIdx.x & 31;
+    uint64_t dest = 0;
+    bool dropped = false;
+    if (i < n) {
+        int s = 0, roff = 0;
+        for (; s < world; s++) {
+            const int c = counts_all[s * world + rank];
+            if (i < roff + c) break;
+            roff += c;
+        }
+        long long row = i - roff;
+        if (s < world)
+            for (int p = 0; p < rank; p++) row += counts_all[s * world + p];
+        if (s >= world || row < 0 || row >= capacity) {
+            atomicExch(err, 4);
+        } else {
+            dest = peer_back[s] + (uint64_t)row * H * sizeof(__nv_bfloat16);
+            if (route_slot[i] < 0)
+                dropped = true;
+            else
+                row_dest[pos_of_route[i]] = dest;
+        }
+    }
+    unsigned todo = __ballot_sync(0xffffffffu, dropped);
+    while (todo) {
+        const int src = __ffs(todo) - 1;
+        todo &= todo - 1;
+        uint4* const z = reinterpret_cast<uint4*>(__shfl_sync(0xffffffffu, dest, src));
+        for (int c = lane; c < H / 8; c += 32) z[c] = make_uint4(0, 0, 0, 0);
+    }
 }
 
 // out[t] = se_gate[t] * shared[t] + sum over the resident routes j of y[pos_of_route[t*k + j]], j ascending
@@ -584,7 +628,7 @@ bool prefill_umma_supported(int hidden, int inter, int slots, int experts, bool 
 int launch_prefill_umma(const BankView& b, const void* x, int x_dtype, const DecodeRoutes& rt,
                         const float* route_weight, int tokens, int top_k, PrefillScratch sc, int sm_count,
                         const float* shared, const float* se_gate, cudaEvent_t join, void* out, int out_dtype,
-                        const PrefillMaps& maps, const Ctx& c) {
+                        const PrefillMaps& maps, const Ctx& c, const EpReturnTo* ret) {
     const int routes = tokens * top_k;
     int launches = 0;
     // 1. buckets, stable: by expert id of the layer (serving call) or by slot id
@@ -636,10 +680,25 @@ int launch_prefill_umma(const BankView& b, const void* x, int x_dtype, const Dec
     c.end();
     a.global = b.dn_global; a.row_scale = sc.row_scale2;
     a.route_weight = route_weight; a.y = sc.y; a.y_f32 = (out_dtype == 1); a.N = b.hidden;
+    if (ret) {
+        // the finished rows go straight to their source ranks: the row addresses live in the scratch the rows
+        // themselves would have taken
+        uint64_t* const row_dest = reinterpret_cast<uint64_t*>(sc.y);
+        c.begin(K_EP_COMBINE);
+        prefill_invert_kernel<<<(routes + 255) / 256, 256, 0, c.s>>>(sc.route_idx, sc.seg + nbins, sc.pos_of_route);
+        ep_row_dest_kernel<<<(routes + 127) / 128, 128, 0, c.s>>>(sc.pos_of_route, route_slot, routes, b.hidden, ret->world, ret->rank,
+                                                             ret->counts_all, ret->peer_back, ret->capacity, row_dest, sc.err);
+        c.end();
+        launches += 2;
+        a.row_dest = row_dest;
+        a.y = nullptr;
+        a.y_f32 = 0;
+    }
     c.begin(K_GROUPED_DOWN);
     umma_grouped_gemm_kernel<false, 512><<<sm_count, kThreads, kUmmaSmem, c.s>>>(map_h, map_dp, map_ds, a);
     c.end();
     launches += 3;
+    if (ret) return launches;
     // 4. un-permute and sum in route order; routes of experts that are not resident are skipped.  Without `out`
     // the rows stay sorted by expert (sc.y, with sc.pos_of_route to find them): the expert-parallel owner hands
     // them to the return kernel as they are.

@@ -91,6 +91,7 @@ class LibBackend:
         # front: router, shared expert, pack, combine (its banks are never used: one slot)
         self.front = _moe.B200MoE(device, shapes, 1, experts=experts, layers=layers, top_k=top_k,
                                   shared_inter=shared_inter, max_tokens=max_tokens)
+        self._fronts = [self.front]
         # owner: this rank's experts, one received route = one token with top_k = 1
         self.recv_capacity = recv_capacity or 4 * max_tokens * top_k
         self.owner = _moe.B200MoE(device, shapes, layers * self.per, experts=experts, layers=layers, top_k=1,
@@ -109,13 +110,40 @@ class LibBackend:
         g = group if group is not None else dist.group.WORLD
         dev = torch.device("cuda", self.front.device)
         H = self.shapes.hidden
-        self.send_capacity = self.front.max_tokens * self.top_k
+        self.send_capacity = (self.front.max_tokens + 8) * self.top_k
         self.p2p_recv_x = symm.empty((self.recv_capacity, H), dtype=torch.bfloat16, device=dev)
         self.p2p_recv_meta = symm.empty((self.recv_capacity, 2), dtype=torch.int32, device=dev)
         self.p2p_back = symm.empty((self.send_capacity, H), dtype=torch.bfloat16, device=dev)
         self._symm = [symm.rendezvous(t, g.group_name) for t in (self.p2p_recv_x, self.p2p_recv_meta, self.p2p_back)]
         self.peer_x, self.peer_meta, self.peer_back = (h.buffer_ptrs_dev for h in self._symm)
         self._tick = torch.zeros((1,), dtype=torch.int32, device=dev)
+        self._regions = {}
+
+    def micro_fronts(self, micro: int):
+        """One front adapter per micro-batch of forward_p2p: a plan lives in its adapter until its dispatch and
+        combine have read it, so batches in flight at the same time need an adapter each."""
+        while len(self._fronts) < micro:
+            self._fronts.append(_moe.B200MoE(self.front.device, self.shapes, 1, experts=self.experts, layers=self.layers,
+                                             top_k=self.top_k, shared_inter=0, max_tokens=self.front.max_tokens))
+        return self._fronts[:micro]
+
+    def peer_regions(self, micro: int):
+        """Per micro-batch: device tables of every rank's receive-row, receive-meta and back-buffer addresses,
+        offset to that batch's region of the buffers."""
+        if micro not in self._regions:
+            dev = torch.device("cuda", self.front.device)
+            H = self.shapes.hidden
+            rcap, scap = self.recv_capacity // micro, -(-self.front.max_tokens // micro) * self.top_k
+            tabs = []
+            for m in range(micro):
+                row = []
+                for hnd, stride, cap in ((self._symm[0], H * 2, rcap), (self._symm[1], 8, rcap), (self._symm[2], H * 2, scap)):
+                    t = torch.tensor([int(p) + m * cap * stride for p in hnd.buffer_ptrs], dtype=torch.int64, device=dev)
+                    row.append(t)
+                tabs.append(row)
+            self._region_tabs = getattr(self, "_region_tabs", []) + [tabs]     # keeps the tables alive
+            self._regions[micro] = [tuple(t.data_ptr() for t in row) for row in tabs]
+        return self._regions[micro]
 
     def owned(self, expert: int) -> bool:
         return expert // self.per == self.rank
@@ -151,7 +179,8 @@ class LibBackend:
         self.front.ep_combine(y, route_idx, shared, se_gate, out)
 
     def close(self):
-        self.front.close()
+        for f in self._fronts:
+            f.close()
         self.owner.close()
 
 
@@ -185,72 +214,132 @@ class ExpertParallelMoE:
         mark("combined")
         return ids, w
 
-    def forward_p2p(self, layer: int, x, gate_w, sh_gate_up, sh_down, sh_gate, out, record=None):
+    def forward_p2p(self, layer: int, x, gate_w, sh_gate_up, sh_down, sh_gate, out, record=None, micro: int = 1,
+                    fused_return: bool = False):
         """The same block with both exchanges done by this library's own kernels over peer memory: the
         dispatch kernel reads a token's activation row once and stores it straight into the owner's
-        receive buffer (no send buffer, no collective), the return kernel stores every output row at the
-        position its source expects.  The backend must have called enable_peer_exchange().
+        receive buffer (no send buffer, no collective); the return kernel stores every output row at the
+        position its source expects, reading the rows where the grouped GEMM left them (sorted by expert), or,
+        with `fused_return`, the owner's down GEMM stores them there itself (no return pass).  The backend
+        must have called enable_peer_exchange().
 
-            route, plan, all-gather of the counts         one host read-back of the [world, world] counts
-            shared expert (while the host reads back)
-            dispatch kernel (peer stores) | barrier | experts | return kernel (peer stores) | barrier | combine
-        """
+        The step's tokens are cut into `micro` batches with a region of the receive and back buffers each,
+        so that the stores of batch m + 1 cross NVLink (exchange stream) while the owner's GEMMs of batch m
+        run (compute stream):
+
+            compute:   route, plans, all-gather of the counts | experts 0 | experts 1 | ... | barrier | combine
+            exchange:                                dispatch 0, barrier | dispatch 1, barrier | ...
+            side:      shared expert
+
+        One host read-back of the counts per step (the launches are sized by them).  Every rank must pass
+        the same `micro`."""
         mark = record or (lambda name: None)
         b = self.b
         world = self.world
+        T = x.shape[0]
+        micro = max(1, min(int(micro), T))
+        fronts = b.micro_fronts(micro)
+        bounds = [T * m // micro for m in range(micro + 1)]
         ids, w = b.route(x, gate_w)
-        route_idx, counts = b.front.ep_plan(ids, world)
-        counts_all = torch.empty((world * world,), dtype=torch.int32, device=counts.device)
-        dist.all_gather_into_tensor(counts_all, counts, group=self.group)
+        plans = [fronts[m].ep_plan(ids[bounds[m]:bounds[m + 1]], world) for m in range(micro)]
+        counts = torch.cat([c for _, c in plans]) if micro > 1 else plans[0][1]
+        gathered = torch.empty((world * micro * world,), dtype=torch.int32, device=counts.device)
+        dist.all_gather_into_tensor(gathered, counts, group=self.group)
+        # [source, batch, owner] -> one [source, owner] table per batch
+        counts_all = gathered.reshape(world, micro, world).permute(1, 0, 2).contiguous()
+        cur = torch.cuda.current_stream() if x.is_cuda else None
         # the shared expert (tensor cores) runs on a side stream under the dispatch (NVLink stores)
         shared = se_gate = None
         side = None
         if sh_gate_up is not None and x.is_cuda:
-            side = self._side_stream(x.device)
-            side.wait_stream(torch.cuda.current_stream())
+            side = self._side_stream(x.device, "_side")
+            side.wait_stream(cur)
             with torch.cuda.stream(side):
                 shared, se_gate = b.shared(x, sh_gate_up, sh_down, sh_gate)
         elif sh_gate_up is not None:
             shared, se_gate = b.shared(x, sh_gate_up, sh_down, sh_gate)
-        ca = counts_all.reshape(world, world).tolist()            # the one host read-back
-        sc = ca[b.rank]
-        rc = [ca[s][b.rank] for s in range(world)]
-        self.last_counts = (sc, rc)
-        n = sum(rc)
-        if n > b.recv_capacity:
-            raise _moe.bad(f"{n} routes received, the receive buffer was sized for {b.recv_capacity}")
+        ca = counts_all.tolist()                                    # the one host read-back
+        sc = [ca[m][b.rank] for m in range(micro)]
+        rc = [[ca[m][s][b.rank] for s in range(world)] for m in range(micro)]
+        self.last_counts = ([sum(v[p] for v in sc) for p in range(world)], [sum(v[s] for v in rc) for s in range(world)])
+        # a batch holds at most ceil(max_tokens / micro) tokens: its back region is sized for that (the back
+        # buffer has eight tokens of slack for the rounding)
+        if micro > 8:
+            raise _moe.bad(f"{micro} micro-batches: at most 8")
+        recv_cap, send_cap = b.recv_capacity // micro, -(-b.front.max_tokens // micro) * b.top_k
+        for m in range(micro):
+            if sum(rc[m]) > recv_cap:
+                raise _moe.bad(f"{sum(rc[m])} routes received, the receive region was sized for {recv_cap}")
+            if sum(sc[m]) > send_cap:
+                raise _moe.bad(f"{sum(sc[m])} routes sent, the back region was sized for {send_cap}")
+        peers = b.peer_regions(micro)
         mark("packed")
-        b.front.ep_dispatch(x, ids, w, route_idx, world, b.rank, counts_all, b.peer_x, b.peer_meta, b.recv_capacity)
-        self._barrier(b)
-        mark("dispatched")
-        if n:
-            meta = b.p2p_recv_meta[:n]
-            rids, rw = meta[:, 0].contiguous(), meta[:, 1].contiguous().view(torch.float32)
-            # large steps: the return kernel reads the rows where the grouped GEMM left them (sorted by expert)
-            if b.owner.ep_experts_sorted(layer, b.p2p_recv_x[:n], rids, rw):
-                mark("computed")
-                b.owner.ep_return_sorted(n, world, b.rank, counts_all, b.peer_back, b.send_capacity)
+        # exchange stream: every batch's rows go out as soon as the plan is known
+        arrived = []
+        xchg = self._side_stream(x.device, "_xchg") if (micro > 1 and x.is_cuda) else None
+        if xchg is not None:
+            xchg.wait_stream(cur)
+        for m in range(micro):
+            lo, hi = bounds[m], bounds[m + 1]
+            px, pm, _ = peers[m]
+            if xchg is None:
+                fronts[m].ep_dispatch(x[lo:hi], ids[lo:hi], w[lo:hi], plans[m][0], world, b.rank, counts_all[m], px, pm, recv_cap)
+                self._barrier(b)
+                arrived.append(None)
             else:
-                y = b.experts_forward(layer, b.p2p_recv_x[:n], rids, rw)
-                mark("computed")
-                b.owner.ep_return(y, world, b.rank, counts_all, b.peer_back, b.send_capacity)
-        else:
+                with torch.cuda.stream(xchg):
+                    fronts[m].ep_dispatch(x[lo:hi], ids[lo:hi], w[lo:hi], plans[m][0], world, b.rank, counts_all[m], px, pm,
+                                          recv_cap)
+                    self._barrier(b)
+                    ev = torch.cuda.Event()
+                    ev.record(xchg)
+                    arrived.append(ev)
+        computed = False
+        for m in range(micro):
+            if arrived[m] is not None:
+                cur.wait_event(arrived[m])
+            if m == 0:
+                mark("dispatched")
+            n = sum(rc[m])
+            if not n:
+                continue
+            rx = b.p2p_recv_x[m * recv_cap:m * recv_cap + n]
+            meta = b.p2p_recv_meta[m * recv_cap:m * recv_cap + n]
+            rids, rw = meta[:, 0].contiguous(), meta[:, 1].contiguous().view(torch.float32)
+            # large steps: the rows leave from where the grouped GEMM put them (or from its epilogue)
+            if fused_return and b.owner.ep_experts_return(layer, rx, rids, rw, world, b.rank, counts_all[m], peers[m][2],
+                                                          send_cap):
+                continue
+            if b.owner.ep_experts_sorted(layer, rx, rids, rw):
+                if micro == 1:
+                    mark("computed")
+                b.owner.ep_return_sorted(n, world, b.rank, counts_all[m], peers[m][2], send_cap)
+            else:
+                y = b.experts_forward(layer, rx, rids, rw)
+                if micro == 1:
+                    mark("computed")
+                b.owner.ep_return(y, world, b.rank, counts_all[m], peers[m][2], send_cap)
+            computed = micro == 1
+        if not computed:
             mark("computed")
         self._barrier(b)
         mark("returned")
         if side is not None:
-            cur = torch.cuda.current_stream()
             cur.wait_stream(side)
             shared.record_stream(cur)       # allocated on the side stream, read on this one
             se_gate.record_stream(cur)
-        b.combine(b.p2p_back[:sum(sc)], route_idx, shared, se_gate, out)
+        for m in range(micro):
+            lo, hi = bounds[m], bounds[m + 1]
+            fronts[m].ep_combine(b.p2p_back[m * send_cap:m * send_cap + sum(sc[m])], plans[m][0],
+                                 shared[lo:hi] if shared is not None else None,
+                                 se_gate[lo:hi] if se_gate is not None else None, out[lo:hi])
         mark("combined")
         return ids, w
 
-    def _side_stream(self, device):
-        if getattr(self, "_side", None) is None:
-            self._side = torch.cuda.Stream(device=device)
-        return self._side
+    def _side_stream(self, device, name):
+        if getattr(self, name, None) is None:
+            setattr(self, name, torch.cuda.Stream(device=device))
+        return getattr(self, name)
 
     def _barrier(self, b):
         # every rank's stores before this point are complete before any rank goes on

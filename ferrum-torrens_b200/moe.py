@@ -469,6 +469,19 @@ class B200MoE:
         self._check(rc)
         return True
 
+    def ep_experts_return(self, layer: int, x, expert_ids, weights, ep_size: int, ep_rank: int, counts_all, peer_back: int,
+                          capacity_rows: int, stream=None) -> bool:
+        """Owner side: the grouped GEMMs on the received rows, every finished row stored by the down GEMM itself into
+        its source's back buffer.  False when the step is too small for that path (use grouped_moe_staged + ep_return)."""
+        rows = x.numel() // self.shapes.hidden
+        rc = self._lib.ftm_ep_experts_return(self._h, layer, _dev(x, "x"), _dev(expert_ids, "ids"), _dev(weights, "weights"),
+                                             rows, ep_size, ep_rank, _dev(counts_all, "counts_all"), C.c_void_p(peer_back),
+                                             capacity_rows, _stream_ptr(stream))
+        if rc == L.ERR_NOT_SUPPORTED:
+            return False
+        self._check(rc)
+        return True
+
     def ep_return_sorted(self, rows: int, ep_size: int, ep_rank: int, counts_all, peer_back: int, capacity_rows: int,
                          stream=None):
         """Owner side: store the rows ep_experts_sorted left in the adapter into their sources' back buffers."""

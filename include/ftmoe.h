@@ -352,6 +352,15 @@ FTM_API int ftm_ep_experts_sorted(ftm_handle* h, int32_t layer, const void* x_bf
                                   const float* weights, int32_t rows, void* stream);
 FTM_API int ftm_ep_return_sorted(ftm_handle* h, int32_t rows, int32_t ep_size, int32_t ep_rank, const int32_t* counts_all,
                                  const uint64_t* peer_back, int64_t capacity_rows, void* stream);
+/* The owner's step with the return inside it: as ftm_ep_experts_sorted, but the down GEMM's epilogue stores every
+ * finished row straight into row r of peer_back[s], where s is the rank the row came from and r its position in
+ * that rank's send order (plain stores over peer memory while the GEMM runs, no return pass and no copy of the
+ * rows in this GPU's memory).  A received row whose expert is not resident returns zeros.  Same limits and
+ * FTM_ERR_NOT_SUPPORTED rule as ftm_ep_experts_sorted; the caller's barrier follows it as it follows ftm_ep_return. */
+FTM_API int ftm_ep_experts_return(ftm_handle* h, int32_t layer, const void* x_bf16, const int32_t* expert_ids,
+                                  const float* weights, int32_t rows, int32_t ep_size, int32_t ep_rank,
+                                  const int32_t* counts_all, const uint64_t* peer_back, int64_t capacity_rows,
+                                  void* stream);
 FTM_API int ftm_ep_combine(ftm_handle* h, const void* y, int y_dtype, const int32_t* route_idx, const float* shared,
                            const float* se_gate, int32_t tokens, void* out, int out_dtype, void* stream);
 

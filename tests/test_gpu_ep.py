@@ -64,9 +64,10 @@ def _worker(rank, world, port, tokens, q):
         rel = max(rel, float((out2 - want).norm() / want.norm()))
         # both exchanges by the library's own kernels over peer memory (two steps: the buffers are reused)
         be.enable_peer_exchange()
-        for _ in range(2):
+        # (then the step cut into two and three micro-batches, each with its own region of the buffers)
+        for micro, fused in ((1, False), (1, True), (2, False), (3, True)):
             out3 = torch.zeros_like(out)
-            ids3, _ = layer.forward_p2p(0, _bf16(xb, dev), *w, out3)
+            ids3, _ = layer.forward_p2p(0, _bf16(xb, dev), *w, out3, micro=micro, fused_return=fused)
             be.front.sync_status()
             be.owner.sync_status()
             same_ids = same_ids and bool(torch.equal(ids3, want_ids))

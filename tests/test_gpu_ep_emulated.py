@@ -193,7 +193,7 @@ def test_sorted_return_on_the_grouped_gemm_path_emulated():
         fronts[r].ep_dispatch(xs[r], ids, w, route_idx, world, r, counts_all, peer_x.data_ptr(), peer_m.data_ptr(), cap)
     torch.cuda.synchronize()
     results = {}
-    for mode in ("sorted", "plain"):
+    for mode in ("sorted", "fused", "plain"):
         back = [torch.zeros((tokens[r] * Kk, Hh), dtype=torch.bfloat16, device=dev) for r in range(world)]
         peer_back = ptrs(back)
         for r in range(world):
@@ -204,6 +204,9 @@ def test_sorted_return_on_the_grouped_gemm_path_emulated():
             if mode == "sorted":
                 assert owners[r].ep_experts_sorted(0, recv_x[r][:n], rids, rw)
                 owners[r].ep_return_sorted(n, world, r, counts_all, peer_back.data_ptr(), max(tokens) * Kk)
+            elif mode == "fused":
+                assert owners[r].ep_experts_return(0, recv_x[r][:n], rids, rw, world, r, counts_all, peer_back.data_ptr(),
+                                                   max(tokens) * Kk)
             else:
                 y = torch.empty((n, Hh), dtype=torch.bfloat16, device=dev)
                 owners[r].grouped_moe_staged(pkg.MoEDeviceRequest(0, Hh, Ii, 1, recv_x[r][:n], rids.reshape(n, 1),
@@ -215,6 +218,7 @@ def test_sorted_return_on_the_grouped_gemm_path_emulated():
         results[mode] = back
     for r in range(world):
         assert torch.equal(results["sorted"][r], results["plain"][r]), "the same rows, whichever pass stored them"
+        assert torch.equal(results["fused"][r], results["plain"][r]), "the same rows when the GEMM stores them itself"
         ids, w, route_idx, _ = routed[r]
         shared, se_gate = fronts[r].shared_expert(xs[r], dense[1], dense[2], dense[3])
         out = torch.empty((tokens[r], Hh), dtype=torch.float32, device=dev)
