@@ -25,6 +25,9 @@
 //                            coalesced over rows
 //             gate_up writes gate and up (globals and row scale applied) as f32; down applies global,
 //             row scale and route weight and writes one row per route (bf16, or f32 for f32 outputs).
+//             An expert-parallel owner's down GEMM (RET) stores every row at an address of its own (a
+//             peer's back buffer): its epilogue passes 128 rows x 16 tokens through shared memory so that a
+//             token's 128 columns leave as one 256-byte run of 16-byte stores.
 //   rescale   silu(gate) * up -> f16 with a per-route power-of-two scale, between the two GEMMs
 //   combine   out[t] = se_gate[t] * shared[t] + sum_j y[position of route (t, j)], j ascending
 //
@@ -214,7 +217,7 @@ struct XMaps {
 // dequantised weights are the A operand in tensor memory (one lane per weight row, two f16 per 32-bit
 // column), the activation tile is the B operand in shared memory and is read by both row tiles; n is
 // the group's row count rounded up to 16.
-template <bool GATE_UP, int K>
+template <bool GATE_UP, int K, bool RET>
 __global__ void __launch_bounds__(kThreads, 1)
 umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_constant__ CUtensorMap tmap_packed,
                          const __grid_constant__ CUtensorMap tmap_scale, UmmaArgs a) {
@@ -226,6 +229,9 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
     uint64_t* const bars = reinterpret_cast<uint64_t*>(raw_ring + kRawStages * kRawStageBytes);
     uint32_t* const s_tmem = reinterpret_cast<uint32_t*>(bars + 40);
     volatile int* const s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
+    // (RET only) per-token factors [row tile][unit parity][128 tokens], bf16 staging [row tile][parity][16 tokens][128 rows]
+    float* const s_fac = reinterpret_cast<float*>(s_tmem + 16);
+    __nv_bfloat16* const s_stage = reinterpret_cast<__nv_bfloat16*>(s_fac + 4 * kTileTok);
     const uint32_t bar0 = smem_u32(bars);
     auto X_FULL = [&](int s) { return bar0 + 8u * s; };                 // kXStages <= 8
     auto X_EMPTY = [&](int s) { return bar0 + 8u * (8 + s); };
@@ -410,68 +416,157 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
             if (!ok) break;
         }
     } else if (warp >= kWarpEpi0) {
-        // ===================== epilogue (warps 4..7 and 24..27: TMEM lane quarters 0..3) ==============
-        // one thread = one weight row of its row tile; a column = one token of the group.  Lane l keeps
-        // the per-token factors of tokens l, l + 32, l + 64, l + 96 and hands them out by shuffle.
-        const int quarter = warp & 3;
-        uint32_t unit_i = 0;
-        for (int u = blockIdx.x; u < n_units && !*s_abort; u += gridDim.x, unit_i++) {
-            const int4 grp = a.groups[u / n_pairs];
-            const int cnt = grp.z, pos0 = grp.y;
-            const int r = (warp >= kWarpEpi1) ? 1 : 0;
-            const int wrow = (u % n_pairs) * 2 * kTileM + r * kTileM + quarter * 32 + lane;
-            const float gl = f16_global_to_f32(a.global[(size_t)grp.x * a.N + wrow]);
-            float fac[4];
-#pragma unroll
-            for (int q = 0; q < 4; q++) {
-                const int i = q * 32 + lane;
-                float f = 0.f;
-                if (i < cnt) {
-                    f = a.row_scale[pos0 + i];
-                    if (!GATE_UP) f *= a.route_weight[a.route_idx[pos0 + i]];
+        if constexpr (!RET) {
+            // ===================== epilogue (warps 4..7 and 24..27: TMEM lane quarters 0..3) ==============
+            // one thread = one weight row of its row tile; a column = one token of the group.  Lane l keeps
+            // the per-token factors of tokens l, l + 32, l + 64, l + 96 and hands them out by shuffle.
+            const int quarter = warp & 3;
+            uint32_t unit_i = 0;
+            for (int u = blockIdx.x; u < n_units && !*s_abort; u += gridDim.x, unit_i++) {
+                const int4 grp = a.groups[u / n_pairs];
+                const int cnt = grp.z, pos0 = grp.y;
+                const int r = (warp >= kWarpEpi1) ? 1 : 0;
+                const int wrow = (u % n_pairs) * 2 * kTileM + r * kTileM + quarter * 32 + lane;
+                const float gl = f16_global_to_f32(a.global[(size_t)grp.x * a.N + wrow]);
+                float fac[4];
+    #pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    const int i = q * 32 + lane;
+                    float f = 0.f;
+                    if (i < cnt) {
+                        f = a.row_scale[pos0 + i];
+                        if (!GATE_UP) f *= a.route_weight[a.route_idx[pos0 + i]];
+                    }
+                    fac[q] = f;
                 }
-                fac[q] = f;
-            }
-            if (!mbar_wait(ACC_FULL, unit_i & 1, s_abort, a.err)) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            {
-                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + kAccCol0 + r * kTileTok;
-#pragma unroll 1
-                for (int c0 = 0; c0 < cnt; c0 += 16) {      // uniform over the warp
-                    {
-                        float v[16];
-                        tmem_ld16(taddr + c0, v);
-                        tmem_ld_wait();
-                        const float fq = c0 < 32 ? fac[0] : c0 < 64 ? fac[1] : c0 < 96 ? fac[2] : fac[3];
-#pragma unroll
-                        for (int j = 0; j < 16; j++) v[j] = (v[j] * gl) * __shfl_sync(0xffffffffu, fq, (c0 & 31) + j);
-                        if (GATE_UP || a.y_f32) {
-                            float* const dst = GATE_UP ? a.ic1 : reinterpret_cast<float*>(a.y);
-#pragma unroll
-                            for (int j = 0; j < 16; j++)
-                                if (c0 + j < cnt) dst[(size_t)(pos0 + c0 + j) * a.N + wrow] = v[j];
-                        } else {
-                            // bf16 rows: neighbouring lanes swap so that every lane stores a pair of rows of one token
-                            __nv_bfloat16* const dst = reinterpret_cast<__nv_bfloat16*>(a.y);
-#pragma unroll
-                            for (int j = 0; j < 16; j += 2) {
-                                const float mine = (lane & 1) ? v[j + 1] : v[j];
-                                const float give = (lane & 1) ? v[j] : v[j + 1];
-                                const float got = __shfl_xor_sync(0xffffffffu, give, 1);
-                                const int tok = c0 + j + (lane & 1);
-                                const __nv_bfloat162 pr = (lane & 1) ? __floats2bfloat162_rn(got, mine) : __floats2bfloat162_rn(mine, got);
-                                if (tok < cnt) {
-                                    __nv_bfloat16* row = dst + (size_t)(pos0 + tok) * a.N;
-                                    if (a.row_dest) row = reinterpret_cast<__nv_bfloat16*>(__ldg(a.row_dest + pos0 + tok));
-                                    if (row) *reinterpret_cast<__nv_bfloat162*>(row + (wrow & ~1)) = pr;
+                if (!mbar_wait(ACC_FULL, unit_i & 1, s_abort, a.err)) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                {
+                    const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + kAccCol0 + r * kTileTok;
+    #pragma unroll 1
+                    for (int c0 = 0; c0 < cnt; c0 += 16) {      // uniform over the warp
+                        {
+                            float v[16];
+                            tmem_ld16(taddr + c0, v);
+                            tmem_ld_wait();
+                            const float fq = c0 < 32 ? fac[0] : c0 < 64 ? fac[1] : c0 < 96 ? fac[2] : fac[3];
+    #pragma unroll
+                            for (int j = 0; j < 16; j++) v[j] = (v[j] * gl) * __shfl_sync(0xffffffffu, fq, (c0 & 31) + j);
+                            if (GATE_UP || a.y_f32) {
+                                float* const dst = GATE_UP ? a.ic1 : reinterpret_cast<float*>(a.y);
+    #pragma unroll
+                                for (int j = 0; j < 16; j++)
+                                    if (c0 + j < cnt) dst[(size_t)(pos0 + c0 + j) * a.N + wrow] = v[j];
+                            } else {
+                                // bf16 rows: neighbouring lanes swap so that every lane stores a pair of rows of one token
+                                __nv_bfloat16* const dst = reinterpret_cast<__nv_bfloat16*>(a.y);
+    #pragma unroll
+                                for (int j = 0; j < 16; j += 2) {
+                                    const float mine = (lane & 1) ? v[j + 1] : v[j];
+                                    const float give = (lane & 1) ? v[j] : v[j + 1];
+                                    const float got = __shfl_xor_sync(0xffffffffu, give, 1);
+                                    const int tok = c0 + j + (lane & 1);
+                                    const __nv_bfloat162 pr = (lane & 1) ? __floats2bfloat162_rn(got, mine) : __floats2bfloat162_rn(mine, got);
+                                    if (tok < cnt)
+                                        *reinterpret_cast<__nv_bfloat162*>(dst + (size_t)(pos0 + tok) * a.N + (wrow & ~1)) = pr;
                                 }
                             }
                         }
                     }
                 }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                mbar_arrive(ACC_EMPTY);
             }
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(ACC_EMPTY);
+    
+        } else {
+            // ===================== epilogue (warps 4..7 and 24..27: TMEM lane quarters 0..3) ==============
+            // one thread = one weight row of its row tile; a column = one token of the group.  The per-token
+            // factors of a unit are computed once per set (thread t: token t), left in shared memory and read
+            // back as broadcasts; the accumulators are read 32 columns per wait.
+            const int quarter = warp & 3;
+            const int r = (warp >= kWarpEpi1) ? 1 : 0;
+            const int tid = quarter * 32 + lane;
+            uint32_t unit_i = 0, stage_i = 0;
+            for (int u = blockIdx.x; u < n_units; u += gridDim.x, unit_i++) {     // (the abort flag is seen inside the wait)
+                const int4 grp = a.groups[u / n_pairs];
+                const int cnt = grp.z, pos0 = grp.y;
+                const int wrow0 = (u % n_pairs) * 2 * kTileM + r * kTileM;
+                const int wrow = wrow0 + tid;
+                const float gl = f16_global_to_f32(a.global[(size_t)grp.x * a.N + wrow]);
+                float* const fac = s_fac + (r * 2 + (unit_i & 1)) * kTileTok;
+                {
+                    float f = 0.f;
+                    if (tid < cnt) {
+                        f = a.row_scale[pos0 + tid];
+                        if (!GATE_UP) f *= a.route_weight[a.route_idx[pos0 + tid]];
+                    }
+                    fac[tid] = f;
+                }
+                // One answer for the 128 threads of this set: they meet at named barriers below, so none may leave
+                // alone.  The same barrier publishes the factors (their buffer alternates by unit, so one barrier
+                // per unit is enough).
+                const bool mine = mbar_wait(ACC_FULL, unit_i & 1, s_abort, a.err);
+                uint32_t all_ok;
+                asm volatile(
+                    "{\n\t.reg .pred p, q;\n\t"
+                    "setp.ne.u32 q, %1, 0;\n\t"
+                    "bar.red.and.pred p, %2, 128, q;\n\t"
+                    "selp.u32 %0, 1, 0, p;\n\t}"
+                    : "=r"(all_ok)
+                    : "r"((uint32_t)mine), "r"(1 + r)
+                    : "memory");
+                if (!all_ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                {
+                    const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + kAccCol0 + r * kTileTok;
+    #pragma unroll 1
+                    for (int c0 = 0; c0 < cnt; c0 += 32) {      // uniform over the warp
+                        float v[2][16];
+                        tmem_ld16(taddr + c0, v[0]);
+                        tmem_ld16(taddr + c0 + 16, v[1]);
+                        tmem_ld_wait();
+    #pragma unroll
+                        for (int h = 0; h < 2; h++) {
+                            const int cb = c0 + 16 * h;
+                            if (cb >= cnt) break;
+    #pragma unroll
+                            for (int j = 0; j < 16; j += 4) {
+                                const float4 f4 = *reinterpret_cast<const float4*>(fac + cb + j);
+                                v[h][j] = (v[h][j] * gl) * f4.x; v[h][j + 1] = (v[h][j + 1] * gl) * f4.y;
+                                v[h][j + 2] = (v[h][j + 2] * gl) * f4.z; v[h][j + 3] = (v[h][j + 3] * gl) * f4.w;
+                            }
+                            if (GATE_UP || a.y_f32) {
+                                float* const dst = GATE_UP ? a.ic1 : reinterpret_cast<float*>(a.y);
+    #pragma unroll
+                                for (int j = 0; j < 16; j++)
+                                    if (cb + j < cnt) dst[(size_t)(pos0 + cb + j) * a.N + wrow] = v[h][j];
+                            } else {
+                                // bf16 rows: the set's 128 rows x 16 tokens go through shared memory, so that every
+                                // thread stores 16 bytes of one token's row and a token's 128 columns leave as one
+                                // 256-byte run (the layout the peer stores of the expert-parallel return want too)
+                                __nv_bfloat16* const st = s_stage + ((r * 2 + (stage_i & 1)) * 16) * kTileM;
+                                stage_i++;
+    #pragma unroll
+                                for (int j = 0; j < 16; j++) st[j * kTileM + tid] = __float2bfloat16_rn(v[h][j]);
+                                asm volatile("bar.sync %0, 128;" ::"r"(1 + r) : "memory");
+    #pragma unroll
+                                for (int q = 0; q < 2; q++) {
+                                    const int piece = tid + q * 128, tok = cb + piece / 16, c8 = (piece % 16) * 8;
+                                    if (tok < cnt) {
+                                        __nv_bfloat16* const row = reinterpret_cast<__nv_bfloat16*>(__ldg(a.row_dest + pos0 + tok));
+                                        if (row)
+                                            *reinterpret_cast<uint4*>(row + wrow0 + c8) =
+                                                *reinterpret_cast<const uint4*>(st + (piece / 16) * kTileM + c8);
+                                    }
+                                }
+                            }
+                        }
+                    }
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                mbar_arrive(ACC_EMPTY);
+            }
+    
         }
     }
     // drain: nobody frees tensor memory while another role may still touch it
@@ -482,7 +577,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
     }
 }
 
-constexpr size_t kUmmaSmem = 1024 + (size_t)kXStages * kTileBytes + (size_t)kRawStages * kRawStageBytes + 40 * 8 + 64;
+constexpr size_t kUmmaSmem = 1024 + (size_t)kXStages * kTileBytes + (size_t)kRawStages * kRawStageBytes + 40 * 8 + 64 + 4 * kTileTok * sizeof(float) + 4 * 16 * kTileM * sizeof(__nv_bfloat16);
 static_assert(kUmmaSmem <= 227 * 1024, "shared memory of the grouped GEMM CTA");
 
 // f16 matrix [rows, K] row-major, box = 64 k x box_rows, 128-byte swizzle
@@ -666,14 +761,16 @@ int launch_prefill_umma(const BankView& b, const void* x, int x_dtype, const Dec
     }
     const CUtensorMap &map_gp = maps.gp, &map_gs = maps.gs, &map_dp = maps.dp, &map_ds = maps.ds;
     static PerDeviceOnce once_gu, once_dn;
-    allow_dyn_smem(once_gu, umma_grouped_gemm_kernel<true, 2048>, kUmmaSmem);
-    allow_dyn_smem(once_dn, umma_grouped_gemm_kernel<false, 512>, kUmmaSmem);
+    allow_dyn_smem(once_gu, umma_grouped_gemm_kernel<true, 2048, false>, kUmmaSmem);
+    allow_dyn_smem(once_dn, umma_grouped_gemm_kernel<false, 512, false>, kUmmaSmem);
+    static PerDeviceOnce once_ret;
+    allow_dyn_smem(once_ret, umma_grouped_gemm_kernel<false, 512, true>, kUmmaSmem);
     UmmaArgs a{};
     a.groups = sc.groups; a.n_groups = sc.n_groups; a.route_idx = sc.route_idx; a.err = sc.err;
     a.global = b.gu_global; a.row_scale = sc.row_scale;
     a.ic1 = sc.ic1; a.N = 2 * b.inter;
     c.begin(K_GROUPED_GATE_UP);
-    umma_grouped_gemm_kernel<true, 2048><<<sm_count, kThreads, kUmmaSmem, c.s>>>(map_x, map_gp, map_gs, a);
+    umma_grouped_gemm_kernel<true, 2048, false><<<sm_count, kThreads, kUmmaSmem, c.s>>>(map_x, map_gp, map_gs, a);
     c.end();
     c.begin(K_PREFILL_RESCALE);
     prefill_rescale_kernel<<<(routes + 7) / 8, 256, 0, c.s>>>(sc.ic1, sc.seg + nbins, b.inter, sc.ic2h, sc.row_scale2);
@@ -695,7 +792,10 @@ int launch_prefill_umma(const BankView& b, const void* x, int x_dtype, const Dec
         a.y_f32 = 0;
     }
     c.begin(K_GROUPED_DOWN);
-    umma_grouped_gemm_kernel<false, 512><<<sm_count, kThreads, kUmmaSmem, c.s>>>(map_h, map_dp, map_ds, a);
+    if (ret)
+        umma_grouped_gemm_kernel<false, 512, true><<<sm_count, kThreads, kUmmaSmem, c.s>>>(map_h, map_dp, map_ds, a);
+    else
+        umma_grouped_gemm_kernel<false, 512, false><<<sm_count, kThreads, kUmmaSmem, c.s>>>(map_h, map_dp, map_ds, a);
     c.end();
     launches += 3;
     if (ret) return launches;
