@@ -62,8 +62,8 @@ def parse():
                          "exchanges run under compute; 1 = the plain schedule")
     ap.add_argument("--ep-exchange", default="p2p", choices=["p2p", "nccl"],
                     help="N > 1: dispatch / return by this library's kernels over peer memory, or by NCCL all-to-all")
-    ap.add_argument("--ep-fused-return", action="store_true",
-                    help="N > 1, peer-memory exchange: the owner's down GEMM stores its rows into the sources' buffers itself")
+    ap.add_argument("--ep-separate-return", action="store_true",
+                    help="N > 1, peer-memory exchange: return the rows by a kernel of its own instead of the owner's down GEMM")
     ap.add_argument("--ep-micro", type=int, default=1,
                     help="N > 1, peer-memory exchange: micro-batches per step (dispatch of one under the experts of the one before)")
     ap.add_argument("--ep-comm-sms", type=int, default=16, help="N > 1: SMs left to the exchange kernels when overlapping")
@@ -617,7 +617,7 @@ def run_ep(args, pkg, dev, world, rank, local):
         if p2p:
             # the phase breakdown (record set) runs the step as one batch, every phase after the one before
             return layer.forward_p2p(l, xin, g, su, sd, sg, dst, record=record, micro=1 if record else micro,
-                                     fused_return=args.ep_fused_return)
+                                     fused_return=not args.ep_separate_return)
         if record is None and chunks > 1:
             return layer.forward_overlapped(l, xin, g, su, sd, sg, dst, chunks=chunks)
         return layer.forward(l, xin, g, su, sd, sg, dst, record=record)
@@ -793,7 +793,7 @@ def run_ep(args, pkg, dev, world, rank, local):
             "data": "synthetic",
             "config": {"workload": f"expert-parallel layer, T={T} tokens per GPU, {EXPERTS} experts split {per} per GPU, "
                                    f"top-{TOP_K}, {'uniform' if args.zipf is None else f'Zipf({args.zipf})-skewed'} routing, " +
-                                   (f"dispatch by a peer-memory kernel, return by {'the down GEMM itself' if args.ep_fused_return else 'a kernel reading the GEMM rows in place'} "
+                                   (f"dispatch by a peer-memory kernel, return by {'the down GEMM itself' if not args.ep_separate_return else 'a kernel reading the GEMM rows in place'} "
                                     f"(plain peer stores over NVLink), {micro} micro-batch(es) "
                                     f"per step (dispatch of one under the experts of the one before, {args.ep_comm_sms if micro > 1 else 0} SMs "
                                     f"left to the exchange)" if p2p else

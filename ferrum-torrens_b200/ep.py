@@ -215,13 +215,13 @@ class ExpertParallelMoE:
         return ids, w
 
     def forward_p2p(self, layer: int, x, gate_w, sh_gate_up, sh_down, sh_gate, out, record=None, micro: int = 1,
-                    fused_return: bool = False):
+                    fused_return: bool = True):
         """The same block with both exchanges done by this library's own kernels over peer memory: the
         dispatch kernel reads a token's activation row once and stores it straight into the owner's
         receive buffer (no send buffer, no collective); the return kernel stores every output row at the
-        position its source expects, reading the rows where the grouped GEMM left them (sorted by expert), or,
-        with `fused_return`, the owner's down GEMM stores them there itself (no return pass).  The backend
-        must have called enable_peer_exchange().
+        position its source expects: with `fused_return` (large steps) the owner's down GEMM stores them there
+        itself, 16 bytes per thread, while it runs; otherwise a return kernel reads the rows where the grouped
+        GEMM left them (sorted by expert).  The backend must have called enable_peer_exchange().
 
         The step's tokens are cut into `micro` batches with a region of the receive and back buffers each,
         so that the stores of batch m + 1 cross NVLink (exchange stream) while the owner's GEMMs of batch m
