@@ -21,8 +21,11 @@
 //                            rounded up to 16, K = 16 per instruction, f16 x f16 -> f32 in TMEM), commit
 //                            to mbarriers
 //               warps 4..7, 24..27  epilogue, one set per row tile: tcgen05.ld of the accumulators while
-//                            the next unit's mainloop runs; a thread owns a weight row, so stores are
-//                            coalesced over rows
+//                            the dequantisers already convert the next unit; a thread owns a weight row,
+//                            so stores are coalesced over rows
+//             The down GEMM (K = 512: a mainloop of eight pieces against an epilogue of the same length)
+//             runs two dequantiser sets (warps 8..15, two weight buffers each) and gives warps 16..23
+//             to the epilogue: two sets per row tile, alternate 16-token steps.
 //             gate_up writes gate and up (globals and row scale applied) as f32; down applies global,
 //             row scale and route weight and writes one row per route (bf16, or f32 for f32 outputs).
 //             An expert-parallel owner's down GEMM (RET) stores every row at an address of its own (a
@@ -196,14 +199,13 @@ struct UmmaArgs {
 
 // warp roles of the GEMM CTA (28 warps)
 constexpr int kWarpActTma = 0, kWarpMma = 1, kWarpRawTma = 2, kWarpMma1 = 3, kWarpEpi0 = 4, kWarpDeq0 = 8;
-constexpr int kEpiWarps = 8;          // warps 4..7 read row tile 0, warps 24..27 row tile 1
-constexpr int kWarpEpi1 = 24;
-constexpr int kDeqSets = 4;                    // dequantiser sets of 4 warps (128 threads = 128 weight rows)
+constexpr int kWarpEpi1 = 24;         // warps 4..7 read row tile 0, warps 24..27 row tile 1
+constexpr int kMaxDeqSets = 4;                 // dequantiser sets of 4 warps (128 threads = 128 weight rows)
 constexpr int kRawStages = 6;
 constexpr int kRawPackedBytes = kTileM * 128;  // two chunks (256 k): 128 weight rows x 128 bytes, 128-byte swizzle
 constexpr int kRawScaleBytes = kTileM * 16;    // 128 rows x 16 scale bytes (256 k)
 constexpr int kRawStageBytes = kRawPackedBytes + kRawScaleBytes;
-constexpr int kWBufs = kDeqSets;               // dequantised weight chunks in tensor memory, 64 columns each
+constexpr int kWBufs = kMaxDeqSets;            // dequantised weight chunks in tensor memory, 64 columns each
 constexpr int kWCols = 64;
 constexpr int kAccCol0 = kWBufs * kWCols;      // accumulators: a ring of two tiles of 128 f32 columns behind them
 
@@ -221,6 +223,14 @@ template <bool GATE_UP, int K, bool RET>
 __global__ void __launch_bounds__(kThreads, 1)
 umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_constant__ CUtensorMap tmap_packed,
                          const __grid_constant__ CUtensorMap tmap_scale, UmmaArgs a) {
+    // Role map.  gate_up (K = 2048, 32 pieces per unit) keeps four dequantiser sets with one weight buffer
+    // each and two epilogue sets.  down (K = 512) has eight pieces per unit and an epilogue as long as its
+    // mainloop: two dequantiser sets with two buffers each (one being filled while the other is multiplied)
+    // and four epilogue sets, two per row tile, each taking every other 16-token step.  The owner's
+    // variant (RET) keeps the gate_up map: its epilogue sets meet at named barriers around shared staging.
+    constexpr int kDeqSets = (GATE_UP || RET) ? 4 : 2;
+    constexpr int kEpiSets = (GATE_UP || RET) ? 2 : 4;
+    constexpr int kWarpEpi2 = kWarpDeq0 + 4 * kDeqSets;     // down: warps 16..19 row tile 0, 20..23 row tile 1
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment for the swizzled tiles
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -256,7 +266,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
             mbar_init(W_FREE(s), 1);
         }
         mbar_init(ACC_FULL, 2);
-        mbar_init(ACC_EMPTY, kEpiWarps * 32);
+        mbar_init(ACC_EMPTY, kEpiSets * 128);
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -273,6 +283,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
     constexpr int kChunks = K / 128;
     constexpr int kItems = 2 * kChunks;   // (chunk, row tile) pieces of a unit, one weight buffer each
     static_assert(kItems % kDeqSets == 0, "every dequantiser set sees the same pieces of every unit");
+    static_assert(kWBufs % kDeqSets == 0, "a weight buffer belongs to one dequantiser set");
     const int n_pairs = a.N / (2 * kTileM);
     const int n_units = *a.n_groups * n_pairs;
 
@@ -364,7 +375,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
                 __syncwarp();
             }
         }
-    } else if (warp >= kWarpDeq0 && warp < kWarpEpi1) {
+    } else if (warp >= kWarpDeq0 && warp < kWarpEpi2) {
         // ===================== dequantisers: raw ring -> f16 weights in tensor memory ================
         // Four sets of four warps; set s takes the pieces w = s (mod 4) of every unit (w = 2 * chunk +
         // row tile) and owns weight buffer s.  Warp quarter q may touch TMEM lanes 32q..32q+31; a thread
@@ -372,7 +383,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
         const int quarter = warp & 3, set = (warp - kWarpDeq0) >> 2;
         const int row = quarter * 32 + lane;
         const int sw = row & 7;             // 128-byte swizzle of the TMA box: 16-byte chunk index ^ (row & 7)
-        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + set * kWCols;
+        const uint32_t tlane = tmem_base + ((uint32_t)(quarter * 32) << 16);
         uint32_t item0 = 0, stage0 = 0;     // pieces and raw stages before this unit
         for (int u = blockIdx.x; u < n_units && !*s_abort; u += gridDim.x, item0 += kItems, stage0 += kChunks) {
             bool ok = true;
@@ -382,7 +393,9 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
                 const uint32_t stage = stage0 + 2 * (c >> 1) + (w & 1);      // the raw stage holds chunks c & ~1 and c | 1
                 const int st = stage % kRawStages;
                 ok = mbar_wait(RAW_FULL(st), (stage / kRawStages) & 1, s_abort, a.err);
-                if (ok) ok = mbar_wait(W_FREE(set), ((item / kWBufs) & 1) ^ 1, s_abort, a.err);
+                const int wb = item % kWBufs;
+                const uint32_t taddr = tlane + wb * kWCols;
+                if (ok) ok = mbar_wait(W_FREE(wb), ((item / kWBufs) & 1) ^ 1, s_abort, a.err);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint8_t* const rp = raw_ring + (size_t)st * kRawStageBytes;
@@ -411,21 +424,24 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
                 mbar_arrive(RAW_EMPTY(st));
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                mbar_arrive(W_READY(set));
+                mbar_arrive(W_READY(wb));
             }
             if (!ok) break;
         }
     } else if (warp >= kWarpEpi0) {
         if constexpr (!RET) {
-            // ===================== epilogue (warps 4..7 and 24..27: TMEM lane quarters 0..3) ==============
+            // ===================== epilogue (TMEM lane quarter = warp % 4) ================================
             // one thread = one weight row of its row tile; a column = one token of the group.  Lane l keeps
             // the per-token factors of tokens l, l + 32, l + 64, l + 96 and hands them out by shuffle.
+            // With four sets (down) the two sets of a row tile take alternate 16-token steps.
             const int quarter = warp & 3;
+            const int r = (warp < kWarpDeq0) ? 0 : (warp >= kWarpEpi1) ? 1 : ((warp - kWarpEpi2) >> 2);
+            const int half = (warp >= kWarpDeq0 && warp < kWarpEpi1) ? 1 : 0;
+            constexpr int kStride = 16 * (kEpiSets / 2);
             uint32_t unit_i = 0;
             for (int u = blockIdx.x; u < n_units && !*s_abort; u += gridDim.x, unit_i++) {
                 const int4 grp = a.groups[u / n_pairs];
                 const int cnt = grp.z, pos0 = grp.y;
-                const int r = (warp >= kWarpEpi1) ? 1 : 0;
                 const int wrow = (u % n_pairs) * 2 * kTileM + r * kTileM + quarter * 32 + lane;
                 const float gl = f16_global_to_f32(a.global[(size_t)grp.x * a.N + wrow]);
                 float fac[4];
@@ -444,7 +460,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
                 {
                     const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + kAccCol0 + r * kTileTok;
     #pragma unroll 1
-                    for (int c0 = 0; c0 < cnt; c0 += 16) {      // uniform over the warp
+                    for (int c0 = 16 * half; c0 < cnt; c0 += kStride) {      // uniform over the warp
                         {
                             float v[16];
                             tmem_ld16(taddr + c0, v);
