@@ -228,8 +228,8 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
     // mainloop: two dequantiser sets with two buffers each (one being filled while the other is multiplied)
     // and four epilogue sets, two per row tile, each taking every other 16-token step.  The owner's
     // variant (RET) keeps the gate_up map: its epilogue sets meet at named barriers around shared staging.
-    constexpr int kDeqSets = (GATE_UP || RET) ? 4 : 2;
-    constexpr int kEpiSets = (GATE_UP || RET) ? 2 : 4;
+    constexpr int kDeqSets = RET ? 4 : 2;
+    constexpr int kEpiSets = RET ? 2 : 4;
     constexpr int kWarpEpi2 = kWarpDeq0 + 4 * kDeqSets;     // down: warps 16..19 row tile 0, 20..23 row tile 1
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment for the swizzled tiles
@@ -393,25 +393,21 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
                 const uint32_t stage = stage0 + 2 * (c >> 1) + (w & 1);      // the raw stage holds chunks c & ~1 and c | 1
                 const int st = stage % kRawStages;
                 ok = mbar_wait(RAW_FULL(st), (stage / kRawStages) & 1, s_abort, a.err);
+                if (!ok) break;
                 const int wb = item % kWBufs;
                 const uint32_t taddr = tlane + wb * kWCols;
-                if (ok) ok = mbar_wait(W_FREE(wb), ((item / kWBufs) & 1) ^ 1, s_abort, a.err);
-                if (!ok) break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint8_t* const rp = raw_ring + (size_t)st * kRawStageBytes;
                 const uint2 sc8 = *reinterpret_cast<const uint2*>(rp + kRawPackedBytes + row * 16 + (c & 1) * 8);
                 uint4 raw[4];
 #pragma unroll
                 for (int g = 0; g < 4; g++) raw[g] = *reinterpret_cast<const uint4*>(rp + row * 128 + ((((c & 1) * 4 + g) ^ sw) << 4));
-#pragma unroll
-                for (int g = 0; g < 4; g++) {
-                    // 32 k: two block scales
+                // 32 k (one 16-byte piece, two block scales) -> 16 columns
+                auto convert = [&](int g, uint32_t (&r)[16]) {
                     const uint32_t two = ((g & 2) ? sc8.y : sc8.x) >> ((g & 1) * 16);
                     uint32_t h2;
                     asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"((uint16_t)(two & 0xffffu)));
                     const uint32_t s0 = __byte_perm(h2, h2, 0x1010), s1 = __byte_perm(h2, h2, 0x3232);
                     const uint32_t wd[4] = {raw[g].x, raw[g].y, raw[g].z, raw[g].w};
-                    uint32_t r[16];
 #pragma unroll
                     for (int j = 0; j < 4; j++) {
                         uint32_t q[4];
@@ -419,8 +415,21 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
 #pragma unroll
                         for (int e = 0; e < 4; e++) r[4 * j + e] = hmul2_f16(q[e], (j < 2) ? s0 : s1);
                     }
-                    tmem_st16(taddr + g * 16, r);
-                }
+                };
+                // the first half of the piece is converted before the buffer is known to be free: it waits in
+                // registers, so the conversion is off the path between "buffer free" and "buffer ready"
+                uint32_t r0[16], r1[16];
+                convert(0, r0);
+                convert(1, r1);
+                ok = mbar_wait(W_FREE(wb), ((item / kWBufs) & 1) ^ 1, s_abort, a.err);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                tmem_st16(taddr, r0);
+                tmem_st16(taddr + 16, r1);
+                convert(2, r0);
+                tmem_st16(taddr + 32, r0);
+                convert(3, r1);
+                tmem_st16(taddr + 48, r1);
                 mbar_arrive(RAW_EMPTY(st));
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
