@@ -344,31 +344,45 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
             const int r = (warp == kWarpMma) ? 0 : 1;
             const uint32_t d_tmem = tmem_base + kAccCol0 + r * kTileTok;
             uint32_t it = 0, item = r, unit_i = 0;
+            // Looking at a barrier costs a shared-memory round trip even when its phase completed long ago, and
+            // this warp's chain (look, issue, look, issue ..) is what the tensor pipe waits for at small token
+            // tiles.  So the barriers of the NEXT step are looked at (without suspending) just before this
+            // step's MMAs are issued, and the blocking wait is taken only when that look came back empty.
+            bool x_seen = false, w_seen = false;
             for (int u = blockIdx.x; u < n_units && !*s_abort; u += gridDim.x, unit_i++) {
                 const int4 grp = a.groups[u / n_pairs];
                 const int n_pad = max(16, (grp.z + 15) & ~15);
                 const uint32_t idesc = kIdescBase | ((uint32_t)(n_pad >> 3) << 17);
                 // the accumulators must have been read back
                 bool ok = mbar_wait_warp(ACC_EMPTY, (unit_i & 1) ^ 1, s_abort, a.err);
-                for (int c = 0; c < kChunks && ok; c++, item += 2) {
+                for (int ks = 0; ks < 2 * kChunks && ok; ks++, it++) {
+                    const int h = ks & 1;                        // half of the 128-k weight piece
                     const int wb = item % kWBufs;
-                    ok = mbar_wait_warp(W_READY(wb), (item / kWBufs) & 1, s_abort, a.err);
-                    const uint32_t w_addr = tmem_base + wb * kWCols;
-                    for (int h = 0; h < 2 && ok; h++, it++) {
-                        const int st = it % kXStages;
-                        ok = mbar_wait_warp(X_FULL(st), (it / kXStages) & 1, s_abort, a.err);
-                        if (!ok) break;
-                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                        const uint64_t xdesc = umma_desc(smem_u32(x_tiles + (size_t)st * kTileBytes));
-                        if (elect_one()) {
-#pragma unroll
-                            for (int kk = 0; kk < 4; kk++)
-                                umma_f16_ts(d_tmem, w_addr + (h * 4 + kk) * 8, xdesc + kk * 2, idesc, (c > 0 || h > 0 || kk > 0) ? 1u : 0u);
-                            umma_commit(X_EMPTY(st));    // the activation stage is free once both issuers' MMAs retire
-                            if (h == 1) umma_commit(W_FREE(wb));   // and so is the weight buffer
+                    if (h == 0 && !w_seen) ok = mbar_wait_warp(W_READY(wb), (item / kWBufs) & 1, s_abort, a.err);
+                    if (!ok) break;
+                    const int st = it % kXStages;
+                    if (!x_seen) ok = mbar_wait_warp(X_FULL(st), (it / kXStages) & 1, s_abort, a.err);
+                    if (!ok) break;
+                    {
+                        const uint32_t it1 = it + 1;
+                        x_seen = __all_sync(0xffffffffu, mbar_test_wait(X_FULL(it1 % kXStages), (it1 / kXStages) & 1));
+                        if (h == 1) {
+                            const uint32_t item1 = item + 2;
+                            w_seen = __all_sync(0xffffffffu, mbar_test_wait(W_READY(item1 % kWBufs), (item1 / kWBufs) & 1));
                         }
-                        __syncwarp();
                     }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t w_addr = tmem_base + wb * kWCols;
+                    const uint64_t xdesc = umma_desc(smem_u32(x_tiles + (size_t)st * kTileBytes));
+                    if (elect_one()) {
+#pragma unroll
+                        for (int kk = 0; kk < 4; kk++)
+                            umma_f16_ts(d_tmem, w_addr + (h * 4 + kk) * 8, xdesc + kk * 2, idesc, (ks > 0 || kk > 0) ? 1u : 0u);
+                        umma_commit(X_EMPTY(st));    // the activation stage is free once both issuers' MMAs retire
+                        if (h == 1) umma_commit(W_FREE(wb));   // and so is the weight buffer
+                    }
+                    __syncwarp();
+                    if (h == 1) item += 2;
                 }
                 if (!ok) break;
                 if (elect_one()) umma_commit(ACC_FULL);

@@ -33,8 +33,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// the phase has completed already?  Never suspends the thread: the cheap first look of mbar_wait.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 // bounded wait: false after kSpin polls or once another role has raised the abort flag
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* err) {
+    if (mbar_test_wait(bar, parity)) return true;
     for (uint32_t i = 0; i < kSpin; i++) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 1023u) == 1023u && *abort_flag) return false;
