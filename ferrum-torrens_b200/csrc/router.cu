@@ -488,10 +488,129 @@ router_logits_wide_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat
     }
 }
 
+// ---- big variant for batches of 4096 tokens and more -------------------------------------------
+// The wide kernel reads a shared-memory wavefront per four FMAs and is bound by that pipe.  Here a lane owns
+// four experts (lane, lane + 32, lane + 64, lane + 96) and a warp eight tokens: 32 independent chains per
+// thread; per eight k a warp reads four 16-byte weight pieces (eight k of one expert each) and sixteen
+// broadcast activation vectors for 256 FMAs, half the shared-memory traffic per FMA.  Every chain still
+// walks k in order with one fma per k.  Needs enough tokens to fill the device with 32-token tiles.
+constexpr int kGE = 128, kGT = 32, kGK = 64;
+constexpr int kGWStride = kGK * 2 + 16;
+
+__global__ void __launch_bounds__(128, 4)
+router_logits_big_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gate_w,
+                         int tokens, int experts, int hidden, float* __restrict__ logits) {
+    extern __shared__ __align__(16) uint8_t rsm[];
+    uint8_t* const wbuf = rsm;                                               // [2][128][kGWStride]
+    float* const xbuf = reinterpret_cast<float*>(rsm + 2 * kGE * kGWStride);  // [2][kGK][32]
+    const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+    const int e0 = blockIdx.x * kGE, t0 = blockIdx.y * kGT;
+    const int nchunks = hidden / kGK;
+    const uint32_t wbase = (uint32_t)__cvta_generic_to_shared(wbuf);
+
+    auto issue_w = [&](int c, int b) {
+        for (int i = tid; i < kGE * (kGK / 8); i += 128) {
+            const int row = i / (kGK / 8), piece = i % (kGK / 8);
+            const int e = min(e0 + row, experts - 1);
+            cp_async16(wbase + b * kGE * kGWStride + row * kGWStride + piece * 16,
+                       gate_w + (size_t)e * hidden + c * kGK + piece * 8);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    // activations: thread -> token lane, 16-byte pieces warp + 4 * i
+    uint4 xr[kGK / 32];
+    auto load_x = [&](int c) {
+        const int t = t0 + lane;
+#pragma unroll
+        for (int i = 0; i < kGK / 32; i++) {
+            xr[i] = make_uint4(0, 0, 0, 0);
+            if (t < tokens) xr[i] = *reinterpret_cast<const uint4*>(x + (size_t)t * hidden + c * kGK + (warp + 4 * i) * 8);
+        }
+    };
+    auto store_x = [&](int b) {
+        float* xs = xbuf + b * kGK * kGT;
+#pragma unroll
+        for (int i = 0; i < kGK / 32; i++) {
+            const int k = (warp + 4 * i) * 8;
+            const uint32_t w[4] = {xr[i].x, xr[i].y, xr[i].z, xr[i].w};
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const float2 v = bf16x2_to_f32(w[q]);
+                xs[(k + 2 * q) * kGT + lane] = v.x;
+                xs[(k + 2 * q + 1) * kGT + lane] = v.y;
+            }
+        }
+    };
+
+    issue_w(0, 0);
+    load_x(0);
+    store_x(0);
+    float acc[4][8];
+#pragma unroll
+    for (int j = 0; j < 4; j++)
+#pragma unroll
+        for (int i = 0; i < 8; i++) acc[j][i] = 0.f;
+    for (int c = 0; c < nchunks; c++) {
+        const int b = c & 1;
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        if (c + 1 < nchunks) {
+            issue_w(c + 1, b ^ 1);
+            load_x(c + 1);
+        }
+        const uint32_t wrow = wbase + b * kGE * kGWStride + lane * kGWStride;
+        const float* xs = xbuf + b * kGK * kGT + warp * 8;
+#pragma unroll 2
+        for (int kk = 0; kk < kGK; kk += 8) {
+            uint4 wq[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(wq[j].x), "=r"(wq[j].y), "=r"(wq[j].z), "=r"(wq[j].w)
+                             : "r"(wrow + j * 32 * kGWStride + kk * 2));
+#pragma unroll
+            for (int q = 0; q < 8; q++) {
+                const float4 x0 = *reinterpret_cast<const float4*>(xs + (kk + q) * kGT);
+                const float4 x1 = *reinterpret_cast<const float4*>(xs + (kk + q) * kGT + 4);
+                const float xv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const uint32_t pair = (q < 2) ? wq[j].x : (q < 4) ? wq[j].y : (q < 6) ? wq[j].z : wq[j].w;
+                    const float wv = (q & 1) ? __uint_as_float(pair & 0xffff0000u) : __uint_as_float(pair << 16);
+#pragma unroll
+                    for (int i = 0; i < 8; i++) acc[j][i] = __fmaf_rn(xv[i], wv, acc[j][i]);
+                }
+            }
+        }
+        if (c + 1 < nchunks) store_x(b ^ 1);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const int e = e0 + lane + 32 * j;
+        if (e < experts) {
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const int t = t0 + warp * 8 + i;
+                if (t < tokens) logits[(size_t)t * experts + e] = acc[j][i];
+            }
+        }
+    }
+}
+
 }  // namespace
 
 int launch_router_logits(const __nv_bfloat16* x, const __nv_bfloat16* gate_w, int tokens, int experts,
                          int hidden, float* logits, const Ctx& c) {
+    if (hidden % kGK == 0 && tokens >= 4096 && experts >= kGE) {
+        dim3 grid((experts + kGE - 1) / kGE, (tokens + kGT - 1) / kGT);
+        const size_t smem = 2 * kGE * kGWStride + 2 * kGK * kGT * sizeof(float);
+        static PerDeviceOnce once;
+        allow_dyn_smem(once, router_logits_big_kernel, smem);
+        c.begin(K_ROUTER_LOGITS);
+        router_logits_big_kernel<<<grid, 128, smem, c.s>>>(x, gate_w, tokens, experts, hidden, logits);
+        c.end();
+        return 1;
+    }
     if (hidden % kBK == 0 && tokens >= 1024) {
         dim3 grid((experts + kBE - 1) / kBE, (tokens + kBT - 1) / kBT);
         const size_t smem = 2 * kBE * kBWStride + 2 * kBK * kBT * sizeof(float);

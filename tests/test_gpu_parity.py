@@ -117,6 +117,20 @@ def test_router_ids_bit_exact_full(full, tokens):
     assert np.abs(w.cpu().numpy() - want_w).max() <= 1e-6
 
 
+def test_router_ids_bit_exact_at_4200_tokens():
+    """Batches of 4096 tokens and more take a kernel of their own (32 chains per thread); 4200 tokens leave a
+    ragged last tile of eight.  Ids and weights equal the CPU path's bit for bit."""
+    lay = pkg.synth.make_layer(31, hidden=2048, inter=512, experts=256, top_k=8, shared_inter=512)
+    moe = pkg.B200MoE(0, pkg.ExpertShapes(2048, 512), 1, experts=256, layers=1, top_k=8, shared_inter=0, max_tokens=4200)
+    ol = oracle_layer(lay)
+    xb = pkg.synth.make_x(4242, 4200, lay.hidden)
+    ids, w = moe.router(bf16_dev(xb), bf16_dev(lay.gate_w))
+    want_ids, want_w = o.router(ol, pkg.synth.bf16_bits_to_f32(xb))
+    assert np.array_equal(ids.cpu().numpy(), want_ids)
+    assert np.array_equal(w.cpu().numpy(), want_w)
+    moe.close()
+
+
 def test_router_ties_take_the_lowest_index(small):
     lay, moe, _ = small
     e = lay.experts
