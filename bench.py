@@ -378,6 +378,32 @@ def measure_stack(torch, moe, dense, x0, nlayers, path, K, W):
     return res
 
 
+def measure_lm_head(torch, moe, dev, pk, K, W):
+    """The neighbour of the layer at the end of the model: the dense NVFP4 GEMV of `lm_head` (K-major bank, vocabulary
+    248320 x hidden 2048), one and eight rows.  HBM-bound: 286.6 MB of bank per call, larger than L2."""
+    N, Kd = 248320, HIDDEN
+    g = torch.Generator(device=dev).manual_seed(4242)
+    packed = torch.randint(-2**31, 2**31 - 1, (Kd // 8, N), generator=g, device=dev, dtype=torch.int64).to(torch.int32)
+    # e4m3 scale bytes 0x28..0x47 (2^-2 .. 1.75): no NaN, no overflow of the f16 product
+    scale = torch.randint(0x28, 0x48, (Kd // 16, N), generator=g, device=dev, dtype=torch.int32).to(torch.uint8)
+    glob = torch.full((N,), 0x3C00, dtype=torch.int16, device=dev)
+    bank_bytes = packed.numel() * 4 + scale.numel() + glob.numel() * 2
+    out = {"workload": f"dense NVFP4 GEMV (lm_head), N={N} K={Kd}, K-major bank of {bank_bytes / 1e6:.1f} MB (larger than L2)",
+           "peak_GBps": pk["hbm_gbs"], "peak_source": pk["which"]}
+    for m in (1, 8):
+        a = torch.randn((m, Kd), generator=g, device=dev).to(torch.bfloat16)
+        c = torch.empty((m, N), dtype=torch.float32, device=dev)
+        ms = timed_steps(torch, lambda i: moe.dense_gemv(a, packed, scale, glob, c), K, W)
+        moe.sync_status()
+        us = ms / K * 1e3
+        algo = bank_bytes + m * Kd * 2 + m * N * 4
+        out[f"M={m}"] = {"us_per_call": us, "algorithmic_bytes": algo, "achieved_GBps": algo / (us * 1e-6) / 1e9,
+                         "frac": algo / (us * 1e-6) / 1e9 / pk["hbm_gbs"]}
+    del packed, scale, c
+    torch.cuda.empty_cache()
+    return out
+
+
 def run_single(args, pkg, dev, local):
     import torch
     T = args.tokens or 64
@@ -557,6 +583,9 @@ def run_single(args, pkg, dev, local):
             stack[f"T={t}"] = measure_stack(torch, moe, dense, x0, total_layers, 0, max(4, K // 4), 3)
         line["stack40"] = stack
         pkg.synth.set_global_bits_on_device(moe, 0, EXPERTS * total_layers, G_ONE)
+
+    if default_line:
+        line["lm_head"] = measure_lm_head(torch, moe, dev, pk, K, W)
 
     # the sampler ran through every timed region above (all GPU-busy)
     line["clocks"] = sampler.stop()

@@ -1147,7 +1147,7 @@ FTM_API int ftm_dense_gemv(ftm_handle* h, const void* a, int a_dtype, const void
     if (!dense_gemv_supported(n, k))
         return fail(h, FTM_ERR_BAD, shapes, "N a multiple of 4 and K a multiple of 32 (at most 3136)");
     h->launches += launch_dense_gemv(a, a_dtype, (const uint32_t*)packed_kmajor_i32, (const uint8_t*)scale_kmajor_u8,
-                                     (const uint16_t*)global_f16, m, n, k, c, h->sm_count, h->ctx(pick(h, stream)));
+                                     (const uint16_t*)global_f16, m, n, k, c, h->sm_count, h->flags + 2, h->ctx(pick(h, stream)));
     CU(h, cudaGetLastError());
     return FTM_OK;
 }

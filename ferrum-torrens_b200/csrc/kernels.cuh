@@ -222,6 +222,6 @@ int launch_add_rmsnorm(const __nv_bfloat16* x, const __nv_bfloat16* r, const __n
 // dense_gemv.cu: K-major NVFP4 GEMV of the decode tail (lm_head)
 bool dense_gemv_supported(int N, int K);
 int launch_dense_gemv(const void* a, int a_dtype, const uint32_t* packed, const uint8_t* scale, const uint16_t* global,
-                      int M, int N, int K, float* c, int sm_count, const Ctx& ctx);
+                      int M, int N, int K, float* c, int sm_count, int32_t* err, const Ctx& ctx);
 
 }  // namespace ftm

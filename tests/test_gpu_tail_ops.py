@@ -138,10 +138,12 @@ def test_dense_gemv_matches_reference_fixture(case):
 
 
 @pytest.mark.parametrize("m,n,k", [(1, 4, 32), (1, 36, 64), (8, 1000, 512), (9, 128, 2048), (16, 260, 96), (17, 64, 2048),
-                                   (40, 32, 256)])
+                                   (40, 32, 256), (1, 448, 256), (3, 1056, 512), (12, 2000, 2048), (20, 464, 768)])
 def test_dense_gemv_ragged_shapes_against_cpu_path(m, n, k):
     """Rows that are not a multiple of the 32-row tile, K with and without the two-way split, one to several
-    token tiles and more than sixteen tokens (several passes over the weight)."""
+    token tiles and more than sixteen tokens (several passes over the weight).  The last four shapes (N a
+    multiple of 16 and at least 448, K a multiple of 256) take the TMA-fed kernel: one tile exactly, a last
+    tile of 160 and of 208 rows, a last tile of 16 rows."""
     a, pk, sk, glob = _gemv_case(m, n, k, 1000 + m + n + k)
     moe = tiny_handle(64)
     got = _run_gemv(moe, a, pk, sk, glob)
