@@ -52,6 +52,8 @@ def parse():
     ap.add_argument("--tokens", type=int, default=0, help="tokens per step (default: 64 at N=1)")
     ap.add_argument("--layers", type=int, default=4, help="independent layers cycled through")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--lm-head", action="store_true",
+                    help="N = 1: only the dense NVFP4 GEMV of the lm_head (248320 x 2048), one and eight rows")
     ap.add_argument("--no-sweep", action="store_true",
                     help="N = 1: leave out the other batch sizes (T = 1, 8, 512, 2048) and the 40-layer stack that the "
                          "default line carries beside the T = 64 headline")
@@ -218,6 +220,12 @@ def run_b200(args):
     if world > 1:
         return run_ep(args, pkg, dev, world, rank, local)
 
+    if args.lm_head:
+        moe = pkg.B200MoE(local, pkg.ExpertShapes(HIDDEN, INTER), 1, experts=EXPERTS, layers=1, top_k=TOP_K, shared_inter=0,
+                          max_tokens=64)
+        print(json.dumps({"lm_head": measure_lm_head(torch, moe, dev, peaks(), max(1, args.steps), max(3, args.warmup))}))
+        moe.close()
+        return
     return run_single(args, pkg, dev, local)
 
 
