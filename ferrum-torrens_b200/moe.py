@@ -15,6 +15,8 @@ computation goes through the library, which has no CPU path.
 from __future__ import annotations
 
 import ctypes as C
+import os
+import sys
 from dataclasses import dataclass
 from typing import Optional, Sequence
 
@@ -132,6 +134,24 @@ def _stream_ptr(stream) -> C.c_void_p:
     if isinstance(stream, int):
         return C.c_void_p(stream)
     return C.c_void_p(stream.cuda_stream)
+
+
+def trace_on() -> bool:
+    """FT_TRACE=1 switches the stage dump on (read at every call, so a test can set it)."""
+    return os.environ.get("FT_TRACE") == "1"
+
+
+def trace(stage: str, layer: int, t) -> None:
+    """One line of the stage dump, in the reference's format (forward.rs:833-855, `trace_vec`): the l2 norm and the
+    largest magnitude of a stage's tensor, on stderr.  The CPU path prints the same lines (oracle.trace_vec), so
+    two runs can be compared stage by stage and the first divergence located.  Synchronises the device."""
+    if not trace_on():
+        return
+    torch = _torch()
+    v = t.detach().to(torch.float64)
+    l2 = float(v.pow(2).sum().sqrt())
+    amax = float(v.abs().max()) if v.numel() else 0.0
+    print(f"TRACE {layer} {stage} l2={l2:.6f} amax={amax:.6f}", file=sys.stderr)
 
 
 class _RawDeviceArray:
@@ -509,6 +529,7 @@ class B200MoE:
             _dev(sh_down, "sh_down"), _dev(sh_gate, "sh_gate"), _dev(out, "out"), _dtype_code(out),
             _dev(ids_out, "ids") if ids_out is not None else null,
             _dev(weights_out, "weights") if weights_out is not None else null, path, _stream_ptr(stream)))
+        trace("moe", layer, out)
 
 
     # -- the steps either side of the block -----------------------------------------------------
@@ -536,11 +557,17 @@ class B200MoE:
             raise bad(f"out holds {out.numel()}, the block produces {tokens * self.shapes.hidden}")
         null = C.c_void_p(0)
         opt = lambda t, n: _dev(t, n) if t is not None else null
+        if trace_on() and h2_out is None:
+            h2_out = _torch().empty_like(attn_out)       # the dump wants the normalised rows
         self._check(self._lib.ftm_moe_block_prenorm(
             self._h, layer, _dev(attn_out, "attn_out"), _dev(residual, "residual"), _dev(norm_w, "norm_w"), C.c_float(eps),
             tokens, _dev(gate_w, "gate"), _dev(sh_gate_up, "sh_gate_up"), _dev(sh_down, "sh_down"), _dev(sh_gate, "sh_gate"),
             _dev(sum_out, "sum_out"), opt(h2_out, "h2"), _dev(out, "out"), _dtype_code(out), opt(ids_out, "ids"),
             opt(weights_out, "weights"), path, _stream_ptr(stream)))
+        if trace_on():
+            trace("sum2", layer, sum_out)
+            trace("h2", layer, h2_out)
+            trace("moe", layer, out)
 
     def dense_gemv(self, a, packed_kmajor, scale_kmajor, glob, c=None, stream=None):
         """DenseGemv::gemv (cuda_linear.rs:48-175): c [M, N] f32 = a [M, K] @ dequant(W)^T for the K-major bank

@@ -6,6 +6,8 @@ can compare the CUDA path against the reference's host algorithm.
 from __future__ import annotations
 
 import ctypes as C
+import os
+import sys
 from dataclasses import dataclass
 
 import numpy as np
@@ -358,6 +360,29 @@ def moe_block(layer: Layer, x, threads: int = 1, form: str = "gemv"):
     if rc != OK:
         raise OracleError("Bad", "moe_block: bad layer shapes")
     return out, ids, w
+
+
+# ---- stage dump ------------------------------------------------------------------
+def trace_vec(stage: str, layer: int, v) -> None:
+    """`trace_vec` of forward.rs:833-855: with FT_TRACE=1, one line per stage on stderr with the l2 norm and the
+    largest magnitude of the stage's values.  The CUDA path prints the same lines."""
+    if os.environ.get("FT_TRACE") != "1":
+        return
+    a = np.asarray(v, dtype=np.float64).reshape(-1)
+    l2 = float(np.sqrt(np.sum(a * a)))
+    amax = float(np.abs(a).max()) if a.size else 0.0
+    print(f"TRACE {layer} {stage} l2={l2:.6f} amax={amax:.6f}", file=sys.stderr)
+
+
+def moe_block_prenorm(layer: Layer, layer_index: int, attn_bits, residual_bits, norm_w_bits, eps: float, threads: int = 1):
+    """forward.rs:942-954 around the block: sum2 = attn + residual, h2 = rms_norm(sum2), moe = block(h2); the three
+    stages are dumped under FT_TRACE=1.  Returns (sum2 bits, h2 bits, out f32, ids, weights)."""
+    s, h2 = add_rmsnorm(attn_bits, residual_bits, norm_w_bits, eps)
+    out, ids, w = moe_block(layer, bf16_bits_to_f32(h2), threads=threads)
+    trace_vec("sum2", layer_index, bf16_bits_to_f32(s))
+    trace_vec("h2", layer_index, bf16_bits_to_f32(h2))
+    trace_vec("moe", layer_index, out)
+    return s, h2, out, ids, w
 
 
 # ---- the steps either side of the block ---------------------------------------

@@ -111,6 +111,51 @@ def test_block_behind_the_post_attention_norm(tokens):
     moe.close()
 
 
+def _trace_lines(err: str):
+    out = []
+    for ln in err.splitlines():
+        if ln.startswith("TRACE "):
+            _, layer, stage, l2, amax = ln.split()
+            out.append((int(layer), stage, float(l2.split("=")[1]), float(amax.split("=")[1])))
+    return out
+
+
+def test_stage_dump_of_the_cuda_path_lines_up_with_the_cpu_path(capfd, monkeypatch):
+    """FT_TRACE=1 (forward.rs:833-855): both paths print `TRACE <layer> <stage> l2= amax=` for sum2, h2 and moe of a
+    layer; the two dumps name the same stages in the same order and agree stage by stage, so a divergence can be
+    pinned to the first stage whose lines differ."""
+    tokens = 24
+    lay = pkg.synth.make_layer(9191, global_scale=(2.0 ** -6, 2.0 ** -10))
+    H = lay.hidden
+    moe = pkg.B200MoE(0, pkg.ExpertShapes(H, lay.inter), lay.experts, experts=lay.experts, layers=4, top_k=lay.top_k,
+                      shared_inter=lay.shared_inter, max_tokens=tokens)
+    for e in range(lay.experts):
+        moe.load(3, e, e, lay.fields(e))
+    attn, resid, w = mg.norm_inputs(tokens, H, 777)
+    banks = o.HostBanks(*lay.banks, slots=lay.experts, gu_rows=2 * lay.inter, gu_cols=H, dn_rows=H, dn_cols=lay.inter)
+    ol = o.Layer(H, lay.inter, lay.experts, lay.top_k, lay.shared_inter, lay.gate_w, lay.sh_gate_up, lay.sh_down,
+                 lay.sh_gate, banks)
+    sum_out = torch.empty((tokens, H), dtype=torch.bfloat16, device=dev())
+    out = torch.empty((tokens, H), dtype=torch.float32, device=dev())
+    args = (3, bf16_dev(attn), bf16_dev(resid), bf16_dev(w), 1e-6, bf16_dev(lay.gate_w), bf16_dev(lay.sh_gate_up),
+            bf16_dev(lay.sh_down), bf16_dev(lay.sh_gate), sum_out, out)
+    moe.moe_block_prenorm(*args)
+    moe.sync_status()
+    assert _trace_lines(capfd.readouterr().err) == [], "nothing is printed unless FT_TRACE=1"
+    monkeypatch.setenv("FT_TRACE", "1")
+    moe.moe_block_prenorm(*args)
+    moe.sync_status()
+    got = _trace_lines(capfd.readouterr().err)
+    o.moe_block_prenorm(ol, 3, attn, resid, w, 1e-6, threads=o.max_threads())
+    want = _trace_lines(capfd.readouterr().err)
+    assert [(l, s) for l, s, _, _ in got] == [(3, "sum2"), (3, "h2"), (3, "moe")]
+    assert [(l, s) for l, s, _, _ in got] == [(l, s) for l, s, _, _ in want]
+    for (_, stage, l2, amax), (_, _, wl2, wamax) in zip(got, want):
+        tol = 0.0 if stage == "sum2" else 5e-3
+        assert abs(l2 - wl2) <= tol * wl2 + 1e-6 and abs(amax - wamax) <= 2 * tol * wamax + 1e-6, (stage, l2, wl2, amax, wamax)
+    moe.close()
+
+
 # ------------------------------------------------------------------ dense K-major NVFP4 GEMV (lm_head)
 def _gemv_case(m, n, k, seed):
     a, packed, scale, glob = mg.gemv_inputs(m, n, k, seed)

@@ -72,3 +72,13 @@ def test_dense_gemv_matches_the_reference_oracle(case):
         byte = int(packed[row, (8 * w + j) // 2])
         want_codes.append((byte >> 4) if j % 2 else (byte & 0xF))
     assert codes == want_codes
+
+
+def test_stage_dump_prints_the_reference_format(capfd, monkeypatch):
+    """FT_TRACE=1: `TRACE <layer> <stage> l2=<..> amax=<..>` on stderr (forward.rs:833-855), nothing without it."""
+    v = np.array([3.0, -4.0], np.float32)
+    o.trace_vec("moe", 7, v)
+    assert capfd.readouterr().err == ""
+    monkeypatch.setenv("FT_TRACE", "1")
+    o.trace_vec("moe", 7, v)
+    assert capfd.readouterr().err == "TRACE 7 moe l2=5.000000 amax=4.000000\n"
