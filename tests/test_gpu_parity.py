@@ -175,9 +175,10 @@ def test_csr_reference_cases(small, routes, bins):
 
 
 @pytest.mark.parametrize("n,bins", [(1, 8), (2, 8), (7, 8), (33, 8), (128, 8), (1025, 8), (2048, 256), (2049, 256),
-                                    (16384, 256), (13001, 32)])
+                                    (16384, 256), (13001, 32), (12000, 300), (4097, 1)])
 def test_csr_random_matches_host(small, n, bins):
-    """xorshift-seeded cases as in cuda_moe.rs:2752-2772, plus multi-CTA sizes."""
+    """xorshift-seeded cases as in cuda_moe.rs:2752-2772, plus the sizes of both builds: one CTA (at most 2048
+    routes) and several CTAs, with 1, 32, 256 and 300 bins."""
     _, moe, _ = small
     seed = 0x2545F4914F6CDD1D
     vals = []
@@ -201,9 +202,11 @@ def test_csr_random_matches_host(small, n, bins):
 
 def test_csr_flags_slots_outside_the_bank(small):
     _, moe, _ = small
-    for routes in ([-1, 0], [3]):
-        _, _, badf = moe.csr_build(torch.tensor(routes, dtype=torch.int32, device=dev()), 3)
+    for routes in ([-1, 0], [3], [0, 1, 2] * 1000 + [3], [2] * 5000 + [-7] + [1] * 4000):
+        seg, idx, badf = moe.csr_build(torch.tensor(routes, dtype=torch.int32, device=dev()), 3)
         assert badf == 1
+        good = [i for i, b in enumerate(routes) if 0 <= b < 3]
+        assert int(seg[3]) == len(good), "the routes inside the bank are still bucketed"
 
 
 # ------------------------------------------------------------------ routed half, known answers
