@@ -814,11 +814,15 @@ def run_ep(args, pkg, dev, world, rank, local):
     if "grouped_gate_up" in oprof:
         pk = peaks()
         g_ms, g_n = oprof["grouped_gate_up"]
-        flops = recv_routes * 2.0 * HIDDEN * (2 * INTER)
+        # three profiled steps; a step that cuts the owner's experts into ranges (or micro-batches) launches the
+        # GEMM once per range, each on its share of the routes
+        launches_per_step = max(1.0, g_n / 3.0)
+        flops = recv_routes / launches_per_step * 2.0 * HIDDEN * (2 * INTER)
         ach = flops / (g_ms / g_n * 1e-3) / 1e12
         roofline = {"bound": "tensor", "kernel": "grouped_gate_up (owner side, rank 0)", "achieved": ach, "peak": pk["bf16_tflops"],
                     "unit": "TFLOP/s", "frac": ach / pk["bf16_tflops"], "peak_source": pk["which"], "traffic": None,
-                    "routes_received": recv_routes, "us_per_launch": g_ms / g_n * 1e3,
+                    "routes_received": recv_routes, "gemm_launches_per_step": launches_per_step,
+                    "us_per_launch": g_ms / g_n * 1e3,
                     "kernels": {k: {"us_per_launch": ms / n * 1e3, "launches": n} for k, (ms, n) in oprof.items()}}
     sent = torch.tensor([sum(layer.last_counts[0]) - layer.last_counts[0][rank]], device=dev, dtype=torch.float32)
     dist.all_reduce(sent, op=dist.ReduceOp.MAX)
