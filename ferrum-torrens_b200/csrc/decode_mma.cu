@@ -942,7 +942,14 @@ void launch_expert(ExpertArgs a, int sm_count, cudaStream_t s, bool pdl) {
             case 1: launch_expert_ldg<GATE_UP, K_, NT, 2, 1>(a, sm_count, s, pdl); break;
             case 3: launch_expert_ldg<GATE_UP, K_, NT, 2, 3>(a, sm_count, s, pdl); break;
             case 4: launch_expert_ldg<GATE_UP, K_, NT, 2, 4>(a, sm_count, s, pdl); break;
-            case 6: launch_expert_ldg<GATE_UP, K_, NT, 2, 6>(a, sm_count, s, pdl); break;
+            case 6:
+                // down with groups of at most eight tokens needs 80 registers: three CTAs (24 warps) per SM,
+                // 36.1 -> 34.2 us at T = 64 (four CTAs spill and lose)
+                if constexpr (!GATE_UP && NT == 1)
+                    launch_expert_ldg<GATE_UP, K_, NT, 3, 6>(a, sm_count, s, pdl);
+                else
+                    launch_expert_ldg<GATE_UP, K_, NT, 2, 6>(a, sm_count, s, pdl);
+                break;
             default: launch_expert_ldg<GATE_UP, K_, NT, 2, 0>(a, sm_count, s, pdl); break;
         }
         return;
