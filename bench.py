@@ -64,6 +64,9 @@ def parse():
                          "exchanges run under compute; 1 = the plain schedule")
     ap.add_argument("--ep-exchange", default="p2p", choices=["p2p", "nccl"],
                     help="N > 1: dispatch / return by this library's kernels over peer memory, or by NCCL all-to-all")
+    ap.add_argument("--ep-unsorted", action="store_true",
+                    help="N > 1, peer-memory exchange: dispatch bf16 rows in receive order (the owner sorts and gathers) "
+                         "instead of storing them straight into the owner's sorted f16 activation matrix")
     ap.add_argument("--ep-separate-return", action="store_true",
                     help="N > 1, peer-memory exchange: return the rows by a kernel of its own instead of the owner's down GEMM")
     ap.add_argument("--ep-micro", type=int, default=1,
@@ -652,6 +655,8 @@ def run_ep(args, pkg, dev, world, rank, local):
         g, su, sd, sg = dense[l]
         xin, dst = (xs[l] if x is None else x), (out if o is None else o)
         if p2p:
+            if not args.ep_unsorted and micro == 1 and not args.ep_separate_return:
+                return layer.forward_p2p_sorted(l, xin, g, su, sd, sg, dst, record=record)
             # the phase breakdown (record set) runs the step as one batch, every phase after the one before
             return layer.forward_p2p(l, xin, g, su, sd, sg, dst, record=record, micro=1 if record else micro,
                                      fused_return=not args.ep_separate_return)
@@ -834,7 +839,9 @@ def run_ep(args, pkg, dev, world, rank, local):
             "data": "synthetic",
             "config": {"workload": f"expert-parallel layer, T={T} tokens per GPU, {EXPERTS} experts split {per} per GPU, "
                                    f"top-{TOP_K}, {'uniform' if args.zipf is None else f'Zipf({args.zipf})-skewed'} routing, " +
-                                   (f"dispatch by a peer-memory kernel, return by {'the down GEMM itself' if not args.ep_separate_return else 'a kernel reading the GEMM rows in place'} "
+                                   (("rows dispatched by a peer-memory kernel straight into the owner's sorted f16 activation matrix (no permutation "
+                                     "build or gather on the owner), " if not args.ep_unsorted and micro == 1 and not args.ep_separate_return
+                                     else "dispatch by a peer-memory kernel in receive order, ") + f"return by {'the down GEMM itself' if not args.ep_separate_return else 'a kernel reading the GEMM rows in place'} "
                                     f"(plain peer stores over NVLink), {micro} micro-batch(es) "
                                     f"per step (dispatch of one under the experts of the one before, {args.ep_comm_sms if micro > 1 else 0} SMs "
                                     f"left to the exchange)" if p2p else

@@ -81,6 +81,9 @@ _PROTOS = {
     "ftm_ep_return": (_int, [_vp, _vp, _i32, _i32, _i32, _vp, _vp, C.c_int64, _vp]),
     "ftm_ep_experts_sorted": (_int, [_vp, _i32, _vp, _vp, _vp, _i32, _vp]),
     "ftm_ep_experts_return": (_int, [_vp, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp, C.c_int64, _vp]),
+    "ftm_ep_plan_seg": (_int, [_vp, _vp, _i32, _vp, _vp, _vp]),
+    "ftm_ep_dispatch_sorted": (_int, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, C.c_int64, _vp]),
+    "ftm_ep_experts_presorted": (_int, [_vp, _i32, _vp, _vp, _vp, _i32, C.c_int64, _i32, _i32, _vp, _vp, C.c_int64, _vp]),
     "ftm_ep_return_sorted": (_int, [_vp, _i32, _i32, _i32, _vp, _vp, C.c_int64, _vp]),
     "ftm_ep_combine": (_int, [_vp, _vp, _int, _vp, _vp, _vp, _i32, _vp, _int, _vp]),
     "ftm_profile_enable": (_int, [_vp, _int]),

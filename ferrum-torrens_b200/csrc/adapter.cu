@@ -121,6 +121,9 @@ struct ftm_handle {
     int4* groups = nullptr;
     int32_t *sorted_route = nullptr, *n_groups = nullptr;
     PrefillMaps maps;     // tensor maps of the grouped GEMMs (fixed addresses: encoded once)
+    PrefillMaps maps_ext; // the same with the activation maps on a caller's matrix (expert-parallel owner)
+    const void* maps_ext_xg = nullptr;
+    int64_t maps_ext_rows = 0;
     int sm_count = 148;   // CTAs of the persistent kernels (ftm_set_sm_budget)
     int sm_total = 148;
     std::vector<void*> allocs;
@@ -241,6 +244,7 @@ BankView bank_view(const ftm_handle* h) {
 // (re)encodes the grouped GEMM's tensor maps; the shapes the tcgen05 path does not cover need none
 void build_maps(ftm_handle* h) {
     h->maps.ok = false;
+    h->maps_ext.ok = false;     // encoded on the old bank addresses
     if (!h->resident || !h->xg || !h->ic2) return;
     if (!prefill_umma_supported(h->cfg.hidden, h->cfg.inter, 1, 1, true)) return;
     prefill_build_maps(bank_view(h), h->xg, reinterpret_cast<const __half*>(h->ic2),
@@ -972,6 +976,92 @@ FTM_API int ftm_ep_experts_return(ftm_handle* h, int32_t layer, const void* x_bf
     rc = run_routed(h, x_bf16, FTM_BF16, expert_ids, FTM_I32, layer, weights, rows, nullptr, nullptr, nullptr, nullptr,
                     FTM_BF16, FTM_PATH_GROUPED, pick(h, stream), &ret);
     if (rc != FTM_OK) return rc;
+    CU(h, cudaGetLastError());
+    h->steps++;
+    return FTM_OK;
+}
+
+FTM_API int ftm_ep_plan_seg(ftm_handle* h, const int32_t* ids, int32_t tokens, int32_t* route_idx, int32_t* seg_out,
+                            void* stream) {
+    if (!h) return FTM_ERR_BAD;
+    std::lock_guard<std::mutex> lk(h->mu);
+    DeviceGuard dg(h->cfg.ordinal);
+    if (!ids || !route_idx || !seg_out) return fail(h, FTM_ERR_BAD, "moe: ep_plan_seg: null buffer");
+    if (tokens <= 0 || tokens > h->cfg.max_tokens)
+        return fail(h, FTM_ERR_BAD, "moe: ep_plan_seg: %d tokens (max_tokens %d)", tokens, h->cfg.max_tokens);
+    cudaStream_t s = pick(h, stream);
+    const int routes = tokens * h->cfg.top_k;
+    CU(h, cudaMemsetAsync(h->flags + 1, 0, sizeof(int32_t), s));
+    // positions the permutation build leaves unwritten (a route whose expert id is out of range) read as -1
+    CU(h, cudaMemsetAsync(route_idx, 0xff, (size_t)routes * sizeof(int32_t), s));
+    h->launches += launch_csr_build(ids, routes, h->cfg.experts, h->seg, route_idx, h->csr_scratch, h->flags + 1, h->ctx(s));
+    CU(h, cudaMemcpyAsync(seg_out, h->seg, (size_t)(h->cfg.experts + 1) * sizeof(int32_t), cudaMemcpyDeviceToDevice, s));
+    CU(h, cudaGetLastError());
+    return FTM_OK;
+}
+
+FTM_API int ftm_ep_dispatch_sorted(ftm_handle* h, const void* x_bf16, const int32_t* ids, const float* weights,
+                                   const int32_t* route_idx, int32_t tokens, int32_t ep_size, int32_t ep_rank,
+                                   const int32_t* seg_all, const uint64_t* peer_xg, const uint64_t* peer_weight,
+                                   const uint64_t* peer_row_scale, int64_t capacity_rows, void* stream) {
+    if (!h) return FTM_ERR_BAD;
+    std::lock_guard<std::mutex> lk(h->mu);
+    DeviceGuard dg(h->cfg.ordinal);
+    if (!x_bf16 || !ids || !weights || !route_idx || !seg_all || !peer_xg || !peer_weight || !peer_row_scale)
+        return fail(h, FTM_ERR_BAD, "moe: ep_dispatch_sorted: null buffer");
+    if (tokens <= 0 || tokens > h->cfg.max_tokens)
+        return fail(h, FTM_ERR_BAD, "moe: ep_dispatch_sorted: %d tokens (max_tokens %d)", tokens, h->cfg.max_tokens);
+    if (ep_size < 1 || ep_size > 32 || h->cfg.experts % ep_size || ep_rank < 0 || ep_rank >= ep_size || capacity_rows < 1)
+        return fail(h, FTM_ERR_BAD, "moe: ep_dispatch_sorted: rank %d of %d, capacity %lld", ep_rank, ep_size, (long long)capacity_rows);
+    if (h->cfg.hidden != 2048)
+        return fail(h, FTM_ERR_NOT_SUPPORTED, "moe: ep_dispatch_sorted is built for hidden 2048, this adapter has %d", h->cfg.hidden);
+    h->launches += launch_ep_dispatch_sorted((const __nv_bfloat16*)x_bf16, ids, weights, route_idx, seg_all, tokens, h->cfg.top_k,
+                                             h->cfg.experts, ep_size, ep_rank, peer_xg, peer_weight, peer_row_scale,
+                                             capacity_rows, h->flags + 2, h->ctx(pick(h, stream)));
+    CU(h, cudaGetLastError());
+    return FTM_OK;
+}
+
+FTM_API int ftm_ep_experts_presorted(ftm_handle* h, int32_t layer, const void* xg_f16, const float* weights,
+                                     const float* row_scale, int32_t rows, int64_t xg_capacity_rows, int32_t ep_size,
+                                     int32_t ep_rank, const int32_t* seg_all, const uint64_t* peer_back,
+                                     int64_t back_capacity_rows, void* stream) {
+    if (!h) return FTM_ERR_BAD;
+    std::lock_guard<std::mutex> lk(h->mu);
+    DeviceGuard dg(h->cfg.ordinal);
+    if (!xg_f16 || !weights || !row_scale || !seg_all || !peer_back)
+        return fail(h, FTM_ERR_BAD, "moe: ep_experts_presorted: null buffer");
+    if (layer < 0 || layer >= h->cfg.layers) return fail(h, FTM_ERR_BAD, "moe: layer %d of %d", layer, h->cfg.layers);
+    if (h->cfg.top_k != 1)
+        return fail(h, FTM_ERR_BAD, "moe: ep_experts_presorted needs an owner adapter (top_k 1), this one has top_k %d", h->cfg.top_k);
+    if (ep_size < 1 || ep_size > 32 || h->cfg.experts % ep_size || ep_rank < 0 || ep_rank >= ep_size || back_capacity_rows < 1 ||
+        xg_capacity_rows < rows)
+        return fail(h, FTM_ERR_BAD, "moe: ep_experts_presorted: rank %d of %d, %d rows in a matrix of %lld", ep_rank, ep_size, rows,
+                    (long long)xg_capacity_rows);
+    int rc = check_tokens(h, rows, 1);
+    if (rc != FTM_OK) return rc;
+    if (!h->maps.ok || !prefill_umma_supported(h->cfg.hidden, h->cfg.inter, h->cfg.slots, h->cfg.experts, true))
+        return fail(h, FTM_ERR_NOT_SUPPORTED, "moe: ep_experts_presorted needs the grouped GEMM (hidden 2048, inter 512)");
+    if ((reinterpret_cast<uintptr_t>(xg_f16) & 127) != 0)
+        return fail(h, FTM_ERR_BAD, "moe: ep_experts_presorted: the activation matrix must be 128-byte aligned");
+    // the activation maps follow the caller's matrix; its address does not change between steps
+    if (h->maps_ext_xg != xg_f16 || h->maps_ext_rows != xg_capacity_rows || !h->maps_ext.ok) {
+        if (!prefill_build_maps(bank_view(h), (const __half*)xg_f16, reinterpret_cast<const __half*>(h->ic2), (size_t)xg_capacity_rows,
+                                &h->maps_ext))
+            return fail(h, FTM_ERR_CUDA, "moe: driver: cuTensorMapEncodeTiled failed");
+        h->maps_ext_xg = xg_f16;
+        h->maps_ext_rows = xg_capacity_rows;
+    }
+    PrefillScratch sc{};
+    sc.seg = h->seg; sc.groups = h->groups; sc.n_groups = h->n_groups; sc.ic1 = h->ic2p;
+    sc.ic2h = reinterpret_cast<__half*>(h->ic2); sc.row_scale2 = h->row_scale2; sc.y = h->yroute; sc.err = h->flags + 2;
+    const int per = h->cfg.experts / ep_size;
+    const int32_t* slot_of_bin = h->d_slot_for_id + (size_t)layer * h->cfg.experts + (size_t)ep_rank * per;
+    EpReturnTo ret{ep_size, ep_rank, nullptr, peer_back, (long long)back_capacity_rows};
+    int n = launch_prefill_umma_presorted(bank_view(h), row_scale, weights, rows, seg_all, h->cfg.experts, slot_of_bin, sc,
+                                          h->sm_count, ret, h->maps_ext, h->ctx(pick(h, stream)));
+    if (n < 0) return fail(h, FTM_ERR_CUDA, "moe: the grouped GEMM's tensor maps are not built");
+    h->launches += n;
     CU(h, cudaGetLastError());
     h->steps++;
     return FTM_OK;

@@ -243,6 +243,96 @@ ep_dispatch_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restric
     }
 }
 
+
+// ---- dispatch into the owner's sorted activation matrix -----------------------------------------
+// seg_all[s * (experts + 1) + e] = first position of expert e in rank s's send order (its permutation build's
+// prefix over the layer's experts), all-gathered.  From it every rank knows where each of its routes lands in
+// the owner's matrix SORTED BY EXPERT (within an expert: source rank, then the source's send order), so the
+// owner needs neither a permutation build nor a gather pass: this kernel reads a token's row once, scales it
+// to f16 exactly as the owner's gather would (largest magnitude into [2^14, 2^15), a power of two) and stores
+// row, route weight and row scale at that position over peer memory.  One warp per route, hidden = 2048.
+__device__ __forceinline__ long long ep_sorted_row(const int32_t* __restrict__ seg_all, int experts, int per, int world, int rank,
+                                                   int e, int lane) {
+    // rows of the owner's experts before e from every source, plus the rows of e from the sources before this one
+    const int p0 = (e / per) * per;
+    long long v = 0;
+    if (lane < world) {
+        const int32_t* sg = seg_all + (size_t)lane * (experts + 1);
+        v = sg[e] - sg[p0];
+        if (lane < rank) v += sg[e + 1] - sg[e];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__global__ void __launch_bounds__(128)
+ep_dispatch_sorted_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ ids, const float* __restrict__ weights,
+                          const int32_t* __restrict__ route_idx, const int32_t* __restrict__ seg_all, int routes, int top_k,
+                          int experts, int per, int world, int rank, const uint64_t* __restrict__ peer_xg,
+                          const uint64_t* __restrict__ peer_w, const uint64_t* __restrict__ peer_rs, long long capacity,
+                          int32_t* err) {
+    constexpr int H = 2048, kChunks = 8;     // a lane holds 8 chunks of 8 k
+    const int lane = threadIdx.x % 32;
+    const int32_t* const seg = seg_all + (size_t)rank * (experts + 1);
+    int i = blockIdx.x * 4 + threadIdx.x / 32;
+    if (i >= routes) return;
+    // walk the send order starting at the next rank's block (see ep_dispatch_kernel)
+    i += seg[((rank + 1) % world) * per];
+    if (i >= routes) i -= routes;
+    const int r = (i >= 0 && i < routes) ? route_idx[i] : -1;
+    const int e = (r >= 0 && r < routes) ? ids[r] : -1;
+    if (e < 0 || e >= per * world) {
+        if (lane == 0) atomicExch(err, 4);
+        return;
+    }
+    const int p = e / per;
+    const long long row = ep_sorted_row(seg_all, experts, per, world, rank, e, lane) + (i - seg[e]);
+    if (row < 0 || row >= capacity || i < seg[e]) {   // never store outside the owner's buffers
+        if (lane == 0) atomicExch(err, 4);
+        return;
+    }
+    const __nv_bfloat16* const src = x + (size_t)(r / top_k) * H;
+    uint4 raw[kChunks];
+#pragma unroll
+    for (int c = 0; c < kChunks; c++) raw[c] = *reinterpret_cast<const uint4*>(src + (c * 32 + lane) * 8);
+    float v[kChunks][8];
+    float m = 0.f;
+#pragma unroll
+    for (int c = 0; c < kChunks; c++) {
+        const uint32_t w[4] = {raw[c].x, raw[c].y, raw[c].z, raw[c].w};
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            const float2 f = bf16x2_to_f32(w[q]);
+            v[c][2 * q] = f.x;
+            v[c][2 * q + 1] = f.y;
+            m = fmaxf(m, fmaxf(fabsf(f.x), fabsf(f.y)));
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    const int ex = max((int)((__float_as_uint(m) >> 23) & 0xff), 15);
+    float inv = 1.0f, sc = 1.0f;
+    if (ex < 255) {
+        inv = __uint_as_float((uint32_t)(127 + 14 - (ex - 127)) << 23);
+        sc = __uint_as_float((uint32_t)(127 - 14 + (ex - 127)) << 23);
+    }
+    __half* const dst = reinterpret_cast<__half*>(peer_xg[p]) + (size_t)row * H;
+#pragma unroll
+    for (int c = 0; c < kChunks; c++) {
+        __half2 h[4];
+#pragma unroll
+        for (int q = 0; q < 4; q++) h[q] = __floats2half2_rn(v[c][2 * q] * inv, v[c][2 * q + 1] * inv);
+        *reinterpret_cast<uint4*>(dst + (c * 32 + lane) * 8) =
+            make_uint4(*reinterpret_cast<uint32_t*>(&h[0]), *reinterpret_cast<uint32_t*>(&h[1]),
+                       *reinterpret_cast<uint32_t*>(&h[2]), *reinterpret_cast<uint32_t*>(&h[3]));
+    }
+    if (lane == 0) {
+        reinterpret_cast<float*>(peer_w[p])[row] = weights[r];
+        reinterpret_cast<float*>(peer_rs[p])[row] = sc;
+    }
+}
+
 // return: row i of the owner's output (receive order) goes to the position its source packed it at.  With
 // pos_of_route the owner's rows are still sorted by expert (y row pos_of_route[i] belongs to received row i,
 // a received row whose expert is not resident returns zeros): the un-permute pass and its extra read and
@@ -321,6 +411,19 @@ int launch_ep_return(const __nv_bfloat16* y, const int32_t* pos_of_route, const 
     c.begin(K_EP_COMBINE);
     ep_return_kernel<<<(n + kEpRows - 1) / kEpRows, 128, 0, c.s>>>(y, pos_of_route, route_slot, n, hidden, world, rank, counts_all,
                                                                   peer_back, capacity, err);
+    c.end();
+    return 1;
+}
+
+int launch_ep_dispatch_sorted(const __nv_bfloat16* x, const int32_t* ids, const float* weights, const int32_t* route_idx,
+                              const int32_t* seg_all, int tokens, int top_k, int experts, int world, int rank,
+                              const uint64_t* peer_xg, const uint64_t* peer_w, const uint64_t* peer_rs, long long capacity,
+                              int32_t* err, const Ctx& c) {
+    const int routes = tokens * top_k;
+    c.begin(K_EP_PACK);
+    ep_dispatch_sorted_kernel<<<(routes + 3) / 4, 128, 0, c.s>>>(x, ids, weights, route_idx, seg_all, routes, top_k, experts,
+                                                               experts / world, world, rank, peer_xg, peer_w, peer_rs, capacity,
+                                                               err);
     c.end();
     return 1;
 }

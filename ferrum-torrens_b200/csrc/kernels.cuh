@@ -182,6 +182,9 @@ int launch_prefill_umma(const BankView& b, const void* x, int x_dtype, const Dec
                         const float* route_weight, int tokens, int top_k, PrefillScratch sc, int sm_count,
                         const float* shared, const float* se_gate, cudaEvent_t join, void* out, int out_dtype,
                         const PrefillMaps& maps, const Ctx& c, const EpReturnTo* ret = nullptr);
+int launch_prefill_umma_presorted(const BankView& b, const float* row_scale, const float* route_weight, int rows,
+                                  const int32_t* seg_all, int experts, const int32_t* slot_of_bin, PrefillScratch sc,
+                                  int sm_count, const EpReturnTo& ret, const PrefillMaps& maps, const Ctx& c);
 
 // shared_expert.cu
 int launch_shared_expert(const __nv_bfloat16* x, int tokens, int hidden, int shared_inter,
@@ -206,6 +209,10 @@ int launch_ep_combine(const void* y, int y_dtype, const int32_t* route_idx, int3
                       int top_k, int hidden, const float* shared, const float* se_gate, void* out, int out_dtype,
                       const Ctx& c);
 int launch_ep_counts(const int32_t* seg, int experts, int ranks, int32_t* counts, const Ctx& c);
+int launch_ep_dispatch_sorted(const __nv_bfloat16* x, const int32_t* ids, const float* weights, const int32_t* route_idx,
+                              const int32_t* seg_all, int tokens, int top_k, int experts, int world, int rank,
+                              const uint64_t* peer_xg, const uint64_t* peer_w, const uint64_t* peer_rs, long long capacity,
+                              int32_t* err, const Ctx& c);
 int launch_ep_dispatch(const __nv_bfloat16* x, const int32_t* ids, const float* weights, const int32_t* route_idx,
                        const int32_t* seg, int tokens, int top_k, int hidden, int experts, int world, int rank,
                        const int32_t* counts_all, const uint64_t* peer_x, const uint64_t* peer_meta, long long capacity,

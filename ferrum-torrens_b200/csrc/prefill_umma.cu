@@ -186,7 +186,7 @@ struct UmmaArgs {
     const uint16_t* global;    // [slots, N] f16 row globals
     const int4* groups;        // (slot, first sorted row, rows <= 128, 0)
     const int32_t* n_groups;
-    const int32_t* route_idx;  // sorted position -> route
+    const int32_t* route_idx;  // sorted position -> route (null: the rows arrived sorted, position = route)
     const float* row_scale;    // per sorted row: power-of-two scale of the activations
     const float* route_weight; // down only, indexed by route
     float* ic1;                // gate_up out [rows, 2 * inter] f32 (sorted rows): gate | up, before silu
@@ -474,7 +474,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
                     float f = 0.f;
                     if (i < cnt) {
                         f = a.row_scale[pos0 + i];
-                        if (!GATE_UP) f *= a.route_weight[a.route_idx[pos0 + i]];
+                        if (!GATE_UP) f *= a.route_weight[a.route_idx ? a.route_idx[pos0 + i] : pos0 + i];
                     }
                     fac[q] = f;
                 }
@@ -537,7 +537,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
                     float f = 0.f;
                     if (tid < cnt) {
                         f = a.row_scale[pos0 + tid];
-                        if (!GATE_UP) f *= a.route_weight[a.route_idx[pos0 + tid]];
+                        if (!GATE_UP) f *= a.route_weight[a.route_idx ? a.route_idx[pos0 + tid] : pos0 + tid];
                     }
                     fac[tid] = f;
                 }
@@ -667,6 +667,67 @@ ep_row_dest_kernel(const int32_t* __restrict__ pos_of_route, const int32_t* __re
                 dropped = true;
             else
                 row_dest[pos_of_route[i]] = dest;
+        }
+    }
+    unsigned todo = __ballot_sync(0xffffffffu, dropped);
+    while (todo) {
+        const int src = __ffs(todo) - 1;
+        todo &= todo - 1;
+        uint4* const z = reinterpret_cast<uint4*>(__shfl_sync(0xffffffffu, dest, src));
+        for (int c = lane; c < H / 8; c += 32) z[c] = make_uint4(0, 0, 0, 0);
+    }
+}
+
+
+// ---- expert-parallel owner whose rows arrived sorted (ep_dispatch_sorted_kernel) -------------------
+// seg_owner[le] = first row of local expert le in the owner's matrix, le = 0 .. per (the total at per)
+__global__ void ep_owner_seg_kernel(const int32_t* __restrict__ seg_all, int experts, int per, int world, int rank,
+                                    int32_t* __restrict__ seg_owner) {
+    const int le = blockIdx.x * blockDim.x + threadIdx.x;
+    if (le > per) return;
+    int v = 0;
+    for (int s = 0; s < world; s++) {
+        const int32_t* sg = seg_all + (size_t)s * (experts + 1);
+        v += sg[rank * per + le] - sg[rank * per];
+    }
+    seg_owner[le] = v;
+}
+
+// One thread per sorted row: the address of its output row in its source's back buffer (row seg_s[e] + j of
+// source s, the position the source sent it from).  A row of an expert that is not resident takes no part in
+// the GEMM and is zero-filled there.
+__global__ void __launch_bounds__(128)
+ep_row_dest_sorted_kernel(const int32_t* __restrict__ seg_all, const int32_t* __restrict__ seg_owner,
+                          const int32_t* __restrict__ slot_of_bin, int slots, int n, int H, int experts, int per, int world,
+                          int rank, const uint64_t* __restrict__ peer_back, long long capacity,
+                          uint64_t* __restrict__ row_dest, int32_t* err) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    const int lane = threadIdx.x & 31;
+    uint64_t dest = 0;
+    bool dropped = false;
+    if (r < n) {
+        int lo = 0, hi = per;              // largest le with seg_owner[le] <= r
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (seg_owner[mid] <= r) lo = mid; else hi = mid;
+        }
+        const int e = rank * per + lo;
+        int j = r - seg_owner[lo], s = 0;
+        for (; s < world; s++) {
+            const int32_t* sg = seg_all + (size_t)s * (experts + 1);
+            const int c = sg[e + 1] - sg[e];
+            if (j < c) break;
+            j -= c;
+        }
+        long long row = -1;
+        if (s < world) row = (long long)seg_all[(size_t)s * (experts + 1) + e] + j;
+        if (row < 0 || row >= capacity) {
+            atomicExch(err, 4);
+        } else {
+            dest = peer_back[s] + (uint64_t)row * H * sizeof(__nv_bfloat16);
+            const int slot = slot_of_bin[lo];
+            if (slot < 0 || slot >= slots) dropped = true;
+            row_dest[r] = dropped ? 0 : dest;
         }
     }
     unsigned todo = __ballot_sync(0xffffffffu, dropped);
@@ -851,6 +912,52 @@ int launch_prefill_umma(const BankView& b, const void* x, int x_dtype, const Dec
     }
     c.end();
     return launches + (out ? 2 : 1);
+}
+
+// The owner's step on rows that arrived sorted by expert as scaled f16 (xg, row_scale, route_weight: one entry per
+// row, in this GPU's memory): no permutation build and no gather; groups from the all-gathered prefixes, the two
+// GEMMs, every finished row stored by the down GEMM into its source's back buffer.  `maps` must hold activation
+// maps encoded on xg.
+int launch_prefill_umma_presorted(const BankView& b, const float* row_scale, const float* route_weight, int rows,
+                                  const int32_t* seg_all, int experts, const int32_t* slot_of_bin, PrefillScratch sc,
+                                  int sm_count, const EpReturnTo& ret, const PrefillMaps& maps, const Ctx& c) {
+    if (!maps.ok) return -1;
+    const int per = experts / ret.world;
+    int launches = 0;
+    c.begin(K_CSR);
+    ep_owner_seg_kernel<<<(per + 1 + 127) / 128, 128, 0, c.s>>>(seg_all, experts, per, ret.world, ret.rank, sc.seg);
+    c.end();
+    launches += 1 + launch_groups_from_csr(sc.seg, per, slot_of_bin, b.slots, kTileTok, sc.groups, sc.n_groups, c);
+    uint64_t* const row_dest = reinterpret_cast<uint64_t*>(sc.y);
+    c.begin(K_EP_COMBINE);
+    ep_row_dest_sorted_kernel<<<(rows + 127) / 128, 128, 0, c.s>>>(seg_all, sc.seg, slot_of_bin, b.slots, rows, b.hidden, experts, per,
+                                                                 ret.world, ret.rank, ret.peer_back, ret.capacity, row_dest, sc.err);
+    c.end();
+    launches++;
+    XMaps map_x, map_h;
+    for (int q = 0; q < 4; q++) {
+        map_x.m[q] = maps.x[q];
+        map_h.m[q] = maps.h[q];
+    }
+    static PerDeviceOnce once_gu, once_ret;
+    allow_dyn_smem(once_gu, umma_grouped_gemm_kernel<true, 2048, false>, kUmmaSmem);
+    allow_dyn_smem(once_ret, umma_grouped_gemm_kernel<false, 512, true>, kUmmaSmem);
+    UmmaArgs a{};
+    a.groups = sc.groups; a.n_groups = sc.n_groups; a.route_idx = nullptr; a.err = sc.err;
+    a.global = b.gu_global; a.row_scale = row_scale;
+    a.ic1 = sc.ic1; a.N = 2 * b.inter;
+    c.begin(K_GROUPED_GATE_UP);
+    umma_grouped_gemm_kernel<true, 2048, false><<<sm_count, kThreads, kUmmaSmem, c.s>>>(map_x, maps.gp, maps.gs, a);
+    c.end();
+    c.begin(K_PREFILL_RESCALE);
+    prefill_rescale_kernel<<<(rows + 7) / 8, 256, 0, c.s>>>(sc.ic1, sc.seg + per, b.inter, sc.ic2h, sc.row_scale2);
+    c.end();
+    a.global = b.dn_global; a.row_scale = sc.row_scale2;
+    a.route_weight = route_weight; a.y = nullptr; a.y_f32 = 0; a.N = b.hidden; a.row_dest = row_dest;
+    c.begin(K_GROUPED_DOWN);
+    umma_grouped_gemm_kernel<false, 512, true><<<sm_count, kThreads, kUmmaSmem, c.s>>>(map_h, maps.dp, maps.ds, a);
+    c.end();
+    return launches + 3;
 }
 
 }  // namespace ftm

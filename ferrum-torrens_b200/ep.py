@@ -116,6 +116,14 @@ class LibBackend:
         self.p2p_back = symm.empty((self.send_capacity, H), dtype=torch.bfloat16, device=dev)
         self._symm = [symm.rendezvous(t, g.group_name) for t in (self.p2p_recv_x, self.p2p_recv_meta, self.p2p_back)]
         self.peer_x, self.peer_meta, self.peer_back = (h.buffer_ptrs_dev for h in self._symm)
+        # the sorted exchange (forward_p2p_sorted): the owner's activation matrix as scaled f16, route weights, row scales
+        self.p2p_xg = self.p2p_w = self.p2p_rs = None
+        if H == 2048:
+            self.p2p_xg = symm.empty((self.recv_capacity, H), dtype=torch.float16, device=dev)
+            self.p2p_w = symm.empty((self.recv_capacity,), dtype=torch.float32, device=dev)
+            self.p2p_rs = symm.empty((self.recv_capacity,), dtype=torch.float32, device=dev)
+            self._symm_sorted = [symm.rendezvous(t, g.group_name) for t in (self.p2p_xg, self.p2p_w, self.p2p_rs)]
+            self.peer_xg, self.peer_w, self.peer_rs = (h.buffer_ptrs_dev for h in self._symm_sorted)
         self._tick = torch.zeros((1,), dtype=torch.int32, device=dev)
         self._regions = {}
 
@@ -333,6 +341,60 @@ class ExpertParallelMoE:
             fronts[m].ep_combine(b.p2p_back[m * send_cap:m * send_cap + sum(sc[m])], plans[m][0],
                                  shared[lo:hi] if shared is not None else None,
                                  se_gate[lo:hi] if se_gate is not None else None, out[lo:hi])
+        mark("combined")
+        return ids, w
+
+    def forward_p2p_sorted(self, layer: int, x, gate_w, sh_gate_up, sh_down, sh_gate, out, record=None):
+        """forward_p2p without a permutation build or a gather pass on the owner: the ranks all-gather the prefixes
+        of their send orders over the experts, from which every rank knows where each of its routes lands in the
+        owner's activation matrix SORTED BY EXPERT; the dispatch kernel stores the rows there as the scaled f16 the
+        grouped GEMM reads, and the owner runs its two GEMMs on them at once (the down GEMM returns the rows, as in
+        forward_p2p).  Steps in which some owner receives too few rows for the grouped GEMM (at most 2048) take
+        forward_p2p; the decision is made from the all-gathered prefixes, so every rank makes the same one."""
+        mark = record or (lambda name: None)
+        b = self.b
+        world = self.world
+        if getattr(b, "p2p_xg", None) is None:
+            return self.forward_p2p(layer, x, gate_w, sh_gate_up, sh_down, sh_gate, out, record=record)
+        ids, w = b.route(x, gate_w)
+        route_idx, seg = b.front.ep_plan_seg(ids)
+        E = b.experts
+        seg_all = torch.empty((world * (E + 1),), dtype=torch.int32, device=seg.device)
+        dist.all_gather_into_tensor(seg_all, seg, group=self.group)
+        cur = torch.cuda.current_stream()
+        shared = se_gate = None
+        side = None
+        if sh_gate_up is not None:
+            side = self._side_stream(x.device, "_side")
+            side.wait_stream(cur)
+            with torch.cuda.stream(side):
+                shared, se_gate = b.shared(x, sh_gate_up, sh_down, sh_gate)
+        bounds = seg_all.reshape(world, E + 1)[:, ::b.per].tolist()     # the one host read-back: [source][owner boundary]
+        sent = [[bounds[s][p + 1] - bounds[s][p] for p in range(world)] for s in range(world)]
+        recv = [sum(sent[s][p] for s in range(world)) for p in range(world)]
+        sc, rc = sent[b.rank], [sent[s][b.rank] for s in range(world)]
+        self.last_counts = (sc, rc)
+        n = recv[b.rank]
+        if min(recv) <= 2048:
+            # the small-step exchange; its own plan and counts (this one's are not in its format)
+            if side is not None:
+                cur.wait_stream(side)
+            return self.forward_p2p(layer, x, gate_w, sh_gate_up, sh_down, sh_gate, out, record=record)
+        if n > b.recv_capacity:
+            raise _moe.bad(f"{n} routes received, the receive buffer was sized for {b.recv_capacity}")
+        mark("packed")
+        b.front.ep_dispatch_sorted(x, ids, w, route_idx, world, b.rank, seg_all, b.peer_xg, b.peer_w, b.peer_rs, b.recv_capacity)
+        self._barrier(b)
+        mark("dispatched")
+        b.owner.ep_experts_presorted(layer, b.p2p_xg, b.p2p_w, b.p2p_rs, n, world, b.rank, seg_all, b.peer_back, b.send_capacity)
+        mark("computed")
+        self._barrier(b)
+        mark("returned")
+        if side is not None:
+            cur.wait_stream(side)
+            shared.record_stream(cur)
+            se_gate.record_stream(cur)
+        b.combine(b.p2p_back[:sum(sc)], route_idx, shared, se_gate, out)
         mark("combined")
         return ids, w
 

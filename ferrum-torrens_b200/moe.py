@@ -502,6 +502,35 @@ class B200MoE:
         self._check(rc)
         return True
 
+    def ep_plan_seg(self, ids, stream=None):
+        """ep_plan that also returns the prefix of the send order over the layer's experts: (route_idx [T*k],
+        seg [experts + 1]), both int32 on the device."""
+        torch = _torch()
+        tokens = ids.numel() // self.top_k
+        route_idx = torch.empty((tokens * self.top_k,), dtype=torch.int32, device=ids.device)
+        seg = torch.empty((self.experts + 1,), dtype=torch.int32, device=ids.device)
+        self._check(self._lib.ftm_ep_plan_seg(self._h, _dev(ids, "ids"), tokens, _dev(route_idx, "route_idx"), _dev(seg, "seg"),
+                                              _stream_ptr(stream)))
+        return route_idx, seg
+
+    def ep_dispatch_sorted(self, x, ids, weights, route_idx, ep_size: int, ep_rank: int, seg_all, peer_xg: int, peer_weight: int,
+                           peer_row_scale: int, capacity_rows: int, stream=None):
+        """Store every route's row (f16, scaled by a power of two), weight and row scale at its place in the owner's
+        matrix sorted by expert; seg_all [ep_size, experts + 1] are the all-gathered prefixes of ep_plan_seg."""
+        tokens = x.numel() // self.shapes.hidden
+        self._check(self._lib.ftm_ep_dispatch_sorted(
+            self._h, _dev(x, "x"), _dev(ids, "ids"), _dev(weights, "weights"), _dev(route_idx, "route_idx"), tokens, ep_size,
+            ep_rank, _dev(seg_all, "seg_all"), C.c_void_p(peer_xg), C.c_void_p(peer_weight), C.c_void_p(peer_row_scale),
+            capacity_rows, _stream_ptr(stream)))
+
+    def ep_experts_presorted(self, layer: int, xg, weights, row_scale, rows: int, ep_size: int, ep_rank: int, seg_all,
+                             peer_back: int, back_capacity_rows: int, stream=None):
+        """Owner side of ep_dispatch_sorted: both GEMMs on the first `rows` rows of xg [capacity, hidden] f16, every
+        finished row stored by the down GEMM into its source's back buffer."""
+        self._check(self._lib.ftm_ep_experts_presorted(
+            self._h, layer, _dev(xg, "xg"), _dev(weights, "weights"), _dev(row_scale, "row_scale"), rows, xg.shape[0], ep_size,
+            ep_rank, _dev(seg_all, "seg_all"), C.c_void_p(peer_back), back_capacity_rows, _stream_ptr(stream)))
+
     def ep_return_sorted(self, rows: int, ep_size: int, ep_rank: int, counts_all, peer_back: int, capacity_rows: int,
                          stream=None):
         """Owner side: store the rows ep_experts_sorted left in the adapter into their sources' back buffers."""

@@ -361,6 +361,28 @@ FTM_API int ftm_ep_experts_return(ftm_handle* h, int32_t layer, const void* x_bf
                                   const float* weights, int32_t rows, int32_t ep_size, int32_t ep_rank,
                                   const int32_t* counts_all, const uint64_t* peer_back, int64_t capacity_rows,
                                   void* stream);
+/* The exchange without a permutation build or a gather pass on the owner.  ftm_ep_plan_seg is ftm_ep_plan that
+ * also hands out the prefix of the send order over the layer's experts (seg_out [experts + 1], device); the
+ * caller all-gathers those prefixes into seg_all [ep_size, experts + 1].  From seg_all every rank knows where
+ * each of its routes lands in the owner's activation matrix sorted by expert (within an expert: source rank,
+ * then the source's send order), and ftm_ep_dispatch_sorted stores there, over peer memory, the token's row as
+ * f16 scaled by a power of two (the layout the grouped GEMM's activation tiles are read from), its route weight
+ * and its row scale: peer_xg / peer_weight / peer_row_scale are device tables of ep_size base addresses of
+ * [capacity_rows, hidden] f16 and [capacity_rows] f32 buffers.  hidden 2048.  After the caller's barrier the owner
+ * runs ftm_ep_experts_presorted on its own three buffers (xg 128-byte aligned, xg_capacity_rows rows long): groups
+ * from seg_all, both GEMMs, every finished row stored by the down GEMM at row (prefix of its expert in the
+ * source's send order + its index) of peer_back[source], i.e. at the position the source sent it from.  rows =
+ * the rows this owner received (more than 0); an expert that is not resident returns zero rows. */
+FTM_API int ftm_ep_plan_seg(ftm_handle* h, const int32_t* ids, int32_t tokens, int32_t* route_idx, int32_t* seg_out,
+                            void* stream);
+FTM_API int ftm_ep_dispatch_sorted(ftm_handle* h, const void* x_bf16, const int32_t* ids, const float* weights,
+                                   const int32_t* route_idx, int32_t tokens, int32_t ep_size, int32_t ep_rank,
+                                   const int32_t* seg_all, const uint64_t* peer_xg, const uint64_t* peer_weight,
+                                   const uint64_t* peer_row_scale, int64_t capacity_rows, void* stream);
+FTM_API int ftm_ep_experts_presorted(ftm_handle* h, int32_t layer, const void* xg_f16, const float* weights,
+                                     const float* row_scale, int32_t rows, int64_t xg_capacity_rows, int32_t ep_size,
+                                     int32_t ep_rank, const int32_t* seg_all, const uint64_t* peer_back,
+                                     int64_t back_capacity_rows, void* stream);
 FTM_API int ftm_ep_combine(ftm_handle* h, const void* y, int y_dtype, const int32_t* route_idx, const float* shared,
                            const float* se_gate, int32_t tokens, void* out, int out_dtype, void* stream);
 

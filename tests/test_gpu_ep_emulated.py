@@ -230,6 +230,31 @@ def test_sorted_return_on_the_grouped_gemm_path_emulated():
         assert torch.equal(ids, want_ids)
         rel = float((out - want).norm() / want.norm())
         assert rel < 5e-3, (r, rel)
+    # the same step with the rows dispatched straight into the owners' sorted activation matrices: no permutation
+    # build and no gather on the owner; the rows reach the GEMMs in the same order, so the results are bit-equal
+    plans = [fronts[r].ep_plan_seg(routed[r][0]) for r in range(world)]
+    seg_all = torch.stack([sg for _, sg in plans]).contiguous()
+    for r in range(world):
+        assert torch.equal(plans[r][0], routed[r][2]), "the same send order as ep_plan"
+    xg = [torch.zeros((cap, Hh), dtype=torch.float16, device=dev) for _ in range(world)]
+    wbuf = [torch.zeros((cap,), dtype=torch.float32, device=dev) for _ in range(world)]
+    rsbuf = [torch.zeros((cap,), dtype=torch.float32, device=dev) for _ in range(world)]
+    peer_xg, peer_w, peer_rs = ptrs(xg), ptrs(wbuf), ptrs(rsbuf)
+    for r in range(world):
+        ids, w, route_idx, _ = routed[r]
+        fronts[r].ep_dispatch_sorted(xs[r], ids, w, route_idx, world, r, seg_all, peer_xg.data_ptr(), peer_w.data_ptr(),
+                                     peer_rs.data_ptr(), cap)
+    torch.cuda.synchronize()
+    back = [torch.zeros((tokens[r] * Kk, Hh), dtype=torch.bfloat16, device=dev) for r in range(world)]
+    peer_back = ptrs(back)
+    for r in range(world):
+        n = int(ca[:, r].sum())
+        owners[r].ep_experts_presorted(0, xg[r], wbuf[r], rsbuf[r], n, world, r, seg_all, peer_back.data_ptr(), max(tokens) * Kk)
+    torch.cuda.synchronize()
+    for r in range(world):
+        fronts[r].sync_status()
+        owners[r].sync_status()
+        assert torch.equal(back[r], results["plain"][r]), "the same rows when they arrive sorted"
     # a step of at most 2048 rows is not taken by this path
     n_small = 100
     assert owners[0].ep_experts_sorted(0, recv_x[0][:n_small], recv_m[0][:n_small, 0].contiguous(),
