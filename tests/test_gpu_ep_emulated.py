@@ -261,3 +261,83 @@ def test_sorted_return_on_the_grouped_gemm_path_emulated():
                                        recv_m[0][:n_small, 1].contiguous().view(torch.float32)) is False
     for m in fronts + owners + [solo]:
         m.close()
+
+
+def test_sorted_dispatch_with_an_expert_that_is_not_resident_and_with_a_short_buffer():
+    """ftm_ep_dispatch_sorted / ftm_ep_experts_presorted, two ranks on one GPU: the rows of an expert the owner does
+    not hold come back as zeros and every other row equals the ordinary path's; a receive matrix that is too short
+    raises the status flag instead of a store outside it."""
+    dev = torch.device("cuda:0")
+    Hh, Ii, Ee, Kk = 2048, 512, 16, 4
+    world, tokens = 2, [680, 690]
+    lay = pkg.synth.make_layer(97, hidden=Hh, inter=Ii, experts=Ee, top_k=Kk, shared_inter=0)
+    shapes = pkg.ExpertShapes(Hh, Ii)
+    per = Ee // world
+    cap = sum(tokens) * Kk
+    missing = 3
+    gate = _bf16(lay.gate_w, dev)
+    fronts, owners = [], []
+    for r in range(world):
+        fronts.append(pkg.B200MoE(0, shapes, 1, experts=Ee, layers=1, top_k=Kk, shared_inter=0, max_tokens=max(tokens)))
+        ow = pkg.B200MoE(0, shapes, per, experts=Ee, layers=1, top_k=1, shared_inter=0, max_tokens=cap)
+        for e in range(r * per, (r + 1) * per):
+            if e != missing:
+                ow.load(0, e, e - r * per, lay.fields(e))
+        owners.append(ow)
+    xs = [_bf16(pkg.synth.make_x(900 + r, tokens[r], Hh), dev) for r in range(world)]
+    ptrs = lambda ts: torch.tensor([t.data_ptr() for t in ts], dtype=torch.int64, device=dev)
+    routed, plans = [], []
+    for r in range(world):
+        ids, w = fronts[r].router(xs[r], gate)
+        route_idx, seg = fronts[r].ep_plan_seg(ids)
+        routed.append((ids, w, route_idx))
+        plans.append(seg)
+    seg_all = torch.stack(plans).contiguous()
+    sa = seg_all.cpu().numpy()
+    recv = [int(sum(sa[s][(p + 1) * per] - sa[s][p * per] for s in range(world))) for p in range(world)]
+    assert min(recv) > 2048
+    xg = [torch.zeros((cap, Hh), dtype=torch.float16, device=dev) for _ in range(world)]
+    wbuf = [torch.zeros((cap,), dtype=torch.float32, device=dev) for _ in range(world)]
+    rsbuf = [torch.zeros((cap,), dtype=torch.float32, device=dev) for _ in range(world)]
+    # the address tables stay alive for as long as a kernel may read them
+    peer_xg, peer_w, peer_rs = ptrs(xg), ptrs(wbuf), ptrs(rsbuf)
+    for r in range(world):
+        ids, w, route_idx = routed[r]
+        fronts[r].ep_dispatch_sorted(xs[r], ids, w, route_idx, world, r, seg_all, peer_xg.data_ptr(), peer_w.data_ptr(),
+                                     peer_rs.data_ptr(), cap)
+    torch.cuda.synchronize()
+    back = [torch.full((tokens[r] * Kk, Hh), 7.0, dtype=torch.bfloat16, device=dev) for r in range(world)]
+    peer_back = ptrs(back)
+    for r in range(world):
+        owners[r].ep_experts_presorted(0, xg[r], wbuf[r], rsbuf[r], recv[r], world, r, seg_all, peer_back.data_ptr(),
+                                       max(tokens) * Kk)
+    torch.cuda.synchronize()
+    for r in range(world):
+        fronts[r].sync_status()
+        owners[r].sync_status()
+        ids, w, route_idx = routed[r]
+        # reference: every route through the ordinary staged call on its owner (missing expert -> zeros)
+        e_of_pos = ids.reshape(-1)[route_idx.long()]
+        for p in range(world):
+            sel = ((e_of_pos // per) == p).nonzero().reshape(-1)
+            if sel.numel() == 0:
+                continue
+            rows = xs[r][(route_idx[sel] // Kk).long()].contiguous()
+            y = torch.empty((sel.numel(), Hh), dtype=torch.bfloat16, device=dev)
+            owners[p].grouped_moe_staged(pkg.MoEDeviceRequest(0, Hh, Ii, 1, rows, e_of_pos[sel].reshape(-1, 1).contiguous(),
+                                                              w.reshape(-1)[route_idx[sel].long()].reshape(-1, 1).contiguous()), y)
+            torch.cuda.synchronize()
+            got = back[r][sel]
+            gone = (e_of_pos[sel] == missing)
+            assert torch.equal(got[gone], torch.zeros_like(got[gone])), "rows of the expert that is not resident are zeros"
+            assert gone.any() or p != missing // per
+            rel = float((got[~gone].float() - y[~gone].float()).norm() / y[~gone].float().norm())
+            assert rel < 5e-3, (r, p, rel)
+    # a receive matrix shorter than the rows it is sent: nothing is stored outside it, the status says so
+    short = 100
+    with pytest.raises(pkg.MoEError):
+        fronts[0].ep_dispatch_sorted(xs[0], routed[0][0], routed[0][1], routed[0][2], world, 0, seg_all, peer_xg.data_ptr(),
+                                     peer_w.data_ptr(), peer_rs.data_ptr(), short)
+        fronts[0].sync_status()
+    for m in fronts + owners:
+        m.close()
