@@ -679,7 +679,7 @@ __device__ __forceinline__ uint32_t ldg_u32(const void* p) {
 template <bool GATE_UP, int K_, int NT_>
 struct LdgCfg {
     static constexpr int K = K_, NT = NT_;
-    static constexpr int kWarps = 8, kThreads = 256;
+    static constexpr int kWarps = GATE_UP ? 10 : 8, kThreads = kWarps * 32;   // gate_up: 96 registers at 10 warps, two CTAs per SM (12 warps spill)
     static constexpr int WINS = K / 128;
     static constexpr int kPre = WINS < 4 ? WINS : 4;     // windows in flight per warp
     static constexpr int RSX = K * 2 + 64;
@@ -688,7 +688,7 @@ struct LdgCfg {
 };
 
 template <bool GATE_UP, int K_, int NT, int OCC, int LV>
-__global__ void __launch_bounds__(256, OCC) expert_ldg_kernel(ExpertArgs a) {
+__global__ void __launch_bounds__((LdgCfg<GATE_UP, K_, NT>::kThreads), OCC) expert_ldg_kernel(ExpertArgs a) {
     using C = LdgCfg<GATE_UP, K_, NT>;
     constexpr int kWarps = C::kWarps, kTok = kGroupTokens * NT, K = C::K, WINS = C::WINS, P = C::kPre, RSX = C::RSX;
     extern __shared__ __align__(128) uint8_t smem[];
