@@ -616,7 +616,9 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
     }
 }
 
-constexpr size_t kUmmaSmem = 1024 + (size_t)kXStages * kTileBytes + (size_t)kRawStages * kRawStageBytes + 40 * 8 + 64 + 4 * kTileTok * sizeof(float) + 4 * 16 * kTileM * sizeof(__nv_bfloat16);
+// the owner's variant (RET) adds the per-token factors and the bf16 staging of its epilogue
+constexpr size_t kUmmaSmemLocal = 1024 + (size_t)kXStages * kTileBytes + (size_t)kRawStages * kRawStageBytes + 40 * 8 + 64 + 64;
+constexpr size_t kUmmaSmem = kUmmaSmemLocal + 4 * kTileTok * sizeof(float) + 4 * 16 * kTileM * sizeof(__nv_bfloat16);
 static_assert(kUmmaSmem <= 227 * 1024, "shared memory of the grouped GEMM CTA");
 
 // f16 matrix [rows, K] row-major, box = 64 k x box_rows, 128-byte swizzle
@@ -870,7 +872,7 @@ int launch_prefill_umma(const BankView& b, const void* x, int x_dtype, const Dec
     a.global = b.gu_global; a.row_scale = sc.row_scale;
     a.ic1 = sc.ic1; a.N = 2 * b.inter;
     c.begin(K_GROUPED_GATE_UP);
-    umma_grouped_gemm_kernel<true, 2048, false><<<sm_count, kThreads, kUmmaSmem, c.s>>>(map_x, map_gp, map_gs, a);
+    umma_grouped_gemm_kernel<true, 2048, false><<<sm_count, kThreads, kUmmaSmemLocal, c.s>>>(map_x, map_gp, map_gs, a);
     c.end();
     c.begin(K_PREFILL_RESCALE);
     prefill_rescale_kernel<<<(routes + 7) / 8, 256, 0, c.s>>>(sc.ic1, sc.seg + nbins, b.inter, sc.ic2h, sc.row_scale2);
@@ -895,7 +897,7 @@ int launch_prefill_umma(const BankView& b, const void* x, int x_dtype, const Dec
     if (ret)
         umma_grouped_gemm_kernel<false, 512, true><<<sm_count, kThreads, kUmmaSmem, c.s>>>(map_h, map_dp, map_ds, a);
     else
-        umma_grouped_gemm_kernel<false, 512, false><<<sm_count, kThreads, kUmmaSmem, c.s>>>(map_h, map_dp, map_ds, a);
+        umma_grouped_gemm_kernel<false, 512, false><<<sm_count, kThreads, kUmmaSmemLocal, c.s>>>(map_h, map_dp, map_ds, a);
     c.end();
     launches += 3;
     if (ret) return launches;
@@ -947,7 +949,7 @@ int launch_prefill_umma_presorted(const BankView& b, const float* row_scale, con
     a.global = b.gu_global; a.row_scale = row_scale;
     a.ic1 = sc.ic1; a.N = 2 * b.inter;
     c.begin(K_GROUPED_GATE_UP);
-    umma_grouped_gemm_kernel<true, 2048, false><<<sm_count, kThreads, kUmmaSmem, c.s>>>(map_x, maps.gp, maps.gs, a);
+    umma_grouped_gemm_kernel<true, 2048, false><<<sm_count, kThreads, kUmmaSmemLocal, c.s>>>(map_x, maps.gp, maps.gs, a);
     c.end();
     c.begin(K_PREFILL_RESCALE);
     prefill_rescale_kernel<<<(rows + 7) / 8, 256, 0, c.s>>>(sc.ic1, sc.seg + per, b.inter, sc.ic2h, sc.row_scale2);
