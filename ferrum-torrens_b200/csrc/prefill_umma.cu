@@ -223,25 +223,26 @@ template <bool GATE_UP, int K, bool RET>
 __global__ void __launch_bounds__(kThreads, 1)
 umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_constant__ CUtensorMap tmap_packed,
                          const __grid_constant__ CUtensorMap tmap_scale, UmmaArgs a) {
-    // Role map.  gate_up (K = 2048, 32 pieces per unit) keeps four dequantiser sets with one weight buffer
-    // each and two epilogue sets.  down (K = 512) has eight pieces per unit and an epilogue as long as its
-    // mainloop: two dequantiser sets with two buffers each (one being filled while the other is multiplied)
-    // and four epilogue sets, two per row tile, each taking every other 16-token step.  The owner's
-    // variant (RET) keeps the gate_up map: its epilogue sets meet at named barriers around shared staging.
-    constexpr int kDeqSets = RET ? 4 : 2;
-    constexpr int kEpiSets = RET ? 2 : 4;
+    // Role map.  Two dequantiser sets (warps 8..15) with two weight buffers each, one being filled while the
+    // other is multiplied, and four epilogue sets, two per row tile (warps 4..7 / 16..19 and 24..27 / 20..23)
+    // taking alternate token steps: with four dequantiser sets and two epilogue sets the dequantisers idled two
+    // thirds of the time while the MMA issuers waited for the accumulators to be read back.  The owner's
+    // variant (RET) gives one raw stage to its epilogue sets' staging buffers.
+    constexpr int kDeqSets = 2;
+    constexpr int kEpiSets = 4;
+    constexpr int kRS = RET ? kRawStages - 1 : kRawStages;   // the owner's variant gives a raw stage to its epilogue staging
     constexpr int kWarpEpi2 = kWarpDeq0 + 4 * kDeqSets;     // down: warps 16..19 row tile 0, 20..23 row tile 1
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment for the swizzled tiles
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* const x_tiles = smem;                                         // [kXStages][16 KiB]: 128 tokens x 64 k
     uint8_t* const raw_ring = x_tiles + kXStages * kTileBytes;             // [kRawStages][packed | scales]
-    uint64_t* const bars = reinterpret_cast<uint64_t*>(raw_ring + kRawStages * kRawStageBytes);
+    uint64_t* const bars = reinterpret_cast<uint64_t*>(raw_ring + kRS * kRawStageBytes);
     uint32_t* const s_tmem = reinterpret_cast<uint32_t*>(bars + 40);
     volatile int* const s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
-    // (RET only) per-token factors [row tile][unit parity][128 tokens], bf16 staging [row tile][parity][16 tokens][128 rows]
+    // (RET only) per-token factors [epilogue set][unit parity][128 tokens], bf16 staging [set][parity][16 tokens][128 rows]
     float* const s_fac = reinterpret_cast<float*>(s_tmem + 16);
-    __nv_bfloat16* const s_stage = reinterpret_cast<__nv_bfloat16*>(s_fac + 4 * kTileTok);
+    __nv_bfloat16* const s_stage = reinterpret_cast<__nv_bfloat16*>(s_fac + 8 * kTileTok);
     const uint32_t bar0 = smem_u32(bars);
     auto X_FULL = [&](int s) { return bar0 + 8u * s; };                 // kXStages <= 8
     auto X_EMPTY = [&](int s) { return bar0 + 8u * (8 + s); };
@@ -257,7 +258,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
             mbar_init(X_FULL(s), 1);
             mbar_init(X_EMPTY(s), 2);
         }
-        for (int s = 0; s < kRawStages; s++) {
+        for (int s = 0; s < kRS; s++) {
             mbar_init(RAW_FULL(s), 1);
             mbar_init(RAW_EMPTY(s), 256);
         }
@@ -321,8 +322,8 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
                 // a stage = two chunks (256 k) of one row tile: full 128-byte lines per weight row
                 for (int q = 0; q < kChunks && ok; q++, it++) {
                     const int cp = q >> 1, r = q & 1;
-                    const int st = it % kRawStages;
-                    ok = mbar_wait_warp(RAW_EMPTY(st), ((it / kRawStages) & 1) ^ 1, s_abort, a.err);
+                    const int st = it % kRS;
+                    ok = mbar_wait_warp(RAW_EMPTY(st), ((it / kRS) & 1) ^ 1, s_abort, a.err);
                     if (!ok) break;
                     if (elect_one()) {
                         const uint32_t dst = smem_u32(raw_ring + (size_t)st * kRawStageBytes);
@@ -405,8 +406,8 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
                 const uint32_t item = item0 + w;
                 const int c = w >> 1;
                 const uint32_t stage = stage0 + 2 * (c >> 1) + (w & 1);      // the raw stage holds chunks c & ~1 and c | 1
-                const int st = stage % kRawStages;
-                ok = mbar_wait(RAW_FULL(st), (stage / kRawStages) & 1, s_abort, a.err);
+                const int st = stage % kRS;
+                ok = mbar_wait(RAW_FULL(st), (stage / kRS) & 1, s_abort, a.err);
                 if (!ok) break;
                 const int wb = item % kWBufs;
                 const uint32_t taddr = tlane + wb * kWCols;
@@ -522,8 +523,12 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
             // one thread = one weight row of its row tile; a column = one token of the group.  The per-token
             // factors of a unit are computed once per set (thread t: token t), left in shared memory and read
             // back as broadcasts; the accumulators are read 32 columns per wait.
+            // Four sets: the two sets of a row tile take alternate 32-token chunks, each with its own factors,
+            // staging buffers and named barrier.
             const int quarter = warp & 3;
-            const int r = (warp >= kWarpEpi1) ? 1 : 0;
+            const int r = (warp < kWarpDeq0) ? 0 : (warp >= kWarpEpi1) ? 1 : ((warp - kWarpEpi2) >> 2);
+            const int half = (warp >= kWarpDeq0 && warp < kWarpEpi1) ? 1 : 0;
+            const int es = r + 2 * half;
             const int tid = quarter * 32 + lane;
             uint32_t unit_i = 0, stage_i = 0;
             for (int u = blockIdx.x; u < n_units; u += gridDim.x, unit_i++) {     // (the abort flag is seen inside the wait)
@@ -532,7 +537,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
                 const int wrow0 = (u % n_pairs) * 2 * kTileM + r * kTileM;
                 const int wrow = wrow0 + tid;
                 const float gl = f16_global_to_f32(a.global[(size_t)grp.x * a.N + wrow]);
-                float* const fac = s_fac + (r * 2 + (unit_i & 1)) * kTileTok;
+                float* const fac = s_fac + (es * 2 + (unit_i & 1)) * kTileTok;
                 {
                     float f = 0.f;
                     if (tid < cnt) {
@@ -552,14 +557,14 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
                     "bar.red.and.pred p, %2, 128, q;\n\t"
                     "selp.u32 %0, 1, 0, p;\n\t}"
                     : "=r"(all_ok)
-                    : "r"((uint32_t)mine), "r"(1 + r)
+                    : "r"((uint32_t)mine), "r"(1 + es)
                     : "memory");
                 if (!all_ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 {
                     const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + kAccCol0 + r * kTileTok;
     #pragma unroll 1
-                    for (int c0 = 0; c0 < cnt; c0 += 32) {      // uniform over the warp
+                    for (int c0 = 32 * half; c0 < cnt; c0 += 64) {      // uniform over the warp
                         float v[2][16];
                         tmem_ld16(taddr + c0, v[0]);
                         tmem_ld16(taddr + c0 + 16, v[1]);
@@ -583,11 +588,11 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
                                 // bf16 rows: the set's 128 rows x 16 tokens go through shared memory, so that every
                                 // thread stores 16 bytes of one token's row and a token's 128 columns leave as one
                                 // 256-byte run (the layout the peer stores of the expert-parallel return want too)
-                                __nv_bfloat16* const st = s_stage + ((r * 2 + (stage_i & 1)) * 16) * kTileM;
+                                __nv_bfloat16* const st = s_stage + ((es * 2 + (stage_i & 1)) * 16) * kTileM;
                                 stage_i++;
     #pragma unroll
                                 for (int j = 0; j < 16; j++) st[j * kTileM + tid] = __float2bfloat16_rn(v[h][j]);
-                                asm volatile("bar.sync %0, 128;" ::"r"(1 + r) : "memory");
+                                asm volatile("bar.sync %0, 128;" ::"r"(1 + es) : "memory");
     #pragma unroll
                                 for (int q = 0; q < 2; q++) {
                                     const int piece = tid + q * 128, tok = cb + piece / 16, c8 = (piece % 16) * 8;
@@ -618,7 +623,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ XMaps xmaps, const __grid_const
 
 // the owner's variant (RET) adds the per-token factors and the bf16 staging of its epilogue
 constexpr size_t kUmmaSmemLocal = 1024 + (size_t)kXStages * kTileBytes + (size_t)kRawStages * kRawStageBytes + 40 * 8 + 64 + 64;
-constexpr size_t kUmmaSmem = kUmmaSmemLocal + 4 * kTileTok * sizeof(float) + 4 * 16 * kTileM * sizeof(__nv_bfloat16);
+constexpr size_t kUmmaSmem = kUmmaSmemLocal - kRawStageBytes + 8 * kTileTok * sizeof(float) + 8 * 16 * kTileM * sizeof(__nv_bfloat16);
 static_assert(kUmmaSmem <= 227 * 1024, "shared memory of the grouped GEMM CTA");
 
 // f16 matrix [rows, K] row-major, box = 64 k x box_rows, 128-byte swizzle
