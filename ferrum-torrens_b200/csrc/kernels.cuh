@@ -99,7 +99,7 @@ int launch_router_fused(const __nv_bfloat16* x, const __nv_bfloat16* gate_w, int
 // scratch: cta_hist needs csr_scratch_ints(routes, bins) int32 entries
 size_t csr_scratch_ints(int routes, int bins);
 int launch_csr_build(const int32_t* route_bin, int routes, int bins, int32_t* seg, int32_t* route_idx,
-                     int32_t* scratch, int32_t* bad_flag, const Ctx& c);
+                     int32_t* scratch, int32_t* bad_flag, const Ctx& c, bool coarse = false);
 int launch_slot_rewrite(const void* expert_ids, int ids_dtype, int routes, int layer, int experts,
                         const int32_t* slot_for_id, int n_ids, int32_t* route_slot, int32_t* route_expert,
                         int32_t* bad_flag, const Ctx& c);

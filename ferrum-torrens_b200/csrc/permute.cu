@@ -27,13 +27,13 @@ constexpr int kWarpRoutes = kChunkRoutes / kWarps;    // contiguous routes per w
 constexpr int kMaxBins = 1024;
 
 __device__ __forceinline__ void count_chunk(const int32_t* __restrict__ route_bin, int routes, int bins,
-                                            int chunk_begin, int* whist /* [kWarps][bins] smem */,
+                                            int chunk_begin, int warp_routes, int* whist /* [kWarps][bins] smem */,
                                             int32_t* bad_flag) {
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     for (int i = threadIdx.x; i < kWarps * bins; i += kThreads) whist[i] = 0;
     __syncthreads();
-    const int begin = chunk_begin + warp * kWarpRoutes;
-    const int end = min(begin + kWarpRoutes, routes);
+    const int begin = min(chunk_begin + warp * warp_routes, routes);
+    const int end = min(begin + warp_routes, routes);
     for (int r = begin + lane; r < end; r += 32) {
         int b = route_bin[r];
         if (b < 0 || b >= bins) {
@@ -47,10 +47,10 @@ __device__ __forceinline__ void count_chunk(const int32_t* __restrict__ route_bi
 
 // stable scatter of this CTA's chunk; wbase[w][b] = first output position of warp w's routes of bin b
 __device__ __forceinline__ void scatter_chunk(const int32_t* __restrict__ route_bin, int routes, int bins,
-                                              int chunk_begin, int* wbase, int32_t* __restrict__ route_idx) {
+                                              int chunk_begin, int warp_routes, int* wbase, int32_t* __restrict__ route_idx) {
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-    const int begin = chunk_begin + warp * kWarpRoutes;
-    const int end = min(begin + kWarpRoutes, routes);
+    const int begin = min(chunk_begin + warp * warp_routes, routes);
+    const int end = min(begin + warp_routes, routes);
     int* mine = wbase + warp * bins;
     for (int r0 = begin; r0 < end; r0 += 32) {
         int r = r0 + lane;
@@ -75,7 +75,7 @@ csr_small_kernel(const int32_t* __restrict__ route_bin, int routes, int bins, in
     extern __shared__ int sm[];
     int* whist = sm;                   // [kWarps][bins]
     int* binbase = sm + kWarps * bins; // [bins + 1]
-    count_chunk(route_bin, routes, bins, 0, whist, bad_flag);
+    count_chunk(route_bin, routes, bins, 0, kWarpRoutes, whist, bad_flag);
     // per-bin totals, then an exclusive scan over bins by warp 0
     for (int b = threadIdx.x; b < bins; b += kThreads) {
         int tot = 0;
@@ -113,15 +113,15 @@ csr_small_kernel(const int32_t* __restrict__ route_bin, int routes, int bins, in
         }
     }
     __syncthreads();
-    scatter_chunk(route_bin, routes, bins, 0, whist, route_idx);
+    scatter_chunk(route_bin, routes, bins, 0, kWarpRoutes, whist, route_idx);
 }
 
 // pass 1: per-(CTA, bin) counts -> cta_hist[cta][bin]
 __global__ void __launch_bounds__(kThreads)
-csr_count_kernel(const int32_t* __restrict__ route_bin, int routes, int bins, int32_t* __restrict__ cta_hist,
+csr_count_kernel(const int32_t* __restrict__ route_bin, int routes, int bins, int chunk, int32_t* __restrict__ cta_hist,
                  int32_t* bad_flag) {
     extern __shared__ int sm[];
-    count_chunk(route_bin, routes, bins, blockIdx.x * kChunkRoutes, sm, bad_flag);
+    count_chunk(route_bin, routes, bins, blockIdx.x * chunk, chunk / kWarps, sm, bad_flag);
     for (int b = threadIdx.x; b < bins; b += kThreads) {
         int tot = 0;
         for (int w = 0; w < kWarps; w++) tot += sm[w * bins + b];
@@ -173,10 +173,10 @@ csr_scan_kernel(int32_t* __restrict__ cta_hist, int nctas, int bins, int32_t* __
 
 // pass 3: recount per warp, then ranked scatter from the CTA's bases
 __global__ void __launch_bounds__(kThreads)
-csr_scatter_kernel(const int32_t* __restrict__ route_bin, int routes, int bins,
+csr_scatter_kernel(const int32_t* __restrict__ route_bin, int routes, int bins, int chunk,
                    const int32_t* __restrict__ cta_base, int32_t* __restrict__ route_idx, int32_t* scratch_flag) {
     extern __shared__ int sm[];
-    count_chunk(route_bin, routes, bins, blockIdx.x * kChunkRoutes, sm, scratch_flag);
+    count_chunk(route_bin, routes, bins, blockIdx.x * chunk, chunk / kWarps, sm, scratch_flag);
     for (int b = threadIdx.x; b < bins; b += kThreads) {
         int run = cta_base[(size_t)blockIdx.x * bins + b];
         for (int w = 0; w < kWarps; w++) {
@@ -186,7 +186,7 @@ csr_scatter_kernel(const int32_t* __restrict__ route_bin, int routes, int bins,
         }
     }
     __syncthreads();
-    scatter_chunk(route_bin, routes, bins, blockIdx.x * kChunkRoutes, sm, route_idx);
+    scatter_chunk(route_bin, routes, bins, blockIdx.x * chunk, chunk / kWarps, sm, route_idx);
 }
 
 // dense expert ids of one layer -> slot ids through the residency table
@@ -235,13 +235,16 @@ std::mutex g_noalloc_mu;
 
 }  // namespace
 
+// the adapter's builds cut the routes into chunks of kFineChunk per CTA (more CTAs in flight for the two passes
+// that read every route); the allocation-free entry keeps chunks of kChunkRoutes, which its fixed scratch is sized for
+constexpr int kFineChunk = 512;
 size_t csr_scratch_ints(int routes, int bins) {
-    size_t nctas = ((size_t)routes + kChunkRoutes - 1) / kChunkRoutes;
+    size_t nctas = ((size_t)routes + kFineChunk - 1) / kFineChunk;
     return (nctas ? nctas : 1) * (size_t)bins;
 }
 
 int launch_csr_build(const int32_t* route_bin, int routes, int bins, int32_t* seg, int32_t* route_idx,
-                     int32_t* scratch, int32_t* bad_flag, const Ctx& c) {
+                     int32_t* scratch, int32_t* bad_flag, const Ctx& c, bool coarse) {
     if (routes <= kChunkRoutes) {
         size_t smem = ((size_t)kWarps * bins + bins + 1) * sizeof(int);
         c.begin(K_CSR);
@@ -249,13 +252,14 @@ int launch_csr_build(const int32_t* route_bin, int routes, int bins, int32_t* se
         c.end();
         return 1;
     }
-    int nctas = (routes + kChunkRoutes - 1) / kChunkRoutes;
+    const int chunk = coarse ? kChunkRoutes : kFineChunk;
+    int nctas = (routes + chunk - 1) / chunk;
     size_t smem = (size_t)kWarps * bins * sizeof(int);
     c.begin(K_CSR);
-    csr_count_kernel<<<nctas, kThreads, smem, c.s>>>(route_bin, routes, bins, scratch, bad_flag);
+    csr_count_kernel<<<nctas, kThreads, smem, c.s>>>(route_bin, routes, bins, chunk, scratch, bad_flag);
     int scan_threads = ((bins + 31) / 32) * 32;
     csr_scan_kernel<<<1, scan_threads, 0, c.s>>>(scratch, nctas, bins, seg);
-    csr_scatter_kernel<<<nctas, kThreads, smem, c.s>>>(route_bin, routes, bins, scratch, route_idx, bad_flag);
+    csr_scatter_kernel<<<nctas, kThreads, smem, c.s>>>(route_bin, routes, bins, chunk, scratch, route_idx, bad_flag);
     c.end();
     return 3;
 }
@@ -307,7 +311,7 @@ extern "C" FTM_API int ftm_csr_build_noalloc(const int32_t* route_slot, int32_t 
     int32_t* flag = scratch + kNoAllocScratchInts;  // the last 256 bytes of the array
     if (cudaMemsetAsync(flag, 0, sizeof(int32_t), s) != cudaSuccess) return FTM_ERR_CUDA;
     Ctx c{s, nullptr};
-    launch_csr_build(route_slot, routes, bins, seg_out, route_idx_out, scratch, flag, c);
+    launch_csr_build(route_slot, routes, bins, seg_out, route_idx_out, scratch, flag, c, /*coarse=*/true);
     if (bad_out && cudaMemcpyAsync(bad_out, flag, sizeof(int32_t), cudaMemcpyDeviceToDevice, s) != cudaSuccess)
         return FTM_ERR_CUDA;
     return cudaGetLastError() == cudaSuccess ? FTM_OK : FTM_ERR_CUDA;
