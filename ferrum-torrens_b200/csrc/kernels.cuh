@@ -98,8 +98,15 @@ int launch_router_fused(const __nv_bfloat16* x, const __nv_bfloat16* gate_w, int
 // permute.cu
 // scratch: cta_hist needs csr_scratch_ints(routes, bins) int32 entries
 size_t csr_scratch_ints(int routes, int bins);
+// optional second output of the permutation build: every bin cut into passes of at most `group` routes
+struct CsrGroups {
+    const int32_t* slot_of_bin = nullptr;   // bin -> slot (null: the bin is the slot); bins of slots outside [0, slots) are skipped
+    int slots = 0, group = 0;
+    int4* groups = nullptr;
+    int32_t* n_groups = nullptr;
+};
 int launch_csr_build(const int32_t* route_bin, int routes, int bins, int32_t* seg, int32_t* route_idx,
-                     int32_t* scratch, int32_t* bad_flag, const Ctx& c, bool coarse = false);
+                     int32_t* scratch, int32_t* bad_flag, const Ctx& c, bool coarse = false, const CsrGroups* groups = nullptr);
 int launch_slot_rewrite(const void* expert_ids, int ids_dtype, int routes, int layer, int experts,
                         const int32_t* slot_for_id, int n_ids, int32_t* route_slot, int32_t* route_expert,
                         int32_t* bad_flag, const Ctx& c);

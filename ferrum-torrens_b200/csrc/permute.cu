@@ -130,8 +130,11 @@ csr_count_kernel(const int32_t* __restrict__ route_bin, int routes, int bins, in
 }
 
 // pass 2 (one CTA): cta_hist[c][b] <- seg[b] + sum of counts of CTAs before c; writes seg
+// With `g.groups` set the same CTA also cuts every bin into passes of at most g.group routes (what
+// groups_from_csr_kernel does in a launch of its own): (slot, first sorted row, rows, 0) per pass, bins whose slot
+// is not resident skipped, the number of passes in *g.n_groups.
 __global__ void __launch_bounds__(kMaxBins)
-csr_scan_kernel(int32_t* __restrict__ cta_hist, int nctas, int bins, int32_t* __restrict__ seg) {
+csr_scan_kernel(int32_t* __restrict__ cta_hist, int nctas, int bins, int32_t* __restrict__ seg, CsrGroups g) {
     __shared__ int wsum[32];
     const int b = threadIdx.x;
     int total = 0;
@@ -169,6 +172,37 @@ csr_scan_kernel(int32_t* __restrict__ cta_hist, int nctas, int bins, int32_t* __
             run += v;
         }
     }
+    if (!g.groups) return;
+    int cnt = 0, slot = -1;
+    if (b < bins) {
+        cnt = total;
+        slot = g.slot_of_bin ? g.slot_of_bin[b] : b;
+        if (slot < 0 || slot >= g.slots) cnt = 0;
+    }
+    const int ng = (cnt + g.group - 1) / g.group;
+    int gi = ng;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        int n = __shfl_up_sync(0xffffffffu, gi, o);
+        if (lane >= o) gi += n;
+    }
+    __syncthreads();     // wsum is reused
+    if (lane == 31) wsum[warp] = gi;
+    __syncthreads();
+    if (warp == 0) {
+        int v = (lane < (int)(blockDim.x / 32)) ? wsum[lane] : 0;
+        int j = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            int n = __shfl_up_sync(0xffffffffu, j, o);
+            if (lane >= o) j += n;
+        }
+        wsum[lane] = j - v;
+        if (lane == 31) *g.n_groups = j;
+    }
+    __syncthreads();
+    const int base = wsum[warp] + gi - ng;
+    for (int q = 0; q < ng; q++) g.groups[base + q] = make_int4(slot, excl + q * g.group, min(g.group, cnt - q * g.group), 0);
 }
 
 // pass 3: recount per warp, then ranked scatter from the CTA's bases
@@ -244,12 +278,15 @@ size_t csr_scratch_ints(int routes, int bins) {
 }
 
 int launch_csr_build(const int32_t* route_bin, int routes, int bins, int32_t* seg, int32_t* route_idx,
-                     int32_t* scratch, int32_t* bad_flag, const Ctx& c, bool coarse) {
+                     int32_t* scratch, int32_t* bad_flag, const Ctx& c, bool coarse, const CsrGroups* groups) {
     if (routes <= kChunkRoutes) {
         size_t smem = ((size_t)kWarps * bins + bins + 1) * sizeof(int);
         c.begin(K_CSR);
         csr_small_kernel<<<1, kThreads, smem, c.s>>>(route_bin, routes, bins, seg, route_idx, bad_flag);
         c.end();
+        if (groups)
+            return 1 + launch_groups_from_csr(seg, bins, groups->slot_of_bin, groups->slots, groups->group, groups->groups,
+                                              groups->n_groups, c);
         return 1;
     }
     const int chunk = coarse ? kChunkRoutes : kFineChunk;
@@ -258,7 +295,7 @@ int launch_csr_build(const int32_t* route_bin, int routes, int bins, int32_t* se
     c.begin(K_CSR);
     csr_count_kernel<<<nctas, kThreads, smem, c.s>>>(route_bin, routes, bins, chunk, scratch, bad_flag);
     int scan_threads = ((bins + 31) / 32) * 32;
-    csr_scan_kernel<<<1, scan_threads, 0, c.s>>>(scratch, nctas, bins, seg);
+    csr_scan_kernel<<<1, scan_threads, 0, c.s>>>(scratch, nctas, bins, seg, groups ? *groups : CsrGroups{});
     csr_scatter_kernel<<<nctas, kThreads, smem, c.s>>>(route_bin, routes, bins, chunk, scratch, route_idx, bad_flag);
     c.end();
     return 3;

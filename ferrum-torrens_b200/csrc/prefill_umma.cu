@@ -850,9 +850,9 @@ int launch_prefill_umma(const BankView& b, const void* x, int x_dtype, const Dec
         route_slot = rt.route_slot_in;
         nbins = b.slots;
     }
-    launches += launch_csr_build(bins_of_route, routes, nbins, sc.seg, sc.route_idx, sc.csr_scratch, sc.csr_flag, c);
-    // 2. passes of <= 128 sorted rows per expert
-    launches += launch_groups_from_csr(sc.seg, nbins, slot_of_bin, b.slots, kTileTok, sc.groups, sc.n_groups, c);
+    // 1. + 2. buckets and, from the same scan, passes of <= 128 sorted rows per expert
+    const CsrGroups cg{slot_of_bin, b.slots, kTileTok, sc.groups, sc.n_groups};
+    launches += launch_csr_build(bins_of_route, routes, nbins, sc.seg, sc.route_idx, sc.csr_scratch, sc.csr_flag, c, false, &cg);
     // 3. sorted, scaled f16 activations
     c.begin(K_PERMUTE_ACT);
     prefill_gather_kernel<<<(routes + 7) / 8, 256, 0, c.s>>>(x, x_dtype, sc.route_idx, sc.seg + nbins, top_k, b.hidden, sc.xg,
