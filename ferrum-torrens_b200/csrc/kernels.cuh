@@ -105,8 +105,20 @@ struct CsrGroups {
     int4* groups = nullptr;
     int32_t* n_groups = nullptr;
 };
+// optional first step of the permutation build: dense expert ids of a layer -> slots (route_slot) and bins (route_expert:
+// the expert id, -1 when not resident); the build then buckets by route_expert
+struct SlotRewrite {
+    const void* expert_ids = nullptr;
+    int ids_dtype = 0, layer = 0, experts = 0;
+    const int32_t* slot_for_id = nullptr;
+    int n_ids = 0;
+    int32_t* route_slot = nullptr;
+    int32_t* route_expert = nullptr;
+    int32_t* bad_flag = nullptr;
+};
 int launch_csr_build(const int32_t* route_bin, int routes, int bins, int32_t* seg, int32_t* route_idx,
-                     int32_t* scratch, int32_t* bad_flag, const Ctx& c, bool coarse = false, const CsrGroups* groups = nullptr);
+                     int32_t* scratch, int32_t* bad_flag, const Ctx& c, bool coarse = false, const CsrGroups* groups = nullptr,
+                     const SlotRewrite* rewrite = nullptr);
 int launch_slot_rewrite(const void* expert_ids, int ids_dtype, int routes, int layer, int experts,
                         const int32_t* slot_for_id, int n_ids, int32_t* route_slot, int32_t* route_expert,
                         int32_t* bad_flag, const Ctx& c);

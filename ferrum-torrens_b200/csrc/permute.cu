@@ -26,7 +26,8 @@ constexpr int kChunkRoutes = 2048;                    // routes per CTA
 constexpr int kWarpRoutes = kChunkRoutes / kWarps;    // contiguous routes per warp
 constexpr int kMaxBins = 1024;
 
-__device__ __forceinline__ void count_chunk(const int32_t* __restrict__ route_bin, int routes, int bins,
+// (route_bin is not declared restrict: the counting kernel may have written this chunk's bins itself just before)
+__device__ __forceinline__ void count_chunk(const int32_t* route_bin, int routes, int bins,
                                             int chunk_begin, int warp_routes, int* whist /* [kWarps][bins] smem */,
                                             int32_t* bad_flag) {
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
@@ -116,11 +117,45 @@ csr_small_kernel(const int32_t* __restrict__ route_bin, int routes, int bins, in
     scatter_chunk(route_bin, routes, bins, 0, kWarpRoutes, whist, route_idx);
 }
 
-// pass 1: per-(CTA, bin) counts -> cta_hist[cta][bin]
+// dense expert id of route r -> slot through the residency table; writes the route's slot and its bin (the expert id,
+// -1 when the expert is not resident)
+__device__ __forceinline__ void rewrite_route(const SlotRewrite& w, int r) {
+    // ids arrive as i32, i64 or f32 (src/infrastructure/cuda_moe.rs:67-86 accepts all three)
+    long long e;
+    if (w.ids_dtype == 3)
+        e = reinterpret_cast<const long long*>(w.expert_ids)[r];
+    else if (w.ids_dtype == 1)
+        e = (long long)reinterpret_cast<const float*>(w.expert_ids)[r];
+    else
+        e = (long long)reinterpret_cast<const int32_t*>(w.expert_ids)[r];
+    int slot = -1;
+    if (e >= 0 && e < w.experts) {
+        long long id = (long long)w.layer * w.experts + e;
+        if (id < w.n_ids) slot = w.slot_for_id[id];
+    } else {
+        atomicExch(w.bad_flag, 1);
+    }
+    w.route_slot[r] = slot;
+    if (w.route_expert) w.route_expert[r] = (slot >= 0) ? (int32_t)e : -1;
+}
+
+// dense expert ids of one layer -> slot ids through the residency table
+__global__ void slot_rewrite_kernel(SlotRewrite w, int routes) {
+    int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r < routes) rewrite_route(w, r);
+}
+
+// pass 1: per-(CTA, bin) counts -> cta_hist[cta][bin].  With `w.expert_ids` set the CTA first maps its chunk's dense
+// expert ids to slots and bins (what slot_rewrite_kernel does in a launch of its own): route_bin is then w.route_expert.
 __global__ void __launch_bounds__(kThreads)
-csr_count_kernel(const int32_t* __restrict__ route_bin, int routes, int bins, int chunk, int32_t* __restrict__ cta_hist,
-                 int32_t* bad_flag) {
+csr_count_kernel(const int32_t* route_bin, int routes, int bins, int chunk, int32_t* __restrict__ cta_hist,
+                 int32_t* bad_flag, SlotRewrite w) {
     extern __shared__ int sm[];
+    if (w.expert_ids) {
+        const int begin = blockIdx.x * chunk, end = min(begin + chunk, routes);
+        for (int r = begin + threadIdx.x; r < end; r += kThreads) rewrite_route(w, r);
+        __syncthreads();     // the chunk's bins are read back by this CTA only
+    }
     count_chunk(route_bin, routes, bins, blockIdx.x * chunk, chunk / kWarps, sm, bad_flag);
     for (int b = threadIdx.x; b < bins; b += kThreads) {
         int tot = 0;
@@ -223,32 +258,6 @@ csr_scatter_kernel(const int32_t* __restrict__ route_bin, int routes, int bins, 
     scatter_chunk(route_bin, routes, bins, blockIdx.x * chunk, chunk / kWarps, sm, route_idx);
 }
 
-// dense expert ids of one layer -> slot ids through the residency table
-__global__ void slot_rewrite_kernel(const void* __restrict__ expert_ids, int ids_dtype, int routes, int layer,
-                                    int experts, const int32_t* __restrict__ slot_for_id, int n_ids,
-                                    int32_t* __restrict__ route_slot, int32_t* __restrict__ route_expert,
-                                    int32_t* bad_flag) {
-    int r = blockIdx.x * blockDim.x + threadIdx.x;
-    if (r >= routes) return;
-    // ids arrive as i32, i64 or f32 (src/infrastructure/cuda_moe.rs:67-86 accepts all three)
-    long long e;
-    if (ids_dtype == 3)
-        e = reinterpret_cast<const long long*>(expert_ids)[r];
-    else if (ids_dtype == 1)
-        e = (long long)reinterpret_cast<const float*>(expert_ids)[r];
-    else
-        e = (long long)reinterpret_cast<const int32_t*>(expert_ids)[r];
-    int slot = -1;
-    if (e >= 0 && e < experts) {
-        long long id = (long long)layer * experts + e;
-        if (id < n_ids) slot = slot_for_id[id];
-    } else {
-        atomicExch(bad_flag, 1);
-    }
-    route_slot[r] = slot;
-    if (route_expert) route_expert[r] = (slot >= 0) ? (int32_t)e : -1;
-}
-
 }  // namespace
 
 // ---- permutation build without any allocation ------------------------------------------------
@@ -278,22 +287,31 @@ size_t csr_scratch_ints(int routes, int bins) {
 }
 
 int launch_csr_build(const int32_t* route_bin, int routes, int bins, int32_t* seg, int32_t* route_idx,
-                     int32_t* scratch, int32_t* bad_flag, const Ctx& c, bool coarse, const CsrGroups* groups) {
+                     int32_t* scratch, int32_t* bad_flag, const Ctx& c, bool coarse, const CsrGroups* groups,
+                     const SlotRewrite* rewrite) {
     if (routes <= kChunkRoutes) {
+        int pre = 0;
+        if (rewrite) {
+            c.begin(K_SLOT_REWRITE);
+            slot_rewrite_kernel<<<(routes + 255) / 256, 256, 0, c.s>>>(*rewrite, routes);
+            c.end();
+            pre = 1;
+        }
         size_t smem = ((size_t)kWarps * bins + bins + 1) * sizeof(int);
         c.begin(K_CSR);
         csr_small_kernel<<<1, kThreads, smem, c.s>>>(route_bin, routes, bins, seg, route_idx, bad_flag);
         c.end();
         if (groups)
-            return 1 + launch_groups_from_csr(seg, bins, groups->slot_of_bin, groups->slots, groups->group, groups->groups,
+            return pre + 1 + launch_groups_from_csr(seg, bins, groups->slot_of_bin, groups->slots, groups->group, groups->groups,
                                               groups->n_groups, c);
-        return 1;
+        return pre + 1;
     }
     const int chunk = coarse ? kChunkRoutes : kFineChunk;
     int nctas = (routes + chunk - 1) / chunk;
     size_t smem = (size_t)kWarps * bins * sizeof(int);
     c.begin(K_CSR);
-    csr_count_kernel<<<nctas, kThreads, smem, c.s>>>(route_bin, routes, bins, chunk, scratch, bad_flag);
+    csr_count_kernel<<<nctas, kThreads, smem, c.s>>>(route_bin, routes, bins, chunk, scratch, bad_flag,
+                                                     rewrite ? *rewrite : SlotRewrite{});
     int scan_threads = ((bins + 31) / 32) * 32;
     csr_scan_kernel<<<1, scan_threads, 0, c.s>>>(scratch, nctas, bins, seg, groups ? *groups : CsrGroups{});
     csr_scatter_kernel<<<nctas, kThreads, smem, c.s>>>(route_bin, routes, bins, chunk, scratch, route_idx, bad_flag);
@@ -305,9 +323,9 @@ int launch_slot_rewrite(const void* expert_ids, int ids_dtype, int routes, int l
                         const int32_t* slot_for_id, int n_ids, int32_t* route_slot, int32_t* route_expert,
                         int32_t* bad_flag, const Ctx& c) {
     int threads = 256;
+    const SlotRewrite w{expert_ids, ids_dtype, layer, experts, slot_for_id, n_ids, route_slot, route_expert, bad_flag};
     c.begin(K_SLOT_REWRITE);
-    slot_rewrite_kernel<<<(routes + threads - 1) / threads, threads, 0, c.s>>>(
-        expert_ids, ids_dtype, routes, layer, experts, slot_for_id, n_ids, route_slot, route_expert, bad_flag);
+    slot_rewrite_kernel<<<(routes + threads - 1) / threads, threads, 0, c.s>>>(w, routes);
     c.end();
     return 1;
 }

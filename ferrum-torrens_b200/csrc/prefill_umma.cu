@@ -838,9 +838,10 @@ int launch_prefill_umma(const BankView& b, const void* x, int x_dtype, const Dec
     const int32_t* slot_of_bin = nullptr;
     const int32_t* route_slot;
     int nbins;
+    SlotRewrite rewrite;      // the id -> slot mapping runs inside the permutation build's first pass
     if (rt.expert_ids) {
-        launches += launch_slot_rewrite(rt.expert_ids, rt.ids_dtype, routes, rt.layer, rt.experts, rt.slot_for_id, rt.n_ids,
-                                        rt.route_slot_out, sc.route_bin, rt.bad_flag, c);
+        rewrite = SlotRewrite{rt.expert_ids, rt.ids_dtype, rt.layer, rt.experts, rt.slot_for_id, rt.n_ids, rt.route_slot_out,
+                              sc.route_bin, rt.bad_flag};
         bins_of_route = sc.route_bin;
         slot_of_bin = rt.slot_for_id + (size_t)rt.layer * rt.experts;
         route_slot = rt.route_slot_out;
@@ -852,7 +853,8 @@ int launch_prefill_umma(const BankView& b, const void* x, int x_dtype, const Dec
     }
     // 1. + 2. buckets and, from the same scan, passes of <= 128 sorted rows per expert
     const CsrGroups cg{slot_of_bin, b.slots, kTileTok, sc.groups, sc.n_groups};
-    launches += launch_csr_build(bins_of_route, routes, nbins, sc.seg, sc.route_idx, sc.csr_scratch, sc.csr_flag, c, false, &cg);
+    launches += launch_csr_build(bins_of_route, routes, nbins, sc.seg, sc.route_idx, sc.csr_scratch, sc.csr_flag, c, false, &cg,
+                                 rt.expert_ids ? &rewrite : nullptr);
     // 3. sorted, scaled f16 activations
     c.begin(K_PERMUTE_ACT);
     prefill_gather_kernel<<<(routes + 7) / 8, 256, 0, c.s>>>(x, x_dtype, sc.route_idx, sc.seg + nbins, top_k, b.hidden, sc.xg,
