@@ -104,6 +104,7 @@ struct CsrGroups {
     int slots = 0, group = 0;
     int4* groups = nullptr;
     int32_t* n_groups = nullptr;
+    int32_t* pos_of_route = nullptr;        // optional: route -> sorted position, written by the scatter pass
 };
 // optional first step of the permutation build: dense expert ids of a layer -> slots (route_slot) and bins (route_expert:
 // the expert id, -1 when not resident); the build then buckets by route_expert

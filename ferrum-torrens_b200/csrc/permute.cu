@@ -48,7 +48,8 @@ __device__ __forceinline__ void count_chunk(const int32_t* route_bin, int routes
 
 // stable scatter of this CTA's chunk; wbase[w][b] = first output position of warp w's routes of bin b
 __device__ __forceinline__ void scatter_chunk(const int32_t* __restrict__ route_bin, int routes, int bins,
-                                              int chunk_begin, int warp_routes, int* wbase, int32_t* __restrict__ route_idx) {
+                                              int chunk_begin, int warp_routes, int* wbase, int32_t* __restrict__ route_idx,
+                                              int32_t* __restrict__ pos_of_route) {
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int begin = min(chunk_begin + warp * warp_routes, routes);
     const int end = min(begin + warp_routes, routes);
@@ -62,6 +63,7 @@ __device__ __forceinline__ void scatter_chunk(const int32_t* __restrict__ route_
             int rank = __popc(peers & ((1u << lane) - 1u));
             int pos = mine[b] + rank;
             route_idx[pos] = r;
+            if (pos_of_route) pos_of_route[r] = pos;      // the inverse, for callers that walk the routes in their own order
         }
         __syncwarp();
         if (ok && lane == 31 - __clz(peers)) mine[b] += __popc(peers);
@@ -72,7 +74,7 @@ __device__ __forceinline__ void scatter_chunk(const int32_t* __restrict__ route_
 // single-CTA build: routes <= kChunkRoutes
 __global__ void __launch_bounds__(kThreads)
 csr_small_kernel(const int32_t* __restrict__ route_bin, int routes, int bins, int32_t* __restrict__ seg,
-                 int32_t* __restrict__ route_idx, int32_t* bad_flag) {
+                 int32_t* __restrict__ route_idx, int32_t* bad_flag, int32_t* __restrict__ pos_of_route) {
     extern __shared__ int sm[];
     int* whist = sm;                   // [kWarps][bins]
     int* binbase = sm + kWarps * bins; // [bins + 1]
@@ -114,7 +116,7 @@ csr_small_kernel(const int32_t* __restrict__ route_bin, int routes, int bins, in
         }
     }
     __syncthreads();
-    scatter_chunk(route_bin, routes, bins, 0, kWarpRoutes, whist, route_idx);
+    scatter_chunk(route_bin, routes, bins, 0, kWarpRoutes, whist, route_idx, pos_of_route);
 }
 
 // dense expert id of route r -> slot through the residency table; writes the route's slot and its bin (the expert id,
@@ -243,7 +245,8 @@ csr_scan_kernel(int32_t* __restrict__ cta_hist, int nctas, int bins, int32_t* __
 // pass 3: recount per warp, then ranked scatter from the CTA's bases
 __global__ void __launch_bounds__(kThreads)
 csr_scatter_kernel(const int32_t* __restrict__ route_bin, int routes, int bins, int chunk,
-                   const int32_t* __restrict__ cta_base, int32_t* __restrict__ route_idx, int32_t* scratch_flag) {
+                   const int32_t* __restrict__ cta_base, int32_t* __restrict__ route_idx, int32_t* scratch_flag,
+                   int32_t* __restrict__ pos_of_route) {
     extern __shared__ int sm[];
     count_chunk(route_bin, routes, bins, blockIdx.x * chunk, chunk / kWarps, sm, scratch_flag);
     for (int b = threadIdx.x; b < bins; b += kThreads) {
@@ -255,7 +258,7 @@ csr_scatter_kernel(const int32_t* __restrict__ route_bin, int routes, int bins, 
         }
     }
     __syncthreads();
-    scatter_chunk(route_bin, routes, bins, blockIdx.x * chunk, chunk / kWarps, sm, route_idx);
+    scatter_chunk(route_bin, routes, bins, blockIdx.x * chunk, chunk / kWarps, sm, route_idx, pos_of_route);
 }
 
 }  // namespace
@@ -299,7 +302,8 @@ int launch_csr_build(const int32_t* route_bin, int routes, int bins, int32_t* se
         }
         size_t smem = ((size_t)kWarps * bins + bins + 1) * sizeof(int);
         c.begin(K_CSR);
-        csr_small_kernel<<<1, kThreads, smem, c.s>>>(route_bin, routes, bins, seg, route_idx, bad_flag);
+        csr_small_kernel<<<1, kThreads, smem, c.s>>>(route_bin, routes, bins, seg, route_idx, bad_flag,
+                                                     groups ? groups->pos_of_route : nullptr);
         c.end();
         if (groups)
             return pre + 1 + launch_groups_from_csr(seg, bins, groups->slot_of_bin, groups->slots, groups->group, groups->groups,
@@ -314,7 +318,8 @@ int launch_csr_build(const int32_t* route_bin, int routes, int bins, int32_t* se
                                                      rewrite ? *rewrite : SlotRewrite{});
     int scan_threads = ((bins + 31) / 32) * 32;
     csr_scan_kernel<<<1, scan_threads, 0, c.s>>>(scratch, nctas, bins, seg, groups ? *groups : CsrGroups{});
-    csr_scatter_kernel<<<nctas, kThreads, smem, c.s>>>(route_bin, routes, bins, chunk, scratch, route_idx, bad_flag);
+    csr_scatter_kernel<<<nctas, kThreads, smem, c.s>>>(route_bin, routes, bins, chunk, scratch, route_idx, bad_flag,
+                                                       groups ? groups->pos_of_route : nullptr);
     c.end();
     return 3;
 }

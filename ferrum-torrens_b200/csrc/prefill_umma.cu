@@ -639,12 +639,6 @@ bool make_act_map(CUtensorMap* map, const void* base, size_t rows, int K, int bo
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-__global__ void prefill_invert_kernel(const int32_t* __restrict__ route_idx, const int32_t* __restrict__ n_sorted,
-                                      int32_t* __restrict__ pos_of_route) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < *n_sorted) pos_of_route[route_idx[i]] = i;
-}
-
 // Expert-parallel owner, one thread per received row i: the address of its output row in the source rank's back
 // buffer goes into row_dest at the row's sorted position, where the down GEMM's epilogue finds it.  A row whose
 // expert is not resident takes no part in the GEMM: its output row is zero-filled here.
@@ -852,7 +846,7 @@ int launch_prefill_umma(const BankView& b, const void* x, int x_dtype, const Dec
         nbins = b.slots;
     }
     // 1. + 2. buckets and, from the same scan, passes of <= 128 sorted rows per expert
-    const CsrGroups cg{slot_of_bin, b.slots, kTileTok, sc.groups, sc.n_groups};
+    const CsrGroups cg{slot_of_bin, b.slots, kTileTok, sc.groups, sc.n_groups, sc.pos_of_route};
     launches += launch_csr_build(bins_of_route, routes, nbins, sc.seg, sc.route_idx, sc.csr_scratch, sc.csr_flag, c, false, &cg,
                                  rt.expert_ids ? &rewrite : nullptr);
     // 3. sorted, scaled f16 activations
@@ -891,11 +885,10 @@ int launch_prefill_umma(const BankView& b, const void* x, int x_dtype, const Dec
         // themselves would have taken
         uint64_t* const row_dest = reinterpret_cast<uint64_t*>(sc.y);
         c.begin(K_EP_COMBINE);
-        prefill_invert_kernel<<<(routes + 255) / 256, 256, 0, c.s>>>(sc.route_idx, sc.seg + nbins, sc.pos_of_route);
         ep_row_dest_kernel<<<(routes + 127) / 128, 128, 0, c.s>>>(sc.pos_of_route, route_slot, routes, b.hidden, ret->world, ret->rank,
                                                              ret->counts_all, ret->peer_back, ret->capacity, row_dest, sc.err);
         c.end();
-        launches += 2;
+        launches += 1;
         a.row_dest = row_dest;
         a.y = nullptr;
         a.y_f32 = 0;
@@ -913,14 +906,13 @@ int launch_prefill_umma(const BankView& b, const void* x, int x_dtype, const Dec
     // them to the return kernel as they are.
     if (join) cudaStreamWaitEvent(c.s, join, 0);
     c.begin(K_SUM_ROUTES);
-    prefill_invert_kernel<<<(routes + 255) / 256, 256, 0, c.s>>>(sc.route_idx, sc.seg + nbins, sc.pos_of_route);
     if (out) {
         dim3 grid(tokens, (b.hidden / 4 + 127) / 128);
         prefill_combine_kernel<<<grid, 128, 0, c.s>>>(sc.y, out_dtype == 1, sc.pos_of_route, route_slot, b.slots, top_k, b.hidden, shared,
                                                       se_gate, out, out_dtype);
     }
     c.end();
-    return launches + (out ? 2 : 1);
+    return launches + (out ? 1 : 0);
 }
 
 // The owner's step on rows that arrived sorted by expert as scaled f16 (xg, row_scale, route_weight: one entry per
