@@ -224,21 +224,22 @@ __global__ void __launch_bounds__(kDgWarps * 32, 2) dense_gemv_kernel(DenseArgs 
 
 // ---- the same GEMV fed by TMA ------------------------------------------------------------------
 // The register-streaming kernel above keeps few bytes in flight per SM for a bank whose k-word rows lie
-// N * 4 bytes apart, and reaches a third of the HBM rate.  Here a CTA owns 448 consecutive rows and one half
-// of K, and a producer warp brings, per stage of sixteen k-words, two boxes of [16 k-words x 232 rows] packed
-// words and two boxes of [8 blocks x 224 rows] block scales into a ring of shared-memory stages (tiled TMA,
-// one mbarrier per stage: four copy instructions per 33 KB; bulk copies of single 2 KB runs spent their time
+// N * 4 bytes apart, and reaches a third of the HBM rate.  Here a CTA owns 672 consecutive rows and one half
+// of K, and a producer warp brings, per stage of sixteen k-words, three boxes of [16 k-words x 232 rows] packed
+// words and three boxes of [8 blocks x 224 rows] block scales into a ring of shared-memory stages (tiled TMA,
+// one mbarrier per stage: six copy instructions per 50 KB; bulk copies of single 2 KB runs spent their time
 // on the per-copy cost).  The 232-row box over-fetches eight rows so that its rows sit at a pitch of 928
-// bytes, which puts the four k-words a quad reads into different banks.  Fourteen consumer warps of 32 rows
+// bytes, which puts the four k-words a quad reads into different banks.  Twenty-one consumer warps of 32 rows
 // each read their fragments from there: the same lane -> (rows, k-word) map, the same conversions and MMAs
 // as above.  The two K halves of a row meet in `c` by atomic add, as above (two partial sums commute).
 constexpr int kTmBoxRows = 232;              // rows a weight box fetches
 constexpr int kTmUseRows = 224;              // rows of it that are used: seven groups of 32
-constexpr int kTmBoxes = 2;
+constexpr int kTmBoxes = 3;
 constexpr int kTmTileRows = kTmBoxes * kTmUseRows;
-constexpr int kTmWarps = kTmTileRows / 32;   // 14 consumer warps
+constexpr int kTmWarps = kTmTileRows / 32;   // 21 consumer warps (the lm_head's 248 320 rows are 370 tiles: with the two
+                                             // K halves 740 items, five for each of 148 CTAs)
 constexpr int kTmKw = 16;                    // k-words per stage: four MMA steps
-constexpr int kTmStages = 4;
+constexpr int kTmStages = 3;
 constexpr int kTmWBoxBytes = kTmKw * kTmBoxRows * 4;
 constexpr int kTmSBoxBytes = (kTmKw / 2) * kTmUseRows;
 constexpr int kTmStageBytes = kTmBoxes * (kTmWBoxBytes + kTmSBoxBytes);
@@ -310,7 +311,7 @@ dense_gemv_tma_kernel(const __grid_constant__ DenseMaps maps, DenseArgs a) {
     }
 
     // ===================== consumers: warp w owns rows 32 w .. 32 w + 31 of the tile ====================
-    // ---- the activations (as in the kernel above): consumer warp w converts tokens w, w + 14, .. while the
+    // ---- the activations (as in the kernel above): consumer warp w converts tokens w, w + 21, .. while the
     // producer already fills the ring ----
     for (int tk = warp; tk < 8 * NT; tk += kTmWarps) {
         __half* const xrow = reinterpret_cast<__half*>(xrows + (size_t)tk * rsx);
@@ -424,7 +425,7 @@ size_t tma_smem(int K) {
 template <int NT>
 void launch_tma(const DenseMaps& maps, const DenseArgs& a, int sm_count, cudaStream_t s) {
     static PerDeviceOnce once;
-    allow_dyn_smem(once, dense_gemv_tma_kernel<NT>, 210 * 1024);
+    allow_dyn_smem(once, dense_gemv_tma_kernel<NT>, 222 * 1024);
     dense_gemv_tma_kernel<NT><<<sm_count, (kTmWarps + 1) * 32, tma_smem<NT>(a.K), s>>>(maps, a);
 }
 
@@ -464,7 +465,7 @@ int launch_dense_gemv(const void* a, int a_dtype, const uint32_t* packed, const 
     // TMA wants the rows of both matrices 16-byte aligned (N % 16 for the scales) and whole stages per K half
     DenseMaps maps;
     const bool tma = N % 16 == 0 && K % 256 == 0 && N >= kTmTileRows && (reinterpret_cast<uintptr_t>(packed) & 15) == 0 &&
-                     (reinterpret_cast<uintptr_t>(scale) & 15) == 0 && tma_smem<2>(K) <= 210 * 1024 &&
+                     (reinterpret_cast<uintptr_t>(scale) & 15) == 0 && tma_smem<2>(K) <= 222 * 1024 &&
                      make_plain_map(&maps.packed, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, packed, (size_t)N, (size_t)K / 8, kTmBoxRows, kTmKw) &&
                      make_plain_map(&maps.scale, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, scale, (size_t)N, (size_t)K / 16, kTmUseRows, kTmKw / 2);
     d.splits = (tma || K % 64 == 0) ? 2 : 1;
